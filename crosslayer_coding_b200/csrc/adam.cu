@@ -1,0 +1,464 @@
+// Backward + optimizer in one pass over the parameters (sm_100a).
+//
+// The reference materialises dense gradients for every decoder and encoder matrix with autograd GEMMs and
+// then runs torch.optim.Adam/AdamW over them (clt/training/trainer.py:751-783).  With a (Batch)TopK or
+// JumpReLU code the gradients are row-sparse sums over the active (token, feature) entries, so this file
+// never writes a gradient tensor: one warp per parameter row gathers the few rows of the gradient seed
+// (decoder) or of the layer input (encoder) that touch its feature, forms the row gradient in registers,
+// and applies the Adam update to (w, m, v) in the same pass.  The decoder pass also produces
+//   * dL/da for every entry (dot of the seed row with the *old* weight row), consumed by the encoder pass,
+//   * the squared decoder norm of every feature after the update (used by the sparsity penalty next step).
+//
+// Row layout: decoder tensor s is [F, R_s, d] (feature-major), encoder is [L, F, d]; bf16 weights with
+// fp32 moments (or fp32 weights).  d must be a multiple of 8.
+#include "common.cuh"
+
+namespace clt {
+
+constexpr int kMaxLayersA = 32;
+
+struct AdamHyper {
+  float lr, beta1, beta2, eps, weight_decay;
+  float bc1, bc2;        // 1 - beta^step
+  int decoupled;         // 1: AdamW, 0: Adam (decay folded into the gradient)
+  float grad_scale;      // multiplies the gathered gradient (e.g. 2/(B*d), 1/loss_scale, clip factor)
+  unsigned int sr_seed;  // stochastic rounding seed; 0 = round to nearest
+};
+
+__device__ __forceinline__ uint32_t hash32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ __nv_bfloat16 to_bf16(float v, unsigned int seed, unsigned long long idx) {
+  if (seed == 0) return __float2bfloat16_rn(v);
+  const uint32_t u = __float_as_uint(v);
+  if ((u & 0x7F800000u) == 0x7F800000u) return __float2bfloat16_rn(v);
+  const uint32_t r = hash32(uint32_t(idx) ^ hash32(seed + uint32_t(idx >> 32))) & 0xFFFFu;
+  const uint32_t t = (u + r) & 0xFFFF0000u;
+  return __float2bfloat16_rn(__uint_as_float(t));
+}
+
+__device__ __forceinline__ void adam_update8(float (&w)[8], float (&m)[8], float (&v)[8], const float (&g)[8], const AdamHyper& h) {
+  const float step = h.lr / h.bc1;
+  const float inv_sqrt_bc2 = rsqrtf(h.bc2);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float gi = g[i];
+    if (h.decoupled) w[i] *= (1.f - h.lr * h.weight_decay);
+    else gi = fmaf(h.weight_decay, w[i], gi);
+    m[i] = fmaf(h.beta1, m[i], (1.f - h.beta1) * gi);
+    v[i] = fmaf(h.beta2, v[i], (1.f - h.beta2) * gi * gi);
+    const float denom = sqrtf(v[i]) * inv_sqrt_bc2 + h.eps;
+    w[i] -= step * (m[i] / denom);
+  }
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&o)[8]) {
+  const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { o[2 * j] = bf16_lo(u[j]); o[2 * j + 1] = bf16_hi(u[j]); }
+}
+__device__ __forceinline__ void load8f(const float* p, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void store8f(float* p, const float (&o)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(o[4], o[5], o[6], o[7]);
+}
+
+template <typename WT>
+__device__ __forceinline__ void load_w8(const WT* p, float (&o)[8]);
+template <>
+__device__ __forceinline__ void load_w8<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
+  unpack8(*reinterpret_cast<const uint4*>(p), o);
+}
+template <>
+__device__ __forceinline__ void load_w8<float>(const float* p, float (&o)[8]) { load8f(p, o); }
+
+template <typename WT>
+__device__ __forceinline__ void store_w8(WT* p, const float (&o)[8], unsigned int seed, unsigned long long idx);
+template <>
+__device__ __forceinline__ void store_w8<__nv_bfloat16>(__nv_bfloat16* p, const float (&o)[8], unsigned int seed, unsigned long long idx) {
+  __nv_bfloat16 b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) b[i] = to_bf16(o[i], seed, idx + i);
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(b);
+}
+template <>
+__device__ __forceinline__ void store_w8<float>(float* p, const float (&o)[8], unsigned int, unsigned long long) { store8f(p, o); }
+
+// ------------------------------------------------------------------ decoder rows
+struct DecAdamParams {
+  void* w[kMaxLayersA];        // tensor i: [F_pitch, rows_i, d]
+  float* m[kMaxLayersA];
+  float* v[kMaxLayersA];
+  long long row_start[kMaxLayersA + 1];  // prefix of F_pitch * rows_i over tensors
+  int rows[kMaxLayersA];
+  int ntensors;
+  int L, B, d, F_pitch, tying;
+  const int* feat_off;         // [L * F_pitch + 1] feature-major CSR
+  const int* fcsr_tok;
+  const float* fcsr_val;
+  const __nv_bfloat16* gs;     // [L, B, d] gradient seed
+  float* grad_a;               // [nnz] dL/da per CSR slot (atomicAdd; zeroed by the caller); may be null
+  const float* pen_coef;       // optional [L * F_pitch]: coefficient of w in the row gradient (sparsity penalty via norms)
+  float* norm2_out;            // optional [L * F_pitch]: sum of squares of the updated rows (atomicAdd; zeroed by caller)
+  const float* feat_offset;    // tied decoders: optional [L, F_pitch] affine applied to the activation
+  const float* feat_scale;
+  AdamHyper h;
+};
+
+// Row r of tensor i (source layer or, for per_target tying, target layer) and feature f.  The gradient of
+// that row is  grad_scale * sum over contributing (entry, target) pairs of  a' * gs[target][tok, :].
+template <typename WT>
+__global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = (blockIdx.x * 1LL * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (gridDim.x * 1LL * blockDim.x) >> 5;
+  const long long total_rows = p.row_start[p.ntensors];
+  const int nseg = (p.d + 255) / 256;
+  for (long long row = warp_global; row < total_rows; row += nwarps) {
+    int ti = 0;
+    while (ti + 1 < p.ntensors && row >= p.row_start[ti + 1]) ++ti;
+    const long long lr = row - p.row_start[ti];
+    const int R = p.rows[ti];
+    const int f = int(lr / R);
+    const int r = int(lr - 1LL * f * R);
+    WT* wrow = static_cast<WT*>(p.w[ti]) + lr * p.d;
+    float* mrow = p.m[ti] + lr * p.d;
+    float* vrow = p.v[ti] + lr * p.d;
+    // contributing (source layer, target layer) pairs of this row
+    int s_lo, s_hi, t_fixed;
+    if (p.tying == 0) { s_lo = s_hi = ti; t_fixed = ti + r; }
+    else if (p.tying == 1) { s_lo = s_hi = ti; t_fixed = -1; }       // all targets >= ti
+    else { s_lo = 0; s_hi = ti; t_fixed = ti; }                        // all sources <= ti, target ti
+    float norm2 = 0.f;
+    for (int seg = 0; seg < nseg; ++seg) {
+      const int e0 = seg * 256 + lane * 8;
+      const bool act = e0 < p.d;
+      float w[8], g[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { g[i] = 0.f; w[i] = 0.f; }
+      if (act) load_w8<WT>(wrow + e0, w);
+      for (int s = s_lo; s <= s_hi; ++s) {
+        const int col = s * p.F_pitch + f;
+        const int b = p.feat_off[col], e = p.feat_off[col + 1];
+        for (int i = b; i < e; ++i) {
+          const int tok = p.fcsr_tok[i];
+          const float a = p.fcsr_val[i];
+          const int t_begin = t_fixed >= 0 ? t_fixed : s;
+          const int t_end = t_fixed >= 0 ? t_fixed : p.L - 1;
+          float dot = 0.f;
+          for (int t = t_begin; t <= t_end; ++t) {
+            float av = a, dscale = 1.f;
+            if (p.tying != 0 && a != 0.f) {
+              if (p.feat_offset) av += p.feat_offset[1LL * t * p.F_pitch + f];
+              if (p.feat_scale) { const float sc = p.feat_scale[1LL * t * p.F_pitch + f]; av *= sc; dscale = sc; }
+            }
+            if (act) {
+              float gv[8];
+              unpack8(__ldg(reinterpret_cast<const uint4*>(p.gs + (1LL * t * p.B + tok) * p.d + e0)), gv);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                g[k] = fmaf(av, gv[k], g[k]);
+                dot = fmaf(gv[k] * dscale, w[k], dot);
+              }
+            }
+          }
+          if (p.grad_a != nullptr) {
+            dot = warp_sum(dot);
+            if (lane == 0 && dot != 0.f) atomicAdd(&p.grad_a[i], dot * p.h.grad_scale);
+          }
+        }
+      }
+      if (act) {
+        // d/dw of the norm-weighted sparsity penalty: coefficient of feature (ti, f); with per-target
+        // tying the row belongs to the norm of every source feature (s <= ti, f).
+        float pc = 0.f;
+        if (p.pen_coef) {
+          if (p.tying == 2) { for (int s = 0; s <= ti; ++s) pc += p.pen_coef[s * p.F_pitch + f]; }
+          else pc = p.pen_coef[ti * p.F_pitch + f];
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] = fmaf(pc, w[k], g[k] * p.h.grad_scale);
+        float m[8], v[8];
+        load8f(mrow + e0, m);
+        load8f(vrow + e0, v);
+        adam_update8(w, m, v, g, p.h);
+        store8f(mrow + e0, m);
+        store8f(vrow + e0, v);
+        store_w8<WT>(wrow + e0, w, p.h.sr_seed, (unsigned long long)(row * p.d + e0));
+        if (sizeof(WT) == 2) {
+          // norms are taken of the stored (rounded) weights
+          float wr[8];
+          load_w8<WT>(wrow + e0, wr);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) norm2 = fmaf(wr[k], wr[k], norm2);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) norm2 = fmaf(w[k], w[k], norm2);
+        }
+      }
+    }
+    if (p.norm2_out != nullptr) {
+      norm2 = warp_sum(norm2);
+      if (lane == 0) atomicAdd(&p.norm2_out[ti * p.F_pitch + f], norm2);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ encoder rows
+struct EncAdamParams {
+  void* w;            // [L, F_pitch, d]
+  float* m;
+  float* v;
+  void* bias;         // [L, F_pitch] (same dtype as w), updated here too
+  float* bias_m;
+  float* bias_v;
+  int L, B, d, F_pitch;
+  const int* feat_off;
+  const int* fcsr_tok;
+  const float* delta;           // [nnz] dL/d(pre-activation) per CSR slot (already scaled)
+  const __nv_bfloat16* x;       // [L, B, d] layer inputs
+  const float* dense_grad;      // optional [L, F_pitch, d] fp32 gradient added to the sparse one (e.g. pre-activation loss)
+  const float* dense_bias_grad; // optional [L, F_pitch]
+  AdamHyper h;                  // grad_scale applies to the sparse part
+};
+
+template <typename WT>
+__global__ void __launch_bounds__(256) encoder_rows_adam_kernel(const EncAdamParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = (blockIdx.x * 1LL * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (gridDim.x * 1LL * blockDim.x) >> 5;
+  const long long total_rows = 1LL * p.L * p.F_pitch;
+  const int nseg = (p.d + 255) / 256;
+  for (long long row = warp_global; row < total_rows; row += nwarps) {
+    const int l = int(row / p.F_pitch);
+    WT* wrow = static_cast<WT*>(p.w) + row * p.d;
+    float* mrow = p.m + row * p.d;
+    float* vrow = p.v + row * p.d;
+    const int b = p.feat_off[row], e = p.feat_off[row + 1];
+    for (int seg = 0; seg < nseg; ++seg) {
+      const int e0 = seg * 256 + lane * 8;
+      if (e0 >= p.d) continue;
+      float w[8], g[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) g[i] = 0.f;
+      load_w8<WT>(wrow + e0, w);
+      for (int i = b; i < e; ++i) {
+        const float dl = p.delta[i];
+        float xv[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.x + (1LL * l * p.B + p.fcsr_tok[i]) * p.d + e0)), xv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] = fmaf(dl, xv[k], g[k]);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] *= p.h.grad_scale;
+      if (p.dense_grad) {
+        float dg[8];
+        load8f(p.dense_grad + row * p.d + e0, dg);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] += dg[k];
+      }
+      float m[8], v[8];
+      load8f(mrow + e0, m);
+      load8f(vrow + e0, v);
+      adam_update8(w, m, v, g, p.h);
+      store8f(mrow + e0, m);
+      store8f(vrow + e0, v);
+      store_w8<WT>(wrow + e0, w, p.h.sr_seed, (unsigned long long)(row * p.d + e0));
+    }
+    if (lane == 0 && p.bias != nullptr) {
+      float gb = 0.f;
+      for (int i = b; i < e; ++i) gb += p.delta[i];
+      gb *= p.h.grad_scale;
+      if (p.dense_bias_grad) gb += p.dense_bias_grad[row];
+      WT* bp = static_cast<WT*>(p.bias) + row;
+      float wv = sizeof(WT) == 2 ? __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(bp)) : *reinterpret_cast<float*>(bp);
+      float mm = p.bias_m[row], vv = p.bias_v[row];
+      if (p.h.decoupled) wv *= (1.f - p.h.lr * p.h.weight_decay);
+      else gb = fmaf(p.h.weight_decay, wv, gb);
+      mm = fmaf(p.h.beta1, mm, (1.f - p.h.beta1) * gb);
+      vv = fmaf(p.h.beta2, vv, (1.f - p.h.beta2) * gb * gb);
+      wv -= (p.h.lr / p.h.bc1) * (mm / (sqrtf(vv) * rsqrtf(p.h.bc2) + p.h.eps));
+      p.bias_m[row] = mm; p.bias_v[row] = vv;
+      if (sizeof(WT) == 2) *reinterpret_cast<__nv_bfloat16*>(bp) = to_bf16(wv, p.h.sr_seed, 0x9000000000ULL + row);
+      else *reinterpret_cast<float*>(bp) = wv;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ dense Adam for the small tensors
+template <typename WT>
+__global__ void __launch_bounds__(256) dense_adam_kernel(WT* __restrict__ w, float* __restrict__ m, float* __restrict__ v,
+                                                           const float* __restrict__ grad, long long n, AdamHyper h) {
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
+    float wv = sizeof(WT) == 2 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(w + i)) : *reinterpret_cast<const float*>(w + i);
+    float g = grad[i] * h.grad_scale;
+    if (h.decoupled) wv *= (1.f - h.lr * h.weight_decay);
+    else g = fmaf(h.weight_decay, wv, g);
+    const float mm = fmaf(h.beta1, m[i], (1.f - h.beta1) * g);
+    const float vv = fmaf(h.beta2, v[i], (1.f - h.beta2) * g * g);
+    wv -= (h.lr / h.bc1) * (mm / (sqrtf(vv) * rsqrtf(h.bc2) + h.eps));
+    m[i] = mm; v[i] = vv;
+    if (sizeof(WT) == 2) *reinterpret_cast<__nv_bfloat16*>(w + i) = to_bf16(wv, h.sr_seed, 0xA000000000ULL + i);
+    else *reinterpret_cast<float*>(w + i) = wv;
+  }
+}
+
+// Squared decoder norms per feature: out[ti * F_pitch + f] = sum over the feature's rows and d of w^2.
+template <typename WT>
+__global__ void __launch_bounds__(256) decoder_norm2_kernel(const WT* __restrict__ w, float* __restrict__ out, int F, int R, int d) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const long long per_feat = 1LL * R * d;
+  for (int f = warp_global; f < F; f += nwarps) {
+    const WT* base = w + per_feat * f;
+    float s = 0.f;
+    for (long long i = lane * 8; i < per_feat; i += 256) {
+      float x[8];
+      load_w8<WT>(base + i, x);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s = fmaf(x[k], x[k], s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) out[f] = s;
+  }
+}
+
+// Norm-weighted tanh sparsity penalty on the active entries (reference clt/training/losses.py:143-195):
+//   penalty = lambda * sum tanh(c * n_f * a),  n_f = decoder norm of the entry's feature.
+// One thread per feature column walks its CSR segment and writes
+//   grad_a[i]   = lambda * c * n * sech^2(c n a)                (assignment: runs before the decoder pass)
+//   pen_coef[f] = lambda * c * sum_i a_i sech^2(c n a_i) / n    (coefficient of w in dL/dw through the norm)
+// and adds the penalty value to *penalty_out.
+__global__ void __launch_bounds__(256) sparsity_penalty_kernel(const int* __restrict__ feat_off, const float* __restrict__ fcsr_val,
+                                                                 const float* __restrict__ norm2, int ncols, float lambda, float c,
+                                                                 float* __restrict__ grad_a, float* __restrict__ pen_coef,
+                                                                 double* __restrict__ penalty_out) {
+  float local = 0.f;
+  for (int col = blockIdx.x * blockDim.x + threadIdx.x; col < ncols; col += gridDim.x * blockDim.x) {
+    const int b = feat_off[col], e = feat_off[col + 1];
+    float coef = 0.f;
+    if (e > b) {
+      const float n = sqrtf(norm2[col]);
+      float acc = 0.f;
+      for (int i = b; i < e; ++i) {
+        const float a = fcsr_val[i];
+        const float th = tanhf(c * n * a);
+        const float sech2 = 1.f - th * th;
+        local += th;
+        grad_a[i] = lambda * c * n * sech2;
+        acc = fmaf(a, sech2, acc);
+      }
+      coef = n > 0.f ? lambda * c * acc / n : 0.f;
+    }
+    pen_coef[col] = coef;
+  }
+  __shared__ float red[8];
+  local = warp_sum(local);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    if (tot != 0.f) atomicAdd(penalty_out, double(tot) * double(lambda));
+  }
+}
+
+}  // namespace clt
+
+using namespace clt;
+
+struct CltAdamHyper {
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2;
+  int decoupled;
+  float grad_scale;
+  unsigned int sr_seed;
+};
+static AdamHyper to_hyper(const CltAdamHyper& c) {
+  AdamHyper h;
+  h.lr = c.lr; h.beta1 = c.beta1; h.beta2 = c.beta2; h.eps = c.eps; h.weight_decay = c.weight_decay;
+  h.bc1 = c.bc1; h.bc2 = c.bc2; h.decoupled = c.decoupled; h.grad_scale = c.grad_scale; h.sr_seed = c.sr_seed;
+  return h;
+}
+
+struct CltDecAdamArgs {
+  void* w[32]; float* m[32]; float* v[32]; int rows[32];
+  int ntensors, L, B, d, F_pitch, tying, weights_bf16;
+  const int* feat_off; const int* fcsr_tok; const float* fcsr_val;
+  const void* gs; float* grad_a; const float* pen_coef; float* norm2_out;
+  const float* feat_offset; const float* feat_scale;
+  CltAdamHyper h;
+};
+
+extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st) {
+  if (a->d % 8 != 0 || a->ntensors > kMaxLayersA) return -1;
+  DecAdamParams p;
+  long long acc = 0;
+  for (int i = 0; i < kMaxLayersA; ++i) {
+    p.w[i] = a->w[i]; p.m[i] = a->m[i]; p.v[i] = a->v[i]; p.rows[i] = a->rows[i];
+    p.row_start[i] = acc;
+    if (i < a->ntensors) acc += 1LL * a->F_pitch * a->rows[i];
+  }
+  p.row_start[kMaxLayersA] = acc;
+  for (int i = a->ntensors; i <= kMaxLayersA; ++i) p.row_start[i] = acc;
+  p.ntensors = a->ntensors; p.L = a->L; p.B = a->B; p.d = a->d; p.F_pitch = a->F_pitch; p.tying = a->tying;
+  p.feat_off = a->feat_off; p.fcsr_tok = a->fcsr_tok; p.fcsr_val = a->fcsr_val;
+  p.gs = static_cast<const __nv_bfloat16*>(a->gs); p.grad_a = a->grad_a; p.pen_coef = a->pen_coef; p.norm2_out = a->norm2_out;
+  p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale; p.h = to_hyper(a->h);
+  if (acc == 0) return 0;
+  const int grid = num_sms * 8;
+  if (a->weights_bf16) decoder_rows_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  else decoder_rows_adam_kernel<float><<<grid, 256, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+struct CltEncAdamArgs {
+  void* w; float* m; float* v; void* bias; float* bias_m; float* bias_v;
+  int L, B, d, F_pitch, weights_bf16;
+  const int* feat_off; const int* fcsr_tok; const float* delta; const void* x;
+  const float* dense_grad; const float* dense_bias_grad;
+  CltAdamHyper h;
+};
+
+extern "C" int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaStream_t st) {
+  if (a->d % 8 != 0) return -1;
+  EncAdamParams p;
+  p.w = a->w; p.m = a->m; p.v = a->v; p.bias = a->bias; p.bias_m = a->bias_m; p.bias_v = a->bias_v;
+  p.L = a->L; p.B = a->B; p.d = a->d; p.F_pitch = a->F_pitch;
+  p.feat_off = a->feat_off; p.fcsr_tok = a->fcsr_tok; p.delta = a->delta; p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.dense_grad = a->dense_grad; p.dense_bias_grad = a->dense_bias_grad; p.h = to_hyper(a->h);
+  const int grid = num_sms * 8;
+  if (a->weights_bf16) encoder_rows_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  else encoder_rows_adam_kernel<float><<<grid, 256, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int clt_dense_adam(void* w, float* m, float* v, const float* grad, long long n, int weights_bf16, const CltAdamHyper* h,
+                              cudaStream_t st) {
+  if (n <= 0) return 0;
+  const int grid = int((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+  if (weights_bf16) dense_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(w), m, v, grad, n, to_hyper(*h));
+  else dense_adam_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(w), m, v, grad, n, to_hyper(*h));
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int clt_decoder_norm2(const void* w, float* out, int F, int R, int d, int weights_bf16, cudaStream_t st) {
+  if ((1LL * R * d) % 8 != 0) return -1;
+  const int grid = (F + 7) / 8 < 1184 ? (F + 7) / 8 : 1184;
+  if (grid == 0) return 0;
+  if (weights_bf16) decoder_norm2_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(w), out, F, R, d);
+  else decoder_norm2_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(w), out, F, R, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int clt_sparsity_penalty(const int* feat_off, const float* fcsr_val, const float* norm2, int ncols, float lambda, float c,
+                                    float* grad_a, float* pen_coef, double* penalty_out, cudaStream_t st) {
+  if (ncols <= 0) return 0;
+  const int grid = (ncols + 255) / 256 < 1184 ? (ncols + 255) / 256 : 1184;
+  sparsity_penalty_kernel<<<grid, 256, 0, st>>>(feat_off, fcsr_val, norm2, ncols, lambda, c, grad_a, pen_coef, penalty_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

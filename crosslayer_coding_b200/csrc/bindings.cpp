@@ -1,0 +1,354 @@
+// Python bindings of the sm_100a kernels.  The kernels live in .cu files that know nothing about
+// PyTorch (raw pointers + a stream); this file checks tensors and forwards to their C launchers.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <cstring>
+#include <vector>
+
+using torch::Tensor;
+using OptTensor = c10::optional<Tensor>;
+
+extern "C" {
+int clt_encoder_gemm(const void* A, const void* B, const void* bias, void* C, int L, int M, int N, int K, long long ldc,
+                     long long layer_stride_c, int* status, int num_sms, cudaStream_t stream);
+int clt_colstats(const void* x, float* mean, float* rstd, int L, int B, int F, long long ld, long long layer_stride, cudaStream_t st);
+
+struct CltExchangeArgs {
+  int world;
+  int rank;
+  void* data[8];
+  void* flags[8];
+  int slot_elems;
+  unsigned int seq;
+};
+struct CltSelectArgs {
+  const void* x;
+  const float* mean;
+  const float* rstd;
+  int L, B, F;
+  int stat_pitch;
+  long long ld, layer_stride;
+  int col_pitch;
+  int feat_offset;
+  long long full_F;
+  long long k_total;
+  unsigned int key_lo;
+  int shift;
+  unsigned int* hist;
+  long long* ctl;
+  int* ent_tok; int* ent_col; float* ent_val; long long ent_cap;
+  unsigned int* cand_key; int* cand_tok; int* cand_col; float* cand_val; long long cand_cap;
+  int* status;
+};
+int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st);
+
+struct CltCsrArgs {
+  const int* ent_tok; const int* ent_col; const float* ent_val; long long ent_cap;
+  const long long* ctl;
+  int num_tokens; int num_cols;
+  int* tok_cnt; int* feat_cnt;
+  int* tok_off; int* feat_off;
+  int* tok_cursor; int* feat_cursor;
+  int* tcsr_col; float* tcsr_val; int* fcsr_tok; float* fcsr_val;
+  unsigned char* fired;
+  int sort_segments;
+};
+int clt_build_csr(const CltCsrArgs* a, cudaStream_t st);
+int clt_dead_counter_update(long long* counter, unsigned char* fired, int n, cudaStream_t st);
+
+struct CltDecodeArgs {
+  const void* w[32];
+  int rows[32];
+  int L, B, d, col_pitch, tying;
+  const int* tok_off; const int* tcsr_col; const float* tcsr_val;
+  const float* feat_offset; const float* feat_scale;
+  float* yhat_partial;
+  const float* bias_sum; const float* addend; const void* target; const float* sigma;
+  void* gs; float* yhat_out; double* sq_err;
+  int mode;
+};
+int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st);
+int clt_recon_epilogue(const float* yhat_sum, const float* bias_sum, const float* addend, const void* target, const float* sigma,
+                       void* gs, float* yhat_out, double* sq_err, int L, int B, int d, int row0, int nrows, cudaStream_t st);
+int clt_gs_colsum(const void* gs, float* out, int L, int B, int d, cudaStream_t st);
+
+struct CltAdamHyper {
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2;
+  int decoupled;
+  float grad_scale;
+  unsigned int sr_seed;
+};
+struct CltDecAdamArgs {
+  void* w[32]; float* m[32]; float* v[32]; int rows[32];
+  int ntensors, L, B, d, F_pitch, tying, weights_bf16;
+  const int* feat_off; const int* fcsr_tok; const float* fcsr_val;
+  const void* gs; float* grad_a; const float* pen_coef; float* norm2_out;
+  const float* feat_offset; const float* feat_scale;
+  CltAdamHyper h;
+};
+int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st);
+struct CltEncAdamArgs {
+  void* w; float* m; float* v; void* bias; float* bias_m; float* bias_v;
+  int L, B, d, F_pitch, weights_bf16;
+  const int* feat_off; const int* fcsr_tok; const float* delta; const void* x;
+  const float* dense_grad; const float* dense_bias_grad;
+  CltAdamHyper h;
+};
+int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaStream_t st);
+int clt_dense_adam(void* w, float* m, float* v, const float* grad, long long n, int weights_bf16, const CltAdamHyper* h, cudaStream_t st);
+int clt_decoder_norm2(const void* w, float* out, int F, int R, int d, int weights_bf16, cudaStream_t st);
+int clt_sparsity_penalty(const int* feat_off, const float* fcsr_val, const float* norm2, int ncols, float lambda, float c,
+                         float* grad_a, float* pen_coef, double* penalty_out, cudaStream_t st);
+}
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int num_sms() {
+  static int n = 0;
+  if (n == 0) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+void check(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, what, " failed with code ", rc);
+}
+void need(const Tensor& t, c10::ScalarType ty, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == ty, name, " has dtype ", t.scalar_type(), ", expected ", ty);
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+template <typename T>
+T* opt_ptr(const OptTensor& t) {
+  return t.has_value() && t->defined() ? static_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+CltAdamHyper hyper_from(const std::vector<double>& h) {
+  TORCH_CHECK(h.size() == 10, "hyper expects 10 values");
+  CltAdamHyper c;
+  c.lr = float(h[0]); c.beta1 = float(h[1]); c.beta2 = float(h[2]); c.eps = float(h[3]); c.weight_decay = float(h[4]);
+  c.bc1 = float(h[5]); c.bc2 = float(h[6]); c.decoupled = int(h[7]); c.grad_scale = float(h[8]); c.sr_seed = static_cast<unsigned int>(h[9]);
+  return c;
+}
+
+// ----------------------------------------------------------------------------------------------
+void encoder_gemm(const Tensor& x, const Tensor& w, const OptTensor& bias, Tensor& out, Tensor& status) {
+  need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w"); need(out, at::kBFloat16, "out"); need(status, at::kInt, "status");
+  TORCH_CHECK(x.dim() == 3 && w.dim() == 3 && out.dim() == 3, "expected [L, M, K], [L, N, K], [L, M, N]");
+  const int L = x.size(0), M = x.size(1), K = x.size(2), N = w.size(1);
+  TORCH_CHECK(w.size(0) == L && w.size(2) == K && out.size(0) == L && out.size(1) == M && out.size(2) == N, "shape mismatch");
+  if (bias.has_value() && bias->defined()) { need(*bias, at::kBFloat16, "bias"); TORCH_CHECK(bias->numel() == 1LL * L * N, "bias must be [L, N]"); }
+  c10::cuda::CUDAGuard guard(x.device());
+  check(clt_encoder_gemm(x.data_ptr(), w.data_ptr(), opt_ptr<void>(bias), out.data_ptr(), L, M, N, K, N, 1LL * M * N,
+                         status.data_ptr<int>(), num_sms(), cur_stream()), "encoder_gemm");
+}
+
+void colstats(const Tensor& x, Tensor& mean, Tensor& rstd) {
+  need(x, at::kBFloat16, "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd");
+  const int L = x.size(0), B = x.size(1), F = x.size(2);
+  TORCH_CHECK(mean.numel() == 1LL * L * F && rstd.numel() == 1LL * L * F, "mean/rstd must be [L, F]");
+  c10::cuda::CUDAGuard guard(x.device());
+  check(clt_colstats(x.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), L, B, F, F, 1LL * B * F, cur_stream()), "colstats");
+}
+
+// exchange: (world, rank, data_ptrs[world], flag_ptrs[world], slot_elems, seq) or empty for a single rank
+bool fill_exchange(CltExchangeArgs& ex, int64_t world, int64_t rank, const std::vector<int64_t>& data, const std::vector<int64_t>& flags,
+                   int64_t slot_elems, int64_t seq) {
+  if (world <= 1) return false;
+  TORCH_CHECK(world <= 8 && int64_t(data.size()) == world && int64_t(flags.size()) == world, "exchange expects `world` pointers");
+  std::memset(&ex, 0, sizeof(ex));
+  ex.world = int(world); ex.rank = int(rank); ex.slot_elems = int(slot_elems); ex.seq = static_cast<unsigned int>(seq);
+  for (int i = 0; i < world; ++i) { ex.data[i] = reinterpret_cast<void*>(data[i]); ex.flags[i] = reinterpret_cast<void*>(flags[i]); }
+  return true;
+}
+
+void batchtopk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, int64_t f_valid, int64_t col_pitch, int64_t feat_offset,
+                      int64_t full_F, int64_t k_total, int64_t key_lo, int64_t shift, Tensor& hist, Tensor& ctl, Tensor& ent_tok,
+                      Tensor& ent_col, Tensor& ent_val, Tensor& cand_key, Tensor& cand_tok, Tensor& cand_col, Tensor& cand_val,
+                      Tensor& status, int64_t world, int64_t rank, const std::vector<int64_t>& ex_data,
+                      const std::vector<int64_t>& ex_flags, int64_t slot_elems, int64_t seq) {
+  need(x, at::kBFloat16, "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd");
+  need(hist, at::kInt, "hist"); need(ctl, at::kLong, "ctl"); need(status, at::kInt, "status");
+  need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
+  need(cand_key, at::kInt, "cand_key"); need(cand_tok, at::kInt, "cand_tok"); need(cand_col, at::kInt, "cand_col"); need(cand_val, at::kFloat, "cand_val");
+  TORCH_CHECK(hist.numel() >= 8192 && ctl.numel() >= 16, "hist needs 8192 and ctl 16 elements");
+  CltSelectArgs a;
+  a.x = x.data_ptr(); a.mean = mean.data_ptr<float>(); a.rstd = rstd.data_ptr<float>();
+  a.L = x.size(0); a.B = x.size(1); a.F = int(f_valid); a.stat_pitch = int(mean.size(-1));
+  a.ld = x.size(2); a.layer_stride = 1LL * x.size(1) * x.size(2);
+  a.col_pitch = int(col_pitch); a.feat_offset = int(feat_offset); a.full_F = full_F; a.k_total = k_total;
+  a.key_lo = static_cast<unsigned int>(key_lo); a.shift = int(shift);
+  a.hist = reinterpret_cast<unsigned int*>(hist.data_ptr<int>()); a.ctl = reinterpret_cast<long long*>(ctl.data_ptr<int64_t>());
+  a.ent_tok = ent_tok.data_ptr<int>(); a.ent_col = ent_col.data_ptr<int>(); a.ent_val = ent_val.data_ptr<float>(); a.ent_cap = ent_tok.numel();
+  a.cand_key = reinterpret_cast<unsigned int*>(cand_key.data_ptr<int>()); a.cand_tok = cand_tok.data_ptr<int>();
+  a.cand_col = cand_col.data_ptr<int>(); a.cand_val = cand_val.data_ptr<float>(); a.cand_cap = cand_key.numel();
+  a.status = status.data_ptr<int>();
+  CltExchangeArgs ex;
+  const bool multi = fill_exchange(ex, world, rank, ex_data, ex_flags, slot_elems, seq);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(clt_batchtopk_select(&a, multi ? &ex : nullptr, cur_stream()), "batchtopk_select");
+}
+
+void build_csr(const Tensor& ent_tok, const Tensor& ent_col, const Tensor& ent_val, const Tensor& ctl, int64_t num_tokens, int64_t num_cols,
+               Tensor& tok_cnt, Tensor& feat_cnt, Tensor& tok_off, Tensor& feat_off, Tensor& tok_cursor, Tensor& feat_cursor,
+               Tensor& tcsr_col, Tensor& tcsr_val, Tensor& fcsr_tok, Tensor& fcsr_val, const OptTensor& fired, int64_t sort_segments) {
+  need(ent_tok, at::kInt, "ent_tok"); need(ctl, at::kLong, "ctl");
+  need(tok_cnt, at::kInt, "tok_cnt"); need(feat_cnt, at::kInt, "feat_cnt"); need(tok_off, at::kInt, "tok_off"); need(feat_off, at::kInt, "feat_off");
+  TORCH_CHECK(tok_off.numel() >= num_tokens + 1 && feat_off.numel() >= num_cols + 1, "offset arrays too small");
+  TORCH_CHECK(tok_cnt.numel() >= num_tokens && feat_cnt.numel() >= num_cols && tok_cursor.numel() >= num_tokens && feat_cursor.numel() >= num_cols, "count arrays too small");
+  CltCsrArgs a;
+  a.ent_tok = ent_tok.data_ptr<int>(); a.ent_col = ent_col.data_ptr<int>(); a.ent_val = ent_val.data_ptr<float>(); a.ent_cap = ent_tok.numel();
+  a.ctl = reinterpret_cast<const long long*>(ctl.data_ptr<int64_t>());
+  a.num_tokens = int(num_tokens); a.num_cols = int(num_cols);
+  a.tok_cnt = tok_cnt.data_ptr<int>(); a.feat_cnt = feat_cnt.data_ptr<int>(); a.tok_off = tok_off.data_ptr<int>(); a.feat_off = feat_off.data_ptr<int>();
+  a.tok_cursor = tok_cursor.data_ptr<int>(); a.feat_cursor = feat_cursor.data_ptr<int>();
+  a.tcsr_col = tcsr_col.data_ptr<int>(); a.tcsr_val = tcsr_val.data_ptr<float>(); a.fcsr_tok = fcsr_tok.data_ptr<int>(); a.fcsr_val = fcsr_val.data_ptr<float>();
+  a.fired = fired.has_value() && fired->defined() ? fired->data_ptr<uint8_t>() : nullptr;
+  a.sort_segments = int(sort_segments);
+  c10::cuda::CUDAGuard guard(ent_tok.device());
+  check(clt_build_csr(&a, cur_stream()), "build_csr");
+}
+
+void dead_counter_update(Tensor& counter, Tensor& fired) {
+  need(counter, at::kLong, "counter"); need(fired, at::kByte, "fired");
+  TORCH_CHECK(counter.numel() == fired.numel(), "counter / fired size mismatch");
+  c10::cuda::CUDAGuard guard(counter.device());
+  check(clt_dead_counter_update(reinterpret_cast<long long*>(counter.data_ptr<int64_t>()), fired.data_ptr<uint8_t>(), int(counter.numel()), cur_stream()),
+        "dead_counter_update");
+}
+
+void sparse_decode(const std::vector<Tensor>& dec_w, int64_t L, int64_t B, int64_t d, int64_t col_pitch, int64_t tying, const Tensor& tok_off,
+                   const Tensor& tcsr_col, const Tensor& tcsr_val, const OptTensor& feat_offset, const OptTensor& feat_scale,
+                   const OptTensor& yhat_partial, const OptTensor& bias_sum, const OptTensor& addend, const OptTensor& target,
+                   const OptTensor& sigma, const OptTensor& gs, const OptTensor& yhat_out, const OptTensor& sq_err, int64_t mode) {
+  TORCH_CHECK(dec_w.size() <= 32, "at most 32 decoder tensors");
+  CltDecodeArgs a;
+  std::memset(&a, 0, sizeof(a));
+  for (size_t i = 0; i < dec_w.size(); ++i) {
+    need(dec_w[i], at::kBFloat16, "dec_w");
+    a.w[i] = dec_w[i].data_ptr();
+    a.rows[i] = int(dec_w[i].size(1));
+  }
+  a.L = int(L); a.B = int(B); a.d = int(d); a.col_pitch = int(col_pitch); a.tying = int(tying);
+  a.tok_off = tok_off.data_ptr<int>(); a.tcsr_col = tcsr_col.data_ptr<int>(); a.tcsr_val = tcsr_val.data_ptr<float>();
+  a.feat_offset = opt_ptr<const float>(feat_offset); a.feat_scale = opt_ptr<const float>(feat_scale);
+  a.yhat_partial = opt_ptr<float>(yhat_partial); a.bias_sum = opt_ptr<const float>(bias_sum); a.addend = opt_ptr<const float>(addend);
+  a.target = opt_ptr<const void>(target); a.sigma = opt_ptr<const float>(sigma); a.gs = opt_ptr<void>(gs);
+  a.yhat_out = opt_ptr<float>(yhat_out); a.sq_err = opt_ptr<double>(sq_err); a.mode = int(mode);
+  if (mode == 0) {
+    TORCH_CHECK(a.yhat_partial != nullptr, "mode 0 needs yhat_partial");
+  } else {
+    TORCH_CHECK(a.bias_sum && a.target && a.gs && a.sq_err, "mode 1 needs bias_sum, target, gs, sq_err");
+  }
+  c10::cuda::CUDAGuard guard(tok_off.device());
+  check(clt_sparse_decode(&a, cur_stream()), "sparse_decode");
+}
+
+void recon_epilogue(const Tensor& yhat_sum, const Tensor& bias_sum, const OptTensor& addend, const Tensor& target, const OptTensor& sigma,
+                    Tensor& gs, const OptTensor& yhat_out, Tensor& sq_err, int64_t row0, int64_t nrows) {
+  need(yhat_sum, at::kFloat, "yhat_sum"); need(bias_sum, at::kFloat, "bias_sum"); need(target, at::kBFloat16, "target");
+  need(gs, at::kBFloat16, "gs"); need(sq_err, at::kDouble, "sq_err");
+  const int L = yhat_sum.size(0), B = yhat_sum.size(1), d = yhat_sum.size(2);
+  c10::cuda::CUDAGuard guard(yhat_sum.device());
+  check(clt_recon_epilogue(yhat_sum.data_ptr<float>(), bias_sum.data_ptr<float>(), opt_ptr<const float>(addend), target.data_ptr(),
+                           opt_ptr<const float>(sigma), gs.data_ptr(), opt_ptr<float>(yhat_out), sq_err.data_ptr<double>(), L, B, d,
+                           int(row0), int(nrows), cur_stream()), "recon_epilogue");
+}
+
+void gs_colsum(const Tensor& gs, Tensor& out) {
+  need(gs, at::kBFloat16, "gs"); need(out, at::kFloat, "out");
+  c10::cuda::CUDAGuard guard(gs.device());
+  check(clt_gs_colsum(gs.data_ptr(), out.data_ptr<float>(), int(gs.size(0)), int(gs.size(1)), int(gs.size(2)), cur_stream()), "gs_colsum");
+}
+
+void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vector<Tensor>& v, int64_t L, int64_t B, int64_t d,
+                       int64_t F_pitch, int64_t tying, const Tensor& feat_off, const Tensor& fcsr_tok, const Tensor& fcsr_val,
+                       const Tensor& gs, const OptTensor& grad_a, const OptTensor& pen_coef, const OptTensor& norm2_out,
+                       const OptTensor& feat_offset, const OptTensor& feat_scale, const std::vector<double>& hyper) {
+  TORCH_CHECK(w.size() <= 32 && w.size() == m.size() && w.size() == v.size(), "bad tensor lists");
+  CltDecAdamArgs a;
+  std::memset(&a, 0, sizeof(a));
+  const bool bf16 = w[0].scalar_type() == at::kBFloat16;
+  for (size_t i = 0; i < w.size(); ++i) {
+    need(w[i], bf16 ? at::kBFloat16 : at::kFloat, "w"); need(m[i], at::kFloat, "m"); need(v[i], at::kFloat, "v");
+    TORCH_CHECK(w[i].dim() == 3 && w[i].size(0) == F_pitch && w[i].size(2) == d, "decoder tensor must be [F, R, d]");
+    a.w[i] = w[i].data_ptr(); a.m[i] = m[i].data_ptr<float>(); a.v[i] = v[i].data_ptr<float>(); a.rows[i] = int(w[i].size(1));
+  }
+  a.ntensors = int(w.size()); a.L = int(L); a.B = int(B); a.d = int(d); a.F_pitch = int(F_pitch); a.tying = int(tying); a.weights_bf16 = bf16;
+  a.feat_off = feat_off.data_ptr<int>(); a.fcsr_tok = fcsr_tok.data_ptr<int>(); a.fcsr_val = fcsr_val.data_ptr<float>();
+  need(gs, at::kBFloat16, "gs");
+  a.gs = gs.data_ptr(); a.grad_a = opt_ptr<float>(grad_a); a.pen_coef = opt_ptr<const float>(pen_coef); a.norm2_out = opt_ptr<float>(norm2_out);
+  a.feat_offset = opt_ptr<const float>(feat_offset); a.feat_scale = opt_ptr<const float>(feat_scale);
+  a.h = hyper_from(hyper);
+  c10::cuda::CUDAGuard guard(gs.device());
+  check(clt_decoder_rows_adam(&a, num_sms(), cur_stream()), "decoder_rows_adam");
+}
+
+void encoder_rows_adam(Tensor& w, Tensor& m, Tensor& v, Tensor& bias, Tensor& bias_m, Tensor& bias_v, const Tensor& feat_off,
+                       const Tensor& fcsr_tok, const Tensor& delta, const Tensor& x, const OptTensor& dense_grad,
+                       const OptTensor& dense_bias_grad, const std::vector<double>& hyper) {
+  const bool bf16 = w.scalar_type() == at::kBFloat16;
+  need(w, bf16 ? at::kBFloat16 : at::kFloat, "w"); need(m, at::kFloat, "m"); need(v, at::kFloat, "v");
+  need(bias, bf16 ? at::kBFloat16 : at::kFloat, "bias"); need(bias_m, at::kFloat, "bias_m"); need(bias_v, at::kFloat, "bias_v");
+  need(x, at::kBFloat16, "x"); need(delta, at::kFloat, "delta");
+  CltEncAdamArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.w = w.data_ptr(); a.m = m.data_ptr<float>(); a.v = v.data_ptr<float>();
+  a.bias = bias.data_ptr(); a.bias_m = bias_m.data_ptr<float>(); a.bias_v = bias_v.data_ptr<float>();
+  a.L = int(w.size(0)); a.F_pitch = int(w.size(1)); a.d = int(w.size(2)); a.B = int(x.size(1)); a.weights_bf16 = bf16;
+  a.feat_off = feat_off.data_ptr<int>(); a.fcsr_tok = fcsr_tok.data_ptr<int>(); a.delta = delta.data_ptr<float>(); a.x = x.data_ptr();
+  a.dense_grad = opt_ptr<const float>(dense_grad); a.dense_bias_grad = opt_ptr<const float>(dense_bias_grad);
+  a.h = hyper_from(hyper);
+  c10::cuda::CUDAGuard guard(w.device());
+  check(clt_encoder_rows_adam(&a, num_sms(), cur_stream()), "encoder_rows_adam");
+}
+
+void dense_adam(Tensor& w, Tensor& m, Tensor& v, const Tensor& grad, const std::vector<double>& hyper) {
+  const bool bf16 = w.scalar_type() == at::kBFloat16;
+  need(w, bf16 ? at::kBFloat16 : at::kFloat, "w"); need(m, at::kFloat, "m"); need(v, at::kFloat, "v"); need(grad, at::kFloat, "grad");
+  TORCH_CHECK(w.numel() == m.numel() && w.numel() == v.numel() && w.numel() == grad.numel(), "size mismatch");
+  const CltAdamHyper h = hyper_from(hyper);
+  c10::cuda::CUDAGuard guard(w.device());
+  check(clt_dense_adam(w.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr<float>(), w.numel(), bf16, &h, cur_stream()), "dense_adam");
+}
+
+void decoder_norm2(const Tensor& w, Tensor& out) {
+  const bool bf16 = w.scalar_type() == at::kBFloat16;
+  need(w, bf16 ? at::kBFloat16 : at::kFloat, "w"); need(out, at::kFloat, "out");
+  TORCH_CHECK(w.dim() == 3 && out.numel() >= w.size(0), "w must be [F, R, d], out [F]");
+  c10::cuda::CUDAGuard guard(w.device());
+  check(clt_decoder_norm2(w.data_ptr(), out.data_ptr<float>(), int(w.size(0)), int(w.size(1)), int(w.size(2)), bf16, cur_stream()), "decoder_norm2");
+}
+
+void sparsity_penalty(const Tensor& feat_off, const Tensor& fcsr_val, const Tensor& norm2, double lambda, double c, Tensor& grad_a,
+                      Tensor& pen_coef, Tensor& penalty_out) {
+  need(feat_off, at::kInt, "feat_off"); need(fcsr_val, at::kFloat, "fcsr_val"); need(norm2, at::kFloat, "norm2");
+  need(grad_a, at::kFloat, "grad_a"); need(pen_coef, at::kFloat, "pen_coef"); need(penalty_out, at::kDouble, "penalty_out");
+  const int ncols = int(norm2.numel());
+  TORCH_CHECK(feat_off.numel() >= ncols + 1 && pen_coef.numel() >= ncols, "size mismatch");
+  c10::cuda::CUDAGuard guard(norm2.device());
+  check(clt_sparsity_penalty(feat_off.data_ptr<int>(), fcsr_val.data_ptr<float>(), norm2.data_ptr<float>(), ncols, float(lambda), float(c),
+                             grad_a.data_ptr<float>(), pen_coef.data_ptr<float>(), penalty_out.data_ptr<double>(), cur_stream()),
+        "sparsity_penalty");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("encoder_gemm", &encoder_gemm);
+  m.def("colstats", &colstats);
+  m.def("batchtopk_select", &batchtopk_select);
+  m.def("build_csr", &build_csr);
+  m.def("dead_counter_update", &dead_counter_update);
+  m.def("sparse_decode", &sparse_decode);
+  m.def("recon_epilogue", &recon_epilogue);
+  m.def("gs_colsum", &gs_colsum);
+  m.def("decoder_rows_adam", &decoder_rows_adam);
+  m.def("encoder_rows_adam", &encoder_rows_adam);
+  m.def("dense_adam", &dense_adam);
+  m.def("decoder_norm2", &decoder_norm2);
+  m.def("sparsity_penalty", &sparsity_penalty);
+}

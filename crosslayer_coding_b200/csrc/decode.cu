@@ -1,0 +1,271 @@
+// Sparse cross-layer decode and the reconstruction loss (sm_100a).
+//
+// The reference decodes with one dense GEMM per (source, target) pair over activations that are more
+// than 99 % zeros, each followed by an all-reduce (clt/models/decoder.py:289-295, clt/models/parallel.py:363-383),
+// and then computes the MSE in separate passes (clt/training/losses.py:76-90).  Here one CTA per token walks
+// that token's active (layer, feature, value) entries, reads each feature's contiguous block of decoder rows
+// (feature-major layout [F, R, d]) and accumulates every target layer's reconstruction in registers.
+// The epilogue either writes the fp32 partial reconstruction (tensor parallel: summed across ranks before
+// the loss) or, single rank, finishes in place: bias, optional dense addend (skip connection), residual,
+// per-layer squared-error sum in de-normalised units and the bf16 gradient seed  gs = (y_hat - y) * sigma^2.
+#include "common.cuh"
+
+namespace clt {
+
+constexpr int kMaxLayers = 32;
+constexpr int kTgtTile = 16;  // target layers accumulated per pass
+
+struct DecodeParams {
+  const __nv_bfloat16* w[kMaxLayers];  // decoder tensor i: [F_pitch, rows_i, d]
+  int rows[kMaxLayers];                // rows per feature of tensor i
+  int L, B, d;
+  int col_pitch;                       // entries encode column = layer * col_pitch + feature
+  int tying;                           // 0 untied, 1 per_source, 2 per_target
+  const int* tok_off;                  // [B+1]
+  const int* tcsr_col;
+  const float* tcsr_val;
+  const float* feat_offset;            // optional [L, col_pitch]  (tied decoders)
+  const float* feat_scale;             // optional [L, col_pitch]
+  // outputs / epilogue
+  float* yhat_partial;                 // mode 0: [L, B, d] fp32 partial sums
+  const float* bias_sum;               // mode 1: [L, d] summed decoder biases per target
+  const float* addend;                 // mode 1: optional [L, B, d] fp32 (skip term)
+  const __nv_bfloat16* target;         // mode 1: [L, B, d]
+  const float* sigma;                  // mode 1: optional [L, d] de-normalisation scale of the targets
+  __nv_bfloat16* gs;                   // mode 1: [L, B, d] (y_hat - y) * sigma^2
+  float* yhat_out;                     // mode 1: optional [L, B, d] fp32 reconstruction
+  double* sq_err;                      // mode 1: [L] sum of ((y_hat - y) * sigma)^2
+  int mode;
+};
+
+__device__ __forceinline__ void fma8(float (&acc)[8], float a, const uint4& v) {
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    acc[2 * j] = fmaf(a, bf16_lo(u[j]), acc[2 * j]);
+    acc[2 * j + 1] = fmaf(a, bf16_hi(u[j]), acc[2 * j + 1]);
+  }
+}
+
+// grid = (B, ceil(L / kTgtTile)); block = d / 8 threads rounded up to a warp multiple.
+__global__ void __launch_bounds__(256) decode_kernel(const DecodeParams p) {
+  const int tok = blockIdx.x;
+  const int t0 = blockIdx.y * kTgtTile;
+  const int nT = min(kTgtTile, p.L - t0);
+  const int e0 = threadIdx.x * 8;
+  const bool active = e0 < p.d;
+  float acc[kTgtTile][8];
+#pragma unroll
+  for (int j = 0; j < kTgtTile; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+
+  const int b = p.tok_off[tok], e = p.tok_off[tok + 1];
+  for (int i = b; i < e; ++i) {
+    const int col = p.tcsr_col[i];
+    const float a = p.tcsr_val[i];
+    const int s = col / p.col_pitch;
+    const int f = col - s * p.col_pitch;
+    if (s >= t0 + nT || a == 0.f || !active) continue;
+    if (p.tying == 0) {
+      const int R = p.rows[s];
+      const __nv_bfloat16* base = p.w[s] + (1LL * f * R) * p.d + e0;
+#pragma unroll
+      for (int j = 0; j < kTgtTile; ++j) {
+        const int t = t0 + j;
+        if (j < nT && t >= s) {
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + 1LL * (t - s) * p.d));
+          fma8(acc[j], a, v);
+        }
+      }
+    } else if (p.tying == 1) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.w[s] + 1LL * f * p.d + e0));
+#pragma unroll
+      for (int j = 0; j < kTgtTile; ++j) {
+        const int t = t0 + j;
+        if (j < nT && t >= s) {
+          float av = a;
+          if (p.feat_offset) av += p.feat_offset[1LL * t * p.col_pitch + f];
+          if (p.feat_scale) av *= p.feat_scale[1LL * t * p.col_pitch + f];
+          fma8(acc[j], av, v);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kTgtTile; ++j) {
+        const int t = t0 + j;
+        if (j < nT && t >= s) {
+          float av = a;
+          if (p.feat_offset) av += p.feat_offset[1LL * t * p.col_pitch + f];
+          if (p.feat_scale) av *= p.feat_scale[1LL * t * p.col_pitch + f];
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.w[t] + 1LL * f * p.d + e0));
+          fma8(acc[j], av, v);
+        }
+      }
+    }
+  }
+
+  __shared__ float red[8];
+#pragma unroll
+  for (int j = 0; j < kTgtTile; ++j) {
+    if (j >= nT) break;  // uniform across the block
+    const int t = t0 + j;
+    const long long off = (1LL * t * p.B + tok) * p.d + e0;
+    float sq = 0.f;
+    if (active) {
+      if (p.mode == 0) {
+        float4* dst = reinterpret_cast<float4*>(p.yhat_partial + off);
+        dst[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+        dst[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+      } else {
+        float y[8], sg[8], out[8];
+        const uint4 tv = *reinterpret_cast<const uint4*>(p.target + off);
+        const uint32_t u[4] = {tv.x, tv.y, tv.z, tv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { y[2 * i] = bf16_lo(u[i]); y[2 * i + 1] = bf16_hi(u[i]); }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float v = acc[j][i] + p.bias_sum[1LL * t * p.d + e0 + i];
+          if (p.addend) v += p.addend[off + i];
+          sg[i] = p.sigma ? p.sigma[1LL * t * p.d + e0 + i] : 1.f;
+          out[i] = v;
+          const float r = (v - y[i]) * sg[i];
+          sq = fmaf(r, r, sq);
+          y[i] = r * sg[i];  // gradient seed
+        }
+        uint4 gv;
+        gv.x = pack_bf16x2(y[0], y[1]); gv.y = pack_bf16x2(y[2], y[3]);
+        gv.z = pack_bf16x2(y[4], y[5]); gv.w = pack_bf16x2(y[6], y[7]);
+        *reinterpret_cast<uint4*>(p.gs + off) = gv;
+        if (p.yhat_out) {
+          float4* dst = reinterpret_cast<float4*>(p.yhat_out + off);
+          dst[0] = make_float4(out[0], out[1], out[2], out[3]);
+          dst[1] = make_float4(out[4], out[5], out[6], out[7]);
+        }
+      }
+    }
+    if (p.mode != 0) {
+      sq = warp_sum(sq);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+        atomicAdd(&p.sq_err[t], double(tot));
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// Epilogue for the tensor-parallel path, run after the partial reconstructions were summed across ranks:
+// bias, addend, residual, loss sum and gradient seed for rows [row0, row0 + nrows) of every layer.
+__global__ void __launch_bounds__(256) recon_epilogue_kernel(const float* __restrict__ yhat_sum, const float* __restrict__ bias_sum,
+                                                               const float* __restrict__ addend, const __nv_bfloat16* __restrict__ target,
+                                                               const float* __restrict__ sigma, __nv_bfloat16* __restrict__ gs,
+                                                               float* __restrict__ yhat_out, double* __restrict__ sq_err, int L, int B,
+                                                               int d, int row0, int nrows) {
+  const int t = blockIdx.y;
+  const int vec_per_row = d / 8;
+  const long long nvec = 1LL * nrows * vec_per_row;
+  float sq = 0.f;
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < nvec; i += 1LL * gridDim.x * blockDim.x) {
+    const int row = row0 + int(i / vec_per_row);
+    const int e0 = int(i % vec_per_row) * 8;
+    const long long off = (1LL * t * B + row) * d + e0;
+    const float4 a0 = *reinterpret_cast<const float4*>(yhat_sum + off), a1 = *reinterpret_cast<const float4*>(yhat_sum + off + 4);
+    float v[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const uint4 tv = *reinterpret_cast<const uint4*>(target + off);
+    const uint32_t u[4] = {tv.x, tv.y, tv.z, tv.w};
+    float g[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j] += bias_sum[1LL * t * d + e0 + j];
+      if (addend) v[j] += addend[off + j];
+      const float y = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+      const float sg = sigma ? sigma[1LL * t * d + e0 + j] : 1.f;
+      const float r = (v[j] - y) * sg;
+      sq = fmaf(r, r, sq);
+      g[j] = r * sg;
+    }
+    uint4 gv;
+    gv.x = pack_bf16x2(g[0], g[1]); gv.y = pack_bf16x2(g[2], g[3]); gv.z = pack_bf16x2(g[4], g[5]); gv.w = pack_bf16x2(g[6], g[7]);
+    *reinterpret_cast<uint4*>(gs + off) = gv;
+    if (yhat_out) {
+      float4* dst = reinterpret_cast<float4*>(yhat_out + off);
+      dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+      dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  }
+  __shared__ float red[8];
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
+    atomicAdd(&sq_err[t], double(tot));
+  }
+}
+
+// Column sums of the gradient seed: out[t, :] = sum_b gs[t, b, :]  (decoder-bias gradient up to a constant).
+__global__ void __launch_bounds__(256) gs_colsum_kernel(const __nv_bfloat16* __restrict__ gs, float* __restrict__ out, int B, int d,
+                                                          int rows_per_block) {
+  const int t = blockIdx.z;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(B, r0 + rows_per_block);
+  float s = 0.f;
+  for (int r = r0; r < r1; ++r) s += __bfloat162float(gs[(1LL * t * B + r) * d + c]);
+  atomicAdd(&out[1LL * t * d + c], s);
+}
+
+}  // namespace clt
+
+using namespace clt;
+
+struct CltDecodeArgs {
+  const void* w[32];
+  int rows[32];
+  int L, B, d, col_pitch, tying;
+  const int* tok_off; const int* tcsr_col; const float* tcsr_val;
+  const float* feat_offset; const float* feat_scale;
+  float* yhat_partial;
+  const float* bias_sum; const float* addend; const void* target; const float* sigma;
+  void* gs; float* yhat_out; double* sq_err;
+  int mode;
+};
+
+extern "C" int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st) {
+  if (a->d % 8 != 0 || a->L > kMaxLayers || a->d > 2048) return -1;
+  DecodeParams p;
+  for (int i = 0; i < kMaxLayers; ++i) { p.w[i] = static_cast<const __nv_bfloat16*>(a->w[i]); p.rows[i] = a->rows[i]; }
+  p.L = a->L; p.B = a->B; p.d = a->d; p.col_pitch = a->col_pitch; p.tying = a->tying;
+  p.tok_off = a->tok_off; p.tcsr_col = a->tcsr_col; p.tcsr_val = a->tcsr_val;
+  p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale;
+  p.yhat_partial = a->yhat_partial; p.bias_sum = a->bias_sum; p.addend = a->addend;
+  p.target = static_cast<const __nv_bfloat16*>(a->target); p.sigma = a->sigma;
+  p.gs = static_cast<__nv_bfloat16*>(a->gs); p.yhat_out = a->yhat_out; p.sq_err = a->sq_err; p.mode = a->mode;
+  const int threads = ((a->d / 8 + 31) / 32) * 32;
+  dim3 grid(a->B, (a->L + kTgtTile - 1) / kTgtTile);
+  decode_kernel<<<grid, threads, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int clt_recon_epilogue(const float* yhat_sum, const float* bias_sum, const float* addend, const void* target,
+                                  const float* sigma, void* gs, float* yhat_out, double* sq_err, int L, int B, int d, int row0,
+                                  int nrows, cudaStream_t st) {
+  if (d % 8 != 0) return -1;
+  if (nrows <= 0) return 0;
+  dim3 grid(148, L);
+  recon_epilogue_kernel<<<grid, 256, 0, st>>>(yhat_sum, bias_sum, addend, static_cast<const __nv_bfloat16*>(target), sigma,
+                                              static_cast<__nv_bfloat16*>(gs), yhat_out, sq_err, L, B, d, row0, nrows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int clt_gs_colsum(const void* gs, float* out, int L, int B, int d, cudaStream_t st) {
+  const int rpb = 128;
+  dim3 grid((d + 255) / 256, (B + rpb - 1) / rpb, L);
+  gs_colsum_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gs), out, B, d, rpb);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

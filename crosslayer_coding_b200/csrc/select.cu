@@ -1,0 +1,645 @@
+// Global BatchTopK without a dense [B, L*F] ranking tensor (sm_100a).
+//
+// The reference concatenates every layer's batch-z-scored pre-activations and calls torch.topk on the
+// flattened tensor (clt/models/activations.py:27-32, 281-357).  Here the same selection is a threshold
+// search over the bf16 pre-activations written by the encoder GEMM:
+//
+//   1. colstats      per-feature batch mean and 1/(std+1e-6) (unbiased std, shifted sums)
+//   2. zhist         8192-bin histogram of the order-preserving key of z = (x-mean)*rstd, keys >= key_lo
+//   3. find_bin      bin that contains the k_total-th largest key (after the ranks' histograms were summed)
+//   4. compact       entries above the bin go to the output list, entries inside it to a candidate list
+//   5. refine        exact key cut inside the bin by radix passes; ties resolved by lowest flat index
+//                    b*(L*F) + l*F + f so the result does not depend on the tensor-parallel world size
+//   6. finalize      candidates on the keep side of the cut are appended to the output list
+//   7. csr           token-major and feature-major CSR views of the list for the decoder / backward
+//
+// Under tensor parallelism every rank runs 1-2 and 4-7 on its feature shard; only histograms cross GPUs
+// (the 8192-bin one and the 512-bin refinement rounds), written straight into the peers' exchange
+// buffers by the kernels below with bounded flag waits.
+#include "common.cuh"
+
+namespace clt {
+
+constexpr int kHistBins = 8192;
+constexpr int kRefineBins = 512;
+constexpr int kMaxPeers = 8;
+
+// Control block shared by the selection kernels (device memory, int64 slots).
+enum SelCtl : int {
+  CTL_BIN = 0,          // threshold bin
+  CTL_ABOVE = 1,        // number of keys in bins above it (global over ranks)
+  CTL_NEED = 2,         // how many the threshold bin has to contribute (global)
+  CTL_NUM_ENTRIES = 3,  // length of the output list (this rank)
+  CTL_NUM_CAND = 4,     // length of the candidate list (this rank)
+  CTL_CUT_KEY = 5,      // exact key cut T
+  CTL_TIE_MODE = 6,     // 0: keep every key == T; 1: keep ties with flat index <= CTL_CUT_FLAT
+  CTL_CUT_FLAT = 7,
+  CTL_SIZE = 16,
+};
+
+// Exchange area for the cross-rank histogram sums.  peers[r] points at rank r's area; each area holds
+// world slots of `slot_elems` uint32 per round plus one flag word per (round, source rank).
+struct Exchange {
+  int world;
+  int rank;
+  uint32_t* peers[kMaxPeers];   // data: [rounds][world][slot_elems]
+  uint32_t* flags[kMaxPeers];   // flags: [rounds][world]
+  int slot_elems;
+  uint32_t seq;                 // value a flag takes in this launch (monotone over launches)
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Sum `n` uint32 counters over all ranks, in place in shared memory `vals` (one CTA).  Every rank stores
+// its vector into slot [round][rank] of every peer, raises flag [round][rank] there, then waits (bounded)
+// for the flags of all peers in its own area and adds the slots up.  Returns false on a timeout.
+__device__ bool exchange_sum(const Exchange& ex, int round, uint32_t* vals, int n, int* timeout_flag_smem) {
+  if (ex.world <= 1) return true;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  for (int p = 0; p < ex.world; ++p) {
+    uint32_t* dst = ex.peers[p] + (size_t(round) * ex.world + ex.rank) * ex.slot_elems;
+    for (int i = tid; i < n; i += nt) dst[i] = vals[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < ex.world) st_release_sys(ex.flags[tid] + size_t(round) * ex.world + ex.rank, ex.seq);
+  if (tid < ex.world) {
+    const uint32_t* f = ex.flags[ex.rank] + size_t(round) * ex.world + tid;
+    const long long start = clock64();
+    while (ld_acquire_sys(f) != ex.seq) {
+      if (clock64() - start > kWaitTimeoutCycles) { *timeout_flag_smem = 1; break; }
+    }
+  }
+  __syncthreads();
+  if (*timeout_flag_smem) return false;
+  const uint32_t* mine = ex.peers[ex.rank] + size_t(round) * ex.world * ex.slot_elems;
+  for (int i = tid; i < n; i += nt) {
+    uint32_t s = 0;
+    for (int p = 0; p < ex.world; ++p) s += mine[size_t(p) * ex.slot_elems + i];
+    vals[i] = s;
+  }
+  __syncthreads();
+  return true;
+}
+
+// ------------------------------------------------------------------ 1. column statistics
+// x: [L, B, ld] bf16.  Each thread owns 8 adjacent columns; blockDim = (32, 8): 8 row groups.
+__global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ mean,
+                                                         float* __restrict__ rstd, int B, int F, long long ld,
+                                                         long long layer_stride) {
+  const int l = blockIdx.y;
+  const int cg = blockIdx.x * 32 + threadIdx.x;  // column group of 8
+  const int c0 = cg * 8;
+  __shared__ float red[8][32][17];
+  float s[8], q[8], shift[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = q[j] = shift[j] = 0.f;
+  const bool active = c0 < F;
+  const __nv_bfloat16* base = x + 1LL * l * layer_stride + c0;
+  if (active) {
+    uint4 v0 = *reinterpret_cast<const uint4*>(base);
+    const uint32_t w[4] = {v0.x, v0.y, v0.z, v0.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { shift[2 * j] = bf16_lo(w[j]); shift[2 * j + 1] = bf16_hi(w[j]); }
+    for (int r = threadIdx.y; r < B; r += 8) {
+      uint4 v = *reinterpret_cast<const uint4*>(base + 1LL * r * ld);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = bf16_lo(u[j]) - shift[2 * j], b = bf16_hi(u[j]) - shift[2 * j + 1];
+        s[2 * j] += a; q[2 * j] += a * a;
+        s[2 * j + 1] += b; q[2 * j + 1] += b * b;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { red[threadIdx.y][threadIdx.x][j] = s[j]; red[threadIdx.y][threadIdx.x][8 + j] = q[j]; }
+  __syncthreads();
+  if (threadIdx.y == 0 && active) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float ss = 0.f, qq = 0.f;
+      for (int y = 0; y < 8; ++y) { ss += red[y][threadIdx.x][j]; qq += red[y][threadIdx.x][8 + j]; }
+      if (c0 + j < F) {
+        const float mu = ss / float(B);
+        float var = B > 1 ? (qq - ss * mu) / float(B - 1) : 0.f;
+        var = fmaxf(var, 0.f);
+        mean[1LL * l * F + c0 + j] = shift[j] + mu;
+        rstd[1LL * l * F + c0 + j] = 1.f / (sqrtf(var) + 1e-6f);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ 2. histogram of z keys
+struct ScanGeom {
+  int B, F, L;           // F = valid local columns per layer
+  int sp;                // pitch of the mean / rstd rows (>= F)
+  long long ld;          // row pitch of x (elements)
+  long long layer_stride;
+  int rows_per_block;
+};
+
+__device__ __forceinline__ void load_cols8(const float* p, float (&o)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+
+__global__ void __launch_bounds__(256) zhist_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+                                                      const float* __restrict__ rstd, ScanGeom g, uint32_t key_lo, int shift,
+                                                      unsigned int* __restrict__ hist) {
+  __shared__ unsigned int sh[kHistBins];
+  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const int l = blockIdx.z;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c0 < g.F) {
+    float mu[8], rs[8];
+    if (c0 + 8 <= g.F) {
+      load_cols8(mean + 1LL * l * g.sp + c0, mu);
+      load_cols8(rstd + 1LL * l * g.sp + c0, rs);
+    } else {
+      for (int j = 0; j < 8; ++j) {
+        const bool in = c0 + j < g.F;
+        mu[j] = in ? mean[1LL * l * g.sp + c0 + j] : 0.f;
+        rs[j] = in ? rstd[1LL * l * g.sp + c0 + j] : 0.f;
+      }
+    }
+    const int nvalid = min(8, g.F - c0);
+    const int r0 = blockIdx.y * g.rows_per_block;
+    const int r1 = min(g.B, r0 + g.rows_per_block);
+    const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+    for (int r = r0; r < r1; ++r) {
+      const uint4 v = *reinterpret_cast<const uint4*>(base + 1LL * r * g.ld);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+        const float z = (xv - mu[j]) * rs[j];
+        const uint32_t key = float_to_key(z);
+        if (key >= key_lo && j < nvalid) atomicAdd(&sh[min((key - key_lo) >> shift, uint32_t(kHistBins - 1))], 1u);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) {
+    const unsigned int c = sh[i];
+    if (c) atomicAdd(&hist[i], c);
+  }
+}
+
+// ------------------------------------------------------------------ 3. threshold bin (one CTA, 1024 threads)
+__global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __restrict__ hist, long long k_total,
+                                                          long long* __restrict__ ctl, Exchange ex, int* __restrict__ status) {
+  __shared__ uint32_t vals[kHistBins];
+  __shared__ unsigned long long part[1024];
+  __shared__ int timeout;
+  const int tid = threadIdx.x;
+  if (tid == 0) timeout = 0;
+  for (int i = tid; i < kHistBins; i += 1024) vals[i] = hist[i];
+  __syncthreads();
+  if (!exchange_sum(ex, 0, vals, kHistBins, &timeout)) {
+    if (tid == 0) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+    return;
+  }
+  // thread t owns bins [8t, 8t+8); suffix sums from the top
+  unsigned long long mine = 0;
+  for (int j = 0; j < 8; ++j) mine += vals[tid * 8 + j];
+  part[tid] = mine;
+  __syncthreads();
+  if (tid == 0) {
+    unsigned long long run = 0;
+    for (int t = 1023; t >= 0; --t) { const unsigned long long c = part[t]; part[t] = run; run += c; }
+    if (run < (unsigned long long)k_total) atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
+  }
+  __syncthreads();
+  unsigned long long above = part[tid];  // keys in bins above this thread's group
+  for (int j = 7; j >= 0; --j) {
+    const unsigned long long c = vals[tid * 8 + j];
+    if (above < (unsigned long long)k_total && above + c >= (unsigned long long)k_total) {
+      ctl[CTL_BIN] = tid * 8 + j;
+      ctl[CTL_ABOVE] = (long long)above;
+      ctl[CTL_NEED] = k_total - (long long)above;
+    }
+    above += c;
+  }
+  if (tid == 0) {
+    ctl[CTL_NUM_ENTRIES] = 0;
+    ctl[CTL_NUM_CAND] = 0;
+  }
+}
+
+// ------------------------------------------------------------------ 4. compaction
+struct Lists {
+  int* ent_tok;    // token index
+  int* ent_col;    // l * F_local_pitch + f_local
+  float* ent_val;  // original pre-activation
+  long long ent_cap;
+  uint32_t* cand_key;
+  int* cand_tok;
+  int* cand_col;
+  float* cand_val;
+  long long cand_cap;
+};
+
+__global__ void __launch_bounds__(256) compact_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+                                                        const float* __restrict__ rstd, ScanGeom g, uint32_t key_lo, int shift,
+                                                        int col_pitch, long long* __restrict__ ctl, Lists o,
+                                                        int* __restrict__ status) {
+  const int l = blockIdx.z;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c0 >= g.F) return;
+  const uint32_t tbin = uint32_t(ctl[CTL_BIN]);
+  float mu[8], rs[8];
+  for (int j = 0; j < 8; ++j) {
+    const bool in = c0 + j < g.F;
+    mu[j] = in ? mean[1LL * l * g.sp + c0 + j] : 0.f;
+    rs[j] = in ? rstd[1LL * l * g.sp + c0 + j] : 0.f;
+  }
+  const int nvalid = min(8, g.F - c0);
+  const int r0 = blockIdx.y * g.rows_per_block;
+  const int r1 = min(g.B, r0 + g.rows_per_block);
+  const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+  unsigned long long* n_ent = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_ENTRIES);
+  unsigned long long* n_cand = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_CAND);
+  for (int r = r0; r < r1; ++r) {
+    const uint4 v = *reinterpret_cast<const uint4*>(base + 1LL * r * g.ld);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+      const float z = (xv - mu[j]) * rs[j];
+      const uint32_t key = float_to_key(z);
+      if (key < key_lo || j >= nvalid) continue;
+      const uint32_t bin = min((key - key_lo) >> shift, uint32_t(kHistBins - 1));
+      if (bin > tbin) {
+        const unsigned long long p = atomicAdd(n_ent, 1ULL);
+        if ((long long)p < o.ent_cap) {
+          o.ent_tok[p] = r; o.ent_col[p] = l * col_pitch + c0 + j; o.ent_val[p] = xv;
+        } else {
+          atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+        }
+      } else if (bin == tbin) {
+        const unsigned long long p = atomicAdd(n_cand, 1ULL);
+        if ((long long)p < o.cand_cap) {
+          o.cand_key[p] = key; o.cand_tok[p] = r; o.cand_col[p] = l * col_pitch + c0 + j; o.cand_val[p] = xv;
+        } else {
+          atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ 5. exact cut inside the bin (one CTA)
+struct FlatGeom {
+  int col_pitch;        // local column pitch used in ent_col / cand_col
+  int feat_offset;      // first global feature of this shard
+  long long full_F;     // un-sharded features per layer
+  long long row_width;  // L * full_F
+};
+__device__ __forceinline__ unsigned long long flat_index(const FlatGeom& fg, int tok, int col) {
+  const int l = col / fg.col_pitch, f = col - l * fg.col_pitch;
+  return (unsigned long long)tok * (unsigned long long)fg.row_width + (unsigned long long)l * fg.full_F + (unsigned long long)(fg.feat_offset + f);
+}
+
+// Picks the digit whose bucket contains the `need`-th element counting from the top (descending=true)
+// or from the bottom (descending=false).  Writes the digit and the remaining need.
+__device__ void pick_digit(const uint32_t* hist, int nb, bool descending, unsigned long long need, int* digit_out,
+                           unsigned long long* need_out) {
+  if (threadIdx.x == 0) {
+    unsigned long long run = 0;
+    int d = descending ? nb - 1 : 0;
+    for (int i = 0; i < nb; ++i) {
+      const int b = descending ? nb - 1 - i : i;
+      const unsigned long long c = hist[b];
+      if (run + c >= need) { d = b; break; }
+      run += c;
+      d = b;
+    }
+    *digit_out = d;
+    *need_out = need - run;
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(1024) refine_kernel(const uint32_t* __restrict__ cand_key, const int* __restrict__ cand_tok,
+                                                        const int* __restrict__ cand_col, long long cand_cap, int shift,
+                                                        FlatGeom fg, long long* __restrict__ ctl, Exchange ex,
+                                                        int* __restrict__ status) {
+  __shared__ uint32_t hist[kRefineBins];
+  __shared__ int digit;
+  __shared__ unsigned long long need;
+  __shared__ int timeout;
+  const int tid = threadIdx.x;
+  long long n = ctl[CTL_NUM_CAND];
+  if (n > cand_cap) n = cand_cap;
+  if (tid == 0) { timeout = 0; need = (unsigned long long)ctl[CTL_NEED]; }
+  __syncthreads();
+  // ---- key cut: radix passes over the low `shift` bits, 9 bits at a time, most significant first.
+  uint32_t prefix = 0, prefix_mask = 0;
+  int round = 1;
+  const uint32_t low_mask = shift >= 32 ? 0xFFFFFFFFu : ((1u << shift) - 1u);
+  for (int hi = shift; hi > 0; hi -= 9, ++round) {
+    const int lo = max(hi - 9, 0);
+    const int nb = 1 << (hi - lo);
+    for (int i = tid; i < kRefineBins; i += 1024) hist[i] = 0;
+    __syncthreads();
+    for (long long i = tid; i < n; i += 1024) {
+      const uint32_t k = cand_key[i] & low_mask;
+      if ((k & prefix_mask) == prefix) atomicAdd(&hist[(k >> lo) & (nb - 1)], 1u);
+    }
+    __syncthreads();
+    if (!exchange_sum(ex, round, hist, kRefineBins, &timeout)) {
+      if (tid == 0) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+      return;
+    }
+    unsigned long long cur = need;
+    __syncthreads();
+    pick_digit(hist, nb, true, cur, &digit, &need);
+    prefix |= uint32_t(digit) << lo;
+    prefix_mask |= uint32_t(nb - 1) << lo;
+    __syncthreads();
+  }
+  // All candidates share the bits above `shift`; recover them from the bin.  `prefix` now holds the low
+  // bits of the cut key T and `need` how many keys equal to T must be kept.
+  // ---- ties: count keys == T (global), then cut by flat index if only part of them is kept.
+  for (int i = tid; i < kRefineBins; i += 1024) hist[i] = 0;
+  __syncthreads();
+  unsigned int local_ties = 0;
+  for (long long i = tid; i < n; i += 1024) local_ties += ((cand_key[i] & low_mask) == prefix) ? 1u : 0u;
+  if (local_ties) atomicAdd(&hist[0], local_ties);
+  __syncthreads();
+  if (!exchange_sum(ex, round++, hist, kRefineBins, &timeout)) {
+    if (tid == 0) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+    return;
+  }
+  const unsigned long long ties = hist[0];
+  __syncthreads();
+  unsigned long long flat_prefix = 0, flat_mask = 0;
+  const bool partial = need < ties;
+  if (partial) {
+    // the `need` smallest flat indices among the ties: radix passes over 45 bits, 9 at a time
+    for (int hi = 45; hi > 0; hi -= 9, ++round) {
+      const int lo = hi - 9;
+      for (int i = tid; i < kRefineBins; i += 1024) hist[i] = 0;
+      __syncthreads();
+      for (long long i = tid; i < n; i += 1024) {
+        if ((cand_key[i] & low_mask) != prefix) continue;
+        const unsigned long long fl = flat_index(fg, cand_tok[i], cand_col[i]);
+        if ((fl & flat_mask) == flat_prefix) atomicAdd(&hist[(fl >> lo) & 511ULL], 1u);
+      }
+      __syncthreads();
+      if (!exchange_sum(ex, round, hist, kRefineBins, &timeout)) {
+        if (tid == 0) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+        return;
+      }
+      unsigned long long cur = need;
+      __syncthreads();
+      pick_digit(hist, 512, false, cur, &digit, &need);
+      flat_prefix |= (unsigned long long)digit << lo;
+      flat_mask |= 511ULL << lo;
+      __syncthreads();
+    }
+  }
+  if (tid == 0) {
+    ctl[CTL_CUT_KEY] = (long long)prefix;  // low bits; compared under low_mask
+    ctl[CTL_TIE_MODE] = partial ? 1 : 0;
+    ctl[CTL_CUT_FLAT] = (long long)flat_prefix;
+  }
+}
+
+// ------------------------------------------------------------------ 6. append the kept candidates
+__global__ void __launch_bounds__(256) finalize_kernel(Lists o, int shift, FlatGeom fg, long long* __restrict__ ctl,
+                                                         int* __restrict__ status) {
+  long long n = ctl[CTL_NUM_CAND];
+  if (n > o.cand_cap) n = o.cand_cap;
+  const uint32_t low_mask = shift >= 32 ? 0xFFFFFFFFu : ((1u << shift) - 1u);
+  const uint32_t cut = uint32_t(ctl[CTL_CUT_KEY]);
+  const bool tie_cut = ctl[CTL_TIE_MODE] != 0;
+  const unsigned long long cut_flat = (unsigned long long)ctl[CTL_CUT_FLAT];
+  unsigned long long* n_ent = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_ENTRIES);
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
+    const uint32_t k = o.cand_key[i] & low_mask;
+    bool keep = k > cut;
+    if (k == cut) keep = !tie_cut || flat_index(fg, o.cand_tok[i], o.cand_col[i]) <= cut_flat;
+    if (keep) {
+      const unsigned long long p = atomicAdd(n_ent, 1ULL);
+      if ((long long)p < o.ent_cap) {
+        o.ent_tok[p] = o.cand_tok[i]; o.ent_col[p] = o.cand_col[i]; o.ent_val[p] = o.cand_val[i];
+      } else {
+        atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ 7. CSR views
+__global__ void __launch_bounds__(256) csr_count_kernel(const int* __restrict__ ent_tok, const int* __restrict__ ent_col,
+                                                          const float* __restrict__ ent_val, long long cap,
+                                                          const long long* __restrict__ ctl, int* __restrict__ tok_cnt,
+                                                          int* __restrict__ feat_cnt, unsigned char* __restrict__ fired) {
+  long long n = ctl[CTL_NUM_ENTRIES];
+  if (n > cap) n = cap;
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
+    atomicAdd(&tok_cnt[ent_tok[i]], 1);
+    const int c = ent_col[i];
+    atomicAdd(&feat_cnt[c], 1);
+    if (fired != nullptr && ent_val[i] > 1e-6f) fired[c] = 1;
+  }
+}
+
+// Exclusive scan of `n` ints by one CTA (1024 threads); out has n+1 entries.  cursor (optional) gets a copy
+// of the offsets for the scatter pass.
+__global__ void __launch_bounds__(1024) exclusive_scan_kernel(const int* __restrict__ in, int* __restrict__ out,
+                                                                int* __restrict__ cursor, int n) {
+  __shared__ int part[1024];
+  const int tid = threadIdx.x;
+  const int per = (n + 1023) / 1024;
+  const int b = min(n, tid * per), e = min(n, b + per);
+  int s = 0;
+  for (int i = b; i < e; ++i) s += in[i];
+  part[tid] = s;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int v = tid >= off ? part[tid - off] : 0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  int run = part[tid] - s;
+  for (int i = b; i < e; ++i) {
+    out[i] = run;
+    if (cursor != nullptr) cursor[i] = run;
+    run += in[i];
+  }
+  if (tid == 1023) out[n] = part[1023];
+}
+
+__global__ void __launch_bounds__(256) csr_scatter_kernel(const int* __restrict__ ent_tok, const int* __restrict__ ent_col,
+                                                            const float* __restrict__ ent_val, long long cap,
+                                                            const long long* __restrict__ ctl, int* __restrict__ tok_cursor,
+                                                            int* __restrict__ feat_cursor, int* __restrict__ tcsr_col,
+                                                            float* __restrict__ tcsr_val, int* __restrict__ fcsr_tok,
+                                                            float* __restrict__ fcsr_val) {
+  long long n = ctl[CTL_NUM_ENTRIES];
+  if (n > cap) n = cap;
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
+    const int t = ent_tok[i], c = ent_col[i];
+    const float v = ent_val[i];
+    const int p = atomicAdd(&tok_cursor[t], 1);
+    tcsr_col[p] = c; tcsr_val[p] = v;
+    const int q = atomicAdd(&feat_cursor[c], 1);
+    fcsr_tok[q] = t; fcsr_val[q] = v;
+  }
+}
+
+// Sort every CSR segment by its integer key (segments are short: insertion sort by one thread), so the
+// order of the entries - and with it every floating-point sum over a segment - is reproducible.
+__global__ void __launch_bounds__(256) csr_sort_segments_kernel(const int* __restrict__ off, int nseg, int* __restrict__ key,
+                                                                  float* __restrict__ val) {
+  for (int sidx = blockIdx.x * blockDim.x + threadIdx.x; sidx < nseg; sidx += gridDim.x * blockDim.x) {
+    const int b = off[sidx], e = off[sidx + 1];
+    for (int i = b + 1; i < e; ++i) {
+      const int k = key[i];
+      const float v = val[i];
+      int j = i - 1;
+      while (j >= b && key[j] > k) { key[j + 1] = key[j]; val[j + 1] = val[j]; --j; }
+      key[j + 1] = k; val[j + 1] = v;
+    }
+  }
+}
+
+// Dead-feature counters: +1 per step, reset where the feature fired (reference trainer.py:693-712).
+__global__ void __launch_bounds__(256) dead_counter_kernel(long long* __restrict__ counter, unsigned char* __restrict__ fired, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    counter[i] = fired[i] ? 0 : counter[i] + 1;
+    fired[i] = 0;
+  }
+}
+
+}  // namespace clt
+
+// ====================================================================== C launchers
+using namespace clt;
+
+extern "C" int clt_colstats(const void* x, float* mean, float* rstd, int L, int B, int F, long long ld, long long layer_stride,
+                            cudaStream_t st) {
+  if (F % 8 != 0 || ld % 8 != 0 || layer_stride % 8 != 0) return -1;
+  dim3 grid((F / 8 + 31) / 32, L), block(32, 8);
+  colstats_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16*>(x), mean, rstd, B, F, ld, layer_stride);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+struct CltExchangeArgs {
+  int world;
+  int rank;
+  void* data[8];
+  void* flags[8];
+  int slot_elems;
+  unsigned int seq;
+};
+
+static Exchange to_exchange(const CltExchangeArgs* a) {
+  Exchange ex;
+  ex.world = a ? a->world : 1;
+  ex.rank = a ? a->rank : 0;
+  ex.slot_elems = a ? a->slot_elems : 0;
+  ex.seq = a ? a->seq : 0;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    ex.peers[i] = a ? static_cast<uint32_t*>(a->data[i]) : nullptr;
+    ex.flags[i] = a ? static_cast<uint32_t*>(a->flags[i]) : nullptr;
+  }
+  return ex;
+}
+
+struct CltSelectArgs {
+  const void* x;  // [L, B, ld] bf16 pre-activations
+  const float* mean;
+  const float* rstd;
+  int L, B, F;  // F: valid local features per layer
+  int stat_pitch;  // row pitch of mean / rstd
+  long long ld, layer_stride;
+  int col_pitch;       // pitch used to encode columns (l * col_pitch + f)
+  int feat_offset;     // first global feature of the shard
+  long long full_F;    // un-sharded feature count
+  long long k_total;   // global number of entries to keep
+  unsigned int key_lo; // histogram covers keys >= key_lo
+  int shift;           // bin = (key - key_lo) >> shift
+  unsigned int* hist;  // [8192], zeroed by the caller
+  long long* ctl;      // [CTL_SIZE]
+  int* ent_tok; int* ent_col; float* ent_val; long long ent_cap;
+  unsigned int* cand_key; int* cand_tok; int* cand_col; float* cand_val; long long cand_cap;
+  int* status;
+};
+
+static ScanGeom scan_geom(const CltSelectArgs* a) {
+  ScanGeom g;
+  g.B = a->B; g.F = a->F; g.L = a->L; g.sp = a->stat_pitch; g.ld = a->ld; g.layer_stride = a->layer_stride;
+  g.rows_per_block = 64;
+  return g;
+}
+static Lists lists_of(const CltSelectArgs* a) {
+  Lists o;
+  o.ent_tok = a->ent_tok; o.ent_col = a->ent_col; o.ent_val = a->ent_val; o.ent_cap = a->ent_cap;
+  o.cand_key = a->cand_key; o.cand_tok = a->cand_tok; o.cand_col = a->cand_col; o.cand_val = a->cand_val; o.cand_cap = a->cand_cap;
+  return o;
+}
+static FlatGeom flat_geom(const CltSelectArgs* a) {
+  FlatGeom fg;
+  fg.col_pitch = a->col_pitch; fg.feat_offset = a->feat_offset; fg.full_F = a->full_F; fg.row_width = a->full_F * a->L;
+  return fg;
+}
+
+// Steps 2-6.  `ex` may be null (single rank).
+extern "C" int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st) {
+  if (a->ld % 8 != 0 || a->layer_stride % 8 != 0 || a->stat_pitch % 4 != 0 || a->F > a->ld) return -1;
+  const ScanGeom g = scan_geom(a);
+  const Exchange ex = to_exchange(exa);
+  dim3 grid(((a->F + 7) / 8 + 255) / 256, (a->B + g.rows_per_block - 1) / g.rows_per_block, a->L);
+  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(a->x);
+  zhist_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->key_lo, a->shift, a->hist);
+  find_bin_kernel<<<1, 1024, 0, st>>>(a->hist, a->k_total, a->ctl, ex, a->status);
+  compact_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->key_lo, a->shift, a->col_pitch, a->ctl, lists_of(a), a->status);
+  refine_kernel<<<1, 1024, 0, st>>>(a->cand_key, a->cand_tok, a->cand_col, a->cand_cap, a->shift, flat_geom(a), a->ctl, ex, a->status);
+  finalize_kernel<<<256, 256, 0, st>>>(lists_of(a), a->shift, flat_geom(a), a->ctl, a->status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+struct CltCsrArgs {
+  const int* ent_tok; const int* ent_col; const float* ent_val; long long ent_cap;
+  const long long* ctl;
+  int num_tokens; int num_cols;
+  int* tok_cnt; int* feat_cnt;        // zeroed by the caller
+  int* tok_off; int* feat_off;        // [num_tokens+1], [num_cols+1]
+  int* tok_cursor; int* feat_cursor;  // scratch
+  int* tcsr_col; float* tcsr_val; int* fcsr_tok; float* fcsr_val;
+  unsigned char* fired;               // optional [num_cols]
+  int sort_segments;                  // bit 0: token segments, bit 1: feature segments
+};
+
+extern "C" int clt_build_csr(const CltCsrArgs* a, cudaStream_t st) {
+  const int blocks = 592;
+  csr_count_kernel<<<blocks, 256, 0, st>>>(a->ent_tok, a->ent_col, a->ent_val, a->ent_cap, a->ctl, a->tok_cnt, a->feat_cnt, a->fired);
+  exclusive_scan_kernel<<<1, 1024, 0, st>>>(a->tok_cnt, a->tok_off, a->tok_cursor, a->num_tokens);
+  exclusive_scan_kernel<<<1, 1024, 0, st>>>(a->feat_cnt, a->feat_off, a->feat_cursor, a->num_cols);
+  csr_scatter_kernel<<<blocks, 256, 0, st>>>(a->ent_tok, a->ent_col, a->ent_val, a->ent_cap, a->ctl, a->tok_cursor, a->feat_cursor,
+                                             a->tcsr_col, a->tcsr_val, a->fcsr_tok, a->fcsr_val);
+  if (a->sort_segments & 1)
+    csr_sort_segments_kernel<<<(a->num_tokens + 255) / 256, 256, 0, st>>>(a->tok_off, a->num_tokens, a->tcsr_col, a->tcsr_val);
+  if (a->sort_segments & 2)
+    csr_sort_segments_kernel<<<(a->num_cols + 255) / 256, 256, 0, st>>>(a->feat_off, a->num_cols, a->fcsr_tok, a->fcsr_val);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int clt_dead_counter_update(long long* counter, unsigned char* fired, int n, cudaStream_t st) {
+  dead_counter_kernel<<<(n + 255) / 256, 256, 0, st>>>(counter, fired, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

@@ -1,0 +1,364 @@
+"""Fused sm_100a training / inference step for (Batch)TopK transcoders.
+
+One step is a fixed sequence of hand-written kernels and never materialises a dense
+``[B, L*F]`` activation tensor or a gradient tensor:
+
+====  =====================================  ============================================
+ #    kernel (csrc/)                         replaces in the reference
+====  =====================================  ============================================
+ 1    encoder_gemm  (tcgen05 + TMA)          L x F.linear + all_gather, run 2-4x per step
+ 2    colstats                               per-layer mean/std temporaries
+ 3    batchtopk_select                       torch.topk over B*L*F + mask + multiply
+ 4    build_csr                              (dense mask is the reference's data structure)
+ 5    sparse_decode (+ loss epilogue)        P dense decoder GEMMs + P all-reduces + MSELoss
+ 6    sparsity_penalty                       dense tanh over [B, F] per layer
+ 7    decoder_rows_adam                      autograd decoder GEMMs + AdamW over 1.5 B params
+ 8    encoder_rows_adam                      autograd encoder GEMMs + AdamW
+ 9    dense_adam / dead_counter_update       small tensors, dead-feature bookkeeping
+====  =====================================  ============================================
+
+(reference call stack: clt/training/trainer.py:661-810, clt/training/losses.py:331-407).
+
+Tensor parallel (features sharded over the ranks): kernels 1-4 and 6-9 run on the shard;
+the selection threshold is agreed through in-kernel histogram exchanges over peer memory
+(``parallel/symm.py``), and the partial reconstructions are summed across ranks before the
+loss epilogue.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import CLTConfig, TrainingConfig
+from ..ops import ext
+from ..parallel import ops as pops
+
+STATUS_NAMES = {0: "ok", 1: "wait timeout", 2: "list capacity exceeded", 3: "threshold outside histogram range", 4: "tie overflow"}
+
+
+def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingConfig], model=None) -> Optional[str]:
+    """``None`` when the fused step covers this configuration, else the reason it does not."""
+    if clt_config.activation_fn != "batchtopk":
+        return f"activation_fn={clt_config.activation_fn!r} (fused step covers batchtopk)"
+    if clt_config.topk_mode != "global":
+        return "topk_mode='per_layer'"
+    if clt_config.skip_connection:
+        return "skip_connection"
+    if clt_config.enable_feature_offset or clt_config.enable_feature_scale:
+        return "feature offset/scale"
+    if clt_config.d_model % 8 != 0 or clt_config.d_model > 2048:
+        return "d_model must be a multiple of 8 and <= 2048"
+    if clt_config.num_layers > 32:
+        return "more than 32 layers"
+    if model is not None:
+        if model.dtype != torch.bfloat16:
+            return f"model dtype {model.dtype} (fused step needs bf16 weights)"
+        if model.local_features % 8 != 0:
+            return "local feature count must be a multiple of 8"
+    if training_config is not None:
+        if training_config.gradient_clip_val is not None:
+            return "gradient clipping"
+        if training_config.aux_loss_factor:
+            # AuxK is evaluated by the autograd path whenever dead features exist; the
+            # fused step handles the (common) steps without dead features.
+            pass
+        if training_config.precision == "fp16":
+            return "fp16 loss scaling"
+    return None
+
+
+@dataclass
+class StepOutput:
+    """Device scalars of one step; nothing here forces a host sync."""
+
+    reconstruction: torch.Tensor
+    sparsity: torch.Tensor
+    preactivation: torch.Tensor
+    auxiliary: torch.Tensor
+    total: torch.Tensor
+    num_entries: torch.Tensor
+
+    def as_dict(self) -> Dict[str, torch.Tensor]:
+        return {
+            "total": self.total, "reconstruction": self.reconstruction, "sparsity": self.sparsity,
+            "preactivation": self.preactivation, "auxiliary": self.auxiliary,
+        }
+
+
+class FusedBatchTopKEngine:
+    def __init__(
+        self,
+        model,
+        training_config: Optional[TrainingConfig],
+        batch_tokens: int,
+        sigma_tg: Optional[torch.Tensor] = None,
+        symm=None,
+    ):
+        reason = engine_supports(model.config, training_config, model)
+        if reason is not None:
+            raise ValueError(f"fused engine does not cover this configuration: {reason}")
+        if not torch.cuda.is_available():
+            raise RuntimeError("the fused engine needs a CUDA device")
+        self.ext = ext.load()
+        self.model = model
+        self.tc = training_config
+        cfg = model.config
+        self.cfg = cfg
+        self.L, self.d, self.F = cfg.num_layers, cfg.d_model, cfg.num_features
+        self.B = int(batch_tokens)
+        self.Fl = model.local_features
+        self.Fv = model.valid_features
+        self.world = model.world_size
+        self.rank = model.rank
+        self.group = model.process_group if self.world > 1 else None
+        self.symm = symm
+        self.dev = model.enc_weight.device
+        self.tying = {"none": 0, "per_source": 1, "per_target": 2}[cfg.decoder_tying]
+        dev = self.dev
+        L, B, d, Fl = self.L, self.B, self.d, self.Fl
+        i32, f32 = torch.int32, torch.float32
+
+        self.k_total = min(int(cfg.batchtopk_k) * B, B * L * self.F)
+        # positive-z histogram when fewer than a quarter of the elements are kept, else full range
+        if self.k_total * 4 <= B * L * self.F:
+            self.key_lo, self.shift = 0x80000000, 18
+        else:
+            self.key_lo, self.shift = 0, 19
+        self.preact = torch.empty(L, B, Fl, dtype=torch.bfloat16, device=dev)
+        self.mean = torch.empty(L, Fl, dtype=f32, device=dev)
+        self.rstd = torch.empty(L, Fl, dtype=f32, device=dev)
+        self.hist = torch.zeros(8192, dtype=i32, device=dev)
+        self.ctl = torch.zeros(16, dtype=torch.int64, device=dev)
+        self.status = torch.zeros(4, dtype=i32, device=dev)
+        cap = max(self.k_total, 8)
+        self.cap = cap
+        numel_local = B * L * max(self.Fv, 1)
+        cand_cap = int(min(numel_local, max(1 << 20, 4 * self.k_total, 1 << 23)))
+        self.ent_tok = torch.empty(cap, dtype=i32, device=dev)
+        self.ent_col = torch.empty(cap, dtype=i32, device=dev)
+        self.ent_val = torch.empty(cap, dtype=f32, device=dev)
+        self.cand_key = torch.empty(cand_cap, dtype=i32, device=dev)
+        self.cand_tok = torch.empty(cand_cap, dtype=i32, device=dev)
+        self.cand_col = torch.empty(cand_cap, dtype=i32, device=dev)
+        self.cand_val = torch.empty(cand_cap, dtype=f32, device=dev)
+        ncols = L * Fl
+        self.ncols = ncols
+        self.tok_cnt = torch.zeros(B, dtype=i32, device=dev)
+        self.feat_cnt = torch.zeros(ncols, dtype=i32, device=dev)
+        self.tok_off = torch.zeros(B + 1, dtype=i32, device=dev)
+        self.feat_off = torch.zeros(ncols + 1, dtype=i32, device=dev)
+        self.tok_cursor = torch.zeros(B, dtype=i32, device=dev)
+        self.feat_cursor = torch.zeros(ncols, dtype=i32, device=dev)
+        self.tcsr_col = torch.zeros(cap, dtype=i32, device=dev)
+        self.tcsr_val = torch.zeros(cap, dtype=f32, device=dev)
+        self.fcsr_tok = torch.zeros(cap, dtype=i32, device=dev)
+        self.fcsr_val = torch.zeros(cap, dtype=f32, device=dev)
+        self.fired = torch.zeros(ncols, dtype=torch.uint8, device=dev)
+        self.dead_counter = torch.zeros(ncols, dtype=torch.int64, device=dev)
+        self.gs = torch.empty(L, B, d, dtype=torch.bfloat16, device=dev)
+        self.sq_err = torch.zeros(L, dtype=torch.float64, device=dev)
+        self.penalty = torch.zeros(1, dtype=torch.float64, device=dev)
+        self.gs_sum = torch.zeros(L, d, dtype=f32, device=dev)
+        self.grad_a = torch.zeros(cap, dtype=f32, device=dev)
+        self.pen_coef = torch.zeros(ncols, dtype=f32, device=dev)
+        self.norm2 = torch.zeros(ncols, dtype=f32, device=dev)      # per decoder tensor rows
+        self.norm2_next = torch.zeros(ncols, dtype=f32, device=dev)
+        self.norms_valid = False
+        self.yhat_partial = torch.empty(L, B, d, dtype=f32, device=dev) if self.world > 1 else None
+        self.sigma = None
+        if sigma_tg is not None:
+            self.sigma = sigma_tg.to(device=dev, dtype=f32).reshape(L, d).contiguous()
+        # target t receives the bias of every pair (s <= t) when untied / per_source, one bias when per_target
+        if self.tying == 0:
+            sel = torch.zeros(L, model.num_pairs, dtype=f32, device=dev)
+            from ..models.clt import pair_index
+
+            for t in range(L):
+                for s in range(t + 1):
+                    sel[t, pair_index(s, t, L)] = 1.0
+        elif self.tying == 1:
+            sel = torch.tril(torch.ones(L, L, dtype=f32, device=dev))
+        else:
+            sel = torch.eye(L, dtype=f32, device=dev)
+        self.bias_sel = sel  # [L targets, n_bias]
+
+        # optimizer state (fp32 moments)
+        self.opt_state: Dict[str, torch.Tensor] = {}
+        if training_config is not None:
+            z = lambda p: torch.zeros_like(p, dtype=f32)  # noqa: E731
+            self.enc_m, self.enc_v = z(model.enc_weight), z(model.enc_weight)
+            self.encb_m, self.encb_v = z(model.enc_bias), z(model.enc_bias)
+            self.dec_m = [z(w) for w in model.dec_weight]
+            self.dec_v = [z(w) for w in model.dec_weight]
+            self.decb_m, self.decb_v = z(model.dec_bias), z(model.dec_bias)
+        self.opt_step = 0
+        self.seq = 0
+
+    # ------------------------------------------------------------------ pieces
+    def _exchange_args(self):
+        if self.world <= 1 or self.symm is None:
+            return 1, 0, [], [], 0, 0
+        self.seq += 1
+        return (self.world, self.rank, self.symm.hist_data_ptrs, self.symm.hist_flag_ptrs, self.symm.slot_elems, self.seq)
+
+    def encode_select(self, X: torch.Tensor) -> None:
+        """Kernels 1-4: pre-activations, batch statistics, global BatchTopK, CSR views."""
+        e = self.ext
+        m = self.model
+        assert X.dtype == torch.bfloat16 and X.shape == (self.L, self.B, self.d), (X.dtype, X.shape)
+        e.encoder_gemm(X, m.enc_weight.data, m.enc_bias.data, self.preact, self.status)
+        e.colstats(self.preact, self.mean, self.rstd)
+        self.hist.zero_()
+        world, rank, dptr, fptr, slot, seq = self._exchange_args()
+        if self.world > 1 and self.symm is None:
+            raise RuntimeError("tensor-parallel fused engine needs a symmetric exchange area (parallel.symm)")
+        e.batchtopk_select(
+            self.preact, self.mean, self.rstd, self.Fv, self.Fl, m.feature_start, self.F, self.k_total,
+            self.key_lo, self.shift, self.hist, self.ctl, self.ent_tok, self.ent_col, self.ent_val,
+            self.cand_key, self.cand_tok, self.cand_col, self.cand_val, self.status,
+            world, rank, dptr, fptr, slot, seq,
+        )
+        self.tok_cnt.zero_()
+        self.feat_cnt.zero_()
+        e.build_csr(
+            self.ent_tok, self.ent_col, self.ent_val, self.ctl, self.B, self.ncols,
+            self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
+            self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2,
+        )
+
+    def _bias_sum(self) -> torch.Tensor:
+        return (self.bias_sel @ self.model.dec_bias.data.float()).contiguous()
+
+    def decode_loss(self, Y: torch.Tensor, want_yhat: bool = False) -> Optional[torch.Tensor]:
+        """Kernel 5: sparse decode, reconstruction loss sums and the gradient seed."""
+        e, m = self.ext, self.model
+        self.sq_err.zero_()
+        yhat = torch.empty(self.L, self.B, self.d, dtype=torch.float32, device=self.dev) if want_yhat else None
+        dec_w = [w.data for w in m.dec_weight]
+        bias_sum = self._bias_sum()
+        if self.world == 1:
+            e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
+                            None, None, None, bias_sum, None, Y, self.sigma, self.gs, yhat, self.sq_err, 1)
+        else:
+            e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
+                            None, None, self.yhat_partial, None, None, None, None, None, None, None, 0)
+            if self.symm is not None and self.symm.supports_reduce:
+                self.symm.all_reduce_sum_(self.yhat_partial)
+            else:
+                pops.all_reduce(self.yhat_partial, group=self.group)
+            e.recon_epilogue(self.yhat_partial, bias_sum, None, Y, self.sigma, self.gs, yhat, self.sq_err, 0, self.B)
+        return yhat
+
+    def _hyper(self, lr: float, grad_scale: float) -> List[float]:
+        tc = self.tc
+        b1 = tc.optimizer_beta1 if tc.optimizer_beta1 is not None else 0.9
+        b2 = tc.optimizer_beta2 if tc.optimizer_beta2 is not None else 0.999
+        decoupled = 1.0 if tc.optimizer == "adamw" else 0.0
+        wd = 0.01 if tc.optimizer == "adamw" else 0.0
+        t = self.opt_step
+        seed = 0.0
+        if tc.enable_stochastic_rounding:
+            seed = float(((tc.seed * 2654435761 + t * 40503) % 0xFFFFFFFE) + 1)
+        return [lr, b1, b2, 1e-8, wd, 1.0 - b1 ** t, 1.0 - b2 ** t, decoupled, grad_scale, seed]
+
+    def ensure_norms(self) -> None:
+        if self.norms_valid:
+            return
+        for i, w in enumerate(self.model.dec_weight):
+            self.ext.decoder_norm2(w.data, self.norm2[i * self.Fl:(i + 1) * self.Fl])
+        self.norms_valid = True
+
+    def feature_norm2(self) -> torch.Tensor:
+        """Squared decoder norm per (layer, feature) column of this shard."""
+        self.ensure_norms()
+        if self.tying == 2:
+            per_t = self.norm2.view(self.L, self.Fl)
+            return torch.flip(torch.cumsum(torch.flip(per_t, dims=[0]), dim=0), dims=[0]).reshape(-1).contiguous()
+        return self.norm2
+
+    # -------------------------------------------------------------------- step
+    def train_step(self, X: torch.Tensor, Y: torch.Tensor, step: int, lr: float, sparsity_lambda: float = 0.0) -> StepOutput:
+        """One optimisation step on inputs/targets ``[L, B, d]`` (bf16, already normalised)."""
+        e, m, tc = self.ext, self.model, self.tc
+        L, B, d = self.L, self.B, self.d
+        self.opt_step += 1
+        self.encode_select(X)
+        self.decode_loss(Y)
+        c_g = 2.0 / (B * d)
+        # decoder biases: dL/db[pair (s,t)] = c_g * sum_b gs[t, b, :]
+        self.gs_sum.zero_()
+        e.gs_colsum(self.gs, self.gs_sum)
+        bias_grad = (self.bias_sel.t() @ self.gs_sum).contiguous()
+        self.grad_a.zero_()
+        self.penalty.zero_()
+        pen = None
+        use_pen = sparsity_lambda > 1e-9 and (tc.apply_sparsity_penalty_to_batchtopk if tc is not None else True)
+        if use_pen:
+            e.sparsity_penalty(self.feat_off, self.fcsr_val, self.feature_norm2(), float(sparsity_lambda), float(tc.sparsity_c),
+                               self.grad_a, self.pen_coef, self.penalty)
+            pen = self.pen_coef
+        self.norm2_next.zero_()
+        e.decoder_rows_adam([w.data for w in m.dec_weight], self.dec_m, self.dec_v, L, B, d, self.Fl, self.tying,
+                            self.feat_off, self.fcsr_tok, self.fcsr_val, self.gs, self.grad_a, pen, self.norm2_next,
+                            None, None, self._hyper(lr, c_g))
+        self.norm2, self.norm2_next = self.norm2_next, self.norm2
+        self.norms_valid = True
+        e.dense_adam(m.dec_bias.data, self.decb_m, self.decb_v, bias_grad, self._hyper(lr, c_g))
+        e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v,
+                            self.feat_off, self.fcsr_tok, self.grad_a, X, None, None, self._hyper(lr, 1.0))
+        e.dead_counter_update(self.dead_counter, self.fired)
+        m.invalidate_decoder_norms()
+        recon = (self.sq_err.sum() / (B * d)).float()
+        sparsity = self.penalty[0].float()
+        if self.world > 1 and use_pen:
+            sp = sparsity.clone()
+            pops.all_reduce(sp, group=self.group)
+            sparsity = sp
+        zero = torch.zeros((), device=self.dev)
+        return StepOutput(recon, sparsity, zero, zero, recon + sparsity, self.ctl[3])
+
+    # --------------------------------------------------------------- inference
+    @torch.no_grad()
+    def forward(self, X: torch.Tensor, Y: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Reconstructions ``[L, B, d]`` (fp32) for inputs ``X``; ``Y`` defaults to zeros."""
+        self.encode_select(X)
+        if Y is None:
+            Y = torch.zeros_like(X)
+        return self.decode_loss(Y, want_yhat=True)
+
+    def activations_dense(self) -> torch.Tensor:
+        """Dense ``[L, B, F_local]`` view of the last selection (testing / evaluation)."""
+        n = int(self.ctl[3].item())
+        out = torch.zeros(self.L, self.B, self.Fl, dtype=torch.float32, device=self.dev)
+        col = self.ent_col[:n].long()
+        l, f = col // self.Fl, col % self.Fl
+        out[l, self.ent_tok[:n].long(), f] = self.ent_val[:n]
+        return out
+
+    def check_status(self) -> None:
+        """Host read of the kernels' status word; raises when a kernel reported a problem."""
+        code = int(self.status[0].item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"rank {self.rank}: fused step reported '{STATUS_NAMES.get(code, code)}'")
+
+    # ------------------------------------------------------- optimizer state io
+    def optimizer_state_dict(self) -> Dict[str, torch.Tensor]:
+        sd = {"step": torch.tensor(self.opt_step), "enc_m": self.enc_m, "enc_v": self.enc_v, "encb_m": self.encb_m,
+              "encb_v": self.encb_v, "decb_m": self.decb_m, "decb_v": self.decb_v, "dead_counter": self.dead_counter}
+        for i, (mm, vv) in enumerate(zip(self.dec_m, self.dec_v)):
+            sd[f"dec_m.{i}"] = mm
+            sd[f"dec_v.{i}"] = vv
+        return sd
+
+    def load_optimizer_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
+        self.opt_step = int(sd["step"])
+        for name in ("enc_m", "enc_v", "encb_m", "encb_v", "decb_m", "decb_v", "dead_counter"):
+            getattr(self, name).copy_(sd[name])
+        for i in range(len(self.dec_m)):
+            self.dec_m[i].copy_(sd[f"dec_m.{i}"])
+            self.dec_v[i].copy_(sd[f"dec_v.{i}"])
+        self.norms_valid = False

@@ -1,0 +1,305 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from crosslayer_coding_b200.ops import ext as ext_mod
+
+    return ext_mod.load()
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+@pytest.mark.parametrize(
+    "L,M,N,K",
+    [(1, 128, 256, 64), (2, 300, 520, 136), (1, 256, 512, 768), (3, 130, 8, 72), (1, 4096, 1024, 768)],
+)
+def test_encoder_gemm_matches_fp32(ext, L, M, N, K):
+    torch.manual_seed(0)
+    dev = _dev()
+    x = torch.randn(L, M, K, device=dev).bfloat16()
+    w = (torch.randn(L, N, K, device=dev) / math.sqrt(K)).bfloat16()
+    b = torch.randn(L, N, device=dev).bfloat16()
+    out = torch.full((L, M, N), float("nan"), device=dev, dtype=torch.bfloat16)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    ext.encoder_gemm(x, w, b, out, status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    ref = torch.einsum("lmk,lnk->lmn", x.float(), w.float()) + b.float()[:, None, :]
+    err = (out.float() - ref).abs().max().item()
+    assert torch.isfinite(out.float()).all()
+    assert err < 0.03 * max(1.0, ref.abs().max().item()), err
+    # bf16 rounding of an fp32 accumulation: relative error of a few 1e-3
+    rel = ((out.float() - ref).norm() / ref.norm()).item()
+    assert rel < 4e-3, rel
+
+
+def test_colstats(ext):
+    torch.manual_seed(1)
+    dev = _dev()
+    L, B, F = 3, 257, 72
+    x = (torch.randn(L, B, F, device=dev) * 2 + 5).bfloat16()
+    mean = torch.empty(L, F, device=dev)
+    rstd = torch.empty(L, F, device=dev)
+    ext.colstats(x, mean, rstd)
+    xf = x.float()
+    assert torch.allclose(mean, xf.mean(dim=1), atol=1e-4, rtol=1e-5)
+    assert torch.allclose(rstd, 1.0 / (xf.std(dim=1) + 1e-6), rtol=1e-4)
+
+
+def _run_select(ext, x, k_total, f_valid=None, feat_offset=0, full_F=None, full_range=False, cand_cap=None):
+    dev = x.device
+    L, B, Fl = x.shape
+    f_valid = Fl if f_valid is None else f_valid
+    full_F = Fl if full_F is None else full_F
+    mean = torch.empty(L, Fl, device=dev)
+    rstd = torch.empty(L, Fl, device=dev)
+    ext.colstats(x, mean, rstd)
+    hist = torch.zeros(8192, dtype=torch.int32, device=dev)
+    ctl = torch.zeros(16, dtype=torch.int64, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    cap = max(k_total, 8)
+    cc = cand_cap or x.numel()
+    i32, f32 = torch.int32, torch.float32
+    ent = [torch.empty(cap, dtype=i32, device=dev), torch.empty(cap, dtype=i32, device=dev), torch.empty(cap, dtype=f32, device=dev)]
+    cand = [torch.empty(cc, dtype=i32, device=dev), torch.empty(cc, dtype=i32, device=dev), torch.empty(cc, dtype=i32, device=dev),
+            torch.empty(cc, dtype=f32, device=dev)]
+    key_lo, shift = (0, 19) if full_range else (0x80000000, 18)
+    ext.batchtopk_select(x, mean, rstd, f_valid, Fl, feat_offset, full_F, k_total, key_lo, shift, hist, ctl,
+                         ent[0], ent[1], ent[2], cand[0], cand[1], cand[2], cand[3], status, 1, 0, [], [], 0, 0)
+    torch.cuda.synchronize()
+    return mean, rstd, ctl, status, ent
+
+
+def _oracle_mask(x, mean, rstd, k_total, f_valid):
+    """Top k_total of z = (x - mean) * rstd over [B, L*F] with lowest-flat-index tie-break."""
+    L, B, Fl = x.shape
+    z = (x.float() - mean[:, None, :]) * rstd[:, None, :]
+    z = z[:, :, :f_valid]
+    flat = z.permute(1, 0, 2).reshape(-1)  # token-major: b, l, f
+    _, order = torch.sort(flat, descending=True, stable=True)
+    mask = torch.zeros_like(flat, dtype=torch.bool)
+    mask[order[:k_total]] = True
+    return mask.view(B, L, f_valid).permute(1, 0, 2)
+
+
+@pytest.mark.parametrize("full_range", [False, True])
+@pytest.mark.parametrize("L,B,F,k", [(2, 64, 128, 5), (3, 200, 264, 17), (1, 33, 40, 3)])
+def test_batchtopk_select_matches_oracle(ext, L, B, F, k, full_range):
+    torch.manual_seed(2)
+    dev = _dev()
+    x = torch.randn(L, B, F, device=dev).bfloat16()
+    k_total = k * B
+    mean, rstd, ctl, status, ent = _run_select(ext, x, k_total, full_range=full_range)
+    assert int(status[0]) == 0
+    n = int(ctl[3])
+    assert n == k_total
+    got = torch.zeros(L, B, F, dtype=torch.bool, device=dev)
+    col = ent[1][:n].long()
+    got[col // F, ent[0][:n].long(), col % F] = True
+    assert int(got.sum()) == n, "duplicate entries"
+    want = _oracle_mask(x, mean, rstd, k_total, F)
+    assert torch.equal(got, want)
+    vals = x.float()[col // F, ent[0][:n].long(), col % F]
+    assert torch.equal(vals, ent[2][:n])
+
+
+def test_batchtopk_select_ties_use_lowest_flat_index(ext):
+    dev = _dev()
+    L, B, F = 2, 16, 64
+    # two distinct values only: massive ties at the cut
+    x = torch.zeros(L, B, F, device=dev)
+    x[:, ::2, :] = 1.0
+    x = x.bfloat16()
+    k_total = 3 * B + 5
+    mean, rstd, ctl, status, ent = _run_select(ext, x, k_total)
+    assert int(status[0]) == 0
+    n = int(ctl[3])
+    assert n == k_total
+    got = torch.zeros(L, B, F, dtype=torch.bool, device=dev)
+    col = ent[1][:n].long()
+    got[col // F, ent[0][:n].long(), col % F] = True
+    want = _oracle_mask(x, mean, rstd, k_total, F)
+    assert torch.equal(got, want)
+
+
+def test_batchtopk_select_respects_valid_columns(ext):
+    torch.manual_seed(3)
+    dev = _dev()
+    L, B, Fl, Fv = 2, 48, 64, 52
+    x = torch.randn(L, B, Fl, device=dev)
+    x[:, :, Fv:] = 100.0  # padding columns must never be selected
+    x = x.bfloat16()
+    k_total = 4 * B
+    mean, rstd, ctl, status, ent = _run_select(ext, x, k_total, f_valid=Fv, feat_offset=7, full_F=Fv + 7)
+    n = int(ctl[3])
+    assert n == k_total and int(status[0]) == 0
+    col = ent[1][:n].long()
+    assert int((col % Fl).max()) < Fv
+    got = torch.zeros(L, B, Fv, dtype=torch.bool, device=dev)
+    got[col // Fl, ent[0][:n].long(), col % Fl] = True
+    assert torch.equal(got, _oracle_mask(x, mean, rstd, k_total, Fv))
+
+
+def _engine_and_model(L=3, d=64, F=256, B=96, k=8, tying="none", seed=0, lr_cfg=None):
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder, TrainingConfig
+    from crosslayer_coding_b200.training.fused_engine import FusedBatchTopKEngine
+
+    torch.manual_seed(seed)
+    dev = _dev()
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="batchtopk", batchtopk_k=k,
+                    clt_dtype="bfloat16", decoder_tying=tying)
+    model = CrossLayerTranscoder(cfg, device=dev)
+    if tying != "none":
+        with torch.no_grad():
+            for w in model.dec_weight:
+                w.uniform_(-0.05, 0.05)
+    tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="bf16",
+                        sparsity_lambda=0.0, preactivation_coef=0.0, optimizer="adamw", **(lr_cfg or {}))
+    eng = FusedBatchTopKEngine(model, tc, B)
+    X = torch.randn(L, B, d, device=dev).bfloat16()
+    Y = torch.randn(L, B, d, device=dev).bfloat16()
+    return cfg, model, tc, eng, X, Y
+
+
+@pytest.mark.parametrize("tying", ["none", "per_source", "per_target"])
+def test_sparse_decode_and_loss_match_dense(tying):
+    cfg, model, tc, eng, X, Y = _engine_and_model(tying=tying)
+    yhat = eng.forward(X, Y)
+    torch.cuda.synchronize()
+    eng.check_status()
+    acts = eng.activations_dense()  # [L, B, F]
+    L = cfg.num_layers
+    ref_model = _fp32_copy(model)
+    a = {l: acts[l] for l in range(L)}
+    for t in range(L):
+        ref = ref_model.decode({s: a[s] for s in range(t + 1)}, t)
+        assert torch.allclose(yhat[t], ref, atol=2e-3, rtol=2e-3), (t, (yhat[t] - ref).abs().max())
+    # loss sums and gradient seed
+    sq = torch.stack([((yhat[t] - Y[t].float()) ** 2).sum() for t in range(L)]).double()
+    assert torch.allclose(eng.sq_err, sq, rtol=1e-3)
+    assert torch.allclose(eng.gs.float(), (yhat - Y.float()), atol=2e-2, rtol=1e-2)
+    # the selection itself equals the PyTorch model's BatchTopK on the same pre-activations
+    want = _oracle_mask(eng.preact, eng.mean, eng.rstd, eng.k_total, cfg.num_features)
+    assert torch.equal(acts != 0, want & (eng.preact.float() != 0))
+
+
+def _fp32_copy(model):
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder
+
+    cfg = CLTConfig(**{**model.config.to_dict(), "clt_dtype": "float32"})
+    ref = CrossLayerTranscoder(cfg, device=model.enc_weight.device)
+    with torch.no_grad():
+        ref.enc_weight.copy_(model.enc_weight.float())
+        ref.enc_bias.copy_(model.enc_bias.float())
+        for a, b in zip(ref.dec_weight, model.dec_weight):
+            a.copy_(b.float())
+        ref.dec_bias.copy_(model.dec_bias.float())
+    return ref
+
+
+@pytest.mark.parametrize("tying", ["none", "per_source", "per_target"])
+@pytest.mark.parametrize("lam", [0.0, 0.05])
+def test_fused_step_losses_match_autograd(tying, lam):
+    """Loss terms reported by the fused step equal the dense PyTorch losses for the same selection."""
+    cfg, model, tc, eng, X, Y = _engine_and_model(tying=tying, seed=5)
+    ref = _fp32_copy(model)
+    L, B, d = cfg.num_layers, eng.B, cfg.d_model
+    out = eng.train_step(X, Y, step=0, lr=1e-3, sparsity_lambda=lam)
+    torch.cuda.synchronize()
+    eng.check_status()
+    # reference step with the engine's own mask (the selection is tested elsewhere)
+    mask = _oracle_mask(eng.preact, eng.mean, eng.rstd, eng.k_total, cfg.num_features)
+    pre = {l: torch.nn.functional.linear(X[l].float(), ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    # the kernels see bf16-rounded pre-activations
+    acts = {l: (pre[l] + (eng.preact[l].float() - pre[l]).detach()) * mask[l] for l in range(L)}
+    recon = sum(torch.nn.functional.mse_loss(ref.decode({s: acts[s] for s in range(t + 1)}, t), Y[t].float()) for t in range(L))
+    pen = torch.zeros((), device=X.device)
+    if lam > 0:
+        norms = ref.get_decoder_norms()
+        pen = lam * sum(torch.tanh(tc.sparsity_c * acts[l] * norms[l][None, :]).sum() for l in range(L))
+    assert abs(out.reconstruction.item() - recon.item()) < 2e-3 * max(1.0, abs(recon.item()))
+    if lam > 0:
+        assert abs(out.sparsity.item() - pen.item()) < 1e-2 * max(1.0, abs(pen.item()))
+
+
+@pytest.mark.parametrize("tying", ["none", "per_source", "per_target"])
+@pytest.mark.parametrize("lam", [0.0, 0.05])
+def test_fused_step_weight_updates(tying, lam):
+    cfg, model, tc, eng, X, Y = _engine_and_model(tying=tying, seed=7)
+    ref = _fp32_copy(model)
+    snap = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+    L = cfg.num_layers
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3)
+    eng.train_step(X, Y, step=0, lr=1e-3, sparsity_lambda=lam)
+    torch.cuda.synchronize()
+    eng.check_status()
+    mask = _oracle_mask(eng.preact, eng.mean, eng.rstd, eng.k_total, cfg.num_features)
+    pre = {l: torch.nn.functional.linear(X[l].float(), ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    acts = {l: (pre[l] + (eng.preact[l].float() - pre[l]).detach()) * mask[l] for l in range(L)}
+    recon = sum(torch.nn.functional.mse_loss(ref.decode({s: acts[s] for s in range(t + 1)}, t), Y[t].float()) for t in range(L))
+    if lam > 0:
+        norms = ref.get_decoder_norms()
+        recon = recon + lam * sum(torch.tanh(tc.sparsity_c * acts[l] * norms[l][None, :]).sum() for l in range(L))
+    recon.backward()
+    opt.step()
+    ref_params = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        old = snap[name]
+        upd = p.detach().float() - old
+        ref_upd = ref_params[name].detach() - old
+        # Adam's first step moves every touched weight by ~lr; compare the sign/magnitude pattern
+        tol = 0.008 * old.abs() + 3e-4
+        bad = ((upd - ref_upd).abs() > tol).float().mean().item()
+        assert bad < 2e-3, (name, bad, (upd - ref_upd).abs().max().item())
+        touched = ref_upd.abs() > 5e-4
+        if touched.any():
+            agree = (torch.sign(upd[touched]) == torch.sign(ref_upd[touched])).float().mean().item()
+            assert agree > 0.98, (name, agree)
+
+
+def test_dead_counter_and_csr_consistency():
+    cfg, model, tc, eng, X, Y = _engine_and_model(seed=9)
+    eng.train_step(X, Y, step=0, lr=1e-3)
+    torch.cuda.synchronize()
+    n = int(eng.ctl[3])
+    assert n == eng.k_total
+    assert int(eng.tok_off[-1]) == n and int(eng.feat_off[-1]) == n
+    acts = eng.activations_dense()
+    fired = (acts > 1e-6).any(dim=1).reshape(-1)
+    assert torch.equal(eng.dead_counter == 0, fired)
+    # feature-major CSR lists tokens in increasing order per feature (sorted segments)
+    off = eng.feat_off.cpu()
+    tok = eng.fcsr_tok.cpu()
+    for c in torch.nonzero(eng.feat_cnt.cpu() > 1).flatten()[:50].tolist():
+        seg = tok[off[c]:off[c + 1]]
+        assert torch.all(seg[1:] >= seg[:-1])
+
+
+def test_decoder_norm2(ext):
+    dev = _dev()
+    w = torch.randn(40, 3, 64, device=dev).bfloat16()
+    out = torch.empty(40, device=dev)
+    ext.decoder_norm2(w, out)
+    assert torch.allclose(out, w.float().pow(2).sum(dim=(1, 2)), rtol=1e-4)
+
+
+def test_loss_decreases_over_steps():
+    cfg, model, tc, eng, X, Y = _engine_and_model(L=2, d=64, F=512, B=128, k=16, seed=11)
+    # learnable target: a fixed linear map of the inputs
+    A = torch.randn(cfg.d_model, cfg.d_model, device=X.device) / math.sqrt(cfg.d_model)
+    Y = (X.float() @ A).bfloat16()
+    losses = []
+    for step in range(60):
+        out = eng.train_step(X, Y, step=step, lr=2e-3)
+        losses.append(out.reconstruction.item())
+    eng.check_status()
+    assert losses[-1] < 0.7 * losses[0], losses[::10]
