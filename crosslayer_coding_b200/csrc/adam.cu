@@ -38,19 +38,60 @@ __device__ __forceinline__ __nv_bfloat16 to_bf16(float v, unsigned int seed, uns
   return __float2bfloat16_rn(__uint_as_float(t));
 }
 
+// Hyper-parameters pre-combined once per thread so the per-element update is 11 instructions.
+struct HyperRegs {
+  float decay;   // 1 - lr * wd (AdamW) or 1
+  float wd_l2;   // wd folded into the gradient (Adam) or 0
+  float omb1, omb2;
+  float step;    // lr / (1 - beta1^t)
+  float isb2;    // 1 / sqrt(1 - beta2^t)
+  float eps;
+  float gscale;
+};
+__device__ __forceinline__ HyperRegs make_regs(const AdamHyper& h) {
+  HyperRegs r;
+  r.decay = h.decoupled ? 1.f - h.lr * h.weight_decay : 1.f;
+  r.wd_l2 = h.decoupled ? 0.f : h.weight_decay;
+  r.omb1 = 1.f - h.beta1;
+  r.omb2 = 1.f - h.beta2;
+  r.step = h.lr / h.bc1;
+  r.isb2 = rsqrtf(h.bc2);
+  r.eps = h.eps;
+  r.gscale = h.grad_scale;
+  return r;
+}
+// m <- m + (1-b1)(g - m);  v <- v + (1-b2)(g^2 - v);  w <- decay*w - step * m / (sqrt(v)/sqrt(bc2) + eps)
+__device__ __forceinline__ void adam1(float& w, float& m, float& v, float g, const HyperRegs& r) {
+  g = fmaf(r.wd_l2, w, g);
+  w *= r.decay;
+  m = fmaf(r.omb1, g - m, m);
+  v = fmaf(r.omb2, fmaf(g, g, -v), v);
+  const float denom = fmaf(sqrtf(v), r.isb2, r.eps);
+  w = fmaf(-r.step, __fdividef(m, denom), w);
+}
 __device__ __forceinline__ void adam_update8(float (&w)[8], float (&m)[8], float (&v)[8], const float (&g)[8], const AdamHyper& h) {
-  const float step = h.lr / h.bc1;
-  const float inv_sqrt_bc2 = rsqrtf(h.bc2);
+  const HyperRegs r = make_regs(h);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    float gi = g[i];
-    if (h.decoupled) w[i] *= (1.f - h.lr * h.weight_decay);
-    else gi = fmaf(h.weight_decay, w[i], gi);
-    m[i] = fmaf(h.beta1, m[i], (1.f - h.beta1) * gi);
-    v[i] = fmaf(h.beta2, v[i], (1.f - h.beta2) * gi * gi);
-    const float denom = sqrtf(v[i]) * inv_sqrt_bc2 + h.eps;
-    w[i] -= step * (m[i] / denom);
+  for (int i = 0; i < 8; ++i) adam1(w[i], m[i], v[i], g[i], r);
+}
+// 8 fp32 -> 8 bf16 (one 16-byte vector); SR selects stochastic rounding with a counter-based hash.
+template <bool SR>
+__device__ __forceinline__ uint4 pack8_bf16(const float (&o)[8], unsigned int seed, unsigned int idx) {
+  uint4 q;
+  if (!SR) {
+    q.x = pack_bf16x2(o[0], o[1]); q.y = pack_bf16x2(o[2], o[3]);
+    q.z = pack_bf16x2(o[4], o[5]); q.w = pack_bf16x2(o[6], o[7]);
+  } else {
+    uint32_t h[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t u = __float_as_uint(o[k]);
+      const uint32_t rnd = hash32((idx + k) ^ seed) & 0xFFFFu;
+      h[k] = ((u & 0x7F800000u) == 0x7F800000u) ? (u >> 16) : ((u + rnd) >> 16);
+    }
+    q.x = h[0] | (h[1] << 16); q.y = h[2] | (h[3] << 16); q.z = h[4] | (h[5] << 16); q.w = h[6] | (h[7] << 16);
   }
+  return q;
 }
 
 __device__ __forceinline__ void unpack8(const uint4& q, float (&o)[8]) {
@@ -109,44 +150,208 @@ struct DecAdamParams {
   AdamHyper h;
 };
 
-// Row r of tensor i (source layer or, for per_target tying, target layer) and feature f.  The gradient of
-// that row is  grad_scale * sum over contributing (entry, target) pairs of  a' * gs[target][tok, :].
+__device__ __forceinline__ void f4x2_to8(const float4& a, const float4& b, float (&o)[8]) {
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void stream_store8f(float* p, const float (&o)[8]) {
+  __stcs(reinterpret_cast<float4*>(p), make_float4(o[0], o[1], o[2], o[3]));
+  __stcs(reinterpret_cast<float4*>(p) + 1, make_float4(o[4], o[5], o[6], o[7]));
+}
+template <typename WT>
+struct WVec;
+template <>
+struct WVec<__nv_bfloat16> {
+  uint4 q;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { q = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void get(float (&o)[8]) const { unpack8(q, o); }
+};
+template <>
+struct WVec<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = __ldcs(reinterpret_cast<const float4*>(p));
+    b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  }
+  __device__ __forceinline__ void get(float (&o)[8]) const { f4x2_to8(a, b, o); }
+};
+
+template <typename WT>
+struct RowRegs {
+  WVec<WT> w;
+  float4 m0, m1, v0, v1;
+  __device__ __forceinline__ void load(const WT* wp, const float* mp, const float* vp) {
+    w.load(wp);
+    m0 = __ldcs(reinterpret_cast<const float4*>(mp)); m1 = __ldcs(reinterpret_cast<const float4*>(mp) + 1);
+    v0 = __ldcs(reinterpret_cast<const float4*>(vp)); v1 = __ldcs(reinterpret_cast<const float4*>(vp) + 1);
+  }
+};
+
+// Untied decoders, the flagship path.  Work item = (source feature, 256-element segment): one warp, 8
+// elements per lane, walking the feature's R = L - s target rows with the next row's (w, m, v) already in
+// flight.  The first four entries of the feature stay in registers: their activation, token and the
+// partial dot products for dL/da, which are reduced once per item instead of once per row.
+template <typename WT, bool SR>
+__global__ void __launch_bounds__(256, 2) decoder_rows_adam_untied_kernel(const DecAdamParams p) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = int((blockIdx.x * 1LL * blockDim.x + threadIdx.x) >> 5);
+  const int nwarps = int((gridDim.x * 1LL * blockDim.x) >> 5);
+  const HyperRegs hr = make_regs(p.h);
+  const int d = p.d, B = p.B, Fp = p.F_pitch;
+  const int nseg = (d + 255) / 256;
+  const int per_tensor = Fp * nseg;
+  const int total_items = per_tensor * p.ntensors;
+  const __nv_bfloat16* __restrict__ gs = p.gs;
+  for (int item = warp_global; item < total_items; item += nwarps) {
+    const int ti = item / per_tensor;
+    const int rem = item - ti * per_tensor;
+    const int f = rem / nseg;
+    const int seg = rem - f * nseg;
+    const int R = p.rows[ti];
+    const int e0 = seg * 256 + lane * 8;
+    const bool act = e0 < d;
+    const long long row0 = 1LL * f * R;
+    WT* wbase = static_cast<WT*>(p.w[ti]) + row0 * d + e0;
+    float* mbase = p.m[ti] + row0 * d + e0;
+    float* vbase = p.v[ti] + row0 * d + e0;
+    RowRegs<WT> cur, nxt;
+    if (act) cur.load(wbase, mbase, vbase);
+    const int col = ti * Fp + f;
+    const int b = __ldg(p.feat_off + col), e = __ldg(p.feat_off + col + 1);
+    const int ne = e - b;
+    int tok4[4];
+    float a4[4], dacc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      tok4[j] = j < ne ? __ldg(p.fcsr_tok + b + j) : 0;
+      a4[j] = j < ne ? __ldg(p.fcsr_val + b + j) : 0.f;
+      dacc[j] = 0.f;
+    }
+    const float pc = p.pen_coef ? p.pen_coef[col] : 0.f;
+    float norm2 = 0.f;
+    const unsigned int idx_base = (unsigned int)((p.row_start[ti] + row0) * d + e0);
+    for (int r = 0; r < R; ++r) {
+      const long long roff = 1LL * r * d;
+      if (act && r + 1 < R) nxt.load(wbase + roff + d, mbase + roff + d, vbase + roff + d);
+      float w[8], g[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { g[i] = 0.f; w[i] = 0.f; }
+      if (act) {
+        cur.w.get(w);
+        const __nv_bfloat16* gs_t = gs + 1LL * (ti + r) * B * d + e0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < ne) {
+            float gv[8];
+            unpack8(__ldg(reinterpret_cast<const uint4*>(gs_t + 1LL * tok4[j] * d)), gv);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              g[k] = fmaf(a4[j], gv[k], g[k]);
+              dacc[j] = fmaf(gv[k], w[k], dacc[j]);
+            }
+          }
+        }
+      }
+      for (int i = b + 4; i < e; ++i) {  // rare: features with more than four entries
+        float dot = 0.f;
+        if (act) {
+          const float a = __ldg(p.fcsr_val + i);
+          float gv[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(gs + (1LL * (ti + r) * B + __ldg(p.fcsr_tok + i)) * d + e0)), gv);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            g[k] = fmaf(a, gv[k], g[k]);
+            dot = fmaf(gv[k], w[k], dot);
+          }
+        }
+        if (p.grad_a != nullptr) {
+          dot = warp_sum(dot);
+          if (lane == 0 && dot != 0.f) atomicAdd(&p.grad_a[i], dot * hr.gscale);
+        }
+      }
+      if (act) {
+        float m[8], v[8];
+        f4x2_to8(cur.m0, cur.m1, m);
+        f4x2_to8(cur.v0, cur.v1, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float gk = fmaf(pc, w[k], g[k] * hr.gscale);
+          adam1(w[k], m[k], v[k], gk, hr);
+          norm2 = fmaf(w[k], w[k], norm2);
+        }
+        stream_store8f(mbase + roff, m);
+        stream_store8f(vbase + roff, v);
+        if (sizeof(WT) == 2) __stcs(reinterpret_cast<uint4*>(wbase + roff), pack8_bf16<SR>(w, p.h.sr_seed, idx_base + (unsigned int)roff));
+        else stream_store8f(reinterpret_cast<float*>(wbase + roff), w);
+      }
+      cur = nxt;
+    }
+    if (p.grad_a != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j < ne) {
+          const float sdot = warp_sum(dacc[j]);
+          if (lane == 0 && sdot != 0.f) atomicAdd(&p.grad_a[b + j], sdot * hr.gscale);
+        }
+      }
+    }
+    if (p.norm2_out != nullptr) {
+      norm2 = warp_sum(norm2);
+      if (lane == 0) atomicAdd(&p.norm2_out[col], norm2);
+    }
+  }
+}
+
+// Tied decoders (per_source / per_target): same structure without the register-resident entries.
+// Work item = (feature of one decoder tensor, 256-element segment): one warp, 8 elements per lane, walking
+// the feature's R rows with the next row's (w, m, v) already in flight while the current row is updated.
+// Row r of tensor i (source layer i, or target layer i with per_target tying); its gradient is
+//   grad_scale * sum over contributing (entry, target) pairs of  a' * gs[target][tok, :]  (+ pen_coef * w).
 template <typename WT>
 __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamParams p) {
   const int lane = threadIdx.x & 31;
   const long long warp_global = (blockIdx.x * 1LL * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (gridDim.x * 1LL * blockDim.x) >> 5;
-  const long long total_rows = p.row_start[p.ntensors];
   const int nseg = (p.d + 255) / 256;
-  for (long long row = warp_global; row < total_rows; row += nwarps) {
-    int ti = 0;
-    while (ti + 1 < p.ntensors && row >= p.row_start[ti + 1]) ++ti;
-    const long long lr = row - p.row_start[ti];
+  const long long per_tensor = 1LL * p.F_pitch * nseg;
+  const long long total_items = per_tensor * p.ntensors;
+  for (long long item = warp_global; item < total_items; item += nwarps) {
+    const int ti = int(item / per_tensor);
+    const long long rem = item - ti * per_tensor;
+    const int f = int(rem / nseg);
+    const int seg = int(rem - 1LL * f * nseg);
     const int R = p.rows[ti];
-    const int f = int(lr / R);
-    const int r = int(lr - 1LL * f * R);
-    WT* wrow = static_cast<WT*>(p.w[ti]) + lr * p.d;
-    float* mrow = p.m[ti] + lr * p.d;
-    float* vrow = p.v[ti] + lr * p.d;
-    // contributing (source layer, target layer) pairs of this row
-    int s_lo, s_hi, t_fixed;
-    if (p.tying == 0) { s_lo = s_hi = ti; t_fixed = ti + r; }
-    else if (p.tying == 1) { s_lo = s_hi = ti; t_fixed = -1; }       // all targets >= ti
-    else { s_lo = 0; s_hi = ti; t_fixed = ti; }                        // all sources <= ti, target ti
+    const int e0 = seg * 256 + lane * 8;
+    const bool act = e0 < p.d;
+    const long long row0 = 1LL * f * R;
+    WT* wbase = static_cast<WT*>(p.w[ti]) + row0 * p.d + e0;
+    float* mbase = p.m[ti] + row0 * p.d + e0;
+    float* vbase = p.v[ti] + row0 * p.d + e0;
+    // contributing source layers of this tensor's rows
+    const int s_lo = p.tying == 2 ? 0 : ti;
+    const int s_hi = ti;
+    // d/dw of the norm-weighted sparsity penalty: coefficient of feature (ti, f); with per-target tying
+    // the row belongs to the norm of every source feature (s <= ti, f).
+    float pc = 0.f;
+    if (p.pen_coef) {
+      if (p.tying == 2) { for (int s = 0; s <= ti; ++s) pc += p.pen_coef[s * p.F_pitch + f]; }
+      else pc = p.pen_coef[ti * p.F_pitch + f];
+    }
+    RowRegs<WT> cur, nxt;
+    if (act) cur.load(wbase, mbase, vbase);
     float norm2 = 0.f;
-    for (int seg = 0; seg < nseg; ++seg) {
-      const int e0 = seg * 256 + lane * 8;
-      const bool act = e0 < p.d;
+    for (int r = 0; r < R; ++r) {
+      if (act && r + 1 < R) nxt.load(wbase + 1LL * (r + 1) * p.d, mbase + 1LL * (r + 1) * p.d, vbase + 1LL * (r + 1) * p.d);
+      const int t_fixed = p.tying == 0 ? ti + r : (p.tying == 2 ? ti : -1);
       float w[8], g[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) { g[i] = 0.f; w[i] = 0.f; }
-      if (act) load_w8<WT>(wrow + e0, w);
+      if (act) cur.w.get(w);
       for (int s = s_lo; s <= s_hi; ++s) {
         const int col = s * p.F_pitch + f;
-        const int b = p.feat_off[col], e = p.feat_off[col + 1];
+        const int b = __ldg(p.feat_off + col), e = __ldg(p.feat_off + col + 1);
         for (int i = b; i < e; ++i) {
-          const int tok = p.fcsr_tok[i];
-          const float a = p.fcsr_val[i];
+          const int tok = __ldg(p.fcsr_tok + i);
+          const float a = __ldg(p.fcsr_val + i);
           const int t_begin = t_fixed >= 0 ? t_fixed : s;
           const int t_end = t_fixed >= 0 ? t_fixed : p.L - 1;
           float dot = 0.f;
@@ -173,33 +378,31 @@ __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamPar
         }
       }
       if (act) {
-        // d/dw of the norm-weighted sparsity penalty: coefficient of feature (ti, f); with per-target
-        // tying the row belongs to the norm of every source feature (s <= ti, f).
-        float pc = 0.f;
-        if (p.pen_coef) {
-          if (p.tying == 2) { for (int s = 0; s <= ti; ++s) pc += p.pen_coef[s * p.F_pitch + f]; }
-          else pc = p.pen_coef[ti * p.F_pitch + f];
-        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) g[k] = fmaf(pc, w[k], g[k] * p.h.grad_scale);
         float m[8], v[8];
-        load8f(mrow + e0, m);
-        load8f(vrow + e0, v);
+        f4x2_to8(cur.m0, cur.m1, m);
+        f4x2_to8(cur.v0, cur.v1, v);
         adam_update8(w, m, v, g, p.h);
-        store8f(mrow + e0, m);
-        store8f(vrow + e0, v);
-        store_w8<WT>(wrow + e0, w, p.h.sr_seed, (unsigned long long)(row * p.d + e0));
+        WT* wrow = wbase + 1LL * r * p.d;
+        stream_store8f(mbase + 1LL * r * p.d, m);
+        stream_store8f(vbase + 1LL * r * p.d, v);
         if (sizeof(WT) == 2) {
-          // norms are taken of the stored (rounded) weights
-          float wr[8];
-          load_w8<WT>(wrow + e0, wr);
+          __nv_bfloat16 bq[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) norm2 = fmaf(wr[k], wr[k], norm2);
+          for (int k = 0; k < 8; ++k) {
+            bq[k] = to_bf16(w[k], p.h.sr_seed, (unsigned long long)((p.row_start[ti] + row0 + r) * p.d + e0 + k));
+            const float wr = __bfloat162float(bq[k]);  // norms are taken of the stored (rounded) weights
+            norm2 = fmaf(wr, wr, norm2);
+          }
+          __stcs(reinterpret_cast<uint4*>(wrow), *reinterpret_cast<const uint4*>(bq));
         } else {
+          stream_store8f(reinterpret_cast<float*>(wrow), w);
 #pragma unroll
           for (int k = 0; k < 8; ++k) norm2 = fmaf(w[k], w[k], norm2);
         }
       }
+      cur = nxt;
     }
     if (p.norm2_out != nullptr) {
       norm2 = warp_sum(norm2);
@@ -231,25 +434,33 @@ __global__ void __launch_bounds__(256) encoder_rows_adam_kernel(const EncAdamPar
   const int lane = threadIdx.x & 31;
   const long long warp_global = (blockIdx.x * 1LL * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (gridDim.x * 1LL * blockDim.x) >> 5;
-  const long long total_rows = 1LL * p.L * p.F_pitch;
   const int nseg = (p.d + 255) / 256;
-  for (long long row = warp_global; row < total_rows; row += nwarps) {
+  const long long total_items = 1LL * p.L * p.F_pitch * nseg;
+  for (long long item = warp_global; item < total_items; item += nwarps) {
+    const long long row = item / nseg;
+    const int seg = int(item - row * nseg);
     const int l = int(row / p.F_pitch);
-    WT* wrow = static_cast<WT*>(p.w) + row * p.d;
-    float* mrow = p.m + row * p.d;
-    float* vrow = p.v + row * p.d;
-    const int b = p.feat_off[row], e = p.feat_off[row + 1];
-    for (int seg = 0; seg < nseg; ++seg) {
-      const int e0 = seg * 256 + lane * 8;
-      if (e0 >= p.d) continue;
+    const int e0 = seg * 256 + lane * 8;
+    const bool act = e0 < p.d;
+    WT* wrow = static_cast<WT*>(p.w) + row * p.d + e0;
+    float* mrow = p.m + row * p.d + e0;
+    float* vrow = p.v + row * p.d + e0;
+    WVec<WT> wq;
+    float4 m0, m1, v0, v1;
+    if (act) {
+      wq.load(wrow);
+      m0 = __ldcs(reinterpret_cast<const float4*>(mrow)); m1 = __ldcs(reinterpret_cast<const float4*>(mrow) + 1);
+      v0 = __ldcs(reinterpret_cast<const float4*>(vrow)); v1 = __ldcs(reinterpret_cast<const float4*>(vrow) + 1);
+    }
+    const int b = __ldg(p.feat_off + row), e = __ldg(p.feat_off + row + 1);
+    if (act) {
       float w[8], g[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) g[i] = 0.f;
-      load_w8<WT>(wrow + e0, w);
       for (int i = b; i < e; ++i) {
-        const float dl = p.delta[i];
+        const float dl = __ldg(p.delta + i);
         float xv[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(p.x + (1LL * l * p.B + p.fcsr_tok[i]) * p.d + e0)), xv);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.x + (1LL * l * p.B + __ldg(p.fcsr_tok + i)) * p.d + e0)), xv);
 #pragma unroll
         for (int k = 0; k < 8; ++k) g[k] = fmaf(dl, xv[k], g[k]);
       }
@@ -262,14 +473,15 @@ __global__ void __launch_bounds__(256) encoder_rows_adam_kernel(const EncAdamPar
         for (int k = 0; k < 8; ++k) g[k] += dg[k];
       }
       float m[8], v[8];
-      load8f(mrow + e0, m);
-      load8f(vrow + e0, v);
+      wq.get(w);
+      f4x2_to8(m0, m1, m);
+      f4x2_to8(v0, v1, v);
       adam_update8(w, m, v, g, p.h);
-      store8f(mrow + e0, m);
-      store8f(vrow + e0, v);
-      store_w8<WT>(wrow + e0, w, p.h.sr_seed, (unsigned long long)(row * p.d + e0));
+      stream_store8f(mrow, m);
+      stream_store8f(vrow, v);
+      store_w8<WT>(wrow, w, p.h.sr_seed, (unsigned long long)(row * p.d + e0));
     }
-    if (lane == 0 && p.bias != nullptr) {
+    if (seg == 0 && lane == 0 && p.bias != nullptr) {
       float gb = 0.f;
       for (int i = b; i < e; ++i) gb += p.delta[i];
       gb *= p.h.grad_scale;
@@ -411,8 +623,19 @@ extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaS
   p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale; p.h = to_hyper(a->h);
   if (acc == 0) return 0;
   const int grid = num_sms * 8;
-  if (a->weights_bf16) decoder_rows_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
-  else decoder_rows_adam_kernel<float><<<grid, 256, 0, st>>>(p);
+  if (a->tying == 0) {
+    const bool sr = a->h.sr_seed != 0;
+    if (a->weights_bf16) {
+      if (sr) decoder_rows_adam_untied_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(p);
+      else decoder_rows_adam_untied_kernel<__nv_bfloat16, false><<<grid, 256, 0, st>>>(p);
+    } else {
+      decoder_rows_adam_untied_kernel<float, false><<<grid, 256, 0, st>>>(p);
+    }
+  } else if (a->weights_bf16) {
+    decoder_rows_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  } else {
+    decoder_rows_adam_kernel<float><<<grid, 256, 0, st>>>(p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

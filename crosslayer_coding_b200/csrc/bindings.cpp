@@ -54,6 +54,7 @@ struct CltCsrArgs {
   int* tcsr_col; float* tcsr_val; int* fcsr_tok; float* fcsr_val;
   unsigned char* fired;
   int sort_segments;
+  int col_pitch;
 };
 int clt_build_csr(const CltCsrArgs* a, cudaStream_t st);
 int clt_dead_counter_update(long long* counter, unsigned char* fired, int n, cudaStream_t st);
@@ -174,7 +175,7 @@ void batchtopk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, i
   need(hist, at::kInt, "hist"); need(ctl, at::kLong, "ctl"); need(status, at::kInt, "status");
   need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
   need(cand_key, at::kInt, "cand_key"); need(cand_tok, at::kInt, "cand_tok"); need(cand_col, at::kInt, "cand_col"); need(cand_val, at::kFloat, "cand_val");
-  TORCH_CHECK(hist.numel() >= 8192 && ctl.numel() >= 16, "hist needs 8192 and ctl 16 elements");
+  TORCH_CHECK(hist.numel() >= 2 * 8192 && ctl.numel() >= 16, "hist needs 2 * 8192 and ctl 16 elements");
   CltSelectArgs a;
   a.x = x.data_ptr(); a.mean = mean.data_ptr<float>(); a.rstd = rstd.data_ptr<float>();
   a.L = x.size(0); a.B = x.size(1); a.F = int(f_valid); a.stat_pitch = int(mean.size(-1));
@@ -194,7 +195,8 @@ void batchtopk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, i
 
 void build_csr(const Tensor& ent_tok, const Tensor& ent_col, const Tensor& ent_val, const Tensor& ctl, int64_t num_tokens, int64_t num_cols,
                Tensor& tok_cnt, Tensor& feat_cnt, Tensor& tok_off, Tensor& feat_off, Tensor& tok_cursor, Tensor& feat_cursor,
-               Tensor& tcsr_col, Tensor& tcsr_val, Tensor& fcsr_tok, Tensor& fcsr_val, const OptTensor& fired, int64_t sort_segments) {
+               Tensor& tcsr_col, Tensor& tcsr_val, Tensor& fcsr_tok, Tensor& fcsr_val, const OptTensor& fired, int64_t sort_segments,
+               int64_t col_pitch) {
   need(ent_tok, at::kInt, "ent_tok"); need(ctl, at::kLong, "ctl");
   need(tok_cnt, at::kInt, "tok_cnt"); need(feat_cnt, at::kInt, "feat_cnt"); need(tok_off, at::kInt, "tok_off"); need(feat_off, at::kInt, "feat_off");
   TORCH_CHECK(tok_off.numel() >= num_tokens + 1 && feat_off.numel() >= num_cols + 1, "offset arrays too small");
@@ -208,6 +210,8 @@ void build_csr(const Tensor& ent_tok, const Tensor& ent_col, const Tensor& ent_v
   a.tcsr_col = tcsr_col.data_ptr<int>(); a.tcsr_val = tcsr_val.data_ptr<float>(); a.fcsr_tok = fcsr_tok.data_ptr<int>(); a.fcsr_val = fcsr_val.data_ptr<float>();
   a.fired = fired.has_value() && fired->defined() ? fired->data_ptr<uint8_t>() : nullptr;
   a.sort_segments = int(sort_segments);
+  a.col_pitch = int(col_pitch);
+  TORCH_CHECK(col_pitch > 0 && col_pitch < (1 << 24), "col_pitch must be in (0, 2^24)");
   c10::cuda::CUDAGuard guard(ent_tok.device());
   check(clt_build_csr(&a, cur_stream()), "build_csr");
 }

@@ -4,7 +4,8 @@
 // than 99 % zeros, each followed by an all-reduce (clt/models/decoder.py:289-295, clt/models/parallel.py:363-383),
 // and then computes the MSE in separate passes (clt/training/losses.py:76-90).  Here one CTA per token walks
 // that token's active (layer, feature, value) entries, reads each feature's contiguous block of decoder rows
-// (feature-major layout [F, R, d]) and accumulates every target layer's reconstruction in registers.
+// (feature-major layout [F, R, d]) and accumulates every target layer's reconstruction in registers
+// (the targets are split over four warp groups to keep the register footprint small).
 // The epilogue either writes the fp32 partial reconstruction (tensor parallel: summed across ranks before
 // the loss) or, single rank, finishes in place: bias, optional dense addend (skip connection), residual,
 // per-layer squared-error sum in de-normalised units and the bf16 gradient seed  gs = (y_hat - y) * sigma^2.
@@ -13,7 +14,6 @@
 namespace clt {
 
 constexpr int kMaxLayers = 32;
-constexpr int kTgtTile = 16;  // target layers accumulated per pass
 
 struct DecodeParams {
   const __nv_bfloat16* w[kMaxLayers];  // decoder tensor i: [F_pitch, rows_i, d]
@@ -22,7 +22,7 @@ struct DecodeParams {
   int col_pitch;                       // entries encode column = layer * col_pitch + feature
   int tying;                           // 0 untied, 1 per_source, 2 per_target
   const int* tok_off;                  // [B+1]
-  const int* tcsr_col;
+  const int* tcsr_col;                 // (layer << 24) | feature
   const float* tcsr_val;
   const float* feat_offset;            // optional [L, col_pitch]  (tied decoders)
   const float* feat_scale;             // optional [L, col_pitch]
@@ -47,114 +47,120 @@ __device__ __forceinline__ void fma8(float (&acc)[8], float a, const uint4& v) {
   }
 }
 
-// grid = (B, ceil(L / kTgtTile)); block = d / 8 threads rounded up to a warp multiple.
-__global__ void __launch_bounds__(256) decode_kernel(const DecodeParams p) {
+constexpr int kGroups = 4;  // warp groups per token; group g owns targets t with t % kGroups == g
+
+// One CTA per token.  The CTA is split into kGroups warp groups of `gthreads` threads; every group walks
+// all entries of the token but only accumulates its own targets (t = g, g + kGroups, ...), so a thread
+// holds TPG x 8 accumulators instead of L x 8 and many more warps fit on an SM (more than 16 layers:
+// blockIdx.y selects the next 16 targets).  Each thread covers 8
+// consecutive elements of d (one 16-byte load per decoder row).
+template <int TPG>
+__global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int gthreads) {
   const int tok = blockIdx.x;
-  const int t0 = blockIdx.y * kTgtTile;
-  const int nT = min(kTgtTile, p.L - t0);
-  const int e0 = threadIdx.x * 8;
+  const int g = threadIdx.x / gthreads;
+  const int gt = threadIdx.x - g * gthreads;
+  const int e0 = gt * 8;
   const bool active = e0 < p.d;
-  float acc[kTgtTile][8];
+  float acc[TPG][8];
 #pragma unroll
-  for (int j = 0; j < kTgtTile; ++j)
+  for (int j = 0; j < TPG; ++j)
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+  __shared__ float sq_s[kMaxLayers];
+  __shared__ const __nv_bfloat16* w_s[kMaxLayers];  // parameter tables in shared memory: indexed per entry
+  __shared__ int rows_s[kMaxLayers];
+  if (threadIdx.x < kMaxLayers) {
+    sq_s[threadIdx.x] = 0.f;
+    w_s[threadIdx.x] = p.w[threadIdx.x];
+    rows_s[threadIdx.x] = p.rows[threadIdx.x];
+  }
+  __syncthreads();
+  const int L = p.L, d = p.d, tying = p.tying;
 
   const int b = p.tok_off[tok], e = p.tok_off[tok + 1];
-  for (int i = b; i < e; ++i) {
-    const int col = p.tcsr_col[i];
-    const float a = p.tcsr_val[i];
-    const int s = col / p.col_pitch;
-    const int f = col - s * p.col_pitch;
-    if (s >= t0 + nT || a == 0.f || !active) continue;
-    if (p.tying == 0) {
-      const int R = p.rows[s];
-      const __nv_bfloat16* base = p.w[s] + (1LL * f * R) * p.d + e0;
+  if (active) {
+    for (int i = b; i < e; ++i) {
+      const int col = __ldg(p.tcsr_col + i);  // packed by the CSR build: (layer << 24) | feature
+      const float a = __ldg(p.tcsr_val + i);
+      const int s = col >> 24;
+      const int f = col & 0xFFFFFF;
+      if (a == 0.f) continue;
+      if (tying == 0) {
+        // row (t - s) of feature f; rows of one feature are contiguous
+        const __nv_bfloat16* base = w_s[s] + (1LL * f * rows_s[s] - s) * d + e0;
 #pragma unroll
-      for (int j = 0; j < kTgtTile; ++j) {
-        const int t = t0 + j;
-        if (j < nT && t >= s) {
-          const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + 1LL * (t - s) * p.d));
-          fma8(acc[j], a, v);
+        for (int j = 0; j < TPG; ++j) {
+          const int t = g + (blockIdx.y * TPG + j) * kGroups;
+          if (t < L && t >= s) fma8(acc[j], a, __ldg(reinterpret_cast<const uint4*>(base + 1LL * t * d)));
         }
-      }
-    } else if (p.tying == 1) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.w[s] + 1LL * f * p.d + e0));
+      } else if (tying == 1) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(w_s[s] + 1LL * f * d + e0));
 #pragma unroll
-      for (int j = 0; j < kTgtTile; ++j) {
-        const int t = t0 + j;
-        if (j < nT && t >= s) {
-          float av = a;
-          if (p.feat_offset) av += p.feat_offset[1LL * t * p.col_pitch + f];
-          if (p.feat_scale) av *= p.feat_scale[1LL * t * p.col_pitch + f];
-          fma8(acc[j], av, v);
+        for (int j = 0; j < TPG; ++j) {
+          const int t = g + (blockIdx.y * TPG + j) * kGroups;
+          if (t < p.L && t >= s) {
+            float av = a;
+            if (p.feat_offset) av += p.feat_offset[1LL * t * p.col_pitch + f];
+            if (p.feat_scale) av *= p.feat_scale[1LL * t * p.col_pitch + f];
+            fma8(acc[j], av, v);
+          }
         }
-      }
-    } else {
+      } else {
 #pragma unroll
-      for (int j = 0; j < kTgtTile; ++j) {
-        const int t = t0 + j;
-        if (j < nT && t >= s) {
-          float av = a;
-          if (p.feat_offset) av += p.feat_offset[1LL * t * p.col_pitch + f];
-          if (p.feat_scale) av *= p.feat_scale[1LL * t * p.col_pitch + f];
-          const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.w[t] + 1LL * f * p.d + e0));
-          fma8(acc[j], av, v);
+        for (int j = 0; j < TPG; ++j) {
+          const int t = g + (blockIdx.y * TPG + j) * kGroups;
+          if (t < p.L && t >= s) {
+            float av = a;
+            if (p.feat_offset) av += p.feat_offset[1LL * t * p.col_pitch + f];
+            if (p.feat_scale) av *= p.feat_scale[1LL * t * p.col_pitch + f];
+            fma8(acc[j], av, __ldg(reinterpret_cast<const uint4*>(w_s[t] + 1LL * f * d + e0)));
+          }
         }
       }
     }
   }
 
-  __shared__ float red[8];
 #pragma unroll
-  for (int j = 0; j < kTgtTile; ++j) {
-    if (j >= nT) break;  // uniform across the block
-    const int t = t0 + j;
+  for (int j = 0; j < TPG; ++j) {
+    const int t = g + (blockIdx.y * TPG + j) * kGroups;
+    if (t >= p.L || !active) continue;
     const long long off = (1LL * t * p.B + tok) * p.d + e0;
-    float sq = 0.f;
-    if (active) {
-      if (p.mode == 0) {
-        float4* dst = reinterpret_cast<float4*>(p.yhat_partial + off);
-        dst[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-        dst[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
-      } else {
-        float y[8], sg[8], out[8];
-        const uint4 tv = *reinterpret_cast<const uint4*>(p.target + off);
-        const uint32_t u[4] = {tv.x, tv.y, tv.z, tv.w};
+    if (p.mode == 0) {
+      float4* dst = reinterpret_cast<float4*>(p.yhat_partial + off);
+      dst[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+      dst[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+    } else {
+      float y[8], out[8];
+      const uint4 tv = *reinterpret_cast<const uint4*>(p.target + off);
+      const uint32_t u[4] = {tv.x, tv.y, tv.z, tv.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { y[2 * i] = bf16_lo(u[i]); y[2 * i + 1] = bf16_hi(u[i]); }
+      for (int i = 0; i < 4; ++i) { y[2 * i] = bf16_lo(u[i]); y[2 * i + 1] = bf16_hi(u[i]); }
+      float sq = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float v = acc[j][i] + p.bias_sum[1LL * t * p.d + e0 + i];
-          if (p.addend) v += p.addend[off + i];
-          sg[i] = p.sigma ? p.sigma[1LL * t * p.d + e0 + i] : 1.f;
-          out[i] = v;
-          const float r = (v - y[i]) * sg[i];
-          sq = fmaf(r, r, sq);
-          y[i] = r * sg[i];  // gradient seed
-        }
-        uint4 gv;
-        gv.x = pack_bf16x2(y[0], y[1]); gv.y = pack_bf16x2(y[2], y[3]);
-        gv.z = pack_bf16x2(y[4], y[5]); gv.w = pack_bf16x2(y[6], y[7]);
-        *reinterpret_cast<uint4*>(p.gs + off) = gv;
-        if (p.yhat_out) {
-          float4* dst = reinterpret_cast<float4*>(p.yhat_out + off);
-          dst[0] = make_float4(out[0], out[1], out[2], out[3]);
-          dst[1] = make_float4(out[4], out[5], out[6], out[7]);
-        }
+      for (int i = 0; i < 8; ++i) {
+        float v = acc[j][i] + p.bias_sum[1LL * t * p.d + e0 + i];
+        if (p.addend) v += p.addend[off + i];
+        const float sg = p.sigma ? p.sigma[1LL * t * p.d + e0 + i] : 1.f;
+        out[i] = v;
+        const float r = (v - y[i]) * sg;
+        sq = fmaf(r, r, sq);
+        y[i] = r * sg;  // gradient seed
       }
-    }
-    if (p.mode != 0) {
-      sq = warp_sum(sq);
-      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        float tot = 0.f;
-        for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
-        atomicAdd(&p.sq_err[t], double(tot));
+      uint4 gv;
+      gv.x = pack_bf16x2(y[0], y[1]); gv.y = pack_bf16x2(y[2], y[3]);
+      gv.z = pack_bf16x2(y[4], y[5]); gv.w = pack_bf16x2(y[6], y[7]);
+      *reinterpret_cast<uint4*>(p.gs + off) = gv;
+      if (p.yhat_out) {
+        float4* dst = reinterpret_cast<float4*>(p.yhat_out + off);
+        dst[0] = make_float4(out[0], out[1], out[2], out[3]);
+        dst[1] = make_float4(out[4], out[5], out[6], out[7]);
       }
-      __syncthreads();
+      atomicAdd(&sq_s[t], sq);
     }
+  }
+  if (p.mode != 0) {
+    __syncthreads();
+    if (threadIdx.x < p.L && sq_s[threadIdx.x] != 0.f) atomicAdd(&p.sq_err[threadIdx.x], double(sq_s[threadIdx.x]));
   }
 }
 
@@ -246,9 +252,14 @@ extern "C" int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st) {
   p.yhat_partial = a->yhat_partial; p.bias_sum = a->bias_sum; p.addend = a->addend;
   p.target = static_cast<const __nv_bfloat16*>(a->target); p.sigma = a->sigma;
   p.gs = static_cast<__nv_bfloat16*>(a->gs); p.yhat_out = a->yhat_out; p.sq_err = a->sq_err; p.mode = a->mode;
-  const int threads = ((a->d / 8 + 31) / 32) * 32;
-  dim3 grid(a->B, (a->L + kTgtTile - 1) / kTgtTile);
-  decode_kernel<<<grid, threads, 0, st>>>(p);
+  const int gthreads = ((a->d / 8 + 31) / 32) * 32;
+  const int threads = gthreads * kGroups;
+  if (threads > 1024) return -1;
+  const int tpg = (a->L + kGroups - 1) / kGroups;  // targets per warp group
+  if (tpg <= 1) decode_kernel<1><<<dim3(a->B, 1), threads, 0, st>>>(p, gthreads);
+  else if (tpg == 2) decode_kernel<2><<<dim3(a->B, 1), threads, 0, st>>>(p, gthreads);
+  else if (tpg == 3) decode_kernel<3><<<dim3(a->B, 1), threads, 0, st>>>(p, gthreads);
+  else decode_kernel<4><<<dim3(a->B, (tpg + 3) / 4), threads, 0, st>>>(p, gthreads);  // 16 targets per pass
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -34,6 +34,9 @@ enum SelCtl : int {
   CTL_CUT_KEY = 5,      // exact key cut T
   CTL_TIE_MODE = 6,     // 0: keep every key == T; 1: keep ties with flat index <= CTL_CUT_FLAT
   CTL_CUT_FLAT = 7,
+  CTL_KEY_LO = 8,       // histogram range actually used: keys >= key_lo, bin = (key - key_lo) >> shift
+  CTL_SHIFT = 9,
+  CTL_RETRY = 10,       // 1: the narrow histogram did not contain the cut, the full-range pass runs
   CTL_SIZE = 16,
 };
 
@@ -108,14 +111,23 @@ __global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __re
     const uint32_t w[4] = {v0.x, v0.y, v0.z, v0.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) { shift[2 * j] = bf16_lo(w[j]); shift[2 * j + 1] = bf16_hi(w[j]); }
-    for (int r = threadIdx.y; r < B; r += 8) {
-      uint4 v = *reinterpret_cast<const uint4*>(base + 1LL * r * ld);
-      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    for (int r0 = threadIdx.y; r0 < B; r0 += 32) {
+      uint4 v[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = bf16_lo(u[j]) - shift[2 * j], b = bf16_hi(u[j]) - shift[2 * j + 1];
-        s[2 * j] += a; q[2 * j] += a * a;
-        s[2 * j + 1] += b; q[2 * j + 1] += b * b;
+      for (int k = 0; k < 4; ++k) {  // four independent loads in flight
+        const int r = r0 + 8 * k;
+        v[k] = r < B ? __ldcs(reinterpret_cast<const uint4*>(base + 1LL * r * ld)) : v0;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (r0 + 8 * k >= B) break;
+        const uint32_t u[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = bf16_lo(u[j]) - shift[2 * j], b = bf16_hi(u[j]) - shift[2 * j + 1];
+          s[2 * j] += a; q[2 * j] += a * a;
+          s[2 * j + 1] += b; q[2 * j + 1] += b * b;
+        }
       }
     }
   }
@@ -152,9 +164,13 @@ __device__ __forceinline__ void load_cols8(const float* p, float (&o)[8]) {
   o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
 }
 
+// `only_if_retry`: the full-range pass; it runs only when the narrow pass asked for it.
 __global__ void __launch_bounds__(256) zhist_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
                                                       const float* __restrict__ rstd, ScanGeom g, uint32_t key_lo, int shift,
-                                                      unsigned int* __restrict__ hist) {
+                                                      unsigned int* __restrict__ hist, const long long* __restrict__ ctl,
+                                                      int only_if_retry) {
+  if (only_if_retry && ctl[CTL_RETRY] == 0) return;
+  const float z_lo = key_lo == 0u ? -INFINITY : key_to_float(key_lo);
   __shared__ unsigned int sh[kHistBins];
   for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) sh[i] = 0;
   __syncthreads();
@@ -176,15 +192,24 @@ __global__ void __launch_bounds__(256) zhist_kernel(const __nv_bfloat16* __restr
     const int r0 = blockIdx.y * g.rows_per_block;
     const int r1 = min(g.B, r0 + g.rows_per_block);
     const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
-    for (int r = r0; r < r1; ++r) {
-      const uint4 v = *reinterpret_cast<const uint4*>(base + 1LL * r * g.ld);
-      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    for (int rb = r0; rb < r1; rb += 4) {
+      uint4 v[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
-        const float z = (xv - mu[j]) * rs[j];
-        const uint32_t key = float_to_key(z);
-        if (key >= key_lo && j < nvalid) atomicAdd(&sh[min((key - key_lo) >> shift, uint32_t(kHistBins - 1))], 1u);
+      for (int k = 0; k < 4; ++k)
+        v[k] = (rb + k < r1) ? __ldg(reinterpret_cast<const uint4*>(base + 1LL * (rb + k) * g.ld)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (rb + k >= r1) break;
+        const uint32_t u[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+          const float z = (xv - mu[j]) * rs[j];
+          if (z >= z_lo && j < nvalid) {  // one float compare for the bulk; keys only for the tail that counts
+            const uint32_t key = float_to_key(z);
+            atomicAdd(&sh[min((key - key_lo) >> shift, uint32_t(kHistBins - 1))], 1u);
+          }
+        }
       }
     }
   }
@@ -196,16 +221,21 @@ __global__ void __launch_bounds__(256) zhist_kernel(const __nv_bfloat16* __restr
 }
 
 // ------------------------------------------------------------------ 3. threshold bin (one CTA, 1024 threads)
+// pass 0: narrow histogram; when it does not contain the cut it only raises CTL_RETRY.
+// pass 1: full-range histogram, runs only on retry; a miss there is a real error.
 __global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __restrict__ hist, long long k_total,
-                                                          long long* __restrict__ ctl, Exchange ex, int* __restrict__ status) {
+                                                          long long* __restrict__ ctl, Exchange ex, uint32_t key_lo, int shift,
+                                                          int pass, int exchange_round, int* __restrict__ status) {
   __shared__ uint32_t vals[kHistBins];
   __shared__ unsigned long long part[1024];
   __shared__ int timeout;
+  __shared__ int found;
   const int tid = threadIdx.x;
-  if (tid == 0) timeout = 0;
+  if (pass == 1 && ctl[CTL_RETRY] == 0) return;
+  if (tid == 0) { timeout = 0; found = 0; }
   for (int i = tid; i < kHistBins; i += 1024) vals[i] = hist[i];
   __syncthreads();
-  if (!exchange_sum(ex, 0, vals, kHistBins, &timeout)) {
+  if (!exchange_sum(ex, exchange_round, vals, kHistBins, &timeout)) {
     if (tid == 0) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
     return;
   }
@@ -217,9 +247,20 @@ __global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __re
   if (tid == 0) {
     unsigned long long run = 0;
     for (int t = 1023; t >= 0; --t) { const unsigned long long c = part[t]; part[t] = run; run += c; }
-    if (run < (unsigned long long)k_total) atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
+    found = run >= (unsigned long long)k_total ? 1 : 0;
+    if (!found) {
+      if (pass == 0) ctl[CTL_RETRY] = 1;
+      else atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
+    } else if (pass == 0) {
+      ctl[CTL_RETRY] = 0;
+    }
+    if (pass == 0 || found) {
+      ctl[CTL_NUM_ENTRIES] = 0;
+      ctl[CTL_NUM_CAND] = 0;
+    }
   }
   __syncthreads();
+  if (!found) return;
   unsigned long long above = part[tid];  // keys in bins above this thread's group
   for (int j = 7; j >= 0; --j) {
     const unsigned long long c = vals[tid * 8 + j];
@@ -227,12 +268,10 @@ __global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __re
       ctl[CTL_BIN] = tid * 8 + j;
       ctl[CTL_ABOVE] = (long long)above;
       ctl[CTL_NEED] = k_total - (long long)above;
+      ctl[CTL_KEY_LO] = (long long)key_lo;
+      ctl[CTL_SHIFT] = shift;
     }
     above += c;
-  }
-  if (tid == 0) {
-    ctl[CTL_NUM_ENTRIES] = 0;
-    ctl[CTL_NUM_CAND] = 0;
   }
 }
 
@@ -249,51 +288,105 @@ struct Lists {
   long long cand_cap;
 };
 
+// Selected elements are staged in shared memory and appended with one global reservation per CTA and
+// list: a single counter cannot absorb one atomic per selected element (hundreds of thousands per step).
+constexpr int kStageCap = 1024;
+
 __global__ void __launch_bounds__(256) compact_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
-                                                        const float* __restrict__ rstd, ScanGeom g, uint32_t key_lo, int shift,
-                                                        int col_pitch, long long* __restrict__ ctl, Lists o,
-                                                        int* __restrict__ status) {
+                                                        const float* __restrict__ rstd, ScanGeom g, int col_pitch,
+                                                        long long* __restrict__ ctl, Lists o, int* __restrict__ status) {
+  __shared__ int s_tok[kStageCap];
+  __shared__ int s_col[kStageCap];
+  __shared__ float s_val[kStageCap];
+  __shared__ uint32_t s_key[kStageCap];  // 0 marks a definite entry, otherwise the candidate's key (never 0 here)
+  __shared__ int s_n;
+  __shared__ unsigned long long s_base_ent, s_base_cand;
+  __shared__ int s_cnt_ent, s_cnt_cand;
+  if (threadIdx.x == 0) { s_n = 0; s_cnt_ent = 0; s_cnt_cand = 0; }
+  __syncthreads();
   const int l = blockIdx.z;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (c0 >= g.F) return;
   const uint32_t tbin = uint32_t(ctl[CTL_BIN]);
-  float mu[8], rs[8];
-  for (int j = 0; j < 8; ++j) {
-    const bool in = c0 + j < g.F;
-    mu[j] = in ? mean[1LL * l * g.sp + c0 + j] : 0.f;
-    rs[j] = in ? rstd[1LL * l * g.sp + c0 + j] : 0.f;
-  }
-  const int nvalid = min(8, g.F - c0);
-  const int r0 = blockIdx.y * g.rows_per_block;
-  const int r1 = min(g.B, r0 + g.rows_per_block);
-  const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+  const uint32_t key_lo = uint32_t(ctl[CTL_KEY_LO]);
+  const int shift = int(ctl[CTL_SHIFT]);
+  // smallest key that can matter: everything below the threshold bin is dropped with one compare
+  const unsigned long long lo64 = (unsigned long long)key_lo + ((unsigned long long)tbin << shift);
+  const uint32_t key_min = lo64 > 0xFFFFFFFFULL ? 0xFFFFFFFFu : uint32_t(lo64);
+  const float z_min = key_min == 0u ? -INFINITY : key_to_float(key_min);
   unsigned long long* n_ent = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_ENTRIES);
   unsigned long long* n_cand = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_CAND);
-  for (int r = r0; r < r1; ++r) {
-    const uint4 v = *reinterpret_cast<const uint4*>(base + 1LL * r * g.ld);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+  if (c0 < g.F) {
+    float mu[8], rs[8];
+    if (c0 + 8 <= g.F) {
+      load_cols8(mean + 1LL * l * g.sp + c0, mu);
+      load_cols8(rstd + 1LL * l * g.sp + c0, rs);
+    } else {
+      for (int j = 0; j < 8; ++j) {
+        const bool in = c0 + j < g.F;
+        mu[j] = in ? mean[1LL * l * g.sp + c0 + j] : 0.f;
+        rs[j] = in ? rstd[1LL * l * g.sp + c0 + j] : 0.f;
+      }
+    }
+    const int nvalid = min(8, g.F - c0);
+    const int r0 = blockIdx.y * g.rows_per_block;
+    const int r1 = min(g.B, r0 + g.rows_per_block);
+    const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+    for (int rb = r0; rb < r1; rb += 4) {
+      uint4 v[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
-      const float z = (xv - mu[j]) * rs[j];
-      const uint32_t key = float_to_key(z);
-      if (key < key_lo || j >= nvalid) continue;
-      const uint32_t bin = min((key - key_lo) >> shift, uint32_t(kHistBins - 1));
-      if (bin > tbin) {
-        const unsigned long long p = atomicAdd(n_ent, 1ULL);
-        if ((long long)p < o.ent_cap) {
-          o.ent_tok[p] = r; o.ent_col[p] = l * col_pitch + c0 + j; o.ent_val[p] = xv;
-        } else {
-          atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
-        }
-      } else if (bin == tbin) {
-        const unsigned long long p = atomicAdd(n_cand, 1ULL);
-        if ((long long)p < o.cand_cap) {
-          o.cand_key[p] = key; o.cand_tok[p] = r; o.cand_col[p] = l * col_pitch + c0 + j; o.cand_val[p] = xv;
-        } else {
-          atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+      for (int k = 0; k < 4; ++k) {
+        const int r = min(rb + k, r1 - 1);
+        v[k] = __ldcs(reinterpret_cast<const uint4*>(base + 1LL * r * g.ld));
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int r = rb + k;
+        const uint32_t u[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+          const float z = (xv - mu[j]) * rs[j];
+          if (!(z >= z_min) || j >= nvalid || r >= r1) continue;
+          const uint32_t key = float_to_key(z);
+          const uint32_t bin = min((key - key_lo) >> shift, uint32_t(kHistBins - 1));
+          if (bin < tbin) continue;
+          const bool is_ent = bin > tbin;
+          const int slot = atomicAdd(&s_n, 1);
+          if (slot < kStageCap) {
+            s_tok[slot] = r; s_col[slot] = l * col_pitch + c0 + j; s_val[slot] = xv; s_key[slot] = is_ent ? 0u : key;
+            atomicAdd(is_ent ? &s_cnt_ent : &s_cnt_cand, 1);
+          } else if (is_ent) {  // staging full: append directly
+            const unsigned long long p = atomicAdd(n_ent, 1ULL);
+            if ((long long)p < o.ent_cap) { o.ent_tok[p] = r; o.ent_col[p] = l * col_pitch + c0 + j; o.ent_val[p] = xv; }
+            else atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+          } else {
+            const unsigned long long p = atomicAdd(n_cand, 1ULL);
+            if ((long long)p < o.cand_cap) { o.cand_key[p] = key; o.cand_tok[p] = r; o.cand_col[p] = l * col_pitch + c0 + j; o.cand_val[p] = xv; }
+            else atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+          }
         }
       }
+    }
+  }
+  __syncthreads();
+  const int staged = min(s_n, kStageCap);
+  if (staged == 0) return;
+  if (threadIdx.x == 0) {
+    s_base_ent = s_cnt_ent ? atomicAdd(n_ent, (unsigned long long)s_cnt_ent) : 0ULL;
+    s_base_cand = s_cnt_cand ? atomicAdd(n_cand, (unsigned long long)s_cnt_cand) : 0ULL;
+    s_cnt_ent = 0; s_cnt_cand = 0;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < staged; i += blockDim.x) {
+    const uint32_t key = s_key[i];
+    if (key == 0u) {
+      const unsigned long long p = s_base_ent + (unsigned long long)atomicAdd(&s_cnt_ent, 1);
+      if ((long long)p < o.ent_cap) { o.ent_tok[p] = s_tok[i]; o.ent_col[p] = s_col[i]; o.ent_val[p] = s_val[i]; }
+      else atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+    } else {
+      const unsigned long long p = s_base_cand + (unsigned long long)atomicAdd(&s_cnt_cand, 1);
+      if ((long long)p < o.cand_cap) { o.cand_key[p] = key; o.cand_tok[p] = s_tok[i]; o.cand_col[p] = s_col[i]; o.cand_val[p] = s_val[i]; }
+      else atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
     }
   }
 }
@@ -331,9 +424,11 @@ __device__ void pick_digit(const uint32_t* hist, int nb, bool descending, unsign
 }
 
 __global__ void __launch_bounds__(1024) refine_kernel(const uint32_t* __restrict__ cand_key, const int* __restrict__ cand_tok,
-                                                        const int* __restrict__ cand_col, long long cand_cap, int shift,
+                                                        const int* __restrict__ cand_col, long long cand_cap,
                                                         FlatGeom fg, long long* __restrict__ ctl, Exchange ex,
                                                         int* __restrict__ status) {
+  const int shift = int(ctl[CTL_SHIFT]);
+  const uint32_t key_lo = uint32_t(ctl[CTL_KEY_LO]);  // bins are over (key - key_lo): refine on the same offset
   __shared__ uint32_t hist[kRefineBins];
   __shared__ int digit;
   __shared__ unsigned long long need;
@@ -345,7 +440,7 @@ __global__ void __launch_bounds__(1024) refine_kernel(const uint32_t* __restrict
   __syncthreads();
   // ---- key cut: radix passes over the low `shift` bits, 9 bits at a time, most significant first.
   uint32_t prefix = 0, prefix_mask = 0;
-  int round = 1;
+  int round = 2;  // rounds 0 and 1 belong to the two histogram passes
   const uint32_t low_mask = shift >= 32 ? 0xFFFFFFFFu : ((1u << shift) - 1u);
   for (int hi = shift; hi > 0; hi -= 9, ++round) {
     const int lo = max(hi - 9, 0);
@@ -353,7 +448,7 @@ __global__ void __launch_bounds__(1024) refine_kernel(const uint32_t* __restrict
     for (int i = tid; i < kRefineBins; i += 1024) hist[i] = 0;
     __syncthreads();
     for (long long i = tid; i < n; i += 1024) {
-      const uint32_t k = cand_key[i] & low_mask;
+      const uint32_t k = (cand_key[i] - key_lo) & low_mask;
       if ((k & prefix_mask) == prefix) atomicAdd(&hist[(k >> lo) & (nb - 1)], 1u);
     }
     __syncthreads();
@@ -374,7 +469,7 @@ __global__ void __launch_bounds__(1024) refine_kernel(const uint32_t* __restrict
   for (int i = tid; i < kRefineBins; i += 1024) hist[i] = 0;
   __syncthreads();
   unsigned int local_ties = 0;
-  for (long long i = tid; i < n; i += 1024) local_ties += ((cand_key[i] & low_mask) == prefix) ? 1u : 0u;
+  for (long long i = tid; i < n; i += 1024) local_ties += (((cand_key[i] - key_lo) & low_mask) == prefix) ? 1u : 0u;
   if (local_ties) atomicAdd(&hist[0], local_ties);
   __syncthreads();
   if (!exchange_sum(ex, round++, hist, kRefineBins, &timeout)) {
@@ -392,7 +487,7 @@ __global__ void __launch_bounds__(1024) refine_kernel(const uint32_t* __restrict
       for (int i = tid; i < kRefineBins; i += 1024) hist[i] = 0;
       __syncthreads();
       for (long long i = tid; i < n; i += 1024) {
-        if ((cand_key[i] & low_mask) != prefix) continue;
+        if (((cand_key[i] - key_lo) & low_mask) != prefix) continue;
         const unsigned long long fl = flat_index(fg, cand_tok[i], cand_col[i]);
         if ((fl & flat_mask) == flat_prefix) atomicAdd(&hist[(fl >> lo) & 511ULL], 1u);
       }
@@ -417,8 +512,10 @@ __global__ void __launch_bounds__(1024) refine_kernel(const uint32_t* __restrict
 }
 
 // ------------------------------------------------------------------ 6. append the kept candidates
-__global__ void __launch_bounds__(256) finalize_kernel(Lists o, int shift, FlatGeom fg, long long* __restrict__ ctl,
+__global__ void __launch_bounds__(256) finalize_kernel(Lists o, FlatGeom fg, long long* __restrict__ ctl,
                                                          int* __restrict__ status) {
+  const int shift = int(ctl[CTL_SHIFT]);
+  const uint32_t key_lo = uint32_t(ctl[CTL_KEY_LO]);
   long long n = ctl[CTL_NUM_CAND];
   if (n > o.cand_cap) n = o.cand_cap;
   const uint32_t low_mask = shift >= 32 ? 0xFFFFFFFFu : ((1u << shift) - 1u);
@@ -427,7 +524,7 @@ __global__ void __launch_bounds__(256) finalize_kernel(Lists o, int shift, FlatG
   const unsigned long long cut_flat = (unsigned long long)ctl[CTL_CUT_FLAT];
   unsigned long long* n_ent = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_ENTRIES);
   for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
-    const uint32_t k = o.cand_key[i] & low_mask;
+    const uint32_t k = (o.cand_key[i] - key_lo) & low_mask;
     bool keep = k > cut;
     if (k == cut) keep = !tie_cut || flat_index(fg, o.cand_tok[i], o.cand_col[i]) <= cut_flat;
     if (keep) {
@@ -456,31 +553,54 @@ __global__ void __launch_bounds__(256) csr_count_kernel(const int* __restrict__ 
   }
 }
 
-// Exclusive scan of `n` ints by one CTA (1024 threads); out has n+1 entries.  cursor (optional) gets a copy
-// of the offsets for the scatter pass.
+// Exclusive scan of `n` ints by one CTA (1024 threads) over coalesced tiles of 4096 elements; out has n+1
+// entries.  cursor (optional) gets a copy of the offsets for the scatter pass.
 __global__ void __launch_bounds__(1024) exclusive_scan_kernel(const int* __restrict__ in, int* __restrict__ out,
                                                                 int* __restrict__ cursor, int n) {
-  __shared__ int part[1024];
-  const int tid = threadIdx.x;
-  const int per = (n + 1023) / 1024;
-  const int b = min(n, tid * per), e = min(n, b + per);
-  int s = 0;
-  for (int i = b; i < e; ++i) s += in[i];
-  part[tid] = s;
+  __shared__ int warp_tot[32];
+  __shared__ int carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) carry_s = 0;
   __syncthreads();
-  for (int off = 1; off < 1024; off <<= 1) {
-    const int v = tid >= off ? part[tid - off] : 0;
+  for (int base = 0; base < n; base += 4096) {
+    const int i0 = base + tid * 4;
+    int v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = (i0 + k < n) ? in[i0 + k] : 0;
+    const int mine = v[0] + v[1] + v[2] + v[3];
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
     __syncthreads();
-    part[tid] += v;
+    if (warp == 0) {
+      int w = warp_tot[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xFFFFFFFFu, w, o);
+        if (lane >= o) w += t;
+      }
+      warp_tot[lane] = w;  // inclusive over warps
+    }
+    __syncthreads();
+    const int carry = carry_s;
+    int run = carry + (warp > 0 ? warp_tot[warp - 1] : 0) + incl - mine;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (i0 + k < n) {
+        out[i0 + k] = run;
+        if (cursor != nullptr) cursor[i0 + k] = run;
+      }
+      run += v[k];
+    }
+    __syncthreads();
+    if (tid == 1023) carry_s = carry + warp_tot[31];
     __syncthreads();
   }
-  int run = part[tid] - s;
-  for (int i = b; i < e; ++i) {
-    out[i] = run;
-    if (cursor != nullptr) cursor[i] = run;
-    run += in[i];
-  }
-  if (tid == 1023) out[n] = part[1023];
+  if (tid == 0) out[n] = carry_s;
 }
 
 __global__ void __launch_bounds__(256) csr_scatter_kernel(const int* __restrict__ ent_tok, const int* __restrict__ ent_col,
@@ -488,14 +608,15 @@ __global__ void __launch_bounds__(256) csr_scatter_kernel(const int* __restrict_
                                                             const long long* __restrict__ ctl, int* __restrict__ tok_cursor,
                                                             int* __restrict__ feat_cursor, int* __restrict__ tcsr_col,
                                                             float* __restrict__ tcsr_val, int* __restrict__ fcsr_tok,
-                                                            float* __restrict__ fcsr_val) {
+                                                            float* __restrict__ fcsr_val, int col_pitch) {
   long long n = ctl[CTL_NUM_ENTRIES];
   if (n > cap) n = cap;
   for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
     const int t = ent_tok[i], c = ent_col[i];
     const float v = ent_val[i];
     const int p = atomicAdd(&tok_cursor[t], 1);
-    tcsr_col[p] = c; tcsr_val[p] = v;
+    const int layer = c / col_pitch;  // token-major view stores (layer << 24) | feature for the decoder
+    tcsr_col[p] = (layer << 24) | (c - layer * col_pitch); tcsr_val[p] = v;
     const int q = atomicAdd(&feat_cursor[c], 1);
     fcsr_tok[q] = t; fcsr_val[q] = v;
   }
@@ -573,7 +694,7 @@ struct CltSelectArgs {
   long long k_total;   // global number of entries to keep
   unsigned int key_lo; // histogram covers keys >= key_lo
   int shift;           // bin = (key - key_lo) >> shift
-  unsigned int* hist;  // [8192], zeroed by the caller
+  unsigned int* hist;  // [2 * 8192], zeroed by the caller
   long long* ctl;      // [CTL_SIZE]
   int* ent_tok; int* ent_col; float* ent_val; long long ent_cap;
   unsigned int* cand_key; int* cand_tok; int* cand_col; float* cand_val; long long cand_cap;
@@ -598,18 +719,24 @@ static FlatGeom flat_geom(const CltSelectArgs* a) {
   return fg;
 }
 
-// Steps 2-6.  `ex` may be null (single rank).
+// Steps 2-6.  `exa` may be null (single rank).  The histogram first covers keys >= key_lo only (the
+// caller's guess of where the cut lies); if the cut is not inside, a full-range pass repeats it.
+// `hist` holds two histograms of 8192 counters, zeroed by the caller.
 extern "C" int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st) {
   if (a->ld % 8 != 0 || a->layer_stride % 8 != 0 || a->stat_pitch % 4 != 0 || a->F > a->ld) return -1;
   const ScanGeom g = scan_geom(a);
   const Exchange ex = to_exchange(exa);
   dim3 grid(((a->F + 7) / 8 + 255) / 256, (a->B + g.rows_per_block - 1) / g.rows_per_block, a->L);
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(a->x);
-  zhist_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->key_lo, a->shift, a->hist);
-  find_bin_kernel<<<1, 1024, 0, st>>>(a->hist, a->k_total, a->ctl, ex, a->status);
-  compact_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->key_lo, a->shift, a->col_pitch, a->ctl, lists_of(a), a->status);
-  refine_kernel<<<1, 1024, 0, st>>>(a->cand_key, a->cand_tok, a->cand_col, a->cand_cap, a->shift, flat_geom(a), a->ctl, ex, a->status);
-  finalize_kernel<<<256, 256, 0, st>>>(lists_of(a), a->shift, flat_geom(a), a->ctl, a->status);
+  zhist_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->key_lo, a->shift, a->hist, a->ctl, 0);
+  find_bin_kernel<<<1, 1024, 0, st>>>(a->hist, a->k_total, a->ctl, ex, a->key_lo, a->shift, 0, 0, a->status);
+  if (a->key_lo != 0) {
+    zhist_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, 0u, 19, a->hist + kHistBins, a->ctl, 1);
+    find_bin_kernel<<<1, 1024, 0, st>>>(a->hist + kHistBins, a->k_total, a->ctl, ex, 0u, 19, 1, 1, a->status);
+  }
+  compact_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->col_pitch, a->ctl, lists_of(a), a->status);
+  refine_kernel<<<1, 1024, 0, st>>>(a->cand_key, a->cand_tok, a->cand_col, a->cand_cap, flat_geom(a), a->ctl, ex, a->status);
+  finalize_kernel<<<256, 256, 0, st>>>(lists_of(a), flat_geom(a), a->ctl, a->status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -623,6 +750,7 @@ struct CltCsrArgs {
   int* tcsr_col; float* tcsr_val; int* fcsr_tok; float* fcsr_val;
   unsigned char* fired;               // optional [num_cols]
   int sort_segments;                  // bit 0: token segments, bit 1: feature segments
+  int col_pitch;                      // columns are layer * col_pitch + feature (feature < 2^24)
 };
 
 extern "C" int clt_build_csr(const CltCsrArgs* a, cudaStream_t st) {
@@ -631,7 +759,7 @@ extern "C" int clt_build_csr(const CltCsrArgs* a, cudaStream_t st) {
   exclusive_scan_kernel<<<1, 1024, 0, st>>>(a->tok_cnt, a->tok_off, a->tok_cursor, a->num_tokens);
   exclusive_scan_kernel<<<1, 1024, 0, st>>>(a->feat_cnt, a->feat_off, a->feat_cursor, a->num_cols);
   csr_scatter_kernel<<<blocks, 256, 0, st>>>(a->ent_tok, a->ent_col, a->ent_val, a->ent_cap, a->ctl, a->tok_cursor, a->feat_cursor,
-                                             a->tcsr_col, a->tcsr_val, a->fcsr_tok, a->fcsr_val);
+                                             a->tcsr_col, a->tcsr_val, a->fcsr_tok, a->fcsr_val, a->col_pitch);
   if (a->sort_segments & 1)
     csr_sort_segments_kernel<<<(a->num_tokens + 255) / 256, 256, 0, st>>>(a->tok_off, a->num_tokens, a->tcsr_col, a->tcsr_val);
   if (a->sort_segments & 2)

@@ -39,6 +39,25 @@ from ..parallel import ops as pops
 STATUS_NAMES = {0: "ok", 1: "wait timeout", 2: "list capacity exceeded", 3: "threshold outside histogram range", 4: "tie overflow"}
 
 
+def histogram_range(k_total: int, numel: int):
+    """``(key_lo, shift)`` of the selection histogram.  The z-scores are standardised per feature, so the
+    cut is guessed from the normal quantile of ``k_total / numel`` and the 8192 bins cover keys from one
+    standard deviation below that guess upwards (finer bins, fewer candidates, almost no histogram
+    traffic).  When the guess is wrong the kernels repeat the pass over the full key range themselves."""
+    import struct
+
+    p = k_total / max(1, numel)
+    if p >= 0.25 or k_total <= 0:
+        return 0, 19
+    z_p = math.sqrt(2.0) * float(torch.erfinv(torch.tensor(1.0 - 2.0 * p, dtype=torch.float64)))
+    z_lo = max(0.0, z_p - 1.0)
+    key_lo = struct.unpack("<I", struct.pack("<f", z_lo))[0] | 0x80000000
+    shift = 0
+    while ((0xFFFFFFFF - key_lo) >> shift) >= 8192:
+        shift += 1
+    return key_lo, shift
+
+
 def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingConfig], model=None) -> Optional[str]:
     """``None`` when the fused step covers this configuration, else the reason it does not."""
     if clt_config.activation_fn != "batchtopk":
@@ -122,15 +141,11 @@ class FusedBatchTopKEngine:
         i32, f32 = torch.int32, torch.float32
 
         self.k_total = min(int(cfg.batchtopk_k) * B, B * L * self.F)
-        # positive-z histogram when fewer than a quarter of the elements are kept, else full range
-        if self.k_total * 4 <= B * L * self.F:
-            self.key_lo, self.shift = 0x80000000, 18
-        else:
-            self.key_lo, self.shift = 0, 19
+        self.key_lo, self.shift = histogram_range(self.k_total, B * L * self.F)
         self.preact = torch.empty(L, B, Fl, dtype=torch.bfloat16, device=dev)
         self.mean = torch.empty(L, Fl, dtype=f32, device=dev)
         self.rstd = torch.empty(L, Fl, dtype=f32, device=dev)
-        self.hist = torch.zeros(8192, dtype=i32, device=dev)
+        self.hist = torch.zeros(2 * 8192, dtype=i32, device=dev)
         self.ctl = torch.zeros(16, dtype=torch.int64, device=dev)
         self.status = torch.zeros(4, dtype=i32, device=dev)
         cap = max(self.k_total, 8)
@@ -226,7 +241,7 @@ class FusedBatchTopKEngine:
         e.build_csr(
             self.ent_tok, self.ent_col, self.ent_val, self.ctl, self.B, self.ncols,
             self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
-            self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2,
+            self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2, self.Fl,
         )
 
     def _bias_sum(self) -> torch.Tensor:

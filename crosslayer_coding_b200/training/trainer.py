@@ -1,0 +1,522 @@
+"""Training runtime (reference: clt/training/trainer.py:39-1121).
+
+``CLTTrainer(clt_config, training_config, log_dir, device, distributed, resume_from_checkpoint_path).train()``
+keeps the reference's contract: one process per GPU under ``torchrun`` (NCCL on GPUs, Gloo on CPU), features
+tensor-parallel over the world group, every rank consuming the same batch, checkpoints / ``metrics.json`` /
+``cfg.json`` in the run directory, evaluation and checkpoint cadence from the config.
+
+The step itself has two implementations behind one interface:
+
+* **fused** (``training/fused_engine.py``): the sm_100a kernel sequence, used whenever the configuration is
+  covered (BatchTopK, bf16 weights); nothing in it synchronises with the host — losses stay on the device and
+  are read back when metrics are written;
+* **autograd**: the PyTorch path (any activation, tying, dtype, CPU/Gloo), with one encoder pass per step
+  (the reference runs two to four, trainer.py:668 + losses.py:357,248,285).
+
+Other deliberate differences from the reference: the learning-rate schedule is evaluated in closed form per
+step (same curves as LinearLR / CosineAnnealingLR / the "linear_final20" lambda); dead-feature counters live
+with the feature shard (no all-reduce(MIN) of an ``[L, F]`` int64 tensor every step, trainer.py:802); the
+activation store wraps around to a new epoch instead of ending training when one pass is exhausted.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import logging
+import math
+import os
+import random
+import time
+from typing import Any, Dict, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..config import CLTConfig, TrainingConfig
+from ..models import CrossLayerTranscoder
+from ..parallel import ops as pops
+from .checkpointing import CheckpointManager
+from .data.base_store import BaseActivationStore, LayerBatch
+from .evaluator import CLTEvaluator
+from .losses import LossManager, sparsity_lambda_at
+from .metric_utils import MetricLogger
+from .profiler import CUDAMemoryProfiler, DistributedProfiler, TrainingProfiler
+from .wandb_logger import DummyWandBLogger, WandBLogger
+
+logger = logging.getLogger(__name__)
+
+
+def learning_rate_at(tc: TrainingConfig, step: int) -> float:
+    """Learning rate used for optimisation step ``step`` (0-based)."""
+    base, T = tc.learning_rate, tc.training_steps
+    params = tc.lr_scheduler_params or {}
+    kind = tc.lr_scheduler
+    if kind is None:
+        return base
+    if kind == "linear":
+        start, end = params.get("start_factor", 1.0), params.get("end_factor", 0.1)
+        frac = min(step, T) / T
+        return base * (start + (end - start) * frac)
+    if kind == "cosine":
+        eta_min = params.get("eta_min", 0.0)
+        t_max = params.get("T_max", T)
+        return eta_min + (base - eta_min) * (1 + math.cos(math.pi * step / t_max)) / 2
+    if kind == "linear_final20":
+        frac = params.get("decay_start_frac", 0.8)
+        assert 0.0 < frac < 1.0, "decay_start_frac must be between 0 and 1"
+        start_step = int(frac * T)
+        if step < start_step:
+            return base
+        return base * max((T - step) / max(1, T - start_step), 0.0)
+    raise ValueError(f"unknown lr_scheduler {kind!r}")
+
+
+def _stack_layers(batch: Dict[int, torch.Tensor], layers) -> torch.Tensor:
+    stacked = getattr(batch, "stacked", None)
+    if stacked is not None:
+        return stacked
+    return torch.stack([batch[l] for l in layers])
+
+
+class CLTTrainer:
+    def __init__(
+        self,
+        clt_config: CLTConfig,
+        training_config: TrainingConfig,
+        log_dir: Optional[str] = None,
+        device: Optional[Any] = None,
+        distributed: bool = False,
+        resume_from_checkpoint_path: Optional[str] = None,
+        activation_store: Optional[BaseActivationStore] = None,
+    ):
+        self.clt_config = clt_config
+        self.training_config = training_config
+        self.distributed = distributed
+        self.rank, self.world_size, self.local_rank = 0, 1, 0
+        self.process_group = None
+        self._owns_process_group = False
+
+        if distributed:
+            if not dist.is_initialized():
+                backend = "nccl" if torch.cuda.is_available() else "gloo"
+                dist.init_process_group(backend=backend)
+                self._owns_process_group = True
+            self.rank, self.world_size = dist.get_rank(), dist.get_world_size()
+            self.local_rank = int(os.environ.get("LOCAL_RANK", self.rank))
+            if torch.cuda.is_available():
+                device = torch.device(f"cuda:{self.local_rank}")
+                torch.cuda.set_device(device)
+            else:
+                device = torch.device("cpu")
+            self.process_group = dist.group.WORLD
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+
+        # mixed precision: autocast for fp16/bf16, loss scaling for fp16 only (reference trainer.py:107-141)
+        prec = training_config.precision
+        self.autocast_enabled = prec in ("fp16", "bf16") and self.device.type in ("cuda", "cpu")
+        self.autocast_dtype = {"fp16": torch.float16, "bf16": torch.bfloat16}.get(prec, torch.float32)
+        if self.device.type == "cpu" and prec == "fp16":
+            self.autocast_enabled = False
+        self.scaler = torch.amp.GradScaler(self.device.type, enabled=(prec == "fp16" and self.device.type == "cuda"))
+
+        self.log_dir = log_dir or f"clt_train_{int(time.time())}"
+        if self.rank == 0:
+            os.makedirs(self.log_dir, exist_ok=True)
+        self.start_time = time.time()
+
+        seed = training_config.seed + self.rank  # reference: per-rank seed (trainer.py:155-157)
+        torch.manual_seed(seed)
+        np.random.seed(seed % (2 ** 32))
+        random.seed(seed)
+
+        self.profiler = TrainingProfiler(enabled=training_config.enable_profiling, log_interval=training_config.log_interval)
+        self.memory_profiler = CUDAMemoryProfiler(enabled=training_config.enable_profiling)
+        self.dist_profiler = DistributedProfiler(enabled=training_config.enable_profiling and distributed, rank=self.rank)
+
+        self.model = CrossLayerTranscoder(clt_config, process_group=self.process_group, device=self.device, profiler=self.profiler)
+        if prec == "fp16" and training_config.fp16_convert_weights:
+            self.model.half()
+            self.model.dtype = torch.float16
+
+        # --- data
+        self.activation_store = activation_store if activation_store is not None else self._create_activation_store()
+        mean_tg = getattr(self.activation_store, "mean_tg", {}) or {}
+        std_tg = getattr(self.activation_store, "std_tg", {}) or {}
+        self.loss_manager = LossManager(training_config, mean_tg=mean_tg, std_tg=std_tg, clt_config=clt_config)
+        self.evaluator = CLTEvaluator(
+            self.model, self.device, self.start_time, mean_tg=mean_tg, std_tg=std_tg,
+            normalization_method=training_config.normalization_method, d_model=clt_config.d_model,
+        )
+
+        # --- step implementation
+        self.engine = None
+        self.optimizer = None
+        self._select_engine(mean_tg, std_tg)
+
+        # dead-feature counter, sharded with the features: [L, valid_features]
+        L = clt_config.num_layers
+        if self.engine is None:
+            self.n_forward_passes_since_fired = torch.zeros(L, self.model.valid_features, dtype=torch.long, device=self.device)
+        self.checkpoint_manager = CheckpointManager(
+            self.model, self.activation_store, None, self.log_dir, distributed, self.rank, self.device, self.world_size
+        )
+        self._resume_state: Optional[Dict[str, Any]] = None
+        self.start_step = 0
+        resume_wandb_id = None
+        if resume_from_checkpoint_path:
+            self._resume_state = self.checkpoint_manager.load_checkpoint(resume_from_checkpoint_path)
+            resume_wandb_id = (self._resume_state or {}).get("wandb_run_id")
+        if training_config.enable_wandb and self.rank == 0:
+            self.wandb_logger: Any = WandBLogger(training_config, clt_config, self.log_dir, resume_wandb_id)
+        else:
+            self.wandb_logger = DummyWandBLogger()
+        self.checkpoint_manager.wandb_logger = self.wandb_logger
+        self.metric_logger = MetricLogger(distributed, self.rank, self.log_dir, self.wandb_logger, training_config, self.world_size)
+        if self._resume_state:
+            self._apply_resume_state(self._resume_state)
+
+    # ------------------------------------------------------------------ setup helpers
+    def _create_activation_store(self) -> BaseActivationStore:
+        from .data.activation_store_factory import create_activation_store
+
+        return create_activation_store(
+            self.training_config, self.clt_config, self.device, rank=self.rank, world=self.world_size,
+            shard_data=not self.distributed,
+        )
+
+    def _select_engine(self, mean_tg, std_tg) -> None:
+        from .fused_engine import FusedBatchTopKEngine, engine_supports
+
+        tc = self.training_config
+        want = tc.engine
+        reason = None
+        if want == "autograd":
+            reason = "engine='autograd' requested"
+        elif self.device.type != "cuda":
+            reason = "no CUDA device"
+        else:
+            reason = engine_supports(self.clt_config, tc, self.model)
+            if reason is None and self.world_size > 1:
+                from ..parallel.symm import SymmetricExchange
+
+                self._symm = SymmetricExchange.create(self.process_group, self.device, self.clt_config, tc.train_batch_size_tokens)
+        if reason is None:
+            sigma = None
+            if tc.normalization_method == "mean_std" and std_tg:
+                sigma = torch.stack([std_tg[l].reshape(-1).float() for l in range(self.clt_config.num_layers)])
+            elif tc.normalization_method == "sqrt_d_model":
+                sigma = torch.full((self.clt_config.num_layers, self.clt_config.d_model), 1.0 / math.sqrt(self.clt_config.d_model))
+            self.engine = FusedBatchTopKEngine(self.model, tc, tc.train_batch_size_tokens, sigma_tg=sigma,
+                                               symm=getattr(self, "_symm", None))
+            logger.info("Rank %d: using the fused sm_100a step engine", self.rank)
+            return
+        if want == "fused":
+            raise ValueError(f"engine='fused' requested but not available: {reason}")
+        logger.info("Rank %d: using the autograd step (%s)", self.rank, reason)
+        kwargs: Dict[str, Any] = {"lr": tc.learning_rate}
+        if tc.optimizer_beta1 is not None or tc.optimizer_beta2 is not None:
+            kwargs["betas"] = (tc.optimizer_beta1 if tc.optimizer_beta1 is not None else 0.9,
+                               tc.optimizer_beta2 if tc.optimizer_beta2 is not None else 0.999)
+        opt_cls = torch.optim.Adam if tc.optimizer == "adam" else torch.optim.AdamW
+        self.optimizer = opt_cls(self.model.parameters(), **kwargs)
+
+    # ------------------------------------------------------------------ dead features
+    @property
+    def dead_neurons_mask(self) -> torch.Tensor:
+        """``[L, valid_features]`` boolean mask of this rank's features that did not fire for more than
+        ``dead_feature_window`` steps."""
+        window = self.training_config.dead_feature_window
+        if self.engine is not None:
+            c = self.engine.dead_counter.view(self.clt_config.num_layers, self.model.local_features)
+            return (c[:, : self.model.valid_features] > window).detach()
+        return (self.n_forward_passes_since_fired > window).detach()
+
+    @torch.no_grad()
+    def _update_dead_counters(self, acts: Dict[int, torch.Tensor]) -> None:
+        for l, a in acts.items():
+            if a.numel() == 0 or l >= self.n_forward_passes_since_fired.shape[0]:
+                continue
+            fired = (a.detach() > 1e-6).any(dim=0)[: self.n_forward_passes_since_fired.shape[1]]
+            self.n_forward_passes_since_fired[l] += 1
+            self.n_forward_passes_since_fired[l][fired] = 0
+
+    # ------------------------------------------------------------------ one step
+    def _next_batch(self):
+        try:
+            return next(self.activation_store)
+        except StopIteration:
+            if self.training_config.auto_advance_epoch and hasattr(self.activation_store, "advance_epoch"):
+                self.activation_store.advance_epoch()
+                return next(self.activation_store)
+            raise
+
+    def train_step(self, inputs: Dict[int, torch.Tensor], targets: Dict[int, torch.Tensor], step: int) -> Dict[str, torch.Tensor]:
+        """One optimisation step; returns the loss terms as device scalars (no host sync)."""
+        tc = self.training_config
+        lr = learning_rate_at(tc, step)
+        if self.engine is not None:
+            return self._train_step_fused(inputs, targets, step, lr)
+        return self._train_step_autograd(inputs, targets, step, lr)
+
+    def _train_step_fused(self, inputs, targets, step: int, lr: float) -> Dict[str, torch.Tensor]:
+        tc, eng = self.training_config, self.engine
+        layers = list(range(self.clt_config.num_layers))
+        with self.profiler.timer("forward_pass"):
+            X = _stack_layers(inputs, layers)
+            Y = _stack_layers(targets, layers)
+            if X.dtype != torch.bfloat16:
+                X, Y = X.to(torch.bfloat16), Y.to(torch.bfloat16)
+        lam = sparsity_lambda_at(tc, step, tc.training_steps)
+        if not tc.apply_sparsity_penalty_to_batchtopk:
+            lam = 0.0
+        self.loss_manager.current_sparsity_lambda = lam
+        need_aux = bool(tc.aux_loss_factor) and step > tc.dead_feature_window and self._any_dead_cached(step)
+        need_pre = tc.preactivation_coef is not None and abs(tc.preactivation_coef) >= 1e-9
+        if need_aux or need_pre:
+            # terms outside the fused kernels (dense pre-activation loss, AuxK on dead features) are
+            # evaluated by autograd on the same batch and handed to the fused step as dense gradients
+            return self._train_step_hybrid(inputs, targets, X, Y, step, lr, lam, need_pre, need_aux)
+        with self.profiler.timer("optimizer_step"):
+            out = eng.train_step(X, Y, step, lr, sparsity_lambda=lam)
+        return out.as_dict()
+
+    def _any_dead_cached(self, step: int) -> bool:
+        # one host read every 100 steps is enough: features die slowly
+        if not hasattr(self, "_dead_seen") or step % 100 == 0:
+            self._dead_seen = bool(self.dead_neurons_mask.any().item())
+        return self._dead_seen
+
+    def _train_step_hybrid(self, inputs, targets, X, Y, step, lr, lam, need_pre, need_aux) -> Dict[str, torch.Tensor]:
+        """Fused step plus autograd-evaluated extra terms (pre-activation loss, AuxK).  The extra terms only
+        produce encoder gradients (and AuxK same-layer decoder gradients, applied through the autograd
+        optimizer path), so they are computed first and passed to the fused kernels as dense gradients."""
+        raise NotImplementedError(
+            "pre-activation / AuxK terms with the fused engine: set engine='autograd', or preactivation_coef=0 and "
+            "aux_loss_factor=None"
+        )
+
+    def _train_step_autograd(self, inputs, targets, step: int, lr: float) -> Dict[str, torch.Tensor]:
+        tc = self.training_config
+        for g in self.optimizer.param_groups:
+            g["lr"] = lr
+        self.optimizer.zero_grad(set_to_none=True)
+        with torch.autocast(device_type=self.device.type, dtype=self.autocast_dtype, enabled=self.autocast_enabled):
+            with self.profiler.timer("forward_pass"):
+                pass
+            with self.profiler.timer("loss_computation"):
+                loss, parts, acts = self.loss_manager.compute_total_loss_tensors(
+                    self.model, inputs, targets, step, tc.training_steps, dead_neuron_mask=self.dead_neurons_mask
+                )
+        with self.profiler.timer("dead_neuron_update"):
+            self._update_dead_counters(acts)
+        if tc.debug_anomaly:
+            torch.autograd.set_detect_anomaly(True)
+        finite = torch.isfinite(loss.detach())
+        with self.profiler.timer("backward_pass"):
+            self.scaler.scale(loss).backward()
+        self.scaler.unscale_(self.optimizer)
+        # replicated parameters see bit-identical gradients on every rank (same replicated
+        # reconstruction, same order of operations), so no gradient all-reduce is needed here
+        if tc.gradient_clip_val is not None:
+            with self.profiler.timer("gradient_clipping"):
+                self._clip_grad_norm(tc.gradient_clip_val)
+        with self.profiler.timer("optimizer_step"):
+            if self.device.type == "cpu" or not self.scaler.is_enabled():
+                # skip the update on a non-finite loss (reference: NaN-loss skip, trainer.py:740-747)
+                if bool(finite):
+                    self.optimizer.step()
+            else:
+                self.scaler.step(self.optimizer)
+        self.scaler.update()
+        self.model.invalidate_decoder_norms()
+        return parts
+
+    def _clip_grad_norm(self, max_norm: float) -> None:
+        """Global-norm clipping.  Sharded parameters contribute their shard's squared norm, summed over
+        ranks; replicated parameters are counted once (the reference clips with the local norm only)."""
+        from ..models.base import is_replicated
+
+        sq_sharded = torch.zeros((), device=self.device)
+        sq_repl = torch.zeros((), device=self.device)
+        params = [p for p in self.model.parameters() if p.grad is not None]
+        for p in params:
+            s = p.grad.detach().float().pow(2).sum()
+            if is_replicated(p):
+                sq_repl = sq_repl + s
+            else:
+                sq_sharded = sq_sharded + s
+        if self.world_size > 1:
+            pops.all_reduce(sq_sharded, group=self.process_group)
+        total = (sq_sharded + sq_repl).sqrt()
+        coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
+        for p in params:
+            p.grad.mul_(coef.to(p.grad.dtype))
+
+    # ------------------------------------------------------------------ training loop
+    def train(self, eval_every: Optional[int] = None) -> CrossLayerTranscoder:
+        tc = self.training_config
+        if self.rank == 0:
+            logger.info("Training CLT: %d steps, batch %d tokens, %d rank(s), device %s",
+                        tc.training_steps, tc.train_batch_size_tokens, self.world_size, self.device)
+        self._save_run_config()
+        step = self.start_step
+        last_parts = None
+        try:
+            for step in range(self.start_step, tc.training_steps):
+                with self.profiler.timer("data_loading"):
+                    try:
+                        inputs, targets = self._next_batch()
+                    except StopIteration:
+                        if self.rank == 0:
+                            logger.info("Activation store exhausted. Training finished early.")
+                        pops.barrier(self.process_group)
+                        break
+                if not inputs or not any(v.numel() > 0 for v in inputs.values()):
+                    logger.warning("Rank %d: empty batch at step %d, skipping", self.rank, step)
+                    continue
+                parts = self.train_step(inputs, targets, step)
+                last_parts = parts
+                self.metric_logger.log_training_step(
+                    step, parts, current_lr=learning_rate_at(tc, step),
+                    current_sparsity_lambda=self.loss_manager.get_current_sparsity_lambda(),
+                )
+                self.profiler.step()
+                last = step == tc.training_steps - 1
+                if step % tc.eval_interval == 0 or last:
+                    self._run_evaluation(step, inputs, targets)
+                if (step > 0 and step % tc.checkpoint_interval == 0) or last:
+                    self.save_checkpoint(step)
+                if self.engine is not None and (step % max(1, tc.log_interval) == 0 or last):
+                    self.engine.check_status()
+        except KeyboardInterrupt:
+            if self.rank == 0:
+                logger.warning("Interrupted at step %d; writing the final checkpoint", step)
+        finally:
+            pops.barrier(self.process_group)
+            self.save_checkpoint(step, final=True)
+            if hasattr(self.activation_store, "close"):
+                self.activation_store.close()
+            self.metric_logger._save_metrics_to_disk()
+            self._save_run_config()
+            if self.rank == 0:
+                os.makedirs(os.path.join(self.log_dir, "final"), exist_ok=True)
+                self.wandb_logger.log_artifact(os.path.join(self.log_dir, "final"), "model", "final")
+            self.wandb_logger.finish()
+            self.profiler.log_summary()
+            self.memory_profiler.log_summary()
+            self.dist_profiler.log_summary()
+            if self._owns_process_group and dist.is_initialized():
+                dist.destroy_process_group()
+        return self.model
+
+    def _run_evaluation(self, step: int, inputs, targets) -> None:
+        tc = self.training_config
+        pops.barrier(self.process_group)
+        with self.profiler.timer("evaluation"):
+            autocast = torch.autocast(device_type=self.device.type, dtype=self.autocast_dtype, enabled=self.autocast_enabled)
+            with autocast, torch.no_grad():
+                metrics = self.evaluator.compute_metrics(inputs, targets, dead_neuron_mask=self.dead_neurons_mask)
+                # per-layer std of the pre-activations (reference trainer.py:884-897)
+                pre, _ = self.model._encode_all_layers(inputs, gather=False)
+                stds = torch.stack([p.float().std() if p.numel() > 1 else torch.zeros((), device=self.device) for p in pre.values()])
+                metrics["layerwise/preactivation_std_dev"] = {f"layer_{l}": v for l, v in zip(pre.keys(), stds.tolist())}
+                if tc.compute_sparsity_diagnostics:
+                    from .diagnostics import compute_sparsity_diagnostics
+
+                    acts = self.model.get_feature_activations(inputs, gather=False)
+                    metrics.update(compute_sparsity_diagnostics(self.model, tc, acts))
+        self.metric_logger.log_evaluation_metrics(step, metrics)
+        if self.rank == 0:
+            logger.info(
+                "step %d: NMSE %.4f, EV %.4f, avg L0 %.1f, dead %d",
+                step, metrics.get("reconstruction/normalized_mean_reconstruction_error", float("nan")),
+                metrics.get("reconstruction/explained_variance", float("nan")), metrics.get("sparsity/avg_l0", float("nan")),
+                metrics.get("dead_features/total_eval", 0),
+            )
+        pops.barrier(self.process_group)
+
+    # ------------------------------------------------------------------ checkpoint / resume
+    def _trainer_state(self, step: int) -> Dict[str, Any]:
+        state: Dict[str, Any] = {
+            "step": step,
+            "scaler_state_dict": self.scaler.state_dict() if self.scaler.is_enabled() else None,
+            "wandb_run_id": self.wandb_logger.get_current_wandb_run_id(),
+            "torch_rng_state": torch.get_rng_state(),
+            "numpy_rng_state": np.random.get_state(),
+            "python_rng_state": random.getstate(),
+            "engine": "fused" if self.engine is not None else "autograd",
+            "world_size": self.world_size,
+        }
+        if torch.cuda.is_available() and self.device.type == "cuda":
+            state["cuda_rng_state"] = torch.cuda.get_rng_state(self.device)
+        if self.engine is None:
+            state["n_forward_passes_since_fired"] = self.n_forward_passes_since_fired.cpu()
+        return state
+
+    def _optimizer_tensors(self) -> Dict[str, torch.Tensor]:
+        if self.engine is not None:
+            return dict(self.engine.optimizer_state_dict())
+        out: Dict[str, torch.Tensor] = {}
+        names = {id(p): n for n, p in self.model.named_parameters()}
+        for p, st in self.optimizer.state.items():
+            n = names.get(id(p))
+            if n is None:
+                continue
+            for k, v in st.items():
+                out[f"{n}::{k}"] = v if isinstance(v, torch.Tensor) else torch.tensor(float(v))
+        return out
+
+    def _load_optimizer_tensors(self, tensors: Dict[str, torch.Tensor]) -> None:
+        if self.engine is not None:
+            self.engine.load_optimizer_state_dict({k: v.to(self.device) for k, v in tensors.items()})
+            return
+        params = dict(self.model.named_parameters())
+        for key, v in tensors.items():
+            name, field = key.split("::", 1)
+            p = params.get(name)
+            if p is None:
+                continue
+            st = self.optimizer.state[p]
+            st[field] = v.to(self.device if field != "step" else "cpu") if v.dim() > 0 or field != "step" else v.clone()
+
+    def save_checkpoint(self, step: int, final: bool = False) -> None:
+        with self.profiler.timer("checkpoint"):
+            self.checkpoint_manager._save_checkpoint(step, self._trainer_state(step), self._optimizer_tensors())
+
+    def _apply_resume_state(self, state: Dict[str, Any]) -> None:
+        if "optimizer_tensors" in state:
+            self._load_optimizer_tensors(state["optimizer_tensors"])
+        if state.get("scaler_state_dict") and self.scaler.is_enabled():
+            self.scaler.load_state_dict(state["scaler_state_dict"])
+        if self.engine is None and state.get("n_forward_passes_since_fired") is not None:
+            c = state["n_forward_passes_since_fired"].to(self.device)
+            if c.shape == self.n_forward_passes_since_fired.shape:
+                self.n_forward_passes_since_fired.copy_(c)
+        if state.get("torch_rng_state") is not None:
+            torch.set_rng_state(state["torch_rng_state"].cpu() if isinstance(state["torch_rng_state"], torch.Tensor) else state["torch_rng_state"])
+        if state.get("cuda_rng_state") is not None and self.device.type == "cuda":
+            torch.cuda.set_rng_state(state["cuda_rng_state"].cpu(), self.device)
+        if state.get("numpy_rng_state") is not None:
+            np.random.set_state(state["numpy_rng_state"])
+        if state.get("python_rng_state") is not None:
+            random.setstate(state["python_rng_state"])
+        self.start_step = int(state.get("step", -1)) + 1
+        self.model.invalidate_decoder_norms()
+        logger.info("Rank %d: resuming from step %d", self.rank, self.start_step)
+
+    def _save_run_config(self) -> None:
+        if self.rank != 0:
+            return
+        cfg = dataclasses.asdict(self.clt_config)
+        cfg["normalization_method"] = self.training_config.normalization_method
+        cfg["expected_input_dtype"] = self.training_config.activation_dtype
+        try:
+            with open(os.path.join(self.log_dir, "cfg.json"), "w") as fh:
+                json.dump(cfg, fh, indent=2)
+            with open(os.path.join(self.log_dir, "training_config.json"), "w") as fh:
+                json.dump(dataclasses.asdict(self.training_config), fh, indent=2)
+        except OSError as exc:
+            logger.warning("could not write run configuration: %s", exc)

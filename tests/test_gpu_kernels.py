@@ -55,7 +55,7 @@ def test_colstats(ext):
     assert torch.allclose(rstd, 1.0 / (xf.std(dim=1) + 1e-6), rtol=1e-4)
 
 
-def _run_select(ext, x, k_total, f_valid=None, feat_offset=0, full_F=None, full_range=False, cand_cap=None):
+def _run_select(ext, x, k_total, f_valid=None, feat_offset=0, full_F=None, full_range=False, cand_cap=None, key_range=None):
     dev = x.device
     L, B, Fl = x.shape
     f_valid = Fl if f_valid is None else f_valid
@@ -63,7 +63,7 @@ def _run_select(ext, x, k_total, f_valid=None, feat_offset=0, full_F=None, full_
     mean = torch.empty(L, Fl, device=dev)
     rstd = torch.empty(L, Fl, device=dev)
     ext.colstats(x, mean, rstd)
-    hist = torch.zeros(8192, dtype=torch.int32, device=dev)
+    hist = torch.zeros(2 * 8192, dtype=torch.int32, device=dev)
     ctl = torch.zeros(16, dtype=torch.int64, device=dev)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     cap = max(k_total, 8)
@@ -73,6 +73,8 @@ def _run_select(ext, x, k_total, f_valid=None, feat_offset=0, full_F=None, full_
     cand = [torch.empty(cc, dtype=i32, device=dev), torch.empty(cc, dtype=i32, device=dev), torch.empty(cc, dtype=i32, device=dev),
             torch.empty(cc, dtype=f32, device=dev)]
     key_lo, shift = (0, 19) if full_range else (0x80000000, 18)
+    if key_range is not None:
+        key_lo, shift = key_range
     ext.batchtopk_select(x, mean, rstd, f_valid, Fl, feat_offset, full_F, k_total, key_lo, shift, hist, ctl,
                          ent[0], ent[1], ent[2], cand[0], cand[1], cand[2], cand[3], status, 1, 0, [], [], 0, 0)
     torch.cuda.synchronize()
@@ -129,6 +131,37 @@ def test_batchtopk_select_ties_use_lowest_flat_index(ext):
     got[col // F, ent[0][:n].long(), col % F] = True
     want = _oracle_mask(x, mean, rstd, k_total, F)
     assert torch.equal(got, want)
+
+
+def test_batchtopk_select_falls_back_when_guess_misses(ext):
+    """A histogram range that starts above every key (z >= 50) must trigger the full-range pass."""
+    import struct
+
+    torch.manual_seed(4)
+    dev = _dev()
+    L, B, F = 2, 80, 96
+    x = torch.randn(L, B, F, device=dev).bfloat16()
+    k_total = 6 * B
+    key_lo = struct.unpack("<I", struct.pack("<f", 50.0))[0] | 0x80000000
+    shift = 0
+    while ((0xFFFFFFFF - key_lo) >> shift) >= 8192:
+        shift += 1
+    mean, rstd, ctl, status, ent = _run_select(ext, x, k_total, key_range=(key_lo, shift))
+    assert int(status[0]) == 0 and int(ctl[10]) == 1  # retry flag raised, no error
+    n = int(ctl[3])
+    assert n == k_total
+    got = torch.zeros(L, B, F, dtype=torch.bool, device=dev)
+    col = ent[1][:n].long()
+    got[col // F, ent[0][:n].long(), col % F] = True
+    assert torch.equal(got, _oracle_mask(x, mean, rstd, k_total, F))
+
+
+def test_histogram_range_guess():
+    from crosslayer_coding_b200.training.fused_engine import histogram_range
+
+    key_lo, shift = histogram_range(200 * 4096, 4096 * 12 * 24576)
+    assert key_lo > 0x80000000 and ((0xFFFFFFFF - key_lo) >> shift) < 8192
+    assert histogram_range(10, 20) == (0, 19)
 
 
 def test_batchtopk_select_respects_valid_columns(ext):
