@@ -68,8 +68,18 @@ struct CltDecodeArgs {
   float* yhat_partial;
   const float* bias_sum; const float* addend; const void* target; const float* sigma;
   void* gs; float* yhat_out; double* sq_err;
+  void* stage_peers[8];
+  int rows_per_rank, rank, world;
   int mode;
 };
+struct CltPeerTable {
+  int world;
+  int rank;
+  void* ptr[8];
+};
+int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int* status, cudaStream_t st);
+int clt_owner_reduce_loss(const float* stage, const CltPeerTable* gs_peers, const float* bias_sum, const float* addend, const void* target,
+                          const float* sigma, float* yhat_out, double* sq_err, int L, int B, int d, int rows_per_rank, cudaStream_t st);
 int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st);
 int clt_recon_epilogue(const float* yhat_sum, const float* bias_sum, const float* addend, const void* target, const float* sigma,
                        void* gs, float* yhat_out, double* sq_err, int L, int B, int d, int row0, int nrows, cudaStream_t st);
@@ -227,7 +237,8 @@ void dead_counter_update(Tensor& counter, Tensor& fired) {
 void sparse_decode(const std::vector<Tensor>& dec_w, int64_t L, int64_t B, int64_t d, int64_t col_pitch, int64_t tying, const Tensor& tok_off,
                    const Tensor& tcsr_col, const Tensor& tcsr_val, const OptTensor& feat_offset, const OptTensor& feat_scale,
                    const OptTensor& yhat_partial, const OptTensor& bias_sum, const OptTensor& addend, const OptTensor& target,
-                   const OptTensor& sigma, const OptTensor& gs, const OptTensor& yhat_out, const OptTensor& sq_err, int64_t mode) {
+                   const OptTensor& sigma, const OptTensor& gs, const OptTensor& yhat_out, const OptTensor& sq_err, int64_t mode,
+                   const std::vector<int64_t>& stage_peers, int64_t rows_per_rank, int64_t rank) {
   TORCH_CHECK(dec_w.size() <= 32, "at most 32 decoder tensors");
   CltDecodeArgs a;
   std::memset(&a, 0, sizeof(a));
@@ -242,7 +253,11 @@ void sparse_decode(const std::vector<Tensor>& dec_w, int64_t L, int64_t B, int64
   a.yhat_partial = opt_ptr<float>(yhat_partial); a.bias_sum = opt_ptr<const float>(bias_sum); a.addend = opt_ptr<const float>(addend);
   a.target = opt_ptr<const void>(target); a.sigma = opt_ptr<const float>(sigma); a.gs = opt_ptr<void>(gs);
   a.yhat_out = opt_ptr<float>(yhat_out); a.sq_err = opt_ptr<double>(sq_err); a.mode = int(mode);
-  if (mode == 0) {
+  if (mode == 2) {
+    TORCH_CHECK(stage_peers.size() >= 1 && stage_peers.size() <= 8 && rows_per_rank > 0, "mode 2 needs the peers' staging pointers");
+    for (size_t i = 0; i < stage_peers.size(); ++i) a.stage_peers[i] = reinterpret_cast<void*>(stage_peers[i]);
+    a.rows_per_rank = int(rows_per_rank); a.rank = int(rank); a.world = int(stage_peers.size());
+  } else if (mode == 0) {
     TORCH_CHECK(a.yhat_partial != nullptr, "mode 0 needs yhat_partial");
   } else {
     TORCH_CHECK(a.bias_sum && a.target && a.gs && a.sq_err, "mode 1 needs bias_sum, target, gs, sq_err");
@@ -260,6 +275,34 @@ void recon_epilogue(const Tensor& yhat_sum, const Tensor& bias_sum, const OptTen
   check(clt_recon_epilogue(yhat_sum.data_ptr<float>(), bias_sum.data_ptr<float>(), opt_ptr<const float>(addend), target.data_ptr(),
                            opt_ptr<const float>(sigma), gs.data_ptr(), opt_ptr<float>(yhat_out), sq_err.data_ptr<double>(), L, B, d,
                            int(row0), int(nrows), cur_stream()), "recon_epilogue");
+}
+
+CltPeerTable make_table(const std::vector<int64_t>& ptrs, int64_t rank) {
+  TORCH_CHECK(ptrs.size() >= 1 && ptrs.size() <= 8, "peer table holds 1..8 pointers");
+  CltPeerTable t;
+  std::memset(&t, 0, sizeof(t));
+  t.world = int(ptrs.size()); t.rank = int(rank);
+  for (size_t i = 0; i < ptrs.size(); ++i) t.ptr[i] = reinterpret_cast<void*>(ptrs[i]);
+  return t;
+}
+
+void peer_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t slot, int64_t seq, Tensor& status) {
+  need(status, at::kInt, "status");
+  const CltPeerTable t = make_table(flag_ptrs, rank);
+  c10::cuda::CUDAGuard guard(status.device());
+  check(clt_peer_barrier(&t, int(slot), static_cast<unsigned int>(seq), status.data_ptr<int>(), cur_stream()), "peer_barrier");
+}
+
+void owner_reduce_loss(const Tensor& stage, const std::vector<int64_t>& gs_ptrs, int64_t rank, const Tensor& bias_sum, const OptTensor& addend,
+                       const Tensor& target, const OptTensor& sigma, const OptTensor& yhat_out, Tensor& sq_err, int64_t rows_per_rank) {
+  need(stage, at::kFloat, "stage"); need(bias_sum, at::kFloat, "bias_sum"); need(target, at::kBFloat16, "target"); need(sq_err, at::kDouble, "sq_err");
+  const int L = target.size(0), B = target.size(1), d = target.size(2);
+  const CltPeerTable t = make_table(gs_ptrs, rank);
+  TORCH_CHECK(stage.numel() >= 1LL * t.world * L * rows_per_rank * d, "staging area too small");
+  c10::cuda::CUDAGuard guard(stage.device());
+  check(clt_owner_reduce_loss(stage.data_ptr<float>(), &t, bias_sum.data_ptr<float>(), opt_ptr<const float>(addend), target.data_ptr(),
+                              opt_ptr<const float>(sigma), opt_ptr<float>(yhat_out), sq_err.data_ptr<double>(), L, B, d, int(rows_per_rank),
+                              cur_stream()), "owner_reduce_loss");
 }
 
 void gs_colsum(const Tensor& gs, Tensor& out) {
@@ -350,6 +393,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sparse_decode", &sparse_decode);
   m.def("recon_epilogue", &recon_epilogue);
   m.def("gs_colsum", &gs_colsum);
+  m.def("peer_barrier", &peer_barrier);
+  m.def("owner_reduce_loss", &owner_reduce_loss);
   m.def("decoder_rows_adam", &decoder_rows_adam);
   m.def("encoder_rows_adam", &encoder_rows_adam);
   m.def("dense_adam", &dense_adam);

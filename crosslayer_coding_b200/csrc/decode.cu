@@ -35,6 +35,10 @@ struct DecodeParams {
   __nv_bfloat16* gs;                   // mode 1: [L, B, d] (y_hat - y) * sigma^2
   float* yhat_out;                     // mode 1: optional [L, B, d] fp32 reconstruction
   double* sq_err;                      // mode 1: [L] sum of ((y_hat - y) * sigma)^2
+  // mode 2 (tensor parallel): partial sums are pushed into the staging area of the rank that owns the token.
+  // stage_peers[o] = rank o's staging area [world][L][rows_per_rank][d] fp32; this rank writes slot `rank`.
+  float* stage_peers[8];
+  int rows_per_rank, rank, world;
   int mode;
 };
 
@@ -129,6 +133,13 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
       float4* dst = reinterpret_cast<float4*>(p.yhat_partial + off);
       dst[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
       dst[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+    } else if (p.mode == 2) {
+      // reduce-scatter by push: peer store into the owner's slot for this rank (NVLink posted writes)
+      const int owner = tok / p.rows_per_rank;
+      const int lrow = tok - owner * p.rows_per_rank;
+      float4* dst = reinterpret_cast<float4*>(p.stage_peers[owner] + ((1LL * p.rank * p.L + t) * p.rows_per_rank + lrow) * p.d + e0);
+      dst[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+      dst[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
     } else {
       float y[8], out[8];
       const uint4 tv = *reinterpret_cast<const uint4*>(p.target + off);
@@ -158,7 +169,7 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
       atomicAdd(&sq_s[t], sq);
     }
   }
-  if (p.mode != 0) {
+  if (p.mode == 1) {
     __syncthreads();
     if (threadIdx.x < p.L && sq_s[threadIdx.x] != 0.f) atomicAdd(&p.sq_err[threadIdx.x], double(sq_s[threadIdx.x]));
   }
@@ -239,6 +250,8 @@ struct CltDecodeArgs {
   float* yhat_partial;
   const float* bias_sum; const float* addend; const void* target; const float* sigma;
   void* gs; float* yhat_out; double* sq_err;
+  void* stage_peers[8];
+  int rows_per_rank, rank, world;
   int mode;
 };
 
@@ -252,6 +265,8 @@ extern "C" int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st) {
   p.yhat_partial = a->yhat_partial; p.bias_sum = a->bias_sum; p.addend = a->addend;
   p.target = static_cast<const __nv_bfloat16*>(a->target); p.sigma = a->sigma;
   p.gs = static_cast<__nv_bfloat16*>(a->gs); p.yhat_out = a->yhat_out; p.sq_err = a->sq_err; p.mode = a->mode;
+  for (int i = 0; i < 8; ++i) p.stage_peers[i] = static_cast<float*>(a->stage_peers[i]);
+  p.rows_per_rank = a->rows_per_rank; p.rank = a->rank; p.world = a->world;
   const int gthreads = ((a->d / 8 + 31) / 32) * 32;
   const int threads = gthreads * kGroups;
   if (threads > 1024) return -1;

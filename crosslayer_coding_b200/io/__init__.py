@@ -1,0 +1,3 @@
+from . import hdf5, manifest, native
+
+__all__ = ["hdf5", "manifest", "native"]

@@ -86,6 +86,8 @@ def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingCon
             pass
         if training_config.precision == "fp16":
             return "fp16 loss scaling"
+        if training_config.preactivation_coef is not None and abs(training_config.preactivation_coef) >= 1e-9:
+            return "pre-activation loss (dense encoder gradient)"
     return None
 
 
@@ -173,7 +175,7 @@ class FusedBatchTopKEngine:
         self.fcsr_val = torch.zeros(cap, dtype=f32, device=dev)
         self.fired = torch.zeros(ncols, dtype=torch.uint8, device=dev)
         self.dead_counter = torch.zeros(ncols, dtype=torch.int64, device=dev)
-        self.gs = torch.empty(L, B, d, dtype=torch.bfloat16, device=dev)
+        self.gs = symm.gs if (symm is not None and self.world > 1) else torch.empty(L, B, d, dtype=torch.bfloat16, device=dev)
         self.sq_err = torch.zeros(L, dtype=torch.float64, device=dev)
         self.penalty = torch.zeros(1, dtype=torch.float64, device=dev)
         self.gs_sum = torch.zeros(L, d, dtype=f32, device=dev)
@@ -182,7 +184,6 @@ class FusedBatchTopKEngine:
         self.norm2 = torch.zeros(ncols, dtype=f32, device=dev)      # per decoder tensor rows
         self.norm2_next = torch.zeros(ncols, dtype=f32, device=dev)
         self.norms_valid = False
-        self.yhat_partial = torch.empty(L, B, d, dtype=f32, device=dev) if self.world > 1 else None
         self.sigma = None
         if sigma_tg is not None:
             self.sigma = sigma_tg.to(device=dev, dtype=f32).reshape(L, d).contiguous()
@@ -211,6 +212,7 @@ class FusedBatchTopKEngine:
             self.decb_m, self.decb_v = z(model.dec_bias), z(model.dec_bias)
         self.opt_step = 0
         self.seq = 0
+        self.kernel_launches = 0  # launches of this package's own kernels (reported by the benchmark)
 
     # ------------------------------------------------------------------ pieces
     def _exchange_args(self):
@@ -243,6 +245,8 @@ class FusedBatchTopKEngine:
             self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
             self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2, self.Fl,
         )
+        # gemm, colstats, select (zhist, find_bin [x2 when the narrow range is used], compact, refine, finalize), csr (5)
+        self.kernel_launches += 2 + (7 if self.key_lo != 0 else 5) + 5
 
     def _bias_sum(self) -> torch.Tensor:
         return (self.bias_sel @ self.model.dec_bias.data.float()).contiguous()
@@ -256,15 +260,23 @@ class FusedBatchTopKEngine:
         bias_sum = self._bias_sum()
         if self.world == 1:
             e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
-                            None, None, None, bias_sum, None, Y, self.sigma, self.gs, yhat, self.sq_err, 1)
+                            None, None, None, bias_sum, None, Y, self.sigma, self.gs, yhat, self.sq_err, 1, [], 0, 0)
+            self.kernel_launches += 1
         else:
+            sy = self.symm
+            if yhat is not None:
+                yhat.zero_()
+            # 1. decode, pushing every token's partial sums into its owner's staging slot (peer stores)
             e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
-                            None, None, self.yhat_partial, None, None, None, None, None, None, None, 0)
-            if self.symm is not None and self.symm.supports_reduce:
-                self.symm.all_reduce_sum_(self.yhat_partial)
-            else:
-                pops.all_reduce(self.yhat_partial, group=self.group)
-            e.recon_epilogue(self.yhat_partial, bias_sum, None, Y, self.sigma, self.gs, yhat, self.sq_err, 0, self.B)
+                            None, None, None, None, None, None, None, None, None, None, 2, sy.stage_ptrs, sy.rows_per_rank, self.rank)
+            sy.barrier(e, self.status)
+            # 2. owners reduce their rows, finish the loss and push the gradient seed to every rank
+            e.owner_reduce_loss(sy.stage, sy.gs_ptrs, self.rank, bias_sum, None, Y, self.sigma, yhat, self.sq_err, sy.rows_per_rank)
+            sy.barrier(e, self.status)
+            pops.all_reduce(self.sq_err, group=self.group)
+            if yhat is not None:
+                pops.all_reduce(yhat, group=self.group)
+            self.kernel_launches += 4
         return yhat
 
     def _hyper(self, lr: float, grad_scale: float) -> List[float]:
@@ -325,6 +337,7 @@ class FusedBatchTopKEngine:
         e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v,
                             self.feat_off, self.fcsr_tok, self.grad_a, X, None, None, self._hyper(lr, 1.0))
         e.dead_counter_update(self.dead_counter, self.fired)
+        self.kernel_launches += 5 + (1 if use_pen else 0)  # gs_colsum, decoder/encoder Adam, dense Adam, dead counters
         m.invalidate_decoder_norms()
         recon = (self.sq_err.sum() / (B * d)).float()
         sparsity = self.penalty[0].float()
