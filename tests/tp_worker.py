@@ -1,0 +1,84 @@
+"""Worker for the tensor-parallel GPU tests (launched with torch.distributed.run, one rank per GPU).
+
+Builds the same seeded full model on every rank, keeps this rank's feature shard, runs a few fused training
+steps on fixed data and writes the per-step losses and the merged (un-sharded) weights from rank 0.
+"""
+import argparse
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder, TrainingConfig  # noqa: E402
+from crosslayer_coding_b200.training.checkpointing import merge_shards, slice_for_rank  # noqa: E402
+from crosslayer_coding_b200.training.fused_engine import FusedBatchTopKEngine  # noqa: E402
+
+
+def build_full_state(cfg):
+    torch.manual_seed(1234)
+    full = CrossLayerTranscoder(CLTConfig(**cfg.to_dict()), device="cpu")
+    return {k: v.clone() for k, v in full.state_dict().items()}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--features", type=int, default=512)
+    ap.add_argument("--lam", type=float, default=0.0)
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    L, d, F, B, k = 3, 64, args.features, 128, 8
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="batchtopk", batchtopk_k=k, clt_dtype="bfloat16")
+    full_state = build_full_state(cfg)
+    model = CrossLayerTranscoder(cfg, process_group=group, device=dev)
+    model.load_state_dict(slice_for_rank(full_state, rank, world, F) if world > 1 else full_state)
+    tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="bf16",
+                        sparsity_lambda=0.0, preactivation_coef=0.0)
+    symm = None
+    if world > 1:
+        from crosslayer_coding_b200.parallel.symm import SymmetricExchange
+
+        symm = SymmetricExchange.create(group, dev, cfg, B)
+    eng = FusedBatchTopKEngine(model, tc, B, symm=symm)
+    g = torch.Generator().manual_seed(7)
+    X = torch.randn(L, B, d, generator=g).bfloat16().to(dev)
+    A = torch.randn(d, d, generator=g) / d ** 0.5
+    Y = (X.float().cpu() @ A).bfloat16().to(dev)
+    losses, entries = [], []
+    for step in range(args.steps):
+        out = eng.train_step(X, Y, step, 1e-3, sparsity_lambda=args.lam)
+        losses.append(float(out.reconstruction))
+        n = out.num_entries.clone().float()
+        if world > 1:
+            dist.all_reduce(n)
+        entries.append(int(n))
+    torch.cuda.synchronize()
+    eng.check_status()
+    sd = {k: v.detach().float().cpu() for k, v in model.state_dict().items()}
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, sd)
+        merged = merge_shards(gathered, F)
+    else:
+        merged = sd
+    if rank == 0:
+        torch.save({"losses": losses, "entries": entries, "state": merged, "world": world}, args.out)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
