@@ -771,3 +771,72 @@ extern "C" int clt_dead_counter_update(long long* counter, unsigned char* fired,
   dead_counter_kernel<<<(n + 255) / 256, 256, 0, st>>>(counter, fired, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
+
+// ====================================================================== allocation-free CSR build
+#include <cstdio>
+#include <mutex>
+
+#include "csr_static.h"
+
+// Scratch of clt_build_csr_static: [tok_cnt | feat_cnt | tok_cursor | feat_cursor], each region sized for the
+// maximum problem.  One copy per GPU that loads this library; host code must not pass this name to a kernel
+// (on the host it is only a stand-in) - the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) int csr_static_scratch[2 * (CLT_CSR_STATIC_MAX_TOKENS + CLT_CSR_STATIC_MAX_COLS)];
+
+namespace {
+constexpr int kMaxDevicesStatic = 64;
+int* g_static_scratch_ptr[kMaxDevicesStatic] = {nullptr};
+std::mutex g_static_scratch_mu;
+
+// Device address of the scratch array on the current device; looked up once per device.
+int* csr_static_scratch_address() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevicesStatic) return nullptr;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    int* p = nullptr;
+    const cudaError_t rc = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), csr_static_scratch);
+    if (rc != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "clt_build_csr_static: cudaGetSymbolAddress failed on device %d: %s\n", dev, cudaGetErrorString(rc));
+      return nullptr;
+    }
+    g_static_scratch_ptr[dev] = p;
+  }
+  return g_static_scratch_ptr[dev];
+}
+}  // namespace
+
+extern "C" int clt_build_csr_static(const int* ent_tok, const int* ent_col, const float* ent_val, long long ent_cap,
+                                    const long long* ctl, int num_tokens, int num_cols, int col_pitch, int* tok_off, int* feat_off,
+                                    int* tcsr_col, float* tcsr_val, int* fcsr_tok, float* fcsr_val, int sort_segments,
+                                    cudaStream_t stream) {
+  if (!ent_tok || !ent_col || !ent_val || !ctl || !tok_off || !feat_off || !tcsr_col || !tcsr_val || !fcsr_tok || !fcsr_val ||
+      ent_cap <= 0 || num_tokens <= 0 || num_cols <= 0 || col_pitch <= 0 || col_pitch >= (1 << 24)) {
+    fprintf(stderr, "clt_build_csr_static: bad argument (null pointer, non-positive size or col_pitch outside (0, 2^24))\n");
+    return -1;
+  }
+  if (num_tokens > CLT_CSR_STATIC_MAX_TOKENS || num_cols > CLT_CSR_STATIC_MAX_COLS) {
+    fprintf(stderr, "clt_build_csr_static: num_tokens=%d / num_cols=%d exceed the built-in scratch (max %d tokens, %d columns); "
+                    "use clt_build_csr with caller-provided scratch\n",
+            num_tokens, num_cols, CLT_CSR_STATIC_MAX_TOKENS, CLT_CSR_STATIC_MAX_COLS);
+    return -2;
+  }
+  int* scratch = csr_static_scratch_address();
+  if (scratch == nullptr) return -3;
+  int* tok_cnt = scratch;
+  int* feat_cnt = tok_cnt + CLT_CSR_STATIC_MAX_TOKENS;
+  int* tok_cursor = feat_cnt + CLT_CSR_STATIC_MAX_COLS;
+  int* feat_cursor = tok_cursor + CLT_CSR_STATIC_MAX_TOKENS;
+  // the array still holds the previous call's counters: clear the parts that must start at zero
+  if (cudaMemsetAsync(tok_cnt, 0, sizeof(int) * size_t(num_tokens), stream) != cudaSuccess) return -5;
+  if (cudaMemsetAsync(feat_cnt, 0, sizeof(int) * size_t(num_cols), stream) != cudaSuccess) return -5;
+  const int blocks = 592;
+  csr_count_kernel<<<blocks, 256, 0, stream>>>(ent_tok, ent_col, ent_val, ent_cap, ctl, tok_cnt, feat_cnt, nullptr);
+  exclusive_scan_kernel<<<1, 1024, 0, stream>>>(tok_cnt, tok_off, tok_cursor, num_tokens);
+  exclusive_scan_kernel<<<1, 1024, 0, stream>>>(feat_cnt, feat_off, feat_cursor, num_cols);
+  csr_scatter_kernel<<<blocks, 256, 0, stream>>>(ent_tok, ent_col, ent_val, ent_cap, ctl, tok_cursor, feat_cursor, tcsr_col, tcsr_val,
+                                                 fcsr_tok, fcsr_val, col_pitch);
+  if (sort_segments & 1) csr_sort_segments_kernel<<<(num_tokens + 255) / 256, 256, 0, stream>>>(tok_off, num_tokens, tcsr_col, tcsr_val);
+  if (sort_segments & 2) csr_sort_segments_kernel<<<(num_cols + 255) / 256, 256, 0, stream>>>(feat_off, num_cols, fcsr_tok, fcsr_val);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
