@@ -33,6 +33,11 @@ import torch.distributed as dist
 from safetensors.torch import load_file as load_safetensors_file
 from safetensors.torch import save_file as save_safetensors_file
 
+try:
+    from safetensors import SafetensorError
+except ImportError:  # very old safetensors
+    SafetensorError = OSError  # type: ignore[misc,assignment]
+
 logger = logging.getLogger(__name__)
 
 _FEATURE_DIM0 = ("encoder_module.encoders.",)  # weight [F_local, d], bias_param [F_local]
@@ -132,7 +137,7 @@ class CheckpointManager:
                 self._save_distributed(step, trainer_state_to_save, optimizer_tensors)
             else:
                 self._save_single(step, trainer_state_to_save, optimizer_tensors)
-        except OSError as exc:  # checkpoint IO problems are logged, not fatal (reference behaviour)
+        except (OSError, SafetensorError) as exc:  # checkpoint IO problems are logged, not fatal (reference behaviour)
             logger.warning("Rank %d: failed to save checkpoint at step %d: %s", self.rank, step, exc)
 
     def _store_state(self):
@@ -165,8 +170,7 @@ class CheckpointManager:
     def _save_distributed(self, step, trainer_state, optimizer_tensors) -> None:
         step_dir = os.path.join(self.log_dir, f"step_{step}")
         latest_dir = os.path.join(self.log_dir, "latest")
-        if self.rank == 0:
-            os.makedirs(step_dir, exist_ok=True)
+        os.makedirs(step_dir, exist_ok=True)
         self._barrier()
         sd = self.model.state_dict()
         _atomic_save_safetensors(sd, os.path.join(step_dir, f"rank_{self.rank}_model.safetensors"))

@@ -50,13 +50,9 @@ class InMemoryActivationStore(BaseActivationStore):
             self.epoch += 1
         idx = self.cursor
         self.cursor += 1
-        if self.stager.cuda:
-            slot = self.stager._next
-            self.stager._next = (slot + 1) % self.stager.depth
-            self.stager.submit(slot, src=self.pool[idx])
-        else:
-            slot = 0
-            self.stager.submit(0, src=self.pool[idx])
+        slot = self.stager._next
+        self.stager._next = (slot + 1) % self.stager.depth
+        self.stager.submit(slot, src=self.pool[idx])
         self._inflight.append((slot, idx))
         return True
 

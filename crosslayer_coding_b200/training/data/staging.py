@@ -17,7 +17,7 @@ class DeviceStager:
     def __init__(self, shape: Tuple[int, ...], dtype: torch.dtype, device: torch.device, depth: int = 3):
         self.device = torch.device(device)
         self.cuda = self.device.type == "cuda"
-        self.depth = max(2, depth) if self.cuda else 1
+        self.depth = max(2, depth)
         self.shape = tuple(shape)
         self.dtype = dtype
         self.bytes_per_batch = int(torch.tensor([], dtype=dtype).element_size()) * int(torch.Size(shape).numel())
@@ -28,8 +28,10 @@ class DeviceStager:
             self.copied: List[Optional[torch.cuda.Event]] = [None] * self.depth
             self.released: List[Optional[torch.cuda.Event]] = [None] * self.depth
         else:
-            self.host = [torch.empty(shape, dtype=dtype)]
-            self.dev = self.host
+            # CPU: the "device" slot is the host buffer itself; several slots so a producer thread never
+            # overwrites a batch the consumer still holds
+            self.host = [torch.empty(shape, dtype=dtype) for _ in range(self.depth)]
+            self.dev = list(self.host)
         self._next = 0
 
     def host_slot(self) -> Tuple[int, torch.Tensor]:
@@ -45,7 +47,7 @@ class DeviceStager:
         """Start the async copy of host slot ``slot`` (or of the pinned tensor ``src``) to its device slot."""
         if not self.cuda:
             if src is not None:
-                self.dev[0] = src
+                self.dev[slot] = src
             return
         with torch.cuda.stream(self.stream):
             if self.released[slot] is not None:
