@@ -147,6 +147,8 @@ struct DecAdamParams {
   float* norm2_out;            // optional [L * F_pitch]: sum of squares of the updated rows (atomicAdd; zeroed by caller)
   const float* feat_offset;    // tied decoders: optional [L, F_pitch] affine applied to the activation
   const float* feat_scale;
+  const float* dgrad_row0;     // optional [ntensors, F_pitch, d] fp32: extra gradient of every feature's first row
+                               // (the same-layer decoder row that the auxiliary loss trains)
   AdamHyper h;
 };
 
@@ -269,12 +271,14 @@ __global__ void __launch_bounds__(256, 2) decoder_rows_adam_untied_kernel(const 
         }
       }
       if (act) {
-        float m[8], v[8];
+        float m[8], v[8], dg0[8];
         f4x2_to8(cur.m0, cur.m1, m);
         f4x2_to8(cur.v0, cur.v1, v);
+        if (r == 0 && p.dgrad_row0) load8f(p.dgrad_row0 + (1LL * col) * d + e0, dg0);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const float gk = fmaf(pc, w[k], g[k] * hr.gscale);
+          float gk = fmaf(pc, w[k], g[k] * hr.gscale);
+          if (r == 0 && p.dgrad_row0) gk += dg0[k];
           adam1(w[k], m[k], v[k], gk, hr);
           norm2 = fmaf(w[k], w[k], norm2);
         }
@@ -380,6 +384,12 @@ __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamPar
       if (act) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) g[k] = fmaf(pc, w[k], g[k] * p.h.grad_scale);
+        if (r == 0 && p.dgrad_row0) {
+          float dg0[8];
+          load8f(p.dgrad_row0 + (1LL * ti * p.F_pitch + f) * p.d + e0, dg0);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) g[k] += dg0[k];
+        }
         float m[8], v[8];
         f4x2_to8(cur.m0, cur.m1, m);
         f4x2_to8(cur.v0, cur.v1, v);
@@ -603,6 +613,7 @@ struct CltDecAdamArgs {
   const int* feat_off; const int* fcsr_tok; const float* fcsr_val;
   const void* gs; float* grad_a; const float* pen_coef; float* norm2_out;
   const float* feat_offset; const float* feat_scale;
+  const float* dgrad_row0;
   CltAdamHyper h;
 };
 
@@ -620,7 +631,7 @@ extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaS
   p.ntensors = a->ntensors; p.L = a->L; p.B = a->B; p.d = a->d; p.F_pitch = a->F_pitch; p.tying = a->tying;
   p.feat_off = a->feat_off; p.fcsr_tok = a->fcsr_tok; p.fcsr_val = a->fcsr_val;
   p.gs = static_cast<const __nv_bfloat16*>(a->gs); p.grad_a = a->grad_a; p.pen_coef = a->pen_coef; p.norm2_out = a->norm2_out;
-  p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale; p.h = to_hyper(a->h);
+  p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale; p.dgrad_row0 = a->dgrad_row0; p.h = to_hyper(a->h);
   if (acc == 0) return 0;
   const int grid = num_sms * 8;
   if (a->tying == 0) {

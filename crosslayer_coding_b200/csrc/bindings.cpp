@@ -97,6 +97,7 @@ struct CltDecAdamArgs {
   const int* feat_off; const int* fcsr_tok; const float* fcsr_val;
   const void* gs; float* grad_a; const float* pen_coef; float* norm2_out;
   const float* feat_offset; const float* feat_scale;
+  const float* dgrad_row0;
   CltAdamHyper h;
 };
 int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st);
@@ -314,7 +315,8 @@ void gs_colsum(const Tensor& gs, Tensor& out) {
 void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vector<Tensor>& v, int64_t L, int64_t B, int64_t d,
                        int64_t F_pitch, int64_t tying, const Tensor& feat_off, const Tensor& fcsr_tok, const Tensor& fcsr_val,
                        const Tensor& gs, const OptTensor& grad_a, const OptTensor& pen_coef, const OptTensor& norm2_out,
-                       const OptTensor& feat_offset, const OptTensor& feat_scale, const std::vector<double>& hyper) {
+                       const OptTensor& feat_offset, const OptTensor& feat_scale, const OptTensor& dgrad_row0,
+                       const std::vector<double>& hyper) {
   TORCH_CHECK(w.size() <= 32 && w.size() == m.size() && w.size() == v.size(), "bad tensor lists");
   CltDecAdamArgs a;
   std::memset(&a, 0, sizeof(a));
@@ -329,6 +331,8 @@ void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vect
   need(gs, at::kBFloat16, "gs");
   a.gs = gs.data_ptr(); a.grad_a = opt_ptr<float>(grad_a); a.pen_coef = opt_ptr<const float>(pen_coef); a.norm2_out = opt_ptr<float>(norm2_out);
   a.feat_offset = opt_ptr<const float>(feat_offset); a.feat_scale = opt_ptr<const float>(feat_scale);
+  a.dgrad_row0 = opt_ptr<const float>(dgrad_row0);
+  if (a.dgrad_row0) TORCH_CHECK(dgrad_row0->scalar_type() == at::kFloat && dgrad_row0->numel() == int64_t(w.size()) * F_pitch * d, "dgrad_row0 must be fp32 [ntensors, F, d]");
   a.h = hyper_from(hyper);
   c10::cuda::CUDAGuard guard(gs.device());
   check(clt_decoder_rows_adam(&a, num_sms(), cur_stream()), "decoder_rows_adam");

@@ -86,8 +86,6 @@ def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingCon
             pass
         if training_config.precision == "fp16":
             return "fp16 loss scaling"
-        if training_config.preactivation_coef is not None and abs(training_config.preactivation_coef) >= 1e-9:
-            return "pre-activation loss (dense encoder gradient)"
     return None
 
 
@@ -307,18 +305,121 @@ class FusedBatchTopKEngine:
         return self.norm2
 
     # -------------------------------------------------------------------- step
-    def train_step(self, X: torch.Tensor, Y: torch.Tensor, step: int, lr: float, sparsity_lambda: float = 0.0) -> StepOutput:
-        """One optimisation step on inputs/targets ``[L, B, d]`` (bf16, already normalised)."""
+    # ------------------------------------------------------- extra loss terms
+    def _extra_buffers(self):
+        if getattr(self, "_enc_dense", None) is None:
+            f32 = torch.float32
+            self._enc_dense = torch.zeros(self.L, self.Fl, self.d, dtype=f32, device=self.dev)
+            self._encb_dense = torch.zeros(self.L, self.Fl, dtype=f32, device=self.dev)
+            self._dec_row0_dense = torch.zeros(len(self.model.dec_weight), self.Fl, self.d, dtype=f32, device=self.dev)
+        return self._enc_dense, self._encb_dense, self._dec_row0_dense
+
+    @torch.no_grad()
+    def _preactivation_term(self, X: torch.Tensor, coef: float) -> torch.Tensor:
+        """``coef * mean(relu(-preact))`` (reference losses.py:203-261) and its dense encoder gradient
+        ``-(coef/numel) * 1[preact < 0]^T X`` - a library GEMM per layer on the stored pre-activations."""
+        enc_dense, encb_dense, _ = self._extra_buffers()
+        numel = float(self.L * self.B * self.F)
+        total = torch.zeros((), device=self.dev)
+        for l in range(self.L):
+            pl = self.preact[l][:, : self.Fv]
+            neg = pl < 0
+            total = total + torch.where(neg, -pl.float(), torch.zeros((), device=self.dev)).sum()
+            g = neg.to(torch.bfloat16)
+            enc_dense[l, : self.Fv].add_((g.t() @ X[l]).float(), alpha=-coef / numel)
+            encb_dense[l, : self.Fv].add_(g.float().sum(dim=0), alpha=-coef / numel)
+        return coef * total / numel
+
+    @torch.no_grad()
+    def _auxiliary_term(self, X: torch.Tensor, dead_mask: torch.Tensor, factor: float, k_aux_default: int = 512) -> torch.Tensor:
+        """AuxK on dead features (reference losses.py:263-329) in closed form on the few dead rows: per layer the
+        top ``k_aux`` dead pre-activations of every token decode to the same layer and are matched to the
+        de-normalised residual.  Gradients go to the dense side buffers (encoder rows, same-layer decoder rows,
+        that pair's bias) and, because the residual depends on the main reconstruction, into the gradient seed."""
+        from ..models import activations as act
+        from ..models.clt import pair_index
+
+        enc_dense, encb_dense, dec0_dense = self._extra_buffers()
+        m = self.model
+        L, B, d = self.L, self.B, self.d
+        n_dead = dead_mask.sum(dim=1).float()
+        if self.world > 1:
+            pops.all_reduce(n_dead, group=self.group)
+        n_dead_host = n_dead.tolist()
+        total = torch.zeros((), device=self.dev)
+        self._aux_bias_grad = torch.zeros_like(self.model.dec_bias.data, dtype=torch.float32)
+        for l in range(L):
+            nd = int(n_dead_host[l])
+            if nd == 0:
+                continue
+            k_aux = max(1, min(k_aux_default, nd))
+            idx = dead_mask[l].nonzero().flatten()
+            xl = X[l].float()
+            pre = xl @ m.enc_weight.data[l][idx].float().t() + m.enc_bias.data[l][idx].float()  # [B, n_local]
+            gidx = (m.feature_start + idx).unsqueeze(0).expand(B, -1)
+            mask = act.sharded_row_topk_mask(pre, gidx, k_aux, self.group) if pre.shape[1] > 0 or self.world > 1 else torch.zeros_like(pre, dtype=torch.bool)
+            aux = pre * mask
+            w_d = m.dec_weight[l].data[idx, 0, :].float()  # the decoder row that maps layer l to itself
+            bias_row = pair_index(l, l, L) if self.tying == 0 else l
+            recon = aux @ w_d
+            if self.world > 1:
+                pops.all_reduce(recon, group=self.group)
+            recon = recon + m.dec_bias.data[bias_row].float()
+            sg = self.sigma[l] if self.sigma is not None else torch.ones(d, device=self.dev)
+            residual = -(self.gs[l].float() / sg)  # (y - y_hat) * sigma
+            r = recon - residual
+            c = factor * min(nd / k_aux, 1.0)
+            total = total + c * (r * r).mean()
+            g_recon = r * (2.0 * c / (B * d))                      # dL/d recon
+            self.gs[l].add_((c * r * sg).to(self.gs.dtype))        # through the residual into the main path
+            g_aux = (g_recon @ w_d.t()) * mask                     # STE: gradient at the kept positions
+            dec0_dense[l].index_add_(0, idx, aux.t() @ g_recon)
+            self._aux_bias_grad[bias_row] += g_recon.sum(dim=0)
+            enc_dense[l].index_add_(0, idx, g_aux.t() @ xl)
+            encb_dense[l].index_add_(0, idx, g_aux.sum(dim=0))
+        return total
+
+    # -------------------------------------------------------------------- step
+    def train_step(self, X: torch.Tensor, Y: torch.Tensor, step: int, lr: float, sparsity_lambda: float = 0.0,
+                   preactivation_coef: float = 0.0, aux_factor: float = 0.0, dead_mask: Optional[torch.Tensor] = None) -> StepOutput:
+        """One optimisation step on inputs/targets ``[L, B, d]`` (bf16, already normalised).
+
+        ``preactivation_coef`` and ``aux_factor`` (with ``dead_mask [L, valid_features]``) switch on the two loss
+        terms that are not sparse: they are evaluated with a few library calls on the stored pre-activations /
+        the dead rows and enter the fused optimizer kernels as dense side gradients."""
         e, m, tc = self.ext, self.model, self.tc
         L, B, d = self.L, self.B, self.d
         self.opt_step += 1
         self.encode_select(X)
         self.decode_loss(Y)
         c_g = 2.0 / (B * d)
+        zero = torch.zeros((), device=self.dev)
+        pre_loss, aux_loss = zero, zero
+        enc_dense = encb_dense = dec0_dense = None
+        extra_bias_grad = None
+        use_pre = abs(preactivation_coef) >= 1e-9
+        use_aux = aux_factor and dead_mask is not None
+        if use_pre or use_aux:
+            enc_dense, encb_dense, dec0_dense = self._extra_buffers()
+            enc_dense.zero_()
+            encb_dense.zero_()
+            if use_pre:
+                pre_loss = self._preactivation_term(X, float(preactivation_coef))
+            if use_aux:
+                dec0_dense.zero_()
+                mask = dead_mask
+                if mask.shape[-1] != self.Fl:
+                    mask = torch.nn.functional.pad(mask, (0, self.Fl - mask.shape[-1]))
+                aux_loss = self._auxiliary_term(X, mask, float(aux_factor))
+                extra_bias_grad = self._aux_bias_grad
+            else:
+                dec0_dense = None
         # decoder biases: dL/db[pair (s,t)] = c_g * sum_b gs[t, b, :]
         self.gs_sum.zero_()
         e.gs_colsum(self.gs, self.gs_sum)
         bias_grad = (self.bias_sel.t() @ self.gs_sum).contiguous()
+        if extra_bias_grad is not None:
+            bias_grad = bias_grad + extra_bias_grad / c_g  # dense_adam multiplies by c_g
         self.grad_a.zero_()
         self.penalty.zero_()
         pen = None
@@ -330,23 +431,22 @@ class FusedBatchTopKEngine:
         self.norm2_next.zero_()
         e.decoder_rows_adam([w.data for w in m.dec_weight], self.dec_m, self.dec_v, L, B, d, self.Fl, self.tying,
                             self.feat_off, self.fcsr_tok, self.fcsr_val, self.gs, self.grad_a, pen, self.norm2_next,
-                            None, None, self._hyper(lr, c_g))
+                            None, None, dec0_dense, self._hyper(lr, c_g))
         self.norm2, self.norm2_next = self.norm2_next, self.norm2
         self.norms_valid = True
         e.dense_adam(m.dec_bias.data, self.decb_m, self.decb_v, bias_grad, self._hyper(lr, c_g))
         e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v,
-                            self.feat_off, self.fcsr_tok, self.grad_a, X, None, None, self._hyper(lr, 1.0))
+                            self.feat_off, self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, self._hyper(lr, 1.0))
         e.dead_counter_update(self.dead_counter, self.fired)
         self.kernel_launches += 5 + (1 if use_pen else 0)  # gs_colsum, decoder/encoder Adam, dense Adam, dead counters
         m.invalidate_decoder_norms()
         recon = (self.sq_err.sum() / (B * d)).float()
         sparsity = self.penalty[0].float()
-        if self.world > 1 and use_pen:
-            sp = sparsity.clone()
-            pops.all_reduce(sp, group=self.group)
-            sparsity = sp
-        zero = torch.zeros((), device=self.dev)
-        return StepOutput(recon, sparsity, zero, zero, recon + sparsity, self.ctl[3])
+        if self.world > 1 and (use_pen or use_pre):
+            both = torch.stack([sparsity, pre_loss.float()])
+            pops.all_reduce(both, group=self.group)
+            sparsity, pre_loss = both[0], both[1]
+        return StepOutput(recon, sparsity, pre_loss, aux_loss, recon + sparsity + pre_loss + aux_loss, self.ctl[3])
 
     # --------------------------------------------------------------- inference
     @torch.no_grad()

@@ -274,13 +274,12 @@ class CLTTrainer:
             lam = 0.0
         self.loss_manager.current_sparsity_lambda = lam
         need_aux = bool(tc.aux_loss_factor) and step > tc.dead_feature_window and self._any_dead_cached(step)
-        need_pre = tc.preactivation_coef is not None and abs(tc.preactivation_coef) >= 1e-9
-        if need_aux or need_pre:
-            # terms outside the fused kernels (dense pre-activation loss, AuxK on dead features) are
-            # evaluated by autograd on the same batch and handed to the fused step as dense gradients
-            return self._train_step_hybrid(inputs, targets, X, Y, step, lr, lam, need_pre, need_aux)
+        pre_coef = tc.preactivation_coef if tc.preactivation_coef is not None else 0.0
         with self.profiler.timer("optimizer_step"):
-            out = eng.train_step(X, Y, step, lr, sparsity_lambda=lam)
+            out = eng.train_step(
+                X, Y, step, lr, sparsity_lambda=lam, preactivation_coef=pre_coef,
+                aux_factor=(tc.aux_loss_factor if need_aux else 0.0), dead_mask=(self.dead_neurons_mask if need_aux else None),
+            )
         return out.as_dict()
 
     def _any_dead_cached(self, step: int) -> bool:
@@ -288,15 +287,6 @@ class CLTTrainer:
         if not hasattr(self, "_dead_seen") or step % 100 == 0:
             self._dead_seen = bool(self.dead_neurons_mask.any().item())
         return self._dead_seen
-
-    def _train_step_hybrid(self, inputs, targets, X, Y, step, lr, lam, need_pre, need_aux) -> Dict[str, torch.Tensor]:
-        """Fused step plus autograd-evaluated extra terms (pre-activation loss, AuxK).  The extra terms only
-        produce encoder gradients (and AuxK same-layer decoder gradients, applied through the autograd
-        optimizer path), so they are computed first and passed to the fused kernels as dense gradients."""
-        raise NotImplementedError(
-            "pre-activation / AuxK terms with the fused engine: set engine='autograd', or preactivation_coef=0 and "
-            "aux_loss_factor=None"
-        )
 
     def _train_step_autograd(self, inputs, targets, step: int, lr: float) -> Dict[str, torch.Tensor]:
         tc = self.training_config

@@ -336,3 +336,48 @@ def test_loss_decreases_over_steps():
         losses.append(out.reconstruction.item())
     eng.check_status()
     assert losses[-1] < 0.7 * losses[0], losses[::10]
+
+
+@pytest.mark.parametrize("tying", ["none", "per_source"])
+def test_fused_step_with_preactivation_and_auxk_terms(tying):
+    """The two dense side terms (pre-activation loss, AuxK on dead features) against the PyTorch LossManager."""
+    from crosslayer_coding_b200.training.losses import LossManager
+
+    cfg, model, tc, eng, X, Y = _engine_and_model(tying=tying, seed=13)
+    tc.preactivation_coef = 0.05
+    tc.aux_loss_factor = 0.5
+    ref = _fp32_copy(model)
+    snap = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+    L, F = cfg.num_layers, cfg.num_features
+    dead = torch.zeros(L, F, dtype=torch.bool, device=X.device)
+    dead[0, ::5] = True
+    dead[2, 3:40] = True
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3)
+    out = eng.train_step(X, Y, step=0, lr=1e-3, preactivation_coef=0.05, aux_factor=0.5, dead_mask=dead)
+    torch.cuda.synchronize()
+    eng.check_status()
+    mask = _oracle_mask(eng.preact, eng.mean, eng.rstd, eng.k_total, F)
+    x = {l: X[l].float() for l in range(L)}
+    y = {l: Y[l].float() for l in range(L)}
+    pre = {l: torch.nn.functional.linear(x[l], ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    acts = {l: (pre[l] + (eng.preact[l].float() - pre[l]).detach()) * mask[l] for l in range(L)}
+    preds = {t: ref.decode({s: acts[s] for s in range(t + 1)}, t) for t in range(L)}
+    lm = LossManager(tc)
+    recon = lm.compute_reconstruction_loss(preds, y)
+    preact = lm.compute_preactivation_loss(ref, x, pre)
+    aux = lm.compute_auxiliary_loss(ref, x, {l: y[l] - preds[l] for l in range(L)}, dead, preacts=pre)
+    (recon + preact + aux).backward()
+    opt.step()
+    assert abs(out.reconstruction.item() - recon.item()) < 2e-3 * max(1.0, recon.item())
+    assert abs(out.preactivation.item() - preact.item()) < 2e-2 * max(1e-3, preact.item())
+    assert abs(out.auxiliary.item() - aux.item()) < 3e-2 * max(1e-3, aux.item()), (out.auxiliary.item(), aux.item())
+    ref_params = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        old = snap[name]
+        upd = p.detach().float() - old
+        ref_upd = ref_params[name].detach() - old
+        bad = ((upd - ref_upd).abs() > 0.008 * old.abs() + 3e-4).float().mean().item()
+        assert bad < 2e-2, (name, bad)
+        touched = ref_upd.abs() > 5e-4
+        agree = (torch.sign(upd[touched]) == torch.sign(ref_upd[touched])).float().mean().item()
+        assert agree > 0.95, (name, agree)
