@@ -1,0 +1,133 @@
+"""BatchTopK/TopK -> JumpReLU conversion with layer-wise L0 calibration.
+
+Workflow of the reference conversion script (scripts/convert_batchtopk_to_jumprelu.py:90-1053):
+estimate per-feature thresholds over N batches (``model.estimate_theta_posthoc``), compare L0 / NMSE of the
+converted model with the original, and optionally calibrate every layer: one scale ``s`` in ``[0.1, 10]``
+multiplies that layer's threshold vector so that the layer's L0 matches the original model's L0.
+
+The reference finds ``s`` by a 15-step binary search that re-encodes a fresh sample of <= 1024 tokens per probe
+(:649-870).  Here the pre-activations of the calibration tokens are computed once per layer and the L0 of
+*every* candidate scale comes from one histogram of ``x / theta`` (``l0_for_scales``), followed by a short exact
+bisection between the two best grid points.
+"""
+from __future__ import annotations
+
+import copy
+import logging
+import math
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+logger = logging.getLogger(__name__)
+
+
+@torch.no_grad()
+def layer_l0(model, inputs: Dict[int, torch.Tensor]) -> Dict[int, float]:
+    """Mean number of active features per token and layer (summed over tensor-parallel shards)."""
+    from .parallel import ops as pops
+
+    acts = model.get_feature_activations(inputs, gather=False)
+    layers = sorted(acts)
+    vals = torch.stack([(acts[l] != 0).float().sum() / max(1, acts[l].shape[0]) for l in layers])
+    if model.world_size > 1:
+        pops.all_reduce(vals, group=model.process_group)
+    return {l: float(v) for l, v in zip(layers, vals.tolist())}
+
+
+@torch.no_grad()
+def l0_for_scales(preact: torch.Tensor, theta: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """``L0(s) = mean_tokens #{f : x_f >= s * theta_f}`` for every ``s`` in the ascending vector ``scales``,
+    from a single pass over ``preact [B, F]``."""
+    ratio = (preact.float() / theta.float().clamp_min(1e-30)).reshape(-1)
+    ratio = ratio[ratio >= scales[0]]
+    # number of scales that an element satisfies = index of the first scale above its ratio
+    k = torch.bucketize(ratio, scales, right=True)  # in 1..len(scales)
+    hist = torch.bincount(k, minlength=scales.numel() + 1).double()
+    # elements with k >= j+1 are active at scale j
+    active = torch.flip(torch.cumsum(torch.flip(hist, dims=[0]), dim=0), dims=[0])[1:]
+    return (active / preact.shape[0]).float()
+
+
+@torch.no_grad()
+def calibrate_layerwise_theta(
+    model,
+    inputs: Dict[int, torch.Tensor],
+    target_l0: Dict[int, float],
+    tolerance: float = 0.5,
+    scale_range: Tuple[float, float] = (0.1, 10.0),
+    grid: int = 257,
+    refine_steps: int = 12,
+) -> Dict[int, float]:
+    """Scale every layer's threshold vector in place so that its L0 on ``inputs`` matches ``target_l0``.
+    Returns the scale applied per layer."""
+    from .parallel import ops as pops
+
+    if model.log_threshold is None:
+        raise ValueError("calibration needs a JumpReLU model (log_threshold missing)")
+    dev = model.log_threshold.device
+    lo, hi = scale_range
+    scales = torch.logspace(math.log10(lo), math.log10(hi), grid, device=dev)
+    applied: Dict[int, float] = {}
+
+    def count(pre, theta, s) -> float:
+        c = (pre >= s * theta).float().sum() / pre.shape[0]
+        if model.world_size > 1:
+            pops.all_reduce(c, group=model.process_group)
+        return float(c)
+
+    for l in sorted(inputs):
+        if l not in target_l0:
+            continue
+        pre = model.get_preactivations(inputs[l].to(dev), l, gather=False).float()
+        theta = model.log_threshold[l][: pre.shape[-1]].float().exp()
+        l0s = l0_for_scales(pre, theta, scales)
+        if model.world_size > 1:
+            pops.all_reduce(l0s, group=model.process_group)
+        tgt = float(target_l0[l])
+        err = (l0s - tgt).abs()
+        j = int(torch.argmin(err))
+        best_s, best_err = float(scales[j]), float(err[j])
+        if best_err > tolerance:
+            # L0 falls with s: bisect exactly between the neighbours that bracket the target
+            a = float(scales[max(j - 1, 0)])
+            b = float(scales[min(j + 1, grid - 1)])
+            for _ in range(refine_steps):
+                mid = math.sqrt(a * b)
+                v = count(pre, theta, mid)
+                if abs(v - tgt) < best_err:
+                    best_s, best_err = mid, abs(v - tgt)
+                if best_err <= tolerance:
+                    break
+                if v > tgt:
+                    a = mid
+                else:
+                    b = mid
+        model.log_threshold.data[l] += math.log(best_s)
+        applied[l] = best_s
+        logger.info("layer %d: scale %.4f, |L0 - target| = %.3f (target %.2f)", l, best_s, best_err, tgt)
+    return applied
+
+
+@torch.no_grad()
+def convert_model_to_jumprelu(
+    model,
+    data_iter: Iterable,
+    num_batches: int,
+    calibration_inputs: Optional[Dict[int, torch.Tensor]] = None,
+    l0_tolerance: float = 0.5,
+    default_theta_value: float = 1e6,
+):
+    """Estimate thresholds, convert ``model`` in place and (when calibration tokens are given) match the
+    original model's layer-wise L0.  Returns ``(report, scales)``."""
+    report: Dict[str, Dict[int, float]] = {}
+    original = None
+    if calibration_inputs is not None:
+        report["l0_original"] = layer_l0(model, calibration_inputs)
+    model.estimate_theta_posthoc(data_iter, num_batches=num_batches, default_theta_value=default_theta_value)
+    scales: Dict[int, float] = {}
+    if calibration_inputs is not None:
+        report["l0_converted"] = layer_l0(model, calibration_inputs)
+        scales = calibrate_layerwise_theta(model, calibration_inputs, report["l0_original"], tolerance=l0_tolerance)
+        report["l0_calibrated"] = layer_l0(model, calibration_inputs)
+    return report, scales

@@ -65,3 +65,28 @@ def test_registry():
         get_activation_fn("nope")
     with pytest.raises(ValueError):
         register_activation_fn("relu")(lambda m, p, l: p)
+
+
+def test_l0_for_scales_matches_direct_count():
+    from crosslayer_coding_b200.conversion import l0_for_scales
+
+    torch.manual_seed(0)
+    pre = torch.randn(200, 40)
+    theta = torch.rand(40) * 0.5 + 0.1
+    scales = torch.logspace(-1, 1, 33)
+    got = l0_for_scales(pre, theta, scales)
+    want = torch.stack([(pre >= s * theta).float().sum() / 200 for s in scales])
+    assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_layerwise_calibration_matches_original_l0():
+    from crosslayer_coding_b200.conversion import convert_model_to_jumprelu, layer_l0
+
+    m = _model(batchtopk_k=8)
+    calib = next(_batches(1, 512))[0]
+    report, scales = convert_model_to_jumprelu(m, _batches(), num_batches=4, calibration_inputs=calib, l0_tolerance=0.25)
+    assert m.config.activation_fn == "jumprelu" and set(scales) == {0, 1}
+    after = layer_l0(m, calib)
+    for l, tgt in report["l0_original"].items():
+        assert abs(after[l] - tgt) <= 0.5, (l, after[l], tgt)
+        assert abs(after[l] - tgt) <= abs(report["l0_converted"][l] - tgt) + 1e-6
