@@ -41,6 +41,8 @@ struct CltSelectArgs {
   int* ent_tok; int* ent_col; float* ent_val; long long ent_cap;
   unsigned int* cand_key; int* cand_tok; int* cand_col; float* cand_val; long long cand_cap;
   int* status;
+  long long* sel_state;
+  unsigned int* pool_key; int* pool_tok; int* pool_col; float* pool_val; long long pool_cap;
 };
 int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st);
 
@@ -71,6 +73,7 @@ struct CltDecodeArgs {
   void* stage_peers[8];
   int rows_per_rank, rank, world;
   int mode;
+  int* status;
 };
 struct CltPeerTable {
   int world;
@@ -181,12 +184,13 @@ void batchtopk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, i
                       int64_t full_F, int64_t k_total, int64_t key_lo, int64_t shift, Tensor& hist, Tensor& ctl, Tensor& ent_tok,
                       Tensor& ent_col, Tensor& ent_val, Tensor& cand_key, Tensor& cand_tok, Tensor& cand_col, Tensor& cand_val,
                       Tensor& status, int64_t world, int64_t rank, const std::vector<int64_t>& ex_data,
-                      const std::vector<int64_t>& ex_flags, int64_t slot_elems, int64_t seq) {
+                      const std::vector<int64_t>& ex_flags, int64_t slot_elems, int64_t seq, const OptTensor& sel_state,
+                      const OptTensor& pool) {
   need(x, at::kBFloat16, "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd");
   need(hist, at::kInt, "hist"); need(ctl, at::kLong, "ctl"); need(status, at::kInt, "status");
   need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
   need(cand_key, at::kInt, "cand_key"); need(cand_tok, at::kInt, "cand_tok"); need(cand_col, at::kInt, "cand_col"); need(cand_val, at::kFloat, "cand_val");
-  TORCH_CHECK(hist.numel() >= 2 * 8192 && ctl.numel() >= 16, "hist needs 2 * 8192 and ctl 16 elements");
+  TORCH_CHECK(hist.numel() >= 2 * 8192 + 32 && ctl.numel() >= 16, "hist needs 2 * 8192 + 32 and ctl 16 elements");
   CltSelectArgs a;
   a.x = x.data_ptr(); a.mean = mean.data_ptr<float>(); a.rstd = rstd.data_ptr<float>();
   a.L = x.size(0); a.B = x.size(1); a.F = int(f_valid); a.stat_pitch = int(mean.size(-1));
@@ -198,6 +202,19 @@ void batchtopk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, i
   a.cand_key = reinterpret_cast<unsigned int*>(cand_key.data_ptr<int>()); a.cand_tok = cand_tok.data_ptr<int>();
   a.cand_col = cand_col.data_ptr<int>(); a.cand_val = cand_val.data_ptr<float>(); a.cand_cap = cand_key.numel();
   a.status = status.data_ptr<int>();
+  a.sel_state = nullptr; a.pool_key = nullptr; a.pool_tok = nullptr; a.pool_col = nullptr; a.pool_val = nullptr; a.pool_cap = 0;
+  if (sel_state.has_value() && sel_state->defined()) {
+    // tracked range: {key_lo, shift} on the device plus the pool [4, cap] (key, token, column, value bits)
+    need(*sel_state, at::kLong, "sel_state");
+    TORCH_CHECK(pool.has_value() && pool->defined(), "sel_state needs a pool");
+    need(*pool, at::kInt, "pool");
+    TORCH_CHECK(sel_state->numel() >= 2 && pool->dim() == 2 && pool->size(0) == 4, "sel_state needs 2 elements and pool the shape [4, cap]");
+    a.sel_state = reinterpret_cast<long long*>(sel_state->data_ptr<int64_t>());
+    a.pool_cap = pool->size(1);
+    int* pb = pool->data_ptr<int>();
+    a.pool_key = reinterpret_cast<unsigned int*>(pb); a.pool_tok = pb + a.pool_cap; a.pool_col = pb + 2 * a.pool_cap;
+    a.pool_val = reinterpret_cast<float*>(pb + 3 * a.pool_cap);
+  }
   CltExchangeArgs ex;
   const bool multi = fill_exchange(ex, world, rank, ex_data, ex_flags, slot_elems, seq);
   c10::cuda::CUDAGuard guard(x.device());
@@ -239,7 +256,7 @@ void sparse_decode(const std::vector<Tensor>& dec_w, int64_t L, int64_t B, int64
                    const Tensor& tcsr_col, const Tensor& tcsr_val, const OptTensor& feat_offset, const OptTensor& feat_scale,
                    const OptTensor& yhat_partial, const OptTensor& bias_sum, const OptTensor& addend, const OptTensor& target,
                    const OptTensor& sigma, const OptTensor& gs, const OptTensor& yhat_out, const OptTensor& sq_err, int64_t mode,
-                   const std::vector<int64_t>& stage_peers, int64_t rows_per_rank, int64_t rank) {
+                   const std::vector<int64_t>& stage_peers, int64_t rows_per_rank, int64_t rank, const OptTensor& status) {
   TORCH_CHECK(dec_w.size() <= 32, "at most 32 decoder tensors");
   CltDecodeArgs a;
   std::memset(&a, 0, sizeof(a));
@@ -254,6 +271,7 @@ void sparse_decode(const std::vector<Tensor>& dec_w, int64_t L, int64_t B, int64
   a.yhat_partial = opt_ptr<float>(yhat_partial); a.bias_sum = opt_ptr<const float>(bias_sum); a.addend = opt_ptr<const float>(addend);
   a.target = opt_ptr<const void>(target); a.sigma = opt_ptr<const float>(sigma); a.gs = opt_ptr<void>(gs);
   a.yhat_out = opt_ptr<float>(yhat_out); a.sq_err = opt_ptr<double>(sq_err); a.mode = int(mode);
+  a.status = opt_ptr<int>(status);
   if (mode == 2) {
     TORCH_CHECK(stage_peers.size() >= 1 && stage_peers.size() <= 8 && rows_per_rank > 0, "mode 2 needs the peers' staging pointers");
     for (size_t i = 0; i < stage_peers.size(); ++i) a.stage_peers[i] = reinterpret_cast<void*>(stage_peers[i]);

@@ -51,6 +51,51 @@ __device__ __forceinline__ void fma8(float (&acc)[8], float a, const uint4& v) {
   }
 }
 
+// Output of one (token, target, 8-element slice): partial sums (mode 0), peer push (mode 2) or the finished
+// loss epilogue (mode 1).
+__device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int tok, int t, int e0, const float (&a)[8], float* sq_s) {
+  const long long off = (1LL * t * p.B + tok) * p.d + e0;
+  if (p.mode == 0) {
+    float4* dst = reinterpret_cast<float4*>(p.yhat_partial + off);
+    dst[0] = make_float4(a[0], a[1], a[2], a[3]);
+    dst[1] = make_float4(a[4], a[5], a[6], a[7]);
+  } else if (p.mode == 2) {
+    // reduce-scatter by push: peer store into the owner's slot for this rank (NVLink posted writes)
+    const int owner = tok / p.rows_per_rank;
+    const int lrow = tok - owner * p.rows_per_rank;
+    float4* dst = reinterpret_cast<float4*>(p.stage_peers[owner] + ((1LL * p.rank * p.L + t) * p.rows_per_rank + lrow) * p.d + e0);
+    dst[0] = make_float4(a[0], a[1], a[2], a[3]);
+    dst[1] = make_float4(a[4], a[5], a[6], a[7]);
+  } else {
+    float y[8], out[8];
+    const uint4 tv = *reinterpret_cast<const uint4*>(p.target + off);
+    const uint32_t u[4] = {tv.x, tv.y, tv.z, tv.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { y[2 * i] = bf16_lo(u[i]); y[2 * i + 1] = bf16_hi(u[i]); }
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float v = a[i] + p.bias_sum[1LL * t * p.d + e0 + i];
+      if (p.addend) v += p.addend[off + i];
+      const float sg = p.sigma ? p.sigma[1LL * t * p.d + e0 + i] : 1.f;
+      out[i] = v;
+      const float r = (v - y[i]) * sg;
+      sq = fmaf(r, r, sq);
+      y[i] = r * sg;  // gradient seed
+    }
+    uint4 gv;
+    gv.x = pack_bf16x2(y[0], y[1]); gv.y = pack_bf16x2(y[2], y[3]);
+    gv.z = pack_bf16x2(y[4], y[5]); gv.w = pack_bf16x2(y[6], y[7]);
+    *reinterpret_cast<uint4*>(p.gs + off) = gv;
+    if (p.yhat_out) {
+      float4* dst = reinterpret_cast<float4*>(p.yhat_out + off);
+      dst[0] = make_float4(out[0], out[1], out[2], out[3]);
+      dst[1] = make_float4(out[4], out[5], out[6], out[7]);
+    }
+    atomicAdd(&sq_s[t], sq);
+  }
+}
+
 constexpr int kGroups = 4;  // warp groups per token; group g owns targets t with t % kGroups == g
 
 // One CTA per token.  The CTA is split into kGroups warp groups of `gthreads` threads; every group walks
@@ -128,51 +173,123 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
   for (int j = 0; j < TPG; ++j) {
     const int t = g + (blockIdx.y * TPG + j) * kGroups;
     if (t >= p.L || !active) continue;
-    const long long off = (1LL * t * p.B + tok) * p.d + e0;
-    if (p.mode == 0) {
-      float4* dst = reinterpret_cast<float4*>(p.yhat_partial + off);
-      dst[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-      dst[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
-    } else if (p.mode == 2) {
-      // reduce-scatter by push: peer store into the owner's slot for this rank (NVLink posted writes)
-      const int owner = tok / p.rows_per_rank;
-      const int lrow = tok - owner * p.rows_per_rank;
-      float4* dst = reinterpret_cast<float4*>(p.stage_peers[owner] + ((1LL * p.rank * p.L + t) * p.rows_per_rank + lrow) * p.d + e0);
-      dst[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-      dst[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
-    } else {
-      float y[8], out[8];
-      const uint4 tv = *reinterpret_cast<const uint4*>(p.target + off);
-      const uint32_t u[4] = {tv.x, tv.y, tv.z, tv.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) { y[2 * i] = bf16_lo(u[i]); y[2 * i + 1] = bf16_hi(u[i]); }
-      float sq = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float v = acc[j][i] + p.bias_sum[1LL * t * p.d + e0 + i];
-        if (p.addend) v += p.addend[off + i];
-        const float sg = p.sigma ? p.sigma[1LL * t * p.d + e0 + i] : 1.f;
-        out[i] = v;
-        const float r = (v - y[i]) * sg;
-        sq = fmaf(r, r, sq);
-        y[i] = r * sg;  // gradient seed
-      }
-      uint4 gv;
-      gv.x = pack_bf16x2(y[0], y[1]); gv.y = pack_bf16x2(y[2], y[3]);
-      gv.z = pack_bf16x2(y[4], y[5]); gv.w = pack_bf16x2(y[6], y[7]);
-      *reinterpret_cast<uint4*>(p.gs + off) = gv;
-      if (p.yhat_out) {
-        float4* dst = reinterpret_cast<float4*>(p.yhat_out + off);
-        dst[0] = make_float4(out[0], out[1], out[2], out[3]);
-        dst[1] = make_float4(out[4], out[5], out[6], out[7]);
-      }
-      atomicAdd(&sq_s[t], sq);
-    }
+    decode_epilogue(p, tok, t, e0, acc[j], sq_s);
   }
   if (p.mode == 1) {
     __syncthreads();
     if (threadIdx.x < p.L && sq_s[threadIdx.x] != 0.f) atomicAdd(&p.sq_err[threadIdx.x], double(sq_s[threadIdx.x]));
   }
+}
+
+// Untied decoders, the flagship path: the rows of one active feature for all its targets are one contiguous
+// block of (L - s) * d bf16.  A producer warp streams these blocks into a shared-memory ring with 1-D bulk
+// copies (cp.async.bulk + mbarrier, no multicast); the four consumer groups take their targets' rows from
+// shared memory.  Large contiguous reads and a ring that is always full keep HBM busy, where the per-row
+// register loads of decode_kernel wait on a dependent load chain.  Every mbarrier wait is bounded.
+constexpr int kDecodeStages = 4;
+
+struct DecodeBulkShared {
+  uint64_t full[kDecodeStages];
+  uint64_t empty[kDecodeStages];
+  float sq_s[kMaxLayers];
+  const __nv_bfloat16* w_s[kMaxLayers];
+  int rows_s[kMaxLayers];
+  int abort_flag;
+};
+
+template <int TPG>
+__global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, int gthreads, int stage_bytes, int* status) {
+  extern __shared__ uint8_t smem_raw_dec[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_dec) + 127) & ~uintptr_t(127));
+  DecodeBulkShared* sh = reinterpret_cast<DecodeBulkShared*>(ring + size_t(kDecodeStages) * stage_bytes);
+  const int tok = blockIdx.x;
+  const int nconsumer = kGroups * gthreads;
+  const bool is_producer = int(threadIdx.x) >= nconsumer;
+  const int L = p.L, d = p.d;
+  if (threadIdx.x < kMaxLayers) {
+    sh->sq_s[threadIdx.x] = 0.f;
+    sh->w_s[threadIdx.x] = p.w[threadIdx.x];
+    sh->rows_s[threadIdx.x] = p.rows[threadIdx.x];
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDecodeStages; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], nconsumer / 32);
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  volatile int* abort_flag = &sh->abort_flag;
+  const int b = p.tok_off[tok], e = p.tok_off[tok + 1];
+
+  if (is_producer) {
+    if (threadIdx.x == nconsumer) {
+      int issued = 0;
+      for (int i = b; i < e; ++i, ++issued) {
+        const int st = issued % kDecodeStages;
+        const uint32_t ph = (issued / kDecodeStages) & 1;
+        if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) break;
+        const int col = __ldg(p.tcsr_col + i);
+        const int sl = col >> 24, f = col & 0xFFFFFF;
+        const int R = sh->rows_s[sl];
+        const uint32_t bytes = uint32_t(R) * uint32_t(d) * 2u;
+        mbar_expect_tx(&sh->full[st], bytes);
+        bulk_load_1d(ring + size_t(st) * stage_bytes, sh->w_s[sl] + 1LL * f * R * d, bytes, &sh->full[st]);
+      }
+      if (*abort_flag) {
+        // give copies already issued a bounded chance to land before the CTA retires
+        const int first = issued > kDecodeStages ? issued - kDecodeStages : 0;
+        for (int j = first; j < issued; ++j) {
+          const long long start = clock64();
+          while (!mbar_try_wait(&sh->full[j % kDecodeStages], (j / kDecodeStages) & 1))
+            if (clock64() - start > kWaitTimeoutCycles) break;
+        }
+      }
+    }
+  } else {
+    const int g = threadIdx.x / gthreads;
+    const int gt = threadIdx.x - g * gthreads;
+    const int e0 = gt * 8;
+    const bool active = e0 < d;
+    const int lane = threadIdx.x & 31;
+    float acc[TPG][8];
+#pragma unroll
+    for (int j = 0; j < TPG; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+    int it = 0;
+    bool ok = true;
+    for (int i = b; i < e; ++i, ++it) {
+      const int st = it % kDecodeStages;
+      const uint32_t ph = (it / kDecodeStages) & 1;
+      if (!mbar_wait(&sh->full[st], ph, abort_flag)) { ok = false; break; }
+      const int col = __ldg(p.tcsr_col + i);
+      const float a = __ldg(p.tcsr_val + i);
+      const int sl = col >> 24;
+      if (active && a != 0.f) {
+        const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(ring + size_t(st) * stage_bytes) + e0;
+#pragma unroll
+        for (int j = 0; j < TPG; ++j) {
+          const int t = g + (blockIdx.y * TPG + j) * kGroups;
+          if (t < L && t >= sl) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (t - sl) * d));
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->empty[st]);  // this warp is done with the stage
+    }
+    if (ok) {
+#pragma unroll
+      for (int j = 0; j < TPG; ++j) {
+        const int t = g + (blockIdx.y * TPG + j) * kGroups;
+        if (t >= L || !active) continue;
+        decode_epilogue(p, tok, t, e0, acc[j], sh->sq_s);
+      }
+    }
+  }
+  __syncthreads();
+  if (p.mode == 1 && threadIdx.x < L && sh->sq_s[threadIdx.x] != 0.f) atomicAdd(&p.sq_err[threadIdx.x], double(sh->sq_s[threadIdx.x]));
+  if (threadIdx.x == 0 && sh->abort_flag && status != nullptr) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
 }
 
 // Epilogue for the tensor-parallel path, run after the partial reconstructions were summed across ranks:
@@ -253,6 +370,7 @@ struct CltDecodeArgs {
   void* stage_peers[8];
   int rows_per_rank, rank, world;
   int mode;
+  int* status;  // when given, untied decoders use the bulk-copy pipeline (its bounded waits report here)
 };
 
 extern "C" int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st) {
@@ -271,7 +389,28 @@ extern "C" int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st) {
   const int threads = gthreads * kGroups;
   if (threads > 1024) return -1;
   const int tpg = (a->L + kGroups - 1) / kGroups;  // targets per warp group
-  if (tpg <= 1) decode_kernel<1><<<dim3(a->B, 1), threads, 0, st>>>(p, gthreads);
+  int max_rows = 0;
+  for (int i = 0; i < a->L; ++i) max_rows = a->rows[i] > max_rows ? a->rows[i] : max_rows;
+  const int stage_bytes = ((max_rows * a->d * 2 + 127) / 128) * 128;
+  const size_t smem = size_t(kDecodeStages) * stage_bytes + sizeof(DecodeBulkShared) + 256;
+  const bool bulk = a->tying == 0 && a->status != nullptr && tpg <= 4 && smem <= 200 * 1024 && threads + 32 <= 544;
+  if (bulk) {
+    static size_t attr_set[5] = {0, 0, 0, 0, 0};
+    auto launch = [&](auto kern) -> int {
+      if (attr_set[tpg] < smem) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
+        attr_set[tpg] = smem;
+      }
+      kern<<<dim3(a->B, 1), threads + 32, smem, st>>>(p, gthreads, stage_bytes, a->status);
+      return 0;
+    };
+    int rc = 0;
+    if (tpg <= 1) rc = launch(decode_bulk_kernel<1>);
+    else if (tpg == 2) rc = launch(decode_bulk_kernel<2>);
+    else if (tpg == 3) rc = launch(decode_bulk_kernel<3>);
+    else rc = launch(decode_bulk_kernel<4>);
+    if (rc != 0) return rc;
+  } else if (tpg <= 1) decode_kernel<1><<<dim3(a->B, 1), threads, 0, st>>>(p, gthreads);
   else if (tpg == 2) decode_kernel<2><<<dim3(a->B, 1), threads, 0, st>>>(p, gthreads);
   else if (tpg == 3) decode_kernel<3><<<dim3(a->B, 1), threads, 0, st>>>(p, gthreads);
   else decode_kernel<4><<<dim3(a->B, (tpg + 3) / 4), threads, 0, st>>>(p, gthreads);  // 16 targets per pass

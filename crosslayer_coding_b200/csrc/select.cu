@@ -220,62 +220,104 @@ __global__ void __launch_bounds__(256) zhist_kernel(const __nv_bfloat16* __restr
   }
 }
 
-// ------------------------------------------------------------------ 3. threshold bin (one CTA, 1024 threads)
-// pass 0: narrow histogram; when it does not contain the cut it only raises CTL_RETRY.
-// pass 1: full-range histogram, runs only on retry; a miss there is a real error.
-__global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __restrict__ hist, long long k_total,
-                                                          long long* __restrict__ ctl, Exchange ex, uint32_t key_lo, int shift,
-                                                          int pass, int exchange_round, int* __restrict__ status) {
-  __shared__ uint32_t vals[kHistBins];
-  __shared__ unsigned long long part[1024];
-  __shared__ int timeout;
-  __shared__ int found;
-  const int tid = threadIdx.x;
-  if (pass == 1 && ctl[CTL_RETRY] == 0) return;
-  if (tid == 0) { timeout = 0; found = 0; }
-  for (int i = tid; i < kHistBins; i += 1024) vals[i] = hist[i];
+// ------------------------------------------------------------------ 2b. histogram + pool in one pass
+// The range of the narrow histogram lives in device memory (`sel_state`: key_lo, shift) and follows the
+// cut from step to step (find_bin_kernel moves it).  Every element inside the range is also appended to a
+// pool (key, token, column, value), so that the later stages read a list of a few k_total elements instead
+// of the whole pre-activation matrix a second time.
+struct Pool {
+  uint32_t* key;
+  int* tok;
+  int* col;
+  float* val;
+  long long cap;
+  unsigned int* count;  // zeroed by the caller together with the histograms
+};
+constexpr int kPoolStage = 768;  // histogram + staging stay inside the 48 KB of static shared memory
+constexpr int kHistExtra = 32;  // words after the two histograms: [0] = pool counter
+
+__global__ void __launch_bounds__(256) zhist_collect_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+                                                              const float* __restrict__ rstd, ScanGeom g, int col_pitch,
+                                                              const long long* __restrict__ sel_state,
+                                                              unsigned int* __restrict__ hist, Pool pool) {
+  const uint32_t key_lo = uint32_t(sel_state[0]);
+  const int shift = int(sel_state[1]);
+  const float z_lo = key_to_float(key_lo);
+  __shared__ unsigned int sh[kHistBins];
+  __shared__ uint32_t s_key[kPoolStage];
+  __shared__ int s_tok[kPoolStage];
+  __shared__ int s_col[kPoolStage];
+  __shared__ float s_val[kPoolStage];
+  __shared__ int s_n;
+  __shared__ unsigned int s_base;
+  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) sh[i] = 0;
+  if (threadIdx.x == 0) s_n = 0;
   __syncthreads();
-  if (!exchange_sum(ex, exchange_round, vals, kHistBins, &timeout)) {
-    if (tid == 0) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
-    return;
+  const int l = blockIdx.z;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c0 < g.F) {
+    float mu[8], rs[8];
+    if (c0 + 8 <= g.F) {
+      load_cols8(mean + 1LL * l * g.sp + c0, mu);
+      load_cols8(rstd + 1LL * l * g.sp + c0, rs);
+    } else {
+      for (int j = 0; j < 8; ++j) {
+        const bool in = c0 + j < g.F;
+        mu[j] = in ? mean[1LL * l * g.sp + c0 + j] : 0.f;
+        rs[j] = in ? rstd[1LL * l * g.sp + c0 + j] : 0.f;
+      }
+    }
+    const int nvalid = min(8, g.F - c0);
+    const int r0 = blockIdx.y * g.rows_per_block;
+    const int r1 = min(g.B, r0 + g.rows_per_block);
+    const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+    for (int rb = r0; rb < r1; rb += 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int r = min(rb + k, r1 - 1);
+        v[k] = __ldcs(reinterpret_cast<const uint4*>(base + 1LL * r * g.ld));
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int r = rb + k;
+        const uint32_t u[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+          const float z = (xv - mu[j]) * rs[j];
+          if (!(z >= z_lo) || j >= nvalid || r >= r1) continue;
+          const uint32_t key = float_to_key(z);
+          atomicAdd(&sh[min((key - key_lo) >> shift, uint32_t(kHistBins - 1))], 1u);
+          const int slot = atomicAdd(&s_n, 1);
+          if (slot < kPoolStage) {
+            s_key[slot] = key; s_tok[slot] = r; s_col[slot] = l * col_pitch + c0 + j; s_val[slot] = xv;
+          } else {  // staging full: append directly
+            const unsigned int q = atomicAdd(pool.count, 1u);
+            if ((long long)q < pool.cap) { pool.key[q] = key; pool.tok[q] = r; pool.col[q] = l * col_pitch + c0 + j; pool.val[q] = xv; }
+          }
+        }
+      }
+    }
   }
-  // thread t owns bins [8t, 8t+8); suffix sums from the top
-  unsigned long long mine = 0;
-  for (int j = 0; j < 8; ++j) mine += vals[tid * 8 + j];
-  part[tid] = mine;
   __syncthreads();
-  if (tid == 0) {
-    unsigned long long run = 0;
-    for (int t = 1023; t >= 0; --t) { const unsigned long long c = part[t]; part[t] = run; run += c; }
-    found = run >= (unsigned long long)k_total ? 1 : 0;
-    if (!found) {
-      if (pass == 0) ctl[CTL_RETRY] = 1;
-      else atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
-    } else if (pass == 0) {
-      ctl[CTL_RETRY] = 0;
-    }
-    if (pass == 0 || found) {
-      ctl[CTL_NUM_ENTRIES] = 0;
-      ctl[CTL_NUM_CAND] = 0;
-    }
+  for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) {
+    const unsigned int c = sh[i];
+    if (c) atomicAdd(&hist[i], c);
   }
+  const int staged = min(s_n, kPoolStage);
+  if (staged == 0) return;
+  if (threadIdx.x == 0) s_base = atomicAdd(pool.count, (unsigned int)staged);
   __syncthreads();
-  if (!found) return;
-  unsigned long long above = part[tid];  // keys in bins above this thread's group
-  for (int j = 7; j >= 0; --j) {
-    const unsigned long long c = vals[tid * 8 + j];
-    if (above < (unsigned long long)k_total && above + c >= (unsigned long long)k_total) {
-      ctl[CTL_BIN] = tid * 8 + j;
-      ctl[CTL_ABOVE] = (long long)above;
-      ctl[CTL_NEED] = k_total - (long long)above;
-      ctl[CTL_KEY_LO] = (long long)key_lo;
-      ctl[CTL_SHIFT] = shift;
-    }
-    above += c;
+  for (int i = threadIdx.x; i < staged; i += blockDim.x) {
+    const long long q = (long long)s_base + i;
+    if (q < pool.cap) { pool.key[q] = s_key[i]; pool.tok[q] = s_tok[i]; pool.col[q] = s_col[i]; pool.val[q] = s_val[i]; }
   }
 }
 
-// ------------------------------------------------------------------ 4. compaction
+// ------------------------------------------------------------------ 3. threshold bin (one CTA, 1024 threads)
+// pass 0: narrow histogram; when it does not contain the cut it only raises CTL_RETRY.
+// pass 1: full-range histogram, runs only on retry; a miss there is a real error.
 struct Lists {
   int* ent_tok;    // token index
   int* ent_col;    // l * F_local_pitch + f_local
@@ -288,13 +330,160 @@ struct Lists {
   long long cand_cap;
 };
 
+// `sel_state` (optional): the tracked range.  Pass 0 reads the range from it; the pass that finds the cut
+// moves the range for the next step so that about kPoolFactor * k_total elements fall inside it.
+constexpr double kPoolFactor = 1.75;
+
+__device__ __forceinline__ int shift_for(uint32_t key_lo) {
+  int sh = 0;
+  while (((0xFFFFFFFFu - key_lo) >> sh) >= uint32_t(kHistBins)) ++sh;
+  return sh;
+}
+
+__global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __restrict__ hist, long long k_total,
+                                                          long long* __restrict__ ctl, Exchange ex, uint32_t key_lo_arg,
+                                                          int shift_arg, int pass, int exchange_round,
+                                                          long long* __restrict__ sel_state,
+                                                          const unsigned int* __restrict__ pool_count, long long pool_cap,
+                                                          int* __restrict__ status) {
+  __shared__ uint32_t vals[kHistBins + kHistExtra];
+  __shared__ unsigned long long part[1024];
+  __shared__ int timeout;
+  __shared__ int found;
+  const int tid = threadIdx.x;
+  if (pass == 1 && ctl[CTL_RETRY] == 0) return;
+  const bool tracked = sel_state != nullptr;
+  const uint32_t key_lo = (pass == 0 && tracked) ? uint32_t(sel_state[0]) : key_lo_arg;
+  const int shift = (pass == 0 && tracked) ? int(sel_state[1]) : shift_arg;
+  if (tid == 0) { timeout = 0; found = 0; }
+  for (int i = tid; i < kHistBins; i += 1024) vals[i] = hist[i];
+  if (tid < kHistExtra) vals[kHistBins + tid] = 0;
+  __syncthreads();
+  // a rank whose pool overflowed makes every rank take the full-range path
+  if (tid == 0 && pass == 0 && pool_count != nullptr && (long long)(*pool_count) > pool_cap) vals[kHistBins] = 1;
+  __syncthreads();
+  if (!exchange_sum(ex, exchange_round, vals, kHistBins + 1, &timeout)) {
+    if (tid == 0) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+    return;
+  }
+  const bool overflow = vals[kHistBins] != 0;
+  // thread t owns bins [8t, 8t+8); suffix sums from the top
+  unsigned long long mine = 0;
+  for (int j = 0; j < 8; ++j) mine += vals[tid * 8 + j];
+  part[tid] = mine;
+  __syncthreads();
+  unsigned long long total = 0;
+  if (tid == 0) {
+    unsigned long long run = 0;
+    for (int t = 1023; t >= 0; --t) { const unsigned long long c = part[t]; part[t] = run; run += c; }
+    total = run;
+    const bool in_range = run >= (unsigned long long)k_total;
+    found = (in_range && !overflow) ? 1 : 0;
+    if (!found) {
+      if (pass == 0) ctl[CTL_RETRY] = 1;
+      else atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
+    } else if (pass == 0) {
+      ctl[CTL_RETRY] = 0;
+    }
+    if (pass == 0 || found) {
+      ctl[CTL_NUM_ENTRIES] = 0;
+      ctl[CTL_NUM_CAND] = 0;
+    }
+    if (tracked && pass == 0 && !in_range) {
+      // the range starts above the cut: lower it (the full-range pass of this step refines the guess)
+      const float z = fmaxf(key_to_float(key_lo) - 0.1f, 0.f);
+      const uint32_t nk = float_to_key(z);
+      sel_state[0] = (long long)nk;
+      sel_state[1] = shift_for(nk);
+    }
+  }
+  __syncthreads();
+  const unsigned long long target = (unsigned long long)(kPoolFactor * double(k_total));
+  unsigned long long above = part[tid];  // keys in bins above this thread's group
+  for (int j = 7; j >= 0; --j) {
+    const unsigned long long c = vals[tid * 8 + j];
+    if (found && above < (unsigned long long)k_total && above + c >= (unsigned long long)k_total) {
+      ctl[CTL_BIN] = tid * 8 + j;
+      ctl[CTL_ABOVE] = (long long)above;
+      ctl[CTL_NEED] = k_total - (long long)above;
+      ctl[CTL_KEY_LO] = (long long)key_lo;
+      ctl[CTL_SHIFT] = shift;
+    }
+    if (tracked && above < target && above + c >= target) {
+      // next step's range starts at the bin that holds the target-th largest key (never below z = 0)
+      const unsigned long long nk64 = (unsigned long long)key_lo + ((unsigned long long)(tid * 8 + j) << shift);
+      uint32_t nk = nk64 > 0xFFFFFFFFULL ? 0xFFFFFFFFu : uint32_t(nk64);
+      if (nk < 0x80000000u) nk = 0x80000000u;
+      sel_state[0] = (long long)nk;
+      sel_state[1] = shift_for(nk);
+    }
+    above += c;
+  }
+  if (tracked && tid == 0 && found && total < target) {
+    // fewer elements in range than wanted: widen a little for the next step
+    const float z = fmaxf(key_to_float(key_lo) - 0.1f, 0.f);
+    const uint32_t nk = float_to_key(z);
+    sel_state[0] = (long long)nk;
+    sel_state[1] = shift_for(nk);
+  }
+}
+
+// ------------------------------------------------------------------ 3b. split the pool at the threshold bin
+// Runs instead of the full compaction pass when the tracked range contained the cut.
+__global__ void __launch_bounds__(256) classify_pool_kernel(Pool pool, long long* __restrict__ ctl, Lists o,
+                                                              int* __restrict__ status) {
+  if (ctl[CTL_RETRY] != 0) return;
+  const uint32_t tbin = uint32_t(ctl[CTL_BIN]);
+  const uint32_t key_lo = uint32_t(ctl[CTL_KEY_LO]);
+  const int shift = int(ctl[CTL_SHIFT]);
+  unsigned long long* n_ent = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_ENTRIES);
+  unsigned long long* n_cand = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_CAND);
+  const long long n = min((long long)(*pool.count), pool.cap);
+  const int lane = threadIdx.x & 31;
+  const long long stride = 1LL * gridDim.x * blockDim.x;
+  const long long n_round = ((n + 31) / 32) * 32;  // whole warps stay together for the ballots
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n_round; i += stride) {
+    int kind = 0;  // 1: entry, 2: candidate
+    uint32_t key = 0;
+    if (i < n) {
+      key = pool.key[i];
+      const uint32_t bin = min((key - key_lo) >> shift, uint32_t(kHistBins - 1));
+      kind = bin > tbin ? 1 : (bin == tbin ? 2 : 0);
+    }
+    // one reservation per warp and list
+    const unsigned m_ent = __ballot_sync(0xFFFFFFFFu, kind == 1);
+    const unsigned m_cand = __ballot_sync(0xFFFFFFFFu, kind == 2);
+    unsigned long long base_ent = 0, base_cand = 0;
+    if (lane == 0) {
+      if (m_ent) base_ent = atomicAdd(n_ent, (unsigned long long)__popc(m_ent));
+      if (m_cand) base_cand = atomicAdd(n_cand, (unsigned long long)__popc(m_cand));
+    }
+    base_ent = __shfl_sync(0xFFFFFFFFu, base_ent, 0);
+    base_cand = __shfl_sync(0xFFFFFFFFu, base_cand, 0);
+    const unsigned below = (1u << lane) - 1u;
+    if (kind == 1) {
+      const long long q = (long long)base_ent + __popc(m_ent & below);
+      if (q < o.ent_cap) { o.ent_tok[q] = pool.tok[i]; o.ent_col[q] = pool.col[i]; o.ent_val[q] = pool.val[i]; }
+      else atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+    } else if (kind == 2) {
+      const long long q = (long long)base_cand + __popc(m_cand & below);
+      if (q < o.cand_cap) { o.cand_key[q] = key; o.cand_tok[q] = pool.tok[i]; o.cand_col[q] = pool.col[i]; o.cand_val[q] = pool.val[i]; }
+      else atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ 4. compaction
+
 // Selected elements are staged in shared memory and appended with one global reservation per CTA and
 // list: a single counter cannot absorb one atomic per selected element (hundreds of thousands per step).
 constexpr int kStageCap = 1024;
 
 __global__ void __launch_bounds__(256) compact_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
                                                         const float* __restrict__ rstd, ScanGeom g, int col_pitch,
-                                                        long long* __restrict__ ctl, Lists o, int* __restrict__ status) {
+                                                        long long* __restrict__ ctl, Lists o, int* __restrict__ status,
+                                                        int only_if_retry) {
+  if (only_if_retry && ctl[CTL_RETRY] == 0) return;
   __shared__ int s_tok[kStageCap];
   __shared__ int s_col[kStageCap];
   __shared__ float s_val[kStageCap];
@@ -603,6 +792,77 @@ __global__ void __launch_bounds__(1024) exclusive_scan_kernel(const int* __restr
   if (tid == 0) out[n] = carry_s;
 }
 
+// Multi-CTA variant without scratch memory: CTA t owns elements [4096 t, 4096 (t + 1)).  It first adds up
+// everything in front of its tile (the counts are small and stay in L2, so the repeated reads are cheaper
+// than a second launch or a look-back protocol), then scans its own tile.
+__global__ void __launch_bounds__(1024) exclusive_scan_tiles_kernel(const int* __restrict__ in, int* __restrict__ out,
+                                                                      int* __restrict__ cursor, int n) {
+  __shared__ int warp_tot[32];
+  __shared__ int carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int base = blockIdx.x * 4096;
+  int front = 0;
+  {
+    const int4* in4 = reinterpret_cast<const int4*>(in);  // base is a multiple of 4
+    for (int i = tid; i < base / 4; i += 1024) {
+      const int4 q = __ldg(in4 + i);
+      front += q.x + q.y + q.z + q.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) front += __shfl_xor_sync(0xFFFFFFFFu, front, o);
+    if (lane == 0) warp_tot[warp] = front;
+    __syncthreads();
+    if (tid == 0) {
+      int c = 0;
+      for (int w = 0; w < 32; ++w) c += warp_tot[w];
+      carry_s = c;
+    }
+    __syncthreads();
+  }
+  const int carry = carry_s;
+  __syncthreads();
+  const int i0 = base + tid * 4;
+  int v[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) v[k] = (i0 + k < n) ? in[i0 + k] : 0;
+  const int mine = v[0] + v[1] + v[2] + v[3];
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_tot[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xFFFFFFFFu, w, o);
+      if (lane >= o) w += t;
+    }
+    warp_tot[lane] = w;
+  }
+  __syncthreads();
+  int run = carry + (warp > 0 ? warp_tot[warp - 1] : 0) + incl - mine;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (i0 + k < n) {
+      out[i0 + k] = run;
+      if (cursor != nullptr) cursor[i0 + k] = run;
+    }
+    run += v[k];
+  }
+  if (blockIdx.x == gridDim.x - 1 && tid == 1023) out[n] = carry + warp_tot[31];
+}
+
+static void launch_exclusive_scan(const int* in, int* out, int* cursor, int n, cudaStream_t st) {
+  const int ntiles = (n + 4095) / 4096;
+  const bool aligned = (reinterpret_cast<uintptr_t>(in) & 15) == 0;
+  if (ntiles >= 2 && ntiles <= 512 && aligned) exclusive_scan_tiles_kernel<<<ntiles, 1024, 0, st>>>(in, out, cursor, n);
+  else exclusive_scan_kernel<<<1, 1024, 0, st>>>(in, out, cursor, n);
+}
+
 __global__ void __launch_bounds__(256) csr_scatter_kernel(const int* __restrict__ ent_tok, const int* __restrict__ ent_col,
                                                             const float* __restrict__ ent_val, long long cap,
                                                             const long long* __restrict__ ctl, int* __restrict__ tok_cursor,
@@ -694,11 +954,15 @@ struct CltSelectArgs {
   long long k_total;   // global number of entries to keep
   unsigned int key_lo; // histogram covers keys >= key_lo
   int shift;           // bin = (key - key_lo) >> shift
-  unsigned int* hist;  // [2 * 8192], zeroed by the caller
+  unsigned int* hist;  // [2 * 8192 + 32], zeroed by the caller
   long long* ctl;      // [CTL_SIZE]
   int* ent_tok; int* ent_col; float* ent_val; long long ent_cap;
   unsigned int* cand_key; int* cand_tok; int* cand_col; float* cand_val; long long cand_cap;
   int* status;
+  // Optional tracked range: sel_state = {key_lo, shift} in device memory, moved by the kernels every step,
+  // and the pool that the single pass over the matrix fills.  Null sel_state: fixed range from key_lo / shift.
+  long long* sel_state;
+  unsigned int* pool_key; int* pool_tok; int* pool_col; float* pool_val; long long pool_cap;
 };
 
 static ScanGeom scan_geom(const CltSelectArgs* a) {
@@ -728,13 +992,26 @@ extern "C" int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArg
   const Exchange ex = to_exchange(exa);
   dim3 grid(((a->F + 7) / 8 + 255) / 256, (a->B + g.rows_per_block - 1) / g.rows_per_block, a->L);
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(a->x);
-  zhist_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->key_lo, a->shift, a->hist, a->ctl, 0);
-  find_bin_kernel<<<1, 1024, 0, st>>>(a->hist, a->k_total, a->ctl, ex, a->key_lo, a->shift, 0, 0, a->status);
-  if (a->key_lo != 0) {
+  if (a->sel_state != nullptr && a->key_lo != 0) {
+    Pool pool;
+    pool.key = a->pool_key; pool.tok = a->pool_tok; pool.col = a->pool_col; pool.val = a->pool_val; pool.cap = a->pool_cap;
+    pool.count = a->hist + 2 * kHistBins;
+    zhist_collect_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->col_pitch, a->sel_state, a->hist, pool);
+    find_bin_kernel<<<1, 1024, 0, st>>>(a->hist, a->k_total, a->ctl, ex, 0u, 0, 0, 0, a->sel_state, pool.count, pool.cap, a->status);
+    classify_pool_kernel<<<148, 256, 0, st>>>(pool, a->ctl, lists_of(a), a->status);
+    // fallback, skipped inside the kernels unless the tracked range missed the cut or the pool overflowed
     zhist_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, 0u, 19, a->hist + kHistBins, a->ctl, 1);
-    find_bin_kernel<<<1, 1024, 0, st>>>(a->hist + kHistBins, a->k_total, a->ctl, ex, 0u, 19, 1, 1, a->status);
+    find_bin_kernel<<<1, 1024, 0, st>>>(a->hist + kHistBins, a->k_total, a->ctl, ex, 0u, 19, 1, 1, a->sel_state, nullptr, 0, a->status);
+    compact_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->col_pitch, a->ctl, lists_of(a), a->status, 1);
+  } else {
+    zhist_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->key_lo, a->shift, a->hist, a->ctl, 0);
+    find_bin_kernel<<<1, 1024, 0, st>>>(a->hist, a->k_total, a->ctl, ex, a->key_lo, a->shift, 0, 0, nullptr, nullptr, 0, a->status);
+    if (a->key_lo != 0) {
+      zhist_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, 0u, 19, a->hist + kHistBins, a->ctl, 1);
+      find_bin_kernel<<<1, 1024, 0, st>>>(a->hist + kHistBins, a->k_total, a->ctl, ex, 0u, 19, 1, 1, nullptr, nullptr, 0, a->status);
+    }
+    compact_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->col_pitch, a->ctl, lists_of(a), a->status, 0);
   }
-  compact_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->col_pitch, a->ctl, lists_of(a), a->status);
   refine_kernel<<<1, 1024, 0, st>>>(a->cand_key, a->cand_tok, a->cand_col, a->cand_cap, flat_geom(a), a->ctl, ex, a->status);
   finalize_kernel<<<256, 256, 0, st>>>(lists_of(a), flat_geom(a), a->ctl, a->status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
@@ -756,8 +1033,8 @@ struct CltCsrArgs {
 extern "C" int clt_build_csr(const CltCsrArgs* a, cudaStream_t st) {
   const int blocks = 592;
   csr_count_kernel<<<blocks, 256, 0, st>>>(a->ent_tok, a->ent_col, a->ent_val, a->ent_cap, a->ctl, a->tok_cnt, a->feat_cnt, a->fired);
-  exclusive_scan_kernel<<<1, 1024, 0, st>>>(a->tok_cnt, a->tok_off, a->tok_cursor, a->num_tokens);
-  exclusive_scan_kernel<<<1, 1024, 0, st>>>(a->feat_cnt, a->feat_off, a->feat_cursor, a->num_cols);
+  launch_exclusive_scan(a->tok_cnt, a->tok_off, a->tok_cursor, a->num_tokens, st);
+  launch_exclusive_scan(a->feat_cnt, a->feat_off, a->feat_cursor, a->num_cols, st);
   csr_scatter_kernel<<<blocks, 256, 0, st>>>(a->ent_tok, a->ent_col, a->ent_val, a->ent_cap, a->ctl, a->tok_cursor, a->feat_cursor,
                                              a->tcsr_col, a->tcsr_val, a->fcsr_tok, a->fcsr_val, a->col_pitch);
   if (a->sort_segments & 1)

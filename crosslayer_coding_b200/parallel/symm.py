@@ -22,6 +22,7 @@ import torch.distributed as dist
 
 HIST_ROUNDS = 16
 HIST_BINS = 8192
+HIST_SLOT = HIST_BINS + 32  # a slot also carries the pool-overflow word of the selection
 BARRIER_SLOTS = 4
 
 
@@ -40,7 +41,7 @@ class SymmetricExchange:
         def align(n: int) -> int:
             return (n + 255) // 256 * 256
 
-        self.hist_bytes = align(HIST_ROUNDS * W * HIST_BINS * 4)
+        self.hist_bytes = align(HIST_ROUNDS * W * HIST_SLOT * 4)
         self.hflag_bytes = align(HIST_ROUNDS * W * 4)
         self.bflag_bytes = align(BARRIER_SLOTS * W * 4)
         self.stage_bytes = align(W * num_layers * self.rows_per_rank * d_model * 4)
@@ -59,7 +60,7 @@ class SymmetricExchange:
         self.barrier_flag_ptrs = [b + o_bflag for b in base]
         self.stage_ptrs = [b + o_stage for b in base]
         self.gs_ptrs = [b + o_gs for b in base]
-        self.slot_elems = HIST_BINS
+        self.slot_elems = HIST_SLOT
         self.stage = self.buffer[o_stage : o_stage + W * num_layers * self.rows_per_rank * d_model * 4].view(torch.float32)
         self.gs = self.buffer[o_gs : o_gs + num_layers * batch_tokens * d_model * 2].view(torch.bfloat16).view(num_layers, batch_tokens, d_model)
         self.barrier_seq = 0

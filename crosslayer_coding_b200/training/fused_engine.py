@@ -39,18 +39,19 @@ from ..parallel import ops as pops
 STATUS_NAMES = {0: "ok", 1: "wait timeout", 2: "list capacity exceeded", 3: "threshold outside histogram range", 4: "tie overflow"}
 
 
-def histogram_range(k_total: int, numel: int):
-    """``(key_lo, shift)`` of the selection histogram.  The z-scores are standardised per feature, so the
-    cut is guessed from the normal quantile of ``k_total / numel`` and the 8192 bins cover keys from one
-    standard deviation below that guess upwards (finer bins, fewer candidates, almost no histogram
-    traffic).  When the guess is wrong the kernels repeat the pass over the full key range themselves."""
+def histogram_range(k_total: int, numel: int, pool_factor: float = 1.75):
+    """First guess ``(key_lo, shift)`` of the selection histogram.  The z-scores are standardised per
+    feature, so the range starts at the normal quantile below which all but ``pool_factor * k_total``
+    elements fall; the 8192 bins cover the keys from there upwards.  The kernels keep the range in device
+    memory and move it every step so that it follows the measured cut; when a step's range misses the cut
+    (or holds more elements than the pool takes) the kernels repeat that step's pass over the full key
+    range themselves."""
     import struct
 
-    p = k_total / max(1, numel)
+    p = pool_factor * k_total / max(1, numel)
     if p >= 0.25 or k_total <= 0:
         return 0, 19
-    z_p = math.sqrt(2.0) * float(torch.erfinv(torch.tensor(1.0 - 2.0 * p, dtype=torch.float64)))
-    z_lo = max(0.0, z_p - 1.0)
+    z_lo = max(0.0, math.sqrt(2.0) * float(torch.erfinv(torch.tensor(1.0 - 2.0 * p, dtype=torch.float64))))
     key_lo = struct.unpack("<I", struct.pack("<f", z_lo))[0] | 0x80000000
     shift = 0
     while ((0xFFFFFFFF - key_lo) >> shift) >= 8192:
@@ -145,7 +146,11 @@ class FusedBatchTopKEngine:
         self.preact = torch.empty(L, B, Fl, dtype=torch.bfloat16, device=dev)
         self.mean = torch.empty(L, Fl, dtype=f32, device=dev)
         self.rstd = torch.empty(L, Fl, dtype=f32, device=dev)
-        self.hist = torch.zeros(2 * 8192, dtype=i32, device=dev)
+        self.hist = torch.zeros(2 * 8192 + 32, dtype=i32, device=dev)  # two histograms + the pool counter
+        # tracked histogram range {key_lo, shift} and the pool filled by the single pass over the pre-activations
+        self.sel_state = torch.tensor([self.key_lo, self.shift], dtype=torch.int64, device=dev) if self.key_lo != 0 else None
+        k_local = -(-self.k_total // max(1, self.world))
+        self.pool = torch.empty(4, int(min(B * L * max(Fl, 1), 3 * k_local + (1 << 16))), dtype=i32, device=dev) if self.key_lo != 0 else None
         self.ctl = torch.zeros(16, dtype=torch.int64, device=dev)
         self.status = torch.zeros(4, dtype=i32, device=dev)
         cap = max(self.k_total, 8)
@@ -234,7 +239,7 @@ class FusedBatchTopKEngine:
             self.preact, self.mean, self.rstd, self.Fv, self.Fl, m.feature_start, self.F, self.k_total,
             self.key_lo, self.shift, self.hist, self.ctl, self.ent_tok, self.ent_col, self.ent_val,
             self.cand_key, self.cand_tok, self.cand_col, self.cand_val, self.status,
-            world, rank, dptr, fptr, slot, seq,
+            world, rank, dptr, fptr, slot, seq, self.sel_state, self.pool,
         )
         self.tok_cnt.zero_()
         self.feat_cnt.zero_()
@@ -243,8 +248,9 @@ class FusedBatchTopKEngine:
             self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
             self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2, self.Fl,
         )
-        # gemm, colstats, select (zhist, find_bin [x2 when the narrow range is used], compact, refine, finalize), csr (5)
-        self.kernel_launches += 2 + (7 if self.key_lo != 0 else 5) + 5
+        # gemm, colstats, select (collect, find_bin, classify, fallback x3, refine, finalize | zhist, find_bin, compact,
+        # refine, finalize), csr (5)
+        self.kernel_launches += 2 + (8 if self.key_lo != 0 else 5) + 5
 
     def _bias_sum(self) -> torch.Tensor:
         return (self.bias_sel @ self.model.dec_bias.data.float()).contiguous()
@@ -258,7 +264,7 @@ class FusedBatchTopKEngine:
         bias_sum = self._bias_sum()
         if self.world == 1:
             e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
-                            None, None, None, bias_sum, None, Y, self.sigma, self.gs, yhat, self.sq_err, 1, [], 0, 0)
+                            None, None, None, bias_sum, None, Y, self.sigma, self.gs, yhat, self.sq_err, 1, [], 0, 0, self.status)
             self.kernel_launches += 1
         else:
             sy = self.symm
@@ -266,7 +272,7 @@ class FusedBatchTopKEngine:
                 yhat.zero_()
             # 1. decode, pushing every token's partial sums into its owner's staging slot (peer stores)
             e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
-                            None, None, None, None, None, None, None, None, None, None, 2, sy.stage_ptrs, sy.rows_per_rank, self.rank)
+                            None, None, None, None, None, None, None, None, None, None, 2, sy.stage_ptrs, sy.rows_per_rank, self.rank, self.status)
             sy.barrier(e, self.status)
             # 2. owners reduce their rows, finish the loss and push the gradient seed to every rank
             e.owner_reduce_loss(sy.stage, sy.gs_ptrs, self.rank, bias_sum, None, Y, self.sigma, yhat, self.sq_err, sy.rows_per_rank)

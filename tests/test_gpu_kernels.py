@@ -55,7 +55,8 @@ def test_colstats(ext):
     assert torch.allclose(rstd, 1.0 / (xf.std(dim=1) + 1e-6), rtol=1e-4)
 
 
-def _run_select(ext, x, k_total, f_valid=None, feat_offset=0, full_F=None, full_range=False, cand_cap=None, key_range=None):
+def _run_select(ext, x, k_total, f_valid=None, feat_offset=0, full_F=None, full_range=False, cand_cap=None, key_range=None,
+                sel_state=None, pool=None):
     dev = x.device
     L, B, Fl = x.shape
     f_valid = Fl if f_valid is None else f_valid
@@ -63,7 +64,7 @@ def _run_select(ext, x, k_total, f_valid=None, feat_offset=0, full_F=None, full_
     mean = torch.empty(L, Fl, device=dev)
     rstd = torch.empty(L, Fl, device=dev)
     ext.colstats(x, mean, rstd)
-    hist = torch.zeros(2 * 8192, dtype=torch.int32, device=dev)
+    hist = torch.zeros(2 * 8192 + 32, dtype=torch.int32, device=dev)
     ctl = torch.zeros(16, dtype=torch.int64, device=dev)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     cap = max(k_total, 8)
@@ -76,7 +77,7 @@ def _run_select(ext, x, k_total, f_valid=None, feat_offset=0, full_F=None, full_
     if key_range is not None:
         key_lo, shift = key_range
     ext.batchtopk_select(x, mean, rstd, f_valid, Fl, feat_offset, full_F, k_total, key_lo, shift, hist, ctl,
-                         ent[0], ent[1], ent[2], cand[0], cand[1], cand[2], cand[3], status, 1, 0, [], [], 0, 0)
+                         ent[0], ent[1], ent[2], cand[0], cand[1], cand[2], cand[3], status, 1, 0, [], [], 0, 0, sel_state, pool)
     torch.cuda.synchronize()
     return mean, rstd, ctl, status, ent
 
@@ -154,6 +155,64 @@ def test_batchtopk_select_falls_back_when_guess_misses(ext):
     col = ent[1][:n].long()
     got[col // F, ent[0][:n].long(), col % F] = True
     assert torch.equal(got, _oracle_mask(x, mean, rstd, k_total, F))
+
+
+def _selected_mask(ent, n, L, B, F, dev):
+    got = torch.zeros(L, B, F, dtype=torch.bool, device=dev)
+    col = ent[1][:n].long()
+    got[col // F, ent[0][:n].long(), col % F] = True
+    return got
+
+
+def test_batchtopk_select_tracked_range_follows_the_cut(ext):
+    """Tracked range + pool: the state starts far too high (first step falls back), then follows the data
+    through a change of distribution; every step must equal the oracle."""
+    import struct
+
+    torch.manual_seed(11)
+    dev = _dev()
+    L, B, F = 3, 256, 512
+    k_total = 9 * B
+    key_lo = struct.unpack("<I", struct.pack("<f", 40.0))[0] | 0x80000000
+    shift = 0
+    while ((0xFFFFFFFF - key_lo) >> shift) >= 8192:
+        shift += 1
+    state = torch.tensor([key_lo, shift], dtype=torch.int64, device=dev)
+    pool = torch.empty(4, 3 * k_total + 4096, dtype=torch.int32, device=dev)
+    retries = []
+    for step in range(6):
+        x = torch.randn(L, B, F, device=dev)
+        if step >= 3:  # heavier tails: the cut moves
+            x = x * (1.0 + 2.0 * (torch.rand(L, B, F, device=dev) < 0.05).float())
+        x = x.bfloat16()
+        mean, rstd, ctl, status, ent = _run_select(ext, x, k_total, key_range=(key_lo, shift), sel_state=state, pool=pool)
+        assert int(status[0]) == 0, f"status {status.tolist()} at step {step}"
+        n = int(ctl[3])
+        assert n == k_total
+        assert torch.equal(_selected_mask(ent, n, L, B, F, dev), _oracle_mask(x, mean, rstd, k_total, F)), f"step {step}"
+        retries.append(int(ctl[10]))
+    assert retries[0] == 1, "first range was above every key: fallback expected"
+    assert retries[1] == 0 and retries[2] == 0, f"range did not lock on: {retries}"
+    assert retries[5] == 0, f"range did not recover after the distribution changed: {retries}"
+    z_lo = struct.unpack("<f", struct.pack("<I", int(state[0]) & 0x7FFFFFFF))[0]
+    assert 0.0 < z_lo < 6.0
+
+
+def test_batchtopk_select_pool_overflow_falls_back(ext):
+    """A pool that cannot hold the elements inside the range: the full-range pass must take over."""
+    torch.manual_seed(12)
+    dev = _dev()
+    L, B, F = 2, 128, 256
+    k_total = 8 * B
+    state = torch.tensor([0x80000000, 18], dtype=torch.int64, device=dev)  # z >= 0: half of all elements
+    pool = torch.empty(4, 64, dtype=torch.int32, device=dev)
+    x = torch.randn(L, B, F, device=dev).bfloat16()
+    mean, rstd, ctl, status, ent = _run_select(ext, x, k_total, sel_state=state, pool=pool)
+    assert int(status[0]) == 0 and int(ctl[10]) == 1
+    n = int(ctl[3])
+    assert n == k_total
+    assert torch.equal(_selected_mask(ent, n, L, B, F, dev), _oracle_mask(x, mean, rstd, k_total, F))
+    assert int(state[0]) > 0x80000000  # the range moved up for the next step
 
 
 def test_histogram_range_guess():
