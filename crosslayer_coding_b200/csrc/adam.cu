@@ -305,6 +305,258 @@ __global__ void __launch_bounds__(256, 2) decoder_rows_adam_untied_kernel(const 
   }
 }
 
+// ---------------------------------------------------------------- untied decoders, bulk-copy pipeline
+// The update streams every decoder row once: (w, m, v) in, (w, m, v) out, 20 bytes per element with bf16
+// weights, so the kernel is a copy with some arithmetic in the middle.  A producer thread per CTA moves
+// whole rows between global and shared memory with 1-D bulk copies (cp.async.bulk, no multicast): row in
+// (w, m, v and the gradient-seed rows of the feature's first four entries) -> consumers update the row in
+// place in shared memory -> row out.  The ring keeps several rows per CTA in flight in both directions and
+// the consumers never wait on a global load, except for the rare feature with more than four entries.
+// Every mbarrier wait is bounded; a timeout sets the status word and drains the copies in flight.
+constexpr int kAdamStages = 4;
+constexpr int kAdamSlots = 4;  // gradient-seed rows per stage
+
+struct AdamStageHdr {  // 64 bytes in front of every stage, written by the producer before it arms the barrier
+  int ne;      // entries of the feature
+  int b;       // start of the feature in the CSR arrays
+  int col;     // ti * F_pitch + f
+  int ti;
+  int r;       // row inside the feature
+  int R;
+  long long elem_off;  // element offset of the row inside its tensor
+  float a[kAdamSlots];
+  int pad[4];
+};
+static_assert(sizeof(AdamStageHdr) == 64, "stage header is 64 bytes");
+
+struct AdamBulkShared {
+  uint64_t full[kAdamStages];
+  uint64_t done[kAdamStages];
+  int abort_flag;
+};
+
+struct FeatMeta {
+  int b, e;
+  int tok[kAdamSlots];
+  float a[kAdamSlots];
+};
+
+template <typename WT, bool SR>
+__global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAdamParams p, int gthreads, int stage_bytes, int* status) {
+  extern __shared__ uint8_t smem_raw_adam[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_adam) + 127) & ~uintptr_t(127));
+  AdamBulkShared* sh = reinterpret_cast<AdamBulkShared*>(ring + size_t(kAdamStages) * stage_bytes);
+  const int d = p.d, B = p.B, Fp = p.F_pitch;
+  const int nconsumer = gthreads;
+  const int tid = threadIdx.x;
+  const int nf = (Fp - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);  // features of this CTA per tensor
+  long long n_rows = 0;
+  for (int ti = 0; ti < p.ntensors; ++ti) n_rows += 1LL * (nf > 0 ? nf : 0) * p.rows[ti];
+  const int n = int(n_rows);
+  const uint32_t w_bytes = uint32_t(d) * sizeof(WT), mv_bytes = uint32_t(d) * 4u, gs_bytes = uint32_t(d) * 2u;
+  const uint32_t off_w = 64, off_m = off_w + w_bytes, off_v = off_m + mv_bytes, off_gs = off_v + mv_bytes;
+  if (tid == 0) {
+    for (int s = 0; s < kAdamStages; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->done[s], nconsumer / 32);
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  volatile int* abort_flag = &sh->abort_flag;
+
+  if (tid == nconsumer) {
+    // ------------------------------------------------------------------ producer / store issuer
+    const int n_feat = nf * p.ntensors;
+    auto col_of = [&](int k) { const int ti = k / nf; return ti * Fp + int(blockIdx.x) + (k - ti * nf) * int(gridDim.x); };
+    auto load_offsets = [&](int k, FeatMeta& mt) {
+      if (k < n_feat) { const int c = col_of(k); mt.b = __ldg(p.feat_off + c); mt.e = __ldg(p.feat_off + c + 1); }
+      else { mt.b = 0; mt.e = 0; }
+    };
+    auto load_entries = [&](FeatMeta& mt) {
+#pragma unroll
+      for (int j = 0; j < kAdamSlots; ++j) {
+        const bool in = mt.b + j < mt.e;
+        mt.tok[j] = in ? __ldg(p.fcsr_tok + mt.b + j) : 0;
+        mt.a[j] = in ? __ldg(p.fcsr_val + mt.b + j) : 0.f;
+      }
+    };
+    FeatMeta cur, nxt, nn;
+    load_offsets(0, cur); load_entries(cur);
+    load_offsets(1, nxt);
+    int k = 0, r = 0;             // feature / row whose loads are issued next
+    int ti = 0, R = n_feat > 0 ? p.rows[0] : 0;
+    int f = int(blockIdx.x);
+    bool fresh = true;            // first row of a feature: start the prefetch of the following ones
+    auto issue_loads = [&](int i) {
+      if (fresh) {
+        load_entries(nxt);        // offsets of k + 1 were requested one feature ago
+        load_offsets(k + 2, nn);
+        fresh = false;
+      }
+      const int st = i % kAdamStages;
+      uint8_t* stage = ring + size_t(st) * stage_bytes;
+      AdamStageHdr* h = reinterpret_cast<AdamStageHdr*>(stage);
+      const int ne = cur.e - cur.b;
+      const long long elem_off = (1LL * f * R + r) * d;
+      h->ne = ne; h->b = cur.b; h->col = ti * Fp + f; h->ti = ti; h->r = r; h->R = R; h->elem_off = elem_off;
+#pragma unroll
+      for (int j = 0; j < kAdamSlots; ++j) h->a[j] = cur.a[j];
+      const int nslot = ne < kAdamSlots ? ne : kAdamSlots;
+      mbar_expect_tx(&sh->full[st], w_bytes + 2u * mv_bytes + uint32_t(nslot) * gs_bytes);
+      bulk_load_1d(stage + off_w, static_cast<const WT*>(p.w[ti]) + elem_off, w_bytes, &sh->full[st]);
+      bulk_load_1d(stage + off_m, p.m[ti] + elem_off, mv_bytes, &sh->full[st]);
+      bulk_load_1d(stage + off_v, p.v[ti] + elem_off, mv_bytes, &sh->full[st]);
+      const __nv_bfloat16* gs_t = p.gs + 1LL * (ti + r) * B * d;
+#pragma unroll
+      for (int j = 0; j < kAdamSlots; ++j)
+        if (j < nslot) bulk_load_1d(stage + off_gs + j * gs_bytes, gs_t + 1LL * cur.tok[j] * d, gs_bytes, &sh->full[st]);
+      // advance to the next row
+      if (++r == R) {
+        r = 0; ++k;
+        cur = nxt; nxt.b = nn.b; nxt.e = nn.e;
+        fresh = true;
+        if (k < n_feat) {
+          const int nti = k / nf;
+          if (nti != ti) { ti = nti; R = p.rows[ti]; }
+          f = int(blockIdx.x) + (k - ti * nf) * int(gridDim.x);
+        }
+      }
+    };
+    int issued = 0;
+    for (; issued < n && issued < kAdamStages; ++issued) issue_loads(issued);
+    int i = 0;
+    for (; i < n; ++i) {
+      const int st = i % kAdamStages;
+      if (!mbar_wait(&sh->done[st], (i / kAdamStages) & 1, abort_flag)) break;
+      uint8_t* stage = ring + size_t(st) * stage_bytes;
+      const AdamStageHdr* h = reinterpret_cast<const AdamStageHdr*>(stage);
+      const int sti = h->ti;
+      const long long eo = h->elem_off;
+      bulk_store_1d(static_cast<WT*>(p.w[sti]) + eo, stage + off_w, w_bytes);
+      bulk_store_1d(p.m[sti] + eo, stage + off_m, mv_bytes);
+      bulk_store_1d(p.v[sti] + eo, stage + off_v, mv_bytes);
+      bulk_commit();
+      if (i >= 1 && issued < n) {
+        bulk_wait_read<1>();  // the stores of row i - 1 have read their stage: it can be refilled
+        issue_loads(issued);
+        ++issued;
+      }
+    }
+    bulk_wait_all();
+    if (*abort_flag) {
+      // rows whose loads were issued but never consumed: give them a bounded chance to land
+      for (int j = i; j < issued; ++j) {
+        const long long start = clock64();
+        while (!mbar_try_wait(&sh->full[j % kAdamStages], (j / kAdamStages) & 1))
+          if (clock64() - start > kWaitTimeoutCycles) break;
+      }
+    }
+  } else if (tid < nconsumer) {
+// ------------------------------------------------------------------ consumers: one row per stage
+    const int lane = tid & 31;
+    const int e0 = tid * 8;
+    const bool act = e0 < d;
+    const HyperRegs hr = make_regs(p.h);
+    float dacc[kAdamSlots] = {0.f, 0.f, 0.f, 0.f};
+    float norm2 = 0.f, pc = 0.f;
+    for (int i = 0; i < n; ++i) {
+      const int st = i % kAdamStages;
+      if (!mbar_wait(&sh->full[st], (i / kAdamStages) & 1, abort_flag)) break;
+      uint8_t* stage = ring + size_t(st) * stage_bytes;
+      const AdamStageHdr* h = reinterpret_cast<const AdamStageHdr*>(stage);
+      const int ne = h->ne, r = h->r, R = h->R, col = h->col, ti = h->ti, b = h->b;
+      if (r == 0) {
+#pragma unroll
+        for (int j = 0; j < kAdamSlots; ++j) dacc[j] = 0.f;
+        norm2 = 0.f;
+        pc = p.pen_coef ? __ldg(p.pen_coef + col) : 0.f;
+      }
+      float w[8], m[8], v[8], g[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) { g[q] = 0.f; w[q] = 0.f; }
+      WT* w_s = reinterpret_cast<WT*>(stage + off_w) + e0;
+      float* m_s = reinterpret_cast<float*>(stage + off_m) + e0;
+      float* v_s = reinterpret_cast<float*>(stage + off_v) + e0;
+      if (act) {
+        load_w8<WT>(w_s, w);
+        load8f(m_s, m);
+        load8f(v_s, v);
+        const __nv_bfloat16* gs_s = reinterpret_cast<const __nv_bfloat16*>(stage + off_gs) + e0;
+#pragma unroll
+        for (int j = 0; j < kAdamSlots; ++j) {
+          if (j < ne) {
+            const float a = h->a[j];
+            float gv[8];
+            unpack8(*reinterpret_cast<const uint4*>(gs_s + j * d), gv);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              g[q] = fmaf(a, gv[q], g[q]);
+              dacc[j] = fmaf(gv[q], w[q], dacc[j]);
+            }
+          }
+        }
+      }
+      for (int x = b + kAdamSlots; x < b + ne; ++x) {  // rare: features with more entries than slots
+        float dot = 0.f;
+        if (act) {
+          const float a = __ldg(p.fcsr_val + x);
+          float gv[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(p.gs + (1LL * (ti + r) * B + __ldg(p.fcsr_tok + x)) * d + e0)), gv);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            g[q] = fmaf(a, gv[q], g[q]);
+            dot = fmaf(gv[q], w[q], dot);
+          }
+        }
+        if (p.grad_a != nullptr) {
+          dot = warp_sum(dot);
+          if (lane == 0 && dot != 0.f) atomicAdd(&p.grad_a[x], dot * hr.gscale);
+        }
+      }
+      if (act) {
+        float dg0[8];
+        const bool extra = r == 0 && p.dgrad_row0 != nullptr;
+        if (extra) load8f(p.dgrad_row0 + (1LL * col) * d + e0, dg0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float gq = fmaf(pc, w[q], g[q] * hr.gscale);
+          if (extra) gq += dg0[q];
+          adam1(w[q], m[q], v[q], gq, hr);
+          norm2 = fmaf(w[q], w[q], norm2);
+        }
+        store8f(m_s, m);
+        store8f(v_s, v);
+        const unsigned long long gidx = (unsigned long long)(p.row_start[ti] * d + h->elem_off + e0);
+        if (sizeof(WT) == 2) *reinterpret_cast<uint4*>(w_s) = pack8_bf16<SR>(w, p.h.sr_seed, (unsigned int)gidx);
+        else store8f(reinterpret_cast<float*>(w_s), w);
+      }
+      if (r == R - 1) {
+        if (p.grad_a != nullptr) {
+          const int nslot = ne < kAdamSlots ? ne : kAdamSlots;
+#pragma unroll
+          for (int j = 0; j < kAdamSlots; ++j) {
+            if (j < nslot) {
+              const float sdot = warp_sum(dacc[j]);
+              if (lane == 0 && sdot != 0.f) atomicAdd(&p.grad_a[b + j], sdot * hr.gscale);
+            }
+          }
+        }
+        if (p.norm2_out != nullptr) {
+          const float sn = warp_sum(norm2);
+          if (lane == 0) atomicAdd(&p.norm2_out[col], sn);
+        }
+      }
+      fence_proxy_async();  // the row written above is read next by the bulk store (async proxy)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->done[st]);
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && sh->abort_flag && status != nullptr) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+}
+
 // Tied decoders (per_source / per_target): same structure without the register-resident entries.
 // Work item = (feature of one decoder tensor, 256-element segment): one warp, 8 elements per lane, walking
 // the feature's R rows with the next row's (w, m, v) already in flight while the current row is updated.
@@ -615,6 +867,7 @@ struct CltDecAdamArgs {
   const float* feat_offset; const float* feat_scale;
   const float* dgrad_row0;
   CltAdamHyper h;
+  int* status;  // when given, untied decoders use the bulk-copy pipeline (its bounded waits report here)
 };
 
 extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st) {
@@ -634,7 +887,30 @@ extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaS
   p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale; p.dgrad_row0 = a->dgrad_row0; p.h = to_hyper(a->h);
   if (acc == 0) return 0;
   const int grid = num_sms * 8;
-  if (a->tying == 0) {
+  const int gthreads = ((a->d / 8 + 31) / 32) * 32;
+  const size_t wsz = a->weights_bf16 ? 2 : 4;
+  const int stage_bytes = int(((64 + size_t(a->d) * (wsz + 8 + 2 * kAdamSlots)) + 127) / 128 * 128);
+  const size_t smem = size_t(kAdamStages) * stage_bytes + sizeof(AdamBulkShared) + 256;
+  if (a->tying == 0 && a->status != nullptr && gthreads <= 256 && smem <= 200 * 1024 && acc * a->d < (1LL << 62)) {
+    const bool sr = a->h.sr_seed != 0;
+    int per_sm = int((227 * 1024) / (smem + 1024));
+    per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
+    int bgrid = num_sms * per_sm;
+    if (bgrid > a->F_pitch) bgrid = a->F_pitch;
+    auto launch = [&](auto kern, int which) -> int {
+      static size_t attr_set[3] = {0, 0, 0};
+      if (attr_set[which] < smem) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
+        attr_set[which] = smem;
+      }
+      kern<<<bgrid, gthreads + 32, smem, st>>>(p, gthreads, stage_bytes, a->status);
+      return 0;
+    };
+    int rc;
+    if (a->weights_bf16) rc = sr ? launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, true>, 0) : launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, false>, 1);
+    else rc = launch(decoder_rows_adam_bulk_kernel<float, false>, 2);
+    if (rc != 0) return rc;
+  } else if (a->tying == 0) {
     const bool sr = a->h.sr_seed != 0;
     if (a->weights_bf16) {
       if (sr) decoder_rows_adam_untied_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(p);

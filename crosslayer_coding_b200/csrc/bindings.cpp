@@ -102,6 +102,7 @@ struct CltDecAdamArgs {
   const float* feat_offset; const float* feat_scale;
   const float* dgrad_row0;
   CltAdamHyper h;
+  int* status;
 };
 int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st);
 struct CltEncAdamArgs {
@@ -334,7 +335,7 @@ void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vect
                        int64_t F_pitch, int64_t tying, const Tensor& feat_off, const Tensor& fcsr_tok, const Tensor& fcsr_val,
                        const Tensor& gs, const OptTensor& grad_a, const OptTensor& pen_coef, const OptTensor& norm2_out,
                        const OptTensor& feat_offset, const OptTensor& feat_scale, const OptTensor& dgrad_row0,
-                       const std::vector<double>& hyper) {
+                       const std::vector<double>& hyper, const OptTensor& status) {
   TORCH_CHECK(w.size() <= 32 && w.size() == m.size() && w.size() == v.size(), "bad tensor lists");
   CltDecAdamArgs a;
   std::memset(&a, 0, sizeof(a));
@@ -352,6 +353,7 @@ void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vect
   a.dgrad_row0 = opt_ptr<const float>(dgrad_row0);
   if (a.dgrad_row0) TORCH_CHECK(dgrad_row0->scalar_type() == at::kFloat && dgrad_row0->numel() == int64_t(w.size()) * F_pitch * d, "dgrad_row0 must be fp32 [ntensors, F, d]");
   a.h = hyper_from(hyper);
+  a.status = opt_ptr<int>(status);
   c10::cuda::CUDAGuard guard(gs.device());
   check(clt_decoder_rows_adam(&a, num_sms(), cur_stream()), "decoder_rows_adam");
 }

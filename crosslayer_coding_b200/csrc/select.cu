@@ -233,9 +233,20 @@ struct Pool {
   long long cap;
   unsigned int* count;  // zeroed by the caller together with the histograms
 };
-constexpr int kPoolStage = 768;  // histogram + staging stay inside the 48 KB of static shared memory
-constexpr int kHistExtra = 32;  // words after the two histograms: [0] = pool counter
+constexpr int kPoolStage = 512;   // histogram + queue + staging stay inside the 48 KB of static shared memory
+constexpr int kHitQueue = 1024;   // 16-byte groups per CTA that passed the coarse filter
+constexpr int kHistExtra = 32;    // words after the two histograms: [0] = pool counter
 
+// Packed compare of two bf16 pairs: 0xFFFF in every half where a >= b (false for NaN).
+__device__ __forceinline__ uint32_t bf16x2_ge_mask(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("set.ge.u32.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// Phase A streams the matrix with a coarse filter in the input's own format (one packed compare per two
+// elements) and only queues the 16-byte groups that may hold an element of the range; phase B runs the exact
+// test on the queued groups, one element per thread.  The hot loop stays a few instructions per group.
 __global__ void __launch_bounds__(256) zhist_collect_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
                                                               const float* __restrict__ rstd, ScanGeom g, int col_pitch,
                                                               const long long* __restrict__ sel_state,
@@ -244,32 +255,38 @@ __global__ void __launch_bounds__(256) zhist_collect_kernel(const __nv_bfloat16*
   const int shift = int(sel_state[1]);
   const float z_lo = key_to_float(key_lo);
   __shared__ unsigned int sh[kHistBins];
+  __shared__ uint32_t s_queue[kHitQueue];
   __shared__ uint32_t s_key[kPoolStage];
   __shared__ int s_tok[kPoolStage];
   __shared__ int s_col[kPoolStage];
   __shared__ float s_val[kPoolStage];
-  __shared__ int s_n;
+  __shared__ int s_q, s_n;
   __shared__ unsigned int s_base;
   for (int i = threadIdx.x; i < kHistBins; i += blockDim.x) sh[i] = 0;
-  if (threadIdx.x == 0) s_n = 0;
+  if (threadIdx.x == 0) { s_q = 0; s_n = 0; }
   __syncthreads();
   const int l = blockIdx.z;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int r0 = blockIdx.y * g.rows_per_block;
+  const int r1 = min(g.B, r0 + g.rows_per_block);
   if (c0 < g.F) {
-    float mu[8], rs[8];
-    if (c0 + 8 <= g.F) {
-      load_cols8(mean + 1LL * l * g.sp + c0, mu);
-      load_cols8(rstd + 1LL * l * g.sp + c0, rs);
-    } else {
-      for (int j = 0; j < 8; ++j) {
-        const bool in = c0 + j < g.F;
-        mu[j] = in ? mean[1LL * l * g.sp + c0 + j] : 0.f;
-        rs[j] = in ? rstd[1LL * l * g.sp + c0 + j] : 0.f;
+    // thr_j = mean_j + z_lo / rstd_j, lowered by a margin for the fp32 rounding of the exact test and rounded
+    // down to bf16: x >= thr_j is implied by z_j >= z_lo
+    uint32_t thr2[4];
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      float t[2];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const bool in = c0 + j + q < g.F;
+        const float mu = in ? __ldg(mean + 1LL * l * g.sp + c0 + j + q) : 0.f;
+        const float rs = in ? __ldg(rstd + 1LL * l * g.sp + c0 + j + q) : 0.f;
+        const float span = z_lo / rs;
+        t[q] = (in && rs > 0.f) ? mu + span - 1e-5f * (fabsf(mu) + fabsf(span)) - 1e-30f : INFINITY;
       }
+      const __nv_bfloat162 pk = __halves2bfloat162(__float2bfloat16_rd(t[0]), __float2bfloat16_rd(t[1]));
+      thr2[j >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
     }
-    const int nvalid = min(8, g.F - c0);
-    const int r0 = blockIdx.y * g.rows_per_block;
-    const int r1 = min(g.B, r0 + g.rows_per_block);
     const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
     for (int rb = r0; rb < r1; rb += 8) {
       uint4 v[8];
@@ -280,24 +297,36 @@ __global__ void __launch_bounds__(256) zhist_collect_kernel(const __nv_bfloat16*
       }
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const int r = rb + k;
-        const uint32_t u[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
-          const float z = (xv - mu[j]) * rs[j];
-          if (!(z >= z_lo) || j >= nvalid || r >= r1) continue;
-          const uint32_t key = float_to_key(z);
-          atomicAdd(&sh[min((key - key_lo) >> shift, uint32_t(kHistBins - 1))], 1u);
-          const int slot = atomicAdd(&s_n, 1);
-          if (slot < kPoolStage) {
-            s_key[slot] = key; s_tok[slot] = r; s_col[slot] = l * col_pitch + c0 + j; s_val[slot] = xv;
-          } else {  // staging full: append directly
-            const unsigned int q = atomicAdd(pool.count, 1u);
-            if ((long long)q < pool.cap) { pool.key[q] = key; pool.tok[q] = r; pool.col[q] = l * col_pitch + c0 + j; pool.val[q] = xv; }
-          }
+        const uint32_t hit = bf16x2_ge_mask(v[k].x, thr2[0]) | bf16x2_ge_mask(v[k].y, thr2[1]) |
+                             bf16x2_ge_mask(v[k].z, thr2[2]) | bf16x2_ge_mask(v[k].w, thr2[3]);
+        if (hit != 0 && rb + k < r1) {
+          const int slot = atomicAdd(&s_q, 1);
+          if (slot < kHitQueue) s_queue[slot] = (uint32_t(rb + k - r0) << 8) | threadIdx.x;
         }
       }
+    }
+  }
+  __syncthreads();
+  // ---- phase B: exact test, histogram and pool staging, one element per thread
+  const int nq_all = s_q;
+  if (nq_all > kHitQueue && threadIdx.x == 0) atomicOr(pool.count, 0x80000000u);  // lost groups: force the full-range pass
+  const int nq = min(nq_all, kHitQueue);
+  for (int e = threadIdx.x; e < nq * 8; e += blockDim.x) {
+    const uint32_t item = s_queue[e >> 3];
+    const int r = r0 + int(item >> 8);
+    const int c = (blockIdx.x * blockDim.x + int(item & 255u)) * 8 + (e & 7);
+    if (c >= g.F) continue;
+    const float xv = __bfloat162float(x[1LL * l * g.layer_stride + 1LL * r * g.ld + c]);
+    const float z = (xv - __ldg(mean + 1LL * l * g.sp + c)) * __ldg(rstd + 1LL * l * g.sp + c);
+    if (!(z >= z_lo)) continue;
+    const uint32_t key = float_to_key(z);
+    atomicAdd(&sh[min((key - key_lo) >> shift, uint32_t(kHistBins - 1))], 1u);
+    const int slot = atomicAdd(&s_n, 1);
+    if (slot < kPoolStage) {
+      s_key[slot] = key; s_tok[slot] = r; s_col[slot] = l * col_pitch + c; s_val[slot] = xv;
+    } else {  // staging full: append directly
+      const unsigned int q = atomicAdd(pool.count, 1u);
+      if ((long long)q < pool.cap) { pool.key[q] = key; pool.tok[q] = r; pool.col[q] = l * col_pitch + c; pool.val[q] = xv; }
     }
   }
   __syncthreads();

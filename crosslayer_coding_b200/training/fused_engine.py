@@ -437,7 +437,7 @@ class FusedBatchTopKEngine:
         self.norm2_next.zero_()
         e.decoder_rows_adam([w.data for w in m.dec_weight], self.dec_m, self.dec_v, L, B, d, self.Fl, self.tying,
                             self.feat_off, self.fcsr_tok, self.fcsr_val, self.gs, self.grad_a, pen, self.norm2_next,
-                            None, None, dec0_dense, self._hyper(lr, c_g))
+                            None, None, dec0_dense, self._hyper(lr, c_g), self.status)
         self.norm2, self.norm2_next = self.norm2_next, self.norm2
         self.norms_valid = True
         e.dense_adam(m.dec_bias.data, self.decb_m, self.decb_v, bias_grad, self._hyper(lr, c_g))
