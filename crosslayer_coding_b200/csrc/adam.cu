@@ -341,10 +341,61 @@ struct FeatMeta {
   float a[kAdamSlots];
 };
 
-template <typename WT, bool SR>
+// Vector access to EPT (4 or 8) consecutive elements of a row held in shared memory.
+template <int EPT>
+__device__ __forceinline__ void ldf(const float* p, float (&o)[EPT]) {
+#pragma unroll
+  for (int i = 0; i < EPT; i += 4) {
+    const float4 a = *reinterpret_cast<const float4*>(p + i);
+    o[i] = a.x; o[i + 1] = a.y; o[i + 2] = a.z; o[i + 3] = a.w;
+  }
+}
+template <int EPT>
+__device__ __forceinline__ void stf(float* p, const float (&o)[EPT]) {
+#pragma unroll
+  for (int i = 0; i < EPT; i += 4) *reinterpret_cast<float4*>(p + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+}
+template <int EPT>
+__device__ __forceinline__ void ldbf(const __nv_bfloat16* p, float (&o)[EPT]) {
+#pragma unroll
+  for (int i = 0; i < EPT; i += 4) {
+    const uint2 q = *reinterpret_cast<const uint2*>(p + i);
+    o[i] = bf16_lo(q.x); o[i + 1] = bf16_hi(q.x); o[i + 2] = bf16_lo(q.y); o[i + 3] = bf16_hi(q.y);
+  }
+}
+template <int EPT>
+__device__ __forceinline__ void ldbf_global(const __nv_bfloat16* p, float (&o)[EPT]) {
+#pragma unroll
+  for (int i = 0; i < EPT; i += 4) {
+    const uint2 q = __ldg(reinterpret_cast<const uint2*>(p + i));
+    o[i] = bf16_lo(q.x); o[i + 1] = bf16_hi(q.x); o[i + 2] = bf16_lo(q.y); o[i + 3] = bf16_hi(q.y);
+  }
+}
+template <int EPT, bool SR>
+__device__ __forceinline__ void stbf(__nv_bfloat16* p, const float (&o)[EPT], unsigned int seed, unsigned int idx) {
+#pragma unroll
+  for (int i = 0; i < EPT; i += 4) {
+    uint2 q;
+    if (!SR) {
+      q.x = pack_bf16x2(o[i], o[i + 1]); q.y = pack_bf16x2(o[i + 2], o[i + 3]);
+    } else {
+      uint32_t h[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t u = __float_as_uint(o[i + k]);
+        const uint32_t rnd = hash32((idx + i + k) ^ seed) & 0xFFFFu;
+        h[k] = ((u & 0x7F800000u) == 0x7F800000u) ? (u >> 16) : ((u + rnd) >> 16);
+      }
+      q.x = h[0] | (h[1] << 16); q.y = h[2] | (h[3] << 16);
+    }
+    *reinterpret_cast<uint2*>(p + i) = q;
+  }
+}
+
+template <typename WT, bool SR, int EPT>
 __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAdamParams p, int gthreads, int stage_bytes, int* status) {
-  extern __shared__ uint8_t smem_raw_adam[];
-  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_adam) + 127) & ~uintptr_t(127));
+  extern __shared__ __align__(128) uint8_t smem_raw_adam[];  // bulk copies need 16-byte alignment only
+  uint8_t* ring = smem_raw_adam;
   AdamBulkShared* sh = reinterpret_cast<AdamBulkShared*>(ring + size_t(kAdamStages) * stage_bytes);
   const int d = p.d, B = p.B, Fp = p.F_pitch;
   const int nconsumer = gthreads;
@@ -382,6 +433,9 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
         mt.a[j] = in ? __ldg(p.fcsr_val + mt.b + j) : 0.f;
       }
     };
+    // rows are touched once per step, the gradient seed is re-read by every feature: keep the latter in L2
+    const uint64_t pol_stream = l2_policy_evict_first();
+    const uint64_t pol_keep = l2_policy_evict_last();
     FeatMeta cur, nxt, nn;
     load_offsets(0, cur); load_entries(cur);
     load_offsets(1, nxt);
@@ -406,12 +460,12 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       const int nslot = ne < kAdamSlots ? ne : kAdamSlots;
       mbar_expect_tx(&sh->full[st], w_bytes + 2u * mv_bytes + uint32_t(nslot) * gs_bytes);
       bulk_load_1d(stage + off_w, static_cast<const WT*>(p.w[ti]) + elem_off, w_bytes, &sh->full[st]);
-      bulk_load_1d(stage + off_m, p.m[ti] + elem_off, mv_bytes, &sh->full[st]);
-      bulk_load_1d(stage + off_v, p.v[ti] + elem_off, mv_bytes, &sh->full[st]);
+      bulk_load_1d_hint(stage + off_m, p.m[ti] + elem_off, mv_bytes, &sh->full[st], pol_stream);
+      bulk_load_1d_hint(stage + off_v, p.v[ti] + elem_off, mv_bytes, &sh->full[st], pol_stream);
       const __nv_bfloat16* gs_t = p.gs + 1LL * (ti + r) * B * d;
 #pragma unroll
       for (int j = 0; j < kAdamSlots; ++j)
-        if (j < nslot) bulk_load_1d(stage + off_gs + j * gs_bytes, gs_t + 1LL * cur.tok[j] * d, gs_bytes, &sh->full[st]);
+        if (j < nslot) bulk_load_1d_hint(stage + off_gs + j * gs_bytes, gs_t + 1LL * cur.tok[j] * d, gs_bytes, &sh->full[st], pol_keep);
       // advance to the next row
       if (++r == R) {
         r = 0; ++k;
@@ -435,8 +489,8 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       const int sti = h->ti;
       const long long eo = h->elem_off;
       bulk_store_1d(static_cast<WT*>(p.w[sti]) + eo, stage + off_w, w_bytes);
-      bulk_store_1d(p.m[sti] + eo, stage + off_m, mv_bytes);
-      bulk_store_1d(p.v[sti] + eo, stage + off_v, mv_bytes);
+      bulk_store_1d_hint(p.m[sti] + eo, stage + off_m, mv_bytes, pol_stream);
+      bulk_store_1d_hint(p.v[sti] + eo, stage + off_v, mv_bytes, pol_stream);
       bulk_commit();
       if (i >= 1 && issued < n) {
         bulk_wait_read<1>();  // the stores of row i - 1 have read their stage: it can be refilled
@@ -456,7 +510,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
   } else if (tid < nconsumer) {
 // ------------------------------------------------------------------ consumers: one row per stage
     const int lane = tid & 31;
-    const int e0 = tid * 8;
+    const int e0 = tid * EPT;
     const bool act = e0 < d;
     const HyperRegs hr = make_regs(p.h);
     float dacc[kAdamSlots] = {0.f, 0.f, 0.f, 0.f};
@@ -473,25 +527,26 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
         norm2 = 0.f;
         pc = p.pen_coef ? __ldg(p.pen_coef + col) : 0.f;
       }
-      float w[8], m[8], v[8], g[8];
+      float w[EPT], m[EPT], v[EPT], g[EPT];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) { g[q] = 0.f; w[q] = 0.f; }
+      for (int q = 0; q < EPT; ++q) { g[q] = 0.f; w[q] = 0.f; }
       WT* w_s = reinterpret_cast<WT*>(stage + off_w) + e0;
       float* m_s = reinterpret_cast<float*>(stage + off_m) + e0;
       float* v_s = reinterpret_cast<float*>(stage + off_v) + e0;
       if (act) {
-        load_w8<WT>(w_s, w);
-        load8f(m_s, m);
-        load8f(v_s, v);
+        if (sizeof(WT) == 2) ldbf<EPT>(reinterpret_cast<const __nv_bfloat16*>(w_s), w);
+        else ldf<EPT>(reinterpret_cast<const float*>(w_s), w);
+        ldf<EPT>(m_s, m);
+        ldf<EPT>(v_s, v);
         const __nv_bfloat16* gs_s = reinterpret_cast<const __nv_bfloat16*>(stage + off_gs) + e0;
 #pragma unroll
         for (int j = 0; j < kAdamSlots; ++j) {
           if (j < ne) {
             const float a = h->a[j];
-            float gv[8];
-            unpack8(*reinterpret_cast<const uint4*>(gs_s + j * d), gv);
+            float gv[EPT];
+            ldbf<EPT>(gs_s + j * d, gv);
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
+            for (int q = 0; q < EPT; ++q) {
               g[q] = fmaf(a, gv[q], g[q]);
               dacc[j] = fmaf(gv[q], w[q], dacc[j]);
             }
@@ -502,10 +557,10 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
         float dot = 0.f;
         if (act) {
           const float a = __ldg(p.fcsr_val + x);
-          float gv[8];
-          unpack8(__ldg(reinterpret_cast<const uint4*>(p.gs + (1LL * (ti + r) * B + __ldg(p.fcsr_tok + x)) * d + e0)), gv);
+          float gv[EPT];
+          ldbf_global<EPT>(p.gs + (1LL * (ti + r) * B + __ldg(p.fcsr_tok + x)) * d + e0, gv);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
+          for (int q = 0; q < EPT; ++q) {
             g[q] = fmaf(a, gv[q], g[q]);
             dot = fmaf(gv[q], w[q], dot);
           }
@@ -516,21 +571,27 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
         }
       }
       if (act) {
-        float dg0[8];
+        float dg0[EPT];
         const bool extra = r == 0 && p.dgrad_row0 != nullptr;
-        if (extra) load8f(p.dgrad_row0 + (1LL * col) * d + e0, dg0);
+        if (extra) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+          for (int q = 0; q < EPT; q += 4) {
+            const float4 t4 = __ldg(reinterpret_cast<const float4*>(p.dgrad_row0 + (1LL * col) * d + e0 + q));
+            dg0[q] = t4.x; dg0[q + 1] = t4.y; dg0[q + 2] = t4.z; dg0[q + 3] = t4.w;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < EPT; ++q) {
           float gq = fmaf(pc, w[q], g[q] * hr.gscale);
           if (extra) gq += dg0[q];
           adam1(w[q], m[q], v[q], gq, hr);
           norm2 = fmaf(w[q], w[q], norm2);
         }
-        store8f(m_s, m);
-        store8f(v_s, v);
+        stf<EPT>(m_s, m);
+        stf<EPT>(v_s, v);
         const unsigned long long gidx = (unsigned long long)(p.row_start[ti] * d + h->elem_off + e0);
-        if (sizeof(WT) == 2) *reinterpret_cast<uint4*>(w_s) = pack8_bf16<SR>(w, p.h.sr_seed, (unsigned int)gidx);
-        else store8f(reinterpret_cast<float*>(w_s), w);
+        if (sizeof(WT) == 2) stbf<EPT, SR>(reinterpret_cast<__nv_bfloat16*>(w_s), w, p.h.sr_seed, (unsigned int)gidx);
+        else stf<EPT>(reinterpret_cast<float*>(w_s), w);
       }
       if (r == R - 1) {
         if (p.grad_a != nullptr) {
@@ -763,6 +824,30 @@ __global__ void __launch_bounds__(256) encoder_rows_adam_kernel(const EncAdamPar
   }
 }
 
+// Encoder bias update on its own (used with the bulk-copy row pipeline, which handles the weight rows).
+template <typename WT>
+__global__ void __launch_bounds__(256) encoder_bias_adam_kernel(const EncAdamParams p) {
+  const long long rows = 1LL * p.L * p.F_pitch;
+  for (long long row = blockIdx.x * 1LL * blockDim.x + threadIdx.x; row < rows; row += 1LL * gridDim.x * blockDim.x) {
+    const int b = __ldg(p.feat_off + row), e = __ldg(p.feat_off + row + 1);
+    float gb = 0.f;
+    for (int i = b; i < e; ++i) gb += p.delta[i];
+    gb *= p.h.grad_scale;
+    if (p.dense_bias_grad) gb += p.dense_bias_grad[row];
+    WT* bp = static_cast<WT*>(p.bias) + row;
+    float wv = sizeof(WT) == 2 ? __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(bp)) : *reinterpret_cast<float*>(bp);
+    float mm = p.bias_m[row], vv = p.bias_v[row];
+    if (p.h.decoupled) wv *= (1.f - p.h.lr * p.h.weight_decay);
+    else gb = fmaf(p.h.weight_decay, wv, gb);
+    mm = fmaf(p.h.beta1, mm, (1.f - p.h.beta1) * gb);
+    vv = fmaf(p.h.beta2, vv, (1.f - p.h.beta2) * gb * gb);
+    wv -= (p.h.lr / p.h.bc1) * (mm / (sqrtf(vv) * rsqrtf(p.h.bc2) + p.h.eps));
+    p.bias_m[row] = mm; p.bias_v[row] = vv;
+    if (sizeof(WT) == 2) *reinterpret_cast<__nv_bfloat16*>(bp) = to_bf16(wv, p.h.sr_seed, 0x9000000000ULL + row);
+    else *reinterpret_cast<float*>(bp) = wv;
+  }
+}
+
 // ------------------------------------------------------------------ dense Adam for the small tensors
 template <typename WT>
 __global__ void __launch_bounds__(256) dense_adam_kernel(WT* __restrict__ w, float* __restrict__ m, float* __restrict__ v,
@@ -870,6 +955,48 @@ struct CltDecAdamArgs {
   int* status;  // when given, untied decoders use the bulk-copy pipeline (its bounded waits report here)
 };
 
+// Launch geometry of the bulk-copy row pipeline (shared by the decoder and the encoder update).
+static int bulk_rows_adam_geometry(int d, bool weights_bf16, int* ept_out, int* gthreads_out, int* stage_bytes_out, size_t* smem_out) {
+  const int ept = d <= 1024 ? 4 : 8;  // elements per consumer thread: more, shorter threads where the row allows
+  const int gthreads = ((d / ept + 31) / 32) * 32;
+  const size_t wsz = weights_bf16 ? 2 : 4;
+  const int stage_bytes = int(((64 + size_t(d) * (wsz + 8 + 2 * kAdamSlots)) + 127) / 128 * 128);
+  const size_t smem = size_t(kAdamStages) * stage_bytes + sizeof(AdamBulkShared) + 256;
+  *ept_out = ept; *gthreads_out = gthreads; *stage_bytes_out = stage_bytes; *smem_out = smem;
+  return (d % 8 == 0 && gthreads <= 256 && smem <= 200 * 1024) ? 1 : 0;
+}
+static bool bulk_rows_adam_fits(int d, int weights_bf16) {
+  int ept, gthreads, stage_bytes;
+  size_t smem;
+  return bulk_rows_adam_geometry(d, weights_bf16 != 0, &ept, &gthreads, &stage_bytes, &smem) != 0;
+}
+static int launch_rows_adam_bulk(const DecAdamParams& p, bool weights_bf16, bool sr, int num_sms, int* status, cudaStream_t st) {
+  int ept, gthreads, stage_bytes;
+  size_t smem;
+  if (!bulk_rows_adam_geometry(p.d, weights_bf16, &ept, &gthreads, &stage_bytes, &smem)) return -1;
+  int per_sm = int((227 * 1024) / (smem + 1024));
+  const int by_threads = 2048 / (gthreads + 32);
+  per_sm = per_sm > by_threads ? by_threads : per_sm;
+  per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
+  int bgrid = num_sms * per_sm;
+  if (bgrid > p.F_pitch) bgrid = p.F_pitch;
+  auto launch = [&](auto kern, int which) -> int {
+    static size_t attr_set[6] = {0, 0, 0, 0, 0, 0};
+    if (attr_set[which] < smem) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
+      attr_set[which] = smem;
+    }
+    kern<<<bgrid, gthreads + 32, smem, st>>>(p, gthreads, stage_bytes, status);
+    return 0;
+  };
+  if (ept == 4) {
+    if (weights_bf16) return sr ? launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, true, 4>, 0) : launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, false, 4>, 1);
+    return launch(decoder_rows_adam_bulk_kernel<float, false, 4>, 2);
+  }
+  if (weights_bf16) return sr ? launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, true, 8>, 3) : launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, false, 8>, 4);
+  return launch(decoder_rows_adam_bulk_kernel<float, false, 8>, 5);
+}
+
 extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st) {
   if (a->d % 8 != 0 || a->ntensors > kMaxLayersA) return -1;
   DecAdamParams p;
@@ -887,28 +1014,8 @@ extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaS
   p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale; p.dgrad_row0 = a->dgrad_row0; p.h = to_hyper(a->h);
   if (acc == 0) return 0;
   const int grid = num_sms * 8;
-  const int gthreads = ((a->d / 8 + 31) / 32) * 32;
-  const size_t wsz = a->weights_bf16 ? 2 : 4;
-  const int stage_bytes = int(((64 + size_t(a->d) * (wsz + 8 + 2 * kAdamSlots)) + 127) / 128 * 128);
-  const size_t smem = size_t(kAdamStages) * stage_bytes + sizeof(AdamBulkShared) + 256;
-  if (a->tying == 0 && a->status != nullptr && gthreads <= 256 && smem <= 200 * 1024 && acc * a->d < (1LL << 62)) {
-    const bool sr = a->h.sr_seed != 0;
-    int per_sm = int((227 * 1024) / (smem + 1024));
-    per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
-    int bgrid = num_sms * per_sm;
-    if (bgrid > a->F_pitch) bgrid = a->F_pitch;
-    auto launch = [&](auto kern, int which) -> int {
-      static size_t attr_set[3] = {0, 0, 0};
-      if (attr_set[which] < smem) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
-        attr_set[which] = smem;
-      }
-      kern<<<bgrid, gthreads + 32, smem, st>>>(p, gthreads, stage_bytes, a->status);
-      return 0;
-    };
-    int rc;
-    if (a->weights_bf16) rc = sr ? launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, true>, 0) : launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, false>, 1);
-    else rc = launch(decoder_rows_adam_bulk_kernel<float, false>, 2);
+  if (a->tying == 0 && a->status != nullptr && bulk_rows_adam_fits(a->d, a->weights_bf16) && acc * a->d < (1LL << 62)) {
+    const int rc = launch_rows_adam_bulk(p, a->weights_bf16 != 0, a->h.sr_seed != 0, num_sms, a->status, st);
     if (rc != 0) return rc;
   } else if (a->tying == 0) {
     const bool sr = a->h.sr_seed != 0;
@@ -932,6 +1039,7 @@ struct CltEncAdamArgs {
   const int* feat_off; const int* fcsr_tok; const float* delta; const void* x;
   const float* dense_grad; const float* dense_bias_grad;
   CltAdamHyper h;
+  int* status;  // when given, the weight rows go through the bulk-copy pipeline
 };
 
 extern "C" int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaStream_t st) {
@@ -942,7 +1050,31 @@ extern "C" int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaS
   p.feat_off = a->feat_off; p.fcsr_tok = a->fcsr_tok; p.delta = a->delta; p.x = static_cast<const __nv_bfloat16*>(a->x);
   p.dense_grad = a->dense_grad; p.dense_bias_grad = a->dense_bias_grad; p.h = to_hyper(a->h);
   const int grid = num_sms * 8;
-  if (a->weights_bf16) encoder_rows_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  if (a->status != nullptr && a->L <= kMaxLayersA && bulk_rows_adam_fits(a->d, a->weights_bf16)) {
+    // the encoder is the one-row-per-feature case of the row pipeline: layer l is "tensor" l with R = 1, the
+    // layer inputs play the gradient seed and delta the activation
+    DecAdamParams q;
+    const size_t wsz = a->weights_bf16 ? 2 : 4;
+    const long long per_layer = 1LL * a->F_pitch * a->d;
+    for (int i = 0; i < kMaxLayersA; ++i) {
+      const int l = i < a->L ? i : 0;
+      q.w[i] = static_cast<char*>(a->w) + size_t(l) * per_layer * wsz;
+      q.m[i] = a->m + l * per_layer; q.v[i] = a->v + l * per_layer; q.rows[i] = 1;
+      q.row_start[i] = 1LL * (i < a->L ? i : a->L) * a->F_pitch;
+    }
+    q.row_start[kMaxLayersA] = 1LL * a->L * a->F_pitch;
+    q.ntensors = a->L; q.L = a->L; q.B = a->B; q.d = a->d; q.F_pitch = a->F_pitch; q.tying = 0;
+    q.feat_off = a->feat_off; q.fcsr_tok = a->fcsr_tok; q.fcsr_val = a->delta; q.gs = p.x;
+    q.grad_a = nullptr; q.pen_coef = nullptr; q.norm2_out = nullptr; q.feat_offset = nullptr; q.feat_scale = nullptr;
+    q.dgrad_row0 = a->dense_grad; q.h = p.h;
+    const int rc = launch_rows_adam_bulk(q, a->weights_bf16 != 0, a->h.sr_seed != 0, num_sms, a->status, st);
+    if (rc != 0) return rc;
+    if (p.bias != nullptr) {
+      const int bgrid = int((1LL * a->L * a->F_pitch + 255) / 256);
+      if (a->weights_bf16) encoder_bias_adam_kernel<__nv_bfloat16><<<bgrid, 256, 0, st>>>(p);
+      else encoder_bias_adam_kernel<float><<<bgrid, 256, 0, st>>>(p);
+    }
+  } else if (a->weights_bf16) encoder_rows_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
   else encoder_rows_adam_kernel<float><<<grid, 256, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -111,6 +111,7 @@ struct CltEncAdamArgs {
   const int* feat_off; const int* fcsr_tok; const float* delta; const void* x;
   const float* dense_grad; const float* dense_bias_grad;
   CltAdamHyper h;
+  int* status;
 };
 int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaStream_t st);
 int clt_dense_adam(void* w, float* m, float* v, const float* grad, long long n, int weights_bf16, const CltAdamHyper* h, cudaStream_t st);
@@ -360,7 +361,7 @@ void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vect
 
 void encoder_rows_adam(Tensor& w, Tensor& m, Tensor& v, Tensor& bias, Tensor& bias_m, Tensor& bias_v, const Tensor& feat_off,
                        const Tensor& fcsr_tok, const Tensor& delta, const Tensor& x, const OptTensor& dense_grad,
-                       const OptTensor& dense_bias_grad, const std::vector<double>& hyper) {
+                       const OptTensor& dense_bias_grad, const std::vector<double>& hyper, const OptTensor& status) {
   const bool bf16 = w.scalar_type() == at::kBFloat16;
   need(w, bf16 ? at::kBFloat16 : at::kFloat, "w"); need(m, at::kFloat, "m"); need(v, at::kFloat, "v");
   need(bias, bf16 ? at::kBFloat16 : at::kFloat, "bias"); need(bias_m, at::kFloat, "bias_m"); need(bias_v, at::kFloat, "bias_v");
@@ -373,6 +374,7 @@ void encoder_rows_adam(Tensor& w, Tensor& m, Tensor& v, Tensor& bias, Tensor& bi
   a.feat_off = feat_off.data_ptr<int>(); a.fcsr_tok = fcsr_tok.data_ptr<int>(); a.delta = delta.data_ptr<float>(); a.x = x.data_ptr();
   a.dense_grad = opt_ptr<const float>(dense_grad); a.dense_bias_grad = opt_ptr<const float>(dense_bias_grad);
   a.h = hyper_from(hyper);
+  a.status = opt_ptr<int>(status);
   c10::cuda::CUDAGuard guard(w.device());
   check(clt_encoder_rows_adam(&a, num_sms(), cur_stream()), "encoder_rows_adam");
 }

@@ -199,8 +199,8 @@ struct DecodeBulkShared {
 
 template <int TPG>
 __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, int gthreads, int stage_bytes, int* status) {
-  extern __shared__ uint8_t smem_raw_dec[];
-  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_dec) + 127) & ~uintptr_t(127));
+  extern __shared__ __align__(128) uint8_t smem_raw_dec[];  // bulk copies need 16-byte alignment only
+  uint8_t* ring = smem_raw_dec;
   DecodeBulkShared* sh = reinterpret_cast<DecodeBulkShared*>(ring + size_t(kDecodeStages) * stage_bytes);
   const int tok = blockIdx.x;
   const int nconsumer = kGroups * gthreads;

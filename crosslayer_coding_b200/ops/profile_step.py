@@ -1,0 +1,101 @@
+"""Run a few fused BatchTopK training steps on synthetic data; the profiler range covers exactly one step.
+
+Usage (one GPU)::
+
+    python -m crosslayer_coding_b200.ops.profile_step --case full          # GPT-2-small shape, F=24576, k=200
+    python -m crosslayer_coding_b200.ops.profile_step --case small         # same layers, F=4096, k=33
+    python -m crosslayer_coding_b200.ops.profile_step --time               # CUDA-event timing per kernel group
+
+Under Nsight Compute pass ``--profile-from-start off`` so that only the step between
+``cudaProfilerStart`` and ``cudaProfilerStop`` is captured (warm-up steps run outside the range).
+``--time`` prints a JSON line with CUDA-event timings (best of five after warm-up) of the encoder GEMM,
+the library GEMM of the same shape, the selection stage, the decode+loss stage and the whole step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+CASES = {
+    # name: (layers, d_model, features per layer, batch tokens, k)
+    "full": (12, 768, 24576, 4096, 200),
+    "small": (12, 768, 4096, 4096, 33),
+    "tiny": (4, 256, 2048, 1024, 16),
+}
+
+
+def build(case: str, device: torch.device):
+    from .. import CLTConfig, CrossLayerTranscoder, TrainingConfig
+    from ..training.fused_engine import FusedBatchTopKEngine
+
+    L, d, F, B, k = CASES[case]
+    torch.manual_seed(0)
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="batchtopk", batchtopk_k=k, clt_dtype="bfloat16")
+    model = CrossLayerTranscoder(cfg, device=device)
+    tc = TrainingConfig(learning_rate=1e-4, training_steps=1000, activation_path="unused", precision="bf16",
+                        sparsity_lambda=0.0, preactivation_coef=0.0)
+    eng = FusedBatchTopKEngine(model, tc, B)
+    X = torch.randn(L, B, d, device=device).bfloat16()
+    Y = torch.randn(L, B, d, device=device).bfloat16()
+    return model, eng, X, Y
+
+
+def _best_of(fn, n: int = 5) -> float:
+    fn()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+    ev[0].record()
+    for i in range(n):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    return min(ev[i].elapsed_time(ev[i + 1]) for i in range(n))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--case", choices=sorted(CASES), default="full")
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--time", action="store_true", help="print CUDA-event timings instead of marking a profiler range")
+    args = ap.parse_args()
+    dev = torch.device("cuda:0")
+    model, eng, X, Y = build(args.case, dev)
+    L, d, F, B, k = CASES[args.case]
+    for s in range(args.warmup):
+        eng.train_step(X, Y, s, 1e-4)
+    torch.cuda.synchronize()
+    if args.time:
+        e = eng.ext
+        step = [args.warmup]
+
+        def full():
+            eng.train_step(X, Y, step[0], 1e-4)
+            step[0] += 1
+
+        res = {
+            "case": args.case,
+            "encoder_gemm_ms": _best_of(lambda: e.encoder_gemm(X, model.enc_weight.data, model.enc_bias.data, eng.preact, eng.status)),
+            "library_bmm_ms": _best_of(lambda: torch.bmm(X, model.enc_weight.data.transpose(1, 2))),
+            "encode_select_ms": _best_of(lambda: eng.encode_select(X)),
+            "decode_loss_ms": _best_of(lambda: eng.decode_loss(Y)),
+            "train_step_ms": _best_of(full, 6),
+        }
+        flops = 2.0 * L * B * F * d
+        res["encoder_gemm_tflops"] = flops / res["encoder_gemm_ms"] / 1e9
+        res["library_bmm_tflops"] = flops / res["library_bmm_ms"] / 1e9
+        res["tokens_per_s"] = B / res["train_step_ms"] * 1e3
+        eng.check_status()
+        print(json.dumps(res))
+        return
+    torch.cuda.profiler.start()
+    eng.train_step(X, Y, args.warmup, 1e-4)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    eng.check_status()
+    print(json.dumps({"case": args.case, "entries": int(eng.ctl[3]), "candidates": int(eng.ctl[4]), "fallback": int(eng.ctl[10])}))
+
+
+if __name__ == "__main__":
+    main()

@@ -442,7 +442,7 @@ class FusedBatchTopKEngine:
         self.norms_valid = True
         e.dense_adam(m.dec_bias.data, self.decb_m, self.decb_v, bias_grad, self._hyper(lr, c_g))
         e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v,
-                            self.feat_off, self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, self._hyper(lr, 1.0))
+                            self.feat_off, self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, self._hyper(lr, 1.0), self.status)
         e.dead_counter_update(self.dead_counter, self.fired)
         self.kernel_launches += 5 + (1 if use_pen else 0)  # gs_colsum, decoder/encoder Adam, dense Adam, dead counters
         m.invalidate_decoder_norms()
