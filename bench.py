@@ -195,7 +195,12 @@ def run_ours(args, world, rank, local):
         optimizer="adamw", lr_scheduler="linear", eval_interval=10 ** 9, checkpoint_interval=10 ** 9, log_interval=10 ** 9,
         engine="fused",
     )
-    store = InMemoryActivationStore(host, dev, loop=True, prefetch=2)
+    shard_group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        shard_group = dist.group.WORLD  # each rank copies 1/W of a batch over PCIe, the rest arrives over NVLink
+    store = InMemoryActivationStore(host, dev, loop=True, prefetch=2, shard_group=shard_group)
     store.mean_tg = {l: mean_tg[l].to(dev) for l in range(L)}
     store.std_tg = {l: (std_tg[l] + 1e-6).to(dev) for l in range(L)}
     log_dir = tempfile.mkdtemp(prefix="clt_bench_")
@@ -253,7 +258,10 @@ def run_ours(args, world, rank, local):
         },
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
-                "h2d_bytes_per_step": int(store.h2d_bytes_per_batch), "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": int(store.h2d_bytes_per_batch), "d2h_bytes_per_step": 4 * world,
+                "h2d_bytes_per_step_per_rank": int(store.h2d_bytes_per_rank),
+                "staging": "pinned host ring -> side-stream copy of this rank's 1/W token rows -> NVLink all-gather" if world > 1
+                else "pinned host ring -> side-stream copy"},
         "gpu_launches": int(launches),
         "final_loss": losses[-1] if losses else None,
         "impl": "ours",

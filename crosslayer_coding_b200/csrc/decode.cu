@@ -105,7 +105,9 @@ constexpr int kGroups = 4;  // warp groups per token; group g owns targets t wit
 // consecutive elements of d (one 16-byte load per decoder row).
 template <int TPG>
 __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int gthreads) {
-  const int tok = blockIdx.x;
+  // Tensor-parallel push: rank r starts with the tokens owned by rank r + 1, so that at any moment the ranks
+  // store into different owners instead of all into the same one.
+  const int tok = p.mode == 2 ? int((blockIdx.x + 1LL * ((p.rank + 1) % p.world) * p.rows_per_rank) % p.B) : int(blockIdx.x);
   const int g = threadIdx.x / gthreads;
   const int gt = threadIdx.x - g * gthreads;
   const int e0 = gt * 8;
@@ -202,7 +204,9 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   extern __shared__ __align__(128) uint8_t smem_raw_dec[];  // bulk copies need 16-byte alignment only
   uint8_t* ring = smem_raw_dec;
   DecodeBulkShared* sh = reinterpret_cast<DecodeBulkShared*>(ring + size_t(kDecodeStages) * stage_bytes);
-  const int tok = blockIdx.x;
+  // Tensor-parallel push: rank r starts with the tokens owned by rank r + 1, so that at any moment the ranks
+  // store into different owners instead of all into the same one.
+  const int tok = p.mode == 2 ? int((blockIdx.x + 1LL * ((p.rank + 1) % p.world) * p.rows_per_rank) % p.B) : int(blockIdx.x);
   const int nconsumer = kGroups * gthreads;
   const bool is_producer = int(threadIdx.x) >= nconsumer;
   const int L = p.L, d = p.d;

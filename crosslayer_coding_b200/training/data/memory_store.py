@@ -21,8 +21,11 @@ class InMemoryActivationStore(BaseActivationStore):
         device,
         loop: bool = True,
         prefetch: int = 2,
+        shard_group=None,
     ):
-        """``pool``: ``[N, 2, L, B, d]`` host tensor (inputs at index 0, targets at 1), already normalised."""
+        """``pool``: ``[N, 2, L, B, d]`` host tensor (inputs at index 0, targets at 1), already normalised.
+        ``shard_group``: tensor-parallel group; each rank then copies ``1/W`` of every batch host->device and
+        the rest arrives over NVLink (see ``DeviceStager``)."""
         assert pool.dim() == 5 and pool.shape[1] == 2, "pool must be [N, 2, L, B, d]"
         self.device = torch.device(device)
         self.pool = pool.pin_memory() if (self.device.type == "cuda" and not pool.is_pinned()) else pool
@@ -34,13 +37,15 @@ class InMemoryActivationStore(BaseActivationStore):
         self.apply_normalization = False
         self.mean_tg: Dict[int, torch.Tensor] = {}
         self.std_tg: Dict[int, torch.Tensor] = {}
-        self.stager = DeviceStager(tuple(pool.shape[1:]), pool.dtype, self.device, depth=max(2, prefetch + 1))
+        self.stager = DeviceStager(tuple(pool.shape[1:]), pool.dtype, self.device, depth=max(2, prefetch + 1),
+                                   shard_group=shard_group, row_dim=2)
         self.cursor = 0
         self.epoch = 0
         self._inflight = []  # (slot, pool index)
         self._last_slot: Optional[int] = None
         self.prefetch = max(1, prefetch) if self.device.type == "cuda" else 1
-        self.h2d_bytes_per_batch = self.stager.bytes_per_batch
+        self.h2d_bytes_per_batch = self.stager.bytes_per_batch          # whole job (sum over ranks)
+        self.h2d_bytes_per_rank = self.stager.h2d_bytes_per_rank
 
     def _submit_next(self) -> bool:
         if self.cursor >= self.num_batches:

@@ -5,6 +5,12 @@ The reference store moves every (layer, chunk) slice with a synchronous pageable
 buffer ``[2, L, B, d]`` (inputs, targets), copied with a single ``cudaMemcpyAsync`` on a dedicated
 stream into one of ``depth`` device slots, and handed to the training stream through an event, so the
 copy of batch ``i+1`` overlaps the step on batch ``i``.  On CPU the stager degenerates to a no-op.
+
+Sharded staging (tensor-parallel jobs): every rank needs the whole batch, but all ranks of a node pull it
+from the same host memory, and W full copies over PCIe cost W times the bytes of one.  With ``shard_group``
+each rank copies only its ``1/W`` slice of the token rows host->device and the slices are all-gathered over
+NVLink on the staging stream (a communicator of its own, so the gather never interleaves with the training
+step's collectives), followed by one device-side re-layout into ``[..., B, d]``.
 """
 from __future__ import annotations
 
@@ -14,7 +20,8 @@ import torch
 
 
 class DeviceStager:
-    def __init__(self, shape: Tuple[int, ...], dtype: torch.dtype, device: torch.device, depth: int = 3):
+    def __init__(self, shape: Tuple[int, ...], dtype: torch.dtype, device: torch.device, depth: int = 3,
+                 shard_group=None, row_dim: int = 2):
         self.device = torch.device(device)
         self.cuda = self.device.type == "cuda"
         self.depth = max(2, depth)
@@ -27,12 +34,39 @@ class DeviceStager:
             self.stream = torch.cuda.Stream(device=self.device)
             self.copied: List[Optional[torch.cuda.Event]] = [None] * self.depth
             self.released: List[Optional[torch.cuda.Event]] = [None] * self.depth
+            self._init_shard(shard_group, row_dim)
         else:
             # CPU: the "device" slot is the host buffer itself; several slots so a producer thread never
             # overwrites a batch the consumer still holds
             self.host = [torch.empty(shape, dtype=dtype) for _ in range(self.depth)]
             self.dev = list(self.host)
         self._next = 0
+        if not self.cuda:
+            self.shard_world = 1
+
+    def _init_shard(self, shard_group, row_dim: int) -> None:
+        """Collective over ``shard_group``: creates the staging communicator and the gather buffers."""
+        import torch.distributed as dist
+
+        self.shard_world, self.shard_rank, self.gather_group = 1, 0, None
+        if shard_group is None or not dist.is_initialized() or dist.get_world_size(shard_group) <= 1:
+            return
+        W = dist.get_world_size(shard_group)
+        rows = self.shape[row_dim]
+        if rows % W != 0:
+            return
+        self.shard_world, self.shard_rank = W, dist.get_rank(shard_group)
+        self.gather_group = dist.new_group(ranks=dist.get_process_group_ranks(shard_group), backend="nccl")
+        self.row_dim = row_dim
+        self.outer = int(torch.Size(self.shape[:row_dim]).numel())
+        self.inner = int(torch.Size(self.shape[row_dim + 1:]).numel())
+        self.rows, self.rows_per_rank = rows, rows // W
+        self.piece = [torch.empty(self.outer, self.rows_per_rank, self.inner, dtype=self.dtype, device=self.device) for _ in range(self.depth)]
+        self.gathered = torch.empty(W, self.outer, self.rows_per_rank, self.inner, dtype=self.dtype, device=self.device)
+
+    @property
+    def h2d_bytes_per_rank(self) -> int:
+        return self.bytes_per_batch // max(1, getattr(self, "shard_world", 1))
 
     def host_slot(self) -> Tuple[int, torch.Tensor]:
         """Pinned buffer to fill for the next batch.  Blocks (host side) only until the copy that last
@@ -52,7 +86,20 @@ class DeviceStager:
         with torch.cuda.stream(self.stream):
             if self.released[slot] is not None:
                 self.stream.wait_event(self.released[slot])  # consumer is done with the old contents
-            self.dev[slot].copy_(self.host[slot] if src is None else src, non_blocking=True)
+            host = self.host[slot] if src is None else src
+            if self.shard_world == 1:
+                self.dev[slot].copy_(host, non_blocking=True)
+            else:
+                import torch.distributed as dist
+
+                # this rank's rows only: one contiguous copy per outer index (a strided pinned source would be
+                # made contiguous on the host first)
+                r0 = self.shard_rank * self.rows_per_rank
+                hv = host.view(self.outer, self.rows, self.inner)
+                for o in range(self.outer):
+                    self.piece[slot][o].copy_(hv[o, r0:r0 + self.rows_per_rank], non_blocking=True)
+                dist.all_gather_into_tensor(self.gathered, self.piece[slot], group=self.gather_group)
+                self.dev[slot].view(self.outer, self.shard_world, self.rows_per_rank, self.inner).copy_(self.gathered.permute(1, 0, 2, 3))
             ev = torch.cuda.Event()
             ev.record(self.stream)
             self.copied[slot] = ev

@@ -40,6 +40,8 @@ def test_tp_matches_single_gpu(tmp_path, world, features, lam):
     ref = _run(1, str(tmp_path / "w1.pt"), features, 29611, lam)
     got = _run(world, str(tmp_path / f"w{world}.pt"), features, 29613 + world, lam)
     assert got["entries"] == ref["entries"], (got["entries"], ref["entries"])
+    assert got["staging_ok"] and ref["staging_ok"], "sharded staging returned a different batch"
+    assert got["h2d_bytes_per_rank"] * world == got["h2d_bytes"]
     for a, b in zip(got["losses"], ref["losses"]):
         assert abs(a - b) < 2e-3 * max(1.0, abs(b)), (got["losses"], ref["losses"])
     for key, w_ref in ref["state"].items():

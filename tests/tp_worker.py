@@ -66,6 +66,20 @@ def main():
         entries.append(int(n))
     torch.cuda.synchronize()
     eng.check_status()
+    # sharded staging: every rank copies 1/W of each batch host->device, the rest arrives over NVLink
+    from crosslayer_coding_b200.training.data import InMemoryActivationStore
+
+    pool = torch.randn(4, 2, L, B, d, generator=torch.Generator().manual_seed(11)).bfloat16()
+    store = InMemoryActivationStore(pool, dev, loop=True, prefetch=2, shard_group=group)
+    staging_ok = True
+    for i in range(6):
+        inputs, targets = next(store)
+        got_x = torch.stack([inputs[l] for l in range(L)]).cpu()
+        got_y = torch.stack([targets[l] for l in range(L)]).cpu()
+        staging_ok = staging_ok and torch.equal(got_x, pool[i % 4, 0]) and torch.equal(got_y, pool[i % 4, 1])
+    flag = torch.tensor([1.0 if staging_ok else 0.0], device=dev)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     sd = {k: v.detach().float().cpu() for k, v in model.state_dict().items()}
     if world > 1:
         gathered = [None] * world
@@ -74,7 +88,8 @@ def main():
     else:
         merged = sd
     if rank == 0:
-        torch.save({"losses": losses, "entries": entries, "state": merged, "world": world}, args.out)
+        torch.save({"losses": losses, "entries": entries, "state": merged, "world": world, "staging_ok": bool(flag.item() == 1.0),
+                    "h2d_bytes_per_rank": store.h2d_bytes_per_rank, "h2d_bytes": store.h2d_bytes_per_batch}, args.out)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
