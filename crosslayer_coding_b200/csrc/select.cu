@@ -94,10 +94,16 @@ __device__ bool exchange_sum(const Exchange& ex, int round, uint32_t* vals, int 
 
 // ------------------------------------------------------------------ 1. column statistics
 // x: [L, B, ld] bf16.  Each thread owns 8 adjacent columns; blockDim = (32, 8): 8 row groups.
+// With gridDim.z > 1 (narrow shards, where one CTA per column block would leave SMs idle) the rows are split
+// over blockIdx.z: the shifted sums are additive because every chunk shifts by the column's first row, so the
+// chunks add them into mean / rstd (zeroed by the launcher) and colstats_finalize_kernel converts in place.
 __global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ mean,
                                                          float* __restrict__ rstd, int B, int F, long long ld,
                                                          long long layer_stride) {
   const int l = blockIdx.y;
+  const int rows_per_z = (((B + int(gridDim.z) - 1) / int(gridDim.z)) + 31) / 32 * 32;
+  const int row_lo = int(blockIdx.z) * rows_per_z;
+  const int row_hi = min(B, row_lo + rows_per_z);
   const int cg = blockIdx.x * 32 + threadIdx.x;  // column group of 8
   const int c0 = cg * 8;
   __shared__ float red[8][32][17];
@@ -111,16 +117,16 @@ __global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __re
     const uint32_t w[4] = {v0.x, v0.y, v0.z, v0.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) { shift[2 * j] = bf16_lo(w[j]); shift[2 * j + 1] = bf16_hi(w[j]); }
-    for (int r0 = threadIdx.y; r0 < B; r0 += 32) {
+    for (int r0 = row_lo + threadIdx.y; r0 < row_hi; r0 += 32) {
       uint4 v[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {  // four independent loads in flight
         const int r = r0 + 8 * k;
-        v[k] = r < B ? __ldcs(reinterpret_cast<const uint4*>(base + 1LL * r * ld)) : v0;
+        v[k] = r < row_hi ? __ldcs(reinterpret_cast<const uint4*>(base + 1LL * r * ld)) : v0;
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        if (r0 + 8 * k >= B) break;
+        if (r0 + 8 * k >= row_hi) break;
         const uint32_t u[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -139,7 +145,10 @@ __global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __re
     for (int j = 0; j < 8; ++j) {
       float ss = 0.f, qq = 0.f;
       for (int y = 0; y < 8; ++y) { ss += red[y][threadIdx.x][j]; qq += red[y][threadIdx.x][8 + j]; }
-      if (c0 + j < F) {
+      if (c0 + j < F && gridDim.z > 1) {
+        atomicAdd(&mean[1LL * l * F + c0 + j], ss);
+        atomicAdd(&rstd[1LL * l * F + c0 + j], qq);
+      } else if (c0 + j < F) {
         const float mu = ss / float(B);
         float var = B > 1 ? (qq - ss * mu) / float(B - 1) : 0.f;
         var = fmaxf(var, 0.f);
@@ -148,6 +157,22 @@ __global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __re
       }
     }
   }
+}
+
+// mean / rstd hold the shifted sum and sum of squares (shift = the column's first row); convert in place.
+__global__ void __launch_bounds__(256) colstats_finalize_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ mean,
+                                                                  float* __restrict__ rstd, int B, int F, long long layer_stride,
+                                                                  long long n) {
+  const long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int l = int(i / F), c = int(i - 1LL * l * F);
+  const float shift = __bfloat162float(x[1LL * l * layer_stride + c]);
+  const float ss = mean[i], qq = rstd[i];
+  const float mu = ss / float(B);
+  float var = B > 1 ? (qq - ss * mu) / float(B - 1) : 0.f;
+  var = fmaxf(var, 0.f);
+  mean[i] = shift + mu;
+  rstd[i] = 1.f / (sqrtf(var) + 1e-6f);
 }
 
 // ------------------------------------------------------------------ 2. histogram of z keys
@@ -363,9 +388,15 @@ struct Lists {
 // moves the range for the next step so that about kPoolFactor * k_total elements fall inside it.
 constexpr double kPoolFactor = 1.75;
 
+// Bin width for a tracked range that starts at key_lo: the bins resolve z in [z_lo, max(2 z_lo, z_lo + 4)];
+// everything above lands in the top bin (kernels clamp the bin index), which is therefore never accepted as
+// the threshold bin.  Finer bins leave fewer candidates for the exact cut.
 __device__ __forceinline__ int shift_for(uint32_t key_lo) {
+  const float z_lo = key_to_float(key_lo);
+  const uint32_t key_hi = float_to_key(fmaxf(2.f * z_lo, z_lo + 4.f));
+  const uint32_t span = key_hi > key_lo ? key_hi - key_lo : 0xFFFFFFFFu - key_lo;
   int sh = 0;
-  while (((0xFFFFFFFFu - key_lo) >> sh) >= uint32_t(kHistBins)) ++sh;
+  while ((span >> sh) >= uint32_t(kHistBins - 1)) ++sh;
   return sh;
 }
 
@@ -406,8 +437,10 @@ __global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __re
     unsigned long long run = 0;
     for (int t = 1023; t >= 0; --t) { const unsigned long long c = part[t]; part[t] = run; run += c; }
     total = run;
+    // tracked ranges clamp large keys into the top bin: a cut inside it cannot be refined, take the full pass
+    const bool top_bin_cut = tracked && pass == 0 && (unsigned long long)vals[kHistBins - 1] >= (unsigned long long)k_total;
     const bool in_range = run >= (unsigned long long)k_total;
-    found = (in_range && !overflow) ? 1 : 0;
+    found = (in_range && !overflow && !top_bin_cut) ? 1 : 0;
     if (!found) {
       if (pass == 0) ctl[CTL_RETRY] = 1;
       else atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
@@ -468,34 +501,37 @@ __global__ void __launch_bounds__(256) classify_pool_kernel(Pool pool, long long
   unsigned long long* n_ent = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_ENTRIES);
   unsigned long long* n_cand = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_CAND);
   const long long n = min((long long)(*pool.count), pool.cap);
-  const int lane = threadIdx.x & 31;
-  const long long stride = 1LL * gridDim.x * blockDim.x;
-  const long long n_round = ((n + 31) / 32) * 32;  // whole warps stay together for the ballots
-  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n_round; i += stride) {
-    int kind = 0;  // 1: entry, 2: candidate
-    uint32_t key = 0;
-    if (i < n) {
-      key = pool.key[i];
-      const uint32_t bin = min((key - key_lo) >> shift, uint32_t(kHistBins - 1));
-      kind = bin > tbin ? 1 : (bin == tbin ? 2 : 0);
-    }
-    // one reservation per warp and list
-    const unsigned m_ent = __ballot_sync(0xFFFFFFFFu, kind == 1);
-    const unsigned m_cand = __ballot_sync(0xFFFFFFFFu, kind == 2);
-    unsigned long long base_ent = 0, base_cand = 0;
-    if (lane == 0) {
-      if (m_ent) base_ent = atomicAdd(n_ent, (unsigned long long)__popc(m_ent));
-      if (m_cand) base_cand = atomicAdd(n_cand, (unsigned long long)__popc(m_cand));
-    }
-    base_ent = __shfl_sync(0xFFFFFFFFu, base_ent, 0);
-    base_cand = __shfl_sync(0xFFFFFFFFu, base_cand, 0);
-    const unsigned below = (1u << lane) - 1u;
-    if (kind == 1) {
-      const long long q = (long long)base_ent + __popc(m_ent & below);
+  // every CTA owns one contiguous slice of the pool: count, reserve once per list, then place
+  const long long per_cta = (n + gridDim.x - 1) / gridDim.x;
+  const long long lo = blockIdx.x * per_cta, hi = min(n, lo + per_cta);
+  __shared__ int cnt[2];
+  __shared__ unsigned long long base[2];
+  if (threadIdx.x < 2) cnt[threadIdx.x] = 0;
+  __syncthreads();
+  int my_ent = 0, my_cand = 0;
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const uint32_t bin = min((pool.key[i] - key_lo) >> shift, uint32_t(kHistBins - 1));
+    my_ent += bin > tbin;
+    my_cand += bin == tbin;
+  }
+  if (my_ent) atomicAdd(&cnt[0], my_ent);
+  if (my_cand) atomicAdd(&cnt[1], my_cand);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    base[0] = cnt[0] ? atomicAdd(n_ent, (unsigned long long)cnt[0]) : 0ULL;
+    base[1] = cnt[1] ? atomicAdd(n_cand, (unsigned long long)cnt[1]) : 0ULL;
+    cnt[0] = 0; cnt[1] = 0;
+  }
+  __syncthreads();
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const uint32_t key = pool.key[i];
+    const uint32_t bin = min((key - key_lo) >> shift, uint32_t(kHistBins - 1));
+    if (bin > tbin) {
+      const long long q = (long long)base[0] + atomicAdd(&cnt[0], 1);
       if (q < o.ent_cap) { o.ent_tok[q] = pool.tok[i]; o.ent_col[q] = pool.col[i]; o.ent_val[q] = pool.val[i]; }
       else atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
-    } else if (kind == 2) {
-      const long long q = (long long)base_cand + __popc(m_cand & below);
+    } else if (bin == tbin) {
+      const long long q = (long long)base[1] + atomicAdd(&cnt[1], 1);
       if (q < o.cand_cap) { o.cand_key[q] = key; o.cand_tok[q] = pool.tok[i]; o.cand_col[q] = pool.col[i]; o.cand_val[q] = pool.val[i]; }
       else atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
     }
@@ -943,8 +979,20 @@ using namespace clt;
 extern "C" int clt_colstats(const void* x, float* mean, float* rstd, int L, int B, int F, long long ld, long long layer_stride,
                             cudaStream_t st) {
   if (F % 8 != 0 || ld % 8 != 0 || layer_stride % 8 != 0) return -1;
-  dim3 grid((F / 8 + 31) / 32, L), block(32, 8);
-  colstats_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16*>(x), mean, rstd, B, F, ld, layer_stride);
+  const int col_blocks = (F / 8 + 31) / 32;
+  int zsplit = 1;
+  while (1LL * col_blocks * L * zsplit < 592 && zsplit < 16 && B / (zsplit * 2) >= 128) zsplit *= 2;
+  dim3 grid(col_blocks, L, zsplit), block(32, 8);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  if (zsplit > 1) {
+    if (cudaMemsetAsync(mean, 0, sizeof(float) * size_t(L) * F, st) != cudaSuccess) return -5;
+    if (cudaMemsetAsync(rstd, 0, sizeof(float) * size_t(L) * F, st) != cudaSuccess) return -5;
+  }
+  colstats_kernel<<<grid, block, 0, st>>>(xp, mean, rstd, B, F, ld, layer_stride);
+  if (zsplit > 1) {
+    const long long n = 1LL * L * F;
+    colstats_finalize_kernel<<<int((n + 255) / 256), 256, 0, st>>>(xp, mean, rstd, B, F, layer_stride, n);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -1027,7 +1075,7 @@ extern "C" int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArg
     pool.count = a->hist + 2 * kHistBins;
     zhist_collect_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, a->col_pitch, a->sel_state, a->hist, pool);
     find_bin_kernel<<<1, 1024, 0, st>>>(a->hist, a->k_total, a->ctl, ex, 0u, 0, 0, 0, a->sel_state, pool.count, pool.cap, a->status);
-    classify_pool_kernel<<<148, 256, 0, st>>>(pool, a->ctl, lists_of(a), a->status);
+    classify_pool_kernel<<<592, 256, 0, st>>>(pool, a->ctl, lists_of(a), a->status);
     // fallback, skipped inside the kernels unless the tracked range missed the cut or the pool overflowed
     zhist_kernel<<<grid, 256, 0, st>>>(x, a->mean, a->rstd, g, 0u, 19, a->hist + kHistBins, a->ctl, 1);
     find_bin_kernel<<<1, 1024, 0, st>>>(a->hist + kHistBins, a->k_total, a->ctl, ex, 0u, 19, 1, 1, a->sel_state, nullptr, 0, a->status);

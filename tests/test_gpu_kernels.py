@@ -42,10 +42,10 @@ def test_encoder_gemm_matches_fp32(ext, L, M, N, K):
     assert rel < 4e-3, rel
 
 
-def test_colstats(ext):
+@pytest.mark.parametrize("L,B,F", [(3, 257, 72), (2, 1030, 256)])  # the second shape takes the row-split path
+def test_colstats(ext, L, B, F):
     torch.manual_seed(1)
     dev = _dev()
-    L, B, F = 3, 257, 72
     x = (torch.randn(L, B, F, device=dev) * 2 + 5).bfloat16()
     mean = torch.empty(L, F, device=dev)
     rstd = torch.empty(L, F, device=dev)
