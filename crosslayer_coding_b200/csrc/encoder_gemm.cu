@@ -28,8 +28,45 @@ constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 // ring + 1024 B alignment slack + barriers/bias
-constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 1024 + 2048;
+constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 4 * 4096 + 1024 + 2048;  // ring + epilogue staging + slack + barriers
 }  // namespace gemm
+
+// Epilogue of one 32-row slab (one warp, lane = row): TMEM -> registers -> + bias -> bf16 -> shared staging
+// tile of 32 rows x 64 columns in the 128-byte-swizzled layout -> one TMA store per 64 columns.  Writing
+// full rows through TMA instead of 16 bytes per lane and row keeps the L1/shared data pipe, which the tensor
+// core's operand reads share, almost free.  `stage` is this warp's 4 KB buffer (1024-byte aligned).
+constexpr int kEpiCols = 64;
+constexpr uint32_t kEpiStageBytes = 32 * kEpiCols * 2;
+
+__device__ __forceinline__ void epilogue_slab(uint32_t taddr, const CUtensorMap* map_c, uint8_t* stage, const float* bias_s,
+                                              int bn, int n_base, int m_base, int l, int lane) {
+  for (int c = 0; c < bn / kEpiCols; ++c) {
+    uint32_t r0[32], r1[32];
+    tmem_ld_32x32(taddr + c * kEpiCols, r0);
+    tmem_ld_32x32(taddr + c * kEpiCols + 32, r1);
+    if (lane == 0) bulk_wait_read<0>();  // the previous store has read the staging tile
+    __syncwarp();
+    tmem_ld_wait();
+    const float4* b4 = reinterpret_cast<const float4*>(bias_s + c * kEpiCols);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {  // 16-byte chunk j of this lane's row: columns [8j, 8j + 8)
+      const uint32_t* r = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
+      const float4 ba = b4[2 * j], bb = b4[2 * j + 1];
+      uint4 q;
+      q.x = pack_bf16x2(__uint_as_float(r[0]) + ba.x, __uint_as_float(r[1]) + ba.y);
+      q.y = pack_bf16x2(__uint_as_float(r[2]) + ba.z, __uint_as_float(r[3]) + ba.w);
+      q.z = pack_bf16x2(__uint_as_float(r[4]) + bb.x, __uint_as_float(r[5]) + bb.y);
+      q.w = pack_bf16x2(__uint_as_float(r[6]) + bb.z, __uint_as_float(r[7]) + bb.w);
+      *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = q;
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_3d(map_c, stage, n_base + c * kEpiCols, m_base, l);
+      bulk_commit();
+    }
+  }
+}
 
 struct GemmShared {
   uint64_t full[gemm::STAGES];
@@ -39,18 +76,19 @@ struct GemmShared {
   uint32_t tmem_base;
   int abort_flag;
   int epi_ok;
-  float bias[gemm::BN];
+  alignas(16) float bias[gemm::BN];
 };
 
 __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)
 encoder_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ C,
+                    const __grid_constant__ CUtensorMap map_c, const __nv_bfloat16* __restrict__ bias,
                     int L, int M, int N, int K, long long ldc, long long layer_stride_c, int* __restrict__ status) {
   using namespace gemm;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  GemmShared* sh = reinterpret_cast<GemmShared*>(tiles + size_t(STAGES) * STAGE_BYTES);
+  uint8_t* epi_stage = tiles + size_t(STAGES) * STAGE_BYTES;  // four 4 KB staging tiles, 1024-byte aligned
+  GemmShared* sh = reinterpret_cast<GemmShared*>(epi_stage + 4 * kEpiStageBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -169,44 +207,198 @@ encoder_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       named_barrier_sync(1, 128);
       if (!sh->epi_ok) { ok = false; break; }
       tc_fence_after();
-      const int m = mt * BM + quarter * 32 + lane;
-      __nv_bfloat16* crow = C + 1LL * l * layer_stride_c + 1LL * m * ldc + 1LL * nt * BN;
+      const int m_base = mt * BM + quarter * 32;
       const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int n0 = nt * BN + c * 32;
-        if (m < M && n0 < N) {
-          uint32_t packed[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float v0 = __uint_as_float(r[2 * j]) + sh->bias[c * 32 + 2 * j];
-            const float v1 = __uint_as_float(r[2 * j + 1]) + sh->bias[c * 32 + 2 * j + 1];
-            packed[j] = pack_bf16x2(v0, v1);
-          }
-          if (n0 + 32 <= N) {
-            uint4* dst = reinterpret_cast<uint4*>(crow + c * 32);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) dst[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-          } else {
-            const __nv_bfloat16* pv = reinterpret_cast<const __nv_bfloat16*>(packed);
-            for (int j = 0; j < 32 && n0 + j < N; ++j) crow[c * 32 + j] = pv[j];
-          }
-        }
-      }
+      if (m_base < M) epilogue_slab(taddr, &map_c, epi_stage + (warp - 2) * kEpiStageBytes, sh->bias, min(BN, ((N - nt * BN + kEpiCols - 1) / kEpiCols) * kEpiCols), nt * BN, m_base, l, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
     }
   }
 
+  if (warp >= 2 && lane == 0) bulk_wait_all();  // output stores of this warp are complete
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && sh->abort_flag && status != nullptr) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+}
+
+// ------------------------------------------------------------------ CTA-pair variant (cta_group::2)
+// Two CTAs of a cluster work on one 256 x 256 tile: each loads its own 128 rows of A and one half (128 rows)
+// of the weight tile, the leader CTA issues tcgen05.mma with cta_group::2 (M = 256), which reads the operand
+// halves from both CTAs' shared memory and writes 128 accumulator rows into each CTA's TMEM.  Per CTA and
+// k-step this moves 32 KB from L2 instead of 48 KB for the same number of MMA cycles, and the ring holds six
+// stages instead of four.  No multicast loads: tcgen05.commit is the only multicast (barrier arrivals).
+//
+//   full[s]        leader only: armed by the leader's producer for the bytes of both CTAs
+//   empty[s]       both CTAs: commit (multicast) after the MMAs of the stage
+//   tmem_full[b]   both CTAs: commit (multicast) after the tile's last MMA
+//   tmem_empty[b]  leader only: 8 arrivals, four epilogue warps of each CTA
+namespace gemm2 {
+constexpr int BM = 128;       // rows per CTA; the pair covers 256
+constexpr int BN = 256;
+constexpr int BN_HALF = 128;  // weight rows loaded per CTA
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int UMMA_K = 16;
+constexpr uint32_t A_BYTES = BM * BK * 2;
+constexpr uint32_t B_BYTES = BN_HALF * BK * 2;
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 4 * 4096 + 1024 + 2048;
+}  // namespace gemm2
+
+struct GemmPairShared {
+  uint64_t full[gemm2::STAGES];
+  uint64_t empty[gemm2::STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int epi_ok;
+  alignas(16) float bias[gemm2::BN];
+};
+
+__global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
+encoder_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_c, const __nv_bfloat16* __restrict__ bias,
+                         int L, int M, int N, int K, long long ldc, long long layer_stride_c, int* __restrict__ status) {
+  using namespace gemm2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi_stage = tiles + size_t(STAGES) * STAGE_BYTES;
+  GemmPairShared* sh = reinterpret_cast<GemmPairShared*>(epi_stage + 4 * kEpiStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_kb = (K + BK - 1) / BK;
+  const long long total_tiles = 1LL * L * tiles_m * tiles_n;
+  volatile int* abort_flag = &sh->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sh->tmem_full[b], 1);
+      mbar_init(&sh->tmem_empty[b], 8);
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&sh->tmem_base, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long t = pair; t < total_tiles && ok; t += npairs) {
+        const int mt = int(t % tiles_m);
+        const int nt = int((t / tiles_m) % tiles_n);
+        const int l = int(t / (1LL * tiles_m * tiles_n));
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&sh->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          if (leader) mbar_expect_tx(&sh->full[s], 2 * STAGE_BYTES);
+          const uint32_t full_leader = mapa_shared(smem_u32(&sh->full[s]), 0);
+          uint8_t* a_dst = tiles + size_t(s) * STAGE_BYTES;
+          tma_load_3d_pair(a_dst, &map_a, full_leader, kb * BK, (mt * 2 + int(cta_rank)) * BM, l);
+          tma_load_3d_pair(a_dst + A_BYTES, &map_b, full_leader, kb * BK, nt * BN + int(cta_rank) * BN_HALF, l);
+        }
+      }
+      // Copies still in flight are counted on the leader's barriers, which the MMA thread consumes; a CTA
+      // that gave up waits below (cluster barrier) until its partner is done as well.
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN);
+      uint32_t it = 0;
+      uint32_t local_tile = 0;
+      bool ok = true;
+      for (long long t = pair; t < total_tiles && ok; t += npairs, ++local_tile) {
+        const uint32_t buf = local_tile & 1;
+        const uint32_t tph = (local_tile >> 1) & 1;
+        if (!mbar_wait(&sh->tmem_empty[buf], tph ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&sh->full[s], ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + size_t(s) * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+          const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
+          const uint64_t b_desc = umma_desc_kmajor_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_ss_pair(d_tmem, a_desc + uint64_t(k * 2), b_desc + uint64_t(k * 2), idesc, (kb | k) != 0);
+          tc_commit_pair(&sh->empty[s], 3);  // frees the stage in both CTAs
+        }
+        if (ok) tc_commit_pair(&sh->tmem_full[buf], 3);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs)
+    const int quarter = warp & 3;
+    const int etid = (warp - 2) * 32 + lane;
+    uint32_t local_tile = 0;
+    bool ok = true;
+    for (long long t = pair; t < total_tiles && ok; t += npairs, ++local_tile) {
+      const int mt = int(t % tiles_m);
+      const int nt = int((t / tiles_m) % tiles_n);
+      const int l = int(t / (1LL * tiles_m * tiles_n));
+      const uint32_t buf = local_tile & 1;
+      const uint32_t tph = (local_tile >> 1) & 1;
+      named_barrier_sync(1, 128);
+      for (int j = etid; j < BN; j += 128) {
+        const int n = nt * BN + j;
+        sh->bias[j] = (bias != nullptr && n < N) ? __bfloat162float(bias[1LL * l * N + n]) : 0.f;
+      }
+      if (etid == 0) sh->epi_ok = mbar_wait(&sh->tmem_full[buf], tph, abort_flag) ? 1 : 0;
+      named_barrier_sync(1, 128);
+      if (!sh->epi_ok) { ok = false; break; }
+      tc_fence_after();
+      const int m_base = (mt * 2 + int(cta_rank)) * BM + quarter * 32;
+      const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quarter * 32) << 16);
+      if (m_base < M) epilogue_slab(taddr, &map_c, epi_stage + (warp - 2) * kEpiStageBytes, sh->bias, min(BN, ((N - nt * BN + kEpiCols - 1) / kEpiCols) * kEpiCols), nt * BN, m_base, l, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->tmem_empty[buf]), 0));  // the leader's barrier
+    }
+  }
+
+  if (warp >= 2 && lane == 0) bulk_wait_all();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA retires (or frees TMEM) while the other may still use its memory
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && sh->abort_flag && status != nullptr) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
 }
@@ -250,8 +442,50 @@ extern "C" int clt_encoder_gemm(const void* A, const void* B, const void* bias, 
   using namespace clt;
   if (K % 8 != 0 || ldc % 8 != 0 || layer_stride_c % 8 != 0) return -1;  // 16-byte TMA strides / vector stores
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -2;
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_c;
   if (!make_kmajor_map(&map_a, A, L, M, K, K, 1LL * M * K, gemm::BM)) return -3;
+  // output map: [L, M, N] with 64-column x 32-row boxes (one epilogue slab store), clipped at M and N
+  if (!make_kmajor_map(&map_c, C, L, M, N, ldc, layer_stride_c, 32)) return -3;
+  // ---- CTA pairs when the problem has full 256-row tiles and the device can co-schedule clusters of two
+  static int pair_clusters = -1;  // co-resident clusters of two, probed once
+  if (pair_clusters < 0) {
+    pair_clusters = 0;
+    if (cudaFuncSetAttribute(encoder_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(gemm2::SMEM_BYTES)) == cudaSuccess) {
+      cudaLaunchConfig_t probe = {};
+      probe.gridDim = dim3(2 * num_sms);
+      probe.blockDim = dim3(gemm2::NUM_THREADS);
+      probe.dynamicSmemBytes = gemm2::SMEM_BYTES;
+      cudaLaunchAttribute pattr[1];
+      pattr[0].id = cudaLaunchAttributeClusterDimension;
+      pattr[0].val.clusterDim.x = 2; pattr[0].val.clusterDim.y = 1; pattr[0].val.clusterDim.z = 1;
+      probe.attrs = pattr;
+      probe.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, encoder_gemm_pair_kernel, &probe) == cudaSuccess && n > 0) pair_clusters = n;
+      else (void)cudaGetLastError();
+    } else {
+      (void)cudaGetLastError();
+    }
+  }
+  const long long pair_tiles = 1LL * L * ((M + 2 * gemm2::BM - 1) / (2 * gemm2::BM)) * ((N + gemm2::BN - 1) / gemm2::BN);
+  if (pair_clusters > 0 && M >= 2 * gemm2::BM && pair_tiles > 0) {
+    if (!make_kmajor_map(&map_b, B, L, N, K, K, 1LL * N * K, gemm2::BN_HALF)) return -3;
+    const int clusters = int(pair_tiles < pair_clusters ? pair_tiles : pair_clusters);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters);
+    cfg.blockDim = dim3(gemm2::NUM_THREADS);
+    cfg.dynamicSmemBytes = gemm2::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const __nv_bfloat16* bias_p = static_cast<const __nv_bfloat16*>(bias);
+    if (cudaLaunchKernelEx(&cfg, encoder_gemm_pair_kernel, map_a, map_b, map_c, bias_p, L, M, N, K, ldc, layer_stride_c, status) != cudaSuccess)
+      return -5;
+    return 0;
+  }
   if (!make_kmajor_map(&map_b, B, L, N, K, K, 1LL * N * K, gemm::BN)) return -3;
   static bool attr_set = false;
   if (!attr_set) {
@@ -262,6 +496,6 @@ extern "C" int clt_encoder_gemm(const void* A, const void* B, const void* bias, 
   if (tiles == 0) return 0;
   const int grid = int(tiles < num_sms ? tiles : num_sms);
   encoder_gemm_kernel<<<grid, gemm::NUM_THREADS, gemm::SMEM_BYTES, stream>>>(
-      map_a, map_b, static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(C), L, M, N, K, ldc, layer_stride_c, status);
+      map_a, map_b, map_c, static_cast<const __nv_bfloat16*>(bias), L, M, N, K, ldc, layer_stride_c, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
