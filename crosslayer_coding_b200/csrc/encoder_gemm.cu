@@ -12,6 +12,8 @@
 // bias and store bf16.  Tiles are ordered m-fastest so CTAs that run together share the weight tile in L2.
 // Every mbarrier wait is bounded; on a timeout the CTA records STATUS_WAIT_TIMEOUT, drains its copies,
 // frees its TMEM and returns.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace clt {
@@ -468,7 +470,9 @@ extern "C" int clt_encoder_gemm(const void* A, const void* B, const void* bias, 
     }
   }
   const long long pair_tiles = 1LL * L * ((M + 2 * gemm2::BM - 1) / (2 * gemm2::BM)) * ((N + gemm2::BN - 1) / gemm2::BN);
-  if (pair_clusters > 0 && M >= 2 * gemm2::BM && pair_tiles > 0) {
+  // CLT_GEMM_SINGLE_CTA=1 keeps the single-CTA 128x256 kernel for every shape (for comparisons)
+  static const bool force_single = [] { const char* e = getenv("CLT_GEMM_SINGLE_CTA"); return e != nullptr && e[0] == '1'; }();
+  if (pair_clusters > 0 && !force_single && M >= 2 * gemm2::BM && pair_tiles > 0) {
     if (!make_kmajor_map(&map_b, B, L, N, K, K, 1LL * N * K, gemm2::BN_HALF)) return -3;
     const int clusters = int(pair_tiles < pair_clusters ? pair_tiles : pair_clusters);
     cudaLaunchConfig_t cfg = {};
