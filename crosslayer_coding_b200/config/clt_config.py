@@ -173,6 +173,9 @@ class TrainingConfig:
     # Wrap around to a new epoch (seed + epoch) when the store is exhausted
     # instead of ending training early.
     auto_advance_epoch: bool = True
+    # Tensor-parallel jobs: seconds after which a rank that has not announced the next step is declared
+    # lost (host-side heartbeat through the job's store, checked before every launch).  None: off.
+    peer_health_timeout_s: Optional[float] = None
 
     def __post_init__(self) -> None:
         self.normalization_method = canonical_normalization(self.normalization_method)

@@ -354,8 +354,17 @@ class CLTTrainer:
         self._save_run_config()
         step = self.start_step
         last_parts = None
+        health = None
+        lost_peer = False
+        if self.world_size > 1 and tc.peer_health_timeout_s:
+            from ..parallel.health import HeartbeatMonitor
+
+            health = HeartbeatMonitor(dist.distributed_c10d._get_default_store(), self.rank, self.world_size,
+                                      timeout_s=float(tc.peer_health_timeout_s))
         try:
             for step in range(self.start_step, tc.training_steps):
+                if health is not None:
+                    health.ready(step)  # raises PeerLostError before anything of this step is launched
                 with self.profiler.timer("data_loading"):
                     try:
                         inputs, targets = self._next_batch()
@@ -384,9 +393,20 @@ class CLTTrainer:
         except KeyboardInterrupt:
             if self.rank == 0:
                 logger.warning("Interrupted at step %d; writing the final checkpoint", step)
+        except BaseException as exc:
+            if health is not None:
+                from ..parallel.health import PeerLostError
+
+                if not isinstance(exc, PeerLostError):
+                    health.leave(f"{type(exc).__name__} at step {step}")
+                # a collective with a lost rank would never complete: skip the final barrier and checkpoint
+                logger.error("Rank %d: stopping at step %d: %s", self.rank, step, exc)
+                lost_peer = True
+            raise
         finally:
-            pops.barrier(self.process_group)
-            self.save_checkpoint(step, final=True)
+            if not lost_peer:
+                pops.barrier(self.process_group)
+                self.save_checkpoint(step, final=True)
             if hasattr(self.activation_store, "close"):
                 self.activation_store.close()
             self.metric_logger._save_metrics_to_disk()
