@@ -45,6 +45,7 @@ struct CltSelectArgs {
   unsigned int* pool_key; int* pool_tok; int* pool_col; float* pool_val; long long pool_cap;
 };
 int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st);
+int clt_threshold_select(const CltSelectArgs* a, cudaStream_t st);
 
 struct CltCsrArgs {
   const int* ent_tok; const int* ent_col; const float* ent_val; long long ent_cap;
@@ -221,6 +222,26 @@ void batchtopk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, i
   const bool multi = fill_exchange(ex, world, rank, ex_data, ex_flags, slot_elems, seq);
   c10::cuda::CUDAGuard guard(x.device());
   check(clt_batchtopk_select(&a, multi ? &ex : nullptr, cur_stream()), "batchtopk_select");
+}
+
+// Entries with x >= theta[l, f] (JumpReLU; ReLU with theta = smallest positive bf16) as a (token, column, value) list.
+void threshold_select(const Tensor& x, const Tensor& theta, int64_t f_valid, int64_t col_pitch, Tensor& ctl, Tensor& ent_tok,
+                      Tensor& ent_col, Tensor& ent_val, Tensor& status) {
+  need(x, at::kBFloat16, "x"); need(theta, at::kFloat, "theta"); need(ctl, at::kLong, "ctl"); need(status, at::kInt, "status");
+  need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
+  TORCH_CHECK(x.dim() == 3 && theta.dim() == 2 && theta.size(0) == x.size(0) && theta.size(1) >= f_valid, "theta must be [L, >= F]");
+  TORCH_CHECK(ctl.numel() >= 16, "ctl needs 16 elements");
+  CltSelectArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.x = x.data_ptr(); a.rstd = theta.data_ptr<float>();
+  a.L = x.size(0); a.B = x.size(1); a.F = int(f_valid); a.stat_pitch = int(theta.size(1));
+  a.ld = x.size(2); a.layer_stride = 1LL * x.size(1) * x.size(2);
+  a.col_pitch = int(col_pitch);
+  a.ctl = reinterpret_cast<long long*>(ctl.data_ptr<int64_t>());
+  a.ent_tok = ent_tok.data_ptr<int>(); a.ent_col = ent_col.data_ptr<int>(); a.ent_val = ent_val.data_ptr<float>(); a.ent_cap = ent_tok.numel();
+  a.status = status.data_ptr<int>();
+  c10::cuda::CUDAGuard guard(x.device());
+  check(clt_threshold_select(&a, cur_stream()), "threshold_select");
 }
 
 void build_csr(const Tensor& ent_tok, const Tensor& ent_col, const Tensor& ent_val, const Tensor& ctl, int64_t num_tokens, int64_t num_cols,
@@ -414,6 +435,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("encoder_gemm", &encoder_gemm);
   m.def("colstats", &colstats);
   m.def("batchtopk_select", &batchtopk_select);
+  m.def("threshold_select", &threshold_select);
   m.def("build_csr", &build_csr);
   m.def("dead_counter_update", &dead_counter_update);
   m.def("sparse_decode", &sparse_decode);

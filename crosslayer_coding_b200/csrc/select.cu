@@ -490,6 +490,90 @@ __global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __re
   }
 }
 
+// ------------------------------------------------------------------ 2c. per-feature threshold selection
+// JumpReLU (x >= theta_f) and ReLU (theta = smallest positive bf16) as a sparse selection: the same two-phase
+// scan as above with the feature's own threshold as the filter; emits the (token, column, value) list that the
+// CSR build and the sparse decode consume.  Meant for sparse activations: when a CTA queues more groups than
+// its queue holds, or the list does not fit, the status word reports STATUS_CAPACITY and the caller falls back
+// to the dense path.
+__global__ void __launch_bounds__(256) threshold_collect_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ theta,
+                                                                  ScanGeom g, int col_pitch, long long* __restrict__ ctl,
+                                                                  Lists o, int* __restrict__ status) {
+  __shared__ uint32_t s_queue[4 * kHitQueue];
+  __shared__ int s_tok[2 * kPoolStage];
+  __shared__ int s_col[2 * kPoolStage];
+  __shared__ float s_val[2 * kPoolStage];
+  __shared__ int s_q, s_n;
+  __shared__ unsigned long long s_base;
+  constexpr int kQueue = 4 * kHitQueue, kStage = 2 * kPoolStage;
+  if (threadIdx.x == 0) { s_q = 0; s_n = 0; }
+  __syncthreads();
+  const int l = blockIdx.z;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int r0 = blockIdx.y * g.rows_per_block;
+  const int r1 = min(g.B, r0 + g.rows_per_block);
+  unsigned long long* n_ent = reinterpret_cast<unsigned long long*>(ctl + CTL_NUM_ENTRIES);
+  if (c0 < g.F) {
+    uint32_t thr2[4];
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      float t[2];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) t[q] = c0 + j + q < g.F ? __ldg(theta + 1LL * l * g.sp + c0 + j + q) : INFINITY;
+      const __nv_bfloat162 pk = __halves2bfloat162(__float2bfloat16_rd(t[0]), __float2bfloat16_rd(t[1]));
+      thr2[j >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+    }
+    const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+    for (int rb = r0; rb < r1; rb += 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int r = min(rb + k, r1 - 1);
+        v[k] = __ldcs(reinterpret_cast<const uint4*>(base + 1LL * r * g.ld));
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t hit = bf16x2_ge_mask(v[k].x, thr2[0]) | bf16x2_ge_mask(v[k].y, thr2[1]) |
+                             bf16x2_ge_mask(v[k].z, thr2[2]) | bf16x2_ge_mask(v[k].w, thr2[3]);
+        if (hit != 0 && rb + k < r1) {
+          const int slot = atomicAdd(&s_q, 1);
+          if (slot < kQueue) s_queue[slot] = (uint32_t(rb + k - r0) << 8) | threadIdx.x;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int nq_all = s_q;
+  if (nq_all > kQueue && threadIdx.x == 0) atomicCAS(status, STATUS_OK, STATUS_CAPACITY);  // too dense for this path
+  const int nq = min(nq_all, kQueue);
+  for (int e0 = 0; e0 < nq * 8; e0 += kStage) {
+    // exact test, staged in rounds so that any number of queued groups fits the staging arrays
+    const int e1 = min(nq * 8, e0 + kStage);
+    for (int e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+      const uint32_t item = s_queue[e >> 3];
+      const int r = r0 + int(item >> 8);
+      const int c = (blockIdx.x * blockDim.x + int(item & 255u)) * 8 + (e & 7);
+      if (c >= g.F) continue;
+      const float xv = __bfloat162float(x[1LL * l * g.layer_stride + 1LL * r * g.ld + c]);
+      if (!(xv >= __ldg(theta + 1LL * l * g.sp + c))) continue;
+      const int slot = atomicAdd(&s_n, 1);
+      s_tok[slot] = r; s_col[slot] = l * col_pitch + c; s_val[slot] = xv;
+    }
+    __syncthreads();
+    const int staged = s_n;
+    if (threadIdx.x == 0) s_base = staged ? atomicAdd(n_ent, (unsigned long long)staged) : 0ULL;
+    __syncthreads();
+    for (int i = threadIdx.x; i < staged; i += blockDim.x) {
+      const long long q = (long long)s_base + i;
+      if (q < o.ent_cap) { o.ent_tok[q] = s_tok[i]; o.ent_col[q] = s_col[i]; o.ent_val[q] = s_val[i]; }
+      else atomicCAS(status, STATUS_OK, STATUS_CAPACITY);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_n = 0;
+    __syncthreads();
+  }
+}
+
 // ------------------------------------------------------------------ 3b. split the pool at the threshold bin
 // Runs instead of the full compaction pass when the tracked range contained the cut.
 __global__ void __launch_bounds__(256) classify_pool_kernel(Pool pool, long long* __restrict__ ctl, Lists o,
@@ -1091,6 +1175,17 @@ extern "C" int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArg
   }
   refine_kernel<<<1, 1024, 0, st>>>(a->cand_key, a->cand_tok, a->cand_col, a->cand_cap, flat_geom(a), a->ctl, ex, a->status);
   finalize_kernel<<<256, 256, 0, st>>>(lists_of(a), flat_geom(a), a->ctl, a->status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Per-feature threshold selection (JumpReLU / ReLU as a sparse list).  theta: [L, stat_pitch] fp32.  Uses of the
+// argument block: x, rstd (= theta), L, B, F, stat_pitch, ld, layer_stride, col_pitch, ctl, ent_*, status.
+extern "C" int clt_threshold_select(const CltSelectArgs* a, cudaStream_t st) {
+  if (a->ld % 8 != 0 || a->layer_stride % 8 != 0 || a->F > a->ld) return -1;
+  const ScanGeom g = scan_geom(a);
+  dim3 grid(((a->F + 7) / 8 + 255) / 256, (a->B + g.rows_per_block - 1) / g.rows_per_block, a->L);
+  if (cudaMemsetAsync(a->ctl + CTL_NUM_ENTRIES, 0, sizeof(long long), st) != cudaSuccess) return -5;
+  threshold_collect_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(a->x), a->rstd, g, a->col_pitch, a->ctl, lists_of(a), a->status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -440,3 +440,67 @@ def test_fused_step_with_preactivation_and_auxk_terms(tying):
         touched = ref_upd.abs() > 5e-4
         agree = (torch.sign(upd[touched]) == torch.sign(ref_upd[touched])).float().mean().item()
         assert agree > 0.95, (name, agree)
+
+
+@pytest.mark.parametrize("fn,tying", [("jumprelu", "none"), ("jumprelu", "per_source"), ("relu", "none"), ("batchtopk", "none")])
+def test_sparse_forward_matches_dense_model(ext, fn, tying):
+    """Inference path: encoder GEMM -> selection -> sparse decode against the dense PyTorch forward."""
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder
+    from crosslayer_coding_b200.models.sparse_forward import SparseForward, supports
+
+    torch.manual_seed(3)
+    dev = _dev()
+    L, d, F, B = 3, 64, 256, 192
+    kw = dict(num_features=F, num_layers=L, d_model=d, activation_fn=fn, decoder_tying=tying, clt_dtype="bfloat16")
+    if fn == "batchtopk":
+        kw["batchtopk_k"] = 12
+    if tying != "none":
+        kw.update(enable_feature_offset=True, enable_feature_scale=True)
+    model = CrossLayerTranscoder(CLTConfig(**kw), device=dev)
+    with torch.no_grad():
+        for w in model.dec_weight:
+            w.copy_(torch.randn_like(w) * 0.05)
+        model.enc_bias.copy_(torch.randn_like(model.enc_bias) * 0.1 - (0.6 if fn == "relu" else 0.0))
+        if model.log_threshold is not None:
+            model.log_threshold.copy_(torch.log(torch.rand_like(model.log_threshold) * 0.4 + 0.5))
+        if model.feature_offset is not None:
+            model.feature_offset.copy_(torch.randn_like(model.feature_offset) * 0.1)
+            model.feature_scale.copy_(1.0 + torch.randn_like(model.feature_scale) * 0.1)
+    assert supports(model) is None
+    X = (torch.randn(L, B, d, device=dev) * 0.7).bfloat16()
+    Y = torch.randn(L, B, d, device=dev).bfloat16()
+    sf = SparseForward(model, B)
+    yhat = sf.reconstruct(X, Y)
+    sf.check_status()
+    inputs = {l: X[l] for l in range(L)}
+    with torch.no_grad():
+        acts = model.get_feature_activations(inputs)
+        want = model(inputs)
+    dense = torch.stack([acts[l].float() for l in range(L)])
+    got_acts = sf.activations_dense()
+    if fn != "batchtopk":
+        # exact against the kernel's own pre-activations and thresholds ...
+        theta = sf._theta()
+        assert torch.equal(got_acts != 0, sf.preact.float() >= theta[:, None, :]), "selection differs from x >= theta"
+        assert torch.equal(got_acts[got_acts != 0], sf.preact.float()[got_acts != 0])
+        # ... and the same set as the dense model up to elements within bf16 rounding of their threshold
+        mism = (got_acts != 0) != (dense != 0)
+        gap = (sf.preact.float() - theta[:, None, :]).abs() / theta[:, None, :]
+        assert mism.float().mean().item() < 1e-3 and (gap[mism] < 0.02).all(), "sets differ away from the thresholds"
+    assert int((got_acts != 0).sum()) == sf.num_entries()
+    # the decode, given the kernel's own active set (elements at their threshold may differ from the dense
+    # model by bf16 rounding of the pre-activation, which would move the reconstruction by a whole feature)
+    with torch.no_grad():
+        own = {l: got_acts[l].to(torch.bfloat16) for l in range(L)}
+        ref = torch.stack([model.decode(own, l).float() for l in range(L)])
+    err = (yhat - ref).abs().max().item()
+    assert err < 0.03 * max(1.0, ref.abs().max().item()), err
+    full = torch.stack([want[l].float() for l in range(L)])
+    assert ((yhat - full).norm() / full.norm()).item() < 0.35
+    l0 = sf.l0_per_layer()
+    assert torch.allclose(l0, (got_acts != 0).float().sum(dim=(1, 2)) / B)
+    sq = ((yhat - Y.float()) ** 2).sum(dim=(1, 2)).double()
+    assert torch.allclose(sf.sq_err, sq, rtol=2e-3)
+    # contract of model.forward
+    out = sf.forward_dict(inputs)
+    assert set(out) == set(range(L)) and out[0].shape == (B, d)
