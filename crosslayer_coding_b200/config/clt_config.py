@@ -176,6 +176,9 @@ class TrainingConfig:
     # Tensor-parallel jobs: seconds after which a rank that has not announced the next step is declared
     # lost (host-side heartbeat through the job's store, checked before every launch).  None: off.
     peer_health_timeout_s: Optional[float] = None
+    # Fused JumpReLU step: capacity of the active-entry lists, in entries per token (a step whose
+    # activations are denser reports it through the status word).
+    fused_max_active_per_token: int = 1024
 
     def __post_init__(self) -> None:
         self.normalization_method = canonical_normalization(self.normalization_method)

@@ -47,6 +47,16 @@ struct CltSelectArgs {
 int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st);
 int clt_threshold_select(const CltSelectArgs* a, cudaStream_t st);
 
+struct CltThetaGradArgs {
+  const void* gs; const void* w[32]; const void* preact;
+  long long ldx, layer_stride_x;
+  const float* theta; int stat_pitch; float bandwidth;
+  float* S1; float* S2;
+  int L, B, F, d;
+  int* status;
+};
+int clt_theta_grad_gemm(const CltThetaGradArgs* a, int num_sms, cudaStream_t st);
+
 struct CltCsrArgs {
   const int* ent_tok; const int* ent_col; const float* ent_val; long long ent_cap;
   const long long* ctl;
@@ -244,6 +254,30 @@ void threshold_select(const Tensor& x, const Tensor& theta, int64_t f_valid, int
   check(clt_threshold_select(&a, cur_stream()), "threshold_select");
 }
 
+// JumpReLU threshold gradient sums: S1[l, f] += sum_b window * x * (gs . W_dec rows), S2[l, f] += sum_b window * x.
+void theta_grad_gemm(const Tensor& gs, const std::vector<Tensor>& dec_w, const Tensor& preact, const Tensor& theta, double bandwidth,
+                     Tensor& S1, Tensor& S2, Tensor& status) {
+  need(gs, at::kBFloat16, "gs"); need(preact, at::kBFloat16, "preact"); need(theta, at::kFloat, "theta");
+  need(S1, at::kFloat, "S1"); need(S2, at::kFloat, "S2"); need(status, at::kInt, "status");
+  const int L = gs.size(0), B = gs.size(1), d = gs.size(2), F = preact.size(2);
+  TORCH_CHECK(int(dec_w.size()) == L && L <= 32, "one untied decoder tensor per layer (at most 32)");
+  TORCH_CHECK(preact.size(0) == L && preact.size(1) == B && theta.size(0) == L && theta.size(1) >= F, "shape mismatch");
+  TORCH_CHECK(S1.sizes() == theta.sizes() && S2.sizes() == theta.sizes(), "S1 / S2 must have theta's shape");
+  CltThetaGradArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.gs = gs.data_ptr(); a.preact = preact.data_ptr(); a.ldx = preact.size(2); a.layer_stride_x = 1LL * B * preact.size(2);
+  for (int s = 0; s < L; ++s) {
+    need(dec_w[s], at::kBFloat16, "decoder weight");
+    TORCH_CHECK(dec_w[s].dim() == 3 && dec_w[s].size(0) == F && dec_w[s].size(1) == L - s && dec_w[s].size(2) == d, "decoder tensor must be [F, L - s, d]");
+    a.w[s] = dec_w[s].data_ptr();
+  }
+  a.theta = theta.data_ptr<float>(); a.stat_pitch = int(theta.size(1)); a.bandwidth = float(bandwidth);
+  a.S1 = S1.data_ptr<float>(); a.S2 = S2.data_ptr<float>();
+  a.L = L; a.B = B; a.F = F; a.d = d; a.status = status.data_ptr<int>();
+  c10::cuda::CUDAGuard guard(gs.device());
+  check(clt_theta_grad_gemm(&a, num_sms(), cur_stream()), "theta_grad_gemm");
+}
+
 void build_csr(const Tensor& ent_tok, const Tensor& ent_col, const Tensor& ent_val, const Tensor& ctl, int64_t num_tokens, int64_t num_cols,
                Tensor& tok_cnt, Tensor& feat_cnt, Tensor& tok_off, Tensor& feat_off, Tensor& tok_cursor, Tensor& feat_cursor,
                Tensor& tcsr_col, Tensor& tcsr_val, Tensor& fcsr_tok, Tensor& fcsr_val, const OptTensor& fired, int64_t sort_segments,
@@ -436,6 +470,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colstats", &colstats);
   m.def("batchtopk_select", &batchtopk_select);
   m.def("threshold_select", &threshold_select);
+  m.def("theta_grad_gemm", &theta_grad_gemm);
   m.def("build_csr", &build_csr);
   m.def("dead_counter_update", &dead_counter_update);
   m.def("sparse_decode", &sparse_decode);

@@ -18,7 +18,7 @@ _PKG = Path(__file__).resolve().parent.parent
 CSRC = _PKG / "csrc"
 BUILD_DIR = _PKG / "_ext"
 EXT_NAME = "clt_b200_ext"
-SOURCES = ["bindings.cpp", "encoder_gemm.cu", "select.cu", "decode.cu", "adam.cu", "comm.cu"]
+SOURCES = ["bindings.cpp", "encoder_gemm.cu", "theta_grad_gemm.cu", "select.cu", "decode.cu", "adam.cu", "comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",

@@ -26,16 +26,28 @@ CASES = {
 }
 
 
-def build(case: str, device: torch.device):
+def build(case: str, device: torch.device, activation: str = "batchtopk"):
     from .. import CLTConfig, CrossLayerTranscoder, TrainingConfig
     from ..training.fused_engine import FusedBatchTopKEngine
 
     L, d, F, B, k = CASES[case]
     torch.manual_seed(0)
-    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="batchtopk", batchtopk_k=k, clt_dtype="bfloat16")
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=activation, batchtopk_k=k, clt_dtype="bfloat16",
+                    jumprelu_threshold=0.03)
     model = CrossLayerTranscoder(cfg, device=device)
+    lam = 0.0
+    if activation == "jumprelu":
+        # thresholds at the value that leaves about k of a token's L * F pre-activations active
+        import math
+
+        torch.manual_seed(0)
+        probe = (torch.randn(512, d, device=device).bfloat16() @ model.enc_weight.data[0].t()).float() + model.enc_bias.data[0].float()
+        theta0 = float(torch.quantile(probe.flatten()[: 1 << 22], 1.0 - k / (L * F)))
+        with torch.no_grad():
+            model.log_threshold.fill_(math.log(max(theta0, 1e-6)))
+        lam = 1e-3
     tc = TrainingConfig(learning_rate=1e-4, training_steps=1000, activation_path="unused", precision="bf16",
-                        sparsity_lambda=0.0, preactivation_coef=0.0)
+                        sparsity_lambda=lam, preactivation_coef=0.0)
     eng = FusedBatchTopKEngine(model, tc, B)
     X = torch.randn(L, B, d, device=device).bfloat16()
     Y = torch.randn(L, B, d, device=device).bfloat16()
@@ -57,25 +69,30 @@ def _best_of(fn, n: int = 5) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--case", choices=sorted(CASES), default="full")
+    ap.add_argument("--activation", choices=["batchtopk", "jumprelu"], default="batchtopk")
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--lr", type=float, default=None,
+                    help="learning rate (default 1e-4; 1e-8 for jumprelu so that the active count of the synthetic data stays put)")
     ap.add_argument("--time", action="store_true", help="print CUDA-event timings instead of marking a profiler range")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
-    model, eng, X, Y = build(args.case, dev)
+    model, eng, X, Y = build(args.case, dev, args.activation)
+    lam = eng.tc.sparsity_lambda
+    lr = args.lr if args.lr is not None else (1e-8 if args.activation == "jumprelu" else 1e-4)
     L, d, F, B, k = CASES[args.case]
     for s in range(args.warmup):
-        eng.train_step(X, Y, s, 1e-4)
+        eng.train_step(X, Y, s, lr, sparsity_lambda=lam)
     torch.cuda.synchronize()
     if args.time:
         e = eng.ext
         step = [args.warmup]
 
         def full():
-            eng.train_step(X, Y, step[0], 1e-4)
+            eng.train_step(X, Y, step[0], lr, sparsity_lambda=lam)
             step[0] += 1
 
         res = {
-            "case": args.case,
+            "case": args.case, "activation": args.activation,
             "encoder_gemm_ms": _best_of(lambda: e.encoder_gemm(X, model.enc_weight.data, model.enc_bias.data, eng.preact, eng.status)),
             "library_bmm_ms": _best_of(lambda: torch.bmm(X, model.enc_weight.data.transpose(1, 2))),
             "encode_select_ms": _best_of(lambda: eng.encode_select(X)),
@@ -86,11 +103,12 @@ def main() -> None:
         res["encoder_gemm_tflops"] = flops / res["encoder_gemm_ms"] / 1e9
         res["library_bmm_tflops"] = flops / res["library_bmm_ms"] / 1e9
         res["tokens_per_s"] = B / res["train_step_ms"] * 1e3
+        res["active_per_token"] = int(eng.ctl[3]) / B
         eng.check_status()
         print(json.dumps(res))
         return
     torch.cuda.profiler.start()
-    eng.train_step(X, Y, args.warmup, 1e-4)
+    eng.train_step(X, Y, args.warmup, lr, sparsity_lambda=lam)
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
     eng.check_status()

@@ -61,10 +61,16 @@ def histogram_range(k_total: int, numel: int, pool_factor: float = 1.75):
 
 def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingConfig], model=None) -> Optional[str]:
     """``None`` when the fused step covers this configuration, else the reason it does not."""
-    if clt_config.activation_fn != "batchtopk":
-        return f"activation_fn={clt_config.activation_fn!r} (fused step covers batchtopk)"
-    if clt_config.topk_mode != "global":
+    if clt_config.activation_fn not in ("batchtopk", "jumprelu"):
+        return f"activation_fn={clt_config.activation_fn!r} (fused step covers batchtopk and jumprelu)"
+    if clt_config.activation_fn == "batchtopk" and clt_config.topk_mode != "global":
         return "topk_mode='per_layer'"
+    if clt_config.activation_fn == "jumprelu":
+        # the threshold gradient runs as one GEMM per source layer over the packed untied decoder tensors
+        if clt_config.decoder_tying != "none":
+            return "jumprelu with tied decoders"
+        if model is not None and model.world_size > 1:
+            return "jumprelu under tensor parallelism"
     if clt_config.skip_connection:
         return "skip_connection"
     if clt_config.enable_feature_offset or clt_config.enable_feature_scale:
@@ -141,8 +147,15 @@ class FusedBatchTopKEngine:
         L, B, d, Fl = self.L, self.B, self.d, self.Fl
         i32, f32 = torch.int32, torch.float32
 
-        self.k_total = min(int(cfg.batchtopk_k) * B, B * L * self.F)
-        self.key_lo, self.shift = histogram_range(self.k_total, B * L * self.F)
+        self.fn = cfg.activation_fn
+        if self.fn == "batchtopk":
+            self.k_total = min(int(cfg.batchtopk_k) * B, B * L * self.F)
+        else:
+            # JumpReLU: the number of active entries is data dependent; the lists hold up to
+            # ``fused_max_active_per_token`` entries per token and a step that needs more reports it
+            per_tok = int(getattr(training_config, "fused_max_active_per_token", 1024) or 1024) if training_config is not None else 1024
+            self.k_total = int(min(B * L * max(self.Fv, 1), per_tok * B))
+        self.key_lo, self.shift = histogram_range(self.k_total, B * L * self.F) if self.fn == "batchtopk" else (0, 19)
         self.preact = torch.empty(L, B, Fl, dtype=torch.bfloat16, device=dev)
         self.mean = torch.empty(L, Fl, dtype=f32, device=dev)
         self.rstd = torch.empty(L, Fl, dtype=f32, device=dev)
@@ -213,6 +226,12 @@ class FusedBatchTopKEngine:
             self.dec_m = [z(w) for w in model.dec_weight]
             self.dec_v = [z(w) for w in model.dec_weight]
             self.decb_m, self.decb_v = z(model.dec_bias), z(model.dec_bias)
+        if self.fn == "jumprelu":
+            self.S1 = torch.zeros(L, Fl, dtype=f32, device=dev)
+            self.S2 = torch.zeros(L, Fl, dtype=f32, device=dev)
+            if training_config is not None:
+                self.theta_m = torch.zeros(L, Fl, dtype=f32, device=dev)
+                self.theta_v = torch.zeros(L, Fl, dtype=f32, device=dev)
         self.opt_step = 0
         self.seq = 0
         self.kernel_launches = 0  # launches of this package's own kernels (reported by the benchmark)
@@ -230,6 +249,18 @@ class FusedBatchTopKEngine:
         m = self.model
         assert X.dtype == torch.bfloat16 and X.shape == (self.L, self.B, self.d), (X.dtype, X.shape)
         e.encoder_gemm(X, m.enc_weight.data, m.enc_bias.data, self.preact, self.status)
+        if self.fn == "jumprelu":
+            self.theta = m.log_threshold.data.float().exp().contiguous()
+            e.threshold_select(self.preact, self.theta, self.Fv, self.Fl, self.ctl, self.ent_tok, self.ent_col, self.ent_val, self.status)
+            self.tok_cnt.zero_()
+            self.feat_cnt.zero_()
+            e.build_csr(
+                self.ent_tok, self.ent_col, self.ent_val, self.ctl, self.B, self.ncols,
+                self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
+                self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2, self.Fl,
+            )
+            self.kernel_launches += 2 + 5  # gemm, threshold selection, csr (5)
+            return
         e.colstats(self.preact, self.mean, self.rstd)
         self.hist.zero_()
         world, rank, dptr, fptr, slot, seq = self._exchange_args()
@@ -399,6 +430,12 @@ class FusedBatchTopKEngine:
         self.encode_select(X)
         self.decode_loss(Y)
         c_g = 2.0 / (B * d)
+        if self.fn == "jumprelu":
+            # window sums for the threshold gradient, from the decoder weights of this step (before their update)
+            self.S1.zero_()
+            self.S2.zero_()
+            e.theta_grad_gemm(self.gs, [w.data for w in m.dec_weight], self.preact, self.theta, float(m.bandwidth), self.S1, self.S2, self.status)
+            self.kernel_launches += 1
         zero = torch.zeros((), device=self.dev)
         pre_loss, aux_loss = zero, zero
         enc_dense = encb_dense = dec0_dense = None
@@ -429,8 +466,10 @@ class FusedBatchTopKEngine:
         self.grad_a.zero_()
         self.penalty.zero_()
         pen = None
-        use_pen = sparsity_lambda > 1e-9 and (tc.apply_sparsity_penalty_to_batchtopk if tc is not None else True)
+        use_pen = sparsity_lambda > 1e-9 and (self.fn != "batchtopk" or (tc.apply_sparsity_penalty_to_batchtopk if tc is not None else True))
         if use_pen:
+            if self.fn == "jumprelu":
+                self.norm_at_step = self.feature_norm2().clamp_min(0).sqrt()  # the update below replaces the norms
             e.sparsity_penalty(self.feat_off, self.fcsr_val, self.feature_norm2(), float(sparsity_lambda), float(tc.sparsity_c),
                                self.grad_a, self.pen_coef, self.penalty)
             pen = self.pen_coef
@@ -443,6 +482,8 @@ class FusedBatchTopKEngine:
         e.dense_adam(m.dec_bias.data, self.decb_m, self.decb_v, bias_grad, self._hyper(lr, c_g))
         e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v,
                             self.feat_off, self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, self._hyper(lr, 1.0), self.status)
+        if self.fn == "jumprelu":
+            self._update_thresholds(lr, c_g, float(sparsity_lambda) if use_pen else 0.0)
         e.dead_counter_update(self.dead_counter, self.fired)
         self.kernel_launches += 5 + (1 if use_pen else 0)  # gs_colsum, decoder/encoder Adam, dense Adam, dead counters
         m.invalidate_decoder_norms()
@@ -453,6 +494,38 @@ class FusedBatchTopKEngine:
             pops.all_reduce(both, group=self.group)
             sparsity, pre_loss = both[0], both[1]
         return StepOutput(recon, sparsity, pre_loss, aux_loss, recon + sparsity + pre_loss + aux_loss, self.ctl[3])
+
+    @torch.no_grad()
+    def _update_thresholds(self, lr: float, c_g: float, lam: float) -> None:
+        """AdamW step on ``log_threshold`` from the window sums of ``theta_grad_gemm``.
+
+        ``d loss / d theta[f] = -(1 / bw) * sum_b window * x * G`` with ``G = c_g * (gs . W rows)`` for the
+        reconstruction and ``lam * c * n_f * sech^2(c * n_f * a)`` for the sparsity penalty; the latter is a
+        per-feature constant except at the active entries, which the entry list corrects
+        (reference: clt/models/activations.py:196-220 with clt/training/losses.py:179-185)."""
+        m, tc = self.model, self.tc
+        bw = float(m.bandwidth)
+        g = c_g * self.S1
+        if lam > 0.0:
+            c = float(tc.sparsity_c)
+            norm = self.norm_at_step.view(self.L, self.Fl)
+            cap = self.ent_val.numel()
+            n = torch.clamp(self.ctl[3], max=cap)
+            live = torch.arange(cap, device=self.dev) < n
+            # unused slots add zero; they are spread over the columns so that they do not pile up on one address
+            col = torch.where(live, self.ent_col, (torch.arange(cap, device=self.dev, dtype=torch.int32) % self.ncols)).long()
+            x = torch.where(live, self.ent_val, torch.zeros_like(self.ent_val))
+            nf = norm.reshape(-1)[col]
+            inside = (x - self.theta.reshape(-1)[col]).abs() <= bw / 2
+            t2 = torch.tanh(c * nf * x) ** 2
+            corr = torch.zeros(self.ncols, dtype=torch.float32, device=self.dev)
+            corr.index_add_(0, col, torch.where(inside & live, x * t2, torch.zeros_like(x)))
+            g = g + lam * c * norm * (self.S2 - corr.view(self.L, self.Fl))
+        grad_theta = -g / bw
+        grad_log = (grad_theta * self.theta).contiguous()  # theta = exp(log_threshold)
+        self.grad_log_threshold = grad_log  # kept for diagnostics and tests
+        self.ext.dense_adam(m.log_threshold.data, self.theta_m, self.theta_v, grad_log, self._hyper(lr, 1.0))
+        self.kernel_launches += 1
 
     # --------------------------------------------------------------- inference
     @torch.no_grad()
@@ -486,6 +559,8 @@ class FusedBatchTopKEngine:
         for i, (mm, vv) in enumerate(zip(self.dec_m, self.dec_v)):
             sd[f"dec_m.{i}"] = mm
             sd[f"dec_v.{i}"] = vv
+        if self.fn == "jumprelu":
+            sd["theta_m"], sd["theta_v"] = self.theta_m, self.theta_v
         return sd
 
     def load_optimizer_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
@@ -495,4 +570,7 @@ class FusedBatchTopKEngine:
         for i in range(len(self.dec_m)):
             self.dec_m[i].copy_(sd[f"dec_m.{i}"])
             self.dec_v[i].copy_(sd[f"dec_v.{i}"])
+        if self.fn == "jumprelu" and "theta_m" in sd:
+            self.theta_m.copy_(sd["theta_m"])
+            self.theta_v.copy_(sd["theta_v"])
         self.norms_valid = False

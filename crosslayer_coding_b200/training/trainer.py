@@ -270,7 +270,7 @@ class CLTTrainer:
             if X.dtype != torch.bfloat16:
                 X, Y = X.to(torch.bfloat16), Y.to(torch.bfloat16)
         lam = sparsity_lambda_at(tc, step, tc.training_steps)
-        if not tc.apply_sparsity_penalty_to_batchtopk:
+        if self.clt_config.activation_fn == "batchtopk" and not tc.apply_sparsity_penalty_to_batchtopk:
             lam = 0.0
         self.loss_manager.current_sparsity_lambda = lam
         need_aux = bool(tc.aux_loss_factor) and step > tc.dead_feature_window and self._any_dead_cached(step)

@@ -504,3 +504,98 @@ def test_sparse_forward_matches_dense_model(ext, fn, tying):
     # contract of model.forward
     out = sf.forward_dict(inputs)
     assert set(out) == set(range(L)) and out[0].shape == (B, d)
+
+
+@pytest.mark.parametrize("L,B,F,d", [(3, 256, 256, 64), (2, 200, 264, 72), (4, 384, 512, 128)])
+def test_theta_grad_gemm_matches_dense(ext, L, B, F, d):
+    """S1 = sum_b window * x * (gs . W rows over the target layers), S2 = sum_b window * x."""
+    torch.manual_seed(5)
+    dev = _dev()
+    gs = (torch.randn(L, B, d, device=dev) * 0.1).bfloat16()
+    ws = [(torch.randn(F, L - s, d, device=dev) * 0.2).bfloat16() for s in range(L)]
+    x = (torch.randn(L, B, F, device=dev) * 0.6).bfloat16()
+    theta = torch.rand(L, F, device=dev) * 0.5 + 0.05
+    S1 = torch.zeros(L, F, device=dev)
+    S2 = torch.zeros(L, F, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    ext.theta_grad_gemm(gs, ws, x, theta, 1.0, S1, S2, status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    for s in range(L):
+        G = torch.zeros(B, F, device=dev)
+        for r in range(L - s):
+            G += gs[s + r].float() @ ws[s][:, r, :].float().t()
+        xf = x[s].float()
+        win = ((xf - theta[s][None, :]).abs() <= 0.5).float()
+        want1 = (win * xf * G).sum(dim=0)
+        want2 = (win * xf).sum(dim=0)
+        assert torch.allclose(S2[s], want2, rtol=1e-4, atol=1e-3), (S2[s] - want2).abs().max()
+        scale = want1.abs().max().item()
+        assert (S1[s] - want1).abs().max().item() < 5e-3 * max(scale, 1.0), ((S1[s] - want1).abs().max().item(), scale)
+
+
+@pytest.mark.parametrize("lam", [0.0, 0.05])
+def test_fused_jumprelu_step_matches_autograd(lam):
+    """Fused JumpReLU training step (threshold selection, sparse decode, threshold-gradient GEMM, fused AdamW)
+    against autograd on an fp32 copy of the model fed with the kernel's own pre-activations."""
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder, TrainingConfig
+    from crosslayer_coding_b200.models import activations as act
+    from crosslayer_coding_b200.training.fused_engine import FusedBatchTopKEngine
+
+    torch.manual_seed(21)
+    dev = _dev()
+    L, d, F, B = 3, 64, 256, 128
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="jumprelu", jumprelu_threshold=0.4, clt_dtype="bfloat16")
+    model = CrossLayerTranscoder(cfg, device=dev)
+    with torch.no_grad():
+        model.log_threshold.copy_(torch.log(torch.rand_like(model.log_threshold.float()) * 0.5 + 0.3))
+        for w in model.dec_weight:
+            w.copy_(torch.randn_like(w) * 0.08)
+    tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="bf16",
+                        sparsity_lambda=lam, sparsity_c=1.0, preactivation_coef=0.0, optimizer="adamw")
+    eng = FusedBatchTopKEngine(model, tc, B)
+    X = torch.randn(L, B, d, device=dev).bfloat16()
+    Y = torch.randn(L, B, d, device=dev).bfloat16()
+    ref = _fp32_copy(model)
+    with torch.no_grad():
+        ref.log_threshold.copy_(model.log_threshold.float())
+    snap = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3)
+    out = eng.train_step(X, Y, step=0, lr=1e-3, sparsity_lambda=lam)
+    torch.cuda.synchronize()
+    eng.check_status()
+    # autograd reference on the same pre-activation values (straight-through to the fp32 encoder)
+    pre = {l: torch.nn.functional.linear(X[l].float(), ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    acts = {}
+    for l in range(L):
+        x = pre[l] + (eng.preact[l].float() - pre[l]).detach()
+        acts[l] = act.JumpReLU.apply(x, ref.log_threshold[l].exp(), 1.0)
+    loss = sum(torch.nn.functional.mse_loss(ref.decode({s: acts[s] for s in range(t + 1)}, t), Y[t].float()) for t in range(L))
+    recon_ref = loss.item()
+    pen_ref = 0.0
+    if lam > 0:
+        norms = ref.get_decoder_norms()
+        pen = lam * sum(torch.tanh(tc.sparsity_c * acts[l] * norms[l][None, :]).sum() for l in range(L))
+        pen_ref = pen.item()
+        loss = loss + pen
+    loss.backward()
+    assert abs(out.reconstruction.item() - recon_ref) < 2e-3 * max(1.0, recon_ref)
+    assert abs(out.sparsity.item() - pen_ref) < 2e-3 * max(1.0, pen_ref)
+    # threshold gradient itself: recover it from the engine's window sums
+    g_ref = ref.log_threshold.grad  # d loss / d log_threshold
+    assert g_ref.abs().max().item() > 0
+    g_err = (eng.grad_log_threshold - g_ref).abs().max().item()
+    assert g_err < 0.02 * g_ref.abs().max().item() + 1e-6, (g_err, g_ref.abs().max().item())
+    opt.step()
+    ref_params = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        old = snap[name]
+        upd = p.detach().float() - old
+        ref_upd = ref_params[name].detach() - old
+        tol = 0.008 * old.abs() + 3e-4
+        bad = ((upd - ref_upd).abs() > tol).float().mean().item()
+        assert bad < 4e-3, (name, bad, (upd - ref_upd).abs().max().item())
+        touched = ref_upd.abs() > 5e-4
+        if touched.any() and "log_threshold" not in name:  # a 1e-3 step is below the bf16 spacing of log theta
+            agree = (torch.sign(upd[touched]) == torch.sign(ref_upd[touched])).float().mean().item()
+            assert agree > 0.97, (name, agree)
