@@ -28,6 +28,7 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
 MODEL = dict(num_layers=12, d_model=768, num_features=24576, k=200, batch=4096)
+JUMPRELU_THETA = 0.33  # --activation jumprelu: leaves about 200 of a token's 294,912 pre-activations active at initialisation
 METRIC = "train tokens/sec (box, device-timed, max over ranks) GPT-2-small CLT 32x BatchTopK"
 
 
@@ -39,6 +40,9 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--ref-variant", choices=["bf16_params", "autocast_fp32"], default="bf16_params")
     ap.add_argument("--pool", type=int, default=4, help="distinct synthetic batches kept in pinned host memory")
+    ap.add_argument("--activation", choices=["batchtopk", "jumprelu"], default="batchtopk",
+                    help="batchtopk is the headline configuration; jumprelu trains thresholds natively (threshold 0.33: "
+                         "about k active features per token on the synthetic data, sparsity penalty on)")
     return ap.parse_args()
 
 
@@ -186,12 +190,15 @@ def run_ours(args, world, rank, local):
     dev = torch.device(f"cuda:{local}")
     L, d, F, k, B = (MODEL[n] for n in ("num_layers", "d_model", "num_features", "k", "batch"))
     host, (mean_tg, std_tg) = make_pool(args.pool, dev)
-    clt_cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="batchtopk", batchtopk_k=k, clt_dtype="bfloat16")
+    jr = args.activation == "jumprelu"
+    clt_cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k, clt_dtype="bfloat16",
+                        jumprelu_threshold=JUMPRELU_THETA)
     total = args.warmup * 2 + args.steps * 2 + 8
     tc = TrainingConfig(
         learning_rate=1e-4, training_steps=max(total, 1000), train_batch_size_tokens=B, precision="bf16",
         activation_path="in-memory", activation_dtype="bfloat16", normalization_method="mean_std",
-        sparsity_lambda=0.0, preactivation_coef=0.0, aux_loss_factor=1 / 32, apply_sparsity_penalty_to_batchtopk=False,
+        sparsity_lambda=(1e-3 if jr else 0.0), sparsity_lambda_schedule="linear", sparsity_lambda_delay_frac=0.0,
+        preactivation_coef=0.0, aux_loss_factor=1 / 32, apply_sparsity_penalty_to_batchtopk=False,
         optimizer="adamw", lr_scheduler="linear", eval_interval=10 ** 9, checkpoint_interval=10 ** 9, log_interval=10 ** 9,
         engine="fused",
     )
@@ -247,11 +254,13 @@ def run_ours(args, world, rank, local):
     value = B * args.steps / (ms / 1e3)
     e2e_value = B * args.steps / (e2e_ms / 1e3)
     return {
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if not jr else METRIC.replace("BatchTopK", "JumpReLU (native thresholds)"),
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded sparse-dictionary activations, random-init weights)",
         "config": {
-            "model": "GPT-2-small-shaped CLT: 12 layers, d_model 768, 24576 features/layer (32x), untied decoders, BatchTopK k=200",
+            "model": "GPT-2-small-shaped CLT: 12 layers, d_model 768, 24576 features/layer (32x), untied decoders, "
+                     + ("JumpReLU theta0=0.33, sparsity lambda 1e-3" if jr else "BatchTopK k=200"),
             "global_batch": B, "seq_len": 1, "parallelism": f"tp{world}",
             "optimizer": "AdamW, fp32 moments, bf16 weights", "loss": "reconstruction + AuxK factor 1/32 (no dead features yet)",
             "l2": "per-step inputs (151 MB) and streamed weights (3.4 GB) exceed the 126 MB L2; 3 device batches cycled",
@@ -294,12 +303,14 @@ def run_reference(args, world, rank, local):
     L, d, F, k, B = (MODEL[n] for n in ("num_layers", "d_model", "num_features", "k", "batch"))
     host, (mean_tg, std_tg) = make_pool(args.pool, dev)
     bf16_params = args.ref_variant == "bf16_params"
-    cfg = RefCLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="batchtopk", batchtopk_k=k,
-                       clt_dtype="bfloat16" if bf16_params else None)
+    jr = args.activation == "jumprelu"
+    cfg = RefCLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k,
+                       jumprelu_threshold=JUMPRELU_THETA, clt_dtype="bfloat16" if bf16_params else None)
     tc = RefTrainingConfig(
         learning_rate=1e-4, training_steps=1000, train_batch_size_tokens=B, precision="bf16",
         activation_path="in-memory", activation_dtype="bfloat16", normalization_method="mean_std",
-        sparsity_lambda=0.0, preactivation_coef=0, aux_loss_factor=1 / 32, apply_sparsity_penalty_to_batchtopk=False,
+        sparsity_lambda=(1e-3 if jr else 0.0), sparsity_lambda_schedule="linear", sparsity_lambda_delay_frac=0.0,
+        preactivation_coef=0, aux_loss_factor=1 / 32, apply_sparsity_penalty_to_batchtopk=False,
         optimizer="adamw", lr_scheduler="linear",
     )
     torch.manual_seed(tc.seed + rank)
@@ -369,11 +380,13 @@ def run_reference(args, world, rank, local):
     sync_all(world)
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, world)
     return {
-        "metric": METRIC, "value": B * args.steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if not jr else METRIC.replace("BatchTopK", "JumpReLU (native thresholds)"),
+        "value": B * args.steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded sparse-dictionary activations, random-init weights)",
         "config": {
-            "model": "GPT-2-small-shaped CLT: 12 layers, d_model 768, 24576 features/layer (32x), untied decoders, BatchTopK k=200",
+            "model": "GPT-2-small-shaped CLT: 12 layers, d_model 768, 24576 features/layer (32x), untied decoders, "
+                     + ("JumpReLU theta0=0.33, sparsity lambda 1e-3" if jr else "BatchTopK k=200"),
             "global_batch": B, "seq_len": 1, "parallelism": f"tp{world}", "variant": args.ref_variant,
             "path": "reference CrossLayerTranscoder + LossManager + average_shared_parameter_grads driven through the step "
                     "sequence of clt/training/trainer.py:661-810" + (f" (CLTTrainer itself is not importable: {trainer_note})" if trainer_note else ""),

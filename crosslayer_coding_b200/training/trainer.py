@@ -199,6 +199,10 @@ class CLTTrainer:
             reason = "no CUDA device"
         else:
             reason = engine_supports(self.clt_config, tc, self.model)
+            if reason is None and want == "auto" and self.clt_config.activation_fn == "jumprelu":
+                # the fused JumpReLU step keeps the active entries in lists of fused_max_active_per_token per token;
+                # a run that starts dense (the default threshold 0.03 does) has to start on the autograd step
+                reason = "jumprelu takes the fused step only with engine='fused' (it needs sparse activations throughout)"
             if reason is None and self.world_size > 1:
                 from ..parallel.symm import SymmetricExchange
 
