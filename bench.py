@@ -235,18 +235,38 @@ def run_ours(args, world, rank, local):
     step_box = [args.warmup + args.steps]
     losses = []
 
-    def e2e_step(_):
+    # every step's loss is read back (4 bytes, device -> pinned host); the read of step i is collected after
+    # step i + 1 has been queued, so the host never idles the GPU while it waits for a scalar
+    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_ready = [torch.cuda.Event() for _ in range(2)]
+    pending = []
+
+    def collect():
+        slot = pending.pop(0)
+        loss_ready[slot].synchronize()
+        losses.append(float(loss_host[slot][0]))
+
+    def e2e_step(i):
         inputs, targets = next(store)
         parts = trainer.train_step(inputs, targets, step_box[0])
         step_box[0] += 1
-        losses.append(parts["total"].item())  # 4-byte device->host read, synchronises the step
+        slot = i % 2
+        loss_host[slot].copy_(parts["total"].detach().float().reshape(1), non_blocking=True)
+        loss_ready[slot].record()
+        pending.append(slot)
+        if len(pending) > 1:
+            collect()
 
     for i in range(args.warmup):
         e2e_step(i)
+    while pending:
+        collect()
     sync_all(world)
     t0 = time.perf_counter()
     for i in range(args.steps):
         e2e_step(i)
+    while pending:
+        collect()
     sync_all(world)
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, world)
     engine.check_status()
