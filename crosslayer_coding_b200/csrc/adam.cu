@@ -459,7 +459,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       for (int j = 0; j < kAdamSlots; ++j) h->a[j] = cur.a[j];
       const int nslot = ne < kAdamSlots ? ne : kAdamSlots;
       mbar_expect_tx(&sh->full[st], w_bytes + 2u * mv_bytes + uint32_t(nslot) * gs_bytes);
-      bulk_load_1d(stage + off_w, static_cast<const WT*>(p.w[ti]) + elem_off, w_bytes, &sh->full[st]);
+      bulk_load_1d_hint(stage + off_w, static_cast<const WT*>(p.w[ti]) + elem_off, w_bytes, &sh->full[st], pol_stream);
       bulk_load_1d_hint(stage + off_m, p.m[ti] + elem_off, mv_bytes, &sh->full[st], pol_stream);
       bulk_load_1d_hint(stage + off_v, p.v[ti] + elem_off, mv_bytes, &sh->full[st], pol_stream);
       const __nv_bfloat16* gs_t = p.gs + 1LL * (ti + r) * B * d;
@@ -488,7 +488,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       const AdamStageHdr* h = reinterpret_cast<const AdamStageHdr*>(stage);
       const int sti = h->ti;
       const long long eo = h->elem_off;
-      bulk_store_1d(static_cast<WT*>(p.w[sti]) + eo, stage + off_w, w_bytes);
+      bulk_store_1d_hint(static_cast<WT*>(p.w[sti]) + eo, stage + off_w, w_bytes, pol_stream);
       bulk_store_1d_hint(p.m[sti] + eo, stage + off_m, mv_bytes, pol_stream);
       bulk_store_1d_hint(p.v[sti] + eo, stage + off_v, mv_bytes, pol_stream);
       bulk_commit();
