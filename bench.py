@@ -40,6 +40,9 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--ref-variant", choices=["bf16_params", "autocast_fp32"], default="bf16_params")
     ap.add_argument("--pool", type=int, default=4, help="distinct synthetic batches kept in pinned host memory")
+    ap.add_argument("--parity-steps", type=int, default=0,
+                    help="after the timed loops, train this many further steps over the pool and report the normalised MSE "
+                         "on a held-out synthetic batch (key 'parity'); use the same value and --pool for both arms")
     ap.add_argument("--activation", choices=["batchtopk", "jumprelu"], default="batchtopk",
                     help="batchtopk is the headline configuration; jumprelu trains thresholds natively (threshold 0.33: "
                          "about k active features per token on the synthetic data, sparsity penalty on)")
@@ -116,6 +119,29 @@ def setup_dist(n_gpus: int):
     if world != n_gpus and rank == 0:
         print(f"note: --gpus {n_gpus} but WORLD_SIZE={world}; using WORLD_SIZE", file=sys.stderr)
     return world, rank, local
+
+
+def heldout_batch(device):
+    """One synthetic batch that is in no pool (seed outside the pool's range), on the device: ``[2, L, B, d]`` bf16."""
+    import torch
+
+    from crosslayer_coding_b200.activation_generation.synthetic import SparseDictionarySynth, SyntheticSpec
+
+    L, d, B = MODEL["num_layers"], MODEL["d_model"], MODEL["batch"]
+    synth = SparseDictionarySynth(SyntheticSpec(num_layers=L, d_model=d, dict_size=4 * d, active_mean=32.0, seed=1234), device=device)
+    synth.fit_norm_stats(8192)
+    x, y = synth.sample(B, seed=987654, normalize=True, dtype=torch.bfloat16)
+    out = torch.stack([x, y])
+    del synth
+    return out
+
+
+def nmse_of(yhat, y) -> float:
+    """Mean over layers of MSE / mean_d var_tokens(target), on ``[L, B, d]`` tensors."""
+    yf, hf = y.float(), yhat.float()
+    mse = ((hf - yf) ** 2).mean(dim=(1, 2))
+    var = yf.var(dim=1, unbiased=False).mean(dim=1)
+    return float((mse / var).mean())
 
 
 def make_pool(pool: int, device):
@@ -271,6 +297,18 @@ def run_ours(args, world, rank, local):
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, world)
     engine.check_status()
 
+    parity = None
+    if args.parity_steps > 0:
+        for i in range(args.parity_steps):
+            inputs, targets = next(store)
+            trainer.train_step(inputs, targets, step_box[0])
+            step_box[0] += 1
+        held = heldout_batch(dev)
+        with torch.no_grad():
+            yhat = engine.forward(held[0], held[1])
+        engine.check_status()
+        parity = {"steps_trained": step_box[0], "nmse_heldout": nmse_of(yhat, held[1]), "pool_batches": args.pool}
+
     value = B * args.steps / (ms / 1e3)
     e2e_value = B * args.steps / (e2e_ms / 1e3)
     return {
@@ -293,6 +331,7 @@ def run_ours(args, world, rank, local):
                 else "pinned host ring -> side-stream copy"},
         "gpu_launches": int(launches),
         "final_loss": losses[-1] if losses else None,
+        "parity": parity,
         "impl": "ours",
     }
 
@@ -399,6 +438,19 @@ def run_reference(args, world, rank, local):
         e2e_step(i)
     sync_all(world)
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, world)
+    parity = None
+    if args.parity_steps > 0:
+        done = args.warmup + args.steps + min(args.warmup, 2) + args.steps
+        for i in range(args.parity_steps):
+            buf = stage[i % 2]
+            buf.copy_(host[i % args.pool], non_blocking=True)
+            x, y = as_dicts(buf)
+            step_fn(x, y, done + i)
+        held = heldout_batch(dev)
+        with torch.no_grad(), torch.autocast(device_type="cuda", dtype=torch.bfloat16, enabled=True):
+            out = model({l: held[0, l] for l in range(L)})
+        yhat = torch.stack([out[l].float() for l in range(L)])
+        parity = {"steps_trained": done + args.parity_steps, "nmse_heldout": nmse_of(yhat, held[1]), "pool_batches": args.pool}
     return {
         "metric": METRIC if not jr else METRIC.replace("BatchTopK", "JumpReLU (native thresholds)"),
         "value": B * args.steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -416,6 +468,7 @@ def run_reference(args, world, rank, local):
                 "h2d_bytes_per_step": int(host[0].numel() * 2), "d2h_bytes_per_step": 20},
         "gpu_launches": 0,
         "final_loss": losses[-1] if losses else None,
+        "parity": parity,
         "impl": "reference",
     }
 
