@@ -69,8 +69,6 @@ def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingCon
         # the threshold gradient runs as one GEMM per source layer over the packed untied decoder tensors
         if clt_config.decoder_tying != "none":
             return "jumprelu with tied decoders"
-        if model is not None and model.world_size > 1:
-            return "jumprelu under tensor parallelism"
     if clt_config.skip_connection:
         return "skip_connection"
     if clt_config.enable_feature_offset or clt_config.enable_feature_scale:

@@ -16,15 +16,15 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(world: int, out: str, features: int, port: int, lam: float = 0.0):
+def _run(world: int, out: str, features: int, port: int, lam: float = 0.0, activation: str = "batchtopk"):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     worker = os.path.join(HERE, "tp_worker.py")
     if world == 1:
-        cmd = [sys.executable, worker, "--out", out, "--features", str(features), "--lam", str(lam)]
+        cmd = [sys.executable, worker, "--out", out, "--features", str(features), "--lam", str(lam), "--activation", activation]
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                "--master-addr", "127.0.0.1", "--master-port", str(port), worker, "--out", out,
-               "--features", str(features), "--lam", str(lam)]
+               "--features", str(features), "--lam", str(lam), "--activation", activation]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     return torch.load(out, weights_only=False)
@@ -49,3 +49,20 @@ def test_tp_matches_single_gpu(tmp_path, world, features, lam):
         assert w.shape == w_ref.shape, key
         bad = ((w - w_ref).abs() > 0.01 * w_ref.abs() + 4e-4).float().mean().item()
         assert bad < 5e-3, (key, bad, (w - w_ref).abs().max().item())
+
+
+def test_tp_jumprelu_matches_single_gpu(tmp_path):
+    """Natively trained JumpReLU under tensor parallelism: thresholds, selection and the threshold-gradient GEMM are
+    all local to the feature shard; only the decode partials and the gradient seed cross NVLink."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ref = _run(1, str(tmp_path / "w1.pt"), 512, 29631, 0.02, "jumprelu")
+    got = _run(2, str(tmp_path / "w2.pt"), 512, 29633, 0.02, "jumprelu")
+    assert got["entries"] == ref["entries"] and ref["entries"][0] > 0, (got["entries"], ref["entries"])
+    for a, b in zip(got["losses"], ref["losses"]):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(b)), (got["losses"], ref["losses"])
+    for key, w_ref in ref["state"].items():
+        w = got["state"][key]
+        assert w.shape == w_ref.shape, key
+        bad = ((w - w_ref).abs() > 0.01 * w_ref.abs() + 2e-3).float().mean().item()
+        assert bad < 5e-3, (key, bad)

@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--features", type=int, default=512)
     ap.add_argument("--lam", type=float, default=0.0)
+    ap.add_argument("--activation", default="batchtopk")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -40,12 +41,13 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     L, d, F, B, k = 3, 64, args.features, 128, 8
-    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="batchtopk", batchtopk_k=k, clt_dtype="bfloat16")
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k, clt_dtype="bfloat16",
+                    jumprelu_threshold=0.25)
     full_state = build_full_state(cfg)
     model = CrossLayerTranscoder(cfg, process_group=group, device=dev)
     model.load_state_dict(slice_for_rank(full_state, rank, world, F) if world > 1 else full_state)
     tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="bf16",
-                        sparsity_lambda=0.0, preactivation_coef=0.0)
+                        sparsity_lambda=args.lam, preactivation_coef=0.0)
     symm = None
     if world > 1:
         from crosslayer_coding_b200.parallel.symm import SymmetricExchange
