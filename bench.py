@@ -27,9 +27,36 @@ import time
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
-MODEL = dict(num_layers=12, d_model=768, num_features=24576, k=200, batch=4096)
-JUMPRELU_THETA = 0.33  # --activation jumprelu: leaves about 200 of a token's 294,912 pre-activations active at initialisation
+SHAPES = {
+    # the headline configuration, and the Llama-3.2-1B-shaped one (16 layers, d_model 2048, 32768 features/layer)
+    "gpt2-small": dict(num_layers=12, d_model=768, num_features=24576, k=200, batch=4096, label="GPT-2-small"),
+    "llama-3.2-1b": dict(num_layers=16, d_model=2048, num_features=32768, k=200, batch=4096, label="Llama-3.2-1B"),
+}
+MODEL = dict(SHAPES["gpt2-small"])
+
+
+def jumprelu_theta() -> float:
+    """--activation jumprelu: the threshold that leaves about k of a token's L*F pre-activations active at
+    initialisation (encoder rows uniform in +-1/sqrt(F), unit-variance inputs): 0.33 for the GPT-2 shape."""
+    import math
+    from statistics import NormalDist
+
+    p = MODEL["k"] / (MODEL["num_layers"] * MODEL["num_features"])
+    return NormalDist().inv_cdf(1.0 - p) * math.sqrt(MODEL["d_model"] / (3.0 * MODEL["num_features"]))
 METRIC = "train tokens/sec (box, device-timed, max over ranks) GPT-2-small CLT 32x BatchTopK"
+
+
+def metric_name(jr: bool) -> str:
+    m = METRIC.replace("GPT-2-small", MODEL["label"])
+    if MODEL["label"] != "GPT-2-small":
+        m = m.replace("32x", f"{MODEL['num_features'] // MODEL['d_model']}x")
+    return m.replace("BatchTopK", "JumpReLU (native thresholds)") if jr else m
+
+
+def model_name(jr: bool) -> str:
+    act = f"JumpReLU theta0={jumprelu_theta():.3f}, sparsity lambda 1e-3" if jr else f"BatchTopK k={MODEL['k']}"
+    return (f"{MODEL['label']}-shaped CLT: {MODEL['num_layers']} layers, d_model {MODEL['d_model']}, {MODEL['num_features']} features/layer "
+            f"({MODEL['num_features'] // MODEL['d_model']}x), untied decoders, {act}")
 
 
 def parse_args():
@@ -40,6 +67,7 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--ref-variant", choices=["bf16_params", "autocast_fp32"], default="bf16_params")
     ap.add_argument("--pool", type=int, default=4, help="distinct synthetic batches kept in pinned host memory")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="gpt2-small", help="model shape; gpt2-small is the headline configuration")
     ap.add_argument("--parity-steps", type=int, default=0,
                     help="after the timed loops, train this many further steps over the pool and report the normalised MSE "
                          "on a held-out synthetic batch (key 'parity'); use the same value and --pool for both arms")
@@ -218,7 +246,7 @@ def run_ours(args, world, rank, local):
     host, (mean_tg, std_tg) = make_pool(args.pool, dev)
     jr = args.activation == "jumprelu"
     clt_cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k, clt_dtype="bfloat16",
-                        jumprelu_threshold=JUMPRELU_THETA)
+                        jumprelu_threshold=jumprelu_theta())
     total = args.warmup * 2 + args.steps * 2 + 8
     tc = TrainingConfig(
         learning_rate=1e-4, training_steps=max(total, 1000), train_batch_size_tokens=B, precision="bf16",
@@ -312,13 +340,12 @@ def run_ours(args, world, rank, local):
     value = B * args.steps / (ms / 1e3)
     e2e_value = B * args.steps / (e2e_ms / 1e3)
     return {
-        "metric": METRIC if not jr else METRIC.replace("BatchTopK", "JumpReLU (native thresholds)"),
+        "metric": metric_name(jr),
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded sparse-dictionary activations, random-init weights)",
         "config": {
-            "model": "GPT-2-small-shaped CLT: 12 layers, d_model 768, 24576 features/layer (32x), untied decoders, "
-                     + ("JumpReLU theta0=0.33, sparsity lambda 1e-3" if jr else "BatchTopK k=200"),
+            "model": model_name(jr),
             "global_batch": B, "seq_len": 1, "parallelism": f"tp{world}",
             "optimizer": "AdamW, fp32 moments, bf16 weights", "loss": "reconstruction + AuxK factor 1/32 (no dead features yet)",
             "l2": "per-step inputs (151 MB) and streamed weights (3.4 GB) exceed the 126 MB L2; 3 device batches cycled",
@@ -364,7 +391,7 @@ def run_reference(args, world, rank, local):
     bf16_params = args.ref_variant == "bf16_params"
     jr = args.activation == "jumprelu"
     cfg = RefCLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k,
-                       jumprelu_threshold=JUMPRELU_THETA, clt_dtype="bfloat16" if bf16_params else None)
+                       jumprelu_threshold=jumprelu_theta(), clt_dtype="bfloat16" if bf16_params else None)
     tc = RefTrainingConfig(
         learning_rate=1e-4, training_steps=1000, train_batch_size_tokens=B, precision="bf16",
         activation_path="in-memory", activation_dtype="bfloat16", normalization_method="mean_std",
@@ -452,13 +479,12 @@ def run_reference(args, world, rank, local):
         yhat = torch.stack([out[l].float() for l in range(L)])
         parity = {"steps_trained": done + args.parity_steps, "nmse_heldout": nmse_of(yhat, held[1]), "pool_batches": args.pool}
     return {
-        "metric": METRIC if not jr else METRIC.replace("BatchTopK", "JumpReLU (native thresholds)"),
+        "metric": metric_name(jr),
         "value": B * args.steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded sparse-dictionary activations, random-init weights)",
         "config": {
-            "model": "GPT-2-small-shaped CLT: 12 layers, d_model 768, 24576 features/layer (32x), untied decoders, "
-                     + ("JumpReLU theta0=0.33, sparsity lambda 1e-3" if jr else "BatchTopK k=200"),
+            "model": model_name(jr),
             "global_batch": B, "seq_len": 1, "parallelism": f"tp{world}", "variant": args.ref_variant,
             "path": "reference CrossLayerTranscoder + LossManager + average_shared_parameter_grads driven through the step "
                     "sequence of clt/training/trainer.py:661-810" + (f" (CLTTrainer itself is not importable: {trainer_note})" if trainer_note else ""),
@@ -475,6 +501,8 @@ def run_reference(args, world, rank, local):
 
 def main():
     args = parse_args()
+    MODEL.clear()
+    MODEL.update(SHAPES[args.shape])
     import torch
 
     if not torch.cuda.is_available():
