@@ -26,6 +26,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 namespace {
@@ -795,6 +796,60 @@ int clt_h5r_read_rows(void* handle, const char* path, const uint64_t* rows, uint
   Reader& r = *static_cast<Reader*>(handle);
   std::lock_guard<std::mutex> lock(r.mu);
   return read_rows_impl(r, path, rows, n, false, static_cast<uint8_t*>(out));
+}
+
+// Gather `n` rows of each of `npaths` datasets (paths separated by '\n') into caller memory: row rows[i] of
+// dataset p goes to dst_bases[p] + dst_pos[i] * dst_row_stride.  Contiguous datasets are copied straight from
+// the mapped file by `nthreads` threads (the batch assembly of a training step is a few hundred thousand small
+// row copies); filtered / chunked datasets take the serial path through the chunk cache.
+int clt_h5r_scatter_rows(void* handle, const char* paths, int npaths, const uint64_t* rows, const int64_t* dst_pos, uint64_t n,
+                         void* const* dst_bases, uint64_t dst_row_stride, int nthreads) {
+  Reader& r = *static_cast<Reader*>(handle);
+  std::lock_guard<std::mutex> lock(r.mu);
+  struct Job { const uint8_t* src; uint8_t* dst; uint64_t rb; };
+  std::vector<Job> jobs;
+  std::vector<std::string> names;
+  {
+    std::string all(paths), cur;
+    for (char c : all) { if (c == '\n') { names.push_back(cur); cur.clear(); } else cur.push_back(c); }
+    if (!cur.empty()) names.push_back(cur);
+  }
+  if (int(names.size()) != npaths) return fail("scatter_rows: path count mismatch");
+  std::vector<uint8_t> tmp;
+  for (int p = 0; p < npaths; ++p) {
+    DatasetInfo* dp;
+    if (!dataset_info(r, names[p], dp)) return -1;
+    DatasetInfo& d = *dp;
+    const uint64_t rb = d.cols * d.elem_size;
+    if (rb > dst_row_stride) return fail("scatter_rows: destination rows are too short");
+    for (uint64_t i = 0; i < n; ++i)
+      if (rows[i] >= d.rows) return fail("row index out of range");
+    if (d.layout == 1 && d.data_addr != UNDEF) {
+      if (!r.ok(d.data_addr, d.rows * rb)) return fail("dataset outside the file");
+      jobs.push_back({r.base + d.data_addr, static_cast<uint8_t*>(dst_bases[p]), rb});
+    } else {
+      tmp.resize(n * rb);
+      if (read_rows_impl(r, names[p], rows, n, false, tmp.data()) != 0) return -1;
+      uint8_t* dst = static_cast<uint8_t*>(dst_bases[p]);
+      for (uint64_t i = 0; i < n; ++i) memcpy(dst + uint64_t(dst_pos[i]) * dst_row_stride, tmp.data() + i * rb, rb);
+    }
+  }
+  if (jobs.empty() || n == 0) return 0;
+  const uint64_t total = uint64_t(jobs.size()) * n;
+  int T = nthreads < 1 ? 1 : nthreads;
+  if (uint64_t(T) > total / 256 + 1) T = int(total / 256 + 1);
+  auto work = [&](uint64_t lo, uint64_t hi) {
+    for (uint64_t k = lo; k < hi; ++k) {
+      const Job& j = jobs[k / n];
+      const uint64_t i = k % n;
+      memcpy(j.dst + uint64_t(dst_pos[i]) * dst_row_stride, j.src + rows[i] * j.rb, j.rb);
+    }
+  };
+  if (T == 1) { work(0, total); return 0; }
+  std::vector<std::thread> pool;
+  for (int t = 0; t < T; ++t) pool.emplace_back(work, total * t / T, total * (t + 1) / T);
+  for (auto& th : pool) th.join();
+  return 0;
 }
 
 int clt_h5r_read_all(void* handle, const char* path, void* out) {

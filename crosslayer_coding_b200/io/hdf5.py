@@ -156,6 +156,19 @@ class H5File:
             ds = self._ds[path] = H5Dataset(self, path)
         return ds
 
+    def scatter_rows(self, paths: Sequence[str], rows: np.ndarray, dst_pos: np.ndarray, dst_ptrs: Sequence[int],
+                     dst_row_stride: int, threads: int = 8) -> None:
+        """Copy rows ``rows[i]`` of every dataset in ``paths`` to ``dst_ptrs[p] + dst_pos[i] * dst_row_stride``
+        (raw addresses, e.g. into a pinned batch buffer) with ``threads`` native threads."""
+        rows = np.ascontiguousarray(np.asarray(rows, dtype=np.uint64))
+        pos = np.ascontiguousarray(np.asarray(dst_pos, dtype=np.int64))
+        assert len(rows) == len(pos) and len(paths) == len(dst_ptrs)
+        bases = (ctypes.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+        rc = self._lib.clt_h5r_scatter_rows(self._h, "\n".join(paths).encode(), len(paths), rows.ctypes.data_as(ctypes.c_void_p),
+                                            pos.ctypes.data_as(ctypes.c_void_p), len(rows), bases, int(dst_row_stride), int(threads))
+        if rc != 0:
+            raise OSError(native.last_error())
+
     def __getitem__(self, path: str) -> H5Dataset:
         return self.dataset(path)
 

@@ -21,7 +21,7 @@ _lib = None
 def build() -> Path:
     LIB.parent.mkdir(parents=True, exist_ok=True)
     tmp = LIB.with_suffix(f".so.{os.getpid()}.tmp")
-    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", str(tmp), str(SRC), "-lz"]
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-pthread", "-o", str(tmp), str(SRC), "-lz"]
     subprocess.run(cmd, check=True, capture_output=True)
     os.replace(tmp, LIB)
     return LIB
@@ -54,6 +54,9 @@ def load() -> ctypes.CDLL:
         lib.clt_h5r_dataset_info.argtypes = [c.c_void_p, c.c_char_p, c.POINTER(c.c_uint64)]
         lib.clt_h5r_read_rows.restype = c.c_int
         lib.clt_h5r_read_rows.argtypes = [c.c_void_p, c.c_char_p, c.c_void_p, c.c_uint64, c.c_void_p]
+        lib.clt_h5r_scatter_rows.restype = c.c_int
+        lib.clt_h5r_scatter_rows.argtypes = [c.c_void_p, c.c_char_p, c.c_int, c.c_void_p, c.c_void_p, c.c_uint64,
+                                             c.c_void_p, c.c_uint64, c.c_int]
         lib.clt_h5r_read_all.restype = c.c_int
         lib.clt_h5r_read_all.argtypes = [c.c_void_p, c.c_char_p, c.c_void_p]
         _lib = lib

@@ -43,6 +43,7 @@ class LocalActivationStore(ManifestActivationStore):
         self._files: "OrderedDict[int, hdf5.H5File]" = OrderedDict()
         self._max_open = max_open_files
         self._layer_names: Dict[int, list] = {}
+        self._gather_threads = max(1, min(16, (os.cpu_count() or 4)))
         super().__init__(
             train_batch_size_tokens=train_batch_size_tokens, device=device, dtype=dtype, rank=rank, world=world,
             seed=seed, sampling_strategy=sampling_strategy, normalization_method=normalization_method,
@@ -82,6 +83,51 @@ class LocalActivationStore(ManifestActivationStore):
             parts.append(f[f"{name}/inputs"].read_rows(row_indices).tobytes())
             parts.append(f[f"{name}/targets"].read_rows(row_indices).tobytes())
         return b"".join(parts)
+
+    def _assemble(self, idx: np.ndarray, host) -> None:
+        """Native batch assembly: every (layer, side) dataset's rows go straight from the mapped chunk file to their
+        batch positions in the pinned ``[2, L, B, d]`` buffer, copied by a pool of native threads.  (The generic path
+        of the base class builds the server's wire format first and re-orders it with numpy.)"""
+        import random
+        import time
+
+        L, d = self.num_layers, self.d_model
+        row_bytes = d * self.bytes_per_element
+        side_stride = host.stride(0) * host.element_size()
+        layer_stride = host.stride(1) * host.element_size()
+        base = host.data_ptr()
+        chunk_ids = idx[:, 0]
+        for cid in np.unique(chunk_ids):
+            pos = np.nonzero(chunk_ids == cid)[0].astype(np.int64)
+            rows = idx[pos, 1].astype(np.uint64)
+            order = np.argsort(rows, kind="stable")  # ascending file order
+            rows, pos = rows[order], pos[order]
+            delay, last = 0.2, None
+            for attempt in range(3):
+                try:
+                    f = self._open(int(cid))
+                    names = self._layer_names[int(cid)]
+                    paths, ptrs = [], []
+                    for l, name in enumerate(names):
+                        for side, key in enumerate(("inputs", "targets")):
+                            ds = f[f"{name}/{key}"]
+                            if ds.cols != d or ds.elem_size != self.bytes_per_element:
+                                raise ValueError(f"chunk {cid}: {name}/{key} has rows of {ds.cols} x {ds.elem_size} bytes")
+                            paths.append(f"{name}/{key}")
+                            ptrs.append(base + side * side_stride + l * layer_stride)
+                    f.scatter_rows(paths, rows, pos, ptrs, row_bytes, threads=self._gather_threads)
+                    last = None
+                    break
+                except Exception as exc:  # noqa: BLE001 - every failure is retried, the last one is raised
+                    last = exc
+                    bad = self._files.pop(int(cid), None)
+                    if bad is not None:
+                        bad.close()
+                    if attempt < 2:
+                        time.sleep(delay + random.random() * 0.1 * delay)
+                        delay *= 2
+            if last is not None:
+                raise RuntimeError(f"Rank {self.rank}: fetching chunk {cid} failed after 3 attempts: {last}") from last
 
     def close(self) -> None:
         super().close()

@@ -213,6 +213,7 @@ class ManifestActivationStore(BaseActivationStore):
                         self.epoch += 1
                         self.sampler.set_epoch(self.epoch)
                         continue
+                    self._producer_done = True
                     self._queue.put(("end", None, None))
                     return
                 state_after = {"epoch": self.epoch, "sampler_state": self.sampler.state_dict()}
@@ -224,6 +225,7 @@ class ManifestActivationStore(BaseActivationStore):
                         self._failed_once = True
                         logger.warning("Rank %d: skipping a batch that could not be fetched: %s", self.rank, exc)
                         continue
+                    self._producer_done = True
                     self._queue.put(("error", exc, None))
                     return
                 self.stager.submit(slot)
@@ -234,9 +236,14 @@ class ManifestActivationStore(BaseActivationStore):
                     except queue.Full:
                         continue
         except Exception as exc:  # noqa: BLE001
+            self._producer_done = True
             self._queue.put(("error", exc, None))
 
     def _ensure_thread(self) -> None:
+        # a producer that ran to the end of the epoch (or failed) has left its verdict in the queue: starting another
+        # one before the consumer has read it would queue a second, stale verdict
+        if getattr(self, "_producer_done", False):
+            return
         if self._thread is None or not self._thread.is_alive():
             self._stop.clear()
             self._thread = threading.Thread(target=self._producer, name="clt-activation-prefetch", daemon=True)
@@ -246,13 +253,17 @@ class ManifestActivationStore(BaseActivationStore):
         if self._last_slot is not None:
             self.stager.release(self._last_slot)
             self._last_slot = None
+        if getattr(self, "_epoch_ended", False):
+            raise StopIteration  # until advance_epoch() / load_state_dict()
         self._ensure_thread()
         kind, payload, state = self._queue.get()
         if kind == "end":
             self._thread = None
+            self._epoch_ended = True
             raise StopIteration
         if kind == "error":
             self._thread = None
+            self._producer_done = False  # the next call starts a new producer at the sampler's position
             raise payload
         slot = payload
         raw = self.stager.acquire(slot)
@@ -284,6 +295,8 @@ class ManifestActivationStore(BaseActivationStore):
             except queue.Empty:
                 break
         self._stop.clear()
+        self._producer_done = False
+        self._epoch_ended = False
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> Dict[str, Any]:

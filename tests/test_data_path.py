@@ -206,17 +206,23 @@ def test_local_store_truncated_chunk_raises_after_retries(dataset, monkeypatch):
     import crosslayer_coding_b200.training.data.manifest_activation_store as mod
 
     monkeypatch.setattr(mod.time, "sleep", lambda s: None)
+    # cut every chunk file short: the row data of the later datasets lies outside the file
+    for cid in range(3):
+        path = os.path.join(dataset, f"chunk_{cid}.hdf5")
+        size = os.path.getsize(path)
+        with open(path, "r+b") as f:
+            f.truncate(size // 2)
     st = LocalActivationStore(dataset, train_batch_size_tokens=16, device="cpu", dtype="float32")
-    calls = {"n": 0}
-    orig = st._fetch_slice
+    opened = {"n": 0}
+    orig = st._open
 
-    def bad(cid, rows):
-        calls["n"] += 1
-        return orig(cid, rows)[:-4]
+    def counting(cid):
+        opened["n"] += 1
+        return orig(cid)
 
-    st._fetch_slice = bad
+    st._open = counting
     with pytest.raises(RuntimeError):
         for _ in range(3):  # first failing batch is skipped, the second one ends the stream
             next(st)
-    assert calls["n"] >= 6
+    assert opened["n"] >= 6  # three attempts per failing batch
     st.close()
