@@ -8,8 +8,11 @@ flags keep working.  Differences that are deliberate:
   everywhere and folded to ``mean_std`` / ``sqrt_d_model`` (the reference only
   folds it in ``CLTConfig.from_json`` and rejects it in ``TrainingConfig``).
 * ``optimizer_states_dtype`` and ``enable_stochastic_rounding`` are live: the
-  fused Adam kernel keeps fp32 moments for bf16 weights and can round the
-  updated weight stochastically.
+  fused Adam kernel keeps fp32 moments for bf16 weights (``"model_dtype"`` and
+  ``"float32"``; the reference's torch optimizer would keep bf16 moments for bf16
+  parameters) and can round the updated weight stochastically;
+  ``optimizer_states_dtype="bfloat16"`` stores the moments of the encoder and
+  decoder weights in bf16 with stochastic rounding (fused step, untied decoders).
 """
 from __future__ import annotations
 

@@ -23,6 +23,7 @@ struct AdamHyper {
   int decoupled;         // 1: AdamW, 0: Adam (decay folded into the gradient)
   float grad_scale;      // multiplies the gathered gradient (e.g. 2/(B*d), 1/loss_scale, clip factor)
   unsigned int sr_seed;  // stochastic rounding seed; 0 = round to nearest
+  unsigned int moment_seed;  // seed for the stochastic rounding of bf16 moments (changes every step)
 };
 
 __device__ __forceinline__ uint32_t hash32(uint32_t x) {
@@ -147,6 +148,7 @@ struct DecAdamParams {
   float* norm2_out;            // optional [L * F_pitch]: sum of squares of the updated rows (atomicAdd; zeroed by caller)
   const float* feat_offset;    // tied decoders: optional [L, F_pitch] affine applied to the activation
   const float* feat_scale;
+  int moments_bf16;            // bulk pipeline only: m / v hold bf16 (stochastically rounded) instead of fp32
   const float* dgrad_row0;     // optional [ntensors, F_pitch, d] fp32: extra gradient of every feature's first row
                                // (the same-layer decoder row that the auxiliary loss trains)
   AdamHyper h;
@@ -392,7 +394,7 @@ __device__ __forceinline__ void stbf(__nv_bfloat16* p, const float (&o)[EPT], un
   }
 }
 
-template <typename WT, bool SR, int EPT>
+template <typename WT, bool SR, int EPT, typename MT>
 __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAdamParams p, int gthreads, int stage_bytes, int* status) {
   extern __shared__ __align__(128) uint8_t smem_raw_adam[];  // bulk copies need 16-byte alignment only
   uint8_t* ring = smem_raw_adam;
@@ -404,7 +406,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
   long long n_rows = 0;
   for (int ti = 0; ti < p.ntensors; ++ti) n_rows += 1LL * (nf > 0 ? nf : 0) * p.rows[ti];
   const int n = int(n_rows);
-  const uint32_t w_bytes = uint32_t(d) * sizeof(WT), mv_bytes = uint32_t(d) * 4u, gs_bytes = uint32_t(d) * 2u;
+  const uint32_t w_bytes = uint32_t(d) * sizeof(WT), mv_bytes = uint32_t(d) * sizeof(MT), gs_bytes = uint32_t(d) * 2u;
   const uint32_t off_w = 64, off_m = off_w + w_bytes, off_v = off_m + mv_bytes, off_gs = off_v + mv_bytes;
   if (tid == 0) {
     for (int s = 0; s < kAdamStages; ++s) {
@@ -460,8 +462,8 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       const int nslot = ne < kAdamSlots ? ne : kAdamSlots;
       mbar_expect_tx(&sh->full[st], w_bytes + 2u * mv_bytes + uint32_t(nslot) * gs_bytes);
       bulk_load_1d_hint(stage + off_w, static_cast<const WT*>(p.w[ti]) + elem_off, w_bytes, &sh->full[st], pol_stream);
-      bulk_load_1d_hint(stage + off_m, p.m[ti] + elem_off, mv_bytes, &sh->full[st], pol_stream);
-      bulk_load_1d_hint(stage + off_v, p.v[ti] + elem_off, mv_bytes, &sh->full[st], pol_stream);
+      bulk_load_1d_hint(stage + off_m, reinterpret_cast<const MT*>(p.m[ti]) + elem_off, mv_bytes, &sh->full[st], pol_stream);
+      bulk_load_1d_hint(stage + off_v, reinterpret_cast<const MT*>(p.v[ti]) + elem_off, mv_bytes, &sh->full[st], pol_stream);
       const __nv_bfloat16* gs_t = p.gs + 1LL * (ti + r) * B * d;
 #pragma unroll
       for (int j = 0; j < kAdamSlots; ++j)
@@ -489,8 +491,8 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       const int sti = h->ti;
       const long long eo = h->elem_off;
       bulk_store_1d_hint(static_cast<WT*>(p.w[sti]) + eo, stage + off_w, w_bytes, pol_stream);
-      bulk_store_1d_hint(p.m[sti] + eo, stage + off_m, mv_bytes, pol_stream);
-      bulk_store_1d_hint(p.v[sti] + eo, stage + off_v, mv_bytes, pol_stream);
+      bulk_store_1d_hint(reinterpret_cast<MT*>(p.m[sti]) + eo, stage + off_m, mv_bytes, pol_stream);
+      bulk_store_1d_hint(reinterpret_cast<MT*>(p.v[sti]) + eo, stage + off_v, mv_bytes, pol_stream);
       bulk_commit();
       if (i >= 1 && issued < n) {
         bulk_wait_read<1>();  // the stores of row i - 1 have read their stage: it can be refilled
@@ -531,13 +533,18 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
 #pragma unroll
       for (int q = 0; q < EPT; ++q) { g[q] = 0.f; w[q] = 0.f; }
       WT* w_s = reinterpret_cast<WT*>(stage + off_w) + e0;
-      float* m_s = reinterpret_cast<float*>(stage + off_m) + e0;
-      float* v_s = reinterpret_cast<float*>(stage + off_v) + e0;
+      MT* m_s = reinterpret_cast<MT*>(stage + off_m) + e0;
+      MT* v_s = reinterpret_cast<MT*>(stage + off_v) + e0;
       if (act) {
         if (sizeof(WT) == 2) ldbf<EPT>(reinterpret_cast<const __nv_bfloat16*>(w_s), w);
         else ldf<EPT>(reinterpret_cast<const float*>(w_s), w);
-        ldf<EPT>(m_s, m);
-        ldf<EPT>(v_s, v);
+        if (sizeof(MT) == 2) {
+          ldbf<EPT>(reinterpret_cast<const __nv_bfloat16*>(m_s), m);
+          ldbf<EPT>(reinterpret_cast<const __nv_bfloat16*>(v_s), v);
+        } else {
+          ldf<EPT>(reinterpret_cast<const float*>(m_s), m);
+          ldf<EPT>(reinterpret_cast<const float*>(v_s), v);
+        }
         const __nv_bfloat16* gs_s = reinterpret_cast<const __nv_bfloat16*>(stage + off_gs) + e0;
 #pragma unroll
         for (int j = 0; j < kAdamSlots; ++j) {
@@ -587,11 +594,32 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
           adam1(w[q], m[q], v[q], gq, hr);
           norm2 = fmaf(w[q], w[q], norm2);
         }
-        stf<EPT>(m_s, m);
-        stf<EPT>(v_s, v);
         const unsigned long long gidx = (unsigned long long)(p.row_start[ti] * d + h->elem_off + e0);
         if (sizeof(WT) == 2) stbf<EPT, SR>(reinterpret_cast<__nv_bfloat16*>(w_s), w, p.h.sr_seed, (unsigned int)gidx);
         else stf<EPT>(reinterpret_cast<float*>(w_s), w);
+        if (sizeof(MT) == 2) {
+          // bf16 moments are always rounded stochastically: with beta2 = 0.999 a nearest rounding would freeze v
+          // one hash per thread and row seeds a linear congruential stream: two 16-bit dither values per element
+          uint32_t rng = hash32((unsigned int)gidx ^ p.h.moment_seed);
+          __nv_bfloat16* mo = reinterpret_cast<__nv_bfloat16*>(m_s);
+          __nv_bfloat16* vo = reinterpret_cast<__nv_bfloat16*>(v_s);
+#pragma unroll
+          for (int q = 0; q < EPT; q += 2) {
+            uint32_t hm[2], hv[2];
+#pragma unroll
+            for (int z = 0; z < 2; ++z) {
+              rng = rng * 1664525u + 1013904223u;
+              const uint32_t um = __float_as_uint(m[q + z]), uv = __float_as_uint(v[q + z]);
+              hm[z] = ((um & 0x7F800000u) == 0x7F800000u) ? (um >> 16) : ((um + (rng >> 16)) >> 16);
+              hv[z] = ((uv & 0x7F800000u) == 0x7F800000u) ? (uv >> 16) : ((uv + ((rng * 0x9E3779B1u) >> 16)) >> 16);
+            }
+            *reinterpret_cast<uint32_t*>(mo + q) = hm[0] | (hm[1] << 16);
+            *reinterpret_cast<uint32_t*>(vo + q) = hv[0] | (hv[1] << 16);
+          }
+        } else {
+          stf<EPT>(reinterpret_cast<float*>(m_s), m);
+          stf<EPT>(reinterpret_cast<float*>(v_s), v);
+        }
       }
       if (r == R - 1) {
         if (p.grad_a != nullptr) {
@@ -936,11 +964,12 @@ struct CltAdamHyper {
   int decoupled;
   float grad_scale;
   unsigned int sr_seed;
+  unsigned int moment_seed;
 };
 static AdamHyper to_hyper(const CltAdamHyper& c) {
   AdamHyper h;
   h.lr = c.lr; h.beta1 = c.beta1; h.beta2 = c.beta2; h.eps = c.eps; h.weight_decay = c.weight_decay;
-  h.bc1 = c.bc1; h.bc2 = c.bc2; h.decoupled = c.decoupled; h.grad_scale = c.grad_scale; h.sr_seed = c.sr_seed;
+  h.bc1 = c.bc1; h.bc2 = c.bc2; h.decoupled = c.decoupled; h.grad_scale = c.grad_scale; h.sr_seed = c.sr_seed; h.moment_seed = c.moment_seed;
   return h;
 }
 
@@ -953,14 +982,16 @@ struct CltDecAdamArgs {
   const float* dgrad_row0;
   CltAdamHyper h;
   int* status;  // when given, untied decoders use the bulk-copy pipeline (its bounded waits report here)
+  int moments_bf16;  // m / v are bf16 tensors (bulk pipeline with bf16 weights only)
 };
 
 // Launch geometry of the bulk-copy row pipeline (shared by the decoder and the encoder update).
-static int bulk_rows_adam_geometry(int d, bool weights_bf16, int* ept_out, int* gthreads_out, int* stage_bytes_out, size_t* smem_out) {
+static int bulk_rows_adam_geometry(int d, bool weights_bf16, bool moments_bf16, int* ept_out, int* gthreads_out, int* stage_bytes_out, size_t* smem_out) {
   const int ept = d <= 1024 ? 4 : 8;  // elements per consumer thread: more, shorter threads where the row allows
   const int gthreads = ((d / ept + 31) / 32) * 32;
   const size_t wsz = weights_bf16 ? 2 : 4;
-  const int stage_bytes = int(((64 + size_t(d) * (wsz + 8 + 2 * kAdamSlots)) + 127) / 128 * 128);
+  const size_t msz = moments_bf16 ? 2 : 4;
+  const int stage_bytes = int(((64 + size_t(d) * (wsz + 2 * msz + 2 * kAdamSlots)) + 127) / 128 * 128);
   const size_t smem = size_t(kAdamStages) * stage_bytes + sizeof(AdamBulkShared) + 256;
   *ept_out = ept; *gthreads_out = gthreads; *stage_bytes_out = stage_bytes; *smem_out = smem;
   return (d % 8 == 0 && gthreads <= 256 && smem <= 200 * 1024) ? 1 : 0;
@@ -968,12 +999,14 @@ static int bulk_rows_adam_geometry(int d, bool weights_bf16, int* ept_out, int* 
 static bool bulk_rows_adam_fits(int d, int weights_bf16) {
   int ept, gthreads, stage_bytes;
   size_t smem;
-  return bulk_rows_adam_geometry(d, weights_bf16 != 0, &ept, &gthreads, &stage_bytes, &smem) != 0;
+  return bulk_rows_adam_geometry(d, weights_bf16 != 0, false, &ept, &gthreads, &stage_bytes, &smem) != 0;
 }
 static int launch_rows_adam_bulk(const DecAdamParams& p, bool weights_bf16, bool sr, int num_sms, int* status, cudaStream_t st) {
   int ept, gthreads, stage_bytes;
   size_t smem;
-  if (!bulk_rows_adam_geometry(p.d, weights_bf16, &ept, &gthreads, &stage_bytes, &smem)) return -1;
+  const bool mb = p.moments_bf16 != 0;
+  if (mb && !weights_bf16) return -1;  // bf16 moments go with bf16 weights
+  if (!bulk_rows_adam_geometry(p.d, weights_bf16, mb, &ept, &gthreads, &stage_bytes, &smem)) return -1;
   int per_sm = int((227 * 1024) / (smem + 1024));
   const int by_threads = 2048 / (gthreads + 32);
   per_sm = per_sm > by_threads ? by_threads : per_sm;
@@ -981,7 +1014,7 @@ static int launch_rows_adam_bulk(const DecAdamParams& p, bool weights_bf16, bool
   int bgrid = num_sms * per_sm;
   if (bgrid > p.F_pitch) bgrid = p.F_pitch;
   auto launch = [&](auto kern, int which) -> int {
-    static size_t attr_set[6] = {0, 0, 0, 0, 0, 0};
+    static size_t attr_set[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     if (attr_set[which] < smem) {
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
       attr_set[which] = smem;
@@ -989,12 +1022,17 @@ static int launch_rows_adam_bulk(const DecAdamParams& p, bool weights_bf16, bool
     kern<<<bgrid, gthreads + 32, smem, st>>>(p, gthreads, stage_bytes, status);
     return 0;
   };
-  if (ept == 4) {
-    if (weights_bf16) return sr ? launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, true, 4>, 0) : launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, false, 4>, 1);
-    return launch(decoder_rows_adam_bulk_kernel<float, false, 4>, 2);
+  using bf = __nv_bfloat16;
+  if (mb) {
+    if (ept == 4) return sr ? launch(decoder_rows_adam_bulk_kernel<bf, true, 4, bf>, 6) : launch(decoder_rows_adam_bulk_kernel<bf, false, 4, bf>, 7);
+    return sr ? launch(decoder_rows_adam_bulk_kernel<bf, true, 8, bf>, 8) : launch(decoder_rows_adam_bulk_kernel<bf, false, 8, bf>, 9);
   }
-  if (weights_bf16) return sr ? launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, true, 8>, 3) : launch(decoder_rows_adam_bulk_kernel<__nv_bfloat16, false, 8>, 4);
-  return launch(decoder_rows_adam_bulk_kernel<float, false, 8>, 5);
+  if (ept == 4) {
+    if (weights_bf16) return sr ? launch(decoder_rows_adam_bulk_kernel<bf, true, 4, float>, 0) : launch(decoder_rows_adam_bulk_kernel<bf, false, 4, float>, 1);
+    return launch(decoder_rows_adam_bulk_kernel<float, false, 4, float>, 2);
+  }
+  if (weights_bf16) return sr ? launch(decoder_rows_adam_bulk_kernel<bf, true, 8, float>, 3) : launch(decoder_rows_adam_bulk_kernel<bf, false, 8, float>, 4);
+  return launch(decoder_rows_adam_bulk_kernel<float, false, 8, float>, 5);
 }
 
 extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st) {
@@ -1012,6 +1050,8 @@ extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaS
   p.feat_off = a->feat_off; p.fcsr_tok = a->fcsr_tok; p.fcsr_val = a->fcsr_val;
   p.gs = static_cast<const __nv_bfloat16*>(a->gs); p.grad_a = a->grad_a; p.pen_coef = a->pen_coef; p.norm2_out = a->norm2_out;
   p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale; p.dgrad_row0 = a->dgrad_row0; p.h = to_hyper(a->h);
+  p.moments_bf16 = a->moments_bf16;
+  if (a->moments_bf16 && !(a->tying == 0 && a->status != nullptr && a->weights_bf16)) return -6;  // only the bulk pipeline handles bf16 moments
   if (acc == 0) return 0;
   const int grid = num_sms * 8;
   if (a->tying == 0 && a->status != nullptr && bulk_rows_adam_fits(a->d, a->weights_bf16) && acc * a->d < (1LL << 62)) {
@@ -1040,6 +1080,7 @@ struct CltEncAdamArgs {
   const float* dense_grad; const float* dense_bias_grad;
   CltAdamHyper h;
   int* status;  // when given, the weight rows go through the bulk-copy pipeline
+  int moments_bf16;
 };
 
 extern "C" int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaStream_t st) {
@@ -1059,7 +1100,10 @@ extern "C" int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaS
     for (int i = 0; i < kMaxLayersA; ++i) {
       const int l = i < a->L ? i : 0;
       q.w[i] = static_cast<char*>(a->w) + size_t(l) * per_layer * wsz;
-      q.m[i] = a->m + l * per_layer; q.v[i] = a->v + l * per_layer; q.rows[i] = 1;
+      const size_t msz = a->moments_bf16 ? 2 : 4;
+      q.m[i] = reinterpret_cast<float*>(reinterpret_cast<char*>(a->m) + size_t(l) * per_layer * msz);
+      q.v[i] = reinterpret_cast<float*>(reinterpret_cast<char*>(a->v) + size_t(l) * per_layer * msz);
+      q.rows[i] = 1;
       q.row_start[i] = 1LL * (i < a->L ? i : a->L) * a->F_pitch;
     }
     q.row_start[kMaxLayersA] = 1LL * a->L * a->F_pitch;
@@ -1067,6 +1111,7 @@ extern "C" int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaS
     q.feat_off = a->feat_off; q.fcsr_tok = a->fcsr_tok; q.fcsr_val = a->delta; q.gs = p.x;
     q.grad_a = nullptr; q.pen_coef = nullptr; q.norm2_out = nullptr; q.feat_offset = nullptr; q.feat_scale = nullptr;
     q.dgrad_row0 = a->dense_grad; q.h = p.h;
+    q.moments_bf16 = a->moments_bf16;
     const int rc = launch_rows_adam_bulk(q, a->weights_bf16 != 0, a->h.sr_seed != 0, num_sms, a->status, st);
     if (rc != 0) return rc;
     if (p.bias != nullptr) {
@@ -1074,6 +1119,8 @@ extern "C" int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaS
       if (a->weights_bf16) encoder_bias_adam_kernel<__nv_bfloat16><<<bgrid, 256, 0, st>>>(p);
       else encoder_bias_adam_kernel<float><<<bgrid, 256, 0, st>>>(p);
     }
+  } else if (a->moments_bf16) {
+    return -6;  // only the bulk pipeline handles bf16 moments
   } else if (a->weights_bf16) encoder_rows_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
   else encoder_rows_adam_kernel<float><<<grid, 256, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

@@ -104,6 +104,7 @@ struct CltAdamHyper {
   int decoupled;
   float grad_scale;
   unsigned int sr_seed;
+  unsigned int moment_seed;
 };
 struct CltDecAdamArgs {
   void* w[32]; float* m[32]; float* v[32]; int rows[32];
@@ -114,6 +115,7 @@ struct CltDecAdamArgs {
   const float* dgrad_row0;
   CltAdamHyper h;
   int* status;
+  int moments_bf16;
 };
 int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st);
 struct CltEncAdamArgs {
@@ -123,6 +125,7 @@ struct CltEncAdamArgs {
   const float* dense_grad; const float* dense_bias_grad;
   CltAdamHyper h;
   int* status;
+  int moments_bf16;
 };
 int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaStream_t st);
 int clt_dense_adam(void* w, float* m, float* v, const float* grad, long long n, int weights_bf16, const CltAdamHyper* h, cudaStream_t st);
@@ -155,10 +158,11 @@ T* opt_ptr(const OptTensor& t) {
 }
 
 CltAdamHyper hyper_from(const std::vector<double>& h) {
-  TORCH_CHECK(h.size() == 10, "hyper expects 10 values");
+  TORCH_CHECK(h.size() == 10 || h.size() == 11, "hyper expects 10 values (+ the moment rounding seed)");
   CltAdamHyper c;
   c.lr = float(h[0]); c.beta1 = float(h[1]); c.beta2 = float(h[2]); c.eps = float(h[3]); c.weight_decay = float(h[4]);
   c.bc1 = float(h[5]); c.bc2 = float(h[6]); c.decoupled = int(h[7]); c.grad_scale = float(h[8]); c.sr_seed = static_cast<unsigned int>(h[9]);
+  c.moment_seed = h.size() > 10 ? static_cast<unsigned int>(h[10]) : 0x1234567u;
   return c;
 }
 
@@ -397,9 +401,11 @@ void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vect
   std::memset(&a, 0, sizeof(a));
   const bool bf16 = w[0].scalar_type() == at::kBFloat16;
   for (size_t i = 0; i < w.size(); ++i) {
-    need(w[i], bf16 ? at::kBFloat16 : at::kFloat, "w"); need(m[i], at::kFloat, "m"); need(v[i], at::kFloat, "v");
+    need(w[i], bf16 ? at::kBFloat16 : at::kFloat, "w");
+    need(m[i], m[0].scalar_type(), "m"); need(v[i], m[0].scalar_type(), "v");
+    TORCH_CHECK(m[0].scalar_type() == at::kFloat || m[0].scalar_type() == at::kBFloat16, "moments must be fp32 or bf16");
     TORCH_CHECK(w[i].dim() == 3 && w[i].size(0) == F_pitch && w[i].size(2) == d, "decoder tensor must be [F, R, d]");
-    a.w[i] = w[i].data_ptr(); a.m[i] = m[i].data_ptr<float>(); a.v[i] = v[i].data_ptr<float>(); a.rows[i] = int(w[i].size(1));
+    a.w[i] = w[i].data_ptr(); a.m[i] = static_cast<float*>(m[i].data_ptr()); a.v[i] = static_cast<float*>(v[i].data_ptr()); a.rows[i] = int(w[i].size(1));
   }
   a.ntensors = int(w.size()); a.L = int(L); a.B = int(B); a.d = int(d); a.F_pitch = int(F_pitch); a.tying = int(tying); a.weights_bf16 = bf16;
   a.feat_off = feat_off.data_ptr<int>(); a.fcsr_tok = fcsr_tok.data_ptr<int>(); a.fcsr_val = fcsr_val.data_ptr<float>();
@@ -410,6 +416,7 @@ void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vect
   if (a.dgrad_row0) TORCH_CHECK(dgrad_row0->scalar_type() == at::kFloat && dgrad_row0->numel() == int64_t(w.size()) * F_pitch * d, "dgrad_row0 must be fp32 [ntensors, F, d]");
   a.h = hyper_from(hyper);
   a.status = opt_ptr<int>(status);
+  a.moments_bf16 = m[0].scalar_type() == at::kBFloat16 ? 1 : 0;
   c10::cuda::CUDAGuard guard(gs.device());
   check(clt_decoder_rows_adam(&a, num_sms(), cur_stream()), "decoder_rows_adam");
 }
@@ -418,12 +425,14 @@ void encoder_rows_adam(Tensor& w, Tensor& m, Tensor& v, Tensor& bias, Tensor& bi
                        const Tensor& fcsr_tok, const Tensor& delta, const Tensor& x, const OptTensor& dense_grad,
                        const OptTensor& dense_bias_grad, const std::vector<double>& hyper, const OptTensor& status) {
   const bool bf16 = w.scalar_type() == at::kBFloat16;
-  need(w, bf16 ? at::kBFloat16 : at::kFloat, "w"); need(m, at::kFloat, "m"); need(v, at::kFloat, "v");
+  const bool mbf16 = m.scalar_type() == at::kBFloat16;
+  need(w, bf16 ? at::kBFloat16 : at::kFloat, "w"); need(m, mbf16 ? at::kBFloat16 : at::kFloat, "m"); need(v, mbf16 ? at::kBFloat16 : at::kFloat, "v");
   need(bias, bf16 ? at::kBFloat16 : at::kFloat, "bias"); need(bias_m, at::kFloat, "bias_m"); need(bias_v, at::kFloat, "bias_v");
   need(x, at::kBFloat16, "x"); need(delta, at::kFloat, "delta");
   CltEncAdamArgs a;
   std::memset(&a, 0, sizeof(a));
-  a.w = w.data_ptr(); a.m = m.data_ptr<float>(); a.v = v.data_ptr<float>();
+  a.w = w.data_ptr(); a.m = static_cast<float*>(m.data_ptr()); a.v = static_cast<float*>(v.data_ptr());
+  a.moments_bf16 = mbf16 ? 1 : 0;
   a.bias = bias.data_ptr(); a.bias_m = bias_m.data_ptr<float>(); a.bias_v = bias_v.data_ptr<float>();
   a.L = int(w.size(0)); a.F_pitch = int(w.size(1)); a.d = int(w.size(2)); a.B = int(x.size(1)); a.weights_bf16 = bf16;
   a.feat_off = feat_off.data_ptr<int>(); a.fcsr_tok = fcsr_tok.data_ptr<int>(); a.delta = delta.data_ptr<float>(); a.x = x.data_ptr();

@@ -26,7 +26,7 @@ CASES = {
 }
 
 
-def build(case: str, device: torch.device, activation: str = "batchtopk"):
+def build(case: str, device: torch.device, activation: str = "batchtopk", states: str = "float32"):
     from .. import CLTConfig, CrossLayerTranscoder, TrainingConfig
     from ..training.fused_engine import FusedBatchTopKEngine
 
@@ -47,7 +47,7 @@ def build(case: str, device: torch.device, activation: str = "batchtopk"):
             model.log_threshold.fill_(math.log(max(theta0, 1e-6)))
         lam = 1e-3
     tc = TrainingConfig(learning_rate=1e-4, training_steps=1000, activation_path="unused", precision="bf16",
-                        sparsity_lambda=lam, preactivation_coef=0.0)
+                        sparsity_lambda=lam, preactivation_coef=0.0, optimizer_states_dtype=states)
     eng = FusedBatchTopKEngine(model, tc, B)
     X = torch.randn(L, B, d, device=device).bfloat16()
     Y = torch.randn(L, B, d, device=device).bfloat16()
@@ -70,13 +70,15 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--case", choices=sorted(CASES), default="full")
     ap.add_argument("--activation", choices=["batchtopk", "jumprelu"], default="batchtopk")
+    ap.add_argument("--optimizer-states", choices=["float32", "bfloat16"], default="float32",
+                    help="moment dtype of the encoder / decoder weights (bfloat16: stochastically rounded, 12 B/param/step)")
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--lr", type=float, default=None,
                     help="learning rate (default 1e-4; 1e-8 for jumprelu so that the active count of the synthetic data stays put)")
     ap.add_argument("--time", action="store_true", help="print CUDA-event timings instead of marking a profiler range")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
-    model, eng, X, Y = build(args.case, dev, args.activation)
+    model, eng, X, Y = build(args.case, dev, args.activation, args.optimizer_states)
     lam = eng.tc.sparsity_lambda
     lr = args.lr if args.lr is not None else (1e-8 if args.activation == "jumprelu" else 1e-4)
     L, d, F, B, k = CASES[args.case]
@@ -92,7 +94,7 @@ def main() -> None:
             step[0] += 1
 
         res = {
-            "case": args.case, "activation": args.activation,
+            "case": args.case, "activation": args.activation, "optimizer_states": args.optimizer_states,
             "encoder_gemm_ms": _best_of(lambda: e.encoder_gemm(X, model.enc_weight.data, model.enc_bias.data, eng.preact, eng.status)),
             "library_bmm_ms": _best_of(lambda: torch.bmm(X, model.enc_weight.data.transpose(1, 2))),
             "encode_select_ms": _best_of(lambda: eng.encode_select(X)),

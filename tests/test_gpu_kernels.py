@@ -599,3 +599,37 @@ def test_fused_jumprelu_step_matches_autograd(lam):
         if touched.any() and "log_threshold" not in name:  # a 1e-3 step is below the bf16 spacing of log theta
             agree = (torch.sign(upd[touched]) == torch.sign(ref_upd[touched])).float().mean().item()
             assert agree > 0.97, (name, agree)
+
+
+def test_fused_step_with_bf16_moments_tracks_fp32_moments():
+    """optimizer_states_dtype='bfloat16': stochastically rounded bf16 moments; the run stays close to fp32 moments."""
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder, TrainingConfig
+    from crosslayer_coding_b200.training.fused_engine import FusedBatchTopKEngine
+
+    dev = _dev()
+    L, d, F, B, k = 2, 64, 512, 128, 16
+    runs = {}
+    for states in ("float32", "bfloat16"):
+        torch.manual_seed(31)
+        cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="batchtopk", batchtopk_k=k, clt_dtype="bfloat16")
+        model = CrossLayerTranscoder(cfg, device=dev)
+        tc = TrainingConfig(learning_rate=2e-3, training_steps=100, activation_path="unused", precision="bf16", sparsity_lambda=0.0,
+                            preactivation_coef=0.0, optimizer_states_dtype=states)
+        eng = FusedBatchTopKEngine(model, tc, B)
+        assert eng.dec_m[0].dtype == (torch.bfloat16 if states == "bfloat16" else torch.float32)
+        g = torch.Generator(device="cpu").manual_seed(5)
+        X = torch.randn(L, B, d, generator=g).bfloat16().to(dev)
+        A = torch.randn(d, d, generator=g) / math.sqrt(d)
+        Y = (X.float().cpu() @ A).bfloat16().to(dev)
+        losses = [eng.train_step(X, Y, step=s, lr=2e-3).reconstruction.item() for s in range(40)]
+        eng.check_status()
+        runs[states] = (losses, model.dec_weight[0].detach().float().clone(), eng.dec_v[0].float().clone())
+    lf, wf, vf = runs["float32"]
+    lb, wb, vb = runs["bfloat16"]
+    assert lb[-1] < 0.8 * lb[0], lb[::8]
+    assert abs(lb[-1] - lf[-1]) < 0.05 * lf[-1], (lb[-1], lf[-1])
+    # second moments agree on average (stochastic rounding is unbiased) although single entries differ
+    touched = vf > 1e-12
+    ratio = (vb[touched] / vf[touched]).mean().item()
+    assert 0.9 < ratio < 1.1, ratio
+    assert ((wb - wf).abs().mean() / wf.abs().mean()).item() < 0.05
