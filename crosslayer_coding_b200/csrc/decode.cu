@@ -197,6 +197,8 @@ struct DecodeBulkShared {
   const __nv_bfloat16* w_s[kMaxLayers];
   int rows_s[kMaxLayers];
   int abort_flag;
+  int ent_sl[kDecodeStages];    // source layer and activation of the entry in each stage, written by the producer
+  float ent_a[kDecodeStages];
 };
 
 template <int TPG>
@@ -230,15 +232,24 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   if (is_producer) {
     if (threadIdx.x == nconsumer) {
       int issued = 0;
+      int col_next = b < e ? __ldg(p.tcsr_col + b) : 0;
+      float a_next = b < e ? __ldg(p.tcsr_val + b) : 0.f;
       for (int i = b; i < e; ++i, ++issued) {
         const int st = issued % kDecodeStages;
         const uint32_t ph = (issued / kDecodeStages) & 1;
+        const int col = col_next;
+        const float a = a_next;
+        if (i + 1 < e) {  // the next entry's index is in flight while this stage is waited for
+          col_next = __ldg(p.tcsr_col + i + 1);
+          a_next = __ldg(p.tcsr_val + i + 1);
+        }
         if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) break;
-        const int col = __ldg(p.tcsr_col + i);
         const int sl = col >> 24, f = col & 0xFFFFFF;
         const int R = sh->rows_s[sl];
         const uint32_t bytes = uint32_t(R) * uint32_t(d) * 2u;
-        mbar_expect_tx(&sh->full[st], bytes);
+        sh->ent_sl[st] = sl;
+        sh->ent_a[st] = a;
+        mbar_expect_tx(&sh->full[st], bytes);  // release: the two words above are visible to whoever sees the phase
         bulk_load_1d(ring + size_t(st) * stage_bytes, sh->w_s[sl] + 1LL * f * R * d, bytes, &sh->full[st]);
       }
       if (*abort_flag) {
@@ -268,9 +279,8 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
       const int st = it % kDecodeStages;
       const uint32_t ph = (it / kDecodeStages) & 1;
       if (!mbar_wait(&sh->full[st], ph, abort_flag)) { ok = false; break; }
-      const int col = __ldg(p.tcsr_col + i);
-      const float a = __ldg(p.tcsr_val + i);
-      const int sl = col >> 24;
+      const int sl = sh->ent_sl[st];
+      const float a = sh->ent_a[st];
       if (active && a != 0.f) {
         const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(ring + size_t(st) * stage_bytes) + e0;
 #pragma unroll
