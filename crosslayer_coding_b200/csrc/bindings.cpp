@@ -12,7 +12,8 @@ using OptTensor = c10::optional<Tensor>;
 
 extern "C" {
 int clt_encoder_gemm(const void* A, const void* B, const void* bias, void* C, int L, int M, int N, int K, long long ldc,
-                     long long layer_stride_c, int* status, int num_sms, cudaStream_t stream);
+                     long long layer_stride_c, int* status, float* tile_stats, int num_sms, cudaStream_t stream);
+int clt_colstats_from_tiles(const float* tile_stats, float* mean, float* rstd, int L, int B, int F, cudaStream_t st);
 int clt_colstats(const void* x, float* mean, float* rstd, int L, int B, int F, long long ld, long long layer_stride, cudaStream_t st);
 
 struct CltExchangeArgs {
@@ -167,15 +168,32 @@ CltAdamHyper hyper_from(const std::vector<double>& h) {
 }
 
 // ----------------------------------------------------------------------------------------------
-void encoder_gemm(const Tensor& x, const Tensor& w, const OptTensor& bias, Tensor& out, Tensor& status) {
+// tile_stats (optional, fp32 [L, ceil(M / 128), N, 2]): per 128-row block sums / sums of squares of the stored outputs.
+void encoder_gemm(const Tensor& x, const Tensor& w, const OptTensor& bias, Tensor& out, Tensor& status, const OptTensor& tile_stats) {
   need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w"); need(out, at::kBFloat16, "out"); need(status, at::kInt, "status");
   TORCH_CHECK(x.dim() == 3 && w.dim() == 3 && out.dim() == 3, "expected [L, M, K], [L, N, K], [L, M, N]");
   const int L = x.size(0), M = x.size(1), K = x.size(2), N = w.size(1);
   TORCH_CHECK(w.size(0) == L && w.size(2) == K && out.size(0) == L && out.size(1) == M && out.size(2) == N, "shape mismatch");
   if (bias.has_value() && bias->defined()) { need(*bias, at::kBFloat16, "bias"); TORCH_CHECK(bias->numel() == 1LL * L * N, "bias must be [L, N]"); }
+  float* ts = nullptr;
+  if (tile_stats.has_value() && tile_stats->defined()) {
+    need(*tile_stats, at::kFloat, "tile_stats");
+    TORCH_CHECK(tile_stats->numel() == 2LL * L * ((M + 127) / 128) * N, "tile_stats must be [L, ceil(M / 128), N, 2]");
+    ts = tile_stats->data_ptr<float>();
+  }
   c10::cuda::CUDAGuard guard(x.device());
   check(clt_encoder_gemm(x.data_ptr(), w.data_ptr(), opt_ptr<void>(bias), out.data_ptr(), L, M, N, K, N, 1LL * M * N,
-                         status.data_ptr<int>(), num_sms(), cur_stream()), "encoder_gemm");
+                         status.data_ptr<int>(), ts, num_sms(), cur_stream()), "encoder_gemm");
+}
+
+// mean / rstd [L, F] from the per-block sums written by encoder_gemm (B rows per column).
+void colstats_from_tiles(const Tensor& tile_stats, Tensor& mean, Tensor& rstd, int64_t B) {
+  need(tile_stats, at::kFloat, "tile_stats"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd");
+  TORCH_CHECK(tile_stats.dim() == 4 && tile_stats.size(3) == 2 && tile_stats.size(1) == (B + 127) / 128, "tile_stats must be [L, ceil(B / 128), F, 2]");
+  const int L = tile_stats.size(0), F = tile_stats.size(2);
+  TORCH_CHECK(mean.numel() == 1LL * L * F && rstd.numel() == 1LL * L * F, "mean/rstd must be [L, F]");
+  c10::cuda::CUDAGuard guard(tile_stats.device());
+  check(clt_colstats_from_tiles(tile_stats.data_ptr<float>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), L, int(B), F, cur_stream()), "colstats_from_tiles");
 }
 
 void colstats(const Tensor& x, Tensor& mean, Tensor& rstd) {
@@ -477,6 +495,7 @@ void sparsity_penalty(const Tensor& feat_off, const Tensor& fcsr_val, const Tens
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("encoder_gemm", &encoder_gemm);
   m.def("colstats", &colstats);
+  m.def("colstats_from_tiles", &colstats_from_tiles);
   m.def("batchtopk_select", &batchtopk_select);
   m.def("threshold_select", &threshold_select);
   m.def("theta_grad_gemm", &theta_grad_gemm);

@@ -30,7 +30,7 @@ constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 // ring + 1024 B alignment slack + barriers/bias
-constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 4 * 4096 + 1024 + 2048;  // ring + epilogue staging + slack + barriers
+constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 4 * 4096 + 1024 + 4096;  // ring + epilogue staging + slack + barriers
 }  // namespace gemm
 
 // Epilogue of one 32-row slab (one warp, lane = row): TMEM -> registers -> + bias -> bf16 -> shared staging
@@ -40,8 +40,11 @@ constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 4 * 4096 + 1024 + 2
 constexpr int kEpiCols = 64;
 constexpr uint32_t kEpiStageBytes = 32 * kEpiCols * 2;
 
+// With `colacc` (shared, [2][BN] floats: sums and sums of squares per tile column) the slab's column statistics
+// of the rounded bf16 values are read back from the staging tile (each lane owns two adjacent columns) and
+// added up over the tile's four slabs; `nrows` masks the rows beyond the matrix.
 __device__ __forceinline__ void epilogue_slab(uint32_t taddr, const CUtensorMap* map_c, uint8_t* stage, const float* bias_s,
-                                              int bn, int n_base, int m_base, int l, int lane) {
+                                              int bn, int n_base, int m_base, int l, int lane, float* colacc, int bn_full, int nrows) {
   for (int c = 0; c < bn / kEpiCols; ++c) {
     uint32_t r0[32], r1[32];
     tmem_ld_32x32(taddr + c * kEpiCols, r0);
@@ -67,6 +70,36 @@ __device__ __forceinline__ void epilogue_slab(uint32_t taddr, const CUtensorMap*
       tma_store_3d(map_c, stage, n_base + c * kEpiCols, m_base, l);
       bulk_commit();
     }
+    if (colacc != nullptr) {
+      float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
+      const uint32_t chunk = uint32_t(lane >> 2), inner = uint32_t(lane & 3) * 4u;
+#pragma unroll 8
+      for (int r = 0; r < 32; ++r) {
+        if (r < nrows) {
+          const uint32_t u = *reinterpret_cast<const uint32_t*>(stage + r * 128 + ((chunk ^ uint32_t(r & 7)) << 4) + inner);
+          const float a = bf16_lo(u), b = bf16_hi(u);
+          s0 += a; q0 = fmaf(a, a, q0);
+          s1 += b; q1 = fmaf(b, b, q1);
+        }
+      }
+      const int col = c * kEpiCols + 2 * lane;
+      atomicAdd(&colacc[col], s0); atomicAdd(&colacc[col + 1], s1);
+      atomicAdd(&colacc[bn_full + col], q0); atomicAdd(&colacc[bn_full + col + 1], q1);
+    }
+  }
+}
+
+// Per-tile column statistics -> global partials [L][row blocks of 128][N][2], then cleared for the next tile.
+__device__ __forceinline__ void flush_tile_stats(float* colacc, int bn_full, float* tile_stats, int l, int row_block, int row_blocks,
+                                                 int n_base, int N, int etid) {
+  for (int j = etid; j < bn_full; j += 128) {
+    const int n = n_base + j;
+    if (n < N && row_block < row_blocks) {
+      float2* dst = reinterpret_cast<float2*>(tile_stats) + (1LL * l * row_blocks + row_block) * N + n;
+      *dst = make_float2(colacc[j], colacc[bn_full + j]);
+    }
+    colacc[j] = 0.f;
+    colacc[bn_full + j] = 0.f;
   }
 }
 
@@ -79,12 +112,14 @@ struct GemmShared {
   int abort_flag;
   int epi_ok;
   alignas(16) float bias[gemm::BN];
+  float colacc[2 * gemm::BN];
 };
 
 __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)
 encoder_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, const __nv_bfloat16* __restrict__ bias,
-                    int L, int M, int N, int K, long long ldc, long long layer_stride_c, int* __restrict__ status) {
+                    int L, int M, int N, int K, long long ldc, long long layer_stride_c, int* __restrict__ status,
+                    float* __restrict__ tile_stats) {
   using namespace gemm;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled tiles need 1024-byte alignment
@@ -112,6 +147,7 @@ encoder_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     sh->abort_flag = 0;
     fence_barrier_init();
   }
+  for (int j = threadIdx.x; j < 2 * BN; j += NUM_THREADS) sh->colacc[j] = 0.f;
   if (warp == 1) {
     tmem_alloc(&sh->tmem_base, TMEM_COLS);
     tmem_relinquish();
@@ -190,6 +226,8 @@ encoder_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     const int etid = (warp - 2) * 32 + lane;
+    const int row_blocks = (M + 127) / 128;
+    int prev_l = -1, prev_rb = 0, prev_n = 0;
     uint32_t local_tile = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local_tile) {
@@ -198,7 +236,9 @@ encoder_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int l = int(t / (1LL * tiles_m * tiles_n));
       const uint32_t buf = local_tile & 1;
       const uint32_t tph = (local_tile >> 1) & 1;
-      named_barrier_sync(1, 128);  // previous tile's bias reads are done
+      named_barrier_sync(1, 128);  // previous tile's bias reads and column sums are done
+      if (tile_stats != nullptr && prev_l >= 0) flush_tile_stats(sh->colacc, BN, tile_stats, prev_l, prev_rb, row_blocks, prev_n, N, etid);
+      prev_l = l; prev_rb = mt; prev_n = nt * BN;
       for (int j = etid; j < BN; j += 128) {
         const int n = nt * BN + j;
         sh->bias[j] = (bias != nullptr && n < N) ? __bfloat162float(bias[1LL * l * N + n]) : 0.f;
@@ -211,10 +251,15 @@ encoder_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc_fence_after();
       const int m_base = mt * BM + quarter * 32;
       const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quarter * 32) << 16);
-      if (m_base < M) epilogue_slab(taddr, &map_c, epi_stage + (warp - 2) * kEpiStageBytes, sh->bias, min(BN, ((N - nt * BN + kEpiCols - 1) / kEpiCols) * kEpiCols), nt * BN, m_base, l, lane);
+      if (m_base < M) epilogue_slab(taddr, &map_c, epi_stage + (warp - 2) * kEpiStageBytes, sh->bias, min(BN, ((N - nt * BN + kEpiCols - 1) / kEpiCols) * kEpiCols), nt * BN, m_base, l, lane,
+                                    tile_stats != nullptr ? sh->colacc : nullptr, BN, min(32, M - m_base));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
+    }
+    if (ok && tile_stats != nullptr && prev_l >= 0) {
+      named_barrier_sync(1, 128);
+      flush_tile_stats(sh->colacc, BN, tile_stats, prev_l, prev_rb, row_blocks, prev_n, N, etid);
     }
   }
 
@@ -251,7 +296,7 @@ constexpr uint32_t B_BYTES = BN_HALF * BK * 2;
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 4 * 4096 + 1024 + 2048;
+constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + 4 * 4096 + 1024 + 4096;
 }  // namespace gemm2
 
 struct GemmPairShared {
@@ -263,12 +308,14 @@ struct GemmPairShared {
   int abort_flag;
   int epi_ok;
   alignas(16) float bias[gemm2::BN];
+  float colacc[2 * gemm2::BN];
 };
 
 __global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
 encoder_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_c, const __nv_bfloat16* __restrict__ bias,
-                         int L, int M, int N, int K, long long ldc, long long layer_stride_c, int* __restrict__ status) {
+                         int L, int M, int N, int K, long long ldc, long long layer_stride_c, int* __restrict__ status,
+                         float* __restrict__ tile_stats) {
   using namespace gemm2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -299,6 +346,7 @@ encoder_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     sh->abort_flag = 0;
     fence_barrier_init();
   }
+  for (int j = threadIdx.x; j < 2 * BN; j += NUM_THREADS) sh->colacc[j] = 0.f;
   if (warp == 1) {
     tmem_alloc_pair(&sh->tmem_base, TMEM_COLS);
     tmem_relinquish_pair();
@@ -368,6 +416,8 @@ encoder_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // ---------------------------------------------------------------- epilogue (both CTAs)
     const int quarter = warp & 3;
     const int etid = (warp - 2) * 32 + lane;
+    const int row_blocks = (M + 127) / 128;
+    int prev_l = -1, prev_rb = 0, prev_n = 0;
     uint32_t local_tile = 0;
     bool ok = true;
     for (long long t = pair; t < total_tiles && ok; t += npairs, ++local_tile) {
@@ -377,6 +427,8 @@ encoder_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const uint32_t buf = local_tile & 1;
       const uint32_t tph = (local_tile >> 1) & 1;
       named_barrier_sync(1, 128);
+      if (tile_stats != nullptr && prev_l >= 0) flush_tile_stats(sh->colacc, BN, tile_stats, prev_l, prev_rb, row_blocks, prev_n, N, etid);
+      prev_l = l; prev_rb = mt * 2 + int(cta_rank); prev_n = nt * BN;
       for (int j = etid; j < BN; j += 128) {
         const int n = nt * BN + j;
         sh->bias[j] = (bias != nullptr && n < N) ? __bfloat162float(bias[1LL * l * N + n]) : 0.f;
@@ -387,10 +439,15 @@ encoder_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc_fence_after();
       const int m_base = (mt * 2 + int(cta_rank)) * BM + quarter * 32;
       const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quarter * 32) << 16);
-      if (m_base < M) epilogue_slab(taddr, &map_c, epi_stage + (warp - 2) * kEpiStageBytes, sh->bias, min(BN, ((N - nt * BN + kEpiCols - 1) / kEpiCols) * kEpiCols), nt * BN, m_base, l, lane);
+      if (m_base < M) epilogue_slab(taddr, &map_c, epi_stage + (warp - 2) * kEpiStageBytes, sh->bias, min(BN, ((N - nt * BN + kEpiCols - 1) / kEpiCols) * kEpiCols), nt * BN, m_base, l, lane,
+                                    tile_stats != nullptr ? sh->colacc : nullptr, BN, min(32, M - m_base));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->tmem_empty[buf]), 0));  // the leader's barrier
+    }
+    if (ok && tile_stats != nullptr && prev_l >= 0) {
+      named_barrier_sync(1, 128);
+      flush_tile_stats(sh->colacc, BN, tile_stats, prev_l, prev_rb, row_blocks, prev_n, N, etid);
     }
   }
 
@@ -439,8 +496,10 @@ static bool make_kmajor_map(CUtensorMap* map, const void* base, int layers, int 
 }  // namespace clt
 
 // Returns 0 on success, a negative value when the arguments cannot be handled (the caller raises).
+// tile_stats (optional): [L][ceil(M / 128)][N][2] fp32, receives per 128-row block and column the sum and the sum of
+// squares of the stored (bf16-rounded) outputs; every element is written, nothing has to be cleared.
 extern "C" int clt_encoder_gemm(const void* A, const void* B, const void* bias, void* C, int L, int M, int N, int K,
-                                long long ldc, long long layer_stride_c, int* status, int num_sms, cudaStream_t stream) {
+                                long long ldc, long long layer_stride_c, int* status, float* tile_stats, int num_sms, cudaStream_t stream) {
   using namespace clt;
   if (K % 8 != 0 || ldc % 8 != 0 || layer_stride_c % 8 != 0) return -1;  // 16-byte TMA strides / vector stores
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -2;
@@ -486,7 +545,7 @@ extern "C" int clt_encoder_gemm(const void* A, const void* B, const void* bias, 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const __nv_bfloat16* bias_p = static_cast<const __nv_bfloat16*>(bias);
-    if (cudaLaunchKernelEx(&cfg, encoder_gemm_pair_kernel, map_a, map_b, map_c, bias_p, L, M, N, K, ldc, layer_stride_c, status) != cudaSuccess)
+    if (cudaLaunchKernelEx(&cfg, encoder_gemm_pair_kernel, map_a, map_b, map_c, bias_p, L, M, N, K, ldc, layer_stride_c, status, tile_stats) != cudaSuccess)
       return -5;
     return 0;
   }
@@ -500,6 +559,6 @@ extern "C" int clt_encoder_gemm(const void* A, const void* B, const void* bias, 
   if (tiles == 0) return 0;
   const int grid = int(tiles < num_sms ? tiles : num_sms);
   encoder_gemm_kernel<<<grid, gemm::NUM_THREADS, gemm::SMEM_BYTES, stream>>>(
-      map_a, map_b, map_c, static_cast<const __nv_bfloat16*>(bias), L, M, N, K, ldc, layer_stride_c, status);
+      map_a, map_b, map_c, static_cast<const __nv_bfloat16*>(bias), L, M, N, K, ldc, layer_stride_c, status, tile_stats);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

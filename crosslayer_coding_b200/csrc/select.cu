@@ -159,6 +159,33 @@ __global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __re
   }
 }
 
+// Column statistics from the per-block sums that the encoder GEMM's epilogue leaves behind:
+// tile_stats [L][row_blocks][F][2] = (sum, sum of squares) over the rows of one 128-row block.  The blocks are merged
+// with the pairwise update of Chan et al. (block means first), which keeps the variance accurate when the mean is
+// large against the spread.
+__global__ void __launch_bounds__(256) colstats_from_tiles_kernel(const float* __restrict__ tile_stats, float* __restrict__ mean,
+                                                                    float* __restrict__ rstd, int B, int F, int row_blocks, long long n) {
+  const long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int l = int(i / F), c = int(i - 1LL * l * F);
+  const float2* src = reinterpret_cast<const float2*>(tile_stats) + (1LL * l * row_blocks) * F + c;
+  float cnt = 0.f, mu = 0.f, m2 = 0.f;
+  for (int rb = 0; rb < row_blocks; ++rb) {
+    const float2 sq = src[1LL * rb * F];
+    const float nb = float(min(128, B - rb * 128));
+    const float mb = sq.x / nb;
+    const float m2b = fmaxf(sq.y - sq.x * mb, 0.f);
+    const float tot = cnt + nb;
+    const float delta = mb - mu;
+    m2 += m2b + delta * delta * (cnt * nb / tot);
+    mu += delta * (nb / tot);
+    cnt = tot;
+  }
+  const float var = B > 1 ? fmaxf(m2 / float(B - 1), 0.f) : 0.f;
+  mean[i] = mu;
+  rstd[i] = 1.f / (sqrtf(var) + 1e-6f);
+}
+
 // mean / rstd hold the shifted sum and sum of squares (shift = the column's first row); convert in place.
 __global__ void __launch_bounds__(256) colstats_finalize_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ mean,
                                                                   float* __restrict__ rstd, int B, int F, long long layer_stride,
@@ -1077,6 +1104,13 @@ extern "C" int clt_colstats(const void* x, float* mean, float* rstd, int L, int 
     const long long n = 1LL * L * F;
     colstats_finalize_kernel<<<int((n + 255) / 256), 256, 0, st>>>(xp, mean, rstd, B, F, layer_stride, n);
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int clt_colstats_from_tiles(const float* tile_stats, float* mean, float* rstd, int L, int B, int F, cudaStream_t st) {
+  const long long n = 1LL * L * F;
+  if (n == 0) return 0;
+  colstats_from_tiles_kernel<<<int((n + 255) / 256), 256, 0, st>>>(tile_stats, mean, rstd, B, F, (B + 127) / 128, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -121,7 +121,7 @@ class SparseForward:
         """Pre-activations, selection and the token-major / feature-major CSR views of the active entries."""
         e, m = self.ext, self.model
         assert X.dtype == torch.bfloat16 and X.shape == (self.L, self.B, self.d), (X.dtype, tuple(X.shape))
-        e.encoder_gemm(X, m.enc_weight.data, m.enc_bias.data, self.preact, self.status)
+        e.encoder_gemm(X, m.enc_weight.data, m.enc_bias.data, self.preact, self.status, None)
         if self.fn == "batchtopk":
             e.colstats(self.preact, self.mean, self.rstd)
             self.hist.zero_()

@@ -95,7 +95,7 @@ def main() -> None:
 
         res = {
             "case": args.case, "activation": args.activation, "optimizer_states": args.optimizer_states,
-            "encoder_gemm_ms": _best_of(lambda: e.encoder_gemm(X, model.enc_weight.data, model.enc_bias.data, eng.preact, eng.status)),
+            "encoder_gemm_ms": _best_of(lambda: e.encoder_gemm(X, model.enc_weight.data, model.enc_bias.data, eng.preact, eng.status, None)),
             "library_bmm_ms": _best_of(lambda: torch.bmm(X, model.enc_weight.data.transpose(1, 2))),
             "encode_select_ms": _best_of(lambda: eng.encode_select(X)),
             "decode_loss_ms": _best_of(lambda: eng.decode_loss(Y)),

@@ -157,6 +157,7 @@ class FusedBatchTopKEngine:
         self.preact = torch.empty(L, B, Fl, dtype=torch.bfloat16, device=dev)
         self.mean = torch.empty(L, Fl, dtype=f32, device=dev)
         self.rstd = torch.empty(L, Fl, dtype=f32, device=dev)
+        self.tile_stats = None  # [L, ceil(B / 128), Fl, 2] fp32 switches the statistics into the GEMM epilogue
         self.hist = torch.zeros(2 * 8192 + 32, dtype=i32, device=dev)  # two histograms + the pool counter
         # tracked histogram range {key_lo, shift} and the pool filled by the single pass over the pre-activations
         self.sel_state = torch.tensor([self.key_lo, self.shift], dtype=torch.int64, device=dev) if self.key_lo != 0 else None
@@ -251,7 +252,10 @@ class FusedBatchTopKEngine:
         e = self.ext
         m = self.model
         assert X.dtype == torch.bfloat16 and X.shape == (self.L, self.B, self.d), (X.dtype, X.shape)
-        e.encoder_gemm(X, m.enc_weight.data, m.enc_bias.data, self.preact, self.status)
+        # The GEMM can leave per-block column sums behind (tile_stats) so that the batch statistics need no second
+        # pass; at K = d_model that epilogue work outlasts the MMAs of a tile (measured: +0.75 ms on the GEMM against
+        # 0.37 ms for the separate pass at the GPT-2 shape), so the separate column-statistics pass is used.
+        e.encoder_gemm(X, m.enc_weight.data, m.enc_bias.data, self.preact, self.status, self.tile_stats)
         if self.fn == "jumprelu":
             self.theta = m.log_threshold.data.float().exp().contiguous()
             e.threshold_select(self.preact, self.theta, self.Fv, self.Fl, self.ctl, self.ent_tok, self.ent_col, self.ent_val, self.status)
@@ -264,7 +268,10 @@ class FusedBatchTopKEngine:
             )
             self.kernel_launches += 2 + 5  # gemm, threshold selection, csr (5)
             return
-        e.colstats(self.preact, self.mean, self.rstd)
+        if self.tile_stats is not None:
+            e.colstats_from_tiles(self.tile_stats, self.mean, self.rstd, self.B)
+        else:
+            e.colstats(self.preact, self.mean, self.rstd)
         self.hist.zero_()
         world, rank, dptr, fptr, slot, seq = self._exchange_args()
         if self.world > 1 and self.symm is None:

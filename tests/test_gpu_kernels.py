@@ -30,9 +30,18 @@ def test_encoder_gemm_matches_fp32(ext, L, M, N, K):
     b = torch.randn(L, N, device=dev).bfloat16()
     out = torch.full((L, M, N), float("nan"), device=dev, dtype=torch.bfloat16)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
-    ext.encoder_gemm(x, w, b, out, status)
+    tile_stats = torch.full((L, (M + 127) // 128, N, 2), float("nan"), device=dev)
+    ext.encoder_gemm(x, w, b, out, status, tile_stats)
     torch.cuda.synchronize()
     assert int(status[0]) == 0
+    # the epilogue's per-block column sums give the batch statistics of the stored (rounded) outputs
+    mean = torch.empty(L, N, device=dev)
+    rstd = torch.empty(L, N, device=dev)
+    ext.colstats_from_tiles(tile_stats, mean, rstd, M)
+    of = out.float()
+    assert torch.isfinite(tile_stats).all()
+    assert torch.allclose(mean, of.mean(dim=1), atol=2e-4, rtol=1e-4)
+    assert torch.allclose(rstd, 1.0 / (of.std(dim=1) + 1e-6), rtol=2e-3)
     ref = torch.einsum("lmk,lnk->lmn", x.float(), w.float()) + b.float()[:, None, :]
     err = (out.float() - ref).abs().max().item()
     assert torch.isfinite(out.float()).all()
