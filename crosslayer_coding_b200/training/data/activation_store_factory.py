@@ -21,6 +21,7 @@ def create_activation_store(
     world: int = 1,
     start_time: float = 0.0,
     shard_data: bool = True,
+    shard_group=None,
 ) -> BaseActivationStore:
     tc = training_config
     common = dict(
@@ -34,7 +35,8 @@ def create_activation_store(
             raise ValueError("activation_path must be set in TrainingConfig when activation_source is 'local_manifest'.")
         from .local_activation_store import LocalActivationStore
 
-        store: BaseActivationStore = LocalActivationStore(dataset_path=tc.activation_path, **common)
+        # tensor-parallel runs on GPUs: every rank assembles and copies 1/W of each batch, the rest arrives over NVLink
+        store: BaseActivationStore = LocalActivationStore(dataset_path=tc.activation_path, shard_group=shard_group, **common)
     elif tc.activation_source == "remote":
         rc = tc.remote_config or {}
         if not rc.get("server_url") or not rc.get("dataset_id"):

@@ -36,6 +36,7 @@ class LocalActivationStore(ManifestActivationStore):
         prefetch_batches: int = 2,
         auto_advance_epoch: bool = False,
         max_open_files: int = 128,
+        shard_group=None,
     ):
         self.dataset_path = str(dataset_path)
         if not os.path.isdir(self.dataset_path):
@@ -48,6 +49,7 @@ class LocalActivationStore(ManifestActivationStore):
             train_batch_size_tokens=train_batch_size_tokens, device=device, dtype=dtype, rank=rank, world=world,
             seed=seed, sampling_strategy=sampling_strategy, normalization_method=normalization_method,
             shard_data=shard_data, prefetch_batches=prefetch_batches, auto_advance_epoch=auto_advance_epoch,
+            shard_group=shard_group,
         )
 
     def _load_metadata(self) -> Optional[Dict[str, Any]]:
@@ -99,6 +101,10 @@ class LocalActivationStore(ManifestActivationStore):
         chunk_ids = idx[:, 0]
         for cid in np.unique(chunk_ids):
             pos = np.nonzero(chunk_ids == cid)[0].astype(np.int64)
+            if self.row_shard is not None:  # tensor-parallel staging: this rank's token rows only
+                pos = pos[(pos >= self.row_shard[0]) & (pos < self.row_shard[0] + self.row_shard[1])]
+                if pos.size == 0:
+                    continue
             rows = idx[pos, 1].astype(np.uint64)
             order = np.argsort(rows, kind="stable")  # ascending file order
             rows, pos = rows[order], pos[order]

@@ -55,7 +55,11 @@ class ManifestActivationStore(BaseActivationStore):
         shard_data: bool = True,
         prefetch_batches: int = 2,
         auto_advance_epoch: bool = False,
+        shard_group=None,
     ):
+        """``shard_group`` (tensor-parallel group, CUDA only): every rank assembles and copies only its ``1/W`` of
+        each batch's token rows and the slices are all-gathered over NVLink (``DeviceStager``); the ranks must
+        draw identical batches, i.e. ``shard_data=False``."""
         self.train_batch_size_tokens = int(train_batch_size_tokens)
         self.device = torch.device(device) if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
         dtype_name = str(dtype).replace("torch.", "")
@@ -106,7 +110,12 @@ class ManifestActivationStore(BaseActivationStore):
         shape = (2, self.num_layers, self.train_batch_size_tokens, self.d_model)
         self._storage_torch = _TORCH_VIEW[self.stored_dtype]
         # slots: prefetch in the queue + one being assembled + one held by the consumer
-        self.stager = DeviceStager(shape, self._storage_torch, self.device, depth=self.prefetch_batches + 2)
+        self.stager = DeviceStager(shape, self._storage_torch, self.device, depth=self.prefetch_batches + 2,
+                                   shard_group=shard_group if not shard_data or world == 1 else None, row_dim=2)
+        self.row_shard = None  # (first row, row count) of the batch positions this rank assembles
+        if getattr(self.stager, "shard_world", 1) > 1:
+            self.row_shard = (self.stager.shard_rank * self.stager.rows_per_rank, self.stager.rows_per_rank)
+        self._submitted: list = []  # sharded staging: slots whose copy + gather the consumer thread has queued
         self.h2d_bytes_per_batch = self.stager.bytes_per_batch
         self._queue: "queue.Queue" = queue.Queue(maxsize=self.prefetch_batches)
         self._stop = threading.Event()
@@ -193,6 +202,10 @@ class ManifestActivationStore(BaseActivationStore):
         chunk_ids = idx[:, 0]
         for cid in np.unique(chunk_ids):
             pos = np.nonzero(chunk_ids == cid)[0]
+            if self.row_shard is not None:
+                pos = pos[(pos >= self.row_shard[0]) & (pos < self.row_shard[0] + self.row_shard[1])]
+                if pos.size == 0:
+                    continue
             rows = idx[pos, 1].astype(np.int64)
             order = np.argsort(rows, kind="stable")
             rows_sorted = rows[order]
@@ -228,7 +241,8 @@ class ManifestActivationStore(BaseActivationStore):
                     self._producer_done = True
                     self._queue.put(("error", exc, None))
                     return
-                self.stager.submit(slot)
+                if self.row_shard is None:
+                    self.stager.submit(slot)  # sharded staging queues its copy + all-gather on the consumer's thread
                 while not self._stop.is_set():
                     try:
                         self._queue.put(("batch", slot, state_after), timeout=0.1)
@@ -256,7 +270,16 @@ class ManifestActivationStore(BaseActivationStore):
         if getattr(self, "_epoch_ended", False):
             raise StopIteration  # until advance_epoch() / load_state_dict()
         self._ensure_thread()
-        kind, payload, state = self._queue.get()
+        if self.row_shard is not None:
+            # collectives are issued from this thread only, in the same order on every rank: queue the copy + gather
+            # of this batch (if not done by the look-ahead of the previous call) and of the next one if it is ready
+            if not self._submitted:
+                self._submitted.append(self._queue.get())
+                if self._submitted[-1][0] == "batch":
+                    self.stager.submit(self._submitted[-1][1])
+            kind, payload, state = self._submitted.pop(0)
+        else:
+            kind, payload, state = self._queue.get()
         if kind == "end":
             self._thread = None
             self._epoch_ended = True
@@ -266,6 +289,11 @@ class ManifestActivationStore(BaseActivationStore):
             self._producer_done = False  # the next call starts a new producer at the sampler's position
             raise payload
         slot = payload
+        if self.row_shard is not None and self._lookahead_ready():
+            nxt = self._queue.get()
+            self._submitted.append(nxt)
+            if nxt[0] == "batch":
+                self.stager.submit(nxt[1])
         raw = self.stager.acquire(slot)
         self._last_slot = slot
         self._consumed_state = state
@@ -273,6 +301,11 @@ class ManifestActivationStore(BaseActivationStore):
         inputs = LayerBatch.from_stacked(batch[0], self.layer_indices)
         targets = LayerBatch.from_stacked(batch[1], self.layer_indices)
         return inputs, targets
+
+    def _lookahead_ready(self) -> bool:
+        """Sharded staging: whether the next message can be taken now.  Every rank has to take the same decision
+        (the gather is a collective), so the look-ahead waits for the producer instead of polling it."""
+        return True
 
     def advance_epoch(self) -> None:
         self._shutdown_thread()
@@ -297,6 +330,7 @@ class ManifestActivationStore(BaseActivationStore):
         self._stop.clear()
         self._producer_done = False
         self._epoch_ended = False
+        self._submitted = []
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> Dict[str, Any]:

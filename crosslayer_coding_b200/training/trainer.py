@@ -185,6 +185,7 @@ class CLTTrainer:
         return create_activation_store(
             self.training_config, self.clt_config, self.device, rank=self.rank, world=self.world_size,
             shard_data=not self.distributed,
+            shard_group=self.process_group if (self.distributed and self.world_size > 1 and self.device.type == "cuda") else None,
         )
 
     def _select_engine(self, mean_tg, std_tg) -> None:

@@ -79,6 +79,28 @@ def main():
         got_x = torch.stack([inputs[l] for l in range(L)]).cpu()
         got_y = torch.stack([targets[l] for l in range(L)]).cpu()
         staging_ok = staging_ok and torch.equal(got_x, pool[i % 4, 0]) and torch.equal(got_y, pool[i % 4, 1])
+    # the same through a chunked dataset on disk: rank-sharded native assembly + gather must equal the plain store
+    import tempfile
+
+    from crosslayer_coding_b200.activation_generation.synthetic import SyntheticSpec, write_synthetic_dataset
+    from crosslayer_coding_b200.training.data.local_activation_store import LocalActivationStore
+
+    ds_dir = os.path.join(tempfile.gettempdir(), f"clt_tp_ds_{os.environ.get('MASTER_PORT', '0')}")
+    if rank == 0 and not os.path.exists(os.path.join(ds_dir, "metadata.json")):
+        write_synthetic_dataset(ds_dir, SyntheticSpec(num_layers=L, d_model=d, dict_size=128, active_mean=4, seed=3),
+                                total_tokens=1024, chunk_tokens=256, dtype="bfloat16", device="cpu")
+    if world > 1:
+        dist.barrier()
+    common = dict(train_batch_size_tokens=B, device=dev, dtype="bfloat16", rank=rank, world=world, seed=5, sampling_strategy="random_chunk",
+                  normalization_method="mean_std", shard_data=False)
+    sharded = LocalActivationStore(ds_dir, shard_group=group, **common)
+    plain = LocalActivationStore(ds_dir, **common)
+    for i in range(5):
+        xs, ys = next(sharded)
+        xp, yp = next(plain)
+        staging_ok = staging_ok and torch.equal(xs.stacked, xp.stacked) and torch.equal(ys.stacked, yp.stacked)
+    sharded.close()
+    plain.close()
     flag = torch.tensor([1.0 if staging_ok else 0.0], device=dev)
     if world > 1:
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
