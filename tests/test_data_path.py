@@ -226,3 +226,25 @@ def test_local_store_truncated_chunk_raises_after_retries(dataset, monkeypatch):
             next(st)
     assert opened["n"] >= 6  # three attempts per failing batch
     st.close()
+
+
+def test_row_sharded_assembly_fills_only_this_ranks_rows(dataset):
+    """Tensor-parallel staging assembles 1/W of a batch per rank: the union over the ranks equals the full batch."""
+    full = LocalActivationStore(dataset, train_batch_size_tokens=16, device="cpu", dtype="float32", seed=3, shard_data=False)
+    idx = next(full.sampler)
+    want = torch.zeros(2, 3, 16, 8, dtype=full._storage_torch)
+    full._assemble(idx, want)
+    got = torch.zeros_like(want)
+    for r in range(4):
+        part = LocalActivationStore(dataset, train_batch_size_tokens=16, device="cpu", dtype="float32", seed=3, shard_data=False)
+        part.row_shard = (4 * r, 4)
+        buf = torch.full_like(want, 7)  # rows of other ranks must stay untouched
+        part._assemble(idx, buf)
+        assert torch.equal(buf[:, :, 4 * r:4 * r + 4], want[:, :, 4 * r:4 * r + 4])
+        untouched = torch.ones(16, dtype=torch.bool)
+        untouched[4 * r:4 * r + 4] = False
+        assert (buf[:, :, untouched].float() == 7).all()
+        got[:, :, 4 * r:4 * r + 4] = buf[:, :, 4 * r:4 * r + 4]
+        part.close()
+    assert torch.equal(got, want)
+    full.close()
