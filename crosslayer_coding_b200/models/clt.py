@@ -433,7 +433,7 @@ class CrossLayerTranscoder(BaseTranscoder):
         return nn.Module.state_dict(self)
 
     def state_dict(self, *args, destination=None, prefix: str = "", keep_vars: bool = False, **kwargs):
-        """Reference key names and layouts (clt/models/clt.py docstring of the survey:
+        """Reference key names and layouts (clt/models/encoder.py:34-46, clt/models/decoder.py:58-95):
         ``encoder_module.encoders.{l}.weight|bias_param``,
         ``decoder_module.decoders.{s}->{t}.weight|bias_param`` ...)."""
         cfg = self.config

@@ -254,8 +254,8 @@ class ManifestActivationStore(BaseActivationStore):
             self._queue.put(("error", exc, None))
 
     def _ensure_thread(self) -> None:
-        # a producer that ran to the end of the epoch (or failed) has left its verdict in the queue: starting another
-        # one before the consumer has read it would queue a second, stale verdict
+        # a producer that ran to the end of the epoch (or failed) has left its final message in the queue: starting another
+        # one before the consumer has read it would queue a second, stale one
         if getattr(self, "_producer_done", False):
             return
         if self._thread is None or not self._thread.is_alive():
