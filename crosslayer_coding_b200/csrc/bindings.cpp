@@ -47,6 +47,7 @@ struct CltSelectArgs {
 };
 int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st);
 int clt_threshold_select(const CltSelectArgs* a, cudaStream_t st);
+int clt_token_topk_select(const CltSelectArgs* a, cudaStream_t st);
 
 struct CltThetaGradArgs {
   const void* gs; const void* w[32]; const void* preact;
@@ -276,6 +277,26 @@ void threshold_select(const Tensor& x, const Tensor& theta, int64_t f_valid, int
   check(clt_threshold_select(&a, cur_stream()), "threshold_select");
 }
 
+// Per-token top-k of the batch z-scores: exactly k entries per token at [token * k, token * k + k) of the entry list.
+void token_topk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, int64_t col_pitch, int64_t k, Tensor& ctl, Tensor& ent_tok,
+                       Tensor& ent_col, Tensor& ent_val, Tensor& status) {
+  need(x, at::kBFloat16, "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd"); need(ctl, at::kLong, "ctl");
+  need(status, at::kInt, "status"); need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
+  TORCH_CHECK(x.dim() == 3 && mean.dim() == 2 && mean.size(0) == x.size(0) && mean.size(1) == x.size(2), "mean / rstd must be [L, F]");
+  TORCH_CHECK(ctl.numel() >= 16 && ent_tok.numel() >= x.size(1) * k, "entry list needs B * k elements");
+  CltSelectArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.x = x.data_ptr(); a.mean = mean.data_ptr<float>(); a.rstd = rstd.data_ptr<float>();
+  a.L = x.size(0); a.B = x.size(1); a.F = x.size(2); a.stat_pitch = int(mean.size(1));
+  a.ld = x.size(2); a.layer_stride = 1LL * x.size(1) * x.size(2);
+  a.col_pitch = int(col_pitch); a.k_total = k;
+  a.ctl = reinterpret_cast<long long*>(ctl.data_ptr<int64_t>());
+  a.ent_tok = ent_tok.data_ptr<int>(); a.ent_col = ent_col.data_ptr<int>(); a.ent_val = ent_val.data_ptr<float>(); a.ent_cap = ent_tok.numel();
+  a.status = status.data_ptr<int>();
+  c10::cuda::CUDAGuard guard(x.device());
+  check(clt_token_topk_select(&a, cur_stream()), "token_topk_select");
+}
+
 // JumpReLU threshold gradient sums: S1[l, f] += sum_b window * x * (gs . W_dec rows), S2[l, f] += sum_b window * x.
 void theta_grad_gemm(const Tensor& gs, const std::vector<Tensor>& dec_w, const Tensor& preact, const Tensor& theta, double bandwidth,
                      Tensor& S1, Tensor& S2, Tensor& status) {
@@ -498,6 +519,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colstats_from_tiles", &colstats_from_tiles);
   m.def("batchtopk_select", &batchtopk_select);
   m.def("threshold_select", &threshold_select);
+  m.def("token_topk_select", &token_topk_select);
   m.def("theta_grad_gemm", &theta_grad_gemm);
   m.def("build_csr", &build_csr);
   m.def("dead_counter_update", &dead_counter_update);

@@ -601,6 +601,127 @@ __global__ void __launch_bounds__(256) threshold_collect_kernel(const __nv_bfloa
   }
 }
 
+// ------------------------------------------------------------------ 2d. per-token top-k (TokenTopK)
+// Every token keeps its k largest z-scores over all layers' features (reference: torch.topk(dim=-1) + scatter_,
+// clt/models/activations.py:121-124, ranking on the per-feature batch z-scores).  One CTA handles four tokens (so
+// that the per-column statistics are loaded once for four rows) and finds each token's k-th largest key exactly
+// with a three-round radix select over the 32-bit keys (11 + 11 + 10 bits, histograms in shared memory), then
+// emits the entries above the cut and the lowest-index ties at the cut.  Output: exactly k entries per token at
+// [token * k, token * k + k) of the entry list.
+constexpr int kTokPerCta = 4;
+constexpr int kTokBins = 2048;
+constexpr int kTieCap = 256;
+
+struct TokenTopkShared {
+  uint32_t hist[kTokPerCta][kTokBins];
+  uint32_t prefix[kTokPerCta], mask[kTokPerCta];
+  unsigned int need[kTokPerCta];
+  int emitted[kTokPerCta];
+  int nties[kTokPerCta];
+  int tie_col[kTokPerCta][kTieCap];
+  float tie_val[kTokPerCta][kTieCap];
+};
+
+template <typename Fn>
+__device__ __forceinline__ void token_rows_scan(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+                                                const float* __restrict__ rstd, const ScanGeom& g, int tok0, int ntok, Fn fn) {
+  for (int l = 0; l < g.L; ++l) {
+    for (int c0 = threadIdx.x * 8; c0 < g.F; c0 += blockDim.x * 8) {
+      float mu[8], rs[8];
+      load_cols8(mean + 1LL * l * g.sp + c0, mu);
+      load_cols8(rstd + 1LL * l * g.sp + c0, rs);
+      uint4 v[kTokPerCta];
+#pragma unroll
+      for (int t = 0; t < kTokPerCta; ++t)
+        v[t] = t < ntok ? __ldg(reinterpret_cast<const uint4*>(x + 1LL * l * g.layer_stride + 1LL * (tok0 + t) * g.ld + c0)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int t = 0; t < kTokPerCta; ++t) {
+        if (t >= ntok) break;
+        const uint32_t u[4] = {v[t].x, v[t].y, v[t].z, v[t].w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+          fn(t, l, c0 + j, xv, float_to_key((xv - mu[j]) * rs[j]));
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) token_topk_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+                                                           const float* __restrict__ rstd, ScanGeom g, int col_pitch, int k,
+                                                           long long* __restrict__ ctl, Lists o, int* __restrict__ status) {
+  extern __shared__ uint8_t tk_smem[];
+  TokenTopkShared* sh = reinterpret_cast<TokenTopkShared*>(tk_smem);
+  const int tok0 = blockIdx.x * kTokPerCta;
+  const int ntok = min(kTokPerCta, g.B - tok0);
+  const int tid = threadIdx.x;
+  if (tid < kTokPerCta) { sh->prefix[tid] = 0; sh->mask[tid] = 0; sh->need[tid] = (unsigned int)k; sh->emitted[tid] = 0; sh->nties[tid] = 0; }
+  if (blockIdx.x == 0 && tid == 0) ctl[CTL_NUM_ENTRIES] = 1LL * g.B * k;
+  // ---- exact k-th largest key per token: radix select, most significant digits first
+  const int shifts[3] = {21, 10, 0};
+  const int widths[3] = {11, 11, 10};
+  for (int round = 0; round < 3; ++round) {
+    const int shift = shifts[round];
+    const uint32_t nb = 1u << widths[round];
+    for (int i = tid; i < kTokPerCta * kTokBins; i += blockDim.x) (&sh->hist[0][0])[i] = 0;
+    __syncthreads();
+    token_rows_scan(x, mean, rstd, g, tok0, ntok, [&](int t, int, int, float, uint32_t key) {
+      if ((key & sh->mask[t]) == sh->prefix[t]) atomicAdd(&sh->hist[t][(key >> shift) & (nb - 1u)], 1u);
+    });
+    __syncthreads();
+    if (tid < ntok) {
+      // digit that holds the need-th largest remaining key (counting from the top)
+      unsigned int run = 0, need = sh->need[tid];
+      int digit = 0;
+      for (int b = int(nb) - 1; b >= 0; --b) {
+        const unsigned int c = sh->hist[tid][b];
+        if (run + c >= need) { digit = b; break; }
+        run += c;
+      }
+      sh->need[tid] = need - run;
+      sh->prefix[tid] |= uint32_t(digit) << shift;
+      sh->mask[tid] |= (nb - 1u) << shift;
+    }
+    __syncthreads();
+  }
+  // prefix[t] is now the cut key T of token t, need[t] the number of keys equal to T that are kept
+  token_rows_scan(x, mean, rstd, g, tok0, ntok, [&](int t, int l, int c, float xv, uint32_t key) {
+    const uint32_t T = sh->prefix[t];
+    if (key > T) {
+      const int slot = atomicAdd(&sh->emitted[t], 1);
+      if (slot < k) {
+        const long long q = 1LL * (tok0 + t) * k + slot;
+        o.ent_tok[q] = tok0 + t; o.ent_col[q] = l * col_pitch + c; o.ent_val[q] = xv;
+      }
+    } else if (key == T) {
+      const int i = atomicAdd(&sh->nties[t], 1);
+      if (i < kTieCap) { sh->tie_col[t][i] = l * col_pitch + c; sh->tie_val[t][i] = xv; }
+    }
+  });
+  __syncthreads();
+  // ---- ties at the cut: the lowest flat indices first (l * col_pitch + c grows with the reference's column order)
+  for (int t = 0; t < ntok; ++t) {
+    const int n = sh->nties[t];
+    const int need = int(sh->need[t]);
+    const int above = sh->emitted[t];
+    if (n > kTieCap && need < n) {
+      if (tid == 0) atomicCAS(status, STATUS_OK, STATUS_TIE_OVERFLOW);
+      continue;
+    }
+    if (tid == 0 && above + need != k) atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
+    for (int i = tid; i < min(n, kTieCap); i += blockDim.x) {
+      const int ci = sh->tie_col[t][i];
+      int rank = 0;
+      for (int j = 0; j < min(n, kTieCap); ++j) rank += sh->tie_col[t][j] < ci;
+      if (rank < need && above + rank < k) {
+        const long long q = 1LL * (tok0 + t) * k + above + rank;
+        o.ent_tok[q] = tok0 + t; o.ent_col[q] = ci; o.ent_val[q] = sh->tie_val[t][i];
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ 3b. split the pool at the threshold bin
 // Runs instead of the full compaction pass when the tracked range contained the cut.
 __global__ void __launch_bounds__(256) classify_pool_kernel(Pool pool, long long* __restrict__ ctl, Lists o,
@@ -1220,6 +1341,24 @@ extern "C" int clt_threshold_select(const CltSelectArgs* a, cudaStream_t st) {
   dim3 grid(((a->F + 7) / 8 + 255) / 256, (a->B + g.rows_per_block - 1) / g.rows_per_block, a->L);
   if (cudaMemsetAsync(a->ctl + CTL_NUM_ENTRIES, 0, sizeof(long long), st) != cudaSuccess) return -5;
   threshold_collect_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(a->x), a->rstd, g, a->col_pitch, a->ctl, lists_of(a), a->status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Per-token top-k of the batch z-scores (TokenTopK).  Uses x, mean, rstd, L, B, F, stat_pitch, ld, layer_stride,
+// col_pitch, ctl, ent_* (capacity >= B * k), status of the argument block; k_total carries the per-token k.
+extern "C" int clt_token_topk_select(const CltSelectArgs* a, cudaStream_t st) {
+  if (a->ld % 8 != 0 || a->layer_stride % 8 != 0 || a->F % 8 != 0 || a->stat_pitch % 4 != 0 || a->F > a->ld) return -1;
+  const long long k = a->k_total;
+  if (k <= 0 || k > 1LL * a->L * a->F || 1LL * a->B * k > a->ent_cap) return -1;
+  const ScanGeom g = scan_geom(a);
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(token_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(TokenTopkShared))) != cudaSuccess) return -4;
+    attr_set = true;
+  }
+  const int grid = (a->B + kTokPerCta - 1) / kTokPerCta;
+  token_topk_kernel<<<grid, 256, sizeof(TokenTopkShared), st>>>(static_cast<const __nv_bfloat16*>(a->x), a->mean, a->rstd, g, a->col_pitch,
+                                                                 int(k), a->ctl, lists_of(a), a->status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

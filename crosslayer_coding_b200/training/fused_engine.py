@@ -61,10 +61,12 @@ def histogram_range(k_total: int, numel: int, pool_factor: float = 1.75):
 
 def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingConfig], model=None) -> Optional[str]:
     """``None`` when the fused step covers this configuration, else the reason it does not."""
-    if clt_config.activation_fn not in ("batchtopk", "jumprelu"):
-        return f"activation_fn={clt_config.activation_fn!r} (fused step covers batchtopk and jumprelu)"
-    if clt_config.activation_fn == "batchtopk" and clt_config.topk_mode != "global":
+    if clt_config.activation_fn not in ("batchtopk", "jumprelu", "topk"):
+        return f"activation_fn={clt_config.activation_fn!r} (fused step covers batchtopk, topk and jumprelu)"
+    if clt_config.activation_fn in ("batchtopk", "topk") and clt_config.topk_mode != "global":
         return "topk_mode='per_layer'"
+    if clt_config.activation_fn == "topk" and model is not None and model.world_size > 1:
+        return "per-token topk under tensor parallelism"
     if clt_config.activation_fn == "jumprelu":
         # the threshold gradient runs as one GEMM per source layer over the packed untied decoder tensors
         if clt_config.decoder_tying != "none":
@@ -148,6 +150,13 @@ class FusedBatchTopKEngine:
         self.fn = cfg.activation_fn
         if self.fn == "batchtopk":
             self.k_total = min(int(cfg.batchtopk_k) * B, B * L * self.F)
+        elif self.fn == "topk":
+            from ..models.activations import resolve_token_k
+
+            self.k_token = resolve_token_k(float(cfg.topk_k), L * self.F)
+            if self.k_token < 1:
+                raise ValueError("topk_k selects no feature")
+            self.k_total = self.k_token * B
         else:
             # JumpReLU: the number of active entries is data dependent; the lists hold up to
             # ``fused_max_active_per_token`` entries per token and a step that needs more reports it
@@ -272,6 +281,18 @@ class FusedBatchTopKEngine:
             e.colstats_from_tiles(self.tile_stats, self.mean, self.rstd, self.B)
         else:
             e.colstats(self.preact, self.mean, self.rstd)
+        if self.fn == "topk":
+            e.token_topk_select(self.preact, self.mean, self.rstd, self.Fl, self.k_token, self.ctl, self.ent_tok, self.ent_col,
+                                self.ent_val, self.status)
+            self.tok_cnt.zero_()
+            self.feat_cnt.zero_()
+            e.build_csr(
+                self.ent_tok, self.ent_col, self.ent_val, self.ctl, self.B, self.ncols,
+                self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
+                self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2, self.Fl,
+            )
+            self.kernel_launches += 3 + 5  # gemm, colstats, per-token selection, csr (5)
+            return
         self.hist.zero_()
         world, rank, dptr, fptr, slot, seq = self._exchange_args()
         if self.world > 1 and self.symm is None:

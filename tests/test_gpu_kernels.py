@@ -642,3 +642,80 @@ def test_fused_step_with_bf16_moments_tracks_fp32_moments():
     ratio = (vb[touched] / vf[touched]).mean().item()
     assert 0.9 < ratio < 1.1, ratio
     assert ((wb - wf).abs().mean() / wf.abs().mean()).item() < 0.05
+
+
+def _token_topk_oracle(x, mean, rstd, k):
+    """[L, B, F] -> bool mask of every token's k largest z-scores over all layers (ties: lowest column first)."""
+    L, B, F = x.shape
+    z = ((x.float() - mean[:, None, :]) * rstd[:, None, :]).permute(1, 0, 2).reshape(B, L * F)
+    _, order = torch.sort(z, dim=-1, descending=True, stable=True)
+    mask = torch.zeros_like(z, dtype=torch.bool)
+    mask.scatter_(-1, order[:, :k], True)
+    return mask.view(B, L, F).permute(1, 0, 2)
+
+
+@pytest.mark.parametrize("L,B,F,k,ties", [(3, 50, 264, 7, False), (2, 33, 512, 40, False), (2, 20, 64, 9, True)])
+def test_token_topk_select_matches_oracle(ext, L, B, F, k, ties):
+    torch.manual_seed(8)
+    dev = _dev()
+    if ties:
+        x = torch.zeros(L, B, F, device=dev)
+        x[:, ::2, ::3] = 1.0   # few distinct values: the cut falls among exact ties
+        x[:, 1::2, 1::4] = -0.5
+        x = x.bfloat16()
+    else:
+        x = torch.randn(L, B, F, device=dev).bfloat16()
+    mean = torch.empty(L, F, device=dev)
+    rstd = torch.empty(L, F, device=dev)
+    ext.colstats(x, mean, rstd)
+    ctl = torch.zeros(16, dtype=torch.int64, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    ent = [torch.full((B * k,), -1, dtype=torch.int32, device=dev), torch.full((B * k,), -1, dtype=torch.int32, device=dev),
+           torch.zeros(B * k, device=dev)]
+    ext.token_topk_select(x, mean, rstd, F, k, ctl, ent[0], ent[1], ent[2], status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0 and int(ctl[3]) == B * k
+    tok, col = ent[0].long(), ent[1].long()
+    assert (tok >= 0).all() and torch.equal(tok.view(B, k), torch.arange(B, device=dev)[:, None].expand(B, k))
+    got = torch.zeros(L, B, F, dtype=torch.bool, device=dev)
+    got[col // F, tok, col % F] = True
+    assert int(got.sum()) == B * k, "duplicate entries"
+    assert torch.equal(got, _token_topk_oracle(x, mean, rstd, k))
+    assert torch.equal(ent[2], x.float()[col // F, tok, col % F])
+
+
+def test_fused_token_topk_step_matches_autograd():
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder, TrainingConfig
+    from crosslayer_coding_b200.training.fused_engine import FusedBatchTopKEngine
+
+    torch.manual_seed(41)
+    dev = _dev()
+    L, d, F, B, k = 3, 64, 256, 96, 12
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="topk", topk_k=k, clt_dtype="bfloat16")
+    model = CrossLayerTranscoder(cfg, device=dev)
+    tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="bf16", sparsity_lambda=0.0,
+                        preactivation_coef=0.0, optimizer="adamw")
+    eng = FusedBatchTopKEngine(model, tc, B)
+    X = torch.randn(L, B, d, device=dev).bfloat16()
+    Y = torch.randn(L, B, d, device=dev).bfloat16()
+    ref = _fp32_copy(model)
+    snap = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3)
+    out = eng.train_step(X, Y, step=0, lr=1e-3)
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert int(out.num_entries) == B * k
+    mask = _token_topk_oracle(eng.preact, eng.mean, eng.rstd, k)
+    assert torch.equal(eng.activations_dense() != 0, mask & (eng.preact.float() != 0))
+    pre = {l: torch.nn.functional.linear(X[l].float(), ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    acts = {l: (pre[l] + (eng.preact[l].float() - pre[l]).detach()) * mask[l] for l in range(L)}
+    loss = sum(torch.nn.functional.mse_loss(ref.decode({s: acts[s] for s in range(t + 1)}, t), Y[t].float()) for t in range(L))
+    assert abs(out.reconstruction.item() - loss.item()) < 2e-3 * max(1.0, loss.item())
+    loss.backward()
+    opt.step()
+    ref_params = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        old = snap[name]
+        upd, ref_upd = p.detach().float() - old, ref_params[name].detach() - old
+        bad = ((upd - ref_upd).abs() > 0.008 * old.abs() + 3e-4).float().mean().item()
+        assert bad < 2e-3, (name, bad)
