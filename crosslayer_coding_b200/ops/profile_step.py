@@ -32,7 +32,7 @@ def build(case: str, device: torch.device, activation: str = "batchtopk", states
 
     L, d, F, B, k = CASES[case]
     torch.manual_seed(0)
-    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=activation, batchtopk_k=k, clt_dtype="bfloat16",
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=activation, batchtopk_k=k, topk_k=k, clt_dtype="bfloat16",
                     jumprelu_threshold=0.03)
     model = CrossLayerTranscoder(cfg, device=device)
     lam = 0.0
@@ -69,7 +69,7 @@ def _best_of(fn, n: int = 5) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--case", choices=sorted(CASES), default="full")
-    ap.add_argument("--activation", choices=["batchtopk", "jumprelu"], default="batchtopk")
+    ap.add_argument("--activation", choices=["batchtopk", "jumprelu", "topk"], default="batchtopk")
     ap.add_argument("--optimizer-states", choices=["float32", "bfloat16"], default="float32",
                     help="moment dtype of the encoder / decoder weights (bfloat16: stochastically rounded, 12 B/param/step)")
     ap.add_argument("--warmup", type=int, default=2)

@@ -204,8 +204,6 @@ class CLTTrainer:
                 # the fused JumpReLU step keeps the active entries in lists of fused_max_active_per_token per token;
                 # a run that starts dense (the default threshold 0.03 does) has to start on the autograd step
                 reason = "jumprelu takes the fused step only with engine='fused' (it needs sparse activations throughout)"
-            if reason is None and want == "auto" and self.clt_config.activation_fn == "topk":
-                reason = "per-token topk takes the fused step only with engine='fused'"
             if reason is None and self.world_size > 1:
                 from ..parallel.symm import SymmetricExchange
 
