@@ -71,8 +71,6 @@ def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingCon
         # the threshold gradient runs as one GEMM per source layer over the packed untied decoder tensors
         if clt_config.decoder_tying != "none":
             return "jumprelu with tied decoders"
-    if clt_config.skip_connection:
-        return "skip_connection"
     if clt_config.enable_feature_offset or clt_config.enable_feature_scale:
         return "feature offset/scale"
     if clt_config.d_model % 8 != 0 or clt_config.d_model > 2048:
@@ -239,6 +237,8 @@ class FusedBatchTopKEngine:
             self.dec_m = [zb(w) for w in model.dec_weight]
             self.dec_v = [zb(w) for w in model.dec_weight]
             self.decb_m, self.decb_v = z(model.dec_bias), z(model.dec_bias)
+            if model.skip_weight is not None:
+                self.skip_m, self.skip_v = z(model.skip_weight), z(model.skip_weight)
         if self.fn == "jumprelu":
             self.S1 = torch.zeros(L, Fl, dtype=f32, device=dev)
             self.S2 = torch.zeros(L, Fl, dtype=f32, device=dev)
@@ -261,6 +261,7 @@ class FusedBatchTopKEngine:
         e = self.ext
         m = self.model
         assert X.dtype == torch.bfloat16 and X.shape == (self.L, self.B, self.d), (X.dtype, X.shape)
+        self._X_last = X
         # The GEMM can leave per-block column sums behind (tile_stats) so that the batch statistics need no second
         # pass; at K = d_model that epilogue work outlasts the MMAs of a tile (measured: +0.75 ms on the GEMM against
         # 0.37 ms for the separate pass at the GPT-2 shape), so the separate column-statistics pass is used.
@@ -317,6 +318,41 @@ class FusedBatchTopKEngine:
     def _bias_sum(self) -> torch.Tensor:
         return (self.bias_sel @ self.model.dec_bias.data.float()).contiguous()
 
+    # The skip connection (reference: clt/models/decoder.py:310,332) is a handful of small dense [B, d] x [d, d]
+    # products: library GEMMs.  Its output enters the fused loss epilogue as the `addend` of the decode kernel and
+    # its weights are updated by the dense Adam kernel from gs^T @ x.
+    def _skip_pairs(self, s: int):
+        from ..models.clt import pair_index
+
+        return [pair_index(s, t, self.L) for t in range(s, self.L)]
+
+    def _skip_term(self, X: torch.Tensor) -> Optional[torch.Tensor]:
+        W = self.model.skip_weight
+        if W is None:
+            return None
+        out = torch.zeros(self.L, self.B, self.d, dtype=torch.float32, device=self.dev)
+        if self.tying == 0:
+            for s in range(self.L):
+                w = W.data[self._skip_pairs(s)]                     # [R, d, d], row t - s is the pair (s, t)
+                out[s:] += torch.matmul(X[s].to(w.dtype), w.transpose(1, 2)).float()
+        else:
+            out += torch.matmul(X.to(W.dtype), W.data.transpose(1, 2)).float()
+        return out
+
+    def _skip_adam(self, X: torch.Tensor, lr: float, c_g: float) -> None:
+        W = self.model.skip_weight
+        if W is None:
+            return
+        grad = torch.zeros(W.shape, dtype=torch.float32, device=self.dev)
+        gs = self.gs
+        if self.tying == 0:
+            for s in range(self.L):
+                # d loss / d W[s -> t] = c_g * gs[t]^T @ x[s]
+                grad[self._skip_pairs(s)] = torch.matmul(gs[s:].transpose(1, 2), X[s].to(gs.dtype)).float()
+        else:
+            grad = torch.matmul(gs.transpose(1, 2), X.to(gs.dtype)).float()
+        self.ext.dense_adam(W.data, self.skip_m, self.skip_v, grad.contiguous(), self._hyper(lr, c_g))
+
     def decode_loss(self, Y: torch.Tensor, want_yhat: bool = False) -> Optional[torch.Tensor]:
         """Kernel 5: sparse decode, reconstruction loss sums and the gradient seed."""
         e, m = self.ext, self.model
@@ -324,9 +360,10 @@ class FusedBatchTopKEngine:
         yhat = torch.empty(self.L, self.B, self.d, dtype=torch.float32, device=self.dev) if want_yhat else None
         dec_w = [w.data for w in m.dec_weight]
         bias_sum = self._bias_sum()
+        addend = self._skip_term(self._X_last) if m.skip_weight is not None else None
         if self.world == 1:
             e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
-                            None, None, None, bias_sum, None, Y, self.sigma, self.gs, yhat, self.sq_err, 1, [], 0, 0, self.status)
+                            None, None, None, bias_sum, addend, Y, self.sigma, self.gs, yhat, self.sq_err, 1, [], 0, 0, self.status)
             self.kernel_launches += 1
         else:
             sy = self.symm
@@ -337,7 +374,7 @@ class FusedBatchTopKEngine:
                             None, None, None, None, None, None, None, None, None, None, 2, sy.stage_ptrs, sy.rows_per_rank, self.rank, self.status)
             sy.barrier(e, self.status)
             # 2. owners reduce their rows, finish the loss and push the gradient seed to every rank
-            e.owner_reduce_loss(sy.stage, sy.gs_ptrs, self.rank, bias_sum, None, Y, self.sigma, yhat, self.sq_err, sy.rows_per_rank)
+            e.owner_reduce_loss(sy.stage, sy.gs_ptrs, self.rank, bias_sum, addend, Y, self.sigma, yhat, self.sq_err, sy.rows_per_rank)
             sy.barrier(e, self.status)
             pops.all_reduce(self.sq_err, group=self.group)
             if yhat is not None:
@@ -512,6 +549,7 @@ class FusedBatchTopKEngine:
         self.norm2, self.norm2_next = self.norm2_next, self.norm2
         self.norms_valid = True
         e.dense_adam(m.dec_bias.data, self.decb_m, self.decb_v, bias_grad, self._hyper(lr, c_g))
+        self._skip_adam(X, lr, c_g)
         e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v,
                             self.feat_off, self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, self._hyper(lr, 1.0), self.status)
         if self.fn == "jumprelu":
@@ -593,6 +631,8 @@ class FusedBatchTopKEngine:
             sd[f"dec_v.{i}"] = vv
         if self.fn == "jumprelu":
             sd["theta_m"], sd["theta_v"] = self.theta_m, self.theta_v
+        if self.model.skip_weight is not None:
+            sd["skip_m"], sd["skip_v"] = self.skip_m, self.skip_v
         return sd
 
     def load_optimizer_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
@@ -602,6 +642,9 @@ class FusedBatchTopKEngine:
         for i in range(len(self.dec_m)):
             self.dec_m[i].copy_(sd[f"dec_m.{i}"])
             self.dec_v[i].copy_(sd[f"dec_v.{i}"])
+        if self.model.skip_weight is not None and "skip_m" in sd:
+            self.skip_m.copy_(sd["skip_m"])
+            self.skip_v.copy_(sd["skip_v"])
         if self.fn == "jumprelu" and "theta_m" in sd:
             self.theta_m.copy_(sd["theta_m"])
             self.theta_v.copy_(sd["theta_v"])

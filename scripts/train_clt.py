@@ -93,6 +93,13 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--enable-profiling", action="store_true")
     g.add_argument("--enable-stochastic-rounding", action="store_true")
     g.add_argument("--engine", choices=["auto", "fused", "autograd"], default="auto")
+    g.add_argument("--optimizer-states-dtype", choices=["model_dtype", "float32", "bfloat16"], default="model_dtype",
+                   help="fused step: fp32 moments unless 'bfloat16' (stochastically rounded bf16 moments)")
+    g.add_argument("--fused-max-active-per-token", type=int, default=1024,
+                   help="fused JumpReLU step: capacity of the active-entry lists per token")
+    g.add_argument("--peer-health-timeout-s", type=float, default=None,
+                   help="tensor-parallel runs: declare a rank lost when it has not announced the next step for this long")
+    g.add_argument("--prefetch-batches", type=int, default=2)
     g.add_argument("--sampling-strategy", choices=["sequential", "random_chunk"], default="sequential")
     g = p.add_argument_group("Logging")
     g.add_argument("--log-interval", type=int, default=100)
@@ -204,6 +211,9 @@ def configs_from_args(args):
         dead_feature_window=args.dead_feature_window, enable_wandb=args.enable_wandb, wandb_project=args.wandb_project,
         wandb_entity=args.wandb_entity, wandb_run_name=run_name, wandb_tags=args.wandb_tags or [],
         enable_stochastic_rounding=getattr(args, "enable_stochastic_rounding", False), engine=getattr(args, "engine", "auto"),
+        optimizer_states_dtype=getattr(args, "optimizer_states_dtype", "model_dtype"),
+        fused_max_active_per_token=getattr(args, "fused_max_active_per_token", 1024),
+        peer_health_timeout_s=getattr(args, "peer_health_timeout_s", None), prefetch_batches=getattr(args, "prefetch_batches", 2),
     )
     return clt_config, training_config
 

@@ -719,3 +719,50 @@ def test_fused_token_topk_step_matches_autograd():
         upd, ref_upd = p.detach().float() - old, ref_params[name].detach() - old
         bad = ((upd - ref_upd).abs() > 0.008 * old.abs() + 3e-4).float().mean().item()
         assert bad < 2e-3, (name, bad)
+
+
+@pytest.mark.parametrize("tying", ["none", "per_source"])
+def test_fused_step_with_skip_connection(tying):
+    """Skip connection inside the fused step: forward term through the loss epilogue, weight update from gs^T x."""
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder, TrainingConfig
+    from crosslayer_coding_b200.training.fused_engine import FusedBatchTopKEngine
+
+    torch.manual_seed(51)
+    dev = _dev()
+    L, d, F, B, k = 3, 64, 256, 96, 8
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn="batchtopk", batchtopk_k=k, clt_dtype="bfloat16",
+                    decoder_tying=tying, skip_connection=True)
+    model = CrossLayerTranscoder(cfg, device=dev)
+    with torch.no_grad():
+        model.skip_weight.copy_(torch.randn_like(model.skip_weight) * 0.05)
+        if tying != "none":
+            for w in model.dec_weight:
+                w.uniform_(-0.05, 0.05)
+    tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="bf16", sparsity_lambda=0.0,
+                        preactivation_coef=0.0, optimizer="adamw")
+    eng = FusedBatchTopKEngine(model, tc, B)
+    X = torch.randn(L, B, d, device=dev).bfloat16()
+    Y = torch.randn(L, B, d, device=dev).bfloat16()
+    ref = _fp32_copy(model)
+    with torch.no_grad():
+        ref.skip_weight.copy_(model.skip_weight.float())
+    snap = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3)
+    out = eng.train_step(X, Y, step=0, lr=1e-3)
+    torch.cuda.synchronize()
+    eng.check_status()
+    mask = _oracle_mask(eng.preact, eng.mean, eng.rstd, eng.k_total, F)
+    pre = {l: torch.nn.functional.linear(X[l].float(), ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    acts = {l: (pre[l] + (eng.preact[l].float() - pre[l]).detach()) * mask[l] for l in range(L)}
+    src = {l: X[l].float() for l in range(L)}
+    loss = sum(torch.nn.functional.mse_loss(ref.decode({s: acts[s] for s in range(t + 1)}, t, source_inputs=src), Y[t].float()) for t in range(L))
+    assert abs(out.reconstruction.item() - loss.item()) < 3e-3 * max(1.0, loss.item()), (out.reconstruction.item(), loss.item())
+    loss.backward()
+    assert ref.skip_weight.grad.abs().max().item() > 0
+    opt.step()
+    ref_params = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        old = snap[name]
+        upd, ref_upd = p.detach().float() - old, ref_params[name].detach() - old
+        bad = ((upd - ref_upd).abs() > 0.008 * old.abs() + 3e-4).float().mean().item()
+        assert bad < 3e-3, (name, bad, (upd - ref_upd).abs().max().item())
