@@ -765,4 +765,5 @@ def test_fused_step_with_skip_connection(tying):
         old = snap[name]
         upd, ref_upd = p.detach().float() - old, ref_params[name].detach() - old
         bad = ((upd - ref_upd).abs() > 0.008 * old.abs() + 3e-4).float().mean().item()
-        assert bad < 3e-3, (name, bad, (upd - ref_upd).abs().max().item())
+        # Adam's first step is +-lr: an element whose gradient is ~0 may flip; allow a handful per tensor
+        assert bad < max(3e-3, 4.0 / old.numel()), (name, bad, (upd - ref_upd).abs().max().item())
