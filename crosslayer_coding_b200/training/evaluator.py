@@ -92,6 +92,58 @@ class CLTEvaluator:
         metrics.update(dead)
         return metrics
 
+    @torch.no_grad()
+    def compute_metrics_from_engine(self, engine, X: torch.Tensor, Y: torch.Tensor,
+                                    dead_neuron_mask: Optional[torch.Tensor] = None) -> Dict[str, Any]:
+        """The same metrics from the fused step's sparse forward: reconstructions from the sparse decode, L0 and
+        feature densities from the entry list (no dense ``[B, F]`` activation tensor is formed).  ``X`` / ``Y``:
+        ``[L, B, d]`` bf16, already normalised."""
+        model = self.model
+        L, B, Fl = engine.L, engine.B, engine.Fl
+        fired_before = engine.fired.clone()  # an evaluation forward must not count as "fired" for the dead-feature window
+        yhat = engine.forward(X, Y)  # [L, B, d] fp32, summed over ranks
+        engine.fired.copy_(fired_before)
+        cap = engine.ent_val.numel()
+        n = torch.clamp(engine.ctl[3], max=cap)
+        live = torch.arange(cap, device=X.device) < n
+        col = torch.where(live, engine.ent_col, (torch.arange(cap, device=X.device, dtype=torch.int32) % engine.ncols)).long()
+        nonzero = torch.zeros(engine.ncols, dtype=torch.float32, device=X.device)
+        fired = torch.zeros(engine.ncols, dtype=torch.float32, device=X.device)
+        nonzero.index_add_(0, col, (live & (engine.ent_val != 0)).float())
+        fired.index_add_(0, col, (live & (engine.ent_val > 1e-6)).float())
+        nonzero, fired = nonzero.view(L, Fl), fired.view(L, Fl)
+        per_layer = nonzero.sum(dim=1) / B
+        if model.world_size > 1:
+            pops.all_reduce(per_layer, group=model.process_group)
+            fired = pops.all_gather_cat(fired, dim=1, group=model.process_group)
+        fired = fired[:, : model.config.num_features]
+        host = per_layer.tolist()
+        total = float(sum(host))
+        avg = total / L
+        metrics: Dict[str, Any] = {
+            "sparsity/total_l0": total, "sparsity/avg_l0": avg,
+            "sparsity/sparsity_fraction": max(0.0, min(1.0, 1.0 - avg / model.config.num_features)),
+            "layerwise/l0": {f"layer_{l}": v for l, v in enumerate(host)},
+        }
+        metrics.update(self._compute_reconstruction_metrics({l: Y[l] for l in range(L)}, {l: yhat[l] for l in range(L)}))
+        dens = {f"layer_{l}": self._log_density(fired[l] / B).tolist() for l in range(L)}
+        heur = {f"layer_{l}": (fired[l] / ((fired[l] > 0).float() + 1e-9)).tolist() for l in range(L)}
+        metrics["layerwise/log_feature_density"] = dens
+        metrics["layerwise/consistent_activation_heuristic"] = heur
+        flat_d = [v for vals in dens.values() for v in vals]
+        flat_h = [v for vals in heur.values() for v in vals]
+        metrics["sparsity/feature_density_mean"] = float(np.mean(flat_d))
+        metrics["sparsity/log_feature_density_agg_hist"] = flat_d
+        metrics["sparsity/consistent_activation_heuristic_mean"] = float(np.mean(flat_h))
+        metrics["sparsity/consistent_activation_heuristic_agg_hist"] = flat_h
+        dead = self._compute_dead_neuron_metrics(dead_neuron_mask)
+        dead["dead_features/total_eval"] = sum(dead.get("layerwise/dead_features", {}).values())
+        metrics.update(dead)
+        # per-layer spread of the pre-activations of this forward (reference trainer.py:884-897)
+        stds = engine.preact[:, :, : engine.Fv].float().std(dim=(1, 2)) if engine.Fv > 0 else torch.zeros(L, device=X.device)
+        metrics["layerwise/preactivation_std_dev"] = {f"layer_{l}": v for l, v in enumerate(stds.tolist())}
+        return metrics
+
     # ------------------------------------------------------------------ pieces
     def _compute_sparsity(self, activations: Dict[int, torch.Tensor]) -> Dict[str, Any]:
         L = self.model.config.num_layers

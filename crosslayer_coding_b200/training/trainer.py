@@ -430,19 +430,29 @@ class CLTTrainer:
     def _run_evaluation(self, step: int, inputs, targets) -> None:
         tc = self.training_config
         pops.barrier(self.process_group)
+        # fused runs evaluate through the sparse forward (no dense [B, F] activations) unless the dense diagnostics
+        # were asked for; the dead-feature counters are not touched by an evaluation forward
+        fused_eval = self.engine is not None and not tc.compute_sparsity_diagnostics
         with self.profiler.timer("evaluation"):
-            autocast = torch.autocast(device_type=self.device.type, dtype=self.autocast_dtype, enabled=self.autocast_enabled)
-            with autocast, torch.no_grad():
-                metrics = self.evaluator.compute_metrics(inputs, targets, dead_neuron_mask=self.dead_neurons_mask)
-                # per-layer std of the pre-activations (reference trainer.py:884-897)
-                pre, _ = self.model._encode_all_layers(inputs, gather=False)
-                stds = torch.stack([p.float().std() if p.numel() > 1 else torch.zeros((), device=self.device) for p in pre.values()])
-                metrics["layerwise/preactivation_std_dev"] = {f"layer_{l}": v for l, v in zip(pre.keys(), stds.tolist())}
-                if tc.compute_sparsity_diagnostics:
-                    from .diagnostics import compute_sparsity_diagnostics
+            if fused_eval:
+                layers = list(range(self.clt_config.num_layers))
+                X, Y = _stack_layers(inputs, layers), _stack_layers(targets, layers)
+                if X.dtype != torch.bfloat16:
+                    X, Y = X.to(torch.bfloat16), Y.to(torch.bfloat16)
+                metrics = self.evaluator.compute_metrics_from_engine(self.engine, X, Y, dead_neuron_mask=self.dead_neurons_mask)
+            else:
+                autocast = torch.autocast(device_type=self.device.type, dtype=self.autocast_dtype, enabled=self.autocast_enabled)
+                with autocast, torch.no_grad():
+                    metrics = self.evaluator.compute_metrics(inputs, targets, dead_neuron_mask=self.dead_neurons_mask)
+                    # per-layer std of the pre-activations (reference trainer.py:884-897)
+                    pre, _ = self.model._encode_all_layers(inputs, gather=False)
+                    stds = torch.stack([p.float().std() if p.numel() > 1 else torch.zeros((), device=self.device) for p in pre.values()])
+                    metrics["layerwise/preactivation_std_dev"] = {f"layer_{l}": v for l, v in zip(pre.keys(), stds.tolist())}
+                    if tc.compute_sparsity_diagnostics:
+                        from .diagnostics import compute_sparsity_diagnostics
 
-                    acts = self.model.get_feature_activations(inputs, gather=False)
-                    metrics.update(compute_sparsity_diagnostics(self.model, tc, acts))
+                        acts = self.model.get_feature_activations(inputs, gather=False)
+                        metrics.update(compute_sparsity_diagnostics(self.model, tc, acts))
         self.metric_logger.log_evaluation_metrics(step, metrics)
         if self.rank == 0:
             logger.info(

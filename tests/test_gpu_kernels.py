@@ -767,3 +767,28 @@ def test_fused_step_with_skip_connection(tying):
         bad = ((upd - ref_upd).abs() > 0.008 * old.abs() + 3e-4).float().mean().item()
         # Adam's first step is +-lr: an element whose gradient is ~0 may flip; allow a handful per tensor
         assert bad < max(3e-3, 4.0 / old.numel()), (name, bad, (upd - ref_upd).abs().max().item())
+
+
+def test_evaluator_metrics_from_engine_match_dense_path():
+    """Evaluation through the sparse forward gives the dense evaluator's numbers."""
+    from crosslayer_coding_b200.training.evaluator import CLTEvaluator
+
+    cfg, model, tc, eng, X, Y = _engine_and_model(L=3, d=64, F=256, B=96, k=8, seed=13)
+    for s in range(3):
+        eng.train_step(X, Y, step=s, lr=1e-3)
+    fired = eng.fired.clone()
+    ev = CLTEvaluator(model, X.device, None, normalization_method="none", d_model=cfg.d_model)
+    dead = torch.zeros(3, 256, dtype=torch.bool, device=X.device)
+    dead[1, :5] = True
+    got = ev.compute_metrics_from_engine(eng, X, Y, dead_neuron_mask=dead)
+    assert torch.equal(eng.fired, fired)
+    with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+        want = ev.compute_metrics({l: X[l] for l in range(3)}, {l: Y[l] for l in range(3)}, dead_neuron_mask=dead)
+    assert got["sparsity/total_l0"] == pytest.approx(8.0) and want["sparsity/total_l0"] == pytest.approx(8.0, abs=0.05)
+    for key in ("reconstruction/normalized_mean_reconstruction_error", "reconstruction/explained_variance"):
+        assert got[key] == pytest.approx(want[key], rel=0.02, abs=0.01), key
+    assert got["dead_features/total_eval"] == want["dead_features/total_eval"] == 5
+    gd = torch.tensor(got["layerwise/log_feature_density"]["layer_0"])
+    wd = torch.tensor(want["layerwise/log_feature_density"]["layer_0"])
+    assert ((gd - wd).abs() > 1e-4).float().mean().item() < 0.05  # selections differ only by bf16 ties of the dense path
+    assert set(got["layerwise/preactivation_std_dev"]) == {"layer_0", "layer_1", "layer_2"}
