@@ -9,10 +9,11 @@ The reference computes ``model(inputs)`` densely: per layer an encoder GEMM, the
 
 Selections:
   * ``batchtopk``  global top ``k*B`` of the per-feature batch z-scores (same kernels as the training step),
+  * ``topk``       every token's top ``k`` of the same z-scores (exact per-token radix selection),
   * ``jumprelu``   ``x >= exp(log_threshold[l, f])``   (the form a converted BatchTopK model is deployed in),
   * ``relu``       ``x > 0`` (only useful while the activations are sparse; dense layers overflow the list and
                    the call reports it, see ``check_status``).
-``topk`` (per-token), skip connections and tensor-parallel groups are not covered here; ``supports`` says so and
+Skip connections and tensor-parallel groups are not covered here; ``supports`` says so and
 callers use ``CrossLayerTranscoder.forward`` for those.
 """
 from __future__ import annotations
@@ -29,9 +30,9 @@ _MIN_POSITIVE_BF16 = 9.183549615799121e-41  # 2**-133, the smallest positive bf1
 def supports(model) -> Optional[str]:
     """``None`` when ``SparseForward`` covers the model's configuration, else the reason it does not."""
     cfg = model.config
-    if cfg.activation_fn not in ("batchtopk", "jumprelu", "relu"):
+    if cfg.activation_fn not in ("batchtopk", "topk", "jumprelu", "relu"):
         return f"activation_fn={cfg.activation_fn!r}"
-    if cfg.activation_fn == "batchtopk" and cfg.topk_mode != "global":
+    if cfg.activation_fn in ("batchtopk", "topk") and cfg.topk_mode != "global":
         return "topk_mode='per_layer'"
     if cfg.skip_connection:
         return "skip_connection"
@@ -64,6 +65,12 @@ class SparseForward:
         if self.fn == "batchtopk":
             self.k_total = min(int(cfg.batchtopk_k) * B, B * L * Fl)
             cap = max(self.k_total, 8)
+        elif self.fn == "topk":
+            from .activations import resolve_token_k
+
+            self.k_token = resolve_token_k(float(cfg.topk_k), L * Fl)
+            self.k_total = self.k_token * B
+            cap = max(self.k_total, 8)
         else:
             cap = int(min(B * L * Fl, max_active_per_token * B))
         self.cap = cap
@@ -73,11 +80,12 @@ class SparseForward:
         self.ent_tok = torch.empty(cap, dtype=i32, device=dev)
         self.ent_col = torch.empty(cap, dtype=i32, device=dev)
         self.ent_val = torch.empty(cap, dtype=f32, device=dev)
+        if self.fn in ("batchtopk", "topk"):
+            self.mean = torch.empty(L, Fl, dtype=f32, device=dev)
+            self.rstd = torch.empty(L, Fl, dtype=f32, device=dev)
         if self.fn == "batchtopk":
             from ..training.fused_engine import histogram_range
 
-            self.mean = torch.empty(L, Fl, dtype=f32, device=dev)
-            self.rstd = torch.empty(L, Fl, dtype=f32, device=dev)
             self.hist = torch.zeros(2 * 8192 + 32, dtype=i32, device=dev)
             self.key_lo, self.shift = histogram_range(self.k_total, B * L * Fl)
             cand_cap = int(min(B * L * Fl, max(1 << 20, 4 * self.k_total)))
@@ -128,6 +136,10 @@ class SparseForward:
             e.batchtopk_select(self.preact, self.mean, self.rstd, self.Fl, self.Fl, 0, self.Fl, self.k_total, self.key_lo, self.shift,
                                self.hist, self.ctl, self.ent_tok, self.ent_col, self.ent_val, self.cand[0], self.cand[1], self.cand[2],
                                self.cand[3], self.status, 1, 0, [], [], 0, 0, self.sel_state, self.pool)
+        elif self.fn == "topk":
+            e.colstats(self.preact, self.mean, self.rstd)
+            e.token_topk_select(self.preact, self.mean, self.rstd, self.Fl, self.k_token, self.ctl, self.ent_tok, self.ent_col,
+                                self.ent_val, self.status)
         else:
             e.threshold_select(self.preact, self._theta(), self.Fl, self.Fl, self.ctl, self.ent_tok, self.ent_col, self.ent_val, self.status)
         self.tok_cnt.zero_()

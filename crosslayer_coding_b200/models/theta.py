@@ -79,6 +79,31 @@ def accumulate_theta_batch(model, inputs: Dict[int, torch.Tensor], stats: Dict[s
 
 
 @torch.no_grad()
+def accumulate_theta_batch_sparse(sf, X: torch.Tensor, stats: Dict[str, torch.Tensor]) -> None:
+    """The same statistic from the sparse forward (``models.sparse_forward.SparseForward``): the batch mean / std of
+    every feature come from the column-statistics kernel, the per-feature minimum of the selected z-scores from the
+    entry list - no dense ``[B, L*F]`` selection, which is what the dense path spends its time on."""
+    sf.encode(X)
+    L, Fl = sf.L, sf.Fl
+    std = 1.0 / sf.rstd - act.ZSCORE_EPS
+    stats["mean"] += sf.mean[:, : stats["mean"].shape[1]]
+    stats["std"] += std[:, : stats["std"].shape[1]]
+    stats["batches"] += 1
+    cap = sf.ent_val.numel()
+    n = torch.clamp(sf.ctl[3], max=cap)
+    live = (torch.arange(cap, device=X.device) < n) & (sf.ent_val > 0)
+    col = torch.where(live, sf.ent_col, torch.zeros_like(sf.ent_col)).long()
+    z = (sf.ent_val - sf.mean.reshape(-1)[col]) * sf.rstd.reshape(-1)[col]
+    z = torch.where(live, z, torch.full_like(z, float("inf")))
+    mins = torch.full((L * Fl,), float("inf"), device=X.device)
+    mins.scatter_reduce_(0, col, z, reduce="amin", include_self=True)
+    mins = mins.view(L, Fl)[:, : stats["sum_min"].shape[1]]
+    ok = torch.isfinite(mins)
+    stats["sum_min"] += torch.where(ok, mins, torch.zeros_like(mins))
+    stats["cnt_min"] += ok.float()
+
+
+@torch.no_grad()
 def estimate_theta_posthoc(
     model,
     data_iter: Iterable,
@@ -92,13 +117,26 @@ def estimate_theta_posthoc(
     model.eval()
     stats = _new_stats(model)
     done = 0
+    sparse = None  # sm_100a sparse forward, built for the first batch's size when the model is covered by it
     for batch in data_iter:
         if num_batches is not None and done >= num_batches:
             break
         inputs = batch[0] if isinstance(batch, (tuple, list)) else batch
         dev = model.enc_weight.device
         inputs = {l: x.to(dev) for l, x in inputs.items()}
-        accumulate_theta_batch(model, inputs, stats)
+        layers = sorted(inputs)
+        rows = inputs[layers[0]].reshape(-1, model.config.d_model).shape[0] if layers else 0
+        if sparse is None and dev.type == "cuda" and layers == list(range(model.config.num_layers)):
+            from . import sparse_forward
+
+            if sparse_forward.supports(model) is None:
+                sparse = sparse_forward.SparseForward(model, rows)
+        if sparse is not None and rows == sparse.B:
+            X = torch.stack([inputs[l].reshape(-1, model.config.d_model) for l in layers]).to(torch.bfloat16)
+            accumulate_theta_batch_sparse(sparse, X, stats)
+            sparse.check_status()
+        else:
+            accumulate_theta_batch(model, inputs, stats)
         done += 1
     if done == 0:
         logger.warning("Rank %d: no batches were processed for theta estimation", model.rank)

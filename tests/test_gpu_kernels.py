@@ -792,3 +792,40 @@ def test_evaluator_metrics_from_engine_match_dense_path():
     wd = torch.tensor(want["layerwise/log_feature_density"]["layer_0"])
     assert ((gd - wd).abs() > 1e-4).float().mean().item() < 0.05  # selections differ only by bf16 ties of the dense path
     assert set(got["layerwise/preactivation_std_dev"]) == {"layer_0", "layer_1", "layer_2"}
+
+
+@pytest.mark.parametrize("fn", ["batchtopk", "topk"])
+def test_theta_estimation_through_the_sparse_forward_matches_dense(fn):
+    """BatchTopK / TopK -> JumpReLU threshold statistics from the entry list against the dense accumulation."""
+    import copy
+
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder
+    from crosslayer_coding_b200.models import theta as theta_mod
+    from crosslayer_coding_b200.models.sparse_forward import SparseForward
+
+    torch.manual_seed(61)
+    dev = _dev()
+    L, d, F, B = 3, 64, 256, 128
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=fn, batchtopk_k=10, topk_k=10, clt_dtype="bfloat16")
+    model = CrossLayerTranscoder(cfg, device=dev)
+    batches = [torch.randn(L, B, d, device=dev).bfloat16() for _ in range(4)]
+    dense_stats = theta_mod._new_stats(model)
+    sparse_stats = theta_mod._new_stats(model)
+    sf = SparseForward(model, B)
+    for X in batches:
+        theta_mod.accumulate_theta_batch(model, {l: X[l] for l in range(L)}, dense_stats)
+        theta_mod.accumulate_theta_batch_sparse(sf, X, sparse_stats)
+    sf.check_status()
+    assert torch.allclose(sparse_stats["mean"], dense_stats["mean"], atol=2e-3)
+    assert torch.allclose(sparse_stats["std"], dense_stats["std"], rtol=2e-2, atol=1e-3)
+    # the selections agree except for bf16 near-ties: compare the per-feature statistic where both paths saw the feature
+    both = (sparse_stats["cnt_min"] > 0) & (dense_stats["cnt_min"] > 0)
+    assert both.float().mean().item() > 0.3
+    assert ((sparse_stats["cnt_min"] != dense_stats["cnt_min"]).float().mean().item()) < 0.02
+    a = sparse_stats["sum_min"][both] / sparse_stats["cnt_min"][both]
+    b = dense_stats["sum_min"][both] / dense_stats["cnt_min"][both]
+    assert ((a - b).abs() > 0.02 * b.abs() + 0.02).float().mean().item() < 0.02
+    # and the public entry point takes the sparse path on its own
+    m2 = copy.deepcopy(model)
+    th = theta_mod.estimate_theta_posthoc(m2, iter([({l: X[l] for l in range(L)}, None) for X in batches]), num_batches=4)
+    assert m2.config.activation_fn == "jumprelu" and torch.isfinite(th).all() and (th > 0).all()
