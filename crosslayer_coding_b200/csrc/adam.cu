@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(256, 2) decoder_rows_adam_untied_kernel(const 
 // place in shared memory -> row out.  The ring keeps several rows per CTA in flight in both directions and
 // the consumers never wait on a global load, except for the rare feature with more than four entries.
 // Every mbarrier wait is bounded; a timeout sets the status word and drains the copies in flight.
-constexpr int kAdamStages = 4;
+constexpr int kAdamStages = 4;  // at most; rows above 24 KB per stage run with three so that two CTAs fit an SM
 constexpr int kAdamSlots = 4;  // gradient-seed rows per stage
 
 struct AdamStageHdr {  // 64 bytes in front of every stage, written by the producer before it arms the barrier
@@ -395,10 +395,10 @@ __device__ __forceinline__ void stbf(__nv_bfloat16* p, const float (&o)[EPT], un
 }
 
 template <typename WT, bool SR, int EPT, typename MT>
-__global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAdamParams p, int gthreads, int stage_bytes, int* status) {
+__global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAdamParams p, int gthreads, int stage_bytes, int ns, int* status) {
   extern __shared__ __align__(128) uint8_t smem_raw_adam[];  // bulk copies need 16-byte alignment only
   uint8_t* ring = smem_raw_adam;
-  AdamBulkShared* sh = reinterpret_cast<AdamBulkShared*>(ring + size_t(kAdamStages) * stage_bytes);
+  AdamBulkShared* sh = reinterpret_cast<AdamBulkShared*>(ring + size_t(ns) * stage_bytes);
   const int d = p.d, B = p.B, Fp = p.F_pitch;
   const int nconsumer = gthreads;
   const int tid = threadIdx.x;
@@ -409,7 +409,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
   const uint32_t w_bytes = uint32_t(d) * sizeof(WT), mv_bytes = uint32_t(d) * sizeof(MT), gs_bytes = uint32_t(d) * 2u;
   const uint32_t off_w = 64, off_m = off_w + w_bytes, off_v = off_m + mv_bytes, off_gs = off_v + mv_bytes;
   if (tid == 0) {
-    for (int s = 0; s < kAdamStages; ++s) {
+    for (int s = 0; s < ns; ++s) {
       mbar_init(&sh->full[s], 1);
       mbar_init(&sh->done[s], nconsumer / 32);
     }
@@ -451,7 +451,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
         load_offsets(k + 2, nn);
         fresh = false;
       }
-      const int st = i % kAdamStages;
+      const int st = i % ns;
       uint8_t* stage = ring + size_t(st) * stage_bytes;
       AdamStageHdr* h = reinterpret_cast<AdamStageHdr*>(stage);
       const int ne = cur.e - cur.b;
@@ -481,11 +481,11 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       }
     };
     int issued = 0;
-    for (; issued < n && issued < kAdamStages; ++issued) issue_loads(issued);
+    for (; issued < n && issued < ns; ++issued) issue_loads(issued);
     int i = 0;
     for (; i < n; ++i) {
-      const int st = i % kAdamStages;
-      if (!mbar_wait(&sh->done[st], (i / kAdamStages) & 1, abort_flag)) break;
+      const int st = i % ns;
+      if (!mbar_wait(&sh->done[st], (i / ns) & 1, abort_flag)) break;
       uint8_t* stage = ring + size_t(st) * stage_bytes;
       const AdamStageHdr* h = reinterpret_cast<const AdamStageHdr*>(stage);
       const int sti = h->ti;
@@ -505,7 +505,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       // rows whose loads were issued but never consumed: give them a bounded chance to land
       for (int j = i; j < issued; ++j) {
         const long long start = clock64();
-        while (!mbar_try_wait(&sh->full[j % kAdamStages], (j / kAdamStages) & 1))
+        while (!mbar_try_wait(&sh->full[j % ns], (j / ns) & 1))
           if (clock64() - start > kWaitTimeoutCycles) break;
       }
     }
@@ -518,8 +518,8 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
     float dacc[kAdamSlots] = {0.f, 0.f, 0.f, 0.f};
     float norm2 = 0.f, pc = 0.f;
     for (int i = 0; i < n; ++i) {
-      const int st = i % kAdamStages;
-      if (!mbar_wait(&sh->full[st], (i / kAdamStages) & 1, abort_flag)) break;
+      const int st = i % ns;
+      if (!mbar_wait(&sh->full[st], (i / ns) & 1, abort_flag)) break;
       uint8_t* stage = ring + size_t(st) * stage_bytes;
       const AdamStageHdr* h = reinterpret_cast<const AdamStageHdr*>(stage);
       const int ne = h->ne, r = h->r, R = h->R, col = h->col, ti = h->ti, b = h->b;
@@ -986,13 +986,16 @@ struct CltDecAdamArgs {
 };
 
 // Launch geometry of the bulk-copy row pipeline (shared by the decoder and the encoder update).
-static int bulk_rows_adam_geometry(int d, bool weights_bf16, bool moments_bf16, int* ept_out, int* gthreads_out, int* stage_bytes_out, size_t* smem_out) {
+static int bulk_rows_adam_geometry(int d, bool weights_bf16, bool moments_bf16, int* ept_out, int* gthreads_out, int* stage_bytes_out, size_t* smem_out,
+                                   int* nstages_out = nullptr) {
   const int ept = d <= 1024 ? 4 : 8;  // elements per consumer thread: more, shorter threads where the row allows
   const int gthreads = ((d / ept + 31) / 32) * 32;
   const size_t wsz = weights_bf16 ? 2 : 4;
   const size_t msz = moments_bf16 ? 2 : 4;
   const int stage_bytes = int(((64 + size_t(d) * (wsz + 2 * msz + 2 * kAdamSlots)) + 127) / 128 * 128);
-  const size_t smem = size_t(kAdamStages) * stage_bytes + sizeof(AdamBulkShared) + 256;
+  const int nstages = stage_bytes > 24 * 1024 ? 3 : kAdamStages;
+  if (nstages_out) *nstages_out = nstages;
+  const size_t smem = size_t(nstages) * stage_bytes + sizeof(AdamBulkShared) + 256;
   *ept_out = ept; *gthreads_out = gthreads; *stage_bytes_out = stage_bytes; *smem_out = smem;
   return (d % 8 == 0 && gthreads <= 256 && smem <= 200 * 1024) ? 1 : 0;
 }
@@ -1006,7 +1009,8 @@ static int launch_rows_adam_bulk(const DecAdamParams& p, bool weights_bf16, bool
   size_t smem;
   const bool mb = p.moments_bf16 != 0;
   if (mb && !weights_bf16) return -1;  // bf16 moments go with bf16 weights
-  if (!bulk_rows_adam_geometry(p.d, weights_bf16, mb, &ept, &gthreads, &stage_bytes, &smem)) return -1;
+  int nstages = kAdamStages;
+  if (!bulk_rows_adam_geometry(p.d, weights_bf16, mb, &ept, &gthreads, &stage_bytes, &smem, &nstages)) return -1;
   int per_sm = int((227 * 1024) / (smem + 1024));
   const int by_threads = 2048 / (gthreads + 32);
   per_sm = per_sm > by_threads ? by_threads : per_sm;
@@ -1019,7 +1023,7 @@ static int launch_rows_adam_bulk(const DecAdamParams& p, bool weights_bf16, bool
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
       attr_set[which] = smem;
     }
-    kern<<<bgrid, gthreads + 32, smem, st>>>(p, gthreads, stage_bytes, status);
+    kern<<<bgrid, gthreads + 32, smem, st>>>(p, gthreads, stage_bytes, nstages, status);
     return 0;
   };
   using bf = __nv_bfloat16;
