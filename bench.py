@@ -261,7 +261,7 @@ def run_ours(args, world, rank, local):
         import torch.distributed as dist
 
         shard_group = dist.group.WORLD  # each rank copies 1/W of a batch over PCIe, the rest arrives over NVLink
-    store = InMemoryActivationStore(host, dev, loop=True, prefetch=2, shard_group=shard_group)
+    store = InMemoryActivationStore(host, dev, loop=True, prefetch=3 if world > 1 else 2, shard_group=shard_group)
     store.mean_tg = {l: mean_tg[l].to(dev) for l in range(L)}
     store.std_tg = {l: (std_tg[l] + 1e-6).to(dev) for l in range(L)}
     log_dir = tempfile.mkdtemp(prefix="clt_bench_")

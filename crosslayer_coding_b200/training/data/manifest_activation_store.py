@@ -110,8 +110,10 @@ class ManifestActivationStore(BaseActivationStore):
         shape = (2, self.num_layers, self.train_batch_size_tokens, self.d_model)
         self._storage_torch = _TORCH_VIEW[self.stored_dtype]
         # slots: prefetch in the queue + one being assembled + one held by the consumer
-        self.stager = DeviceStager(shape, self._storage_torch, self.device, depth=self.prefetch_batches + 2,
-                                   shard_group=shard_group if not shard_data or world == 1 else None, row_dim=2)
+        use_shard = shard_group if (not shard_data or world == 1) else None
+        # sharded staging keeps two batches' copy + gather queued ahead of the consumer: more slots in flight
+        self.stager = DeviceStager(shape, self._storage_torch, self.device, depth=self.prefetch_batches + (4 if use_shard is not None else 2),
+                                   shard_group=use_shard, row_dim=2)
         self.row_shard = None  # (first row, row count) of the batch positions this rank assembles
         if getattr(self.stager, "shard_world", 1) > 1:
             self.row_shard = (self.stager.shard_rank * self.stager.rows_per_rank, self.stager.rows_per_rank)
@@ -289,7 +291,9 @@ class ManifestActivationStore(BaseActivationStore):
             self._producer_done = False  # the next call starts a new producer at the sampler's position
             raise payload
         slot = payload
-        if self.row_shard is not None and self._lookahead_ready():
+        # two batches ahead: the gather of a batch queued only one step ahead tends to sit behind the step's long
+        # kernels and to finish after the step does
+        while self.row_shard is not None and len(self._submitted) < 2 and (not self._submitted or self._submitted[-1][0] == "batch"):
             nxt = self._queue.get()
             self._submitted.append(nxt)
             if nxt[0] == "batch":
@@ -301,11 +305,6 @@ class ManifestActivationStore(BaseActivationStore):
         inputs = LayerBatch.from_stacked(batch[0], self.layer_indices)
         targets = LayerBatch.from_stacked(batch[1], self.layer_indices)
         return inputs, targets
-
-    def _lookahead_ready(self) -> bool:
-        """Sharded staging: whether the next message can be taken now.  Every rank has to take the same decision
-        (the gather is a collective), so the look-ahead waits for the producer instead of polling it."""
-        return True
 
     def advance_epoch(self) -> None:
         self._shutdown_thread()

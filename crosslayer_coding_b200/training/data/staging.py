@@ -31,7 +31,8 @@ class DeviceStager:
         if self.cuda:
             self.host = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(self.depth)]
             self.dev = [torch.empty(shape, dtype=dtype, device=self.device) for _ in range(self.depth)]
-            self.stream = torch.cuda.Stream(device=self.device)
+            # high priority: the copy / gather kernels are tiny and should slip in between the step's long kernels
+            self.stream = torch.cuda.Stream(device=self.device, priority=-1)
             self.copied: List[Optional[torch.cuda.Event]] = [None] * self.depth
             self.released: List[Optional[torch.cuda.Event]] = [None] * self.depth
             self._init_shard(shard_group, row_dim)
