@@ -45,8 +45,17 @@ def _topk_flat_mask(rank: torch.Tensor, k_total: int) -> torch.Tensor:
     if k_total >= n:
         return torch.ones_like(mask).view_as(rank)
     flat = rank.reshape(-1)
-    _, order = torch.sort(flat, descending=True, stable=True)
-    mask[order[:k_total]] = True
+    # k-th largest value by partial selection, then the ties at that value in index order: the same set as a
+    # stable descending sort, without sorting the (mostly discarded) rest
+    kth = torch.topk(flat, k_total, sorted=False).values.min()
+    if torch.isnan(kth):
+        _, order = torch.sort(flat, descending=True, stable=True)
+        mask[order[:k_total]] = True
+        return mask.view_as(rank)
+    torch.gt(flat, kth, out=mask)
+    need = k_total - int(mask.sum())
+    if need > 0:
+        mask[(flat == kth).nonzero(as_tuple=True)[0][:need]] = True
     return mask.view_as(rank)
 
 
@@ -96,9 +105,17 @@ class TokenTopK(torch.autograd.Function):
         if k >= width:
             return torch.ones_like(x, dtype=torch.bool)
         rank = x if x_for_ranking is None else x_for_ranking
-        _, order = torch.sort(rank, dim=-1, descending=True, stable=True)
-        mask = torch.zeros_like(x, dtype=torch.bool)
-        mask.scatter_(-1, order[..., :k], True)
+        kth = torch.topk(rank, k, dim=-1, sorted=False).values.amin(dim=-1, keepdim=True)
+        if bool(torch.isnan(kth).any()):
+            _, order = torch.sort(rank, dim=-1, descending=True, stable=True)
+            mask = torch.zeros_like(x, dtype=torch.bool)
+            mask.scatter_(-1, order[..., :k], True)
+            return mask
+        # strictly larger entries, then the ties at the k-th value in index order (what a stable sort keeps)
+        mask = rank > kth
+        tie = rank == kth
+        need = k - mask.sum(dim=-1, keepdim=True)
+        mask |= tie & (tie.cumsum(dim=-1) <= need)
         return mask
 
     @staticmethod
