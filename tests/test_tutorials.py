@@ -10,11 +10,11 @@ REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.integration
 
 
-def _run(name, tmp_path):
+def _run(name, tmp_path, *args, expect=0):
     env = dict(os.environ, CLT_TUTORIAL_DIR=str(tmp_path), CUDA_VISIBLE_DEVICES="")
-    res = subprocess.run([sys.executable, os.path.join(REPO, "tutorials", name)], capture_output=True, text=True, timeout=900,
+    res = subprocess.run([sys.executable, os.path.join(REPO, "tutorials", name), *args], capture_output=True, text=True, timeout=900,
                          env=env, cwd=os.path.join(REPO, "tutorials"))
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert res.returncode == expect, res.stdout[-2000:] + res.stderr[-3000:]
     return res.stdout
 
 
@@ -25,11 +25,46 @@ def test_end_to_end_and_conversion(tmp_path):
     assert "activation function is now: jumprelu" in out
 
 
+def test_topk_and_jumprelu_walkthroughs(tmp_path):
+    out = _run("1C_end_to_end_topk.py", tmp_path)
+    assert "topk_k=16.0: active features per token min/max = 16/16" in out and "reloaded: topk" in out
+    out = _run("1D_end_to_end_jumprelu.py", tmp_path)
+    assert "reloaded model with trained thresholds" in out
+
+
 def test_server_protocol_and_remote_training(tmp_path):
+    import socket
+    import time
+
+    import requests
+
     out = _run("3_server_upload_and_slice.py", tmp_path)
     assert "slice: (4, 2, 4, 64)" in out
     out = _run("2_remote_training.py", tmp_path)
     assert "server info" in out
+    # tutorial 4 trains from a server somebody else started: none there -> exit code 2, then one serving tutorial 2's data
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    url = f"http://127.0.0.1:{port}"
+    assert "no activation server" in _run("4_train_against_running_server.py", tmp_path, "--server-url", url, expect=2)
+    env = dict(os.environ, HOST="127.0.0.1", PORT=str(port), STORAGE_BASE_DIR=str(tmp_path / "2" / "server_data"), PYTHONPATH=REPO)
+    server = subprocess.Popen([sys.executable, "-m", "crosslayer_coding_b200.server.main"], env=env,
+                              stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    try:
+        for _ in range(200):
+            try:
+                if requests.get(url + "/api/v1/health", timeout=1).ok:
+                    break
+            except requests.RequestException:
+                time.sleep(0.1)
+        out = _run("4_train_against_running_server.py", tmp_path, "--server-url", url, "--steps", "10")
+        assert "trained from the remote store" in out
+        assert "is not on the server" in _run("4_train_against_running_server.py", tmp_path, "--server-url", url,
+                                              "--dataset-id", "nobody/nothing", expect=3)
+    finally:
+        server.terminate()
+        server.wait(timeout=10)
 
 
 def test_analysis_helpers(tmp_path):
