@@ -93,7 +93,7 @@ struct CltPeerTable {
   int rank;
   void* ptr[8];
 };
-int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int* status, cudaStream_t st);
+int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int* status, long long timeout_cycles, cudaStream_t st);
 int clt_owner_reduce_loss(const float* stage, const CltPeerTable* gs_peers, const float* bias_sum, const float* addend, const void* target,
                           const float* sigma, float* yhat_out, double* sq_err, int L, int B, int d, int rows_per_rank, cudaStream_t st);
 int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st);
@@ -405,11 +405,23 @@ CltPeerTable make_table(const std::vector<int64_t>& ptrs, int64_t rank) {
   return t;
 }
 
-void peer_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t slot, int64_t seq, Tensor& status) {
+// timeout_s <= 0: the default bound of every device-side wait (about a second)
+void peer_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t slot, int64_t seq, Tensor& status, double timeout_s) {
   need(status, at::kInt, "status");
   const CltPeerTable t = make_table(flag_ptrs, rank);
   c10::cuda::CUDAGuard guard(status.device());
-  check(clt_peer_barrier(&t, int(slot), static_cast<unsigned int>(seq), status.data_ptr<int>(), cur_stream()), "peer_barrier");
+  const long long cycles = timeout_s > 0 ? static_cast<long long>(timeout_s * 2.0e9) : 0;  // SM clock <= 2 GHz
+  check(clt_peer_barrier(&t, int(slot), static_cast<unsigned int>(seq), status.data_ptr<int>(), cycles, cur_stream()), "peer_barrier");
+}
+
+// One strided copy on the current stream through the copy engines: `height` rows of `width` bytes, source and
+// destination pitches in bytes.  Either side may be pinned host memory, local device memory or a peer's
+// memory that is mapped into this process (the driver picks the direction from the pointers).
+void memcpy_2d(int64_t dst, int64_t dst_pitch, int64_t src, int64_t src_pitch, int64_t width, int64_t height) {
+  TORCH_CHECK(dst != 0 && src != 0 && width > 0 && height > 0 && dst_pitch >= width && src_pitch >= width, "memcpy_2d: bad geometry");
+  const cudaError_t err = cudaMemcpy2DAsync(reinterpret_cast<void*>(dst), size_t(dst_pitch), reinterpret_cast<const void*>(src),
+                                            size_t(src_pitch), size_t(width), size_t(height), cudaMemcpyDefault, cur_stream());
+  TORCH_CHECK(err == cudaSuccess, "memcpy_2d: ", cudaGetErrorString(err));
 }
 
 void owner_reduce_loss(const Tensor& stage, const std::vector<int64_t>& gs_ptrs, int64_t rank, const Tensor& bias_sum, const OptTensor& addend,
@@ -526,7 +538,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sparse_decode", &sparse_decode);
   m.def("recon_epilogue", &recon_epilogue);
   m.def("gs_colsum", &gs_colsum);
-  m.def("peer_barrier", &peer_barrier);
+  m.def("peer_barrier", &peer_barrier, py::arg("flag_ptrs"), py::arg("rank"), py::arg("slot"), py::arg("seq"), py::arg("status"),
+        py::arg("timeout_s") = 0.0);
+  m.def("memcpy_2d", &memcpy_2d);
   m.def("owner_reduce_loss", &owner_reduce_loss);
   m.def("decoder_rows_adam", &decoder_rows_adam);
   m.def("encoder_rows_adam", &encoder_rows_adam);

@@ -36,7 +36,9 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 
 // flags[r] points at rank r's flag array [slots][world]; every rank writes `seq` into slot/rank position of
 // every peer and waits until all peers wrote theirs.  One CTA of at least `world` threads.
-__global__ void peer_barrier_kernel(PeerTable flags, int slot, uint32_t seq, int* __restrict__ status) {
+// `timeout_cycles`: the phase barriers of the training step use kWaitTimeoutCycles (the ranks reach them within
+// microseconds of one another); the staging barriers wait for a peer's data loader and are given a longer limit.
+__global__ void peer_barrier_kernel(PeerTable flags, int slot, uint32_t seq, int* __restrict__ status, long long timeout_cycles) {
   const int tid = threadIdx.x;
   __threadfence_system();
   if (tid < flags.world) {
@@ -45,7 +47,7 @@ __global__ void peer_barrier_kernel(PeerTable flags, int slot, uint32_t seq, int
     const uint32_t* mine = static_cast<const uint32_t*>(flags.ptr[flags.rank]) + slot * flags.world + tid;
     const long long start = clock64();
     while (ld_acquire_sys_u32(mine) != seq) {
-      if (clock64() - start > kWaitTimeoutCycles) {
+      if (clock64() - start > timeout_cycles) {
         atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
         break;
       }
@@ -136,9 +138,10 @@ static PeerTable to_table(const CltPeerTable* a) {
   return t;
 }
 
-extern "C" int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int* status, cudaStream_t st) {
+extern "C" int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int* status, long long timeout_cycles,
+                                cudaStream_t st) {
   if (flags->world <= 1) return 0;
-  peer_barrier_kernel<<<1, 32, 0, st>>>(to_table(flags), slot, seq, status);
+  peer_barrier_kernel<<<1, 32, 0, st>>>(to_table(flags), slot, seq, status, timeout_cycles > 0 ? timeout_cycles : kWaitTimeoutCycles);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
