@@ -354,8 +354,9 @@ def run_ours(args, world, rank, local):
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": int(store.h2d_bytes_per_batch), "d2h_bytes_per_step": 4 * world,
                 "h2d_bytes_per_step_per_rank": int(store.h2d_bytes_per_rank),
-                "staging": "pinned host ring -> side-stream copy of this rank's 1/W token rows -> NVLink all-gather" if world > 1
-                else "pinned host ring -> side-stream copy"},
+                "staging": ("pinned host ring -> side-stream copy of this rank's 1/W token rows -> "
+                            + ("copy-engine push into every peer's symmetric-memory slot over NVLink" if getattr(store.stager, "push", False)
+                               else "NVLink all-gather")) if world > 1 else "pinned host ring -> side-stream copy"},
         "gpu_launches": int(launches),
         "final_loss": losses[-1] if losses else None,
         "parity": parity,

@@ -73,7 +73,7 @@ class InMemoryActivationStore(BaseActivationStore):
         dev = self.stager.acquire(slot)
         self._last_slot = slot
         # keep the pipeline full: queue the copy of the batch after this one now
-        while len(self._inflight) < self.prefetch - 0 and self.stager.cuda and len(self._inflight) < self.stager.depth - 1:
+        while len(self._inflight) < self.prefetch and self.stager.cuda and len(self._inflight) < self.stager.depth - 1:
             if not self._submit_next():
                 break
         inputs = LayerBatch.from_stacked(dev[0], self.layer_indices)

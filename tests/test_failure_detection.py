@@ -116,3 +116,9 @@ def test_bounded_peer_wait_reports_timeout_and_keeps_the_context():
     # the context is still usable
     x = torch.arange(10, device=dev).float()
     assert float((x * 2).sum()) == 90.0
+    # the limit is a parameter (the staging barriers wait longer than the step's phase barriers): a quarter of the default
+    status.zero_()
+    t0 = time.time()
+    ext.peer_barrier([f.data_ptr() for f in flags], 0, 1, 2, status, timeout_s=0.25)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 1 and time.time() - t0 < 0.6 * max(waited, 0.5), (time.time() - t0, waited)

@@ -829,3 +829,22 @@ def test_theta_estimation_through_the_sparse_forward_matches_dense(fn):
     m2 = copy.deepcopy(model)
     th = theta_mod.estimate_theta_posthoc(m2, iter([({l: X[l] for l in range(L)}, None) for X in batches]), num_batches=4)
     assert m2.config.activation_fn == "jumprelu" and torch.isfinite(th).all() and (th > 0).all()
+
+
+def test_strided_copy_places_a_row_range(ext):
+    """The staging copy: rows [r0, r0 + n) of every outer index, pinned host -> device and device -> device."""
+    dev = _dev()
+    outer, rows, inner, r0, n = 6, 32, 40, 8, 8
+    host = torch.randn(outer, rows, inner).bfloat16().pin_memory()
+    a = torch.zeros(outer, rows, inner, dtype=torch.bfloat16, device=dev)
+    b = torch.zeros_like(a)
+    es = host.element_size()
+    pitch, width, off = rows * inner * es, n * inner * es, r0 * inner * es
+    ext.memcpy_2d(a.data_ptr() + off, pitch, host.data_ptr() + off, pitch, width, outer)
+    ext.memcpy_2d(b.data_ptr() + off, pitch, a.data_ptr() + off, pitch, width, outer)
+    torch.cuda.synchronize()
+    want = torch.zeros_like(host)
+    want[:, r0:r0 + n] = host[:, r0:r0 + n]
+    assert torch.equal(a.cpu(), want) and torch.equal(b.cpu(), want)
+    with pytest.raises(RuntimeError):
+        ext.memcpy_2d(a.data_ptr(), 8, host.data_ptr(), 8, 16, 1)  # pitch below the width
