@@ -52,13 +52,16 @@ __device__ __forceinline__ void fma8(float (&acc)[8], float a, const uint4& v) {
 }
 
 // Output of one (token, target, 8-element slice): partial sums (mode 0), peer push (mode 2) or the finished
-// loss epilogue (mode 1).
-__device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int tok, int t, int e0, const float (&a)[8], float* sq_s) {
+// loss epilogue (mode 1).  Returns the slice's squared error (mode 1, else 0); the callers sum it in registers and
+// across the warp: a shared-memory atomic per thread on the L per-target sums costs tens of thousands of cycles
+// per token (32 lanes on one address, floating-point add as a compare-and-swap loop).
+__device__ __forceinline__ float decode_epilogue(const DecodeParams& p, int tok, int t, int e0, const float (&a)[8]) {
   const long long off = (1LL * t * p.B + tok) * p.d + e0;
   if (p.mode == 0) {
     float4* dst = reinterpret_cast<float4*>(p.yhat_partial + off);
     dst[0] = make_float4(a[0], a[1], a[2], a[3]);
     dst[1] = make_float4(a[4], a[5], a[6], a[7]);
+    return 0.f;
   } else if (p.mode == 2) {
     // reduce-scatter by push: peer store into the owner's slot for this rank (NVLink posted writes)
     const int owner = tok / p.rows_per_rank;
@@ -66,6 +69,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int tok, 
     float4* dst = reinterpret_cast<float4*>(p.stage_peers[owner] + ((1LL * p.rank * p.L + t) * p.rows_per_rank + lrow) * p.d + e0);
     dst[0] = make_float4(a[0], a[1], a[2], a[3]);
     dst[1] = make_float4(a[4], a[5], a[6], a[7]);
+    return 0.f;
   } else {
     float y[8], out[8];
     const uint4 tv = *reinterpret_cast<const uint4*>(p.target + off);
@@ -92,7 +96,7 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int tok, 
       dst[0] = make_float4(out[0], out[1], out[2], out[3]);
       dst[1] = make_float4(out[4], out[5], out[6], out[7]);
     }
-    atomicAdd(&sq_s[t], sq);
+    return sq;
   }
 }
 
@@ -173,9 +177,13 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
 
 #pragma unroll
   for (int j = 0; j < TPG; ++j) {
-    const int t = g + (blockIdx.y * TPG + j) * kGroups;
-    if (t >= p.L || !active) continue;
-    decode_epilogue(p, tok, t, e0, acc[j], sq_s);
+    const int t = g + (blockIdx.y * TPG + j) * kGroups;  // the same for all lanes of a warp (gthreads is a multiple of 32)
+    if (t >= p.L) continue;
+    float sq = active ? decode_epilogue(p, tok, t, e0, acc[j]) : 0.f;
+    if (p.mode == 1) {
+      sq = warp_sum(sq);
+      if ((threadIdx.x & 31) == 0) atomicAdd(&sq_s[t], sq);
+    }
   }
   if (p.mode == 1) {
     __syncthreads();
@@ -208,7 +216,8 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   DecodeBulkShared* sh = reinterpret_cast<DecodeBulkShared*>(ring + size_t(kDecodeStages) * stage_bytes);
   // Tensor-parallel push: rank r starts with the tokens owned by rank r + 1, so that at any moment the ranks
   // store into different owners instead of all into the same one.
-  const int tok = p.mode == 2 ? int((blockIdx.x + 1LL * ((p.rank + 1) % p.world) * p.rows_per_rank) % p.B) : int(blockIdx.x);
+  const long long tok_shift = p.mode == 2 ? 1LL * ((p.rank + 1) % p.world) * p.rows_per_rank : 0;
+  auto token_of = [&](int v) { return int((v + tok_shift) % p.B); };
   const int nconsumer = kGroups * gthreads;
   const bool is_producer = int(threadIdx.x) >= nconsumer;
   const int L = p.L, d = p.d;
@@ -227,30 +236,59 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   }
   __syncthreads();
   volatile int* abort_flag = &sh->abort_flag;
-  const int b = p.tok_off[tok], e = p.tok_off[tok + 1];
+  // Persistent CTA: tokens blockIdx.x, blockIdx.x + gridDim.x, ...  The producer runs through the entries of all of
+  // them without a break, so the ring already holds the first rows of the next token while the consumers are in the
+  // epilogue of the current one (loss, gradient seed, stores).
+  const int B = p.B, stride = int(gridDim.x);
 
   if (is_producer) {
     if (threadIdx.x == nconsumer) {
       int issued = 0;
+      int v = int(blockIdx.x);
+      int b = 0, e = 0;
+      if (v < B) {
+        const int tok = token_of(v);
+        b = __ldg(p.tok_off + tok);
+        e = __ldg(p.tok_off + tok + 1);
+      }
       int col_next = b < e ? __ldg(p.tcsr_col + b) : 0;
       float a_next = b < e ? __ldg(p.tcsr_val + b) : 0.f;
-      for (int i = b; i < e; ++i, ++issued) {
-        const int st = issued % kDecodeStages;
-        const uint32_t ph = (issued / kDecodeStages) & 1;
-        const int col = col_next;
-        const float a = a_next;
-        if (i + 1 < e) {  // the next entry's index is in flight while this stage is waited for
-          col_next = __ldg(p.tcsr_col + i + 1);
-          a_next = __ldg(p.tcsr_val + i + 1);
+      bool ok = true;
+      while (v < B && ok) {
+        // offsets of the token after this one: in flight while this token's entries are issued
+        const int vn = v + stride;
+        int bn = 0, en = 0;
+        if (vn < B) {
+          const int tokn = token_of(vn);
+          bn = __ldg(p.tok_off + tokn);
+          en = __ldg(p.tok_off + tokn + 1);
         }
-        if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) break;
-        const int sl = col >> 24, f = col & 0xFFFFFF;
-        const int R = sh->rows_s[sl];
-        const uint32_t bytes = uint32_t(R) * uint32_t(d) * 2u;
-        sh->ent_sl[st] = sl;
-        sh->ent_a[st] = a;
-        mbar_expect_tx(&sh->full[st], bytes);  // release: the two words above are visible to whoever sees the phase
-        bulk_load_1d(ring + size_t(st) * stage_bytes, sh->w_s[sl] + 1LL * f * R * d, bytes, &sh->full[st]);
+        for (int i = b; i < e; ++i, ++issued) {
+          const int st = issued % kDecodeStages;
+          const uint32_t ph = (issued / kDecodeStages) & 1;
+          const int col = col_next;
+          const float a = a_next;
+          if (i + 1 < e) {  // the next entry's index is in flight while this stage is waited for
+            col_next = __ldg(p.tcsr_col + i + 1);
+            a_next = __ldg(p.tcsr_val + i + 1);
+          } else if (bn < en) {
+            col_next = __ldg(p.tcsr_col + bn);
+            a_next = __ldg(p.tcsr_val + bn);
+          }
+          if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) { ok = false; break; }
+          const int sl = col >> 24, f = col & 0xFFFFFF;
+          const int R = sh->rows_s[sl];
+          const uint32_t bytes = uint32_t(R) * uint32_t(d) * 2u;
+          sh->ent_sl[st] = sl;
+          sh->ent_a[st] = a;
+          mbar_expect_tx(&sh->full[st], bytes);  // release: the two words above are visible to whoever sees the phase
+          bulk_load_1d(ring + size_t(st) * stage_bytes, sh->w_s[sl] + 1LL * f * R * d, bytes, &sh->full[st]);
+        }
+        if (b >= e && bn < en) {  // an empty token: the look-ahead above did not run
+          col_next = __ldg(p.tcsr_col + bn);
+          a_next = __ldg(p.tcsr_val + bn);
+        }
+        v = vn; b = bn; e = en;
       }
       if (*abort_flag) {
         // give copies already issued a bounded chance to land before the CTA retires
@@ -268,36 +306,52 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
     const int e0 = gt * 8;
     const bool active = e0 < d;
     const int lane = threadIdx.x & 31;
-    float acc[TPG][8];
-#pragma unroll
-    for (int j = 0; j < TPG; ++j)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
     int it = 0;
     bool ok = true;
-    for (int i = b; i < e; ++i, ++it) {
-      const int st = it % kDecodeStages;
-      const uint32_t ph = (it / kDecodeStages) & 1;
-      if (!mbar_wait(&sh->full[st], ph, abort_flag)) { ok = false; break; }
-      const int sl = sh->ent_sl[st];
-      const float a = sh->ent_a[st];
-      if (active && a != 0.f) {
-        const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(ring + size_t(st) * stage_bytes) + e0;
+    float sq_acc[TPG];
+#pragma unroll
+    for (int j = 0; j < TPG; ++j) sq_acc[j] = 0.f;
+    for (int v = int(blockIdx.x); v < B && ok; v += stride) {
+      const int tok = token_of(v);
+      const int b = __ldg(p.tok_off + tok), e = __ldg(p.tok_off + tok + 1);
+      float acc[TPG][8];
+#pragma unroll
+      for (int j = 0; j < TPG; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+      for (int i = b; i < e; ++i, ++it) {
+        const int st = it % kDecodeStages;
+        const uint32_t ph = (it / kDecodeStages) & 1;
+        if (!mbar_wait(&sh->full[st], ph, abort_flag)) { ok = false; break; }
+        const int sl = sh->ent_sl[st];
+        const float a = sh->ent_a[st];
+        if (active && a != 0.f) {
+          const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(ring + size_t(st) * stage_bytes) + e0;
+#pragma unroll
+          for (int j = 0; j < TPG; ++j) {
+            const int t = g + j * kGroups;
+            if (t < L && t >= sl) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (t - sl) * d));
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->empty[st]);  // this warp is done with the stage
+      }
+      if (ok) {
 #pragma unroll
         for (int j = 0; j < TPG; ++j) {
-          const int t = g + (blockIdx.y * TPG + j) * kGroups;
-          if (t < L && t >= sl) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (t - sl) * d));
+          const int t = g + j * kGroups;
+          if (t >= L || !active) continue;
+          sq_acc[j] += decode_epilogue(p, tok, t, e0, acc[j]);
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->empty[st]);  // this warp is done with the stage
     }
-    if (ok) {
+    if (p.mode == 1) {
 #pragma unroll
       for (int j = 0; j < TPG; ++j) {
-        const int t = g + (blockIdx.y * TPG + j) * kGroups;
-        if (t >= L || !active) continue;
-        decode_epilogue(p, tok, t, e0, acc[j], sh->sq_s);
+        const int t = g + j * kGroups;  // the same for all lanes of a warp
+        if (t >= L) continue;
+        const float sq = warp_sum(sq_acc[j]);
+        if (lane == 0) atomicAdd(&sh->sq_s[t], sq);
       }
     }
   }
@@ -410,12 +464,22 @@ extern "C" int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st) {
   const bool bulk = a->tying == 0 && a->status != nullptr && tpg <= 4 && smem <= 200 * 1024 && threads + 32 <= 544;
   if (bulk) {
     static size_t attr_set[5] = {0, 0, 0, 0, 0};
+    static int sm_count = 0;
+    if (sm_count == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
     auto launch = [&](auto kern) -> int {
       if (attr_set[tpg] < smem) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
         attr_set[tpg] = smem;
       }
-      kern<<<dim3(a->B, 1), threads + 32, smem, st>>>(p, gthreads, stage_bytes, a->status);
+      // persistent: as many CTAs as are resident at once, each walks its tokens with the ring kept full
+      int per_sm = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads + 32, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+      const int ctas = a->B < sm_count * per_sm ? a->B : sm_count * per_sm;
+      kern<<<dim3(ctas, 1), threads + 32, smem, st>>>(p, gthreads, stage_bytes, a->status);
       return 0;
     };
     int rc = 0;

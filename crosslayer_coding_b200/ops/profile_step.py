@@ -23,6 +23,7 @@ CASES = {
     "full": (12, 768, 24576, 4096, 200),
     "small": (12, 768, 4096, 4096, 33),
     "tiny": (4, 256, 2048, 1024, 16),
+    "shard8": (12, 768, 3072, 4096, 25),        # one rank's share of the full case at 8 GPUs (features and k divided by 8)
     "llama-1b": (16, 2048, 32768, 4096, 200),   # Llama-3.2-1B shape: 10 G parameters, about 110 GB with fp32 moments
 }
 
