@@ -205,9 +205,13 @@ struct DecodeBulkShared {
   const __nv_bfloat16* w_s[kMaxLayers];
   int rows_s[kMaxLayers];
   int abort_flag;
-  int ent_sl[kDecodeStages];    // source layer and activation of the entry in each stage, written by the producer
+  int ent_sl[kDecodeStages];    // source layer, activation, token and flags of the entry in each stage (producer)
   float ent_a[kDecodeStages];
+  int ent_tok[kDecodeStages];
+  int ent_flag[kDecodeStages];
 };
+constexpr int kDecodeLast = 1;  // last entry of its token: the consumers run the token's epilogue after it
+constexpr int kDecodeEnd = 2;   // no more tokens for this CTA
 
 template <int TPG>
 __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, int gthreads, int stage_bytes, int* status) {
@@ -236,15 +240,41 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   }
   __syncthreads();
   volatile int* abort_flag = &sh->abort_flag;
-  // Persistent CTA: tokens blockIdx.x, blockIdx.x + gridDim.x, ...  The producer runs through the entries of all of
-  // them without a break, so the ring already holds the first rows of the next token while the consumers are in the
-  // epilogue of the current one (loss, gradient seed, stores).
-  const int B = p.B, stride = int(gridDim.x);
+  // Persistent CTAs with dynamic token assignment: the producer draws token numbers from a global counter (the
+  // number of active features per token varies widely under BatchTopK, a static split leaves a long tail) and runs
+  // through the entries of its tokens without a break, so the ring already holds the first rows of the next token
+  // while the consumers are in the epilogue of the current one.  Every stage carries its entry's source layer,
+  // activation, token and a flag word (last entry of the token / end of work); the consumers need no other input.
+  const int B = p.B;
+  int* work_counter = status + 2;  // words 2 and 3 of the status array: next token, CTAs finished (reset by the last CTA)
 
   if (is_producer) {
     if (threadIdx.x == nconsumer) {
       int issued = 0;
-      int v = int(blockIdx.x);
+      bool ok = true;
+      auto emit = [&](int sl, int f, float a, int tok, int flags, bool copy) -> bool {
+        const int st = issued % kDecodeStages;
+        const uint32_t ph = (issued / kDecodeStages) & 1;
+        if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) return false;
+        sh->ent_sl[st] = sl;
+        sh->ent_a[st] = a;
+        sh->ent_tok[st] = tok;
+        sh->ent_flag[st] = flags;
+        if (copy) {
+          const int R = sh->rows_s[sl];
+          const uint32_t bytes = uint32_t(R) * uint32_t(d) * 2u;
+          mbar_expect_tx(&sh->full[st], bytes);  // release: the words above are visible to whoever sees the phase
+          bulk_load_1d(ring + size_t(st) * stage_bytes, sh->w_s[sl] + 1LL * f * R * d, bytes, &sh->full[st]);
+        } else {
+          mbar_arrive(&sh->full[st]);  // a record without rows: token without active features, or the end mark
+        }
+        ++issued;
+        return true;
+      };
+      // two tokens of look-ahead: the counter value for token n + 2 and the offsets of token n + 1 are in flight
+      // while the entries of token n are issued
+      int v = atomicAdd(work_counter, 1);
+      int vn = atomicAdd(work_counter, 1);
       int b = 0, e = 0;
       if (v < B) {
         const int tok = token_of(v);
@@ -253,19 +283,23 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
       }
       int col_next = b < e ? __ldg(p.tcsr_col + b) : 0;
       float a_next = b < e ? __ldg(p.tcsr_val + b) : 0.f;
-      bool ok = true;
       while (v < B && ok) {
-        // offsets of the token after this one: in flight while this token's entries are issued
-        const int vn = v + stride;
+        const int tok = token_of(v);
+        const int vnn = vn < B ? atomicAdd(work_counter, 1) : B;
         int bn = 0, en = 0;
         if (vn < B) {
           const int tokn = token_of(vn);
           bn = __ldg(p.tok_off + tokn);
           en = __ldg(p.tok_off + tokn + 1);
         }
-        for (int i = b; i < e; ++i, ++issued) {
-          const int st = issued % kDecodeStages;
-          const uint32_t ph = (issued / kDecodeStages) & 1;
+        if (b >= e) {
+          ok = emit(0, 0, 0.f, tok, kDecodeLast, false);
+          if (bn < en) {
+            col_next = __ldg(p.tcsr_col + bn);
+            a_next = __ldg(p.tcsr_val + bn);
+          }
+        }
+        for (int i = b; i < e && ok; ++i) {
           const int col = col_next;
           const float a = a_next;
           if (i + 1 < e) {  // the next entry's index is in flight while this stage is waited for
@@ -275,21 +309,11 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
             col_next = __ldg(p.tcsr_col + bn);
             a_next = __ldg(p.tcsr_val + bn);
           }
-          if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) { ok = false; break; }
-          const int sl = col >> 24, f = col & 0xFFFFFF;
-          const int R = sh->rows_s[sl];
-          const uint32_t bytes = uint32_t(R) * uint32_t(d) * 2u;
-          sh->ent_sl[st] = sl;
-          sh->ent_a[st] = a;
-          mbar_expect_tx(&sh->full[st], bytes);  // release: the two words above are visible to whoever sees the phase
-          bulk_load_1d(ring + size_t(st) * stage_bytes, sh->w_s[sl] + 1LL * f * R * d, bytes, &sh->full[st]);
+          ok = emit(col >> 24, col & 0xFFFFFF, a, tok, i + 1 == e ? kDecodeLast : 0, true);
         }
-        if (b >= e && bn < en) {  // an empty token: the look-ahead above did not run
-          col_next = __ldg(p.tcsr_col + bn);
-          a_next = __ldg(p.tcsr_val + bn);
-        }
-        v = vn; b = bn; e = en;
+        v = vn; vn = vnn; b = bn; e = en;
       }
+      if (ok) ok = emit(0, 0, 0.f, 0, kDecodeEnd, false);
       if (*abort_flag) {
         // give copies already issued a bounded chance to land before the CTA retires
         const int first = issued > kDecodeStages ? issued - kDecodeStages : 0;
@@ -306,42 +330,40 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
     const int e0 = gt * 8;
     const bool active = e0 < d;
     const int lane = threadIdx.x & 31;
-    int it = 0;
-    bool ok = true;
     float sq_acc[TPG];
+    float acc[TPG][8];
 #pragma unroll
-    for (int j = 0; j < TPG; ++j) sq_acc[j] = 0.f;
-    for (int v = int(blockIdx.x); v < B && ok; v += stride) {
-      const int tok = token_of(v);
-      const int b = __ldg(p.tok_off + tok), e = __ldg(p.tok_off + tok + 1);
-      float acc[TPG][8];
+    for (int j = 0; j < TPG; ++j) {
+      sq_acc[j] = 0.f;
 #pragma unroll
-      for (int j = 0; j < TPG; ++j)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
-      for (int i = b; i < e; ++i, ++it) {
-        const int st = it % kDecodeStages;
-        const uint32_t ph = (it / kDecodeStages) & 1;
-        if (!mbar_wait(&sh->full[st], ph, abort_flag)) { ok = false; break; }
-        const int sl = sh->ent_sl[st];
-        const float a = sh->ent_a[st];
-        if (active && a != 0.f) {
-          const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(ring + size_t(st) * stage_bytes) + e0;
-#pragma unroll
-          for (int j = 0; j < TPG; ++j) {
-            const int t = g + j * kGroups;
-            if (t < L && t >= sl) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (t - sl) * d));
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->empty[st]);  // this warp is done with the stage
-      }
-      if (ok) {
+      for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+    }
+    for (int it = 0;; ++it) {
+      const int st = it % kDecodeStages;
+      const uint32_t ph = (it / kDecodeStages) & 1;
+      if (!mbar_wait(&sh->full[st], ph, abort_flag)) break;
+      const int sl = sh->ent_sl[st];
+      const float a = sh->ent_a[st];
+      const int tok = sh->ent_tok[st];
+      const int flags = sh->ent_flag[st];
+      if (flags & kDecodeEnd) break;
+      if (active && a != 0.f) {
+        const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(ring + size_t(st) * stage_bytes) + e0;
 #pragma unroll
         for (int j = 0; j < TPG; ++j) {
           const int t = g + j * kGroups;
-          if (t >= L || !active) continue;
-          sq_acc[j] += decode_epilogue(p, tok, t, e0, acc[j]);
+          if (t < L && t >= sl) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (t - sl) * d));
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->empty[st]);  // this warp is done with the stage
+      if (flags & kDecodeLast) {
+#pragma unroll
+        for (int j = 0; j < TPG; ++j) {
+          const int t = g + j * kGroups;
+          if (t < L && active) sq_acc[j] += decode_epilogue(p, tok, t, e0, acc[j]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
         }
       }
     }
@@ -357,7 +379,15 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   }
   __syncthreads();
   if (p.mode == 1 && threadIdx.x < L && sh->sq_s[threadIdx.x] != 0.f) atomicAdd(&p.sq_err[threadIdx.x], double(sh->sq_s[threadIdx.x]));
-  if (threadIdx.x == 0 && sh->abort_flag && status != nullptr) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+  if (threadIdx.x == 0) {
+    if (sh->abort_flag) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+    // the last CTA to finish leaves both counters at zero for the next launch
+    __threadfence();
+    if (atomicAdd(status + 3, 1) == int(gridDim.x) - 1) {
+      status[2] = 0;
+      status[3] = 0;
+    }
+  }
 }
 
 // Epilogue for the tensor-parallel path, run after the partial reconstructions were summed across ranks:
