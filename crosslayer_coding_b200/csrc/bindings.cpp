@@ -371,7 +371,7 @@ void sparse_decode(const std::vector<Tensor>& dec_w, int64_t L, int64_t B, int64
   a.yhat_partial = opt_ptr<float>(yhat_partial); a.bias_sum = opt_ptr<const float>(bias_sum); a.addend = opt_ptr<const float>(addend);
   a.target = opt_ptr<const void>(target); a.sigma = opt_ptr<const float>(sigma); a.gs = opt_ptr<void>(gs);
   a.yhat_out = opt_ptr<float>(yhat_out); a.sq_err = opt_ptr<double>(sq_err); a.mode = int(mode);
-  if (status.has_value()) TORCH_CHECK(status->scalar_type() == at::kInt && status->numel() >= 4, "status: int32[4] (word 0 code, words 2-3 work counters of the decode kernel)");
+  if (status.has_value()) TORCH_CHECK(status->scalar_type() == at::kInt && status->numel() >= 4, "status: int32 tensor of at least 4 words (word 0 holds the code)");
   a.status = opt_ptr<int>(status);
   if (mode == 2) {
     TORCH_CHECK(stage_peers.size() >= 1 && stage_peers.size() <= 8 && rows_per_rank > 0, "mode 2 needs the peers' staging pointers");

@@ -205,13 +205,9 @@ struct DecodeBulkShared {
   const __nv_bfloat16* w_s[kMaxLayers];
   int rows_s[kMaxLayers];
   int abort_flag;
-  int ent_sl[kDecodeStages];    // source layer, activation, token and flags of the entry in each stage (producer)
+  int ent_sl[kDecodeStages];    // source layer and activation of the entry in each stage, written by the producer
   float ent_a[kDecodeStages];
-  int ent_tok[kDecodeStages];
-  int ent_flag[kDecodeStages];
 };
-constexpr int kDecodeLast = 1;  // last entry of its token: the consumers run the token's epilogue after it
-constexpr int kDecodeEnd = 2;   // no more tokens for this CTA
 
 template <int TPG>
 __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, int gthreads, int stage_bytes, int* status) {
@@ -220,8 +216,7 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   DecodeBulkShared* sh = reinterpret_cast<DecodeBulkShared*>(ring + size_t(kDecodeStages) * stage_bytes);
   // Tensor-parallel push: rank r starts with the tokens owned by rank r + 1, so that at any moment the ranks
   // store into different owners instead of all into the same one.
-  const long long tok_shift = p.mode == 2 ? 1LL * ((p.rank + 1) % p.world) * p.rows_per_rank : 0;
-  auto token_of = [&](int v) { return int((v + tok_shift) % p.B); };
+  const int tok = p.mode == 2 ? int((blockIdx.x + 1LL * ((p.rank + 1) % p.world) * p.rows_per_rank) % p.B) : int(blockIdx.x);
   const int nconsumer = kGroups * gthreads;
   const bool is_producer = int(threadIdx.x) >= nconsumer;
   const int L = p.L, d = p.d;
@@ -240,80 +235,31 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   }
   __syncthreads();
   volatile int* abort_flag = &sh->abort_flag;
-  // Persistent CTAs with dynamic token assignment: the producer draws token numbers from a global counter (the
-  // number of active features per token varies widely under BatchTopK, a static split leaves a long tail) and runs
-  // through the entries of its tokens without a break, so the ring already holds the first rows of the next token
-  // while the consumers are in the epilogue of the current one.  Every stage carries its entry's source layer,
-  // activation, token and a flag word (last entry of the token / end of work); the consumers need no other input.
-  const int B = p.B;
-  int* work_counter = status + 2;  // words 2 and 3 of the status array: next token, CTAs finished (reset by the last CTA)
+  const int b = p.tok_off[tok], e = p.tok_off[tok + 1];
 
   if (is_producer) {
     if (threadIdx.x == nconsumer) {
       int issued = 0;
-      bool ok = true;
-      auto emit = [&](int sl, int f, float a, int tok, int flags, bool copy) -> bool {
-        const int st = issued % kDecodeStages;
-        const uint32_t ph = (issued / kDecodeStages) & 1;
-        if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) return false;
-        sh->ent_sl[st] = sl;
-        sh->ent_a[st] = a;
-        sh->ent_tok[st] = tok;
-        sh->ent_flag[st] = flags;
-        if (copy) {
-          const int R = sh->rows_s[sl];
-          const uint32_t bytes = uint32_t(R) * uint32_t(d) * 2u;
-          mbar_expect_tx(&sh->full[st], bytes);  // release: the words above are visible to whoever sees the phase
-          bulk_load_1d(ring + size_t(st) * stage_bytes, sh->w_s[sl] + 1LL * f * R * d, bytes, &sh->full[st]);
-        } else {
-          mbar_arrive(&sh->full[st]);  // a record without rows: token without active features, or the end mark
-        }
-        ++issued;
-        return true;
-      };
-      // two tokens of look-ahead: the counter value for token n + 2 and the offsets of token n + 1 are in flight
-      // while the entries of token n are issued
-      int v = atomicAdd(work_counter, 1);
-      int vn = atomicAdd(work_counter, 1);
-      int b = 0, e = 0;
-      if (v < B) {
-        const int tok = token_of(v);
-        b = __ldg(p.tok_off + tok);
-        e = __ldg(p.tok_off + tok + 1);
-      }
       int col_next = b < e ? __ldg(p.tcsr_col + b) : 0;
       float a_next = b < e ? __ldg(p.tcsr_val + b) : 0.f;
-      while (v < B && ok) {
-        const int tok = token_of(v);
-        const int vnn = vn < B ? atomicAdd(work_counter, 1) : B;
-        int bn = 0, en = 0;
-        if (vn < B) {
-          const int tokn = token_of(vn);
-          bn = __ldg(p.tok_off + tokn);
-          en = __ldg(p.tok_off + tokn + 1);
+      for (int i = b; i < e; ++i, ++issued) {
+        const int st = issued % kDecodeStages;
+        const uint32_t ph = (issued / kDecodeStages) & 1;
+        const int col = col_next;
+        const float a = a_next;
+        if (i + 1 < e) {  // the next entry's index is in flight while this stage is waited for
+          col_next = __ldg(p.tcsr_col + i + 1);
+          a_next = __ldg(p.tcsr_val + i + 1);
         }
-        if (b >= e) {
-          ok = emit(0, 0, 0.f, tok, kDecodeLast, false);
-          if (bn < en) {
-            col_next = __ldg(p.tcsr_col + bn);
-            a_next = __ldg(p.tcsr_val + bn);
-          }
-        }
-        for (int i = b; i < e && ok; ++i) {
-          const int col = col_next;
-          const float a = a_next;
-          if (i + 1 < e) {  // the next entry's index is in flight while this stage is waited for
-            col_next = __ldg(p.tcsr_col + i + 1);
-            a_next = __ldg(p.tcsr_val + i + 1);
-          } else if (bn < en) {
-            col_next = __ldg(p.tcsr_col + bn);
-            a_next = __ldg(p.tcsr_val + bn);
-          }
-          ok = emit(col >> 24, col & 0xFFFFFF, a, tok, i + 1 == e ? kDecodeLast : 0, true);
-        }
-        v = vn; vn = vnn; b = bn; e = en;
+        if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) break;
+        const int sl = col >> 24, f = col & 0xFFFFFF;
+        const int R = sh->rows_s[sl];
+        const uint32_t bytes = uint32_t(R) * uint32_t(d) * 2u;
+        sh->ent_sl[st] = sl;
+        sh->ent_a[st] = a;
+        mbar_expect_tx(&sh->full[st], bytes);  // release: the two words above are visible to whoever sees the phase
+        bulk_load_1d(ring + size_t(st) * stage_bytes, sh->w_s[sl] + 1LL * f * R * d, bytes, &sh->full[st]);
       }
-      if (ok) ok = emit(0, 0, 0.f, 0, kDecodeEnd, false);
       if (*abort_flag) {
         // give copies already issued a bounded chance to land before the CTA retires
         const int first = issued > kDecodeStages ? issued - kDecodeStages : 0;
@@ -330,64 +276,45 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
     const int e0 = gt * 8;
     const bool active = e0 < d;
     const int lane = threadIdx.x & 31;
-    float sq_acc[TPG];
     float acc[TPG][8];
 #pragma unroll
-    for (int j = 0; j < TPG; ++j) {
-      sq_acc[j] = 0.f;
+    for (int j = 0; j < TPG; ++j)
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
-    }
-    for (int it = 0;; ++it) {
+    int it = 0;
+    bool ok = true;
+    for (int i = b; i < e; ++i, ++it) {
       const int st = it % kDecodeStages;
       const uint32_t ph = (it / kDecodeStages) & 1;
-      if (!mbar_wait(&sh->full[st], ph, abort_flag)) break;
+      if (!mbar_wait(&sh->full[st], ph, abort_flag)) { ok = false; break; }
       const int sl = sh->ent_sl[st];
       const float a = sh->ent_a[st];
-      const int tok = sh->ent_tok[st];
-      const int flags = sh->ent_flag[st];
-      if (flags & kDecodeEnd) break;
       if (active && a != 0.f) {
         const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(ring + size_t(st) * stage_bytes) + e0;
 #pragma unroll
         for (int j = 0; j < TPG; ++j) {
-          const int t = g + j * kGroups;
+          const int t = g + (blockIdx.y * TPG + j) * kGroups;
           if (t < L && t >= sl) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (t - sl) * d));
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->empty[st]);  // this warp is done with the stage
-      if (flags & kDecodeLast) {
-#pragma unroll
-        for (int j = 0; j < TPG; ++j) {
-          const int t = g + j * kGroups;
-          if (t < L && active) sq_acc[j] += decode_epilogue(p, tok, t, e0, acc[j]);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
-        }
-      }
     }
-    if (p.mode == 1) {
+    // one warp-level sum and one shared atomic per warp and target (the lanes of a warp share their targets)
 #pragma unroll
-      for (int j = 0; j < TPG; ++j) {
-        const int t = g + j * kGroups;  // the same for all lanes of a warp
-        if (t >= L) continue;
-        const float sq = warp_sum(sq_acc[j]);
+    for (int j = 0; j < TPG; ++j) {
+      const int t = g + (blockIdx.y * TPG + j) * kGroups;
+      if (t >= L) continue;
+      float sq = (ok && active) ? decode_epilogue(p, tok, t, e0, acc[j]) : 0.f;
+      if (p.mode == 1) {
+        sq = warp_sum(sq);
         if (lane == 0) atomicAdd(&sh->sq_s[t], sq);
       }
     }
   }
   __syncthreads();
   if (p.mode == 1 && threadIdx.x < L && sh->sq_s[threadIdx.x] != 0.f) atomicAdd(&p.sq_err[threadIdx.x], double(sh->sq_s[threadIdx.x]));
-  if (threadIdx.x == 0) {
-    if (sh->abort_flag) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
-    // the last CTA to finish leaves both counters at zero for the next launch
-    __threadfence();
-    if (atomicAdd(status + 3, 1) == int(gridDim.x) - 1) {
-      status[2] = 0;
-      status[3] = 0;
-    }
-  }
+  if (threadIdx.x == 0 && sh->abort_flag && status != nullptr) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
 }
 
 // Epilogue for the tensor-parallel path, run after the partial reconstructions were summed across ranks:
@@ -494,22 +421,12 @@ extern "C" int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st) {
   const bool bulk = a->tying == 0 && a->status != nullptr && tpg <= 4 && smem <= 200 * 1024 && threads + 32 <= 544;
   if (bulk) {
     static size_t attr_set[5] = {0, 0, 0, 0, 0};
-    static int sm_count = 0;
-    if (sm_count == 0) {
-      int dev = 0;
-      cudaGetDevice(&dev);
-      if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
-    }
     auto launch = [&](auto kern) -> int {
       if (attr_set[tpg] < smem) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
         attr_set[tpg] = smem;
       }
-      // persistent: as many CTAs as are resident at once, each walks its tokens with the ring kept full
-      int per_sm = 0;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads + 32, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
-      const int ctas = a->B < sm_count * per_sm ? a->B : sm_count * per_sm;
-      kern<<<dim3(ctas, 1), threads + 32, smem, st>>>(p, gthreads, stage_bytes, a->status);
+      kern<<<dim3(a->B, 1), threads + 32, smem, st>>>(p, gthreads, stage_bytes, a->status);
       return 0;
     };
     int rc = 0;
