@@ -122,8 +122,6 @@ class DeviceStager:
 
     def _push_rows(self, slot: int, host: torch.Tensor) -> None:
         """Own rows: pinned host -> own slot -> every peer's slot, as strided copies on the staging stream."""
-        import torch.distributed as dist
-
         es = host.element_size()
         width = self.rows_per_rank * self.inner * es          # bytes of this rank's rows per outer index
         pitch = self.rows * self.inner * es
