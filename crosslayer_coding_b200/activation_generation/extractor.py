@@ -167,6 +167,30 @@ class ActivationExtractorCLT:
             inputs[l], targets[l] = x, y
         return inputs, targets
 
+    @torch.no_grad()
+    def capture_layer_sequences(self, texts: List[str], layer: int):
+        """MLP-input activations of ``layer`` with the sequence axis kept: ``(input_ids [b, s], attention_mask [b, s],
+        activations [b, s, d])`` for one batch of texts (truncated to ``context_size``, padded to the longest).
+        Used by the feature-analysis tools, which map activations back to tokens (the reference traces the model per
+        batch for the same purpose, scripts/analysis/collect_top_activations.py:362-376)."""
+        enc = self.tokenizer(texts, **self.tokenizer_args)
+        input_ids = enc["input_ids"].to(self.device)
+        mask = enc.get("attention_mask")
+        mask = mask.to(self.device) if mask is not None else torch.ones_like(input_ids)
+        captured: Dict[str, torch.Tensor] = {}
+        module = self._resolve_module(self.mlp_input_module_path_template.format(layer))
+
+        def pre_hook(_m, args, kwargs=None):
+            x = args[0] if args else next(iter(kwargs.values()))
+            captured["x"] = x.detach()
+
+        handle = module.register_forward_pre_hook(pre_hook)
+        try:
+            self.model(input_ids, attention_mask=mask)
+        finally:
+            handle.remove()
+        return input_ids, mask, captured["x"]
+
     def stream_activations(
         self,
         dataset_path: Union[str, Iterable],

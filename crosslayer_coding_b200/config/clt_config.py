@@ -182,6 +182,12 @@ class TrainingConfig:
     # Fused JumpReLU step: capacity of the active-entry lists, in entries per token (a step whose
     # activations are denser reports it through the status word).
     fused_max_active_per_token: int = 1024
+    # Checkpoints: copy device -> pinned host on a side stream and write the files from a background thread
+    # (None: on for CUDA runs, off on CPU).
+    async_checkpoint: Optional[bool] = None
+    # fp16 loss scaling of the fused step (same defaults as torch.amp.GradScaler, reference trainer.py:107-141)
+    loss_scale_init: float = 65536.0
+    loss_scale_growth_interval: int = 2000
 
     def __post_init__(self) -> None:
         self.normalization_method = canonical_normalization(self.normalization_method)

@@ -36,6 +36,46 @@ def layer_l0(model, inputs: Dict[int, torch.Tensor]) -> Dict[int, float]:
 
 
 @torch.no_grad()
+def quick_l0_check(model, inputs: Dict[int, torch.Tensor], num_tokens: int = 1024, seed: Optional[int] = None) -> Dict[int, float]:
+    """Empirical L0 per layer on ``inputs`` (reference: ``run_quick_l0_checks_script``,
+    scripts/convert_batchtopk_to_jumprelu.py:766-870).  (Batch)TopK models are measured on the whole batch
+    through ``get_feature_activations`` (the selection is global), per-layer activations (JumpReLU, ReLU) on a
+    random sample of at most ``num_tokens`` tokens through ``encode``.  Entries count as active when
+    ``|a| > 1e-8``; a layer without tokens reports NaN."""
+    from .parallel import ops as pops
+
+    L = model.config.num_layers
+    out: Dict[int, float] = {l: float("nan") for l in range(L)}
+    dev, dt = model.enc_weight.device, model.enc_weight.dtype
+    live = {l: (x.reshape(-1, x.shape[-1]) if x.dim() == 3 else x).to(device=dev, dtype=dt) for l, x in inputs.items() if x.numel() > 0}
+    if not live:
+        return out
+    if model.config.activation_fn in ("batchtopk", "topk"):
+        acts = model.get_feature_activations(live, gather=False)
+        vals = {l: (a.abs() > 1e-8).sum(dim=1).float().mean() for l, a in acts.items() if a.shape[0] > 0}
+    else:
+        gen = torch.Generator(device="cpu")
+        if seed is not None:
+            gen.manual_seed(int(seed))
+        else:
+            gen.seed()
+        vals = {}
+        for l, x in live.items():
+            n = min(int(num_tokens), x.shape[0])
+            idx = torch.randperm(x.shape[0], generator=gen)[:n].to(dev)
+            a = model.encode(x[idx], l, gather=False)
+            vals[l] = (a.abs() > 1e-8).sum(dim=1).float().mean()
+    if vals:
+        layers = sorted(vals)
+        t = torch.stack([vals[l] for l in layers])
+        if model.world_size > 1:
+            pops.all_reduce(t, group=model.process_group)
+        for l, v in zip(layers, t.tolist()):
+            out[l] = float(v)
+    return out
+
+
+@torch.no_grad()
 def l0_for_scales(preact: torch.Tensor, theta: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """``L0(s) = mean_tokens #{f : x_f >= s * theta_f}`` for every ``s`` in the ascending vector ``scales``,
     from a single pass over ``preact [B, F]``."""
@@ -58,9 +98,14 @@ def calibrate_layerwise_theta(
     scale_range: Tuple[float, float] = (0.1, 10.0),
     grid: int = 257,
     refine_steps: int = 12,
+    max_tokens: Optional[int] = None,
+    seed: Optional[int] = None,
 ) -> Dict[int, float]:
     """Scale every layer's threshold vector in place so that its L0 on ``inputs`` matches ``target_l0``.
-    Returns the scale applied per layer."""
+    Returns the scale applied per layer.  ``scale_range`` and ``refine_steps`` are the reference's search
+    range and iteration limit (``--l0-calibration-search-min/max-scale``, ``--l0-calibration-max-iters``);
+    ``max_tokens`` draws one random sample of the calibration tokens (the reference re-samples <= 1024 tokens
+    per probe; one fixed sample makes L0(s) monotone, so the search cannot oscillate)."""
     from .parallel import ops as pops
 
     if model.log_threshold is None:
@@ -79,7 +124,12 @@ def calibrate_layerwise_theta(
     for l in sorted(inputs):
         if l not in target_l0:
             continue
-        pre = model.get_preactivations(inputs[l].to(dev), l, gather=False).float()
+        x_l = inputs[l]
+        if max_tokens is not None and x_l.shape[0] > max_tokens:
+            gen = torch.Generator(device="cpu")
+            gen.manual_seed(int(seed if seed is not None else 0) + l)
+            x_l = x_l[torch.randperm(x_l.shape[0], generator=gen)[: int(max_tokens)].to(x_l.device)]
+        pre = model.get_preactivations(x_l.to(dev), l, gather=False).float()
         theta = model.log_threshold[l][: pre.shape[-1]].float().exp()
         l0s = l0_for_scales(pre, theta, scales)
         if model.world_size > 1:

@@ -21,6 +21,17 @@ def is_replicated(param: torch.nn.Parameter) -> bool:
     return getattr(param, "_is_replicated", False)
 
 
+def shard_width(num_features: int, world_size: int) -> int:
+    """Padded number of features per tensor-parallel rank: ``ceil(F / W)`` like the reference
+    (clt/models/parallel.py:53-77), rounded up to a multiple of 8 when sharded so that every shard satisfies
+    the 16-byte alignment of the fused kernels' vector loads and TMA boxes; the padding columns hold zeros and
+    sit behind the last valid feature of the rank."""
+    local = -(-num_features // max(1, world_size))
+    if world_size > 1:
+        local = (local + 7) // 8 * 8
+    return local
+
+
 class BaseTranscoder(nn.Module, ABC):
     def __init__(self, config: CLTConfig):
         super().__init__()

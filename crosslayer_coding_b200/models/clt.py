@@ -33,7 +33,7 @@ import torch.nn as nn
 from ..config import CLTConfig
 from ..parallel import ops as pops
 from . import activations as act
-from .base import BaseTranscoder, mark_replicated
+from .base import BaseTranscoder, mark_replicated, shard_width
 
 logger = logging.getLogger(__name__)
 
@@ -80,7 +80,7 @@ class CrossLayerTranscoder(BaseTranscoder):
         self.bandwidth = 1.0
 
         L, F, d = config.num_layers, config.num_features, config.d_model
-        self.local_features = -(-F // self.world_size)  # ceil: uniform padding like the reference
+        self.local_features = shard_width(F, self.world_size)  # uniform padding like the reference
         self.feature_start = self.rank * self.local_features
         self.valid_features = max(0, min(F, self.feature_start + self.local_features) - self.feature_start)
         Fl = self.local_features

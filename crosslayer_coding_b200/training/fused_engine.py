@@ -39,6 +39,11 @@ from ..parallel import ops as pops
 STATUS_NAMES = {0: "ok", 1: "wait timeout", 2: "list capacity exceeded", 3: "threshold outside histogram range", 4: "tie overflow"}
 
 
+class EngineStatusError(RuntimeError):
+    """A kernel of the fused step reported a problem through the status word (a bounded wait that ran out, a
+    list that did not fit).  The step that reported it skipped its parameter update."""
+
+
 def histogram_range(k_total: int, numel: int, pool_factor: float = 1.75):
     """First guess ``(key_lo, shift)`` of the selection histogram.  The z-scores are standardised per
     feature, so the range starts at the normal quantile below which all but ``pool_factor * k_total``
@@ -620,7 +625,7 @@ class FusedBatchTopKEngine:
         code = int(self.status[0].item())
         if code != 0:
             self.status.zero_()
-            raise RuntimeError(f"rank {self.rank}: fused step reported '{STATUS_NAMES.get(code, code)}'")
+            raise EngineStatusError(f"rank {self.rank}: fused step reported '{STATUS_NAMES.get(code, code)}'")
 
     # ------------------------------------------------------- optimizer state io
     def optimizer_state_dict(self) -> Dict[str, torch.Tensor]:

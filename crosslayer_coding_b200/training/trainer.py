@@ -160,8 +160,12 @@ class CLTTrainer:
         L = clt_config.num_layers
         if self.engine is None:
             self.n_forward_passes_since_fired = torch.zeros(L, self.model.valid_features, dtype=torch.long, device=self.device)
+        async_ckpt = training_config.async_checkpoint
+        if async_ckpt is None:
+            async_ckpt = self.device.type == "cuda"
         self.checkpoint_manager = CheckpointManager(
-            self.model, self.activation_store, None, self.log_dir, distributed, self.rank, self.device, self.world_size
+            self.model, self.activation_store, None, self.log_dir, distributed, self.rank, self.device, self.world_size,
+            async_save=bool(async_ckpt),
         )
         self._resume_state: Optional[Dict[str, Any]] = None
         self.start_step = 0
@@ -288,9 +292,14 @@ class CLTTrainer:
         return out.as_dict()
 
     def _any_dead_cached(self, step: int) -> bool:
-        # one host read every 100 steps is enough: features die slowly
+        """True when any rank holds a dead feature.  One host read every 100 steps is enough (features die
+        slowly).  The answer is agreed over the process group (all-reduce MAX at the same steps on every rank):
+        the auxiliary term runs collectives, so every rank has to take the same branch."""
         if not hasattr(self, "_dead_seen") or step % 100 == 0:
-            self._dead_seen = bool(self.dead_neurons_mask.any().item())
+            flag = self.dead_neurons_mask.any().to(torch.int32).reshape(1)
+            if self.world_size > 1:
+                pops.all_reduce(flag, op=pops.MAX, group=self.process_group)
+            self._dead_seen = bool(flag.item())
         return self._dead_seen
 
     def _train_step_autograd(self, inputs, targets, step: int, lr: float) -> Dict[str, torch.Tensor]:
@@ -391,14 +400,19 @@ class CLTTrainer:
                 last = step == tc.training_steps - 1
                 if step % tc.eval_interval == 0 or last:
                     self._run_evaluation(step, inputs, targets)
-                if (step > 0 and step % tc.checkpoint_interval == 0) or last:
+                want_ckpt = (step > 0 and step % tc.checkpoint_interval == 0) or last
+                if self.engine is not None and (want_ckpt or step % max(1, tc.log_interval) == 0):
+                    # before anything of this step is written out: a step whose kernels gave up a wait (or ran out
+                    # of list capacity) skipped its update, and the run stops here instead of saving it as good
+                    self._check_device_status()
+                if want_ckpt:
                     self.save_checkpoint(step)
-                if self.engine is not None and (step % max(1, tc.log_interval) == 0 or last):
-                    self.engine.check_status()
         except KeyboardInterrupt:
             if self.rank == 0:
                 logger.warning("Interrupted at step %d; writing the final checkpoint", step)
         except BaseException as exc:
+            from .fused_engine import EngineStatusError
+
             if health is not None:
                 from ..parallel.health import PeerLostError
 
@@ -407,11 +421,17 @@ class CLTTrainer:
                 # a collective with a lost rank would never complete: skip the final barrier and checkpoint
                 logger.error("Rank %d: stopping at step %d: %s", self.rank, step, exc)
                 lost_peer = True
+            if isinstance(exc, EngineStatusError):
+                # this rank's kernels reported a failed step: the other ranks may not have seen one, so no collective
+                # is entered here, and the weights of a failed step are not written over the last good checkpoint
+                logger.error("Rank %d: stopping at step %d without a final checkpoint: %s", self.rank, step, exc)
+                lost_peer = True
             raise
         finally:
             if not lost_peer:
                 pops.barrier(self.process_group)
                 self.save_checkpoint(step, final=True)
+            self.checkpoint_manager.wait()
             if hasattr(self.activation_store, "close"):
                 self.activation_store.close()
             self.metric_logger._save_metrics_to_disk()
@@ -426,6 +446,12 @@ class CLTTrainer:
             if self._owns_process_group and dist.is_initialized():
                 dist.destroy_process_group()
         return self.model
+
+    def _check_device_status(self) -> None:
+        self.engine.check_status()
+        stager = getattr(self.activation_store, "stager", None)
+        if stager is not None and hasattr(stager, "check_status"):
+            stager.check_status()
 
     def _run_evaluation(self, step: int, inputs, targets) -> None:
         tc = self.training_config
@@ -485,6 +511,9 @@ class CLTTrainer:
         if self.engine is not None:
             return dict(self.engine.optimizer_state_dict())
         out: Dict[str, torch.Tensor] = {}
+        # this rank's dead-feature counters travel with its optimizer shard (the pickled trainer state is rank 0's)
+        pad = self.model.local_features - self.n_forward_passes_since_fired.shape[1]
+        out["dead_counter_2d"] = torch.nn.functional.pad(self.n_forward_passes_since_fired, (0, pad)) if pad else self.n_forward_passes_since_fired
         names = {id(p): n for n, p in self.model.named_parameters()}
         for p, st in self.optimizer.state.items():
             n = names.get(id(p))
@@ -500,6 +529,12 @@ class CLTTrainer:
             return
         params = dict(self.model.named_parameters())
         for key, v in tensors.items():
+            if key == "dead_counter_2d":
+                self.n_forward_passes_since_fired.copy_(v[:, : self.n_forward_passes_since_fired.shape[1]].to(self.device))
+                self._dead_counter_restored = True
+                continue
+            if "::" not in key:
+                continue
             name, field = key.split("::", 1)
             p = params.get(name)
             if p is None:
@@ -516,7 +551,7 @@ class CLTTrainer:
             self._load_optimizer_tensors(state["optimizer_tensors"])
         if state.get("scaler_state_dict") and self.scaler.is_enabled():
             self.scaler.load_state_dict(state["scaler_state_dict"])
-        if self.engine is None and state.get("n_forward_passes_since_fired") is not None:
+        if self.engine is None and state.get("n_forward_passes_since_fired") is not None and not getattr(self, "_dead_counter_restored", False):
             c = state["n_forward_passes_since_fired"].to(self.device)
             if c.shape == self.n_forward_passes_since_fired.shape:
                 self.n_forward_passes_since_fired.copy_(c)

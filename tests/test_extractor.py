@@ -79,3 +79,47 @@ def test_layer_groups_are_ordered_numerically(tmp_path):
     with hdf5.H5File(path) as f:
         assert f.layer_groups() == ["layer_1", "layer_2", "layer_10", "layer_20", "layer_100"]
         assert float(f["layer_10/inputs"].read_rows([0])[0, 0]) == 10.0
+
+
+def test_collect_top_activations_with_base_model_in_the_loop(tiny_gpt2, tmp_path):
+    """The analysis script's base-model mode: text -> tiny GPT-2 (hooks) -> clt.encode -> per-feature top sequences with
+    token text, in the reference's JSON layout."""
+    import importlib.util
+    import json
+    import os
+    import types
+
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("collect_top", os.path.join(repo, "scripts", "analysis", "collect_top_activations.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    cfg = CLTConfig(num_features=12, num_layers=3, d_model=32, activation_fn="relu", normalization_method="none")
+    torch.manual_seed(1)
+    clt = CrossLayerTranscoder(cfg)
+    ex = ActivationExtractorCLT("tiny-gpt2", "transformer.h.{}.ln_2.input", "transformer.h.{}.mlp.output", device="cpu",
+                                context_size=8, inference_batch_size=2, model=tiny_gpt2, tokenizer=_Tok())
+    texts = ["a b c d", "e f g", "h i j k l", "m n", "o p q r s t"]
+    args = types.SimpleNamespace(layer=1, topk_per_feature=2, batch_size=2, max_dataset_samples=None, clt_config=str(tmp_path / "cfg.json"),
+                                 output_json=str(tmp_path / "out" / "top.json"), features_per_file=5, mlp_input_template="x", mlp_output_template="y",
+                                 context_size=8, model_name="tiny", dataset=None, dataset_split="validation", dataset_text_column="text")
+    files = mod.run_with_base_model(args, clt, torch.device("cpu"), extractor=ex, texts=texts)
+    assert len(files) == 3 and files[0].endswith("top_features_0_to_4.json")
+    merged = {}
+    for f in files:
+        merged.update(json.load(open(f)))
+    assert sorted(merged, key=int) == [str(i) for i in range(12)]
+    # oracle: encode every sequence by itself
+    best = {}
+    for sid, t in enumerate(texts):
+        ids, mask, x = ex.capture_layer_sequences([t], 1)
+        a = clt.encode(x[0].float(), 1)
+        for f in range(12):
+            best.setdefault(f, []).append((float(a[:, f].max()), sid, a[:, f].tolist()))
+    for f in range(12):
+        want = sorted(best[f], reverse=True)[:2]
+        got = merged[str(f)]["activations"]
+        assert abs(got["0"]["score"] - want[0][0]) < 1e-4 and abs(got["1"]["score"] - want[1][0]) < 1e-4
+        assert len(got["0"]["text"]) == len(got["0"]["values"]) == len(texts[want[0][1]].split())
+        assert all(abs(u - v) < 1e-4 for u, v in zip(got["0"]["values"], want[0][2]))

@@ -156,3 +156,47 @@ def test_parallel_ops_under_gloo_and_uninitialised():
     ops.all_gather(lst, t)
     assert lst[0] is t
     mp.spawn(_ops_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def _layers_worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from crosslayer_coding_b200.parallel.layers import ColumnParallelLinear, RowParallelLinear
+
+        g = torch.Generator().manual_seed(3)
+        d_in, feats, d_out, rows = 6, 21, 5, 7  # 21 features over 2 ranks: shards of 16 with 5 valid on the last rank
+        w_col, b_col = torch.randn(feats, d_in, generator=g), torch.randn(feats, generator=g)
+        w_row, b_row = torch.randn(d_out, feats, generator=g), torch.randn(d_out, generator=g)
+        x = torch.randn(rows, d_in, generator=g)
+        col = ColumnParallelLinear(d_in, feats, process_group=dist.group.WORLD)
+        row = RowParallelLinear(feats, d_out, process_group=dist.group.WORLD)
+        assert col.local_features == 16 and col.valid_features == (16 if rank == 0 else 5)
+        lo, n = col.feature_start, col.valid_features
+        with torch.no_grad():
+            col.weight.zero_(); col.bias_param.zero_(); row.weight.zero_()
+            col.weight[:n].copy_(w_col[lo:lo + n]); col.bias_param[:n].copy_(b_col[lo:lo + n])
+            row.weight[:, :n].copy_(w_row[:, lo:lo + n]); row.bias_param.copy_(b_row)
+        h = col(x)                                   # gathered [rows, feats] on every rank
+        y = row(torch.relu(h))                       # split locally, reduced, bias after the reduce
+        want_h = x @ w_col.t() + b_col
+        want_y = torch.relu(want_h) @ w_row.t() + b_row
+        assert h.shape == (rows, feats) and torch.allclose(h, want_h, atol=1e-5)
+        assert torch.allclose(y, want_y, atol=1e-5)
+        y.sum().backward()
+        ref_w = w_col.clone().requires_grad_(True)
+        (torch.relu(x @ ref_w.t() + b_col) @ w_row.t() + b_row).sum().backward()
+        assert torch.allclose(col.weight.grad[:n], ref_w.grad[lo:lo + n], atol=1e-5)
+        assert float(col.weight.grad[n:].abs().sum()) == 0.0  # padding rows receive nothing
+    finally:
+        dist.destroy_process_group()
+
+
+def test_standalone_parallel_linear_layers():
+    from crosslayer_coding_b200.parallel.layers import ColumnParallelLinear, RowParallelLinear
+
+    col = ColumnParallelLinear(4, 10)
+    row = RowParallelLinear(10, 3)
+    x = torch.randn(2, 4)
+    assert col(x).shape == (2, 10) and row(col(x)).shape == (2, 3) and col.local_features == 10
+    mp.spawn(_layers_worker, args=(2, _free_port()), nprocs=2, join=True)

@@ -4,6 +4,7 @@ import os
 import pytest
 import torch
 
+from crosslayer_coding_b200.models.base import shard_width
 from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder, TrainingConfig
 from crosslayer_coding_b200.activation_generation.synthetic import SparseDictionarySynth, SyntheticSpec, write_synthetic_dataset
 from crosslayer_coding_b200.training.checkpointing import CheckpointManager, merge_shards, slice_for_rank
@@ -123,7 +124,7 @@ def test_distributed_checkpoint_layout_merge_and_reshard(tmp_path, monkeypatch):
     def sharded(rank, world):
         m = CrossLayerTranscoder(cfg)
         m.world_size, m.rank = world, rank
-        m.local_features = -(-30 // world)
+        m.local_features = shard_width(30, world)
         m.feature_start = rank * m.local_features
         m.valid_features = max(0, min(30, m.feature_start + m.local_features) - m.feature_start)
         sd = slice_for_rank(full_sd, rank, world, 30)
@@ -141,7 +142,8 @@ def test_distributed_checkpoint_layout_merge_and_reshard(tmp_path, monkeypatch):
     models = [sharded(r, 2) for r in range(2)]
     for r in (1, 0):  # rank 0 merges, so it goes last
         cm = CheckpointManager(models[r], None, None, str(tmp_path), True, r, torch.device("cpu"), world_size=2)
-        cm._save_checkpoint(5, {"step": 5}, {"enc_m": torch.full((2, 15, 4), float(r))})
+        cm._save_checkpoint(5, {"step": 5}, {"enc_m": torch.full((2, 16, 4), float(r)), "dec_m.0": torch.full((16, 1, 4), float(r)),
+                                             "dead_counter": torch.arange(32) + 100 * r, "decb_m": torch.ones(2, 4), "step": torch.tensor(7)})
     step_dir = tmp_path / "step_5"
     names = set(os.listdir(step_dir))
     assert {"rank_0_model.safetensors", "rank_1_model.safetensors", "rank_0_optim.safetensors", "rank_1_optim.safetensors",
@@ -163,8 +165,20 @@ def test_distributed_checkpoint_layout_merge_and_reshard(tmp_path, monkeypatch):
     with torch.no_grad():
         three.enc_weight.zero_()
     CheckpointManager(three, None, None, str(tmp_path), True, 2, torch.device("cpu"), world_size=3).load_checkpoint(str(step_dir))
+    state3 = CheckpointManager(three, None, None, str(tmp_path), True, 2, torch.device("cpu"), world_size=3).load_checkpoint(str(step_dir))
     want = slice_for_rank(full_sd, 2, 3, 30)
     assert torch.equal(three.state_dict()["encoder_module.encoders.1.weight"], want["encoder_module.encoders.1.weight"])
+    # ... and so are the optimizer tensors: rank 2 of 3 holds features [32, 30) -> nothing valid; rank 1 of 3 holds [16, 30)
+    ot = CheckpointManager(sharded(1, 3), None, None, str(tmp_path), True, 1, torch.device("cpu"), world_size=3).load_checkpoint(str(step_dir))["optimizer_tensors"]
+    assert ot["enc_m"].shape == (2, 16, 4) and float(ot["enc_m"][:, :14].mean()) == 1.0 and float(ot["enc_m"][:, 14:].abs().sum()) == 0.0
+    assert ot["dec_m.0"].shape == (16, 1, 4) and float(ot["dec_m.0"][:14].mean()) == 1.0
+    # saved rank 1 counted 100 + l * 16 + j for its local feature j of layer l: global feature 16 + j
+    assert ot["dead_counter"].shape == (32,) and int(ot["dead_counter"][0]) == 100 and int(ot["dead_counter"][16 + 3]) == 100 + 16 + 3
+    assert int(ot["step"]) == 7 and torch.equal(ot["decb_m"], torch.ones(2, 4))
+    assert state3["optimizer_resharded_from"] == 2
+    # one world: everything concatenated, padding dropped
+    one = CheckpointManager(sharded(0, 1), None, None, str(tmp_path), False, 0, torch.device("cpu"), world_size=1).load_checkpoint(str(step_dir))["optimizer_tensors"]
+    assert one["enc_m"].shape == (2, 30, 4) and float(one["enc_m"][:, :16].sum()) == 0.0 and float(one["enc_m"][:, 16:].mean()) == 1.0
     # pruning keeps the newest three step directories
     cm0 = CheckpointManager(models[0], None, None, str(tmp_path), True, 0, torch.device("cpu"), world_size=1)
     for s in (6, 7, 8):
