@@ -30,13 +30,18 @@ __device__ __forceinline__ uint32_t hash32(uint32_t x) {
   x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16;
   return x;
 }
-__device__ __forceinline__ __nv_bfloat16 to_bf16(float v, unsigned int seed, unsigned long long idx) {
-  if (seed == 0) return __float2bfloat16_rn(v);
+// fp32 -> 16-bit weight; a non-zero seed asks for stochastic rounding (bf16 builds; fp16 rounds to nearest)
+__device__ __forceinline__ t16 to_bf16(float v, unsigned int seed, unsigned long long idx) {
+#if CLT_T16_IS_HALF
+  return float_to_t16(v);
+#else
+  if (seed == 0) return float_to_t16(v);
   const uint32_t u = __float_as_uint(v);
-  if ((u & 0x7F800000u) == 0x7F800000u) return __float2bfloat16_rn(v);
+  if ((u & 0x7F800000u) == 0x7F800000u) return float_to_t16(v);
   const uint32_t r = hash32(uint32_t(idx) ^ hash32(seed + uint32_t(idx >> 32))) & 0xFFFFu;
   const uint32_t t = (u + r) & 0xFFFF0000u;
-  return __float2bfloat16_rn(__uint_as_float(t));
+  return float_to_t16(__uint_as_float(t));
+#endif
 }
 
 // Hyper-parameters pre-combined once per thread so the per-element update is 11 instructions.
@@ -79,9 +84,9 @@ __device__ __forceinline__ void adam_update8(float (&w)[8], float (&m)[8], float
 template <bool SR>
 __device__ __forceinline__ uint4 pack8_bf16(const float (&o)[8], unsigned int seed, unsigned int idx) {
   uint4 q;
-  if (!SR) {
-    q.x = pack_bf16x2(o[0], o[1]); q.y = pack_bf16x2(o[2], o[3]);
-    q.z = pack_bf16x2(o[4], o[5]); q.w = pack_bf16x2(o[6], o[7]);
+  if (!SR || CLT_T16_IS_HALF) {
+    q.x = pack_t16x2(o[0], o[1]); q.y = pack_t16x2(o[2], o[3]);
+    q.z = pack_t16x2(o[4], o[5]); q.w = pack_t16x2(o[6], o[7]);
   } else {
     uint32_t h[8];
 #pragma unroll
@@ -98,7 +103,7 @@ __device__ __forceinline__ uint4 pack8_bf16(const float (&o)[8], unsigned int se
 __device__ __forceinline__ void unpack8(const uint4& q, float (&o)[8]) {
   const uint32_t u[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-  for (int j = 0; j < 4; ++j) { o[2 * j] = bf16_lo(u[j]); o[2 * j + 1] = bf16_hi(u[j]); }
+  for (int j = 0; j < 4; ++j) { o[2 * j] = t16_lo(u[j]); o[2 * j + 1] = t16_hi(u[j]); }
 }
 __device__ __forceinline__ void load8f(const float* p, float (&o)[8]) {
   const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
@@ -112,7 +117,7 @@ __device__ __forceinline__ void store8f(float* p, const float (&o)[8]) {
 template <typename WT>
 __device__ __forceinline__ void load_w8(const WT* p, float (&o)[8]);
 template <>
-__device__ __forceinline__ void load_w8<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
+__device__ __forceinline__ void load_w8<t16>(const t16* p, float (&o)[8]) {
   unpack8(*reinterpret_cast<const uint4*>(p), o);
 }
 template <>
@@ -121,8 +126,8 @@ __device__ __forceinline__ void load_w8<float>(const float* p, float (&o)[8]) { 
 template <typename WT>
 __device__ __forceinline__ void store_w8(WT* p, const float (&o)[8], unsigned int seed, unsigned long long idx);
 template <>
-__device__ __forceinline__ void store_w8<__nv_bfloat16>(__nv_bfloat16* p, const float (&o)[8], unsigned int seed, unsigned long long idx) {
-  __nv_bfloat16 b[8];
+__device__ __forceinline__ void store_w8<t16>(t16* p, const float (&o)[8], unsigned int seed, unsigned long long idx) {
+  t16 b[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) b[i] = to_bf16(o[i], seed, idx + i);
   *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(b);
@@ -142,7 +147,7 @@ struct DecAdamParams {
   const int* feat_off;         // [L * F_pitch + 1] feature-major CSR
   const int* fcsr_tok;
   const float* fcsr_val;
-  const __nv_bfloat16* gs;     // [L, B, d] gradient seed
+  const t16* gs;     // [L, B, d] gradient seed
   float* grad_a;               // [nnz] dL/da per CSR slot (atomicAdd; zeroed by the caller); may be null
   const float* pen_coef;       // optional [L * F_pitch]: coefficient of w in the row gradient (sparsity penalty via norms)
   float* norm2_out;            // optional [L * F_pitch]: sum of squares of the updated rows (atomicAdd; zeroed by caller)
@@ -150,9 +155,36 @@ struct DecAdamParams {
   const float* feat_scale;
   int moments_bf16;            // bulk pipeline only: m / v hold bf16 (stochastically rounded) instead of fp32
   const float* dgrad_row0;     // optional [ntensors, F_pitch, d] fp32: extra gradient of every feature's first row
-                               // (the same-layer decoder row that the auxiliary loss trains)
+  // optional compact extras (auxiliary loss on dead features): extra_idx[col] = row of extra_rows, or -1
+  const int* extra_idx;
+  const float* extra_rows;     // [n_extra, d] fp32, added to the feature's first row
+  const float* ctl;            // optional step control block (skip flag, 1 / loss scale, clip coefficient)
+  int use_inv_scale;           // the "gradient seed" operand carries the loss scale (decoder: yes; encoder inputs: no)
+  float* norm_sq_out;          // norm-only pass: squared norm of all row gradients is added here
   AdamHyper h;
 };
+
+// Extra gradient of a feature's first row (dense buffer or compact rows through an index), or null.
+__device__ __forceinline__ const float* extra_row_ptr(const DecAdamParams& p, int col) {
+  if (p.dgrad_row0 != nullptr) return p.dgrad_row0 + 1LL * col * p.d;
+  if (p.extra_idx != nullptr) {
+    const int i = __ldg(p.extra_idx + col);
+    if (i >= 0) return p.extra_rows + 1LL * i * p.d;
+  }
+  return nullptr;
+}
+// Block-wide sum of `v` added to *out (one atomic per CTA); every thread of the CTA calls it.
+__device__ __forceinline__ void block_add(float v, float* out) {
+  __shared__ float red_s[32];
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red_s[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < int((blockDim.x + 31) >> 5); ++w) tot += red_s[w];
+    if (tot != 0.f && out != nullptr) atomicAdd(out, tot);
+  }
+}
 
 __device__ __forceinline__ void f4x2_to8(const float4& a, const float4& b, float (&o)[8]) {
   o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
@@ -164,9 +196,9 @@ __device__ __forceinline__ void stream_store8f(float* p, const float (&o)[8]) {
 template <typename WT>
 struct WVec;
 template <>
-struct WVec<__nv_bfloat16> {
+struct WVec<t16> {
   uint4 q;
-  __device__ __forceinline__ void load(const __nv_bfloat16* p) { q = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void load(const t16* p) { q = __ldcs(reinterpret_cast<const uint4*>(p)); }
   __device__ __forceinline__ void get(float (&o)[8]) const { unpack8(q, o); }
 };
 template <>
@@ -194,17 +226,24 @@ struct RowRegs {
 // elements per lane, walking the feature's R = L - s target rows with the next row's (w, m, v) already in
 // flight.  The first four entries of the feature stay in registers: their activation, token and the
 // partial dot products for dL/da, which are reduced once per item instead of once per row.
-template <typename WT, bool SR>
+// NORM_ONLY: the gradient-norm pre-pass of gradient clipping.  Nothing is updated: features without entries (and
+// without an extra row) are skipped, the row gradients of the others are formed as in the update, their squares
+// are summed into p.norm_sq_out and dL/da is written to p.grad_a.
+template <typename WT, bool SR, bool NORM_ONLY>
 __global__ void __launch_bounds__(256, 2) decoder_rows_adam_untied_kernel(const DecAdamParams p) {
   const int lane = threadIdx.x & 31;
   const int warp_global = int((blockIdx.x * 1LL * blockDim.x + threadIdx.x) >> 5);
   const int nwarps = int((gridDim.x * 1LL * blockDim.x) >> 5);
   const HyperRegs hr = make_regs(p.h);
+  const StepScales sc = read_step_ctl(p.ctl);
+  if (sc.skip) return;
+  const float gsc = hr.gscale * (p.use_inv_scale ? sc.inv_scale : 1.f);
+  float nsq = 0.f;
   const int d = p.d, B = p.B, Fp = p.F_pitch;
   const int nseg = (d + 255) / 256;
   const int per_tensor = Fp * nseg;
   const int total_items = per_tensor * p.ntensors;
-  const __nv_bfloat16* __restrict__ gs = p.gs;
+  const t16* __restrict__ gs = p.gs;
   for (int item = warp_global; item < total_items; item += nwarps) {
     const int ti = item / per_tensor;
     const int rem = item - ti * per_tensor;
@@ -217,11 +256,13 @@ __global__ void __launch_bounds__(256, 2) decoder_rows_adam_untied_kernel(const 
     WT* wbase = static_cast<WT*>(p.w[ti]) + row0 * d + e0;
     float* mbase = p.m[ti] + row0 * d + e0;
     float* vbase = p.v[ti] + row0 * d + e0;
-    RowRegs<WT> cur, nxt;
-    if (act) cur.load(wbase, mbase, vbase);
     const int col = ti * Fp + f;
     const int b = __ldg(p.feat_off + col), e = __ldg(p.feat_off + col + 1);
     const int ne = e - b;
+    const float* xrow = extra_row_ptr(p, col);
+    if (NORM_ONLY && ne == 0 && xrow == nullptr) continue;
+    RowRegs<WT> cur, nxt;
+    if (act) { if (NORM_ONLY) cur.w.load(wbase); else cur.load(wbase, mbase, vbase); }
     int tok4[4];
     float a4[4], dacc[4];
 #pragma unroll
@@ -235,13 +276,13 @@ __global__ void __launch_bounds__(256, 2) decoder_rows_adam_untied_kernel(const 
     const unsigned int idx_base = (unsigned int)((p.row_start[ti] + row0) * d + e0);
     for (int r = 0; r < R; ++r) {
       const long long roff = 1LL * r * d;
-      if (act && r + 1 < R) nxt.load(wbase + roff + d, mbase + roff + d, vbase + roff + d);
+      if (act && r + 1 < R) { if (NORM_ONLY) nxt.w.load(wbase + roff + d); else nxt.load(wbase + roff + d, mbase + roff + d, vbase + roff + d); }
       float w[8], g[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) { g[i] = 0.f; w[i] = 0.f; }
       if (act) {
         cur.w.get(w);
-        const __nv_bfloat16* gs_t = gs + 1LL * (ti + r) * B * d + e0;
+        const t16* gs_t = gs + 1LL * (ti + r) * B * d + e0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (j < ne) {
@@ -269,25 +310,36 @@ __global__ void __launch_bounds__(256, 2) decoder_rows_adam_untied_kernel(const 
         }
         if (p.grad_a != nullptr) {
           dot = warp_sum(dot);
-          if (lane == 0 && dot != 0.f) atomicAdd(&p.grad_a[i], dot * hr.gscale);
+          if (lane == 0 && dot != 0.f) atomicAdd(&p.grad_a[i], dot * gsc);
         }
       }
       if (act) {
-        float m[8], v[8], dg0[8];
-        f4x2_to8(cur.m0, cur.m1, m);
-        f4x2_to8(cur.v0, cur.v1, v);
-        if (r == 0 && p.dgrad_row0) load8f(p.dgrad_row0 + (1LL * col) * d + e0, dg0);
+        float dg0[8];
+        const bool extra = r == 0 && xrow != nullptr;
+        if (extra) load8f(xrow + e0, dg0);
+        if (NORM_ONLY) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          float gk = fmaf(pc, w[k], g[k] * hr.gscale);
-          if (r == 0 && p.dgrad_row0) gk += dg0[k];
-          adam1(w[k], m[k], v[k], gk, hr);
-          norm2 = fmaf(w[k], w[k], norm2);
+          for (int k = 0; k < 8; ++k) {
+            float gk = fmaf(pc, w[k], g[k] * gsc);
+            if (extra) gk += dg0[k];
+            nsq = fmaf(gk, gk, nsq);
+          }
+        } else {
+          float m[8], v[8];
+          f4x2_to8(cur.m0, cur.m1, m);
+          f4x2_to8(cur.v0, cur.v1, v);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            float gk = fmaf(pc, w[k], g[k] * gsc);
+            if (extra) gk += dg0[k];
+            adam1(w[k], m[k], v[k], gk * sc.clip, hr);
+            norm2 = fmaf(w[k], w[k], norm2);
+          }
+          stream_store8f(mbase + roff, m);
+          stream_store8f(vbase + roff, v);
+          if (sizeof(WT) == 2) __stcs(reinterpret_cast<uint4*>(wbase + roff), pack8_bf16<SR>(w, p.h.sr_seed, idx_base + (unsigned int)roff));
+          else stream_store8f(reinterpret_cast<float*>(wbase + roff), w);
         }
-        stream_store8f(mbase + roff, m);
-        stream_store8f(vbase + roff, v);
-        if (sizeof(WT) == 2) __stcs(reinterpret_cast<uint4*>(wbase + roff), pack8_bf16<SR>(w, p.h.sr_seed, idx_base + (unsigned int)roff));
-        else stream_store8f(reinterpret_cast<float*>(wbase + roff), w);
       }
       cur = nxt;
     }
@@ -296,15 +348,16 @@ __global__ void __launch_bounds__(256, 2) decoder_rows_adam_untied_kernel(const 
       for (int j = 0; j < 4; ++j) {
         if (j < ne) {
           const float sdot = warp_sum(dacc[j]);
-          if (lane == 0 && sdot != 0.f) atomicAdd(&p.grad_a[b + j], sdot * hr.gscale);
+          if (lane == 0 && sdot != 0.f) atomicAdd(&p.grad_a[b + j], sdot * gsc);
         }
       }
     }
-    if (p.norm2_out != nullptr) {
+    if (!NORM_ONLY && p.norm2_out != nullptr) {
       norm2 = warp_sum(norm2);
       if (lane == 0) atomicAdd(&p.norm2_out[col], norm2);
     }
   }
+  if (NORM_ONLY) block_add(nsq, p.norm_sq_out);
 }
 
 // ---------------------------------------------------------------- untied decoders, bulk-copy pipeline
@@ -358,28 +411,28 @@ __device__ __forceinline__ void stf(float* p, const float (&o)[EPT]) {
   for (int i = 0; i < EPT; i += 4) *reinterpret_cast<float4*>(p + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
 }
 template <int EPT>
-__device__ __forceinline__ void ldbf(const __nv_bfloat16* p, float (&o)[EPT]) {
+__device__ __forceinline__ void ldbf(const t16* p, float (&o)[EPT]) {
 #pragma unroll
   for (int i = 0; i < EPT; i += 4) {
     const uint2 q = *reinterpret_cast<const uint2*>(p + i);
-    o[i] = bf16_lo(q.x); o[i + 1] = bf16_hi(q.x); o[i + 2] = bf16_lo(q.y); o[i + 3] = bf16_hi(q.y);
+    o[i] = t16_lo(q.x); o[i + 1] = t16_hi(q.x); o[i + 2] = t16_lo(q.y); o[i + 3] = t16_hi(q.y);
   }
 }
 template <int EPT>
-__device__ __forceinline__ void ldbf_global(const __nv_bfloat16* p, float (&o)[EPT]) {
+__device__ __forceinline__ void ldbf_global(const t16* p, float (&o)[EPT]) {
 #pragma unroll
   for (int i = 0; i < EPT; i += 4) {
     const uint2 q = __ldg(reinterpret_cast<const uint2*>(p + i));
-    o[i] = bf16_lo(q.x); o[i + 1] = bf16_hi(q.x); o[i + 2] = bf16_lo(q.y); o[i + 3] = bf16_hi(q.y);
+    o[i] = t16_lo(q.x); o[i + 1] = t16_hi(q.x); o[i + 2] = t16_lo(q.y); o[i + 3] = t16_hi(q.y);
   }
 }
 template <int EPT, bool SR>
-__device__ __forceinline__ void stbf(__nv_bfloat16* p, const float (&o)[EPT], unsigned int seed, unsigned int idx) {
+__device__ __forceinline__ void stbf(t16* p, const float (&o)[EPT], unsigned int seed, unsigned int idx) {
 #pragma unroll
   for (int i = 0; i < EPT; i += 4) {
     uint2 q;
-    if (!SR) {
-      q.x = pack_bf16x2(o[i], o[i + 1]); q.y = pack_bf16x2(o[i + 2], o[i + 3]);
+    if (!SR || CLT_T16_IS_HALF) {
+      q.x = pack_t16x2(o[i], o[i + 1]); q.y = pack_t16x2(o[i + 2], o[i + 3]);
     } else {
       uint32_t h[4];
 #pragma unroll
@@ -402,6 +455,8 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
   const int d = p.d, B = p.B, Fp = p.F_pitch;
   const int nconsumer = gthreads;
   const int tid = threadIdx.x;
+  const StepScales sc = read_step_ctl(p.ctl);
+  if (sc.skip) return;  // the whole grid sees the same flag: a skipped step touches nothing
   const int nf = (Fp - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);  // features of this CTA per tensor
   long long n_rows = 0;
   for (int ti = 0; ti < p.ntensors; ++ti) n_rows += 1LL * (nf > 0 ? nf : 0) * p.rows[ti];
@@ -464,7 +519,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       bulk_load_1d_hint(stage + off_w, static_cast<const WT*>(p.w[ti]) + elem_off, w_bytes, &sh->full[st], pol_stream);
       bulk_load_1d_hint(stage + off_m, reinterpret_cast<const MT*>(p.m[ti]) + elem_off, mv_bytes, &sh->full[st], pol_stream);
       bulk_load_1d_hint(stage + off_v, reinterpret_cast<const MT*>(p.v[ti]) + elem_off, mv_bytes, &sh->full[st], pol_stream);
-      const __nv_bfloat16* gs_t = p.gs + 1LL * (ti + r) * B * d;
+      const t16* gs_t = p.gs + 1LL * (ti + r) * B * d;
 #pragma unroll
       for (int j = 0; j < kAdamSlots; ++j)
         if (j < nslot) bulk_load_1d_hint(stage + off_gs + j * gs_bytes, gs_t + 1LL * cur.tok[j] * d, gs_bytes, &sh->full[st], pol_keep);
@@ -515,6 +570,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
     const int e0 = tid * EPT;
     const bool act = e0 < d;
     const HyperRegs hr = make_regs(p.h);
+    const float gsc = hr.gscale * (p.use_inv_scale ? sc.inv_scale : 1.f);
     float dacc[kAdamSlots] = {0.f, 0.f, 0.f, 0.f};
     float norm2 = 0.f, pc = 0.f;
     for (int i = 0; i < n; ++i) {
@@ -536,16 +592,16 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
       MT* m_s = reinterpret_cast<MT*>(stage + off_m) + e0;
       MT* v_s = reinterpret_cast<MT*>(stage + off_v) + e0;
       if (act) {
-        if (sizeof(WT) == 2) ldbf<EPT>(reinterpret_cast<const __nv_bfloat16*>(w_s), w);
+        if (sizeof(WT) == 2) ldbf<EPT>(reinterpret_cast<const t16*>(w_s), w);
         else ldf<EPT>(reinterpret_cast<const float*>(w_s), w);
         if (sizeof(MT) == 2) {
-          ldbf<EPT>(reinterpret_cast<const __nv_bfloat16*>(m_s), m);
-          ldbf<EPT>(reinterpret_cast<const __nv_bfloat16*>(v_s), v);
+          ldbf<EPT>(reinterpret_cast<const t16*>(m_s), m);
+          ldbf<EPT>(reinterpret_cast<const t16*>(v_s), v);
         } else {
           ldf<EPT>(reinterpret_cast<const float*>(m_s), m);
           ldf<EPT>(reinterpret_cast<const float*>(v_s), v);
         }
-        const __nv_bfloat16* gs_s = reinterpret_cast<const __nv_bfloat16*>(stage + off_gs) + e0;
+        const t16* gs_s = reinterpret_cast<const t16*>(stage + off_gs) + e0;
 #pragma unroll
         for (int j = 0; j < kAdamSlots; ++j) {
           if (j < ne) {
@@ -574,35 +630,36 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
         }
         if (p.grad_a != nullptr) {
           dot = warp_sum(dot);
-          if (lane == 0 && dot != 0.f) atomicAdd(&p.grad_a[x], dot * hr.gscale);
+          if (lane == 0 && dot != 0.f) atomicAdd(&p.grad_a[x], dot * gsc);
         }
       }
       if (act) {
         float dg0[EPT];
-        const bool extra = r == 0 && p.dgrad_row0 != nullptr;
+        const float* xrow = r == 0 ? extra_row_ptr(p, col) : nullptr;
+        const bool extra = xrow != nullptr;
         if (extra) {
 #pragma unroll
           for (int q = 0; q < EPT; q += 4) {
-            const float4 t4 = __ldg(reinterpret_cast<const float4*>(p.dgrad_row0 + (1LL * col) * d + e0 + q));
+            const float4 t4 = __ldg(reinterpret_cast<const float4*>(xrow + e0 + q));
             dg0[q] = t4.x; dg0[q + 1] = t4.y; dg0[q + 2] = t4.z; dg0[q + 3] = t4.w;
           }
         }
 #pragma unroll
         for (int q = 0; q < EPT; ++q) {
-          float gq = fmaf(pc, w[q], g[q] * hr.gscale);
+          float gq = fmaf(pc, w[q], g[q] * gsc);
           if (extra) gq += dg0[q];
-          adam1(w[q], m[q], v[q], gq, hr);
+          adam1(w[q], m[q], v[q], gq * sc.clip, hr);
           norm2 = fmaf(w[q], w[q], norm2);
         }
         const unsigned long long gidx = (unsigned long long)(p.row_start[ti] * d + h->elem_off + e0);
-        if (sizeof(WT) == 2) stbf<EPT, SR>(reinterpret_cast<__nv_bfloat16*>(w_s), w, p.h.sr_seed, (unsigned int)gidx);
+        if (sizeof(WT) == 2) stbf<EPT, SR>(reinterpret_cast<t16*>(w_s), w, p.h.sr_seed, (unsigned int)gidx);
         else stf<EPT>(reinterpret_cast<float*>(w_s), w);
         if (sizeof(MT) == 2) {
           // bf16 moments are always rounded stochastically: with beta2 = 0.999 a nearest rounding would freeze v
           // one hash per thread and row seeds a linear congruential stream: two 16-bit dither values per element
           uint32_t rng = hash32((unsigned int)gidx ^ p.h.moment_seed);
-          __nv_bfloat16* mo = reinterpret_cast<__nv_bfloat16*>(m_s);
-          __nv_bfloat16* vo = reinterpret_cast<__nv_bfloat16*>(v_s);
+          t16* mo = reinterpret_cast<t16*>(m_s);
+          t16* vo = reinterpret_cast<t16*>(v_s);
 #pragma unroll
           for (int q = 0; q < EPT; q += 2) {
             uint32_t hm[2], hv[2];
@@ -628,7 +685,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
           for (int j = 0; j < kAdamSlots; ++j) {
             if (j < nslot) {
               const float sdot = warp_sum(dacc[j]);
-              if (lane == 0 && sdot != 0.f) atomicAdd(&p.grad_a[b + j], sdot * hr.gscale);
+              if (lane == 0 && sdot != 0.f) atomicAdd(&p.grad_a[b + j], sdot * gsc);
             }
           }
         }
@@ -651,11 +708,15 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
 // the feature's R rows with the next row's (w, m, v) already in flight while the current row is updated.
 // Row r of tensor i (source layer i, or target layer i with per_target tying); its gradient is
 //   grad_scale * sum over contributing (entry, target) pairs of  a' * gs[target][tok, :]  (+ pen_coef * w).
-template <typename WT>
+template <typename WT, bool NORM_ONLY>
 __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamParams p) {
   const int lane = threadIdx.x & 31;
   const long long warp_global = (blockIdx.x * 1LL * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (gridDim.x * 1LL * blockDim.x) >> 5;
+  const StepScales sc = read_step_ctl(p.ctl);
+  if (sc.skip) return;
+  const float gsc = p.h.grad_scale * (p.use_inv_scale ? sc.inv_scale : 1.f);
+  float nsq = 0.f;
   const int nseg = (p.d + 255) / 256;
   const long long per_tensor = 1LL * p.F_pitch * nseg;
   const long long total_items = per_tensor * p.ntensors;
@@ -681,11 +742,20 @@ __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamPar
       if (p.tying == 2) { for (int s = 0; s <= ti; ++s) pc += p.pen_coef[s * p.F_pitch + f]; }
       else pc = p.pen_coef[ti * p.F_pitch + f];
     }
+    const float* xrow = extra_row_ptr(p, ti * p.F_pitch + f);
+    if (NORM_ONLY && xrow == nullptr) {
+      bool any = false;
+      for (int s = s_lo; s <= s_hi; ++s) any |= __ldg(p.feat_off + s * p.F_pitch + f + 1) > __ldg(p.feat_off + s * p.F_pitch + f);
+      if (!any) continue;
+    }
     RowRegs<WT> cur, nxt;
-    if (act) cur.load(wbase, mbase, vbase);
+    if (act) { if (NORM_ONLY) cur.w.load(wbase); else cur.load(wbase, mbase, vbase); }
     float norm2 = 0.f;
     for (int r = 0; r < R; ++r) {
-      if (act && r + 1 < R) nxt.load(wbase + 1LL * (r + 1) * p.d, mbase + 1LL * (r + 1) * p.d, vbase + 1LL * (r + 1) * p.d);
+      if (act && r + 1 < R) {
+        if (NORM_ONLY) nxt.w.load(wbase + 1LL * (r + 1) * p.d);
+        else nxt.load(wbase + 1LL * (r + 1) * p.d, mbase + 1LL * (r + 1) * p.d, vbase + 1LL * (r + 1) * p.d);
+      }
       const int t_fixed = p.tying == 0 ? ti + r : (p.tying == 2 ? ti : -1);
       float w[8], g[8];
 #pragma unroll
@@ -704,7 +774,7 @@ __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamPar
             float av = a, dscale = 1.f;
             if (p.tying != 0 && a != 0.f) {
               if (p.feat_offset) av += p.feat_offset[1LL * t * p.F_pitch + f];
-              if (p.feat_scale) { const float sc = p.feat_scale[1LL * t * p.F_pitch + f]; av *= sc; dscale = sc; }
+              if (p.feat_scale) { const float fsc = p.feat_scale[1LL * t * p.F_pitch + f]; av *= fsc; dscale = fsc; }
             }
             if (act) {
               float gv[8];
@@ -718,19 +788,27 @@ __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamPar
           }
           if (p.grad_a != nullptr) {
             dot = warp_sum(dot);
-            if (lane == 0 && dot != 0.f) atomicAdd(&p.grad_a[i], dot * p.h.grad_scale);
+            if (lane == 0 && dot != 0.f) atomicAdd(&p.grad_a[i], dot * gsc);
           }
         }
       }
       if (act) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) g[k] = fmaf(pc, w[k], g[k] * p.h.grad_scale);
-        if (r == 0 && p.dgrad_row0) {
+        for (int k = 0; k < 8; ++k) g[k] = fmaf(pc, w[k], g[k] * gsc);
+        if (r == 0 && xrow != nullptr) {
           float dg0[8];
-          load8f(p.dgrad_row0 + (1LL * ti * p.F_pitch + f) * p.d + e0, dg0);
+          load8f(xrow + e0, dg0);
 #pragma unroll
           for (int k = 0; k < 8; ++k) g[k] += dg0[k];
         }
+        if (NORM_ONLY) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) nsq = fmaf(g[k], g[k], nsq);
+          cur = nxt;
+          continue;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] *= sc.clip;
         float m[8], v[8];
         f4x2_to8(cur.m0, cur.m1, m);
         f4x2_to8(cur.v0, cur.v1, v);
@@ -739,11 +817,11 @@ __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamPar
         stream_store8f(mbase + 1LL * r * p.d, m);
         stream_store8f(vbase + 1LL * r * p.d, v);
         if (sizeof(WT) == 2) {
-          __nv_bfloat16 bq[8];
+          t16 bq[8];
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             bq[k] = to_bf16(w[k], p.h.sr_seed, (unsigned long long)((p.row_start[ti] + row0 + r) * p.d + e0 + k));
-            const float wr = __bfloat162float(bq[k]);  // norms are taken of the stored (rounded) weights
+            const float wr = t16_to_float(bq[k]);  // norms are taken of the stored (rounded) weights
             norm2 = fmaf(wr, wr, norm2);
           }
           __stcs(reinterpret_cast<uint4*>(wrow), *reinterpret_cast<const uint4*>(bq));
@@ -755,11 +833,12 @@ __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamPar
       }
       cur = nxt;
     }
-    if (p.norm2_out != nullptr) {
+    if (!NORM_ONLY && p.norm2_out != nullptr) {
       norm2 = warp_sum(norm2);
       if (lane == 0) atomicAdd(&p.norm2_out[ti * p.F_pitch + f], norm2);
     }
   }
+  if (NORM_ONLY) block_add(nsq, p.norm_sq_out);
 }
 
 // ------------------------------------------------------------------ encoder rows
@@ -774,17 +853,29 @@ struct EncAdamParams {
   const int* feat_off;
   const int* fcsr_tok;
   const float* delta;           // [nnz] dL/d(pre-activation) per CSR slot (already scaled)
-  const __nv_bfloat16* x;       // [L, B, d] layer inputs
+  const t16* x;       // [L, B, d] layer inputs
   const float* dense_grad;      // optional [L, F_pitch, d] fp32 gradient added to the sparse one (e.g. pre-activation loss)
   const float* dense_bias_grad; // optional [L, F_pitch]
+  const int* extra_idx;         // optional compact extras (auxiliary loss): extra_idx[row] = row of extra_rows / extra_bias, or -1
+  const float* extra_rows;      // [n_extra, d]
+  const float* extra_bias;      // [n_extra]
+  const float* ctl;             // optional step control block
+  float* norm_sq_out;           // norm-only pass
+  int norm_only;                // bias kernel: 1 = only add the squared bias gradients to norm_sq_out
   AdamHyper h;                  // grad_scale applies to the sparse part
 };
+__device__ __forceinline__ int enc_extra_index(const EncAdamParams& p, long long row) {
+  return p.extra_idx != nullptr ? __ldg(p.extra_idx + row) : -1;
+}
 
-template <typename WT>
+template <typename WT, bool NORM_ONLY>
 __global__ void __launch_bounds__(256) encoder_rows_adam_kernel(const EncAdamParams p) {
   const int lane = threadIdx.x & 31;
   const long long warp_global = (blockIdx.x * 1LL * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (gridDim.x * 1LL * blockDim.x) >> 5;
+  const StepScales sc = read_step_ctl(p.ctl);
+  if (sc.skip) return;
+  float nsq = 0.f;
   const int nseg = (p.d + 255) / 256;
   const long long total_items = 1LL * p.L * p.F_pitch * nseg;
   for (long long item = warp_global; item < total_items; item += nwarps) {
@@ -793,17 +884,19 @@ __global__ void __launch_bounds__(256) encoder_rows_adam_kernel(const EncAdamPar
     const int l = int(row / p.F_pitch);
     const int e0 = seg * 256 + lane * 8;
     const bool act = e0 < p.d;
+    const int b = __ldg(p.feat_off + row), e = __ldg(p.feat_off + row + 1);
+    const int xi = enc_extra_index(p, row);
+    if (NORM_ONLY && e == b && xi < 0 && p.dense_grad == nullptr) continue;
     WT* wrow = static_cast<WT*>(p.w) + row * p.d + e0;
     float* mrow = p.m + row * p.d + e0;
     float* vrow = p.v + row * p.d + e0;
     WVec<WT> wq;
     float4 m0, m1, v0, v1;
-    if (act) {
+    if (act && !NORM_ONLY) {
       wq.load(wrow);
       m0 = __ldcs(reinterpret_cast<const float4*>(mrow)); m1 = __ldcs(reinterpret_cast<const float4*>(mrow) + 1);
       v0 = __ldcs(reinterpret_cast<const float4*>(vrow)); v1 = __ldcs(reinterpret_cast<const float4*>(vrow) + 1);
     }
-    const int b = __ldg(p.feat_off + row), e = __ldg(p.feat_off + row + 1);
     if (act) {
       float w[8], g[8];
 #pragma unroll
@@ -823,22 +916,38 @@ __global__ void __launch_bounds__(256) encoder_rows_adam_kernel(const EncAdamPar
 #pragma unroll
         for (int k = 0; k < 8; ++k) g[k] += dg[k];
       }
-      float m[8], v[8];
-      wq.get(w);
-      f4x2_to8(m0, m1, m);
-      f4x2_to8(v0, v1, v);
-      adam_update8(w, m, v, g, p.h);
-      stream_store8f(mrow, m);
-      stream_store8f(vrow, v);
-      store_w8<WT>(wrow, w, p.h.sr_seed, (unsigned long long)(row * p.d + e0));
+      if (xi >= 0) {
+        float dg[8];
+        load8f(p.extra_rows + 1LL * xi * p.d + e0, dg);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] += dg[k];
+      }
+      if (NORM_ONLY) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) nsq = fmaf(g[k], g[k], nsq);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] *= sc.clip;
+        float m[8], v[8];
+        wq.get(w);
+        f4x2_to8(m0, m1, m);
+        f4x2_to8(v0, v1, v);
+        adam_update8(w, m, v, g, p.h);
+        stream_store8f(mrow, m);
+        stream_store8f(vrow, v);
+        store_w8<WT>(wrow, w, p.h.sr_seed, (unsigned long long)(row * p.d + e0));
+      }
     }
     if (seg == 0 && lane == 0 && p.bias != nullptr) {
       float gb = 0.f;
       for (int i = b; i < e; ++i) gb += p.delta[i];
       gb *= p.h.grad_scale;
       if (p.dense_bias_grad) gb += p.dense_bias_grad[row];
+      if (xi >= 0 && p.extra_bias != nullptr) gb += p.extra_bias[xi];
+      if (NORM_ONLY) { nsq = fmaf(gb, gb, nsq); continue; }
+      gb *= sc.clip;
       WT* bp = static_cast<WT*>(p.bias) + row;
-      float wv = sizeof(WT) == 2 ? __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(bp)) : *reinterpret_cast<float*>(bp);
+      float wv = sizeof(WT) == 2 ? t16_to_float(*reinterpret_cast<t16*>(bp)) : *reinterpret_cast<float*>(bp);
       float mm = p.bias_m[row], vv = p.bias_v[row];
       if (p.h.decoupled) wv *= (1.f - p.h.lr * p.h.weight_decay);
       else gb = fmaf(p.h.weight_decay, wv, gb);
@@ -846,24 +955,32 @@ __global__ void __launch_bounds__(256) encoder_rows_adam_kernel(const EncAdamPar
       vv = fmaf(p.h.beta2, vv, (1.f - p.h.beta2) * gb * gb);
       wv -= (p.h.lr / p.h.bc1) * (mm / (sqrtf(vv) * rsqrtf(p.h.bc2) + p.h.eps));
       p.bias_m[row] = mm; p.bias_v[row] = vv;
-      if (sizeof(WT) == 2) *reinterpret_cast<__nv_bfloat16*>(bp) = to_bf16(wv, p.h.sr_seed, 0x9000000000ULL + row);
+      if (sizeof(WT) == 2) *reinterpret_cast<t16*>(bp) = to_bf16(wv, p.h.sr_seed, 0x9000000000ULL + row);
       else *reinterpret_cast<float*>(bp) = wv;
     }
   }
+  if (NORM_ONLY) block_add(nsq, p.norm_sq_out);
 }
 
 // Encoder bias update on its own (used with the bulk-copy row pipeline, which handles the weight rows).
 template <typename WT>
 __global__ void __launch_bounds__(256) encoder_bias_adam_kernel(const EncAdamParams p) {
   const long long rows = 1LL * p.L * p.F_pitch;
+  const StepScales sc = read_step_ctl(p.ctl);
+  if (sc.skip) return;
+  float nsq = 0.f;
   for (long long row = blockIdx.x * 1LL * blockDim.x + threadIdx.x; row < rows; row += 1LL * gridDim.x * blockDim.x) {
     const int b = __ldg(p.feat_off + row), e = __ldg(p.feat_off + row + 1);
     float gb = 0.f;
     for (int i = b; i < e; ++i) gb += p.delta[i];
     gb *= p.h.grad_scale;
     if (p.dense_bias_grad) gb += p.dense_bias_grad[row];
+    const int xi = enc_extra_index(p, row);
+    if (xi >= 0 && p.extra_bias != nullptr) gb += p.extra_bias[xi];
+    if (p.norm_only) { nsq = fmaf(gb, gb, nsq); continue; }
+    gb *= sc.clip;
     WT* bp = static_cast<WT*>(p.bias) + row;
-    float wv = sizeof(WT) == 2 ? __bfloat162float(*reinterpret_cast<__nv_bfloat16*>(bp)) : *reinterpret_cast<float*>(bp);
+    float wv = sizeof(WT) == 2 ? t16_to_float(*reinterpret_cast<t16*>(bp)) : *reinterpret_cast<float*>(bp);
     float mm = p.bias_m[row], vv = p.bias_v[row];
     if (p.h.decoupled) wv *= (1.f - p.h.lr * p.h.weight_decay);
     else gb = fmaf(p.h.weight_decay, wv, gb);
@@ -871,25 +988,41 @@ __global__ void __launch_bounds__(256) encoder_bias_adam_kernel(const EncAdamPar
     vv = fmaf(p.h.beta2, vv, (1.f - p.h.beta2) * gb * gb);
     wv -= (p.h.lr / p.h.bc1) * (mm / (sqrtf(vv) * rsqrtf(p.h.bc2) + p.h.eps));
     p.bias_m[row] = mm; p.bias_v[row] = vv;
-    if (sizeof(WT) == 2) *reinterpret_cast<__nv_bfloat16*>(bp) = to_bf16(wv, p.h.sr_seed, 0x9000000000ULL + row);
+    if (sizeof(WT) == 2) *reinterpret_cast<t16*>(bp) = to_bf16(wv, p.h.sr_seed, 0x9000000000ULL + row);
     else *reinterpret_cast<float*>(bp) = wv;
   }
+  if (p.norm_only) block_add(nsq, p.norm_sq_out);
 }
 
 // ------------------------------------------------------------------ dense Adam for the small tensors
+// `ctl` (optional): skip flag and clip coefficient; `seed_scaled`: the gradient carries the loss scale (times 1 / scale);
+// `norm_weight` > 0: norm-only pass, norm_weight * sum g^2 is added to ctl[SC_GRAD_NORM_SQ] and nothing is updated.
 template <typename WT>
 __global__ void __launch_bounds__(256) dense_adam_kernel(WT* __restrict__ w, float* __restrict__ m, float* __restrict__ v,
-                                                           const float* __restrict__ grad, long long n, AdamHyper h) {
+                                                           const float* __restrict__ grad, long long n, AdamHyper h,
+                                                           float* __restrict__ ctl, int seed_scaled, float norm_weight) {
+  const StepScales sc = read_step_ctl(ctl);
+  if (sc.skip) return;
+  const float gmul = h.grad_scale * (seed_scaled ? sc.inv_scale : 1.f);
+  if (norm_weight > 0.f) {
+    float nsq = 0.f;
+    for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
+      const float g = grad[i] * gmul;
+      nsq = fmaf(g, g, nsq);
+    }
+    block_add(nsq * norm_weight, ctl != nullptr ? ctl + SC_GRAD_NORM_SQ : nullptr);
+    return;
+  }
   for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
-    float wv = sizeof(WT) == 2 ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(w + i)) : *reinterpret_cast<const float*>(w + i);
-    float g = grad[i] * h.grad_scale;
+    float wv = sizeof(WT) == 2 ? t16_to_float(*reinterpret_cast<const t16*>(w + i)) : *reinterpret_cast<const float*>(w + i);
+    float g = grad[i] * gmul * sc.clip;
     if (h.decoupled) wv *= (1.f - h.lr * h.weight_decay);
     else g = fmaf(h.weight_decay, wv, g);
     const float mm = fmaf(h.beta1, m[i], (1.f - h.beta1) * g);
     const float vv = fmaf(h.beta2, v[i], (1.f - h.beta2) * g * g);
     wv -= (h.lr / h.bc1) * (mm / (sqrtf(vv) * rsqrtf(h.bc2) + h.eps));
     m[i] = mm; v[i] = vv;
-    if (sizeof(WT) == 2) *reinterpret_cast<__nv_bfloat16*>(w + i) = to_bf16(wv, h.sr_seed, 0xA000000000ULL + i);
+    if (sizeof(WT) == 2) *reinterpret_cast<t16*>(w + i) = to_bf16(wv, h.sr_seed, 0xA000000000ULL + i);
     else *reinterpret_cast<float*>(w + i) = wv;
   }
 }
@@ -983,6 +1116,9 @@ struct CltDecAdamArgs {
   CltAdamHyper h;
   int* status;  // when given, untied decoders use the bulk-copy pipeline (its bounded waits report here)
   int moments_bf16;  // m / v are bf16 tensors (bulk pipeline with bf16 weights only)
+  const int* extra_idx; const float* extra_rows;  // compact extra gradient rows (auxiliary loss), see DecAdamParams
+  float* ctl;        // step control block (skip flag, 1 / loss scale, clip coefficient); may be null
+  int norm_only;     // 1: gradient-norm pre-pass (adds to ctl[SC_GRAD_NORM_SQ], writes grad_a, updates nothing)
 };
 
 // Launch geometry of the bulk-copy row pipeline (shared by the decoder and the encoder update).
@@ -1026,10 +1162,14 @@ static int launch_rows_adam_bulk(const DecAdamParams& p, bool weights_bf16, bool
     kern<<<bgrid, gthreads + 32, smem, st>>>(p, gthreads, stage_bytes, nstages, status);
     return 0;
   };
-  using bf = __nv_bfloat16;
+  using bf = t16;
   if (mb) {
+#if CLT_T16_IS_HALF
+    return -6;  // bf16 moments go with bf16 weights
+#else
     if (ept == 4) return sr ? launch(decoder_rows_adam_bulk_kernel<bf, true, 4, bf>, 6) : launch(decoder_rows_adam_bulk_kernel<bf, false, 4, bf>, 7);
     return sr ? launch(decoder_rows_adam_bulk_kernel<bf, true, 8, bf>, 8) : launch(decoder_rows_adam_bulk_kernel<bf, false, 8, bf>, 9);
+#endif
   }
   if (ept == 4) {
     if (weights_bf16) return sr ? launch(decoder_rows_adam_bulk_kernel<bf, true, 4, float>, 0) : launch(decoder_rows_adam_bulk_kernel<bf, false, 4, float>, 1);
@@ -1039,7 +1179,7 @@ static int launch_rows_adam_bulk(const DecAdamParams& p, bool weights_bf16, bool
   return launch(decoder_rows_adam_bulk_kernel<float, false, 8, float>, 5);
 }
 
-extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st) {
+extern "C" int CLT_FN(clt_decoder_rows_adam)(const CltDecAdamArgs* a, int num_sms, cudaStream_t st) {
   if (a->d % 8 != 0 || a->ntensors > kMaxLayersA) return -1;
   DecAdamParams p;
   long long acc = 0;
@@ -1052,27 +1192,41 @@ extern "C" int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaS
   for (int i = a->ntensors; i <= kMaxLayersA; ++i) p.row_start[i] = acc;
   p.ntensors = a->ntensors; p.L = a->L; p.B = a->B; p.d = a->d; p.F_pitch = a->F_pitch; p.tying = a->tying;
   p.feat_off = a->feat_off; p.fcsr_tok = a->fcsr_tok; p.fcsr_val = a->fcsr_val;
-  p.gs = static_cast<const __nv_bfloat16*>(a->gs); p.grad_a = a->grad_a; p.pen_coef = a->pen_coef; p.norm2_out = a->norm2_out;
+  p.gs = static_cast<const t16*>(a->gs); p.grad_a = a->grad_a; p.pen_coef = a->pen_coef; p.norm2_out = a->norm2_out;
   p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale; p.dgrad_row0 = a->dgrad_row0; p.h = to_hyper(a->h);
   p.moments_bf16 = a->moments_bf16;
+  p.extra_idx = a->extra_idx; p.extra_rows = a->extra_rows; p.ctl = a->ctl; p.use_inv_scale = 1;
+  p.norm_sq_out = a->ctl != nullptr ? a->ctl + SC_GRAD_NORM_SQ : nullptr;
   if (a->moments_bf16 && !(a->tying == 0 && a->status != nullptr && a->weights_bf16)) return -6;  // only the bulk pipeline handles bf16 moments
   if (acc == 0) return 0;
   const int grid = num_sms * 8;
+  if (a->norm_only) {
+    if (a->ctl == nullptr) return -1;
+    if (a->tying == 0) {
+      if (a->weights_bf16) decoder_rows_adam_untied_kernel<t16, false, true><<<grid, 256, 0, st>>>(p);
+      else decoder_rows_adam_untied_kernel<float, false, true><<<grid, 256, 0, st>>>(p);
+    } else if (a->weights_bf16) {
+      decoder_rows_adam_kernel<t16, true><<<grid, 256, 0, st>>>(p);
+    } else {
+      decoder_rows_adam_kernel<float, true><<<grid, 256, 0, st>>>(p);
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  }
   if (a->tying == 0 && a->status != nullptr && bulk_rows_adam_fits(a->d, a->weights_bf16) && acc * a->d < (1LL << 62)) {
     const int rc = launch_rows_adam_bulk(p, a->weights_bf16 != 0, a->h.sr_seed != 0, num_sms, a->status, st);
     if (rc != 0) return rc;
   } else if (a->tying == 0) {
     const bool sr = a->h.sr_seed != 0;
     if (a->weights_bf16) {
-      if (sr) decoder_rows_adam_untied_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(p);
-      else decoder_rows_adam_untied_kernel<__nv_bfloat16, false><<<grid, 256, 0, st>>>(p);
+      if (sr) decoder_rows_adam_untied_kernel<t16, true, false><<<grid, 256, 0, st>>>(p);
+      else decoder_rows_adam_untied_kernel<t16, false, false><<<grid, 256, 0, st>>>(p);
     } else {
-      decoder_rows_adam_untied_kernel<float, false><<<grid, 256, 0, st>>>(p);
+      decoder_rows_adam_untied_kernel<float, false, false><<<grid, 256, 0, st>>>(p);
     }
   } else if (a->weights_bf16) {
-    decoder_rows_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+    decoder_rows_adam_kernel<t16, false><<<grid, 256, 0, st>>>(p);
   } else {
-    decoder_rows_adam_kernel<float><<<grid, 256, 0, st>>>(p);
+    decoder_rows_adam_kernel<float, false><<<grid, 256, 0, st>>>(p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
@@ -1085,16 +1239,27 @@ struct CltEncAdamArgs {
   CltAdamHyper h;
   int* status;  // when given, the weight rows go through the bulk-copy pipeline
   int moments_bf16;
+  const int* extra_idx; const float* extra_rows; const float* extra_bias;  // compact extras, see EncAdamParams
+  float* ctl;
+  int norm_only;
 };
 
-extern "C" int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaStream_t st) {
+extern "C" int CLT_FN(clt_encoder_rows_adam)(const CltEncAdamArgs* a, int num_sms, cudaStream_t st) {
   if (a->d % 8 != 0) return -1;
   EncAdamParams p;
   p.w = a->w; p.m = a->m; p.v = a->v; p.bias = a->bias; p.bias_m = a->bias_m; p.bias_v = a->bias_v;
   p.L = a->L; p.B = a->B; p.d = a->d; p.F_pitch = a->F_pitch;
-  p.feat_off = a->feat_off; p.fcsr_tok = a->fcsr_tok; p.delta = a->delta; p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.feat_off = a->feat_off; p.fcsr_tok = a->fcsr_tok; p.delta = a->delta; p.x = static_cast<const t16*>(a->x);
   p.dense_grad = a->dense_grad; p.dense_bias_grad = a->dense_bias_grad; p.h = to_hyper(a->h);
+  p.extra_idx = a->extra_idx; p.extra_rows = a->extra_rows; p.extra_bias = a->extra_bias; p.ctl = a->ctl;
+  p.norm_sq_out = a->ctl != nullptr ? a->ctl + SC_GRAD_NORM_SQ : nullptr; p.norm_only = a->norm_only;
   const int grid = num_sms * 8;
+  if (a->norm_only) {
+    if (a->ctl == nullptr) return -1;
+    if (a->weights_bf16) encoder_rows_adam_kernel<t16, true><<<grid, 256, 0, st>>>(p);
+    else encoder_rows_adam_kernel<float, true><<<grid, 256, 0, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  }
   if (a->status != nullptr && a->L <= kMaxLayersA && bulk_rows_adam_fits(a->d, a->weights_bf16)) {
     // the encoder is the one-row-per-feature case of the row pipeline: layer l is "tensor" l with R = 1, the
     // layer inputs play the gradient seed and delta the activation
@@ -1116,38 +1281,42 @@ extern "C" int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaS
     q.grad_a = nullptr; q.pen_coef = nullptr; q.norm2_out = nullptr; q.feat_offset = nullptr; q.feat_scale = nullptr;
     q.dgrad_row0 = a->dense_grad; q.h = p.h;
     q.moments_bf16 = a->moments_bf16;
+    q.extra_idx = a->dense_grad == nullptr ? a->extra_idx : nullptr; q.extra_rows = a->extra_rows;
+    q.ctl = a->ctl; q.use_inv_scale = 0; q.norm_sq_out = nullptr;
+    if (a->dense_grad != nullptr && a->extra_idx != nullptr) return -7;  // the row pipeline takes one kind of extra rows
     const int rc = launch_rows_adam_bulk(q, a->weights_bf16 != 0, a->h.sr_seed != 0, num_sms, a->status, st);
     if (rc != 0) return rc;
     if (p.bias != nullptr) {
       const int bgrid = int((1LL * a->L * a->F_pitch + 255) / 256);
-      if (a->weights_bf16) encoder_bias_adam_kernel<__nv_bfloat16><<<bgrid, 256, 0, st>>>(p);
+      if (a->weights_bf16) encoder_bias_adam_kernel<t16><<<bgrid, 256, 0, st>>>(p);
       else encoder_bias_adam_kernel<float><<<bgrid, 256, 0, st>>>(p);
     }
   } else if (a->moments_bf16) {
     return -6;  // only the bulk pipeline handles bf16 moments
-  } else if (a->weights_bf16) encoder_rows_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
-  else encoder_rows_adam_kernel<float><<<grid, 256, 0, st>>>(p);
+  } else if (a->weights_bf16) encoder_rows_adam_kernel<t16, false><<<grid, 256, 0, st>>>(p);
+  else encoder_rows_adam_kernel<float, false><<<grid, 256, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-extern "C" int clt_dense_adam(void* w, float* m, float* v, const float* grad, long long n, int weights_bf16, const CltAdamHyper* h,
-                              cudaStream_t st) {
+extern "C" int CLT_FN(clt_dense_adam)(void* w, float* m, float* v, const float* grad, long long n, int weights_bf16, const CltAdamHyper* h,
+                                      float* ctl, int seed_scaled, float norm_weight, cudaStream_t st) {
   if (n <= 0) return 0;
   const int grid = int((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
-  if (weights_bf16) dense_adam_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(w), m, v, grad, n, to_hyper(*h));
-  else dense_adam_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(w), m, v, grad, n, to_hyper(*h));
+  if (weights_bf16) dense_adam_kernel<t16><<<grid, 256, 0, st>>>(static_cast<t16*>(w), m, v, grad, n, to_hyper(*h), ctl, seed_scaled, norm_weight);
+  else dense_adam_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(w), m, v, grad, n, to_hyper(*h), ctl, seed_scaled, norm_weight);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-extern "C" int clt_decoder_norm2(const void* w, float* out, int F, int R, int d, int weights_bf16, cudaStream_t st) {
+extern "C" int CLT_FN(clt_decoder_norm2)(const void* w, float* out, int F, int R, int d, int weights_bf16, cudaStream_t st) {
   if ((1LL * R * d) % 8 != 0) return -1;
   const int grid = (F + 7) / 8 < 1184 ? (F + 7) / 8 : 1184;
   if (grid == 0) return 0;
-  if (weights_bf16) decoder_norm2_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(w), out, F, R, d);
+  if (weights_bf16) decoder_norm2_kernel<t16><<<grid, 256, 0, st>>>(static_cast<const t16*>(w), out, F, R, d);
   else decoder_norm2_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(w), out, F, R, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+#if !CLT_T16_IS_HALF
 extern "C" int clt_sparsity_penalty(const int* feat_off, const float* fcsr_val, const float* norm2, int ncols, float lambda, float c,
                                     float* grad_a, float* pen_coef, double* penalty_out, cudaStream_t st) {
   if (ncols <= 0) return 0;
@@ -1155,3 +1324,4 @@ extern "C" int clt_sparsity_penalty(const int* feat_off, const float* fcsr_val, 
   sparsity_penalty_kernel<<<grid, 256, 0, st>>>(feat_off, fcsr_val, norm2, ncols, lambda, c, grad_a, pen_coef, penalty_out);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
+#endif

@@ -10,12 +10,7 @@
 using torch::Tensor;
 using OptTensor = c10::optional<Tensor>;
 
-extern "C" {
-int clt_encoder_gemm(const void* A, const void* B, const void* bias, void* C, int L, int M, int N, int K, long long ldc,
-                     long long layer_stride_c, int* status, float* tile_stats, int num_sms, cudaStream_t stream);
-int clt_colstats_from_tiles(const float* tile_stats, float* mean, float* rstd, int L, int B, int F, cudaStream_t st);
-int clt_colstats(const void* x, float* mean, float* rstd, int L, int B, int F, long long ld, long long layer_stride, cudaStream_t st);
-
+// ---- argument blocks shared with the .cu files ------------------------------------------------------------------
 struct CltExchangeArgs {
   int world;
   int rank;
@@ -45,10 +40,6 @@ struct CltSelectArgs {
   long long* sel_state;
   unsigned int* pool_key; int* pool_tok; int* pool_col; float* pool_val; long long pool_cap;
 };
-int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st);
-int clt_threshold_select(const CltSelectArgs* a, cudaStream_t st);
-int clt_token_topk_select(const CltSelectArgs* a, cudaStream_t st);
-
 struct CltThetaGradArgs {
   const void* gs; const void* w[32]; const void* preact;
   long long ldx, layer_stride_x;
@@ -56,9 +47,9 @@ struct CltThetaGradArgs {
   float* S1; float* S2;
   int L, B, F, d;
   int* status;
+  int tying;            // 0 untied ([F, L - s, d] per source), 1 per_source, 2 per_target ([F, 1, d] per layer)
+  const void* gs_cum;   // per_source: suffix sums of the gradient seed over the layers
 };
-int clt_theta_grad_gemm(const CltThetaGradArgs* a, int num_sms, cudaStream_t st);
-
 struct CltCsrArgs {
   const int* ent_tok; const int* ent_col; const float* ent_val; long long ent_cap;
   const long long* ctl;
@@ -71,9 +62,6 @@ struct CltCsrArgs {
   int sort_segments;
   int col_pitch;
 };
-int clt_build_csr(const CltCsrArgs* a, cudaStream_t st);
-int clt_dead_counter_update(long long* counter, unsigned char* fired, int n, cudaStream_t st);
-
 struct CltDecodeArgs {
   const void* w[32];
   int rows[32];
@@ -87,20 +75,14 @@ struct CltDecodeArgs {
   int rows_per_rank, rank, world;
   int mode;
   int* status;
+  float* ctl;
+  int rows_limit;
 };
 struct CltPeerTable {
   int world;
   int rank;
   void* ptr[8];
 };
-int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int* status, long long timeout_cycles, cudaStream_t st);
-int clt_owner_reduce_loss(const float* stage, const CltPeerTable* gs_peers, const float* bias_sum, const float* addend, const void* target,
-                          const float* sigma, float* yhat_out, double* sq_err, int L, int B, int d, int rows_per_rank, cudaStream_t st);
-int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st);
-int clt_recon_epilogue(const float* yhat_sum, const float* bias_sum, const float* addend, const void* target, const float* sigma,
-                       void* gs, float* yhat_out, double* sq_err, int L, int B, int d, int row0, int nrows, cudaStream_t st);
-int clt_gs_colsum(const void* gs, float* out, int L, int B, int d, cudaStream_t st);
-
 struct CltAdamHyper {
   float lr, beta1, beta2, eps, weight_decay, bc1, bc2;
   int decoupled;
@@ -118,8 +100,10 @@ struct CltDecAdamArgs {
   CltAdamHyper h;
   int* status;
   int moments_bf16;
+  const int* extra_idx; const float* extra_rows;
+  float* ctl;
+  int norm_only;
 };
-int clt_decoder_rows_adam(const CltDecAdamArgs* a, int num_sms, cudaStream_t st);
 struct CltEncAdamArgs {
   void* w; float* m; float* v; void* bias; float* bias_m; float* bias_v;
   int L, B, d, F_pitch, weights_bf16;
@@ -128,13 +112,45 @@ struct CltEncAdamArgs {
   CltAdamHyper h;
   int* status;
   int moments_bf16;
+  const int* extra_idx; const float* extra_rows; const float* extra_bias;
+  float* ctl;
+  int norm_only;
 };
-int clt_encoder_rows_adam(const CltEncAdamArgs* a, int num_sms, cudaStream_t st);
-int clt_dense_adam(void* w, float* m, float* v, const float* grad, long long n, int weights_bf16, const CltAdamHyper* h, cudaStream_t st);
-int clt_decoder_norm2(const void* w, float* out, int F, int R, int d, int weights_bf16, cudaStream_t st);
+struct CltStepControlArgs {
+  float* ctl; const int* status; double* sq_err; int L; double* scalars; int n_scalars; float* losses; double inv_bd;
+  int phase, dynamic_scale, growth_interval; float max_norm; int round;
+};
+struct CltThetaAdamArgs {
+  void* log_theta; float* m; float* v; float* theta; const float* S1; const float* S2; const float* norm2;
+  const int* feat_off; const float* fcsr_val;
+  int L, pitch, tying, weights_16;
+  float c_g, lambda, c, bandwidth;
+  CltAdamHyper h;
+  float* ctl;
+  float norm_weight;
+  float* grad_out;
+};
+
+extern "C" {
+// type-independent entry points (compiled once)
+int clt_colstats_from_tiles(const float* tile_stats, float* mean, float* rstd, int L, int B, int F, cudaStream_t st);
+int clt_build_csr(const CltCsrArgs* a, cudaStream_t st);
+int clt_dead_counter_update(long long* counter, unsigned char* fired, int n, cudaStream_t st);
+int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int* status, long long timeout_cycles, cudaStream_t st);
 int clt_sparsity_penalty(const int* feat_off, const float* fcsr_val, const float* norm2, int ncols, float lambda, float c,
                          float* grad_a, float* pen_coef, double* penalty_out, cudaStream_t st);
+int clt_step_control(const CltStepControlArgs* a, const CltExchangeArgs* exa, cudaStream_t st);
+// entry points that exist once per 16-bit storage type: name (bf16) and name_h (fp16)
+#define CLT_API(name) name
+#include "clt_api.inc"
+#undef CLT_API
+#define CLT_API(name) name##_h
+#include "clt_api.inc"
+#undef CLT_API
 }
+
+// picks the fp16 or the bf16 build of an entry point
+#define CLT_PICK(half, name) ((half) ? name##_h : name)
 
 namespace {
 
@@ -154,9 +170,20 @@ void need(const Tensor& t, c10::ScalarType ty, const char* name) {
   TORCH_CHECK(t.scalar_type() == ty, name, " has dtype ", t.scalar_type(), ", expected ", ty);
   TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
 }
+// 16-bit storage type of a tensor: true for fp16, false for bf16 (anything else is refused)
+bool is_half(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.scalar_type() == at::kHalf || t.scalar_type() == at::kBFloat16, name, " must be bf16 or fp16, got ", t.scalar_type());
+  return t.scalar_type() == at::kHalf;
+}
+c10::ScalarType t16_of(bool half) { return half ? at::kHalf : at::kBFloat16; }
 template <typename T>
 T* opt_ptr(const OptTensor& t) {
   return t.has_value() && t->defined() ? static_cast<T*>(t->data_ptr()) : nullptr;
+}
+float* ctl_ptr(const OptTensor& ctl) {
+  if (!ctl.has_value() || !ctl->defined()) return nullptr;
+  TORCH_CHECK(ctl->is_cuda() && ctl->scalar_type() == at::kFloat && ctl->numel() >= 16 && ctl->is_contiguous(), "ctl: contiguous fp32 CUDA tensor of 16 words");
+  return ctl->data_ptr<float>();
 }
 
 CltAdamHyper hyper_from(const std::vector<double>& h) {
@@ -171,11 +198,13 @@ CltAdamHyper hyper_from(const std::vector<double>& h) {
 // ----------------------------------------------------------------------------------------------
 // tile_stats (optional, fp32 [L, ceil(M / 128), N, 2]): per 128-row block sums / sums of squares of the stored outputs.
 void encoder_gemm(const Tensor& x, const Tensor& w, const OptTensor& bias, Tensor& out, Tensor& status, const OptTensor& tile_stats) {
-  need(x, at::kBFloat16, "x"); need(w, at::kBFloat16, "w"); need(out, at::kBFloat16, "out"); need(status, at::kInt, "status");
+  const bool half = is_half(x, "x");
+  const auto ty = t16_of(half);
+  need(x, ty, "x"); need(w, ty, "w"); need(out, ty, "out"); need(status, at::kInt, "status");
   TORCH_CHECK(x.dim() == 3 && w.dim() == 3 && out.dim() == 3, "expected [L, M, K], [L, N, K], [L, M, N]");
   const int L = x.size(0), M = x.size(1), K = x.size(2), N = w.size(1);
   TORCH_CHECK(w.size(0) == L && w.size(2) == K && out.size(0) == L && out.size(1) == M && out.size(2) == N, "shape mismatch");
-  if (bias.has_value() && bias->defined()) { need(*bias, at::kBFloat16, "bias"); TORCH_CHECK(bias->numel() == 1LL * L * N, "bias must be [L, N]"); }
+  if (bias.has_value() && bias->defined()) { need(*bias, ty, "bias"); TORCH_CHECK(bias->numel() == 1LL * L * N, "bias must be [L, N]"); }
   float* ts = nullptr;
   if (tile_stats.has_value() && tile_stats->defined()) {
     need(*tile_stats, at::kFloat, "tile_stats");
@@ -183,8 +212,8 @@ void encoder_gemm(const Tensor& x, const Tensor& w, const OptTensor& bias, Tenso
     ts = tile_stats->data_ptr<float>();
   }
   c10::cuda::CUDAGuard guard(x.device());
-  check(clt_encoder_gemm(x.data_ptr(), w.data_ptr(), opt_ptr<void>(bias), out.data_ptr(), L, M, N, K, N, 1LL * M * N,
-                         status.data_ptr<int>(), ts, num_sms(), cur_stream()), "encoder_gemm");
+  check(CLT_PICK(half, clt_encoder_gemm)(x.data_ptr(), w.data_ptr(), opt_ptr<void>(bias), out.data_ptr(), L, M, N, K, N, 1LL * M * N,
+                                         status.data_ptr<int>(), ts, num_sms(), cur_stream()), "encoder_gemm");
 }
 
 // mean / rstd [L, F] from the per-block sums written by encoder_gemm (B rows per column).
@@ -198,11 +227,12 @@ void colstats_from_tiles(const Tensor& tile_stats, Tensor& mean, Tensor& rstd, i
 }
 
 void colstats(const Tensor& x, Tensor& mean, Tensor& rstd) {
-  need(x, at::kBFloat16, "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd");
+  const bool half = is_half(x, "x");
+  need(x, t16_of(half), "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd");
   const int L = x.size(0), B = x.size(1), F = x.size(2);
   TORCH_CHECK(mean.numel() == 1LL * L * F && rstd.numel() == 1LL * L * F, "mean/rstd must be [L, F]");
   c10::cuda::CUDAGuard guard(x.device());
-  check(clt_colstats(x.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), L, B, F, F, 1LL * B * F, cur_stream()), "colstats");
+  check(CLT_PICK(half, clt_colstats)(x.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), L, B, F, F, 1LL * B * F, cur_stream()), "colstats");
 }
 
 // exchange: (world, rank, data_ptrs[world], flag_ptrs[world], slot_elems, seq) or empty for a single rank
@@ -222,7 +252,8 @@ void batchtopk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, i
                       Tensor& status, int64_t world, int64_t rank, const std::vector<int64_t>& ex_data,
                       const std::vector<int64_t>& ex_flags, int64_t slot_elems, int64_t seq, const OptTensor& sel_state,
                       const OptTensor& pool) {
-  need(x, at::kBFloat16, "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd");
+  const bool half = is_half(x, "x");
+  need(x, t16_of(half), "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd");
   need(hist, at::kInt, "hist"); need(ctl, at::kLong, "ctl"); need(status, at::kInt, "status");
   need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
   need(cand_key, at::kInt, "cand_key"); need(cand_tok, at::kInt, "cand_tok"); need(cand_col, at::kInt, "cand_col"); need(cand_val, at::kFloat, "cand_val");
@@ -254,13 +285,14 @@ void batchtopk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, i
   CltExchangeArgs ex;
   const bool multi = fill_exchange(ex, world, rank, ex_data, ex_flags, slot_elems, seq);
   c10::cuda::CUDAGuard guard(x.device());
-  check(clt_batchtopk_select(&a, multi ? &ex : nullptr, cur_stream()), "batchtopk_select");
+  check(CLT_PICK(half, clt_batchtopk_select)(&a, multi ? &ex : nullptr, cur_stream()), "batchtopk_select");
 }
 
-// Entries with x >= theta[l, f] (JumpReLU; ReLU with theta = smallest positive bf16) as a (token, column, value) list.
+// Entries with x >= theta[l, f] (JumpReLU; ReLU with theta = smallest positive value) as a (token, column, value) list.
 void threshold_select(const Tensor& x, const Tensor& theta, int64_t f_valid, int64_t col_pitch, Tensor& ctl, Tensor& ent_tok,
                       Tensor& ent_col, Tensor& ent_val, Tensor& status) {
-  need(x, at::kBFloat16, "x"); need(theta, at::kFloat, "theta"); need(ctl, at::kLong, "ctl"); need(status, at::kInt, "status");
+  const bool half = is_half(x, "x");
+  need(x, t16_of(half), "x"); need(theta, at::kFloat, "theta"); need(ctl, at::kLong, "ctl"); need(status, at::kInt, "status");
   need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
   TORCH_CHECK(x.dim() == 3 && theta.dim() == 2 && theta.size(0) == x.size(0) && theta.size(1) >= f_valid, "theta must be [L, >= F]");
   TORCH_CHECK(ctl.numel() >= 16, "ctl needs 16 elements");
@@ -274,13 +306,14 @@ void threshold_select(const Tensor& x, const Tensor& theta, int64_t f_valid, int
   a.ent_tok = ent_tok.data_ptr<int>(); a.ent_col = ent_col.data_ptr<int>(); a.ent_val = ent_val.data_ptr<float>(); a.ent_cap = ent_tok.numel();
   a.status = status.data_ptr<int>();
   c10::cuda::CUDAGuard guard(x.device());
-  check(clt_threshold_select(&a, cur_stream()), "threshold_select");
+  check(CLT_PICK(half, clt_threshold_select)(&a, cur_stream()), "threshold_select");
 }
 
 // Per-token top-k of the batch z-scores: exactly k entries per token at [token * k, token * k + k) of the entry list.
 void token_topk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, int64_t col_pitch, int64_t k, Tensor& ctl, Tensor& ent_tok,
                        Tensor& ent_col, Tensor& ent_val, Tensor& status) {
-  need(x, at::kBFloat16, "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd"); need(ctl, at::kLong, "ctl");
+  const bool half = is_half(x, "x");
+  need(x, t16_of(half), "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd"); need(ctl, at::kLong, "ctl");
   need(status, at::kInt, "status"); need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
   TORCH_CHECK(x.dim() == 3 && mean.dim() == 2 && mean.size(0) == x.size(0) && mean.size(1) == x.size(2), "mean / rstd must be [L, F]");
   TORCH_CHECK(ctl.numel() >= 16 && ent_tok.numel() >= x.size(1) * k, "entry list needs B * k elements");
@@ -294,31 +327,44 @@ void token_topk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, 
   a.ent_tok = ent_tok.data_ptr<int>(); a.ent_col = ent_col.data_ptr<int>(); a.ent_val = ent_val.data_ptr<float>(); a.ent_cap = ent_tok.numel();
   a.status = status.data_ptr<int>();
   c10::cuda::CUDAGuard guard(x.device());
-  check(clt_token_topk_select(&a, cur_stream()), "token_topk_select");
+  check(CLT_PICK(half, clt_token_topk_select)(&a, cur_stream()), "token_topk_select");
 }
 
 // JumpReLU threshold gradient sums: S1[l, f] += sum_b window * x * (gs . W_dec rows), S2[l, f] += sum_b window * x.
+// tying: 0 untied (decoder tensor s is [F, L - s, d]), 1 per_source, 2 per_target (tensors [F, 1, d]); per_source needs
+// gs_cum, the suffix sums of the gradient seed over the layers (gs_suffix_sum).
 void theta_grad_gemm(const Tensor& gs, const std::vector<Tensor>& dec_w, const Tensor& preact, const Tensor& theta, double bandwidth,
-                     Tensor& S1, Tensor& S2, Tensor& status) {
-  need(gs, at::kBFloat16, "gs"); need(preact, at::kBFloat16, "preact"); need(theta, at::kFloat, "theta");
+                     Tensor& S1, Tensor& S2, Tensor& status, int64_t tying, const OptTensor& gs_cum) {
+  const bool half = is_half(gs, "gs");
+  const auto ty = t16_of(half);
+  need(gs, ty, "gs"); need(preact, ty, "preact"); need(theta, at::kFloat, "theta");
   need(S1, at::kFloat, "S1"); need(S2, at::kFloat, "S2"); need(status, at::kInt, "status");
   const int L = gs.size(0), B = gs.size(1), d = gs.size(2), F = preact.size(2);
-  TORCH_CHECK(int(dec_w.size()) == L && L <= 32, "one untied decoder tensor per layer (at most 32)");
+  TORCH_CHECK(int(dec_w.size()) == L && L <= 32, "one decoder tensor per layer (at most 32)");
   TORCH_CHECK(preact.size(0) == L && preact.size(1) == B && theta.size(0) == L && theta.size(1) >= F, "shape mismatch");
   TORCH_CHECK(S1.sizes() == theta.sizes() && S2.sizes() == theta.sizes(), "S1 / S2 must have theta's shape");
+  TORCH_CHECK(tying >= 0 && tying <= 2, "tying must be 0, 1 or 2");
   CltThetaGradArgs a;
   std::memset(&a, 0, sizeof(a));
   a.gs = gs.data_ptr(); a.preact = preact.data_ptr(); a.ldx = preact.size(2); a.layer_stride_x = 1LL * B * preact.size(2);
   for (int s = 0; s < L; ++s) {
-    need(dec_w[s], at::kBFloat16, "decoder weight");
-    TORCH_CHECK(dec_w[s].dim() == 3 && dec_w[s].size(0) == F && dec_w[s].size(1) == L - s && dec_w[s].size(2) == d, "decoder tensor must be [F, L - s, d]");
+    need(dec_w[s], ty, "decoder weight");
+    const int rows = tying == 0 ? L - s : 1;
+    TORCH_CHECK(dec_w[s].dim() == 3 && dec_w[s].size(0) == F && dec_w[s].size(1) == rows && dec_w[s].size(2) == d, "decoder tensor must be [F, rows, d]");
     a.w[s] = dec_w[s].data_ptr();
   }
   a.theta = theta.data_ptr<float>(); a.stat_pitch = int(theta.size(1)); a.bandwidth = float(bandwidth);
   a.S1 = S1.data_ptr<float>(); a.S2 = S2.data_ptr<float>();
   a.L = L; a.B = B; a.F = F; a.d = d; a.status = status.data_ptr<int>();
+  a.tying = int(tying);
+  if (tying == 1) {
+    TORCH_CHECK(gs_cum.has_value() && gs_cum->defined(), "per_source tying needs gs_cum");
+    need(*gs_cum, ty, "gs_cum");
+    TORCH_CHECK(gs_cum->sizes() == gs.sizes(), "gs_cum must have the shape of gs");
+    a.gs_cum = gs_cum->data_ptr();
+  }
   c10::cuda::CUDAGuard guard(gs.device());
-  check(clt_theta_grad_gemm(&a, num_sms(), cur_stream()), "theta_grad_gemm");
+  check(CLT_PICK(half, clt_theta_grad_gemm)(&a, num_sms(), cur_stream()), "theta_grad_gemm");
 }
 
 void build_csr(const Tensor& ent_tok, const Tensor& ent_col, const Tensor& ent_val, const Tensor& ctl, int64_t num_tokens, int64_t num_cols,
@@ -352,16 +398,21 @@ void dead_counter_update(Tensor& counter, Tensor& fired) {
         "dead_counter_update");
 }
 
+// ctl (optional): step control block; the gradient seed is multiplied by its loss scale and a seed outside the 16-bit range
+// raises its found-inf flag.  rows_limit > 0: only the first rows_limit target rows of every feature are decoded.
 void sparse_decode(const std::vector<Tensor>& dec_w, int64_t L, int64_t B, int64_t d, int64_t col_pitch, int64_t tying, const Tensor& tok_off,
                    const Tensor& tcsr_col, const Tensor& tcsr_val, const OptTensor& feat_offset, const OptTensor& feat_scale,
                    const OptTensor& yhat_partial, const OptTensor& bias_sum, const OptTensor& addend, const OptTensor& target,
                    const OptTensor& sigma, const OptTensor& gs, const OptTensor& yhat_out, const OptTensor& sq_err, int64_t mode,
-                   const std::vector<int64_t>& stage_peers, int64_t rows_per_rank, int64_t rank, const OptTensor& status) {
-  TORCH_CHECK(dec_w.size() <= 32, "at most 32 decoder tensors");
+                   const std::vector<int64_t>& stage_peers, int64_t rows_per_rank, int64_t rank, const OptTensor& status,
+                   const OptTensor& ctl, int64_t rows_limit) {
+  TORCH_CHECK(dec_w.size() >= 1 && dec_w.size() <= 32, "1..32 decoder tensors");
+  const bool half = is_half(dec_w[0], "dec_w");
+  const auto ty = t16_of(half);
   CltDecodeArgs a;
   std::memset(&a, 0, sizeof(a));
   for (size_t i = 0; i < dec_w.size(); ++i) {
-    need(dec_w[i], at::kBFloat16, "dec_w");
+    need(dec_w[i], ty, "dec_w");
     a.w[i] = dec_w[i].data_ptr();
     a.rows[i] = int(dec_w[i].size(1));
   }
@@ -369,10 +420,14 @@ void sparse_decode(const std::vector<Tensor>& dec_w, int64_t L, int64_t B, int64
   a.tok_off = tok_off.data_ptr<int>(); a.tcsr_col = tcsr_col.data_ptr<int>(); a.tcsr_val = tcsr_val.data_ptr<float>();
   a.feat_offset = opt_ptr<const float>(feat_offset); a.feat_scale = opt_ptr<const float>(feat_scale);
   a.yhat_partial = opt_ptr<float>(yhat_partial); a.bias_sum = opt_ptr<const float>(bias_sum); a.addend = opt_ptr<const float>(addend);
+  if (target.has_value() && target->defined()) need(*target, ty, "target");
+  if (gs.has_value() && gs->defined()) need(*gs, ty, "gs");
   a.target = opt_ptr<const void>(target); a.sigma = opt_ptr<const float>(sigma); a.gs = opt_ptr<void>(gs);
   a.yhat_out = opt_ptr<float>(yhat_out); a.sq_err = opt_ptr<double>(sq_err); a.mode = int(mode);
   if (status.has_value()) TORCH_CHECK(status->scalar_type() == at::kInt && status->numel() >= 4, "status: int32 tensor of at least 4 words (word 0 holds the code)");
   a.status = opt_ptr<int>(status);
+  a.ctl = ctl_ptr(ctl);
+  a.rows_limit = int(rows_limit);
   if (mode == 2) {
     TORCH_CHECK(stage_peers.size() >= 1 && stage_peers.size() <= 8 && rows_per_rank > 0, "mode 2 needs the peers' staging pointers");
     for (size_t i = 0; i < stage_peers.size(); ++i) a.stage_peers[i] = reinterpret_cast<void*>(stage_peers[i]);
@@ -383,18 +438,19 @@ void sparse_decode(const std::vector<Tensor>& dec_w, int64_t L, int64_t B, int64
     TORCH_CHECK(a.bias_sum && a.target && a.gs && a.sq_err, "mode 1 needs bias_sum, target, gs, sq_err");
   }
   c10::cuda::CUDAGuard guard(tok_off.device());
-  check(clt_sparse_decode(&a, cur_stream()), "sparse_decode");
+  check(CLT_PICK(half, clt_sparse_decode)(&a, cur_stream()), "sparse_decode");
 }
 
 void recon_epilogue(const Tensor& yhat_sum, const Tensor& bias_sum, const OptTensor& addend, const Tensor& target, const OptTensor& sigma,
-                    Tensor& gs, const OptTensor& yhat_out, Tensor& sq_err, int64_t row0, int64_t nrows) {
-  need(yhat_sum, at::kFloat, "yhat_sum"); need(bias_sum, at::kFloat, "bias_sum"); need(target, at::kBFloat16, "target");
-  need(gs, at::kBFloat16, "gs"); need(sq_err, at::kDouble, "sq_err");
+                    Tensor& gs, const OptTensor& yhat_out, Tensor& sq_err, int64_t row0, int64_t nrows, const OptTensor& ctl) {
+  const bool half = is_half(target, "target");
+  need(yhat_sum, at::kFloat, "yhat_sum"); need(bias_sum, at::kFloat, "bias_sum"); need(target, t16_of(half), "target");
+  need(gs, t16_of(half), "gs"); need(sq_err, at::kDouble, "sq_err");
   const int L = yhat_sum.size(0), B = yhat_sum.size(1), d = yhat_sum.size(2);
   c10::cuda::CUDAGuard guard(yhat_sum.device());
-  check(clt_recon_epilogue(yhat_sum.data_ptr<float>(), bias_sum.data_ptr<float>(), opt_ptr<const float>(addend), target.data_ptr(),
-                           opt_ptr<const float>(sigma), gs.data_ptr(), opt_ptr<float>(yhat_out), sq_err.data_ptr<double>(), L, B, d,
-                           int(row0), int(nrows), cur_stream()), "recon_epilogue");
+  check(CLT_PICK(half, clt_recon_epilogue)(yhat_sum.data_ptr<float>(), bias_sum.data_ptr<float>(), opt_ptr<const float>(addend), target.data_ptr(),
+                                           opt_ptr<const float>(sigma), gs.data_ptr(), opt_ptr<float>(yhat_out), sq_err.data_ptr<double>(), L, B, d,
+                                           int(row0), int(nrows), ctl_ptr(ctl), cur_stream()), "recon_epilogue");
 }
 
 CltPeerTable make_table(const std::vector<int64_t>& ptrs, int64_t rank) {
@@ -426,90 +482,123 @@ void memcpy_2d(int64_t dst, int64_t dst_pitch, int64_t src, int64_t src_pitch, i
 }
 
 void owner_reduce_loss(const Tensor& stage, const std::vector<int64_t>& gs_ptrs, int64_t rank, const Tensor& bias_sum, const OptTensor& addend,
-                       const Tensor& target, const OptTensor& sigma, const OptTensor& yhat_out, Tensor& sq_err, int64_t rows_per_rank) {
-  need(stage, at::kFloat, "stage"); need(bias_sum, at::kFloat, "bias_sum"); need(target, at::kBFloat16, "target"); need(sq_err, at::kDouble, "sq_err");
+                       const Tensor& target, const OptTensor& sigma, const OptTensor& yhat_out, Tensor& sq_err, int64_t rows_per_rank,
+                       const OptTensor& ctl) {
+  const bool half = is_half(target, "target");
+  need(stage, at::kFloat, "stage"); need(bias_sum, at::kFloat, "bias_sum"); need(target, t16_of(half), "target"); need(sq_err, at::kDouble, "sq_err");
   const int L = target.size(0), B = target.size(1), d = target.size(2);
   const CltPeerTable t = make_table(gs_ptrs, rank);
   TORCH_CHECK(stage.numel() >= 1LL * t.world * L * rows_per_rank * d, "staging area too small");
   c10::cuda::CUDAGuard guard(stage.device());
-  check(clt_owner_reduce_loss(stage.data_ptr<float>(), &t, bias_sum.data_ptr<float>(), opt_ptr<const float>(addend), target.data_ptr(),
-                              opt_ptr<const float>(sigma), opt_ptr<float>(yhat_out), sq_err.data_ptr<double>(), L, B, d, int(rows_per_rank),
-                              cur_stream()), "owner_reduce_loss");
+  check(CLT_PICK(half, clt_owner_reduce_loss)(stage.data_ptr<float>(), &t, bias_sum.data_ptr<float>(), opt_ptr<const float>(addend), target.data_ptr(),
+                                              opt_ptr<const float>(sigma), opt_ptr<float>(yhat_out), sq_err.data_ptr<double>(), L, B, d, int(rows_per_rank),
+                                              ctl_ptr(ctl), cur_stream()), "owner_reduce_loss");
 }
 
 void gs_colsum(const Tensor& gs, Tensor& out) {
-  need(gs, at::kBFloat16, "gs"); need(out, at::kFloat, "out");
+  const bool half = is_half(gs, "gs");
+  need(gs, t16_of(half), "gs"); need(out, at::kFloat, "out");
   c10::cuda::CUDAGuard guard(gs.device());
-  check(clt_gs_colsum(gs.data_ptr(), out.data_ptr<float>(), int(gs.size(0)), int(gs.size(1)), int(gs.size(2)), cur_stream()), "gs_colsum");
+  check(CLT_PICK(half, clt_gs_colsum)(gs.data_ptr(), out.data_ptr<float>(), int(gs.size(0)), int(gs.size(1)), int(gs.size(2)), cur_stream()), "gs_colsum");
 }
 
+// out[s] = sum over t >= s of gs[t] (same shape and type)
+void gs_suffix_sum(const Tensor& gs, Tensor& out) {
+  const bool half = is_half(gs, "gs");
+  need(gs, t16_of(half), "gs"); need(out, t16_of(half), "out");
+  TORCH_CHECK(gs.dim() == 3 && out.sizes() == gs.sizes(), "gs / out must be [L, B, d]");
+  c10::cuda::CUDAGuard guard(gs.device());
+  check(CLT_PICK(half, clt_gs_suffix_sum)(gs.data_ptr(), out.data_ptr(), int(gs.size(0)), int(gs.size(1)), int(gs.size(2)), cur_stream()), "gs_suffix_sum");
+}
+
+// extra_idx / extra_rows: compact extra gradient rows for the features' first rows (extra_idx[col] = row or -1);
+// ctl: step control block (skip flag, 1 / loss scale, clip coefficient); norm_only: gradient-norm pre-pass.
 void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vector<Tensor>& v, int64_t L, int64_t B, int64_t d,
                        int64_t F_pitch, int64_t tying, const Tensor& feat_off, const Tensor& fcsr_tok, const Tensor& fcsr_val,
                        const Tensor& gs, const OptTensor& grad_a, const OptTensor& pen_coef, const OptTensor& norm2_out,
                        const OptTensor& feat_offset, const OptTensor& feat_scale, const OptTensor& dgrad_row0,
-                       const std::vector<double>& hyper, const OptTensor& status) {
-  TORCH_CHECK(w.size() <= 32 && w.size() == m.size() && w.size() == v.size(), "bad tensor lists");
+                       const std::vector<double>& hyper, const OptTensor& status, const OptTensor& extra_idx, const OptTensor& extra_rows,
+                       const OptTensor& ctl, bool norm_only) {
+  TORCH_CHECK(w.size() >= 1 && w.size() <= 32 && w.size() == m.size() && w.size() == v.size(), "bad tensor lists");
   CltDecAdamArgs a;
   std::memset(&a, 0, sizeof(a));
-  const bool bf16 = w[0].scalar_type() == at::kBFloat16;
+  const bool half = is_half(gs, "gs");
+  const bool w16 = w[0].scalar_type() != at::kFloat;
   for (size_t i = 0; i < w.size(); ++i) {
-    need(w[i], bf16 ? at::kBFloat16 : at::kFloat, "w");
+    need(w[i], w16 ? t16_of(half) : at::kFloat, "w");
     need(m[i], m[0].scalar_type(), "m"); need(v[i], m[0].scalar_type(), "v");
     TORCH_CHECK(m[0].scalar_type() == at::kFloat || m[0].scalar_type() == at::kBFloat16, "moments must be fp32 or bf16");
     TORCH_CHECK(w[i].dim() == 3 && w[i].size(0) == F_pitch && w[i].size(2) == d, "decoder tensor must be [F, R, d]");
     a.w[i] = w[i].data_ptr(); a.m[i] = static_cast<float*>(m[i].data_ptr()); a.v[i] = static_cast<float*>(v[i].data_ptr()); a.rows[i] = int(w[i].size(1));
   }
-  a.ntensors = int(w.size()); a.L = int(L); a.B = int(B); a.d = int(d); a.F_pitch = int(F_pitch); a.tying = int(tying); a.weights_bf16 = bf16;
+  a.ntensors = int(w.size()); a.L = int(L); a.B = int(B); a.d = int(d); a.F_pitch = int(F_pitch); a.tying = int(tying); a.weights_bf16 = w16;
   a.feat_off = feat_off.data_ptr<int>(); a.fcsr_tok = fcsr_tok.data_ptr<int>(); a.fcsr_val = fcsr_val.data_ptr<float>();
-  need(gs, at::kBFloat16, "gs");
+  need(gs, t16_of(half), "gs");
   a.gs = gs.data_ptr(); a.grad_a = opt_ptr<float>(grad_a); a.pen_coef = opt_ptr<const float>(pen_coef); a.norm2_out = opt_ptr<float>(norm2_out);
   a.feat_offset = opt_ptr<const float>(feat_offset); a.feat_scale = opt_ptr<const float>(feat_scale);
   a.dgrad_row0 = opt_ptr<const float>(dgrad_row0);
   if (a.dgrad_row0) TORCH_CHECK(dgrad_row0->scalar_type() == at::kFloat && dgrad_row0->numel() == int64_t(w.size()) * F_pitch * d, "dgrad_row0 must be fp32 [ntensors, F, d]");
+  a.extra_idx = opt_ptr<const int>(extra_idx); a.extra_rows = opt_ptr<const float>(extra_rows);
+  if (a.extra_idx) {
+    TORCH_CHECK(extra_idx->scalar_type() == at::kInt && extra_idx->numel() >= int64_t(w.size()) * F_pitch && a.extra_rows != nullptr && extra_rows->scalar_type() == at::kFloat,
+                "extra_idx: int32 [ntensors * F]; extra_rows: fp32 [n, d]");
+  }
   a.h = hyper_from(hyper);
   a.status = opt_ptr<int>(status);
   a.moments_bf16 = m[0].scalar_type() == at::kBFloat16 ? 1 : 0;
+  a.ctl = ctl_ptr(ctl);
+  a.norm_only = norm_only ? 1 : 0;
   c10::cuda::CUDAGuard guard(gs.device());
-  check(clt_decoder_rows_adam(&a, num_sms(), cur_stream()), "decoder_rows_adam");
+  check(CLT_PICK(half, clt_decoder_rows_adam)(&a, num_sms(), cur_stream()), "decoder_rows_adam");
 }
 
 void encoder_rows_adam(Tensor& w, Tensor& m, Tensor& v, Tensor& bias, Tensor& bias_m, Tensor& bias_v, const Tensor& feat_off,
                        const Tensor& fcsr_tok, const Tensor& delta, const Tensor& x, const OptTensor& dense_grad,
-                       const OptTensor& dense_bias_grad, const std::vector<double>& hyper, const OptTensor& status) {
-  const bool bf16 = w.scalar_type() == at::kBFloat16;
+                       const OptTensor& dense_bias_grad, const std::vector<double>& hyper, const OptTensor& status,
+                       const OptTensor& extra_idx, const OptTensor& extra_rows, const OptTensor& extra_bias, const OptTensor& ctl, bool norm_only) {
+  const bool half = is_half(x, "x");
+  const bool w16 = w.scalar_type() != at::kFloat;
   const bool mbf16 = m.scalar_type() == at::kBFloat16;
-  need(w, bf16 ? at::kBFloat16 : at::kFloat, "w"); need(m, mbf16 ? at::kBFloat16 : at::kFloat, "m"); need(v, mbf16 ? at::kBFloat16 : at::kFloat, "v");
-  need(bias, bf16 ? at::kBFloat16 : at::kFloat, "bias"); need(bias_m, at::kFloat, "bias_m"); need(bias_v, at::kFloat, "bias_v");
-  need(x, at::kBFloat16, "x"); need(delta, at::kFloat, "delta");
+  need(w, w16 ? t16_of(half) : at::kFloat, "w"); need(m, mbf16 ? at::kBFloat16 : at::kFloat, "m"); need(v, mbf16 ? at::kBFloat16 : at::kFloat, "v");
+  need(bias, w16 ? t16_of(half) : at::kFloat, "bias"); need(bias_m, at::kFloat, "bias_m"); need(bias_v, at::kFloat, "bias_v");
+  need(x, t16_of(half), "x"); need(delta, at::kFloat, "delta");
   CltEncAdamArgs a;
   std::memset(&a, 0, sizeof(a));
   a.w = w.data_ptr(); a.m = static_cast<float*>(m.data_ptr()); a.v = static_cast<float*>(v.data_ptr());
   a.moments_bf16 = mbf16 ? 1 : 0;
   a.bias = bias.data_ptr(); a.bias_m = bias_m.data_ptr<float>(); a.bias_v = bias_v.data_ptr<float>();
-  a.L = int(w.size(0)); a.F_pitch = int(w.size(1)); a.d = int(w.size(2)); a.B = int(x.size(1)); a.weights_bf16 = bf16;
+  a.L = int(w.size(0)); a.F_pitch = int(w.size(1)); a.d = int(w.size(2)); a.B = int(x.size(1)); a.weights_bf16 = w16;
   a.feat_off = feat_off.data_ptr<int>(); a.fcsr_tok = fcsr_tok.data_ptr<int>(); a.delta = delta.data_ptr<float>(); a.x = x.data_ptr();
   a.dense_grad = opt_ptr<const float>(dense_grad); a.dense_bias_grad = opt_ptr<const float>(dense_bias_grad);
+  a.extra_idx = opt_ptr<const int>(extra_idx); a.extra_rows = opt_ptr<const float>(extra_rows); a.extra_bias = opt_ptr<const float>(extra_bias);
   a.h = hyper_from(hyper);
   a.status = opt_ptr<int>(status);
+  a.ctl = ctl_ptr(ctl);
+  a.norm_only = norm_only ? 1 : 0;
   c10::cuda::CUDAGuard guard(w.device());
-  check(clt_encoder_rows_adam(&a, num_sms(), cur_stream()), "encoder_rows_adam");
+  check(CLT_PICK(half, clt_encoder_rows_adam)(&a, num_sms(), cur_stream()), "encoder_rows_adam");
 }
 
-void dense_adam(Tensor& w, Tensor& m, Tensor& v, const Tensor& grad, const std::vector<double>& hyper) {
-  const bool bf16 = w.scalar_type() == at::kBFloat16;
-  need(w, bf16 ? at::kBFloat16 : at::kFloat, "w"); need(m, at::kFloat, "m"); need(v, at::kFloat, "v"); need(grad, at::kFloat, "grad");
+// seed_scaled: the gradient carries the loss scale; norm_weight > 0: norm-only pass (adds norm_weight * |g|^2 to the control block)
+void dense_adam(Tensor& w, Tensor& m, Tensor& v, const Tensor& grad, const std::vector<double>& hyper, const OptTensor& ctl, bool seed_scaled,
+                double norm_weight) {
+  const bool w16 = w.scalar_type() != at::kFloat;
+  const bool half = w16 && is_half(w, "w");
+  need(w, w16 ? t16_of(half) : at::kFloat, "w"); need(m, at::kFloat, "m"); need(v, at::kFloat, "v"); need(grad, at::kFloat, "grad");
   TORCH_CHECK(w.numel() == m.numel() && w.numel() == v.numel() && w.numel() == grad.numel(), "size mismatch");
   const CltAdamHyper h = hyper_from(hyper);
   c10::cuda::CUDAGuard guard(w.device());
-  check(clt_dense_adam(w.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr<float>(), w.numel(), bf16, &h, cur_stream()), "dense_adam");
+  check(CLT_PICK(half, clt_dense_adam)(w.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr<float>(), w.numel(), w16, &h,
+                                       ctl_ptr(ctl), seed_scaled ? 1 : 0, float(norm_weight), cur_stream()), "dense_adam");
 }
 
 void decoder_norm2(const Tensor& w, Tensor& out) {
-  const bool bf16 = w.scalar_type() == at::kBFloat16;
-  need(w, bf16 ? at::kBFloat16 : at::kFloat, "w"); need(out, at::kFloat, "out");
+  const bool w16 = w.scalar_type() != at::kFloat;
+  const bool half = w16 && is_half(w, "w");
+  need(w, w16 ? t16_of(half) : at::kFloat, "w"); need(out, at::kFloat, "out");
   TORCH_CHECK(w.dim() == 3 && out.numel() >= w.size(0), "w must be [F, R, d], out [F]");
   c10::cuda::CUDAGuard guard(w.device());
-  check(clt_decoder_norm2(w.data_ptr(), out.data_ptr<float>(), int(w.size(0)), int(w.size(1)), int(w.size(2)), bf16, cur_stream()), "decoder_norm2");
+  check(CLT_PICK(half, clt_decoder_norm2)(w.data_ptr(), out.data_ptr<float>(), int(w.size(0)), int(w.size(1)), int(w.size(2)), w16, cur_stream()), "decoder_norm2");
 }
 
 void sparsity_penalty(const Tensor& feat_off, const Tensor& fcsr_val, const Tensor& norm2, double lambda, double c, Tensor& grad_a,
@@ -524,28 +613,149 @@ void sparsity_penalty(const Tensor& feat_off, const Tensor& fcsr_val, const Tens
         "sparsity_penalty");
 }
 
+// Device-side decision of a step (see step.cu): phase 0 after the loss kernels, phase 1 after the gradient-norm pre-pass.
+// scalars: fp64 [n] further loss sums (penalty, pre-activation, auxiliary); losses: fp32 [8] out.
+void step_control(Tensor& ctl, const OptTensor& status, Tensor& sq_err, const OptTensor& scalars, Tensor& losses, double inv_bd, int64_t phase,
+                  bool dynamic_scale, int64_t growth_interval, double max_norm, int64_t world, int64_t rank,
+                  const std::vector<int64_t>& ex_data, const std::vector<int64_t>& ex_flags, int64_t slot_elems, int64_t seq, int64_t round) {
+  need(sq_err, at::kDouble, "sq_err"); need(losses, at::kFloat, "losses");
+  TORCH_CHECK(losses.numel() >= 8, "losses needs 8 elements");
+  CltStepControlArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.ctl = ctl_ptr(ctl);
+  TORCH_CHECK(a.ctl != nullptr, "ctl is required");
+  a.status = opt_ptr<const int>(status);
+  a.sq_err = sq_err.data_ptr<double>(); a.L = int(sq_err.numel());
+  if (scalars.has_value() && scalars->defined()) { need(*scalars, at::kDouble, "scalars"); a.scalars = scalars->data_ptr<double>(); a.n_scalars = int(scalars->numel()); }
+  a.losses = losses.data_ptr<float>(); a.inv_bd = inv_bd; a.phase = int(phase); a.dynamic_scale = dynamic_scale ? 1 : 0;
+  a.growth_interval = int(growth_interval); a.max_norm = float(max_norm); a.round = int(round);
+  CltExchangeArgs ex;
+  const bool multi = fill_exchange(ex, world, rank, ex_data, ex_flags, slot_elems, seq);
+  c10::cuda::CUDAGuard guard(sq_err.device());
+  check(clt_step_control(&a, multi ? &ex : nullptr, cur_stream()), "step_control");
+}
+
+// Decoder-bias gradient from the column sums of the gradient seed (sel [L, n_bias]: which targets a bias feeds) + AdamW.
+void decoder_bias_adam(Tensor& bias, Tensor& m, Tensor& v, const Tensor& sel, const Tensor& gs_sum, const OptTensor& extra,
+                       const std::vector<double>& hyper, const OptTensor& ctl, double norm_weight) {
+  const bool w16 = bias.scalar_type() != at::kFloat;
+  const bool half = w16 && is_half(bias, "bias");
+  need(bias, w16 ? t16_of(half) : at::kFloat, "bias"); need(m, at::kFloat, "m"); need(v, at::kFloat, "v");
+  need(sel, at::kFloat, "sel"); need(gs_sum, at::kFloat, "gs_sum");
+  const int n_bias = bias.size(0), d = bias.size(1), L = gs_sum.size(0);
+  TORCH_CHECK(sel.dim() == 2 && sel.size(0) == L && sel.size(1) == n_bias && gs_sum.size(1) == d && m.numel() == bias.numel() && v.numel() == bias.numel(), "shape mismatch");
+  if (extra.has_value() && extra->defined()) { need(*extra, at::kFloat, "extra"); TORCH_CHECK(extra->numel() == bias.numel(), "extra must have the shape of bias"); }
+  const CltAdamHyper h = hyper_from(hyper);
+  c10::cuda::CUDAGuard guard(bias.device());
+  check(CLT_PICK(half, clt_decoder_bias_adam)(bias.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(), sel.data_ptr<float>(), gs_sum.data_ptr<float>(),
+                                              opt_ptr<const float>(extra), n_bias, L, d, w16, &h, ctl_ptr(ctl), float(norm_weight), cur_stream()),
+        "decoder_bias_adam");
+}
+
+// End of a step: dead-feature counters (optional) and bias_sum[t] = sum_p sel[t, p] bias[p] (optional).
+void step_finish(const OptTensor& counter, const OptTensor& fired, const OptTensor& bias, const OptTensor& sel, const OptTensor& bias_sum) {
+  long long* cnt = nullptr; unsigned char* frd = nullptr; int ncols = 0;
+  if (counter.has_value() && counter->defined()) {
+    need(*counter, at::kLong, "counter"); TORCH_CHECK(fired.has_value() && fired->defined(), "counter needs fired"); need(*fired, at::kByte, "fired");
+    TORCH_CHECK(counter->numel() == fired->numel(), "counter / fired size mismatch");
+    cnt = reinterpret_cast<long long*>(counter->data_ptr<int64_t>()); frd = fired->data_ptr<uint8_t>(); ncols = int(counter->numel());
+  }
+  const void* bp = nullptr; const float* sp = nullptr; float* bs = nullptr; int n_bias = 0, L = 0, d = 0; bool w16 = false, half = false;
+  at::Device dev = counter.has_value() && counter->defined() ? counter->device() : bias->device();
+  if (bias_sum.has_value() && bias_sum->defined()) {
+    TORCH_CHECK(bias.has_value() && sel.has_value(), "bias_sum needs bias and sel");
+    w16 = bias->scalar_type() != at::kFloat; half = w16 && is_half(*bias, "bias");
+    need(*bias, w16 ? t16_of(half) : at::kFloat, "bias"); need(*sel, at::kFloat, "sel"); need(*bias_sum, at::kFloat, "bias_sum");
+    n_bias = bias->size(0); d = bias->size(1); L = sel->size(0);
+    TORCH_CHECK(sel->size(1) == n_bias && bias_sum->numel() == 1LL * L * d, "shape mismatch");
+    bp = bias->data_ptr(); sp = sel->data_ptr<float>(); bs = bias_sum->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(dev);
+  check(CLT_PICK(half, clt_step_finish)(cnt, frd, ncols, bp, sp, bs, n_bias, L, d, w16, cur_stream()), "step_finish");
+}
+
+// JumpReLU threshold update from the window sums (see step.cu); theta holds exp(log_theta) and is refreshed.
+void theta_adam(Tensor& log_theta, Tensor& m, Tensor& v, Tensor& theta, const Tensor& S1, const Tensor& S2, const Tensor& norm2,
+                const Tensor& feat_off, const Tensor& fcsr_val, int64_t tying, double c_g, double lambda, double c, double bandwidth,
+                const std::vector<double>& hyper, const OptTensor& ctl, double norm_weight, const OptTensor& grad_out) {
+  const bool w16 = log_theta.scalar_type() != at::kFloat;
+  const bool half = w16 && is_half(log_theta, "log_theta");
+  need(log_theta, w16 ? t16_of(half) : at::kFloat, "log_theta"); need(m, at::kFloat, "m"); need(v, at::kFloat, "v"); need(theta, at::kFloat, "theta");
+  need(S1, at::kFloat, "S1"); need(S2, at::kFloat, "S2"); need(norm2, at::kFloat, "norm2"); need(feat_off, at::kInt, "feat_off"); need(fcsr_val, at::kFloat, "fcsr_val");
+  TORCH_CHECK(log_theta.dim() == 2 && theta.sizes() == log_theta.sizes() && S1.sizes() == log_theta.sizes() && S2.sizes() == log_theta.sizes() &&
+              m.sizes() == log_theta.sizes() && v.sizes() == log_theta.sizes() && norm2.numel() >= log_theta.numel() && feat_off.numel() >= log_theta.numel() + 1,
+              "shape mismatch");
+  CltThetaAdamArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.log_theta = log_theta.data_ptr(); a.m = m.data_ptr<float>(); a.v = v.data_ptr<float>(); a.theta = theta.data_ptr<float>();
+  a.S1 = S1.data_ptr<float>(); a.S2 = S2.data_ptr<float>(); a.norm2 = norm2.data_ptr<float>();
+  a.feat_off = feat_off.data_ptr<int>(); a.fcsr_val = fcsr_val.data_ptr<float>();
+  a.L = int(log_theta.size(0)); a.pitch = int(log_theta.size(1)); a.tying = int(tying); a.weights_16 = w16;
+  a.c_g = float(c_g); a.lambda = float(lambda); a.c = float(c); a.bandwidth = float(bandwidth);
+  a.h = hyper_from(hyper); a.ctl = ctl_ptr(ctl); a.norm_weight = float(norm_weight); a.grad_out = opt_ptr<float>(grad_out);
+  c10::cuda::CUDAGuard guard(log_theta.device());
+  check(CLT_PICK(half, clt_theta_adam)(&a, cur_stream()), "theta_adam");
+}
+
+void theta_exp(const Tensor& log_theta, Tensor& theta) {
+  const bool w16 = log_theta.scalar_type() != at::kFloat;
+  const bool half = w16 && is_half(log_theta, "log_theta");
+  need(log_theta, w16 ? t16_of(half) : at::kFloat, "log_theta"); need(theta, at::kFloat, "theta");
+  TORCH_CHECK(theta.numel() == log_theta.numel(), "size mismatch");
+  c10::cuda::CUDAGuard guard(log_theta.device());
+  check(CLT_PICK(half, clt_theta_exp)(log_theta.data_ptr(), theta.data_ptr<float>(), log_theta.numel(), w16, cur_stream()), "theta_exp");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  const auto none = py::none();
   m.def("encoder_gemm", &encoder_gemm);
   m.def("colstats", &colstats);
   m.def("colstats_from_tiles", &colstats_from_tiles);
   m.def("batchtopk_select", &batchtopk_select);
   m.def("threshold_select", &threshold_select);
   m.def("token_topk_select", &token_topk_select);
-  m.def("theta_grad_gemm", &theta_grad_gemm);
+  m.def("theta_grad_gemm", &theta_grad_gemm, py::arg("gs"), py::arg("dec_w"), py::arg("preact"), py::arg("theta"), py::arg("bandwidth"),
+        py::arg("S1"), py::arg("S2"), py::arg("status"), py::arg("tying") = 0, py::arg("gs_cum") = none);
   m.def("build_csr", &build_csr);
   m.def("dead_counter_update", &dead_counter_update);
-  m.def("sparse_decode", &sparse_decode);
-  m.def("recon_epilogue", &recon_epilogue);
+  m.def("sparse_decode", &sparse_decode, py::arg("dec_w"), py::arg("L"), py::arg("B"), py::arg("d"), py::arg("col_pitch"), py::arg("tying"),
+        py::arg("tok_off"), py::arg("tcsr_col"), py::arg("tcsr_val"), py::arg("feat_offset"), py::arg("feat_scale"), py::arg("yhat_partial"),
+        py::arg("bias_sum"), py::arg("addend"), py::arg("target"), py::arg("sigma"), py::arg("gs"), py::arg("yhat_out"), py::arg("sq_err"),
+        py::arg("mode"), py::arg("stage_peers"), py::arg("rows_per_rank"), py::arg("rank"), py::arg("status"), py::arg("ctl") = none,
+        py::arg("rows_limit") = 0);
+  m.def("recon_epilogue", &recon_epilogue, py::arg("yhat_sum"), py::arg("bias_sum"), py::arg("addend"), py::arg("target"), py::arg("sigma"),
+        py::arg("gs"), py::arg("yhat_out"), py::arg("sq_err"), py::arg("row0"), py::arg("nrows"), py::arg("ctl") = none);
   m.def("gs_colsum", &gs_colsum);
+  m.def("gs_suffix_sum", &gs_suffix_sum);
   m.def("peer_barrier", &peer_barrier, py::arg("flag_ptrs"), py::arg("rank"), py::arg("slot"), py::arg("seq"), py::arg("status"),
         py::arg("timeout_s") = 0.0);
   m.def("memcpy_2d", &memcpy_2d);
-  m.def("owner_reduce_loss", &owner_reduce_loss);
-  m.def("decoder_rows_adam", &decoder_rows_adam);
-  m.def("encoder_rows_adam", &encoder_rows_adam);
-  m.def("dense_adam", &dense_adam);
+  m.def("owner_reduce_loss", &owner_reduce_loss, py::arg("stage"), py::arg("gs_ptrs"), py::arg("rank"), py::arg("bias_sum"), py::arg("addend"),
+        py::arg("target"), py::arg("sigma"), py::arg("yhat_out"), py::arg("sq_err"), py::arg("rows_per_rank"), py::arg("ctl") = none);
+  m.def("decoder_rows_adam", &decoder_rows_adam, py::arg("w"), py::arg("m"), py::arg("v"), py::arg("L"), py::arg("B"), py::arg("d"),
+        py::arg("F_pitch"), py::arg("tying"), py::arg("feat_off"), py::arg("fcsr_tok"), py::arg("fcsr_val"), py::arg("gs"), py::arg("grad_a"),
+        py::arg("pen_coef"), py::arg("norm2_out"), py::arg("feat_offset"), py::arg("feat_scale"), py::arg("dgrad_row0"), py::arg("hyper"),
+        py::arg("status"), py::arg("extra_idx") = none, py::arg("extra_rows") = none, py::arg("ctl") = none, py::arg("norm_only") = false);
+  m.def("encoder_rows_adam", &encoder_rows_adam, py::arg("w"), py::arg("m"), py::arg("v"), py::arg("bias"), py::arg("bias_m"), py::arg("bias_v"),
+        py::arg("feat_off"), py::arg("fcsr_tok"), py::arg("delta"), py::arg("x"), py::arg("dense_grad"), py::arg("dense_bias_grad"),
+        py::arg("hyper"), py::arg("status"), py::arg("extra_idx") = none, py::arg("extra_rows") = none, py::arg("extra_bias") = none,
+        py::arg("ctl") = none, py::arg("norm_only") = false);
+  m.def("dense_adam", &dense_adam, py::arg("w"), py::arg("m"), py::arg("v"), py::arg("grad"), py::arg("hyper"), py::arg("ctl") = none,
+        py::arg("seed_scaled") = false, py::arg("norm_weight") = 0.0);
   m.def("decoder_norm2", &decoder_norm2);
   m.def("sparsity_penalty", &sparsity_penalty);
+  m.def("step_control", &step_control, py::arg("ctl"), py::arg("status"), py::arg("sq_err"), py::arg("scalars"), py::arg("losses"),
+        py::arg("inv_bd"), py::arg("phase") = 0, py::arg("dynamic_scale") = false, py::arg("growth_interval") = 2000, py::arg("max_norm") = 0.0,
+        py::arg("world") = 1, py::arg("rank") = 0, py::arg("ex_data") = std::vector<int64_t>(), py::arg("ex_flags") = std::vector<int64_t>(),
+        py::arg("slot_elems") = 0, py::arg("seq") = 0, py::arg("round") = 14);
+  m.def("decoder_bias_adam", &decoder_bias_adam, py::arg("bias"), py::arg("m"), py::arg("v"), py::arg("sel"), py::arg("gs_sum"), py::arg("extra"),
+        py::arg("hyper"), py::arg("ctl") = none, py::arg("norm_weight") = 0.0);
+  m.def("step_finish", &step_finish, py::arg("counter") = none, py::arg("fired") = none, py::arg("bias") = none, py::arg("sel") = none,
+        py::arg("bias_sum") = none);
+  m.def("theta_adam", &theta_adam, py::arg("log_theta"), py::arg("m"), py::arg("v"), py::arg("theta"), py::arg("S1"), py::arg("S2"),
+        py::arg("norm2"), py::arg("feat_off"), py::arg("fcsr_val"), py::arg("tying"), py::arg("c_g"), py::arg("lambda_"), py::arg("c"),
+        py::arg("bandwidth"), py::arg("hyper"), py::arg("ctl") = none, py::arg("norm_weight") = 0.0, py::arg("grad_out") = none);
+  m.def("theta_exp", &theta_exp);
 }

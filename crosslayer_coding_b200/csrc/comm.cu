@@ -62,11 +62,13 @@ __global__ void peer_barrier_kernel(PeerTable flags, int slot, uint32_t seq, int
 __global__ void __launch_bounds__(256) owner_reduce_loss_kernel(const float* __restrict__ stage, PeerTable gs_peers,
                                                                   const float* __restrict__ bias_sum,
                                                                   const float* __restrict__ addend,
-                                                                  const __nv_bfloat16* __restrict__ target,
+                                                                  const t16* __restrict__ target,
                                                                   const float* __restrict__ sigma, float* __restrict__ yhat_out,
                                                                   double* __restrict__ sq_err, int L, int B, int d,
-                                                                  int rows_per_rank) {
+                                                                  int rows_per_rank, float* __restrict__ ctl) {
   const int t = blockIdx.y;
+  const float loss_scale = ctl != nullptr ? ctl[SC_LOSS_SCALE] : 1.f;
+  bool bad = false;
   const int world = gs_peers.world, rank = gs_peers.rank;
   const int row_base = rank * rows_per_rank;
   const int nrows = max(0, min(rows_per_rank, B - row_base));
@@ -95,16 +97,17 @@ __global__ void __launch_bounds__(256) owner_reduce_loss_kernel(const float* __r
     for (int j = 0; j < 8; ++j) {
       v[j] += bias_sum[1LL * t * d + e0 + j];
       if (addend) v[j] += addend[off + j];
-      const float y = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+      const float y = (j & 1) ? t16_hi(u[j >> 1]) : t16_lo(u[j >> 1]);
       const float sg = sigma ? sigma[1LL * t * d + e0 + j] : 1.f;
       const float r = (v[j] - y) * sg;
       sq = fmaf(r, r, sq);
-      g[j] = r * sg;
+      g[j] = r * sg * loss_scale;
+      bad |= !(fabsf(g[j]) <= kT16Max);
     }
     uint4 gv;
-    gv.x = pack_bf16x2(g[0], g[1]); gv.y = pack_bf16x2(g[2], g[3]); gv.z = pack_bf16x2(g[4], g[5]); gv.w = pack_bf16x2(g[6], g[7]);
+    gv.x = pack_t16x2(g[0], g[1]); gv.y = pack_t16x2(g[2], g[3]); gv.z = pack_t16x2(g[4], g[5]); gv.w = pack_t16x2(g[6], g[7]);
     for (int q = 0; q < world; ++q)  // all-gather by push: the seed rows land in every rank's buffer
-      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(gs_peers.ptr[q]) + off) = gv;
+      *reinterpret_cast<uint4*>(static_cast<t16*>(gs_peers.ptr[q]) + off) = gv;
     if (yhat_out) {
       float4* dst = reinterpret_cast<float4*>(yhat_out + off);
       dst[0] = make_float4(v[0], v[1], v[2], v[3]);
@@ -120,6 +123,7 @@ __global__ void __launch_bounds__(256) owner_reduce_loss_kernel(const float* __r
     for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
     if (tot != 0.f) atomicAdd(&sq_err[t], double(tot));
   }
+  if (bad && ctl != nullptr) atomicOr(reinterpret_cast<int*>(ctl) + SC_FOUND_INF, 1);
 }
 
 }  // namespace clt
@@ -138,6 +142,7 @@ static PeerTable to_table(const CltPeerTable* a) {
   return t;
 }
 
+#if !CLT_T16_IS_HALF
 extern "C" int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int* status, long long timeout_cycles,
                                 cudaStream_t st) {
   if (flags->world <= 1) return 0;
@@ -145,12 +150,14 @@ extern "C" int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned in
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-extern "C" int clt_owner_reduce_loss(const float* stage, const CltPeerTable* gs_peers, const float* bias_sum, const float* addend,
+#endif
+
+extern "C" int CLT_FN(clt_owner_reduce_loss)(const float* stage, const CltPeerTable* gs_peers, const float* bias_sum, const float* addend,
                                      const void* target, const float* sigma, float* yhat_out, double* sq_err, int L, int B, int d,
-                                     int rows_per_rank, cudaStream_t st) {
+                                     int rows_per_rank, float* ctl, cudaStream_t st) {
   if (d % 8 != 0) return -1;
   dim3 grid(148, L);
-  owner_reduce_loss_kernel<<<grid, 256, 0, st>>>(stage, to_table(gs_peers), bias_sum, addend, static_cast<const __nv_bfloat16*>(target),
-                                                 sigma, yhat_out, sq_err, L, B, d, rows_per_rank);
+  owner_reduce_loss_kernel<<<grid, 256, 0, st>>>(stage, to_table(gs_peers), bias_sum, addend, static_cast<const t16*>(target),
+                                                 sigma, yhat_out, sq_err, L, B, d, rows_per_rank, ctl);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

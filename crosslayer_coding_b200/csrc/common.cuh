@@ -7,7 +7,32 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// ---------------------------------------------------------------------------------------------------------
+// 16-bit storage type of weights / activations.  Every translation unit is compiled twice: once for bf16
+// (namespace clt, C symbols clt_*) and once with -DCLT_HALF for fp16 (namespace clt_h, C symbols clt_*_h),
+// through one-line wrapper files that define CLT_HALF and include the .cu file.
+#ifdef CLT_HALF
+#define CLT_NS clt_h
+#define CLT_FN(name) name##_h
+#define CLT_T16_IS_HALF 1
+#else
+#define CLT_NS clt
+#define CLT_FN(name) name
+#define CLT_T16_IS_HALF 0
+#endif
+#define clt CLT_NS
+
 namespace clt {
+
+#if CLT_T16_IS_HALF
+using t16 = __half;
+using t16x2 = __half2;
+constexpr float kT16Max = 65504.f;
+#else
+using t16 = __nv_bfloat16;
+using t16x2 = __nv_bfloat162;
+constexpr float kT16Max = 3.3895313892515355e38f;
+#endif
 
 // Status words written by kernels into a caller-provided int32 buffer.  The host reads
 // them after the step; nothing traps or spins forever.
@@ -232,9 +257,14 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor_sw128(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(2) << 61;                      // layout type: 128-byte swizzle
   return d;
 }
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, tile M x N.
+// Instruction descriptor: 16-bit x 16-bit -> fp32 (operand format 0 = fp16, 1 = bf16), both operands K-major, tile M x N.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+  return (1u << 4) | (static_cast<uint32_t>(CLT_T16_IS_HALF ? 0 : 1) << 7) | (static_cast<uint32_t>(CLT_T16_IS_HALF ? 0 : 1) << 10) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+// Same with the A operand MN-major (bit 15) and / or the B operand MN-major (bit 16).
+__host__ __device__ constexpr uint32_t umma_idesc_t16(int m, int n, int a_mn_major, int b_mn_major) {
+  return umma_idesc_bf16(m, n) | (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16);
 }
 
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
@@ -242,12 +272,45 @@ __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
 }
 
 // ------------------------------------------------------------------- math
+// real bf16 (optimizer moments may be bf16 whatever the weight type is)
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+// the build's 16-bit type
+#if CLT_T16_IS_HALF
+__device__ __forceinline__ uint32_t pack_t16x2(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float t16_lo(uint32_t v) { return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu))); }
+__device__ __forceinline__ float t16_hi(uint32_t v) { return __half2float(__ushort_as_half(static_cast<unsigned short>(v >> 16))); }
+__device__ __forceinline__ float t16_to_float(t16 v) { return __half2float(v); }
+__device__ __forceinline__ t16 float_to_t16(float v) { return __float2half_rn(v); }
+__device__ __forceinline__ t16 float_to_t16_rd(float v) { return __float2half_rd(v); }
+__device__ __forceinline__ t16x2 make_t16x2(t16 a, t16 b) { return __halves2half2(a, b); }
+// 0xFFFF in every half where a >= b (false for NaN)
+__device__ __forceinline__ uint32_t t16x2_ge_mask(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("set.ge.u32.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+#else
+__device__ __forceinline__ uint32_t pack_t16x2(float lo, float hi) { return pack_bf16x2(lo, hi); }
+__device__ __forceinline__ float t16_lo(uint32_t v) { return bf16_lo(v); }
+__device__ __forceinline__ float t16_hi(uint32_t v) { return bf16_hi(v); }
+__device__ __forceinline__ float t16_to_float(t16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ t16 float_to_t16(float v) { return __float2bfloat16_rn(v); }
+__device__ __forceinline__ t16 float_to_t16_rd(float v) { return __float2bfloat16_rd(v); }
+__device__ __forceinline__ t16x2 make_t16x2(t16 a, t16 b) { return __halves2bfloat162(a, b); }
+__device__ __forceinline__ uint32_t t16x2_ge_mask(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("set.ge.u32.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+#endif
 
 // Monotone map float -> uint32 (larger float => larger key); NaN sorts above +inf.
 __device__ __forceinline__ uint32_t float_to_key(float f) {
@@ -263,6 +326,84 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
   return v;
+}
+
+// ------------------------------------------------------------------- step control block
+// 16 32-bit words in device memory that steer the optimizer kernels of a step without a host round trip.
+// step_control_kernel (step.cu) fills it after the loss is known; every Adam kernel reads it.
+enum StepCtl : int {
+  SC_SKIP = 0,          // int: non-zero -> the optimizer kernels return without touching anything
+  SC_INV_SCALE = 1,     // float: 1 / loss scale, multiplies every term derived from the gradient seed
+  SC_LOSS_SCALE = 2,    // float: loss scale the gradient seed of this step is multiplied with (1 unless fp16)
+  SC_GROWTH = 3,        // int: steps since the loss scale last changed
+  SC_FOUND_INF = 4,     // int: set by the loss kernels when the gradient seed left the 16-bit range or is NaN
+  SC_GRAD_NORM_SQ = 5,  // float: squared gradient norm gathered by the norm pre-pass (gradient clipping)
+  SC_CLIP = 6,          // float: clip coefficient, multiplies every row gradient
+  SC_SKIPPED = 7,       // int: number of skipped steps so far
+  SC_SIZE = 16,
+};
+struct StepScales {
+  float inv_scale, clip;
+  bool skip;
+};
+__device__ __forceinline__ StepScales read_step_ctl(const float* ctl) {
+  StepScales s;
+  s.inv_scale = 1.f; s.clip = 1.f; s.skip = false;
+  if (ctl != nullptr) {
+    s.skip = __float_as_int(__ldg(ctl + SC_SKIP)) != 0;
+    s.inv_scale = __ldg(ctl + SC_INV_SCALE);
+    s.clip = __ldg(ctl + SC_CLIP);
+  }
+  return s;
+}
+
+// ------------------------------------------------------------------- cross-rank exchange of small vectors
+constexpr int kMaxPeers = 8;
+// peers[r] points at rank r's exchange area: [rounds][world][slot_elems] uint32 data plus one flag word per
+// (round, source rank).  A round may be used once per launch sequence; `seq` grows with every step.
+struct Exchange {
+  int world;
+  int rank;
+  uint32_t* peers[kMaxPeers];
+  uint32_t* flags[kMaxPeers];
+  int slot_elems;
+  uint32_t seq;
+};
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// All-gather of `n` 32-bit words per rank (one CTA): every rank stores its words into slot [round][rank] of every
+// peer, raises flag [round][rank] there and waits (bounded) for all peers' flags in its own area.  Afterwards rank
+// q's words are at exchange_slot(ex, round, q).  Returns false on a timeout.  Because every rank waits for every
+// other rank's flag, the call is also a barrier: all device work that a rank completed before its call (earlier
+// kernels of the stream included) is visible to the ranks that return from theirs.
+__device__ __forceinline__ const uint32_t* exchange_slot(const Exchange& ex, int round, int q) {
+  return ex.peers[ex.rank] + (size_t(round) * ex.world + q) * ex.slot_elems;
+}
+__device__ __forceinline__ bool exchange_gather(const Exchange& ex, int round, const uint32_t* vals, int n, int* timeout_flag_smem) {
+  if (ex.world <= 1) return true;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  for (int p = 0; p < ex.world; ++p) {
+    uint32_t* dst = ex.peers[p] + (size_t(round) * ex.world + ex.rank) * ex.slot_elems;
+    for (int i = tid; i < n; i += nt) dst[i] = vals[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < ex.world) st_release_sys(ex.flags[tid] + size_t(round) * ex.world + ex.rank, ex.seq);
+  if (tid < ex.world) {
+    const uint32_t* f = ex.flags[ex.rank] + size_t(round) * ex.world + tid;
+    const long long start = clock64();
+    while (ld_acquire_sys(f) != ex.seq) {
+      if (clock64() - start > kWaitTimeoutCycles) { *timeout_flag_smem = 1; break; }
+    }
+  }
+  __syncthreads();
+  return *timeout_flag_smem == 0;
 }
 
 }  // namespace clt

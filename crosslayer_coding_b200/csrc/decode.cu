@@ -16,7 +16,7 @@ namespace clt {
 constexpr int kMaxLayers = 32;
 
 struct DecodeParams {
-  const __nv_bfloat16* w[kMaxLayers];  // decoder tensor i: [F_pitch, rows_i, d]
+  const t16* w[kMaxLayers];  // decoder tensor i: [F_pitch, rows_i, d]
   int rows[kMaxLayers];                // rows per feature of tensor i
   int L, B, d;
   int col_pitch;                       // entries encode column = layer * col_pitch + feature
@@ -30,9 +30,9 @@ struct DecodeParams {
   float* yhat_partial;                 // mode 0: [L, B, d] fp32 partial sums
   const float* bias_sum;               // mode 1: [L, d] summed decoder biases per target
   const float* addend;                 // mode 1: optional [L, B, d] fp32 (skip term)
-  const __nv_bfloat16* target;         // mode 1: [L, B, d]
+  const t16* target;         // mode 1: [L, B, d]
   const float* sigma;                  // mode 1: optional [L, d] de-normalisation scale of the targets
-  __nv_bfloat16* gs;                   // mode 1: [L, B, d] (y_hat - y) * sigma^2
+  t16* gs;                   // mode 1: [L, B, d] (y_hat - y) * sigma^2
   float* yhat_out;                     // mode 1: optional [L, B, d] fp32 reconstruction
   double* sq_err;                      // mode 1: [L] sum of ((y_hat - y) * sigma)^2
   // mode 2 (tensor parallel): partial sums are pushed into the staging area of the rank that owns the token.
@@ -40,14 +40,18 @@ struct DecodeParams {
   float* stage_peers[8];
   int rows_per_rank, rank, world;
   int mode;
+  // optional step control block: the gradient seed is multiplied by ctl[SC_LOSS_SCALE] (fp16 loss scaling) and a
+  // seed that leaves the 16-bit range or is NaN raises ctl[SC_FOUND_INF] (the step is then skipped)
+  float* ctl;
+  int rows_limit;  // > 0: only the first rows_limit target rows of a feature are decoded (auxiliary loss: same layer only)
 };
 
 __device__ __forceinline__ void fma8(float (&acc)[8], float a, const uint4& v) {
   const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    acc[2 * j] = fmaf(a, bf16_lo(u[j]), acc[2 * j]);
-    acc[2 * j + 1] = fmaf(a, bf16_hi(u[j]), acc[2 * j + 1]);
+    acc[2 * j] = fmaf(a, t16_lo(u[j]), acc[2 * j]);
+    acc[2 * j + 1] = fmaf(a, t16_hi(u[j]), acc[2 * j + 1]);
   }
 }
 
@@ -55,7 +59,7 @@ __device__ __forceinline__ void fma8(float (&acc)[8], float a, const uint4& v) {
 // loss epilogue (mode 1).  Returns the slice's squared error (mode 1, else 0); the callers sum it in registers and
 // across the warp: a shared-memory atomic per thread on the L per-target sums costs tens of thousands of cycles
 // per token (32 lanes on one address, floating-point add as a compare-and-swap loop).
-__device__ __forceinline__ float decode_epilogue(const DecodeParams& p, int tok, int t, int e0, const float (&a)[8]) {
+__device__ __forceinline__ float decode_epilogue(const DecodeParams& p, int tok, int t, int e0, const float (&a)[8], float loss_scale) {
   const long long off = (1LL * t * p.B + tok) * p.d + e0;
   if (p.mode == 0) {
     float4* dst = reinterpret_cast<float4*>(p.yhat_partial + off);
@@ -75,8 +79,9 @@ __device__ __forceinline__ float decode_epilogue(const DecodeParams& p, int tok,
     const uint4 tv = *reinterpret_cast<const uint4*>(p.target + off);
     const uint32_t u[4] = {tv.x, tv.y, tv.z, tv.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { y[2 * i] = bf16_lo(u[i]); y[2 * i + 1] = bf16_hi(u[i]); }
+    for (int i = 0; i < 4; ++i) { y[2 * i] = t16_lo(u[i]); y[2 * i + 1] = t16_hi(u[i]); }
     float sq = 0.f;
+    bool bad = false;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       float v = a[i] + p.bias_sum[1LL * t * p.d + e0 + i];
@@ -85,11 +90,13 @@ __device__ __forceinline__ float decode_epilogue(const DecodeParams& p, int tok,
       out[i] = v;
       const float r = (v - y[i]) * sg;
       sq = fmaf(r, r, sq);
-      y[i] = r * sg;  // gradient seed
+      y[i] = r * sg * loss_scale;  // gradient seed
+      bad |= !(fabsf(y[i]) <= kT16Max);
     }
+    if (bad && p.ctl != nullptr) atomicOr(reinterpret_cast<int*>(p.ctl) + SC_FOUND_INF, 1);
     uint4 gv;
-    gv.x = pack_bf16x2(y[0], y[1]); gv.y = pack_bf16x2(y[2], y[3]);
-    gv.z = pack_bf16x2(y[4], y[5]); gv.w = pack_bf16x2(y[6], y[7]);
+    gv.x = pack_t16x2(y[0], y[1]); gv.y = pack_t16x2(y[2], y[3]);
+    gv.z = pack_t16x2(y[4], y[5]); gv.w = pack_t16x2(y[6], y[7]);
     *reinterpret_cast<uint4*>(p.gs + off) = gv;
     if (p.yhat_out) {
       float4* dst = reinterpret_cast<float4*>(p.yhat_out + off);
@@ -122,7 +129,7 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
   __shared__ float sq_s[kMaxLayers];
-  __shared__ const __nv_bfloat16* w_s[kMaxLayers];  // parameter tables in shared memory: indexed per entry
+  __shared__ const t16* w_s[kMaxLayers];  // parameter tables in shared memory: indexed per entry
   __shared__ int rows_s[kMaxLayers];
   if (threadIdx.x < kMaxLayers) {
     sq_s[threadIdx.x] = 0.f;
@@ -131,6 +138,8 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
   }
   __syncthreads();
   const int L = p.L, d = p.d, tying = p.tying;
+  const float loss_scale = p.ctl != nullptr ? p.ctl[SC_LOSS_SCALE] : 1.f;
+  const int t_span = p.rows_limit > 0 ? p.rows_limit : kMaxLayers;  // targets s .. s + t_span - 1 of a source layer s
 
   const int b = p.tok_off[tok], e = p.tok_off[tok + 1];
   if (active) {
@@ -142,18 +151,18 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
       if (a == 0.f) continue;
       if (tying == 0) {
         // row (t - s) of feature f; rows of one feature are contiguous
-        const __nv_bfloat16* base = w_s[s] + (1LL * f * rows_s[s] - s) * d + e0;
+        const t16* base = w_s[s] + (1LL * f * rows_s[s] - s) * d + e0;
 #pragma unroll
         for (int j = 0; j < TPG; ++j) {
           const int t = g + (blockIdx.y * TPG + j) * kGroups;
-          if (t < L && t >= s) fma8(acc[j], a, __ldg(reinterpret_cast<const uint4*>(base + 1LL * t * d)));
+          if (t < L && t >= s && t - s < t_span) fma8(acc[j], a, __ldg(reinterpret_cast<const uint4*>(base + 1LL * t * d)));
         }
       } else if (tying == 1) {
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(w_s[s] + 1LL * f * d + e0));
 #pragma unroll
         for (int j = 0; j < TPG; ++j) {
           const int t = g + (blockIdx.y * TPG + j) * kGroups;
-          if (t < p.L && t >= s) {
+          if (t < p.L && t >= s && t - s < t_span) {
             float av = a;
             if (p.feat_offset) av += p.feat_offset[1LL * t * p.col_pitch + f];
             if (p.feat_scale) av *= p.feat_scale[1LL * t * p.col_pitch + f];
@@ -164,7 +173,7 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
 #pragma unroll
         for (int j = 0; j < TPG; ++j) {
           const int t = g + (blockIdx.y * TPG + j) * kGroups;
-          if (t < p.L && t >= s) {
+          if (t < p.L && t >= s && t - s < t_span) {
             float av = a;
             if (p.feat_offset) av += p.feat_offset[1LL * t * p.col_pitch + f];
             if (p.feat_scale) av *= p.feat_scale[1LL * t * p.col_pitch + f];
@@ -179,7 +188,7 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
   for (int j = 0; j < TPG; ++j) {
     const int t = g + (blockIdx.y * TPG + j) * kGroups;  // the same for all lanes of a warp (gthreads is a multiple of 32)
     if (t >= p.L) continue;
-    float sq = active ? decode_epilogue(p, tok, t, e0, acc[j]) : 0.f;
+    float sq = active ? decode_epilogue(p, tok, t, e0, acc[j], loss_scale) : 0.f;
     if (p.mode == 1) {
       sq = warp_sum(sq);
       if ((threadIdx.x & 31) == 0) atomicAdd(&sq_s[t], sq);
@@ -202,7 +211,7 @@ struct DecodeBulkShared {
   uint64_t full[kDecodeStages];
   uint64_t empty[kDecodeStages];
   float sq_s[kMaxLayers];
-  const __nv_bfloat16* w_s[kMaxLayers];
+  const t16* w_s[kMaxLayers];
   int rows_s[kMaxLayers];
   int abort_flag;
   int ent_sl[kDecodeStages];    // source layer and activation of the entry in each stage, written by the producer
@@ -236,6 +245,7 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   __syncthreads();
   volatile int* abort_flag = &sh->abort_flag;
   const int b = p.tok_off[tok], e = p.tok_off[tok + 1];
+  const float loss_scale = p.ctl != nullptr ? p.ctl[SC_LOSS_SCALE] : 1.f;
 
   if (is_producer) {
     if (threadIdx.x == nconsumer) {
@@ -254,7 +264,8 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
         if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) break;
         const int sl = col >> 24, f = col & 0xFFFFFF;
         const int R = sh->rows_s[sl];
-        const uint32_t bytes = uint32_t(R) * uint32_t(d) * 2u;
+        const int r_eff = (p.rows_limit > 0 && p.rows_limit < R) ? p.rows_limit : R;
+        const uint32_t bytes = uint32_t(r_eff) * uint32_t(d) * 2u;
         sh->ent_sl[st] = sl;
         sh->ent_a[st] = a;
         mbar_expect_tx(&sh->full[st], bytes);  // release: the two words above are visible to whoever sees the phase
@@ -283,6 +294,7 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
       for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
     int it = 0;
     bool ok = true;
+    const int t_span = p.rows_limit > 0 ? p.rows_limit : kMaxLayers;
     for (int i = b; i < e; ++i, ++it) {
       const int st = it % kDecodeStages;
       const uint32_t ph = (it / kDecodeStages) & 1;
@@ -290,11 +302,11 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
       const int sl = sh->ent_sl[st];
       const float a = sh->ent_a[st];
       if (active && a != 0.f) {
-        const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(ring + size_t(st) * stage_bytes) + e0;
+        const t16* rows = reinterpret_cast<const t16*>(ring + size_t(st) * stage_bytes) + e0;
 #pragma unroll
         for (int j = 0; j < TPG; ++j) {
           const int t = g + (blockIdx.y * TPG + j) * kGroups;
-          if (t < L && t >= sl) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (t - sl) * d));
+          if (t < L && t >= sl && t - sl < t_span) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (t - sl) * d));
         }
       }
       __syncwarp();
@@ -305,7 +317,7 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
     for (int j = 0; j < TPG; ++j) {
       const int t = g + (blockIdx.y * TPG + j) * kGroups;
       if (t >= L) continue;
-      float sq = (ok && active) ? decode_epilogue(p, tok, t, e0, acc[j]) : 0.f;
+      float sq = (ok && active) ? decode_epilogue(p, tok, t, e0, acc[j], loss_scale) : 0.f;
       if (p.mode == 1) {
         sq = warp_sum(sq);
         if (lane == 0) atomicAdd(&sh->sq_s[t], sq);
@@ -320,11 +332,13 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
 // Epilogue for the tensor-parallel path, run after the partial reconstructions were summed across ranks:
 // bias, addend, residual, loss sum and gradient seed for rows [row0, row0 + nrows) of every layer.
 __global__ void __launch_bounds__(256) recon_epilogue_kernel(const float* __restrict__ yhat_sum, const float* __restrict__ bias_sum,
-                                                               const float* __restrict__ addend, const __nv_bfloat16* __restrict__ target,
-                                                               const float* __restrict__ sigma, __nv_bfloat16* __restrict__ gs,
+                                                               const float* __restrict__ addend, const t16* __restrict__ target,
+                                                               const float* __restrict__ sigma, t16* __restrict__ gs,
                                                                float* __restrict__ yhat_out, double* __restrict__ sq_err, int L, int B,
-                                                               int d, int row0, int nrows) {
+                                                               int d, int row0, int nrows, float* __restrict__ ctl) {
   const int t = blockIdx.y;
+  const float loss_scale = ctl != nullptr ? ctl[SC_LOSS_SCALE] : 1.f;
+  bool bad = false;
   const int vec_per_row = d / 8;
   const long long nvec = 1LL * nrows * vec_per_row;
   float sq = 0.f;
@@ -341,14 +355,15 @@ __global__ void __launch_bounds__(256) recon_epilogue_kernel(const float* __rest
     for (int j = 0; j < 8; ++j) {
       v[j] += bias_sum[1LL * t * d + e0 + j];
       if (addend) v[j] += addend[off + j];
-      const float y = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+      const float y = (j & 1) ? t16_hi(u[j >> 1]) : t16_lo(u[j >> 1]);
       const float sg = sigma ? sigma[1LL * t * d + e0 + j] : 1.f;
       const float r = (v[j] - y) * sg;
       sq = fmaf(r, r, sq);
-      g[j] = r * sg;
+      g[j] = r * sg * loss_scale;
+      bad |= !(fabsf(g[j]) <= kT16Max);
     }
     uint4 gv;
-    gv.x = pack_bf16x2(g[0], g[1]); gv.y = pack_bf16x2(g[2], g[3]); gv.z = pack_bf16x2(g[4], g[5]); gv.w = pack_bf16x2(g[6], g[7]);
+    gv.x = pack_t16x2(g[0], g[1]); gv.y = pack_t16x2(g[2], g[3]); gv.z = pack_t16x2(g[4], g[5]); gv.w = pack_t16x2(g[6], g[7]);
     *reinterpret_cast<uint4*>(gs + off) = gv;
     if (yhat_out) {
       float4* dst = reinterpret_cast<float4*>(yhat_out + off);
@@ -365,18 +380,60 @@ __global__ void __launch_bounds__(256) recon_epilogue_kernel(const float* __rest
     for (int w = 0; w < (blockDim.x >> 5); ++w) tot += red[w];
     atomicAdd(&sq_err[t], double(tot));
   }
+  if (bad && ctl != nullptr) atomicOr(reinterpret_cast<int*>(ctl) + SC_FOUND_INF, 1);
 }
 
-// Column sums of the gradient seed: out[t, :] = sum_b gs[t, b, :]  (decoder-bias gradient up to a constant).
-__global__ void __launch_bounds__(256) gs_colsum_kernel(const __nv_bfloat16* __restrict__ gs, float* __restrict__ out, int B, int d,
+// Column sums of the gradient seed: out[t, :] += sum_b gs[t, b, :]  (decoder-bias gradient up to a constant).
+// blockDim = (d / 8 rounded up to 32, 256 / that): a thread owns 8 adjacent columns (one 16-byte load per row), the
+// threadIdx.y rows of a block walk the block's row range, shared memory folds them, one atomic per column and block.
+__global__ void __launch_bounds__(256) gs_colsum_kernel(const t16* __restrict__ gs, float* __restrict__ out, int B, int d,
                                                           int rows_per_block) {
   const int t = blockIdx.z;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   const int r0 = blockIdx.y * rows_per_block, r1 = min(B, r0 + rows_per_block);
-  float s = 0.f;
-  for (int r = r0; r < r1; ++r) s += __bfloat162float(gs[(1LL * t * B + r) * d + c]);
-  atomicAdd(&out[1LL * t * d + c], s);
+  float s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = 0.f;
+  if (c0 < d) {
+    for (int r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(gs + (1LL * t * B + r) * d + c0));
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { s[2 * j] += t16_lo(u[j]); s[2 * j + 1] += t16_hi(u[j]); }
+    }
+  }
+  __shared__ float red[256][9];
+  const int lin = threadIdx.y * blockDim.x + threadIdx.x;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[lin][j] = s[j];
+  __syncthreads();
+  if (threadIdx.y == 0 && c0 < d) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float tot = 0.f;
+      for (int y = 0; y < int(blockDim.y); ++y) tot += red[y * blockDim.x + threadIdx.x][j];
+      atomicAdd(&out[1LL * t * d + c0 + j], tot);
+    }
+  }
+}
+
+// Suffix sums of the gradient seed over the layers: out[s] = sum over t >= s of gs[t]  (per_source tied decoders:
+// the threshold-gradient GEMM of source layer s needs the seed of all its targets added up).  fp32 accumulation.
+__global__ void __launch_bounds__(256) gs_suffix_sum_kernel(const t16* __restrict__ gs, t16* __restrict__ out, int L, long long per_layer) {
+  for (long long i = (blockIdx.x * 1LL * blockDim.x + threadIdx.x) * 8; i < per_layer; i += 1LL * gridDim.x * blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int t = L - 1; t >= 0; --t) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(gs + t * per_layer + i));
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { acc[2 * j] += t16_lo(u[j]); acc[2 * j + 1] += t16_hi(u[j]); }
+      uint4 o;
+      o.x = pack_t16x2(acc[0], acc[1]); o.y = pack_t16x2(acc[2], acc[3]); o.z = pack_t16x2(acc[4], acc[5]); o.w = pack_t16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out + t * per_layer + i) = o;
+    }
+  }
 }
 
 }  // namespace clt
@@ -396,20 +453,23 @@ struct CltDecodeArgs {
   int rows_per_rank, rank, world;
   int mode;
   int* status;  // when given, untied decoders use the bulk-copy pipeline (its bounded waits report here)
+  float* ctl;   // optional step control block (loss scale in, found-inf flag out)
+  int rows_limit;
 };
 
-extern "C" int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st) {
+extern "C" int CLT_FN(clt_sparse_decode)(const CltDecodeArgs* a, cudaStream_t st) {
   if (a->d % 8 != 0 || a->L > kMaxLayers || a->d > 2048) return -1;
   DecodeParams p;
-  for (int i = 0; i < kMaxLayers; ++i) { p.w[i] = static_cast<const __nv_bfloat16*>(a->w[i]); p.rows[i] = a->rows[i]; }
+  for (int i = 0; i < kMaxLayers; ++i) { p.w[i] = static_cast<const t16*>(a->w[i]); p.rows[i] = a->rows[i]; }
   p.L = a->L; p.B = a->B; p.d = a->d; p.col_pitch = a->col_pitch; p.tying = a->tying;
   p.tok_off = a->tok_off; p.tcsr_col = a->tcsr_col; p.tcsr_val = a->tcsr_val;
   p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale;
   p.yhat_partial = a->yhat_partial; p.bias_sum = a->bias_sum; p.addend = a->addend;
-  p.target = static_cast<const __nv_bfloat16*>(a->target); p.sigma = a->sigma;
-  p.gs = static_cast<__nv_bfloat16*>(a->gs); p.yhat_out = a->yhat_out; p.sq_err = a->sq_err; p.mode = a->mode;
+  p.target = static_cast<const t16*>(a->target); p.sigma = a->sigma;
+  p.gs = static_cast<t16*>(a->gs); p.yhat_out = a->yhat_out; p.sq_err = a->sq_err; p.mode = a->mode;
   for (int i = 0; i < 8; ++i) p.stage_peers[i] = static_cast<float*>(a->stage_peers[i]);
   p.rows_per_rank = a->rows_per_rank; p.rank = a->rank; p.world = a->world;
+  p.ctl = a->ctl; p.rows_limit = a->rows_limit;
   const int gthreads = ((a->d / 8 + 31) / 32) * 32;
   const int threads = gthreads * kGroups;
   if (threads > 1024) return -1;
@@ -442,20 +502,32 @@ extern "C" int clt_sparse_decode(const CltDecodeArgs* a, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-extern "C" int clt_recon_epilogue(const float* yhat_sum, const float* bias_sum, const float* addend, const void* target,
+extern "C" int CLT_FN(clt_recon_epilogue)(const float* yhat_sum, const float* bias_sum, const float* addend, const void* target,
                                   const float* sigma, void* gs, float* yhat_out, double* sq_err, int L, int B, int d, int row0,
-                                  int nrows, cudaStream_t st) {
+                                  int nrows, float* ctl, cudaStream_t st) {
   if (d % 8 != 0) return -1;
   if (nrows <= 0) return 0;
   dim3 grid(148, L);
-  recon_epilogue_kernel<<<grid, 256, 0, st>>>(yhat_sum, bias_sum, addend, static_cast<const __nv_bfloat16*>(target), sigma,
-                                              static_cast<__nv_bfloat16*>(gs), yhat_out, sq_err, L, B, d, row0, nrows);
+  recon_epilogue_kernel<<<grid, 256, 0, st>>>(yhat_sum, bias_sum, addend, static_cast<const t16*>(target), sigma,
+                                              static_cast<t16*>(gs), yhat_out, sq_err, L, B, d, row0, nrows, ctl);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-extern "C" int clt_gs_colsum(const void* gs, float* out, int L, int B, int d, cudaStream_t st) {
-  const int rpb = 128;
-  dim3 grid((d + 255) / 256, (B + rpb - 1) / rpb, L);
-  gs_colsum_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gs), out, B, d, rpb);
+extern "C" int CLT_FN(clt_gs_colsum)(const void* gs, float* out, int L, int B, int d, cudaStream_t st) {
+  if (d % 8 != 0) return -1;
+  const int tx = d / 8 >= 256 ? 256 : ((d / 8 + 31) / 32) * 32;
+  const int ty = 256 / tx;
+  const int rpb = 256;
+  dim3 grid((d / 8 + tx - 1) / tx, (B + rpb - 1) / rpb, L), block(tx, ty);
+  gs_colsum_kernel<<<grid, block, 0, st>>>(static_cast<const t16*>(gs), out, B, d, rpb);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int CLT_FN(clt_gs_suffix_sum)(const void* gs, void* out, int L, int B, int d, cudaStream_t st) {
+  const long long per_layer = 1LL * B * d;
+  if (per_layer % 8 != 0) return -1;
+  const long long nvec = per_layer / 8;
+  const int grid = int(nvec / 256 + 1 < 1184 ? nvec / 256 + 1 : 1184);
+  gs_suffix_sum_kernel<<<grid, 256, 0, st>>>(static_cast<const t16*>(gs), static_cast<t16*>(out), L, per_layer);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

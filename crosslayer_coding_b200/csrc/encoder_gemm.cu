@@ -58,10 +58,10 @@ __device__ __forceinline__ void epilogue_slab(uint32_t taddr, const CUtensorMap*
       const uint32_t* r = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
       const float4 ba = b4[2 * j], bb = b4[2 * j + 1];
       uint4 q;
-      q.x = pack_bf16x2(__uint_as_float(r[0]) + ba.x, __uint_as_float(r[1]) + ba.y);
-      q.y = pack_bf16x2(__uint_as_float(r[2]) + ba.z, __uint_as_float(r[3]) + ba.w);
-      q.z = pack_bf16x2(__uint_as_float(r[4]) + bb.x, __uint_as_float(r[5]) + bb.y);
-      q.w = pack_bf16x2(__uint_as_float(r[6]) + bb.z, __uint_as_float(r[7]) + bb.w);
+      q.x = pack_t16x2(__uint_as_float(r[0]) + ba.x, __uint_as_float(r[1]) + ba.y);
+      q.y = pack_t16x2(__uint_as_float(r[2]) + ba.z, __uint_as_float(r[3]) + ba.w);
+      q.z = pack_t16x2(__uint_as_float(r[4]) + bb.x, __uint_as_float(r[5]) + bb.y);
+      q.w = pack_t16x2(__uint_as_float(r[6]) + bb.z, __uint_as_float(r[7]) + bb.w);
       *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = q;
     }
     fence_proxy_async();
@@ -77,7 +77,7 @@ __device__ __forceinline__ void epilogue_slab(uint32_t taddr, const CUtensorMap*
       for (int r = 0; r < 32; ++r) {
         if (r < nrows) {
           const uint32_t u = *reinterpret_cast<const uint32_t*>(stage + r * 128 + ((chunk ^ uint32_t(r & 7)) << 4) + inner);
-          const float a = bf16_lo(u), b = bf16_hi(u);
+          const float a = t16_lo(u), b = t16_hi(u);
           s0 += a; q0 = fmaf(a, a, q0);
           s1 += b; q1 = fmaf(b, b, q1);
         }
@@ -117,7 +117,7 @@ struct GemmShared {
 
 __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)
 encoder_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ CUtensorMap map_c, const __nv_bfloat16* __restrict__ bias,
+                    const __grid_constant__ CUtensorMap map_c, const t16* __restrict__ bias,
                     int L, int M, int N, int K, long long ldc, long long layer_stride_c, int* __restrict__ status,
                     float* __restrict__ tile_stats) {
   using namespace gemm;
@@ -241,7 +241,7 @@ encoder_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       prev_l = l; prev_rb = mt; prev_n = nt * BN;
       for (int j = etid; j < BN; j += 128) {
         const int n = nt * BN + j;
-        sh->bias[j] = (bias != nullptr && n < N) ? __bfloat162float(bias[1LL * l * N + n]) : 0.f;
+        sh->bias[j] = (bias != nullptr && n < N) ? t16_to_float(bias[1LL * l * N + n]) : 0.f;
       }
       // One thread performs the bounded wait and publishes the outcome, so the four warps always
       // take the same branch and nobody is left alone at a named barrier.
@@ -313,7 +313,7 @@ struct GemmPairShared {
 
 __global__ void __launch_bounds__(gemm2::NUM_THREADS, 1)
 encoder_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const __grid_constant__ CUtensorMap map_c, const __nv_bfloat16* __restrict__ bias,
+                         const __grid_constant__ CUtensorMap map_c, const t16* __restrict__ bias,
                          int L, int M, int N, int K, long long ldc, long long layer_stride_c, int* __restrict__ status,
                          float* __restrict__ tile_stats) {
   using namespace gemm2;
@@ -431,7 +431,7 @@ encoder_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       prev_l = l; prev_rb = mt * 2 + int(cta_rank); prev_n = nt * BN;
       for (int j = etid; j < BN; j += 128) {
         const int n = nt * BN + j;
-        sh->bias[j] = (bias != nullptr && n < N) ? __bfloat162float(bias[1LL * l * N + n]) : 0.f;
+        sh->bias[j] = (bias != nullptr && n < N) ? t16_to_float(bias[1LL * l * N + n]) : 0.f;
       }
       if (etid == 0) sh->epi_ok = mbar_wait(&sh->tmem_full[buf], tph, abort_flag) ? 1 : 0;
       named_barrier_sync(1, 128);
@@ -487,7 +487,7 @@ static bool make_kmajor_map(CUtensorMap* map, const void* base, int layers, int 
   cuuint64_t strides[2] = {cuuint64_t(row_stride_elems) * 2, cuuint64_t(layer_stride_elems) * 2};
   cuuint32_t box[3] = {cuuint32_t(gemm::BK), cuuint32_t(box_rows), 1};
   cuuint32_t elem[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+  CUresult r = enc(map, (CLT_T16_IS_HALF ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16), 3, const_cast<void*>(base), dims, strides, box, elem,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -498,7 +498,7 @@ static bool make_kmajor_map(CUtensorMap* map, const void* base, int layers, int 
 // Returns 0 on success, a negative value when the arguments cannot be handled (the caller raises).
 // tile_stats (optional): [L][ceil(M / 128)][N][2] fp32, receives per 128-row block and column the sum and the sum of
 // squares of the stored (bf16-rounded) outputs; every element is written, nothing has to be cleared.
-extern "C" int clt_encoder_gemm(const void* A, const void* B, const void* bias, void* C, int L, int M, int N, int K,
+extern "C" int CLT_FN(clt_encoder_gemm)(const void* A, const void* B, const void* bias, void* C, int L, int M, int N, int K,
                                 long long ldc, long long layer_stride_c, int* status, float* tile_stats, int num_sms, cudaStream_t stream) {
   using namespace clt;
   if (K % 8 != 0 || ldc % 8 != 0 || layer_stride_c % 8 != 0) return -1;  // 16-byte TMA strides / vector stores
@@ -544,7 +544,7 @@ extern "C" int clt_encoder_gemm(const void* A, const void* B, const void* bias, 
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const __nv_bfloat16* bias_p = static_cast<const __nv_bfloat16*>(bias);
+    const t16* bias_p = static_cast<const t16*>(bias);
     if (cudaLaunchKernelEx(&cfg, encoder_gemm_pair_kernel, map_a, map_b, map_c, bias_p, L, M, N, K, ldc, layer_stride_c, status, tile_stats) != cudaSuccess)
       return -5;
     return 0;
@@ -559,6 +559,6 @@ extern "C" int clt_encoder_gemm(const void* A, const void* B, const void* bias, 
   if (tiles == 0) return 0;
   const int grid = int(tiles < num_sms ? tiles : num_sms);
   encoder_gemm_kernel<<<grid, gemm::NUM_THREADS, gemm::SMEM_BYTES, stream>>>(
-      map_a, map_b, map_c, static_cast<const __nv_bfloat16*>(bias), L, M, N, K, ldc, layer_stride_c, status, tile_stats);
+      map_a, map_b, map_c, static_cast<const t16*>(bias), L, M, N, K, ldc, layer_stride_c, status, tile_stats);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -1,0 +1,3 @@
+// fp16 build of adam.cu (namespace clt_h, C symbols with the suffix _h)
+#define CLT_HALF 1
+#include "../adam.cu"

@@ -22,7 +22,6 @@ namespace clt {
 
 constexpr int kHistBins = 8192;
 constexpr int kRefineBins = 512;
-constexpr int kMaxPeers = 8;
 
 // Control block shared by the selection kernels (device memory, int64 slots).
 enum SelCtl : int {
@@ -40,50 +39,14 @@ enum SelCtl : int {
   CTL_SIZE = 16,
 };
 
-// Exchange area for the cross-rank histogram sums.  peers[r] points at rank r's area; each area holds
-// world slots of `slot_elems` uint32 per round plus one flag word per (round, source rank).
-struct Exchange {
-  int world;
-  int rank;
-  uint32_t* peers[kMaxPeers];   // data: [rounds][world][slot_elems]
-  uint32_t* flags[kMaxPeers];   // flags: [rounds][world]
-  int slot_elems;
-  uint32_t seq;                 // value a flag takes in this launch (monotone over launches)
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
 // Sum `n` uint32 counters over all ranks, in place in shared memory `vals` (one CTA).  Every rank stores
 // its vector into slot [round][rank] of every peer, raises flag [round][rank] there, then waits (bounded)
 // for the flags of all peers in its own area and adds the slots up.  Returns false on a timeout.
 __device__ bool exchange_sum(const Exchange& ex, int round, uint32_t* vals, int n, int* timeout_flag_smem) {
   if (ex.world <= 1) return true;
-  const int tid = threadIdx.x, nt = blockDim.x;
-  for (int p = 0; p < ex.world; ++p) {
-    uint32_t* dst = ex.peers[p] + (size_t(round) * ex.world + ex.rank) * ex.slot_elems;
-    for (int i = tid; i < n; i += nt) dst[i] = vals[i];
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (tid < ex.world) st_release_sys(ex.flags[tid] + size_t(round) * ex.world + ex.rank, ex.seq);
-  if (tid < ex.world) {
-    const uint32_t* f = ex.flags[ex.rank] + size_t(round) * ex.world + tid;
-    const long long start = clock64();
-    while (ld_acquire_sys(f) != ex.seq) {
-      if (clock64() - start > kWaitTimeoutCycles) { *timeout_flag_smem = 1; break; }
-    }
-  }
-  __syncthreads();
-  if (*timeout_flag_smem) return false;
-  const uint32_t* mine = ex.peers[ex.rank] + size_t(round) * ex.world * ex.slot_elems;
-  for (int i = tid; i < n; i += nt) {
+  if (!exchange_gather(ex, round, vals, n, timeout_flag_smem)) return false;
+  const uint32_t* mine = exchange_slot(ex, round, 0);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
     uint32_t s = 0;
     for (int p = 0; p < ex.world; ++p) s += mine[size_t(p) * ex.slot_elems + i];
     vals[i] = s;
@@ -97,7 +60,7 @@ __device__ bool exchange_sum(const Exchange& ex, int round, uint32_t* vals, int 
 // With gridDim.z > 1 (narrow shards, where one CTA per column block would leave SMs idle) the rows are split
 // over blockIdx.z: the shifted sums are additive because every chunk shifts by the column's first row, so the
 // chunks add them into mean / rstd (zeroed by the launcher) and colstats_finalize_kernel converts in place.
-__global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ mean,
+__global__ void __launch_bounds__(256) colstats_kernel(const t16* __restrict__ x, float* __restrict__ mean,
                                                          float* __restrict__ rstd, int B, int F, long long ld,
                                                          long long layer_stride) {
   const int l = blockIdx.y;
@@ -111,12 +74,12 @@ __global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __re
 #pragma unroll
   for (int j = 0; j < 8; ++j) s[j] = q[j] = shift[j] = 0.f;
   const bool active = c0 < F;
-  const __nv_bfloat16* base = x + 1LL * l * layer_stride + c0;
+  const t16* base = x + 1LL * l * layer_stride + c0;
   if (active) {
     uint4 v0 = *reinterpret_cast<const uint4*>(base);
     const uint32_t w[4] = {v0.x, v0.y, v0.z, v0.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { shift[2 * j] = bf16_lo(w[j]); shift[2 * j + 1] = bf16_hi(w[j]); }
+    for (int j = 0; j < 4; ++j) { shift[2 * j] = t16_lo(w[j]); shift[2 * j + 1] = t16_hi(w[j]); }
     for (int r0 = row_lo + threadIdx.y; r0 < row_hi; r0 += 32) {
       uint4 v[4];
 #pragma unroll
@@ -130,7 +93,7 @@ __global__ void __launch_bounds__(256) colstats_kernel(const __nv_bfloat16* __re
         const uint32_t u[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float a = bf16_lo(u[j]) - shift[2 * j], b = bf16_hi(u[j]) - shift[2 * j + 1];
+          const float a = t16_lo(u[j]) - shift[2 * j], b = t16_hi(u[j]) - shift[2 * j + 1];
           s[2 * j] += a; q[2 * j] += a * a;
           s[2 * j + 1] += b; q[2 * j + 1] += b * b;
         }
@@ -187,13 +150,13 @@ __global__ void __launch_bounds__(256) colstats_from_tiles_kernel(const float* _
 }
 
 // mean / rstd hold the shifted sum and sum of squares (shift = the column's first row); convert in place.
-__global__ void __launch_bounds__(256) colstats_finalize_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ mean,
+__global__ void __launch_bounds__(256) colstats_finalize_kernel(const t16* __restrict__ x, float* __restrict__ mean,
                                                                   float* __restrict__ rstd, int B, int F, long long layer_stride,
                                                                   long long n) {
   const long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int l = int(i / F), c = int(i - 1LL * l * F);
-  const float shift = __bfloat162float(x[1LL * l * layer_stride + c]);
+  const float shift = t16_to_float(x[1LL * l * layer_stride + c]);
   const float ss = mean[i], qq = rstd[i];
   const float mu = ss / float(B);
   float var = B > 1 ? (qq - ss * mu) / float(B - 1) : 0.f;
@@ -217,7 +180,7 @@ __device__ __forceinline__ void load_cols8(const float* p, float (&o)[8]) {
 }
 
 // `only_if_retry`: the full-range pass; it runs only when the narrow pass asked for it.
-__global__ void __launch_bounds__(256) zhist_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+__global__ void __launch_bounds__(256) zhist_kernel(const t16* __restrict__ x, const float* __restrict__ mean,
                                                       const float* __restrict__ rstd, ScanGeom g, uint32_t key_lo, int shift,
                                                       unsigned int* __restrict__ hist, const long long* __restrict__ ctl,
                                                       int only_if_retry) {
@@ -243,7 +206,7 @@ __global__ void __launch_bounds__(256) zhist_kernel(const __nv_bfloat16* __restr
     const int nvalid = min(8, g.F - c0);
     const int r0 = blockIdx.y * g.rows_per_block;
     const int r1 = min(g.B, r0 + g.rows_per_block);
-    const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+    const t16* base = x + 1LL * l * g.layer_stride + c0;
     for (int rb = r0; rb < r1; rb += 4) {
       uint4 v[4];
 #pragma unroll
@@ -255,7 +218,7 @@ __global__ void __launch_bounds__(256) zhist_kernel(const __nv_bfloat16* __restr
         const uint32_t u[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+          const float xv = (j & 1) ? t16_hi(u[j >> 1]) : t16_lo(u[j >> 1]);
           const float z = (xv - mu[j]) * rs[j];
           if (z >= z_lo && j < nvalid) {  // one float compare for the bulk; keys only for the tail that counts
             const uint32_t key = float_to_key(z);
@@ -289,17 +252,10 @@ constexpr int kPoolStage = 512;   // histogram + queue + staging stay inside the
 constexpr int kHitQueue = 1024;   // 16-byte groups per CTA that passed the coarse filter
 constexpr int kHistExtra = 32;    // words after the two histograms: [0] = pool counter
 
-// Packed compare of two bf16 pairs: 0xFFFF in every half where a >= b (false for NaN).
-__device__ __forceinline__ uint32_t bf16x2_ge_mask(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("set.ge.u32.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-
 // Phase A streams the matrix with a coarse filter in the input's own format (one packed compare per two
 // elements) and only queues the 16-byte groups that may hold an element of the range; phase B runs the exact
 // test on the queued groups, one element per thread.  The hot loop stays a few instructions per group.
-__global__ void __launch_bounds__(256) zhist_collect_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+__global__ void __launch_bounds__(256) zhist_collect_kernel(const t16* __restrict__ x, const float* __restrict__ mean,
                                                               const float* __restrict__ rstd, ScanGeom g, int col_pitch,
                                                               const long long* __restrict__ sel_state,
                                                               unsigned int* __restrict__ hist, Pool pool) {
@@ -336,10 +292,10 @@ __global__ void __launch_bounds__(256) zhist_collect_kernel(const __nv_bfloat16*
         const float span = z_lo / rs;
         t[q] = (in && rs > 0.f) ? mu + span - 1e-5f * (fabsf(mu) + fabsf(span)) - 1e-30f : INFINITY;
       }
-      const __nv_bfloat162 pk = __halves2bfloat162(__float2bfloat16_rd(t[0]), __float2bfloat16_rd(t[1]));
+      const t16x2 pk = make_t16x2(float_to_t16_rd(t[0]), float_to_t16_rd(t[1]));
       thr2[j >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
     }
-    const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+    const t16* base = x + 1LL * l * g.layer_stride + c0;
     for (int rb = r0; rb < r1; rb += 8) {
       uint4 v[8];
 #pragma unroll
@@ -349,8 +305,8 @@ __global__ void __launch_bounds__(256) zhist_collect_kernel(const __nv_bfloat16*
       }
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const uint32_t hit = bf16x2_ge_mask(v[k].x, thr2[0]) | bf16x2_ge_mask(v[k].y, thr2[1]) |
-                             bf16x2_ge_mask(v[k].z, thr2[2]) | bf16x2_ge_mask(v[k].w, thr2[3]);
+        const uint32_t hit = t16x2_ge_mask(v[k].x, thr2[0]) | t16x2_ge_mask(v[k].y, thr2[1]) |
+                             t16x2_ge_mask(v[k].z, thr2[2]) | t16x2_ge_mask(v[k].w, thr2[3]);
         if (hit != 0 && rb + k < r1) {
           const int slot = atomicAdd(&s_q, 1);
           if (slot < kHitQueue) s_queue[slot] = (uint32_t(rb + k - r0) << 8) | threadIdx.x;
@@ -368,7 +324,7 @@ __global__ void __launch_bounds__(256) zhist_collect_kernel(const __nv_bfloat16*
     const int r = r0 + int(item >> 8);
     const int c = (blockIdx.x * blockDim.x + int(item & 255u)) * 8 + (e & 7);
     if (c >= g.F) continue;
-    const float xv = __bfloat162float(x[1LL * l * g.layer_stride + 1LL * r * g.ld + c]);
+    const float xv = t16_to_float(x[1LL * l * g.layer_stride + 1LL * r * g.ld + c]);
     const float z = (xv - __ldg(mean + 1LL * l * g.sp + c)) * __ldg(rstd + 1LL * l * g.sp + c);
     if (!(z >= z_lo)) continue;
     const uint32_t key = float_to_key(z);
@@ -454,15 +410,37 @@ __global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __re
     return;
   }
   const bool overflow = vals[kHistBins] != 0;
-  // thread t owns bins [8t, 8t+8); suffix sums from the top
+  // thread t owns bins [8t, 8t+8); part[t] = number of keys in the bins of all threads above t (suffix scan:
+  // shuffles inside a warp, then over the 32 warp totals)
   unsigned long long mine = 0;
   for (int j = 0; j < 8; ++j) mine += vals[tid * 8 + j];
-  part[tid] = mine;
+  {
+    __shared__ unsigned long long warp_tot[32], warp_above[32];
+    const int lane = tid & 31, warp = tid >> 5;
+    unsigned long long incl = mine;  // sum over lanes >= this lane
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long t = __shfl_down_sync(0xFFFFFFFFu, incl, o);
+      if (lane + o < 32) incl += t;
+    }
+    if (lane == 0) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      unsigned long long w = warp_tot[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long t = __shfl_down_sync(0xFFFFFFFFu, w, o);
+        if (lane + o < 32) w += t;
+      }
+      warp_above[lane] = w - warp_tot[lane];
+    }
+    __syncthreads();
+    part[tid] = (incl - mine) + warp_above[warp];
+  }
   __syncthreads();
   unsigned long long total = 0;
   if (tid == 0) {
-    unsigned long long run = 0;
-    for (int t = 1023; t >= 0; --t) { const unsigned long long c = part[t]; part[t] = run; run += c; }
+    const unsigned long long run = part[0] + mine;
     total = run;
     // tracked ranges clamp large keys into the top bin: a cut inside it cannot be refined, take the full pass
     const bool top_bin_cut = tracked && pass == 0 && (unsigned long long)vals[kHistBins - 1] >= (unsigned long long)k_total;
@@ -523,7 +501,7 @@ __global__ void __launch_bounds__(1024) find_bin_kernel(const unsigned int* __re
 // CSR build and the sparse decode consume.  Meant for sparse activations: when a CTA queues more groups than
 // its queue holds, or the list does not fit, the status word reports STATUS_CAPACITY and the caller falls back
 // to the dense path.
-__global__ void __launch_bounds__(256) threshold_collect_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ theta,
+__global__ void __launch_bounds__(256) threshold_collect_kernel(const t16* __restrict__ x, const float* __restrict__ theta,
                                                                   ScanGeom g, int col_pitch, long long* __restrict__ ctl,
                                                                   Lists o, int* __restrict__ status) {
   __shared__ uint32_t s_queue[4 * kHitQueue];
@@ -547,10 +525,10 @@ __global__ void __launch_bounds__(256) threshold_collect_kernel(const __nv_bfloa
       float t[2];
 #pragma unroll
       for (int q = 0; q < 2; ++q) t[q] = c0 + j + q < g.F ? __ldg(theta + 1LL * l * g.sp + c0 + j + q) : INFINITY;
-      const __nv_bfloat162 pk = __halves2bfloat162(__float2bfloat16_rd(t[0]), __float2bfloat16_rd(t[1]));
+      const t16x2 pk = make_t16x2(float_to_t16_rd(t[0]), float_to_t16_rd(t[1]));
       thr2[j >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
     }
-    const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+    const t16* base = x + 1LL * l * g.layer_stride + c0;
     for (int rb = r0; rb < r1; rb += 8) {
       uint4 v[8];
 #pragma unroll
@@ -560,8 +538,8 @@ __global__ void __launch_bounds__(256) threshold_collect_kernel(const __nv_bfloa
       }
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const uint32_t hit = bf16x2_ge_mask(v[k].x, thr2[0]) | bf16x2_ge_mask(v[k].y, thr2[1]) |
-                             bf16x2_ge_mask(v[k].z, thr2[2]) | bf16x2_ge_mask(v[k].w, thr2[3]);
+        const uint32_t hit = t16x2_ge_mask(v[k].x, thr2[0]) | t16x2_ge_mask(v[k].y, thr2[1]) |
+                             t16x2_ge_mask(v[k].z, thr2[2]) | t16x2_ge_mask(v[k].w, thr2[3]);
         if (hit != 0 && rb + k < r1) {
           const int slot = atomicAdd(&s_q, 1);
           if (slot < kQueue) s_queue[slot] = (uint32_t(rb + k - r0) << 8) | threadIdx.x;
@@ -581,7 +559,7 @@ __global__ void __launch_bounds__(256) threshold_collect_kernel(const __nv_bfloa
       const int r = r0 + int(item >> 8);
       const int c = (blockIdx.x * blockDim.x + int(item & 255u)) * 8 + (e & 7);
       if (c >= g.F) continue;
-      const float xv = __bfloat162float(x[1LL * l * g.layer_stride + 1LL * r * g.ld + c]);
+      const float xv = t16_to_float(x[1LL * l * g.layer_stride + 1LL * r * g.ld + c]);
       if (!(xv >= __ldg(theta + 1LL * l * g.sp + c))) continue;
       const int slot = atomicAdd(&s_n, 1);
       s_tok[slot] = r; s_col[slot] = l * col_pitch + c; s_val[slot] = xv;
@@ -623,7 +601,7 @@ struct TokenTopkShared {
 };
 
 template <typename Fn>
-__device__ __forceinline__ void token_rows_scan(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+__device__ __forceinline__ void token_rows_scan(const t16* __restrict__ x, const float* __restrict__ mean,
                                                 const float* __restrict__ rstd, const ScanGeom& g, int tok0, int ntok, Fn fn) {
   for (int l = 0; l < g.L; ++l) {
     for (int c0 = threadIdx.x * 8; c0 < g.F; c0 += blockDim.x * 8) {
@@ -640,7 +618,7 @@ __device__ __forceinline__ void token_rows_scan(const __nv_bfloat16* __restrict_
         const uint32_t u[4] = {v[t].x, v[t].y, v[t].z, v[t].w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+          const float xv = (j & 1) ? t16_hi(u[j >> 1]) : t16_lo(u[j >> 1]);
           fn(t, l, c0 + j, xv, float_to_key((xv - mu[j]) * rs[j]));
         }
       }
@@ -648,7 +626,7 @@ __device__ __forceinline__ void token_rows_scan(const __nv_bfloat16* __restrict_
   }
 }
 
-__global__ void __launch_bounds__(256) token_topk_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+__global__ void __launch_bounds__(256) token_topk_kernel(const t16* __restrict__ x, const float* __restrict__ mean,
                                                            const float* __restrict__ rstd, ScanGeom g, int col_pitch, int k,
                                                            long long* __restrict__ ctl, Lists o, int* __restrict__ status) {
   extern __shared__ uint8_t tk_smem[];
@@ -776,7 +754,7 @@ __global__ void __launch_bounds__(256) classify_pool_kernel(Pool pool, long long
 // list: a single counter cannot absorb one atomic per selected element (hundreds of thousands per step).
 constexpr int kStageCap = 1024;
 
-__global__ void __launch_bounds__(256) compact_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean,
+__global__ void __launch_bounds__(256) compact_kernel(const t16* __restrict__ x, const float* __restrict__ mean,
                                                         const float* __restrict__ rstd, ScanGeom g, int col_pitch,
                                                         long long* __restrict__ ctl, Lists o, int* __restrict__ status,
                                                         int only_if_retry) {
@@ -816,7 +794,7 @@ __global__ void __launch_bounds__(256) compact_kernel(const __nv_bfloat16* __res
     const int nvalid = min(8, g.F - c0);
     const int r0 = blockIdx.y * g.rows_per_block;
     const int r1 = min(g.B, r0 + g.rows_per_block);
-    const __nv_bfloat16* base = x + 1LL * l * g.layer_stride + c0;
+    const t16* base = x + 1LL * l * g.layer_stride + c0;
     for (int rb = r0; rb < r1; rb += 4) {
       uint4 v[4];
 #pragma unroll
@@ -830,7 +808,7 @@ __global__ void __launch_bounds__(256) compact_kernel(const __nv_bfloat16* __res
         const uint32_t u[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float xv = (j & 1) ? bf16_hi(u[j >> 1]) : bf16_lo(u[j >> 1]);
+          const float xv = (j & 1) ? t16_hi(u[j >> 1]) : t16_lo(u[j >> 1]);
           const float z = (xv - mu[j]) * rs[j];
           if (!(z >= z_min) || j >= nvalid || r >= r1) continue;
           const uint32_t key = float_to_key(z);
@@ -878,6 +856,8 @@ __global__ void __launch_bounds__(256) compact_kernel(const __nv_bfloat16* __res
 }
 
 // ------------------------------------------------------------------ 5. exact cut inside the bin (one CTA)
+constexpr int kGatherCap = 4096;   // candidates (all ranks together) that the one-round exact cut handles
+constexpr int kGatherSlot = 4096;  // ... and per rank: 2 + 2 * 4096 words fit one exchange slot (8224 words)
 struct FlatGeom {
   int col_pitch;        // local column pitch used in ent_col / cand_col
   int feat_offset;      // first global feature of this shard
@@ -924,10 +904,80 @@ __global__ void __launch_bounds__(1024) refine_kernel(const uint32_t* __restrict
   if (n > cand_cap) n = cand_cap;
   if (tid == 0) { timeout = 0; need = (unsigned long long)ctl[CTL_NEED]; }
   __syncthreads();
+  const uint32_t low_mask = shift >= 32 ? 0xFFFFFFFFu : ((1u << shift) - 1u);
+  // ---- fast path: one all-gather of the candidates of the threshold bin, exact cut found locally.
+  // A candidate travels as one 64-bit word: (low key bits << 45) | (2^45 - 1 - flat index), so that a larger word
+  // ranks first and, among equal keys, the lowest flat index does.  Every rank sorts out the same cut from the
+  // same words.  Bins with more candidates than the gather holds (heavy ties) take the radix rounds below.
+  {
+    __shared__ unsigned long long comp[kGatherCap];
+    __shared__ int total_s, fits_s;
+    constexpr unsigned long long kFlatMask = (1ULL << 45) - 1ULL;
+    const bool local_fits = n <= kGatherSlot && shift <= 19;
+    const int world = ex.world <= 1 ? 1 : ex.world;
+    // own candidates -> comp[0 .. n) (single rank) or through the exchange area
+    if (world == 1) {
+      if (tid == 0) { total_s = int(n); fits_s = (local_fits && n <= kGatherCap) ? 1 : 0; }
+      __syncthreads();
+      if (fits_s)
+        for (long long i = tid; i < n; i += 1024)
+          comp[i] = ((unsigned long long)((cand_key[i] - key_lo) & low_mask) << 45) | (kFlatMask - flat_index(fg, cand_tok[i], cand_col[i]));
+    } else {
+      // message: word 0 = count (0xFFFFFFFF: does not fit), then the 64-bit words
+      uint32_t* msg = reinterpret_cast<uint32_t*>(comp);
+      if (tid == 0) { msg[0] = local_fits ? uint32_t(n) : 0xFFFFFFFFu; msg[1] = 0; }
+      if (local_fits)
+        for (long long i = tid; i < n; i += 1024)
+          comp[1 + i] = ((unsigned long long)((cand_key[i] - key_lo) & low_mask) << 45) | (kFlatMask - flat_index(fg, cand_tok[i], cand_col[i]));
+      __syncthreads();
+      if (!exchange_gather(ex, 2, msg, local_fits ? 2 + 2 * int(n) : 2, &timeout)) {
+        if (tid == 0) atomicCAS(status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+        return;
+      }
+      if (tid == 0) {
+        long long tot = 0;
+        bool ok = true;
+        for (int q = 0; q < world; ++q) {
+          const uint32_t c = exchange_slot(ex, 2, q)[0];
+          if (c == 0xFFFFFFFFu) ok = false; else tot += c;
+        }
+        fits_s = (ok && tot <= kGatherCap) ? 1 : 0;
+        total_s = int(tot < kGatherCap ? tot : kGatherCap);
+      }
+      __syncthreads();
+      if (fits_s) {
+        int base = 0;
+        for (int q = 0; q < world; ++q) {
+          const uint32_t* slot = exchange_slot(ex, 2, q);
+          const int c = int(slot[0]);
+          const unsigned long long* src = reinterpret_cast<const unsigned long long*>(slot) + 1;
+          for (int i = tid; i < c; i += 1024) comp[base + i] = src[i];
+          base += c;
+        }
+      }
+    }
+    __syncthreads();
+    if (fits_s) {
+      const int G = total_s;
+      const unsigned long long want = need;  // the want-th largest word is the cut
+      for (int i = tid; i < G; i += 1024) {
+        const unsigned long long mine = comp[i];
+        int above = 0;
+        for (int j = 0; j < G; ++j) above += comp[j] > mine;
+        if ((unsigned long long)above + 1ULL == want) {
+          ctl[CTL_CUT_KEY] = (long long)(mine >> 45);
+          ctl[CTL_TIE_MODE] = 1;
+          ctl[CTL_CUT_FLAT] = (long long)(kFlatMask - (mine & kFlatMask));
+        }
+      }
+      if (tid == 0 && (want == 0 || want > (unsigned long long)G)) atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
+      return;
+    }
+  }
   // ---- key cut: radix passes over the low `shift` bits, 9 bits at a time, most significant first.
   uint32_t prefix = 0, prefix_mask = 0;
-  int round = 2;  // rounds 0 and 1 belong to the two histogram passes
-  const uint32_t low_mask = shift >= 32 ? 0xFFFFFFFFu : ((1u << shift) - 1u);
+  int round = 3;  // rounds 0 and 1 belong to the two histogram passes, round 2 to the candidate gather
+
   for (int hi = shift; hi > 0; hi -= 9, ++round) {
     const int lo = max(hi - 9, 0);
     const int nb = 1 << (hi - lo);
@@ -1208,14 +1258,14 @@ __global__ void __launch_bounds__(256) dead_counter_kernel(long long* __restrict
 // ====================================================================== C launchers
 using namespace clt;
 
-extern "C" int clt_colstats(const void* x, float* mean, float* rstd, int L, int B, int F, long long ld, long long layer_stride,
+extern "C" int CLT_FN(clt_colstats)(const void* x, float* mean, float* rstd, int L, int B, int F, long long ld, long long layer_stride,
                             cudaStream_t st) {
   if (F % 8 != 0 || ld % 8 != 0 || layer_stride % 8 != 0) return -1;
   const int col_blocks = (F / 8 + 31) / 32;
   int zsplit = 1;
   while (1LL * col_blocks * L * zsplit < 592 && zsplit < 16 && B / (zsplit * 2) >= 128) zsplit *= 2;
   dim3 grid(col_blocks, L, zsplit), block(32, 8);
-  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const t16* xp = static_cast<const t16*>(x);
   if (zsplit > 1) {
     if (cudaMemsetAsync(mean, 0, sizeof(float) * size_t(L) * F, st) != cudaSuccess) return -5;
     if (cudaMemsetAsync(rstd, 0, sizeof(float) * size_t(L) * F, st) != cudaSuccess) return -5;
@@ -1228,12 +1278,15 @@ extern "C" int clt_colstats(const void* x, float* mean, float* rstd, int L, int 
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+#if !CLT_T16_IS_HALF
 extern "C" int clt_colstats_from_tiles(const float* tile_stats, float* mean, float* rstd, int L, int B, int F, cudaStream_t st) {
   const long long n = 1LL * L * F;
   if (n == 0) return 0;
   colstats_from_tiles_kernel<<<int((n + 255) / 256), 256, 0, st>>>(tile_stats, mean, rstd, B, F, (B + 127) / 128, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
+
+#endif
 
 struct CltExchangeArgs {
   int world;
@@ -1302,12 +1355,12 @@ static FlatGeom flat_geom(const CltSelectArgs* a) {
 // Steps 2-6.  `exa` may be null (single rank).  The histogram first covers keys >= key_lo only (the
 // caller's guess of where the cut lies); if the cut is not inside, a full-range pass repeats it.
 // `hist` holds two histograms of 8192 counters, zeroed by the caller.
-extern "C" int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st) {
+extern "C" int CLT_FN(clt_batchtopk_select)(const CltSelectArgs* a, const CltExchangeArgs* exa, cudaStream_t st) {
   if (a->ld % 8 != 0 || a->layer_stride % 8 != 0 || a->stat_pitch % 4 != 0 || a->F > a->ld) return -1;
   const ScanGeom g = scan_geom(a);
   const Exchange ex = to_exchange(exa);
   dim3 grid(((a->F + 7) / 8 + 255) / 256, (a->B + g.rows_per_block - 1) / g.rows_per_block, a->L);
-  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(a->x);
+  const t16* x = static_cast<const t16*>(a->x);
   if (a->sel_state != nullptr && a->key_lo != 0) {
     Pool pool;
     pool.key = a->pool_key; pool.tok = a->pool_tok; pool.col = a->pool_col; pool.val = a->pool_val; pool.cap = a->pool_cap;
@@ -1335,18 +1388,18 @@ extern "C" int clt_batchtopk_select(const CltSelectArgs* a, const CltExchangeArg
 
 // Per-feature threshold selection (JumpReLU / ReLU as a sparse list).  theta: [L, stat_pitch] fp32.  Uses of the
 // argument block: x, rstd (= theta), L, B, F, stat_pitch, ld, layer_stride, col_pitch, ctl, ent_*, status.
-extern "C" int clt_threshold_select(const CltSelectArgs* a, cudaStream_t st) {
+extern "C" int CLT_FN(clt_threshold_select)(const CltSelectArgs* a, cudaStream_t st) {
   if (a->ld % 8 != 0 || a->layer_stride % 8 != 0 || a->F > a->ld) return -1;
   const ScanGeom g = scan_geom(a);
   dim3 grid(((a->F + 7) / 8 + 255) / 256, (a->B + g.rows_per_block - 1) / g.rows_per_block, a->L);
   if (cudaMemsetAsync(a->ctl + CTL_NUM_ENTRIES, 0, sizeof(long long), st) != cudaSuccess) return -5;
-  threshold_collect_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(a->x), a->rstd, g, a->col_pitch, a->ctl, lists_of(a), a->status);
+  threshold_collect_kernel<<<grid, 256, 0, st>>>(static_cast<const t16*>(a->x), a->rstd, g, a->col_pitch, a->ctl, lists_of(a), a->status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 // Per-token top-k of the batch z-scores (TokenTopK).  Uses x, mean, rstd, L, B, F, stat_pitch, ld, layer_stride,
 // col_pitch, ctl, ent_* (capacity >= B * k), status of the argument block; k_total carries the per-token k.
-extern "C" int clt_token_topk_select(const CltSelectArgs* a, cudaStream_t st) {
+extern "C" int CLT_FN(clt_token_topk_select)(const CltSelectArgs* a, cudaStream_t st) {
   if (a->ld % 8 != 0 || a->layer_stride % 8 != 0 || a->F % 8 != 0 || a->stat_pitch % 4 != 0 || a->F > a->ld) return -1;
   const long long k = a->k_total;
   if (k <= 0 || k > 1LL * a->L * a->F || 1LL * a->B * k > a->ent_cap) return -1;
@@ -1357,11 +1410,12 @@ extern "C" int clt_token_topk_select(const CltSelectArgs* a, cudaStream_t st) {
     attr_set = true;
   }
   const int grid = (a->B + kTokPerCta - 1) / kTokPerCta;
-  token_topk_kernel<<<grid, 256, sizeof(TokenTopkShared), st>>>(static_cast<const __nv_bfloat16*>(a->x), a->mean, a->rstd, g, a->col_pitch,
+  token_topk_kernel<<<grid, 256, sizeof(TokenTopkShared), st>>>(static_cast<const t16*>(a->x), a->mean, a->rstd, g, a->col_pitch,
                                                                  int(k), a->ctl, lists_of(a), a->status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+#if !CLT_T16_IS_HALF
 struct CltCsrArgs {
   const int* ent_tok; const int* ent_col; const float* ent_val; long long ent_cap;
   const long long* ctl;
@@ -1462,3 +1516,4 @@ extern "C" int clt_build_csr_static(const int* ent_tok, const int* ent_col, cons
   if (sort_segments & 2) csr_sort_segments_kernel<<<(num_cols + 255) / 256, 256, 0, stream>>>(feat_off, num_cols, fcsr_tok, fcsr_val);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
+#endif  // !CLT_T16_IS_HALF

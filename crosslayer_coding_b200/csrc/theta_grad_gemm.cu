@@ -67,8 +67,9 @@ __device__ __forceinline__ float warp_transpose_sum(float (&v)[32], int lane) {
 }
 
 __global__ void __launch_bounds__(tg::NUM_THREADS, 1)
-theta_grad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ ThetaGradMaps maps_b,
-                       const __nv_bfloat16* __restrict__ preact, long long ldx, long long layer_stride_x,
+theta_grad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_cum,
+                       const __grid_constant__ ThetaGradMaps maps_b, int tying,
+                       const t16* __restrict__ preact, long long ldx, long long layer_stride_x,
                        const float* __restrict__ theta, int stat_pitch, float half_bw, float* __restrict__ S1,
                        float* __restrict__ S2, int L, int M, int N, int d, int* __restrict__ status) {
   using namespace tg;
@@ -118,7 +119,9 @@ theta_grad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const long long rem = t - 1LL * src * tiles_per_layer;
         const int mt = int(rem % tiles_m);
         const int nt = int(rem / tiles_m);
-        const int num_kb = (L - src) * kb_per_layer;
+        // K runs over the target layers t >= src (untied: rows of the packed tensor of layer src; per_target: the
+        // tensors of the layers t); per_source has one decoder row per feature, its A operand is the seed summed over t
+        const int num_kb = (tying == 1 ? 1 : L - src) * kb_per_layer;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int tl = kb / kb_per_layer, kk = kb - tl * kb_per_layer;
           const int s = it % STAGES;
@@ -126,8 +129,10 @@ theta_grad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           if (!mbar_wait(&sh->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&sh->full[s], STAGE_BYTES);
           uint8_t* a_dst = tiles + size_t(s) * STAGE_BYTES;
-          tma_load_3d(a_dst, &map_a, &sh->full[s], kk * BK, mt * BM, src + tl);
-          tma_load_3d(a_dst + A_BYTES, &maps_b.b[src], &sh->full[s], tl * d + kk * BK, nt * BN, 0);
+          if (tying == 1) tma_load_3d(a_dst, &map_a_cum, &sh->full[s], kk * BK, mt * BM, src);
+          else tma_load_3d(a_dst, &map_a, &sh->full[s], kk * BK, mt * BM, src + tl);
+          if (tying == 0) tma_load_3d(a_dst + A_BYTES, &maps_b.b[src], &sh->full[s], tl * d + kk * BK, nt * BN, 0);
+          else tma_load_3d(a_dst + A_BYTES, &maps_b.b[tying == 2 ? src + tl : src], &sh->full[s], kk * BK, nt * BN, 0);
         }
       }
       if (!ok) {
@@ -150,7 +155,7 @@ theta_grad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       bool ok = true;
       for (long long t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local_tile) {
         const int src = int(t / tiles_per_layer);
-        const int num_kb = (L - src) * kb_per_layer;
+        const int num_kb = (tying == 1 ? 1 : L - src) * kb_per_layer;
         const uint32_t buf = local_tile & 1;
         const uint32_t tph = (local_tile >> 1) & 1;
         if (!mbar_wait(&sh->tmem_empty[buf], tph ^ 1, abort_flag)) { ok = false; break; }
@@ -196,7 +201,7 @@ theta_grad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       tc_fence_after();
       const int m = mt * BM + quarter * 32 + lane;
       const bool row_ok = m < M;
-      const __nv_bfloat16* xrow = preact + 1LL * src * layer_stride_x + 1LL * (row_ok ? m : 0) * ldx + 1LL * nt * BN;
+      const t16* xrow = preact + 1LL * src * layer_stride_x + 1LL * (row_ok ? m : 0) * ldx + 1LL * nt * BN;
       const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quarter * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -211,11 +216,11 @@ theta_grad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const uint4 u = __ldg(xp + q);
             const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { wx[q * 8 + 2 * j] = bf16_lo(w[j]); wx[q * 8 + 2 * j + 1] = bf16_hi(w[j]); }
+            for (int j = 0; j < 4; ++j) { wx[q * 8 + 2 * j] = t16_lo(w[j]); wx[q * 8 + 2 * j + 1] = t16_hi(w[j]); }
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) wx[j] = (row_ok && n0 + j < N) ? __bfloat162float(xrow[c * 32 + j]) : INFINITY;
+          for (int j = 0; j < 32; ++j) wx[j] = (row_ok && n0 + j < N) ? t16_to_float(xrow[c * 32 + j]) : INFINITY;
         }
         tmem_ld_wait();
         float p[32];
@@ -280,7 +285,7 @@ static bool tg_make_map(CUtensorMap* map, const void* base, int layers, int rows
   cuuint64_t strides[2] = {cuuint64_t(row_stride_elems) * 2, cuuint64_t(layer_stride_elems) * 2};
   cuuint32_t box[3] = {cuuint32_t(tg::BK), cuuint32_t(box_rows), 1};
   cuuint32_t elem[3] = {1, 1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+  return enc(map, (CLT_T16_IS_HALF ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16), 3, const_cast<void*>(base), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -299,18 +304,22 @@ struct CltThetaGradArgs {
   float* S2;
   int L, B, F, d;
   int* status;
+  int tying;               // 0 untied ([F, L - s, d]), 1 per_source, 2 per_target (tensors [F, 1, d])
+  const void* gs_cum;      // per_source: [L, B, d] suffix sums of gs over the layers
 };
 
 // Returns 0 on success, a negative value when the arguments cannot be handled (the caller raises).
-extern "C" int clt_theta_grad_gemm(const CltThetaGradArgs* a, int num_sms, cudaStream_t stream) {
+extern "C" int CLT_FN(clt_theta_grad_gemm)(const CltThetaGradArgs* a, int num_sms, cudaStream_t stream) {
   using namespace clt;
   if (a->d % 8 != 0 || a->ldx % 8 != 0 || a->layer_stride_x % 8 != 0 || a->L > tg::kMaxLayers || a->L < 1) return -1;
-  CUtensorMap map_a;
+  CUtensorMap map_a, map_a_cum;
   ThetaGradMaps maps;
+  if (a->tying < 0 || a->tying > 2 || (a->tying == 1 && a->gs_cum == nullptr)) return -1;
   if (!tg_make_map(&map_a, a->gs, a->L, a->B, a->d, a->d, 1LL * a->B * a->d, tg::BM)) return -3;
+  if (!tg_make_map(&map_a_cum, a->tying == 1 ? a->gs_cum : a->gs, a->L, a->B, a->d, a->d, 1LL * a->B * a->d, tg::BM)) return -3;
   for (int s = 0; s < tg::kMaxLayers; ++s) {
     const int src = s < a->L ? s : a->L - 1;
-    const long long K = 1LL * (a->L - src) * a->d;
+    const long long K = a->tying == 0 ? 1LL * (a->L - src) * a->d : a->d;
     if ((reinterpret_cast<uintptr_t>(a->w[src]) & 15) != 0) return -2;
     if (!tg_make_map(&maps.b[s], a->w[src], 1, a->F, K, K, 1LL * a->F * K, tg::BN)) return -3;
   }
@@ -323,7 +332,7 @@ extern "C" int clt_theta_grad_gemm(const CltThetaGradArgs* a, int num_sms, cudaS
   if (tiles == 0) return 0;
   const int grid = int(tiles < num_sms ? tiles : num_sms);
   theta_grad_gemm_kernel<<<grid, tg::NUM_THREADS, tg::SMEM_BYTES, stream>>>(
-      map_a, maps, static_cast<const __nv_bfloat16*>(a->preact), a->ldx, a->layer_stride_x, a->theta, a->stat_pitch,
+      map_a, map_a_cum, maps, a->tying, static_cast<const t16*>(a->preact), a->ldx, a->layer_stride_x, a->theta, a->stat_pitch,
       0.5f * a->bandwidth, a->S1, a->S2, a->L, a->B, a->F, a->d, a->status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

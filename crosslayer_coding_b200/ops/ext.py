@@ -18,7 +18,9 @@ _PKG = Path(__file__).resolve().parent.parent
 CSRC = _PKG / "csrc"
 BUILD_DIR = _PKG / "_ext"
 EXT_NAME = "clt_b200_ext"
-SOURCES = ["bindings.cpp", "encoder_gemm.cu", "theta_grad_gemm.cu", "select.cu", "decode.cu", "adam.cu", "comm.cu"]
+# every kernel file is compiled for bf16 and, through a one-line wrapper that defines CLT_HALF, for fp16
+KERNEL_FILES = ["encoder_gemm.cu", "theta_grad_gemm.cu", "select.cu", "decode.cu", "adam.cu", "comm.cu", "step.cu"]
+SOURCES = ["bindings.cpp"] + KERNEL_FILES + [f"half/{name[:-3]}_h.cu" for name in KERNEL_FILES]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
@@ -40,7 +42,7 @@ def _stale() -> bool:
     so = _so_path()
     if not so.exists():
         return True
-    newest = max(os.path.getmtime(p) for p in _sources() + [str(CSRC / "common.cuh")])
+    newest = max(os.path.getmtime(p) for p in _sources() + [str(CSRC / "common.cuh"), str(CSRC / "clt_api.inc"), str(CSRC / "csr_static.h")])
     return newest > os.path.getmtime(so)
 
 

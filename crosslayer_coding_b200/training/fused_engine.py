@@ -66,55 +66,113 @@ def histogram_range(k_total: int, numel: int, pool_factor: float = 1.75):
 
 def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingConfig], model=None) -> Optional[str]:
     """``None`` when the fused step covers this configuration, else the reason it does not."""
-    if clt_config.activation_fn not in ("batchtopk", "jumprelu", "topk"):
-        return f"activation_fn={clt_config.activation_fn!r} (fused step covers batchtopk, topk and jumprelu)"
+    if clt_config.activation_fn not in ("batchtopk", "jumprelu", "topk", "relu"):
+        return f"activation_fn={clt_config.activation_fn!r} (fused step covers batchtopk, topk, jumprelu and relu)"
     if clt_config.activation_fn in ("batchtopk", "topk") and clt_config.topk_mode != "global":
         return "topk_mode='per_layer'"
     if clt_config.activation_fn == "topk" and model is not None and model.world_size > 1:
         return "per-token topk under tensor parallelism"
-    if clt_config.activation_fn == "jumprelu":
-        # the threshold gradient runs as one GEMM per source layer over the packed untied decoder tensors
-        if clt_config.decoder_tying != "none":
-            return "jumprelu with tied decoders"
-    if clt_config.enable_feature_offset or clt_config.enable_feature_scale:
+    if clt_config.activation_fn == "jumprelu" and (clt_config.enable_feature_offset or clt_config.enable_feature_scale) \
+            and clt_config.decoder_tying != "none":
+        return "jumprelu with feature offset/scale (the threshold-gradient GEMM has no per-target affine)"
+    if (clt_config.enable_feature_offset or clt_config.enable_feature_scale) and clt_config.decoder_tying != "none":
         return "feature offset/scale"
     if clt_config.d_model % 8 != 0 or clt_config.d_model > 2048:
         return "d_model must be a multiple of 8 and <= 2048"
     if clt_config.num_layers > 32:
         return "more than 32 layers"
     if model is not None:
-        if model.dtype != torch.bfloat16:
-            return f"model dtype {model.dtype} (fused step needs bf16 weights)"
+        if model.dtype not in (torch.bfloat16, torch.float16):
+            return f"model dtype {model.dtype} (fused step needs bf16 or fp16 weights)"
         if model.local_features % 8 != 0:
             return "local feature count must be a multiple of 8"
     if training_config is not None:
-        if training_config.gradient_clip_val is not None:
-            return "gradient clipping"
-        if training_config.aux_loss_factor:
-            # AuxK is evaluated by the autograd path whenever dead features exist; the
-            # fused step handles the (common) steps without dead features.
-            pass
-        if training_config.precision == "fp16":
-            return "fp16 loss scaling"
+        if training_config.precision == "fp16" and model is not None and model.dtype != torch.float16:
+            return "precision='fp16' needs fp16 weights (clt_dtype='float16' or fp16_convert_weights)"
     return None
 
 
 @dataclass
 class StepOutput:
-    """Device scalars of one step; nothing here forces a host sync."""
+    """Device scalars of one step; nothing here forces a host sync.  All of them are views of ``vector``
+    (fp32 ``[8]``: total, reconstruction, sparsity, pre-activation, auxiliary, gradient norm, skipped steps so far,
+    loss scale), which the step-control kernel fills."""
 
-    reconstruction: torch.Tensor
-    sparsity: torch.Tensor
-    preactivation: torch.Tensor
-    auxiliary: torch.Tensor
-    total: torch.Tensor
+    vector: torch.Tensor
     num_entries: torch.Tensor
+
+    @property
+    def total(self): return self.vector[0]
+
+    @property
+    def reconstruction(self): return self.vector[1]
+
+    @property
+    def sparsity(self): return self.vector[2]
+
+    @property
+    def preactivation(self): return self.vector[3]
+
+    @property
+    def auxiliary(self): return self.vector[4]
+
+    @property
+    def grad_norm(self): return self.vector[5]
+
+    @property
+    def skipped_steps(self): return self.vector[6]
+
+    @property
+    def loss_scale(self): return self.vector[7]
 
     def as_dict(self) -> Dict[str, torch.Tensor]:
         return {
             "total": self.total, "reconstruction": self.reconstruction, "sparsity": self.sparsity,
-            "preactivation": self.preactivation, "auxiliary": self.auxiliary,
+            "preactivation": self.preactivation, "auxiliary": self.auxiliary, "_vector": self.vector,
         }
+
+
+# rounds of the symmetric exchange area used outside the selection (which owns rounds 0 .. 13)
+ROUND_LOSS, ROUND_NORM = 14, 15
+# words of the step control block (csrc/common.cuh: StepCtl)
+SC_SKIP, SC_INV_SCALE, SC_LOSS_SCALE, SC_GROWTH, SC_FOUND_INF, SC_GRAD_NORM_SQ, SC_CLIP, SC_SKIPPED = range(8)
+
+
+class _Arena:
+    """One allocation for everything a step needs zeroed, so that a step starts with a single memset.  The two
+    decoder-norm buffers sit at the two ends: the one that receives this step's norms is zeroed together with the
+    middle part (the range to clear is contiguous either way), the other one keeps the norms of the previous step."""
+
+    def __init__(self, device, norm_bytes: int):
+        self.device = device
+        self.specs = []
+        self.norm_bytes = (norm_bytes + 255) // 256 * 256
+        self.size = self.norm_bytes
+
+    def add(self, name: str, numel: int, dtype: torch.dtype):
+        nbytes = (numel * torch.empty((), dtype=dtype).element_size() + 255) // 256 * 256
+        self.specs.append((name, self.size, numel, dtype))
+        self.size += nbytes
+
+    def build(self):
+        total = self.size + self.norm_bytes
+        self.buf = torch.zeros(total, dtype=torch.uint8, device=self.device)
+        views = {}
+        for name, off, numel, dtype in self.specs:
+            es = torch.empty((), dtype=dtype).element_size()
+            views[name] = self.buf[off: off + numel * es].view(dtype)
+        self.mid_lo, self.mid_hi = self.norm_bytes, self.size
+        return views
+
+    def norm_view(self, which: int, numel: int) -> torch.Tensor:
+        off = 0 if which == 0 else self.size
+        return self.buf[off: off + numel * 4].view(torch.float32)
+
+    def clear_for_step(self, next_norm: int) -> None:
+        if next_norm == 0:
+            self.buf[: self.mid_hi].zero_()
+        else:
+            self.buf[self.mid_lo:].zero_()
 
 
 class FusedBatchTopKEngine:
@@ -145,10 +203,11 @@ class FusedBatchTopKEngine:
         self.group = model.process_group if self.world > 1 else None
         self.symm = symm
         self.dev = model.enc_weight.device
+        self.t16 = model.dtype  # bf16 or fp16: storage type of weights, inputs, pre-activations and the gradient seed
         self.tying = {"none": 0, "per_source": 1, "per_target": 2}[cfg.decoder_tying]
         dev = self.dev
         L, B, d, Fl = self.L, self.B, self.d, self.Fl
-        i32, f32 = torch.int32, torch.float32
+        i32, f32, f64 = torch.int32, torch.float32, torch.float64
 
         self.fn = cfg.activation_fn
         if self.fn == "batchtopk":
@@ -161,16 +220,15 @@ class FusedBatchTopKEngine:
                 raise ValueError("topk_k selects no feature")
             self.k_total = self.k_token * B
         else:
-            # JumpReLU: the number of active entries is data dependent; the lists hold up to
+            # JumpReLU / ReLU: the number of active entries is data dependent; the lists hold up to
             # ``fused_max_active_per_token`` entries per token and a step that needs more reports it
             per_tok = int(getattr(training_config, "fused_max_active_per_token", 1024) or 1024) if training_config is not None else 1024
             self.k_total = int(min(B * L * max(self.Fv, 1), per_tok * B))
         self.key_lo, self.shift = histogram_range(self.k_total, B * L * self.F) if self.fn == "batchtopk" else (0, 19)
-        self.preact = torch.empty(L, B, Fl, dtype=torch.bfloat16, device=dev)
+        self.preact = torch.empty(L, B, Fl, dtype=self.t16, device=dev)
         self.mean = torch.empty(L, Fl, dtype=f32, device=dev)
         self.rstd = torch.empty(L, Fl, dtype=f32, device=dev)
         self.tile_stats = None  # [L, ceil(B / 128), Fl, 2] fp32 switches the statistics into the GEMM epilogue
-        self.hist = torch.zeros(2 * 8192 + 32, dtype=i32, device=dev)  # two histograms + the pool counter
         # tracked histogram range {key_lo, shift} and the pool filled by the single pass over the pre-activations
         self.sel_state = torch.tensor([self.key_lo, self.shift], dtype=torch.int64, device=dev) if self.key_lo != 0 else None
         k_local = -(-self.k_total // max(1, self.world))
@@ -190,8 +248,30 @@ class FusedBatchTopKEngine:
         self.cand_val = torch.empty(cand_cap, dtype=f32, device=dev)
         ncols = L * Fl
         self.ncols = ncols
-        self.tok_cnt = torch.zeros(B, dtype=i32, device=dev)
-        self.feat_cnt = torch.zeros(ncols, dtype=i32, device=dev)
+        # --- everything that has to be zero when a step starts lives in one arena (one memset per step)
+        ar = _Arena(dev, ncols * 4)
+        ar.add("hist", 2 * 8192 + 32, i32)          # two histograms + the pool counter
+        ar.add("tok_cnt", B, i32)
+        ar.add("feat_cnt", ncols, i32)
+        ar.add("sq_err", L, f64)
+        ar.add("scalars", 4, f64)                    # penalty, pre-activation loss, auxiliary loss (+ spare)
+        ar.add("gs_sum", L * d, f32)
+        ar.add("grad_a", cap, f32)
+        if self.fn == "jumprelu":
+            ar.add("S1", L * Fl, f32)
+            ar.add("S2", L * Fl, f32)
+        views = ar.build()
+        self.arena = ar
+        self.hist, self.tok_cnt, self.feat_cnt = views["hist"], views["tok_cnt"], views["feat_cnt"]
+        self.sq_err, self.scalars = views["sq_err"], views["scalars"]
+        self.penalty = self.scalars[0:1]
+        self.gs_sum = views["gs_sum"].view(L, d)
+        self.grad_a = views["grad_a"]
+        if self.fn == "jumprelu":
+            self.S1, self.S2 = views["S1"].view(L, Fl), views["S2"].view(L, Fl)
+        self._norm_cur = 0                            # which end of the arena holds the current decoder norms
+        self.norm2 = ar.norm_view(0, ncols)           # per decoder tensor rows
+        self.norm2_next = ar.norm_view(1, ncols)
         self.tok_off = torch.zeros(B + 1, dtype=i32, device=dev)
         self.feat_off = torch.zeros(ncols + 1, dtype=i32, device=dev)
         self.tok_cursor = torch.zeros(B, dtype=i32, device=dev)
@@ -202,14 +282,10 @@ class FusedBatchTopKEngine:
         self.fcsr_val = torch.zeros(cap, dtype=f32, device=dev)
         self.fired = torch.zeros(ncols, dtype=torch.uint8, device=dev)
         self.dead_counter = torch.zeros(ncols, dtype=torch.int64, device=dev)
-        self.gs = symm.gs if (symm is not None and self.world > 1) else torch.empty(L, B, d, dtype=torch.bfloat16, device=dev)
-        self.sq_err = torch.zeros(L, dtype=torch.float64, device=dev)
-        self.penalty = torch.zeros(1, dtype=torch.float64, device=dev)
-        self.gs_sum = torch.zeros(L, d, dtype=f32, device=dev)
-        self.grad_a = torch.zeros(cap, dtype=f32, device=dev)
+        self.gs = symm.gs if (symm is not None and self.world > 1) else torch.empty(L, B, d, dtype=self.t16, device=dev)
+        if self.gs.dtype != self.t16:
+            self.gs = self.gs.view(self.t16)  # same width: the symmetric buffer is typed by its user
         self.pen_coef = torch.zeros(ncols, dtype=f32, device=dev)
-        self.norm2 = torch.zeros(ncols, dtype=f32, device=dev)      # per decoder tensor rows
-        self.norm2_next = torch.zeros(ncols, dtype=f32, device=dev)
         self.norms_valid = False
         self.sigma = None
         if sigma_tg is not None:
@@ -226,7 +302,19 @@ class FusedBatchTopKEngine:
             sel = torch.tril(torch.ones(L, L, dtype=f32, device=dev))
         else:
             sel = torch.eye(L, dtype=f32, device=dev)
-        self.bias_sel = sel  # [L targets, n_bias]
+        self.bias_sel = sel.contiguous()  # [L targets, n_bias]
+        self.bias_sum = torch.zeros(L, d, dtype=f32, device=dev)
+        self._bias_sum_valid = False
+
+        # step control block: skip flag, 1 / loss scale, loss scale, growth counter, found-inf, norm^2, clip, skipped
+        self.fp16 = self.t16 == torch.float16
+        init_scale = float(getattr(training_config, "loss_scale_init", 65536.0)) if (training_config is not None and self.fp16) else 1.0
+        self.step_ctl = torch.zeros(16, dtype=f32, device=dev)
+        self.step_ctl[SC_INV_SCALE] = 1.0 / init_scale
+        self.step_ctl[SC_LOSS_SCALE] = init_scale
+        self.step_ctl[SC_CLIP] = 1.0
+        self.growth_interval = int(getattr(training_config, "loss_scale_growth_interval", 2000)) if training_config is not None else 2000
+        self.clip_val = float(training_config.gradient_clip_val) if (training_config is not None and training_config.gradient_clip_val) else 0.0
 
         # optimizer state: fp32 moments; optimizer_states_dtype="bfloat16" keeps the moments of the two big weight
         # families in bf16 with stochastic rounding (12 instead of 20 bytes per parameter and step through HBM)
@@ -234,8 +322,8 @@ class FusedBatchTopKEngine:
         if training_config is not None:
             z = lambda p: torch.zeros_like(p, dtype=f32)  # noqa: E731
             self.moments_bf16 = str(getattr(training_config, "optimizer_states_dtype", "")).lower() in ("bfloat16", "bf16")
-            if self.moments_bf16 and self.tying != 0:
-                raise ValueError("optimizer_states_dtype='bfloat16' needs untied decoders (row pipeline)")
+            if self.moments_bf16 and (self.tying != 0 or self.fp16):
+                raise ValueError("optimizer_states_dtype='bfloat16' needs untied bf16 decoders (row pipeline)")
             zb = (lambda p: torch.zeros_like(p, dtype=torch.bfloat16)) if self.moments_bf16 else z  # noqa: E731
             self.enc_m, self.enc_v = zb(model.enc_weight), zb(model.enc_weight)
             self.encb_m, self.encb_v = z(model.enc_bias), z(model.enc_bias)
@@ -244,15 +332,23 @@ class FusedBatchTopKEngine:
             self.decb_m, self.decb_v = z(model.dec_bias), z(model.dec_bias)
             if model.skip_weight is not None:
                 self.skip_m, self.skip_v = z(model.skip_weight), z(model.skip_weight)
-        if self.fn == "jumprelu":
-            self.S1 = torch.zeros(L, Fl, dtype=f32, device=dev)
-            self.S2 = torch.zeros(L, Fl, dtype=f32, device=dev)
-            if training_config is not None:
+        if self.fn in ("jumprelu", "relu"):
+            self.theta = torch.zeros(L, Fl, dtype=f32, device=dev)
+            self._theta_valid = False
+            if self.fn == "relu":
+                # ReLU as a threshold selection: x >= smallest positive value of the storage type
+                self.theta.fill_(float(torch.finfo(self.t16).tiny))
+                self._theta_valid = True
+            if training_config is not None and self.fn == "jumprelu":
                 self.theta_m = torch.zeros(L, Fl, dtype=f32, device=dev)
                 self.theta_v = torch.zeros(L, Fl, dtype=f32, device=dev)
+                self.grad_log_threshold = torch.zeros(L, Fl, dtype=f32, device=dev)  # kept for diagnostics and tests
+            if self.tying == 1 and self.fn == "jumprelu":
+                self.gs_cum = torch.empty(L, B, d, dtype=self.t16, device=dev)
         self.opt_step = 0
         self.seq = 0
         self.kernel_launches = 0  # launches of this package's own kernels (reported by the benchmark)
+        self.last_output: Optional[StepOutput] = None
 
     # ------------------------------------------------------------------ pieces
     def _exchange_args(self):
@@ -261,26 +357,39 @@ class FusedBatchTopKEngine:
         self.seq += 1
         return (self.world, self.rank, self.symm.hist_data_ptrs, self.symm.hist_flag_ptrs, self.symm.slot_elems, self.seq)
 
-    def encode_select(self, X: torch.Tensor) -> None:
-        """Kernels 1-4: pre-activations, batch statistics, global BatchTopK, CSR views."""
+    def _begin_step(self) -> None:
+        """One memset for everything that has to start at zero (histograms, counters, loss sums, dL/da, next norms)."""
+        self.arena.clear_for_step(1 - self._norm_cur)
+
+    def _ensure_theta(self) -> None:
+        if self.fn == "jumprelu" and not self._theta_valid:
+            self.ext.theta_exp(self.model.log_threshold.data, self.theta)
+            self._theta_valid = True
+
+    def _build_csr(self) -> None:
+        self.ext.build_csr(
+            self.ent_tok, self.ent_col, self.ent_val, self.ctl, self.B, self.ncols,
+            self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
+            self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2, self.Fl,
+        )
+
+    def encode_select(self, X: torch.Tensor, fresh: bool = True) -> None:
+        """Kernels 1-4: pre-activations, batch statistics, selection, CSR views.  ``fresh``: clear the per-step
+        arena first (the training step does it itself)."""
         e = self.ext
         m = self.model
-        assert X.dtype == torch.bfloat16 and X.shape == (self.L, self.B, self.d), (X.dtype, X.shape)
+        assert X.dtype == self.t16 and X.shape == (self.L, self.B, self.d), (X.dtype, X.shape)
+        if fresh:
+            self._begin_step()
         self._X_last = X
         # The GEMM can leave per-block column sums behind (tile_stats) so that the batch statistics need no second
         # pass; at K = d_model that epilogue work outlasts the MMAs of a tile (measured: +0.75 ms on the GEMM against
         # 0.37 ms for the separate pass at the GPT-2 shape), so the separate column-statistics pass is used.
         e.encoder_gemm(X, m.enc_weight.data, m.enc_bias.data, self.preact, self.status, self.tile_stats)
-        if self.fn == "jumprelu":
-            self.theta = m.log_threshold.data.float().exp().contiguous()
+        if self.fn in ("jumprelu", "relu"):
+            self._ensure_theta()
             e.threshold_select(self.preact, self.theta, self.Fv, self.Fl, self.ctl, self.ent_tok, self.ent_col, self.ent_val, self.status)
-            self.tok_cnt.zero_()
-            self.feat_cnt.zero_()
-            e.build_csr(
-                self.ent_tok, self.ent_col, self.ent_val, self.ctl, self.B, self.ncols,
-                self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
-                self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2, self.Fl,
-            )
+            self._build_csr()
             self.kernel_launches += 2 + 5  # gemm, threshold selection, csr (5)
             return
         if self.tile_stats is not None:
@@ -290,16 +399,9 @@ class FusedBatchTopKEngine:
         if self.fn == "topk":
             e.token_topk_select(self.preact, self.mean, self.rstd, self.Fl, self.k_token, self.ctl, self.ent_tok, self.ent_col,
                                 self.ent_val, self.status)
-            self.tok_cnt.zero_()
-            self.feat_cnt.zero_()
-            e.build_csr(
-                self.ent_tok, self.ent_col, self.ent_val, self.ctl, self.B, self.ncols,
-                self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
-                self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2, self.Fl,
-            )
+            self._build_csr()
             self.kernel_launches += 3 + 5  # gemm, colstats, per-token selection, csr (5)
             return
-        self.hist.zero_()
         world, rank, dptr, fptr, slot, seq = self._exchange_args()
         if self.world > 1 and self.symm is None:
             raise RuntimeError("tensor-parallel fused engine needs a symmetric exchange area (parallel.symm)")
@@ -309,19 +411,16 @@ class FusedBatchTopKEngine:
             self.cand_key, self.cand_tok, self.cand_col, self.cand_val, self.status,
             world, rank, dptr, fptr, slot, seq, self.sel_state, self.pool,
         )
-        self.tok_cnt.zero_()
-        self.feat_cnt.zero_()
-        e.build_csr(
-            self.ent_tok, self.ent_col, self.ent_val, self.ctl, self.B, self.ncols,
-            self.tok_cnt, self.feat_cnt, self.tok_off, self.feat_off, self.tok_cursor, self.feat_cursor,
-            self.tcsr_col, self.tcsr_val, self.fcsr_tok, self.fcsr_val, self.fired, 2, self.Fl,
-        )
+        self._build_csr()
         # gemm, colstats, select (collect, find_bin, classify, fallback x3, refine, finalize | zhist, find_bin, compact,
         # refine, finalize), csr (5)
         self.kernel_launches += 2 + (8 if self.key_lo != 0 else 5) + 5
 
-    def _bias_sum(self) -> torch.Tensor:
-        return (self.bias_sel @ self.model.dec_bias.data.float()).contiguous()
+    def _ensure_bias_sum(self) -> None:
+        """Per-target sums of the decoder biases; kept current by the last kernel of every training step."""
+        if not self._bias_sum_valid:
+            self.ext.step_finish(None, None, self.model.dec_bias.data, self.bias_sel, self.bias_sum)
+            self._bias_sum_valid = True
 
     # The skip connection (reference: clt/models/decoder.py:310,332) is a handful of small dense [B, d] x [d, d]
     # products: library GEMMs.  Its output enters the fused loss epilogue as the `addend` of the decode kernel and
@@ -344,31 +443,29 @@ class FusedBatchTopKEngine:
             out += torch.matmul(X.to(W.dtype), W.data.transpose(1, 2)).float()
         return out
 
-    def _skip_adam(self, X: torch.Tensor, lr: float, c_g: float) -> None:
+    def _skip_grad(self, X: torch.Tensor) -> torch.Tensor:
         W = self.model.skip_weight
-        if W is None:
-            return
-        grad = torch.zeros(W.shape, dtype=torch.float32, device=self.dev)
         gs = self.gs
         if self.tying == 0:
+            grad = torch.zeros(W.shape, dtype=torch.float32, device=self.dev)
             for s in range(self.L):
                 # d loss / d W[s -> t] = c_g * gs[t]^T @ x[s]
                 grad[self._skip_pairs(s)] = torch.matmul(gs[s:].transpose(1, 2), X[s].to(gs.dtype)).float()
-        else:
-            grad = torch.matmul(gs.transpose(1, 2), X.to(gs.dtype)).float()
-        self.ext.dense_adam(W.data, self.skip_m, self.skip_v, grad.contiguous(), self._hyper(lr, c_g))
+            return grad
+        return torch.matmul(gs.transpose(1, 2), X.to(gs.dtype)).float().contiguous()
 
     def decode_loss(self, Y: torch.Tensor, want_yhat: bool = False) -> Optional[torch.Tensor]:
         """Kernel 5: sparse decode, reconstruction loss sums and the gradient seed."""
         e, m = self.ext, self.model
-        self.sq_err.zero_()
         yhat = torch.empty(self.L, self.B, self.d, dtype=torch.float32, device=self.dev) if want_yhat else None
         dec_w = [w.data for w in m.dec_weight]
-        bias_sum = self._bias_sum()
+        self._ensure_bias_sum()
+        bias_sum = self.bias_sum
         addend = self._skip_term(self._X_last) if m.skip_weight is not None else None
         if self.world == 1:
             e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
-                            None, None, None, bias_sum, addend, Y, self.sigma, self.gs, yhat, self.sq_err, 1, [], 0, 0, self.status)
+                            None, None, None, bias_sum, addend, Y, self.sigma, self.gs, yhat, self.sq_err, 1, [], 0, 0, self.status,
+                            self.step_ctl)
             self.kernel_launches += 1
         else:
             sy = self.symm
@@ -378,14 +475,23 @@ class FusedBatchTopKEngine:
             e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
                             None, None, None, None, None, None, None, None, None, None, 2, sy.stage_ptrs, sy.rows_per_rank, self.rank, self.status)
             sy.barrier(e, self.status)
-            # 2. owners reduce their rows, finish the loss and push the gradient seed to every rank
-            e.owner_reduce_loss(sy.stage, sy.gs_ptrs, self.rank, bias_sum, addend, Y, self.sigma, yhat, self.sq_err, sy.rows_per_rank)
-            sy.barrier(e, self.status)
-            pops.all_reduce(self.sq_err, group=self.group)
+            # 2. owners reduce their rows, finish their part of the loss and push the gradient seed to every rank; the
+            #    exchange inside the step-control kernel that follows is the barrier behind these pushes
+            e.owner_reduce_loss(sy.stage, sy.gs_ptrs, self.rank, bias_sum, addend, Y, self.sigma, yhat, self.sq_err, sy.rows_per_rank,
+                                self.step_ctl)
             if yhat is not None:
+                sy.barrier(e, self.status)
                 pops.all_reduce(yhat, group=self.group)
-            self.kernel_launches += 4
+            self.kernel_launches += 3
         return yhat
+
+    def _control(self, phase: int, losses: torch.Tensor) -> None:
+        """Device-side decision of the step (sums the loss terms over the ranks, skip flag, loss scale, clip)."""
+        world, rank, dptr, fptr, slot, seq = self._exchange_args()
+        self.ext.step_control(self.step_ctl, self.status, self.sq_err, self.scalars, losses, 1.0 / (self.B * self.d), phase,
+                              self.fp16 and self.tc is not None, self.growth_interval, self.clip_val, world, rank, dptr, fptr, slot, seq,
+                              ROUND_LOSS if phase == 0 else ROUND_NORM)
+        self.kernel_launches += 1
 
     def _hyper(self, lr: float, grad_scale: float) -> List[float]:
         tc = self.tc
@@ -415,7 +521,6 @@ class FusedBatchTopKEngine:
             return torch.flip(torch.cumsum(torch.flip(per_t, dims=[0]), dim=0), dims=[0]).reshape(-1).contiguous()
         return self.norm2
 
-    # -------------------------------------------------------------------- step
     # ------------------------------------------------------- extra loss terms
     def _extra_buffers(self):
         if getattr(self, "_enc_dense", None) is None:
@@ -426,27 +531,29 @@ class FusedBatchTopKEngine:
         return self._enc_dense, self._encb_dense, self._dec_row0_dense
 
     @torch.no_grad()
-    def _preactivation_term(self, X: torch.Tensor, coef: float) -> torch.Tensor:
+    def _preactivation_term(self, X: torch.Tensor, coef: float) -> None:
         """``coef * mean(relu(-preact))`` (reference losses.py:203-261) and its dense encoder gradient
-        ``-(coef/numel) * 1[preact < 0]^T X`` - a library GEMM per layer on the stored pre-activations."""
+        ``-(coef/numel) * 1[preact < 0]^T X`` - a library GEMM per layer on the stored pre-activations.  The loss sum of
+        this shard goes to ``scalars[1]``."""
         enc_dense, encb_dense, _ = self._extra_buffers()
         numel = float(self.L * self.B * self.F)
-        total = torch.zeros((), device=self.dev)
+        total = torch.zeros((), device=self.dev, dtype=torch.float64)
         for l in range(self.L):
             pl = self.preact[l][:, : self.Fv]
             neg = pl < 0
-            total = total + torch.where(neg, -pl.float(), torch.zeros((), device=self.dev)).sum()
-            g = neg.to(torch.bfloat16)
+            total = total + torch.where(neg, -pl.float(), torch.zeros((), device=self.dev)).sum().double()
+            g = neg.to(self.t16)
             enc_dense[l, : self.Fv].add_((g.t() @ X[l]).float(), alpha=-coef / numel)
             encb_dense[l, : self.Fv].add_(g.float().sum(dim=0), alpha=-coef / numel)
-        return coef * total / numel
+        self.scalars[1] += coef * total / numel
 
     @torch.no_grad()
     def _auxiliary_term(self, X: torch.Tensor, dead_mask: torch.Tensor, factor: float, k_aux_default: int = 512) -> torch.Tensor:
         """AuxK on dead features (reference losses.py:263-329) in closed form on the few dead rows: per layer the
         top ``k_aux`` dead pre-activations of every token decode to the same layer and are matched to the
         de-normalised residual.  Gradients go to the dense side buffers (encoder rows, same-layer decoder rows,
-        that pair's bias) and, because the residual depends on the main reconstruction, into the gradient seed."""
+        that pair's bias) and, because the residual depends on the main reconstruction, into the gradient seed.
+        Returns the loss value (the same on every rank)."""
         from ..models import activations as act
         from ..models.clt import pair_index
 
@@ -458,6 +565,7 @@ class FusedBatchTopKEngine:
             pops.all_reduce(n_dead, group=self.group)
         n_dead_host = n_dead.tolist()
         total = torch.zeros((), device=self.dev)
+        scale = self.step_ctl[SC_LOSS_SCALE]
         self._aux_bias_grad = torch.zeros_like(self.model.dec_bias.data, dtype=torch.float32)
         for l in range(L):
             nd = int(n_dead_host[l])
@@ -477,12 +585,12 @@ class FusedBatchTopKEngine:
                 pops.all_reduce(recon, group=self.group)
             recon = recon + m.dec_bias.data[bias_row].float()
             sg = self.sigma[l] if self.sigma is not None else torch.ones(d, device=self.dev)
-            residual = -(self.gs[l].float() / sg)  # (y - y_hat) * sigma
+            residual = -(self.gs[l].float() / scale / sg)  # (y - y_hat) * sigma
             r = recon - residual
             c = factor * min(nd / k_aux, 1.0)
             total = total + c * (r * r).mean()
             g_recon = r * (2.0 * c / (B * d))                      # dL/d recon
-            self.gs[l].add_((c * r * sg).to(self.gs.dtype))        # through the residual into the main path
+            self.gs[l].add_((c * r * sg * scale).to(self.gs.dtype))  # through the residual into the main path
             g_aux = (g_recon @ w_d.t()) * mask                     # STE: gradient at the kept positions
             dec0_dense[l].index_add_(0, idx, aux.t() @ g_recon)
             self._aux_bias_grad[bias_row] += g_recon.sum(dim=0)
@@ -493,113 +601,128 @@ class FusedBatchTopKEngine:
     # -------------------------------------------------------------------- step
     def train_step(self, X: torch.Tensor, Y: torch.Tensor, step: int, lr: float, sparsity_lambda: float = 0.0,
                    preactivation_coef: float = 0.0, aux_factor: float = 0.0, dead_mask: Optional[torch.Tensor] = None) -> StepOutput:
-        """One optimisation step on inputs/targets ``[L, B, d]`` (bf16, already normalised).
+        """One optimisation step on inputs/targets ``[L, B, d]`` (bf16 or fp16, already normalised).
+
+        Everything that decides whether and how the update is applied stays on the device: the loss kernels raise a
+        flag when the gradient seed overflows (fp16 loss scaling) or is not finite, ``step_control`` turns flag,
+        status word and loss into the skip decision, keeps the loss scale and (with ``gradient_clip_val``) computes
+        the clip coefficient from the norm pre-pass; the optimizer kernels read all of it from ``step_ctl``.
 
         ``preactivation_coef`` and ``aux_factor`` (with ``dead_mask [L, valid_features]``) switch on the two loss
-        terms that are not sparse: they are evaluated with a few library calls on the stored pre-activations /
-        the dead rows and enter the fused optimizer kernels as dense side gradients."""
+        terms that are not sparse; they enter the optimizer kernels as side gradients."""
         e, m, tc = self.ext, self.model, self.tc
         L, B, d = self.L, self.B, self.d
         self.opt_step += 1
-        self.encode_select(X)
-        self.decode_loss(Y)
+        self._begin_step()
+        self.encode_select(X, fresh=False)
         c_g = 2.0 / (B * d)
-        if self.fn == "jumprelu":
-            # window sums for the threshold gradient, from the decoder weights of this step (before their update)
-            self.S1.zero_()
-            self.S2.zero_()
-            e.theta_grad_gemm(self.gs, [w.data for w in m.dec_weight], self.preact, self.theta, float(m.bandwidth), self.S1, self.S2, self.status)
-            self.kernel_launches += 1
-        zero = torch.zeros((), device=self.dev)
-        pre_loss, aux_loss = zero, zero
+        ctl = self.step_ctl
+        jr = self.fn == "jumprelu"
         enc_dense = encb_dense = dec0_dense = None
         extra_bias_grad = None
         use_pre = abs(preactivation_coef) >= 1e-9
-        use_aux = aux_factor and dead_mask is not None
+        use_aux = bool(aux_factor) and dead_mask is not None
+        # loss terms that only need the selection come first, so that their sums are there when the loss is settled
+        pen = None
+        use_pen = sparsity_lambda > 1e-9 and (self.fn != "batchtopk" or (tc.apply_sparsity_penalty_to_batchtopk if tc is not None else True))
+        if use_pen:
+            e.sparsity_penalty(self.feat_off, self.fcsr_val, self.feature_norm2(), float(sparsity_lambda), float(tc.sparsity_c),
+                               self.grad_a, self.pen_coef, self.penalty)
+            pen = self.pen_coef
+            self.kernel_launches += 1
         if use_pre or use_aux:
             enc_dense, encb_dense, dec0_dense = self._extra_buffers()
             enc_dense.zero_()
             encb_dense.zero_()
             if use_pre:
-                pre_loss = self._preactivation_term(X, float(preactivation_coef))
-            if use_aux:
-                dec0_dense.zero_()
-                mask = dead_mask
-                if mask.shape[-1] != self.Fl:
-                    mask = torch.nn.functional.pad(mask, (0, self.Fl - mask.shape[-1]))
-                aux_loss = self._auxiliary_term(X, mask, float(aux_factor))
-                extra_bias_grad = self._aux_bias_grad
-            else:
+                self._preactivation_term(X, float(preactivation_coef))
+            if not use_aux:
                 dec0_dense = None
+        self.decode_loss(Y)
+        # the loss is settled here; under tensor parallelism the exchange inside is also the barrier behind the
+        # all-gather of the gradient seed, so everything below sees every token's seed row
+        losses = torch.empty(8, dtype=torch.float32, device=self.dev)
+        self._control(0, losses)
+        if jr:
+            # window sums for the threshold gradient, from the decoder weights of this step (before their update)
+            gs_cum = None
+            if self.tying == 1:
+                e.gs_suffix_sum(self.gs, self.gs_cum)
+                gs_cum = self.gs_cum
+                self.kernel_launches += 1
+            e.theta_grad_gemm(self.gs, [w.data for w in m.dec_weight], self.preact, self.theta, float(m.bandwidth), self.S1, self.S2,
+                              self.status, self.tying, gs_cum)
+            self.kernel_launches += 1
+        if use_aux:
+            dec0_dense.zero_()
+            mask = dead_mask
+            if mask.shape[-1] != self.Fl:
+                mask = torch.nn.functional.pad(mask, (0, self.Fl - mask.shape[-1]))
+            aux_val = self._auxiliary_term(X, mask, float(aux_factor))
+            extra_bias_grad = self._aux_bias_grad
+            losses[4] += aux_val  # the auxiliary term is evaluated on the finished residual, after the loss was settled
+            losses[0] += aux_val
         # decoder biases: dL/db[pair (s,t)] = c_g * sum_b gs[t, b, :]
-        self.gs_sum.zero_()
         e.gs_colsum(self.gs, self.gs_sum)
-        bias_grad = (self.bias_sel.t() @ self.gs_sum).contiguous()
-        if extra_bias_grad is not None:
-            bias_grad = bias_grad + extra_bias_grad / c_g  # dense_adam multiplies by c_g
-        self.grad_a.zero_()
-        self.penalty.zero_()
-        pen = None
-        use_pen = sparsity_lambda > 1e-9 and (self.fn != "batchtopk" or (tc.apply_sparsity_penalty_to_batchtopk if tc is not None else True))
-        if use_pen:
-            if self.fn == "jumprelu":
-                self.norm_at_step = self.feature_norm2().clamp_min(0).sqrt()  # the update below replaces the norms
-            e.sparsity_penalty(self.feat_off, self.fcsr_val, self.feature_norm2(), float(sparsity_lambda), float(tc.sparsity_c),
-                               self.grad_a, self.pen_coef, self.penalty)
-            pen = self.pen_coef
-        self.norm2_next.zero_()
-        e.decoder_rows_adam([w.data for w in m.dec_weight], self.dec_m, self.dec_v, L, B, d, self.Fl, self.tying,
-                            self.feat_off, self.fcsr_tok, self.fcsr_val, self.gs, self.grad_a, pen, self.norm2_next,
-                            None, None, dec0_dense, self._hyper(lr, c_g), self.status)
-        self.norm2, self.norm2_next = self.norm2_next, self.norm2
-        self.norms_valid = True
-        e.dense_adam(m.dec_bias.data, self.decb_m, self.decb_v, bias_grad, self._hyper(lr, c_g))
-        self._skip_adam(X, lr, c_g)
+        dec_w = [w.data for w in m.dec_weight]
+        skip_grad = self._skip_grad(X) if m.skip_weight is not None else None
+        h_dec, h_enc = self._hyper(lr, c_g), self._hyper(lr, 1.0)
+        clip = self.clip_val > 0.0
+        grad_a_for_update = self.grad_a
+        if clip:
+            # gradient-norm pre-pass: the row gradients are formed once without touching weights or moments (features
+            # without entries have none), dL/da is written on the way; step_control turns the norm into the coefficient
+            rep = 1.0 / self.world  # replicated parameters are counted once over the ranks
+            e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, self.tying, self.feat_off, self.fcsr_tok, self.fcsr_val,
+                                self.gs, self.grad_a, pen, None, None, None, dec0_dense, h_dec, None, None, None, ctl, True)
+            e.decoder_bias_adam(m.dec_bias.data, self.decb_m, self.decb_v, self.bias_sel, self.gs_sum, extra_bias_grad, h_dec, ctl, rep)
+            e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v, self.feat_off,
+                                self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, h_enc, None, None, None, None, ctl, True)
+            if skip_grad is not None:
+                e.dense_adam(m.skip_weight.data, self.skip_m, self.skip_v, skip_grad, h_dec, ctl, True, rep)
+            if jr:
+                self._theta_update(lr, c_g, float(sparsity_lambda) if use_pen else 0.0, norm_weight=1.0)
+            self._control(1, losses)
+            grad_a_for_update = None  # dL/da is complete; the update pass must not add to it again
+            self.kernel_launches += 4
+        e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, self.tying,
+                            self.feat_off, self.fcsr_tok, self.fcsr_val, self.gs, grad_a_for_update, pen, self.norm2_next,
+                            None, None, dec0_dense, h_dec, self.status, None, None, ctl, False)
+        if jr:
+            # thresholds: uses the decoder norms of this step (before the swap below)
+            self._theta_update(lr, c_g, float(sparsity_lambda) if use_pen else 0.0)
+        self._swap_norms()
+        e.decoder_bias_adam(m.dec_bias.data, self.decb_m, self.decb_v, self.bias_sel, self.gs_sum, extra_bias_grad, h_dec, ctl, 0.0)
+        if skip_grad is not None:
+            e.dense_adam(m.skip_weight.data, self.skip_m, self.skip_v, skip_grad, h_dec, ctl, True, 0.0)
         e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v,
-                            self.feat_off, self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, self._hyper(lr, 1.0), self.status)
-        if self.fn == "jumprelu":
-            self._update_thresholds(lr, c_g, float(sparsity_lambda) if use_pen else 0.0)
-        e.dead_counter_update(self.dead_counter, self.fired)
-        self.kernel_launches += 5 + (1 if use_pen else 0)  # gs_colsum, decoder/encoder Adam, dense Adam, dead counters
+                            self.feat_off, self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, h_enc, self.status, None, None, None, ctl, False)
+        # dead-feature counters and the bias sums of the next step's loss epilogue
+        e.step_finish(self.dead_counter, self.fired, m.dec_bias.data, self.bias_sel, self.bias_sum)
+        self.kernel_launches += 6  # gs_colsum, decoder rows, decoder biases, encoder rows (+ bias), finish
         m.invalidate_decoder_norms()
-        recon = (self.sq_err.sum() / (B * d)).float()
-        sparsity = self.penalty[0].float()
-        if self.world > 1 and (use_pen or use_pre):
-            both = torch.stack([sparsity, pre_loss.float()])
-            pops.all_reduce(both, group=self.group)
-            sparsity, pre_loss = both[0], both[1]
-        return StepOutput(recon, sparsity, pre_loss, aux_loss, recon + sparsity + pre_loss + aux_loss, self.ctl[3])
+        out = StepOutput(losses, self.ctl[3])
+        self.last_output = out
+        return out
+
+    def _swap_norms(self) -> None:
+        self.norm2, self.norm2_next = self.norm2_next, self.norm2
+        self._norm_cur = 1 - self._norm_cur
+        self.norms_valid = True
 
     @torch.no_grad()
-    def _update_thresholds(self, lr: float, c_g: float, lam: float) -> None:
-        """AdamW step on ``log_threshold`` from the window sums of ``theta_grad_gemm``.
+    def _theta_update(self, lr: float, c_g: float, lam: float, norm_weight: float = 0.0) -> None:
+        """AdamW step on ``log_threshold`` from the window sums of ``theta_grad_gemm`` (one kernel).
 
         ``d loss / d theta[f] = -(1 / bw) * sum_b window * x * G`` with ``G = c_g * (gs . W rows)`` for the
         reconstruction and ``lam * c * n_f * sech^2(c * n_f * a)`` for the sparsity penalty; the latter is a
-        per-feature constant except at the active entries, which the entry list corrects
+        per-feature constant except at the active entries, which the feature's entry list corrects
         (reference: clt/models/activations.py:196-220 with clt/training/losses.py:179-185)."""
         m, tc = self.model, self.tc
-        bw = float(m.bandwidth)
-        g = c_g * self.S1
-        if lam > 0.0:
-            c = float(tc.sparsity_c)
-            norm = self.norm_at_step.view(self.L, self.Fl)
-            cap = self.ent_val.numel()
-            n = torch.clamp(self.ctl[3], max=cap)
-            live = torch.arange(cap, device=self.dev) < n
-            # unused slots add zero; they are spread over the columns so that they do not pile up on one address
-            col = torch.where(live, self.ent_col, (torch.arange(cap, device=self.dev, dtype=torch.int32) % self.ncols)).long()
-            x = torch.where(live, self.ent_val, torch.zeros_like(self.ent_val))
-            nf = norm.reshape(-1)[col]
-            inside = (x - self.theta.reshape(-1)[col]).abs() <= bw / 2
-            t2 = torch.tanh(c * nf * x) ** 2
-            corr = torch.zeros(self.ncols, dtype=torch.float32, device=self.dev)
-            corr.index_add_(0, col, torch.where(inside & live, x * t2, torch.zeros_like(x)))
-            g = g + lam * c * norm * (self.S2 - corr.view(self.L, self.Fl))
-        grad_theta = -g / bw
-        grad_log = (grad_theta * self.theta).contiguous()  # theta = exp(log_threshold)
-        self.grad_log_threshold = grad_log  # kept for diagnostics and tests
-        self.ext.dense_adam(m.log_threshold.data, self.theta_m, self.theta_v, grad_log, self._hyper(lr, 1.0))
+        self.ensure_norms()
+        self.ext.theta_adam(m.log_threshold.data, self.theta_m, self.theta_v, self.theta, self.S1, self.S2, self.norm2,
+                            self.feat_off, self.fcsr_val, self.tying, c_g, lam, float(tc.sparsity_c), float(m.bandwidth),
+                            self._hyper(lr, 1.0), self.step_ctl, norm_weight, self.grad_log_threshold)
         self.kernel_launches += 1
 
     # --------------------------------------------------------------- inference
@@ -609,7 +732,10 @@ class FusedBatchTopKEngine:
         self.encode_select(X)
         if Y is None:
             Y = torch.zeros_like(X)
-        return self.decode_loss(Y, want_yhat=True)
+        keep = self.step_ctl.clone()  # an inference forward must not disturb the loss-scale state
+        yhat = self.decode_loss(Y, want_yhat=True)
+        self.step_ctl.copy_(keep)
+        return yhat
 
     def activations_dense(self) -> torch.Tensor:
         """Dense ``[L, B, F_local]`` view of the last selection (testing / evaluation)."""
@@ -630,7 +756,8 @@ class FusedBatchTopKEngine:
     # ------------------------------------------------------- optimizer state io
     def optimizer_state_dict(self) -> Dict[str, torch.Tensor]:
         sd = {"step": torch.tensor(self.opt_step), "enc_m": self.enc_m, "enc_v": self.enc_v, "encb_m": self.encb_m,
-              "encb_v": self.encb_v, "decb_m": self.decb_m, "decb_v": self.decb_v, "dead_counter": self.dead_counter}
+              "encb_v": self.encb_v, "decb_m": self.decb_m, "decb_v": self.decb_v, "dead_counter": self.dead_counter,
+              "step_ctl": self.step_ctl}
         for i, (mm, vv) in enumerate(zip(self.dec_m, self.dec_v)):
             sd[f"dec_m.{i}"] = mm
             sd[f"dec_v.{i}"] = vv
@@ -653,4 +780,13 @@ class FusedBatchTopKEngine:
         if self.fn == "jumprelu" and "theta_m" in sd:
             self.theta_m.copy_(sd["theta_m"])
             self.theta_v.copy_(sd["theta_v"])
+        if "step_ctl" in sd:
+            self.step_ctl.copy_(sd["step_ctl"].to(self.step_ctl.dtype))
+        self.invalidate_cached()
+
+    def invalidate_cached(self) -> None:
+        """Forget everything derived from the parameters (after a checkpoint load or an external weight change)."""
         self.norms_valid = False
+        self._bias_sum_valid = False
+        if self.fn == "jumprelu":
+            self._theta_valid = False

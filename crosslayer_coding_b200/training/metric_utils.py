@@ -50,7 +50,10 @@ class MetricLogger:
         current_lr: Optional[float] = None,
         current_sparsity_lambda: Optional[float] = None,
     ) -> None:
-        if any(isinstance(v, torch.Tensor) for v in loss_dict.values()):
+        if isinstance(loss_dict.get("_vector"), torch.Tensor):
+            # the fused step hands over its loss terms as one device vector in LOSS_KEYS order: nothing to launch here
+            self._pending.append((step, loss_dict["_vector"][: len(LOSS_KEYS)], current_lr, current_sparsity_lambda))
+        elif any(isinstance(v, torch.Tensor) for v in loss_dict.values()):
             dev = next(v.device for v in loss_dict.values() if isinstance(v, torch.Tensor))
             vec = torch.stack([
                 (loss_dict.get(k) if isinstance(loss_dict.get(k), torch.Tensor) else torch.tensor(float(loss_dict.get(k, 0.0)), device=dev)).detach().float().reshape(())
@@ -58,7 +61,7 @@ class MetricLogger:
             ])
             self._pending.append((step, vec, current_lr, current_sparsity_lambda))
         else:
-            self.metrics["train_losses"].append({"step": step, **{k: float(v) for k, v in loss_dict.items()}})
+            self.metrics["train_losses"].append({"step": step, **{k: float(v) for k, v in loss_dict.items() if not k.startswith("_")}})
             if self.wandb_logger is not None and (not self.distributed or self.rank == 0):
                 tokens = self.training_config.train_batch_size_tokens * (step + 1)
                 self.wandb_logger.log_step(step, loss_dict, lr=current_lr, sparsity_lambda=current_sparsity_lambda,

@@ -204,10 +204,10 @@ class CLTTrainer:
             reason = "no CUDA device"
         else:
             reason = engine_supports(self.clt_config, tc, self.model)
-            if reason is None and want == "auto" and self.clt_config.activation_fn == "jumprelu":
-                # the fused JumpReLU step keeps the active entries in lists of fused_max_active_per_token per token;
-                # a run that starts dense (the default threshold 0.03 does) has to start on the autograd step
-                reason = "jumprelu takes the fused step only with engine='fused' (it needs sparse activations throughout)"
+            if reason is None and want == "auto" and self.clt_config.activation_fn in ("jumprelu", "relu"):
+                # the fused threshold step keeps the active entries in lists of fused_max_active_per_token per token; whether
+                # a run is sparse enough for them is decided on its first batch (see _probe_density)
+                self._probe_pending = True
             if reason is None and self.world_size > 1:
                 from ..parallel.symm import SymmetricExchange
 
@@ -225,6 +225,10 @@ class CLTTrainer:
         if want == "fused":
             raise ValueError(f"engine='fused' requested but not available: {reason}")
         logger.info("Rank %d: using the autograd step (%s)", self.rank, reason)
+        self._build_autograd_optimizer()
+
+    def _build_autograd_optimizer(self) -> None:
+        tc = self.training_config
         kwargs: Dict[str, Any] = {"lr": tc.learning_rate}
         if tc.optimizer_beta1 is not None or tc.optimizer_beta2 is not None:
             kwargs["betas"] = (tc.optimizer_beta1 if tc.optimizer_beta1 is not None else 0.9,
@@ -266,9 +270,36 @@ class CLTTrainer:
         """One optimisation step; returns the loss terms as device scalars (no host sync)."""
         tc = self.training_config
         lr = learning_rate_at(tc, step)
+        if self.engine is not None and getattr(self, "_probe_pending", False):
+            self._probe_density(inputs)
         if self.engine is not None:
             return self._train_step_fused(inputs, targets, step, lr)
         return self._train_step_autograd(inputs, targets, step, lr)
+
+    def _probe_density(self, inputs) -> None:
+        """engine="auto" with JumpReLU / ReLU: one selection pass over the first batch decides between the two step
+        implementations.  The fused step holds at most ``fused_max_active_per_token`` active entries per token; a model
+        that starts denser than half of that (the reference's default threshold 0.03 on unit-variance inputs does) takes
+        the autograd step, whose dense kernels are the better fit there.  All ranks take the same branch."""
+        self._probe_pending = False
+        eng, tc = self.engine, self.training_config
+        layers = list(range(self.clt_config.num_layers))
+        X = _stack_layers(inputs, layers).to(eng.t16)
+        eng.encode_select(X)
+        per_token = (eng.ctl[3].float() / eng.B).reshape(1)
+        if self.world_size > 1:
+            pops.all_reduce(per_token, group=self.process_group)
+        too_dense = torch.tensor([float(per_token.item()) > 0.5 * tc.fused_max_active_per_token or int(eng.status[0].item()) != 0],
+                                 dtype=torch.int32, device=self.device)
+        if self.world_size > 1:
+            pops.all_reduce(too_dense, op=pops.MAX, group=self.process_group)
+        eng.status.zero_()
+        eng.fired.zero_()
+        if bool(too_dense.item()):
+            logger.info("Rank %d: %.0f active features per token on the first batch: using the autograd step", self.rank, float(per_token.item()))
+            self.engine = None
+            self._build_autograd_optimizer()
+            self.n_forward_passes_since_fired = torch.zeros(self.clt_config.num_layers, self.model.valid_features, dtype=torch.long, device=self.device)
 
     def _train_step_fused(self, inputs, targets, step: int, lr: float) -> Dict[str, torch.Tensor]:
         tc, eng = self.training_config, self.engine
@@ -276,8 +307,8 @@ class CLTTrainer:
         with self.profiler.timer("forward_pass"):
             X = _stack_layers(inputs, layers)
             Y = _stack_layers(targets, layers)
-            if X.dtype != torch.bfloat16:
-                X, Y = X.to(torch.bfloat16), Y.to(torch.bfloat16)
+            if X.dtype != eng.t16:
+                X, Y = X.to(eng.t16), Y.to(eng.t16)
         lam = sparsity_lambda_at(tc, step, tc.training_steps)
         if self.clt_config.activation_fn == "batchtopk" and not tc.apply_sparsity_penalty_to_batchtopk:
             lam = 0.0
@@ -463,8 +494,8 @@ class CLTTrainer:
             if fused_eval:
                 layers = list(range(self.clt_config.num_layers))
                 X, Y = _stack_layers(inputs, layers), _stack_layers(targets, layers)
-                if X.dtype != torch.bfloat16:
-                    X, Y = X.to(torch.bfloat16), Y.to(torch.bfloat16)
+                if X.dtype != self.engine.t16:
+                    X, Y = X.to(self.engine.t16), Y.to(self.engine.t16)
                 metrics = self.evaluator.compute_metrics_from_engine(self.engine, X, Y, dead_neuron_mask=self.dead_neurons_mask)
             else:
                 autocast = torch.autocast(device_type=self.device.type, dtype=self.autocast_dtype, enabled=self.autocast_enabled)

@@ -1,0 +1,289 @@
+"""Fused step: gradient magnitudes, multi-step trajectories against torch.optim.AdamW, the device-side step control
+(non-finite skip, fp16 loss scaling, gradient clipping), ReLU training and JumpReLU with tied decoders.
+Every kernel result is compared with a plain PyTorch fp32 restatement of the same step."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SC_SKIP, SC_INV_SCALE, SC_LOSS_SCALE, SC_GROWTH, SC_FOUND_INF, SC_GRAD_NORM_SQ, SC_CLIP, SC_SKIPPED = range(8)
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _make(fn="batchtopk", tying="none", dtype="bfloat16", L=3, B=192, d=64, F=256, k=6, seed=0, theta=0.35, **tc_kw):
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder, TrainingConfig
+    from crosslayer_coding_b200.training.fused_engine import FusedBatchTopKEngine
+
+    torch.manual_seed(seed)
+    dev = _dev()
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=fn, batchtopk_k=k, clt_dtype=dtype, decoder_tying=tying,
+                    jumprelu_threshold=theta)
+    model = CrossLayerTranscoder(cfg, device=dev)
+    with torch.no_grad():
+        model.enc_weight.normal_(0, 1.0 / math.sqrt(d))
+        if tying != "none":
+            for w in model.dec_weight:
+                w.uniform_(-0.05, 0.05)
+    kw = dict(learning_rate=1e-3, training_steps=100, activation_path="unused", precision=("fp16" if dtype == "float16" else "bf16"),
+              sparsity_lambda=0.0, preactivation_coef=0.0, optimizer="adamw")
+    kw.update(tc_kw)
+    tc = TrainingConfig(**kw)
+    eng = FusedBatchTopKEngine(model, tc, B)
+    t16 = torch.float16 if dtype == "float16" else torch.bfloat16
+    X = torch.randn(L, B, d, device=dev).to(t16)
+    Y = torch.randn(L, B, d, device=dev).to(t16)
+    return cfg, model, tc, eng, X, Y
+
+
+def _fp32_copy(model):
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder
+
+    cfg = CLTConfig(**{**model.config.to_dict(), "clt_dtype": "float32"})
+    ref = CrossLayerTranscoder(cfg, device=model.enc_weight.device)
+    with torch.no_grad():
+        for (_, a), (_, b) in zip(ref.named_parameters(), model.named_parameters()):
+            a.copy_(b.float())
+    return ref
+
+
+def _reference_loss(ref, eng, X, Y, lam, tc):
+    """Loss of the fp32 model on the entries that the engine selected (pre-activations as the kernels saw them)."""
+    L = ref.config.num_layers
+    dense = eng.activations_dense()
+    mask = dense != 0
+    pre = {l: torch.nn.functional.linear(X[l].float(), ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    acts = {l: (pre[l] + (eng.preact[l].float() - pre[l]).detach()) * mask[l] for l in range(L)}
+    loss = sum(torch.nn.functional.mse_loss(ref.decode({s: acts[s] for s in range(t + 1)}, t), Y[t].float()) for t in range(L))
+    if lam > 0:
+        ref.invalidate_decoder_norms()  # the cached norms belong to the previous step's graph
+        norms = ref.get_decoder_norms()
+        loss = loss + lam * sum(torch.tanh(tc.sparsity_c * acts[l] * norms[l][None, :]).sum() for l in range(L))
+    return loss
+
+
+def _rel_err(a, b):
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+@pytest.mark.parametrize("tying", ["none", "per_source", "per_target"])
+@pytest.mark.parametrize("lam", [0.0, 0.05])
+def test_first_moments_equal_autograd_gradients(tying, lam):
+    """After one step from zero moments, m / (1 - beta1) is the gradient itself: a wrong factor in the gradient scale, the
+    penalty coefficient or dL/da shows up here (the weight update of a first Adam step only shows the sign)."""
+    cfg, model, tc, eng, X, Y = _make(tying=tying, seed=11)
+    ref = _fp32_copy(model)
+    eng.train_step(X, Y, step=0, lr=1e-3, sparsity_lambda=lam)
+    torch.cuda.synchronize()
+    eng.check_status()
+    _reference_loss(ref, eng, X, Y, lam, tc).backward()
+    b1 = 0.9
+    for i, w in enumerate(ref.dec_weight):
+        assert _rel_err(eng.dec_m[i] / (1 - b1), w.grad) < 2e-2, (tying, lam, i)
+    assert _rel_err(eng.enc_m / (1 - b1), ref.enc_weight.grad) < 2e-2
+    assert _rel_err(eng.encb_m / (1 - b1), ref.enc_bias.grad) < 2e-2
+    assert _rel_err(eng.decb_m / (1 - b1), ref.dec_bias.grad) < 2e-2
+
+
+def test_five_step_trajectory_tracks_adamw():
+    """Five fused steps against five steps of torch.optim.AdamW on an fp32 copy fed with the engine's own selections."""
+    cfg, model, tc, eng, X, Y = _make(seed=13)
+    ref = _fp32_copy(model)
+    start = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3)
+    for step in range(5):
+        eng.train_step(X, Y, step=step, lr=1e-3, sparsity_lambda=0.02)
+        torch.cuda.synchronize()
+        opt.zero_grad()
+        _reference_loss(ref, eng, X, Y, 0.02, tc).backward()
+        opt.step()
+    eng.check_status()
+    refp = dict(ref.named_parameters())
+    for n, p in model.named_parameters():
+        moved = refp[n].detach() - start[n]
+        got = p.detach().float() - start[n]
+        # bf16 weights: each of the five updates is rounded to 8 bits of mantissa, so the end point is compared in units of
+        # the weight's own spacing (2^-8 relative), the direction of the move as a whole
+        ulp = refp[n].detach().abs() * 2.0 ** -8 + 1e-6
+        off = ((p.detach().float() - refp[n].detach()).abs() > 3.0 * ulp).float().mean().item()
+        assert off < 5e-3, (n, off)
+        assert _rel_err(got, moved) < 0.35, (n, _rel_err(got, moved))
+        cos = float((got * moved).sum() / (got.norm() * moved.norm() + 1e-12))
+        assert cos > 0.93, (n, cos)
+
+
+def test_nonfinite_target_skips_the_step():
+    cfg, model, tc, eng, X, Y = _make(seed=3)
+    eng.train_step(X, Y, step=0, lr=1e-3)
+    torch.cuda.synchronize()
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    m_before = eng.dec_m[0].clone()
+    bad = Y.clone()
+    bad[1, 5, 3] = float("nan")
+    out = eng.train_step(X, bad, step=1, lr=1e-3)
+    torch.cuda.synchronize()
+    assert int(eng.step_ctl[SC_SKIP].view(torch.int32)) == 1 and int(out.skipped_steps) == 1
+    for n, p in model.named_parameters():
+        assert torch.equal(p.detach(), before[n]), n
+    assert torch.equal(eng.dec_m[0], m_before)
+    out = eng.train_step(X, Y, step=2, lr=1e-3)  # the next clean step is applied again
+    torch.cuda.synchronize()
+    assert int(eng.step_ctl[SC_SKIP].view(torch.int32)) == 0 and not torch.equal(model.dec_weight[0].detach(), before["dec_weight.0"])
+    assert math.isfinite(float(out.total))
+
+
+@pytest.mark.parametrize("tying", ["none", "per_source"])
+def test_fp16_loss_scaling_backs_off_then_trains(tying):
+    """fp16 weights and gradient seed with the dynamic loss scale on the device: the initial scale overflows the fp16 seed,
+    the step is skipped and the scale halves (GradScaler's policy); once it fits, the update equals the unscaled one."""
+    cfg, model, tc, eng, X, Y = _make(tying=tying, dtype="float16", seed=5, loss_scale_init=2.0 ** 17, loss_scale_growth_interval=3)
+    assert eng.fp16 and float(eng.step_ctl[SC_LOSS_SCALE]) == 2.0 ** 17
+    w0 = model.dec_weight[0].detach().clone()
+    out = eng.train_step(X, Y, step=0, lr=1e-3)          # |gs| ~ a few units * 131072 > 65504: overflow
+    torch.cuda.synchronize()
+    assert int(out.skipped_steps) == 1 and float(eng.step_ctl[SC_LOSS_SCALE]) == 2.0 ** 16
+    assert torch.equal(model.dec_weight[0].detach(), w0)
+    scales = []
+    for step in range(1, 12):
+        out = eng.train_step(X, Y, step=step, lr=1e-3)
+        scales.append(float(out.loss_scale))
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert min(scales) < 2.0 ** 16 and int(out.skipped_steps) < 11      # it backed off further and then trained
+    assert not torch.equal(model.dec_weight[0].detach(), w0)
+    # a clean step at a fitting scale: the moments hold unscaled gradients
+    cfg2, model2, tc2, eng2, _, _ = _make(tying=tying, dtype="float16", seed=5, loss_scale_init=256.0, loss_scale_growth_interval=4)
+    ref = _fp32_copy(model2)
+    eng2.train_step(X, Y, step=0, lr=1e-3)
+    torch.cuda.synchronize()
+    assert int(eng2.step_ctl[SC_SKIP].view(torch.int32)) == 0
+    _reference_loss(ref, eng2, X, Y, 0.0, tc2).backward()
+    assert _rel_err(eng2.dec_m[0] / 0.1, ref.dec_weight[0].grad) < 2e-2
+    assert _rel_err(eng2.enc_m / 0.1, ref.enc_weight.grad) < 2e-2
+    # growth: after `growth_interval` clean steps the scale doubles
+    for step in range(1, 4):
+        out = eng2.train_step(X, Y, step=step, lr=1e-3)
+    torch.cuda.synchronize()
+    assert float(eng2.step_ctl[SC_LOSS_SCALE]) == 512.0
+
+
+@pytest.mark.parametrize("tying", ["none", "per_target"])
+def test_gradient_clipping_by_global_norm(tying):
+    """gradient_clip_val: the norm pre-pass reports the global gradient norm and the update uses clipped gradients."""
+    lam = 0.03
+    cfg, model, tc, eng, X, Y = _make(tying=tying, seed=17, gradient_clip_val=0.05)
+    ref = _fp32_copy(model)
+    out = eng.train_step(X, Y, step=0, lr=1e-3, sparsity_lambda=lam)
+    torch.cuda.synchronize()
+    eng.check_status()
+    _reference_loss(ref, eng, X, Y, lam, tc).backward()
+    total = torch.sqrt(sum((p.grad.float() ** 2).sum() for p in ref.parameters() if p.grad is not None))
+    assert abs(float(out.grad_norm) - float(total)) < 2e-2 * float(total), (float(out.grad_norm), float(total))
+    coef = min(1.0, 0.05 / (float(total) + 1e-6))
+    assert coef < 1.0 and abs(float(eng.step_ctl[SC_CLIP]) - coef) < 2e-2 * coef
+    assert _rel_err(eng.dec_m[0] / 0.1, ref.dec_weight[0].grad * coef) < 3e-2
+    assert _rel_err(eng.enc_m / 0.1, ref.enc_weight.grad * coef) < 3e-2
+    assert _rel_err(eng.decb_m / 0.1, ref.dec_bias.grad * coef) < 3e-2
+    # a generous limit leaves the step unchanged
+    _, model_a, _, eng_a, _, _ = _make(tying=tying, seed=17, gradient_clip_val=1e6)
+    _, model_b, _, eng_b, _, _ = _make(tying=tying, seed=17)
+    eng_a.train_step(X, Y, step=0, lr=1e-3, sparsity_lambda=lam)
+    eng_b.train_step(X, Y, step=0, lr=1e-3, sparsity_lambda=lam)
+    torch.cuda.synchronize()
+    assert torch.allclose(eng_a.enc_m, eng_b.enc_m, rtol=1e-4, atol=1e-7) and torch.equal(model_a.dec_weight[0], model_b.dec_weight[0])
+
+
+def _jumprelu_reference(ref, eng, X, Y, lam, tc):
+    """Dense fp32 JumpReLU step with the straight-through threshold gradient, on the pre-activations the kernels saw."""
+    from crosslayer_coding_b200.models import activations as act
+
+    L = ref.config.num_layers
+    acts = {}
+    for l in range(L):
+        pre = torch.nn.functional.linear(X[l].float(), ref.enc_weight[l], ref.enc_bias[l])
+        pre = pre + (eng.preact[l].float() - pre).detach()
+        acts[l] = act.JumpReLU.apply(pre, ref.log_threshold[l].exp(), ref.bandwidth)
+    loss = sum(torch.nn.functional.mse_loss(ref.decode({s: acts[s] for s in range(t + 1)}, t), Y[t].float()) for t in range(L))
+    if lam > 0:
+        norms = ref.get_decoder_norms()
+        loss = loss + lam * sum(torch.tanh(tc.sparsity_c * acts[l] * norms[l][None, :]).sum() for l in range(L))
+    return loss
+
+
+@pytest.mark.parametrize("tying", ["per_source", "per_target"])
+@pytest.mark.parametrize("lam", [0.0, 0.02])
+def test_fused_jumprelu_with_tied_decoders_matches_autograd(tying, lam):
+    cfg, model, tc, eng, X, Y = _make(fn="jumprelu", tying=tying, seed=23, B=256, F=256, d=64, theta=1.2)
+    ref = _fp32_copy(model)
+    eng.train_step(X, Y, step=0, lr=1e-3, sparsity_lambda=lam)
+    torch.cuda.synchronize()
+    eng.check_status()
+    _jumprelu_reference(ref, eng, X, Y, lam, tc).backward()
+    g = ref.log_threshold.grad
+    assert _rel_err(eng.grad_log_threshold, g) < 3e-2, _rel_err(eng.grad_log_threshold, g)
+    assert _rel_err(eng.theta_m / 0.1, g) < 3e-2
+    for i, w in enumerate(ref.dec_weight):
+        assert _rel_err(eng.dec_m[i] / 0.1, w.grad) < 2e-2
+    assert _rel_err(eng.enc_m / 0.1, ref.enc_weight.grad) < 2e-2
+
+
+def test_fused_relu_training_step_matches_autograd():
+    cfg, model, tc, eng, X, Y = _make(fn="relu", seed=29, B=128, F=128, d=64, fused_max_active_per_token=512)
+    with torch.no_grad():
+        model.enc_bias.fill_(-1.6)  # sparse enough for the entry lists
+    ref = _fp32_copy(model)
+    out = eng.train_step(X, Y, step=0, lr=1e-3, sparsity_lambda=0.01)
+    torch.cuda.synchronize()
+    eng.check_status()
+    L = cfg.num_layers
+    pre = {l: torch.nn.functional.linear(X[l].float(), ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    acts = {l: torch.relu(pre[l] + (eng.preact[l].float() - pre[l]).detach()) for l in range(L)}
+    assert torch.equal(eng.activations_dense() != 0, torch.stack([acts[l] for l in range(L)]) > 0)
+    loss = sum(torch.nn.functional.mse_loss(ref.decode({s: acts[s] for s in range(t + 1)}, t), Y[t].float()) for t in range(L))
+    norms = ref.get_decoder_norms()
+    loss = loss + 0.01 * sum(torch.tanh(tc.sparsity_c * acts[l] * norms[l][None, :]).sum() for l in range(L))
+    loss.backward()
+    assert abs(float(out.total) - float(loss)) < 5e-3 * abs(float(loss))
+    assert _rel_err(eng.enc_m / 0.1, ref.enc_weight.grad) < 2e-2
+    assert _rel_err(eng.dec_m[0] / 0.1, ref.dec_weight[0].grad) < 2e-2
+
+
+def test_exact_cut_with_heavy_ties_is_world_invariant_and_lowest_index_first():
+    """Many identical z-scores at the cut (constant columns give equal keys): the gathered exact cut keeps the lowest
+    flat indices, whatever the number of candidates; with more ties than the one-round gather holds the radix rounds
+    give the same answer."""
+    from crosslayer_coding_b200.ops import ext as ext_mod
+
+    e = ext_mod.load()
+    dev = _dev()
+    for B, F, k in ((8, 16, 5), (64, 128, 5), (512, 1024, 3)):  # gathered cut; radix rounds; radix rounds, large
+        L = 2
+        x = torch.zeros(L, B, F, device=dev)
+        x[:, ::2, :] = 1.0          # every column: half the rows at 1, half at 0 -> two distinct z values, massive ties
+        x[0, 1, 7] = 3.0            # a few distinct larger ones
+        x = x.bfloat16().contiguous()
+        mean = torch.empty(L, F, device=dev)
+        rstd = torch.empty(L, F, device=dev)
+        e.colstats(x, mean, rstd)
+        k_total = k * B
+        i32, f32 = torch.int32, torch.float32
+        hist = torch.zeros(2 * 8192 + 32, dtype=i32, device=dev)
+        ctl = torch.zeros(16, dtype=torch.int64, device=dev)
+        status = torch.zeros(4, dtype=i32, device=dev)
+        cap = L * B * F
+        ent = [torch.empty(cap, dtype=i32, device=dev), torch.empty(cap, dtype=i32, device=dev), torch.empty(cap, dtype=f32, device=dev)]
+        cand = [torch.empty(cap, dtype=i32, device=dev), torch.empty(cap, dtype=i32, device=dev), torch.empty(cap, dtype=i32, device=dev),
+                torch.empty(cap, dtype=f32, device=dev)]
+        e.batchtopk_select(x, mean, rstd, F, F, 0, F, k_total, 0, 19, hist, ctl, ent[0], ent[1], ent[2], cand[0], cand[1], cand[2], cand[3],
+                           status, 1, 0, [], [], 0, 0, None, None)
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0 and int(ctl[3]) == k_total
+        n = k_total
+        flat = ent[0][:n].long() * (L * F) + ent[1][:n].long()
+        z = ((x.float() - mean[:, None, :]) * rstd[:, None, :]).permute(1, 0, 2).reshape(-1)   # flat index = b * L * F + l * F + f
+        order = torch.sort(z, descending=True, stable=True).indices[:n]                           # stable: lowest index first among ties
+        assert torch.equal(torch.sort(flat).values, torch.sort(order).values)

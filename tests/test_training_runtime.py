@@ -214,9 +214,12 @@ def test_in_memory_store_and_fused_engine_gate():
     cfg = CLTConfig(num_features=F, num_layers=L, d_model=D, activation_fn="batchtopk", batchtopk_k=2, clt_dtype="bfloat16")
     tc = TrainingConfig(learning_rate=1e-3, training_steps=5, activation_path="x", preactivation_coef=0.0, precision="bf16")
     assert engine_supports(cfg, tc) is None
-    assert engine_supports(CLTConfig(num_features=F, num_layers=L, d_model=D, activation_fn="relu"), tc) is not None
-    assert "clipping" in engine_supports(cfg, TrainingConfig(learning_rate=1e-3, training_steps=5, activation_path="x",
-                                                              preactivation_coef=0.0, gradient_clip_val=1.0))
+    assert engine_supports(CLTConfig(num_features=F, num_layers=L, d_model=D + 1, activation_fn="relu"), tc) is not None  # d_model % 8
+    # gradient clipping, ReLU and fp16 (with fp16 weights) are covered by the fused step
+    assert engine_supports(cfg, TrainingConfig(learning_rate=1e-3, training_steps=5, activation_path="x",
+                                               preactivation_coef=0.0, gradient_clip_val=1.0)) is None
+    assert engine_supports(CLTConfig(num_features=F, num_layers=L, d_model=D, activation_fn="relu", clt_dtype="bfloat16"), tc) is None
+    assert engine_supports(CLTConfig(num_features=F, num_layers=L, d_model=D, activation_fn="batchtopk", batchtopk_k=2, topk_mode="per_layer"), tc) is not None
     pool = torch.randn(3, 2, L, B, D)
     st = InMemoryActivationStore(pool, "cpu", loop=False)
     got = [x.stacked.clone() for x, _ in st]
