@@ -1153,6 +1153,19 @@ static int launch_rows_adam_bulk(const DecAdamParams& p, bool weights_bf16, bool
   per_sm = per_sm < 1 ? 1 : (per_sm > 6 ? 6 : per_sm);
   int bgrid = num_sms * per_sm;
   if (bgrid > p.F_pitch) bgrid = p.F_pitch;
+  {
+    // CTA b owns the features b, b + grid, ... of every tensor: pick the grid (between half of the resident slots and all
+    // of them) that splits the features most evenly, so that no CTA still streams rows when the others are done.  On a
+    // narrow shard (3072 features, 888 slots) the naive grid leaves CTAs with 3 and with 4 features per tensor.
+    int best = bgrid;
+    double best_waste = double((p.F_pitch + bgrid - 1) / bgrid) * bgrid / double(p.F_pitch) - 0.03;  // a few per cent do not pay for fewer CTAs
+    for (int g = bgrid - 1; g >= (3 * bgrid) / 4 && g >= 1; --g) {
+      const int per = (p.F_pitch + g - 1) / g;
+      const double waste = double(per) * g / double(p.F_pitch);
+      if (waste < best_waste - 1e-9) { best_waste = waste; best = g; }
+    }
+    bgrid = best;
+  }
   auto launch = [&](auto kern, int which) -> int {
     static size_t attr_set[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     if (attr_set[which] < smem) {

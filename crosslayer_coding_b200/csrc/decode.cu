@@ -384,9 +384,9 @@ __global__ void __launch_bounds__(256) recon_epilogue_kernel(const float* __rest
 }
 
 // Column sums of the gradient seed: out[t, :] += sum_b gs[t, b, :]  (decoder-bias gradient up to a constant).
-// blockDim = (d / 8 rounded up to 32, 256 / that): a thread owns 8 adjacent columns (one 16-byte load per row), the
-// threadIdx.y rows of a block walk the block's row range, shared memory folds them, one atomic per column and block.
-__global__ void __launch_bounds__(256) gs_colsum_kernel(const t16* __restrict__ gs, float* __restrict__ out, int B, int d,
+// blockDim = (d / 8 rounded up to 32, up to 8 row lanes): a thread owns 8 adjacent columns (one 16-byte load per row), the
+// threadIdx.y lanes of a block walk the block's row range, shared memory folds them, one atomic per column and block.
+__global__ void __launch_bounds__(1024) gs_colsum_kernel(const t16* __restrict__ gs, float* __restrict__ out, int B, int d,
                                                           int rows_per_block) {
   const int t = blockIdx.z;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
@@ -402,7 +402,7 @@ __global__ void __launch_bounds__(256) gs_colsum_kernel(const t16* __restrict__ 
       for (int j = 0; j < 4; ++j) { s[2 * j] += t16_lo(u[j]); s[2 * j + 1] += t16_hi(u[j]); }
     }
   }
-  __shared__ float red[256][9];
+  __shared__ float red[1024][9];
   const int lin = threadIdx.y * blockDim.x + threadIdx.x;
 #pragma unroll
   for (int j = 0; j < 8; ++j) red[lin][j] = s[j];
@@ -515,9 +515,9 @@ extern "C" int CLT_FN(clt_recon_epilogue)(const float* yhat_sum, const float* bi
 
 extern "C" int CLT_FN(clt_gs_colsum)(const void* gs, float* out, int L, int B, int d, cudaStream_t st) {
   if (d % 8 != 0) return -1;
-  const int tx = d / 8 >= 256 ? 256 : ((d / 8 + 31) / 32) * 32;
-  const int ty = 256 / tx;
-  const int rpb = 256;
+  const int tx = d / 8 >= 128 ? 128 : ((d / 8 + 31) / 32) * 32;
+  const int ty = 1024 / tx < 8 ? 1024 / tx : 8;
+  const int rpb = 128;
   dim3 grid((d / 8 + tx - 1) / tx, (B + rpb - 1) / rpb, L), block(tx, ty);
   gs_colsum_kernel<<<grid, block, 0, st>>>(static_cast<const t16*>(gs), out, B, d, rpb);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

@@ -103,6 +103,17 @@ def main() -> None:
             "decode_loss_ms": _best_of(lambda: eng.decode_loss(Y)),
             "train_step_ms": _best_of(full, 6),
         }
+        # host side of a step: enqueue time of one train_step on an idle device (nothing in it waits for the GPU)
+        import time as _time
+
+        host = []
+        for _ in range(5):
+            torch.cuda.synchronize()
+            t0 = _time.perf_counter()
+            full()
+            host.append((_time.perf_counter() - t0) * 1e3)
+        torch.cuda.synchronize()
+        res["host_enqueue_ms"] = min(host)
         flops = 2.0 * L * B * F * d
         res["encoder_gemm_tflops"] = flops / res["encoder_gemm_ms"] / 1e9
         res["library_bmm_tflops"] = flops / res["library_bmm_ms"] / 1e9

@@ -30,6 +30,9 @@ def main():
     ap.add_argument("--features", type=int, default=512)
     ap.add_argument("--lam", type=float, default=0.0)
     ap.add_argument("--activation", default="batchtopk")
+    ap.add_argument("--tying", default="none")
+    ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--clip", type=float, default=0.0)
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -41,13 +44,19 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
     L, d, F, B, k = 3, 64, args.features, 128, 8
-    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k, clt_dtype="bfloat16",
-                    jumprelu_threshold=0.25)
+    t16 = torch.float16 if args.dtype == "float16" else torch.bfloat16
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k, clt_dtype=args.dtype,
+                    jumprelu_threshold=0.25, decoder_tying=args.tying)
     full_state = build_full_state(cfg)
+    if args.tying != "none":  # tied decoders start at zero; give them values so that the first steps have a signal
+        gen = torch.Generator().manual_seed(99)
+        for key in list(full_state):
+            if key.startswith("decoder_module.decoders.") and key.endswith(".weight"):
+                full_state[key] = (torch.rand(full_state[key].shape, generator=gen) * 0.1 - 0.05).to(full_state[key].dtype)
     model = CrossLayerTranscoder(cfg, process_group=group, device=dev)
     model.load_state_dict(slice_for_rank(full_state, rank, world, F) if world > 1 else full_state)
-    tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="bf16",
-                        sparsity_lambda=args.lam, preactivation_coef=0.0)
+    tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="fp16" if args.dtype == "float16" else "bf16",
+                        sparsity_lambda=args.lam, preactivation_coef=0.0, gradient_clip_val=(args.clip or None), loss_scale_init=1024.0)
     symm = None
     if world > 1:
         from crosslayer_coding_b200.parallel.symm import SymmetricExchange
@@ -55,13 +64,14 @@ def main():
         symm = SymmetricExchange.create(group, dev, cfg, B)
     eng = FusedBatchTopKEngine(model, tc, B, symm=symm)
     g = torch.Generator().manual_seed(7)
-    X = torch.randn(L, B, d, generator=g).bfloat16().to(dev)
+    X = torch.randn(L, B, d, generator=g).to(t16).to(dev)
     A = torch.randn(d, d, generator=g) / d ** 0.5
-    Y = (X.float().cpu() @ A).bfloat16().to(dev)
-    losses, entries = [], []
+    Y = (X.float().cpu() @ A).to(t16).to(dev)
+    losses, entries, norms = [], [], []
     for step in range(args.steps):
         out = eng.train_step(X, Y, step, 1e-3, sparsity_lambda=args.lam)
-        losses.append(float(out.reconstruction))
+        losses.append(float(out.total))
+        norms.append(float(out.grad_norm))
         n = out.num_entries.clone().float()
         if world > 1:
             dist.all_reduce(n)
@@ -112,7 +122,7 @@ def main():
     else:
         merged = sd
     if rank == 0:
-        torch.save({"losses": losses, "entries": entries, "state": merged, "world": world, "staging_ok": bool(flag.item() == 1.0),
+        torch.save({"losses": losses, "entries": entries, "grad_norms": norms, "skipped": float(out.skipped_steps), "state": merged, "world": world, "staging_ok": bool(flag.item() == 1.0),
                     "h2d_bytes_per_rank": store.h2d_bytes_per_rank, "h2d_bytes": store.h2d_bytes_per_batch}, args.out)
     if world > 1:
         dist.barrier()
