@@ -79,6 +79,14 @@ def quick_l0_check(model, inputs: Dict[int, torch.Tensor], num_tokens: int = 102
 def l0_for_scales(preact: torch.Tensor, theta: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """``L0(s) = mean_tokens #{f : x_f >= s * theta_f}`` for every ``s`` in the ascending vector ``scales``,
     from a single pass over ``preact [B, F]``."""
+    if preact.is_cuda and preact.dtype in (torch.bfloat16, torch.float16) and preact.dim() == 2 and scales.numel() <= 1024:
+        # one kernel pass over the 16-bit pre-activations (csrc/step.cu: scale_histogram_kernel)
+        from .ops import ext
+
+        hist = torch.empty(scales.numel() + 1, dtype=torch.int64, device=preact.device)
+        ext.load().scale_histogram(preact.contiguous(), theta.float().contiguous(), scales.float().contiguous(), hist)
+        active = torch.flip(torch.cumsum(torch.flip(hist.double(), dims=[0]), dim=0), dims=[0])[1:]
+        return (active / preact.shape[0]).float()
     ratio = (preact.float() / theta.float().clamp_min(1e-30)).reshape(-1)
     ratio = ratio[ratio >= scales[0]]
     # number of scales that an element satisfies = index of the first scale above its ratio
@@ -129,9 +137,10 @@ def calibrate_layerwise_theta(
             gen = torch.Generator(device="cpu")
             gen.manual_seed(int(seed if seed is not None else 0) + l)
             x_l = x_l[torch.randperm(x_l.shape[0], generator=gen)[: int(max_tokens)].to(x_l.device)]
-        pre = model.get_preactivations(x_l.to(dev), l, gather=False).float()
+        pre16 = model.get_preactivations(x_l.to(dev), l, gather=False)
+        pre = pre16.float()
         theta = model.log_threshold[l][: pre.shape[-1]].float().exp()
-        l0s = l0_for_scales(pre, theta, scales)
+        l0s = l0_for_scales(pre16 if pre16.dtype in (torch.bfloat16, torch.float16) else pre, theta, scales)
         if model.world_size > 1:
             pops.all_reduce(l0s, group=model.process_group)
         tgt = float(target_l0[l])

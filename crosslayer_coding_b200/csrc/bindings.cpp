@@ -706,6 +706,41 @@ void theta_exp(const Tensor& log_theta, Tensor& theta) {
   check(CLT_PICK(half, clt_theta_exp)(log_theta.data_ptr(), theta.data_ptr<float>(), log_theta.numel(), w16, cur_stream()), "theta_exp");
 }
 
+// out = ((in - mean) * inv_std) * mul cast to out's 16-bit type; in: [..., rows, d] fp32 / bf16 / fp16, mean / inv_std (optional):
+// one row of d statistics per rows_per_stat consecutive rows.
+void normalize_cast(const Tensor& in, Tensor& out, const OptTensor& mean, const OptTensor& inv_std, int64_t rows_per_stat, double mul) {
+  const bool half = is_half(out, "out");
+  need(out, t16_of(half), "out");
+  TORCH_CHECK(in.is_cuda() && in.is_contiguous() && in.numel() == out.numel() && in.dim() >= 2, "in / out: contiguous CUDA tensors of one shape");
+  const int in_type = in.scalar_type() == at::kFloat ? 0 : in.scalar_type() == at::kBFloat16 ? 1 : in.scalar_type() == at::kHalf ? 2 : -1;
+  TORCH_CHECK(in_type >= 0, "in must be fp32, bf16 or fp16");
+  const int d = int(in.size(-1));
+  const long long rows = in.numel() / d;
+  const float* mp = nullptr; const float* sp = nullptr;
+  if (mean.has_value() && mean->defined()) {
+    need(*mean, at::kFloat, "mean"); TORCH_CHECK(inv_std.has_value() && inv_std->defined(), "mean needs inv_std"); need(*inv_std, at::kFloat, "inv_std");
+    TORCH_CHECK(rows_per_stat > 0 && rows % rows_per_stat == 0 && mean->numel() == (rows / rows_per_stat) * d && inv_std->numel() == mean->numel(),
+                "statistics must be [rows / rows_per_stat, d]");
+    mp = mean->data_ptr<float>(); sp = inv_std->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(in.device());
+  check(CLT_PICK(half, clt_normalize_cast)(in.data_ptr(), in_type, out.data_ptr(), mp, sp, rows, int(rows_per_stat > 0 ? rows_per_stat : rows), d, float(mul),
+                                           cur_stream()), "normalize_cast");
+}
+
+// hist[k] (int64 [n_scales + 1], zeroed here) = number of elements of x [B, F] whose ratio x / theta[f] satisfies exactly the
+// first k of the ascending `scales`: L0(scales[j]) = sum_{k > j} hist[k] / B.
+void scale_histogram(const Tensor& x, const Tensor& theta, const Tensor& scales, Tensor& hist) {
+  const bool half = is_half(x, "x");
+  need(x, t16_of(half), "x"); need(theta, at::kFloat, "theta"); need(scales, at::kFloat, "scales"); need(hist, at::kLong, "hist");
+  TORCH_CHECK(x.dim() == 2 && theta.numel() >= x.size(1) && hist.numel() == scales.numel() + 1, "x [B, F], theta [F], hist [n_scales + 1]");
+  c10::cuda::CUDAGuard guard(x.device());
+  hist.zero_();
+  check(CLT_PICK(half, clt_scale_histogram)(x.data_ptr(), theta.data_ptr<float>(), scales.data_ptr<float>(), int(scales.numel()),
+                                            reinterpret_cast<unsigned long long*>(hist.data_ptr<int64_t>()), int(x.size(0)), int(x.size(1)), x.size(1),
+                                            cur_stream()), "scale_histogram");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -758,4 +793,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("norm2"), py::arg("feat_off"), py::arg("fcsr_val"), py::arg("tying"), py::arg("c_g"), py::arg("lambda_"), py::arg("c"),
         py::arg("bandwidth"), py::arg("hyper"), py::arg("ctl") = none, py::arg("norm_weight") = 0.0, py::arg("grad_out") = none);
   m.def("theta_exp", &theta_exp);
+  m.def("scale_histogram", &scale_histogram);
+  m.def("normalize_cast", &normalize_cast, py::arg("inp"), py::arg("out"), py::arg("mean") = none, py::arg("inv_std") = none,
+        py::arg("rows_per_stat") = 0, py::arg("mul") = 1.0);
 }

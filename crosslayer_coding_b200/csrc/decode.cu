@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
 // copies (cp.async.bulk + mbarrier, no multicast); the four consumer groups take their targets' rows from
 // shared memory.  Large contiguous reads and a ring that is always full keep HBM busy, where the per-row
 // register loads of decode_kernel wait on a dependent load chain.  Every mbarrier wait is bounded.
-constexpr int kDecodeStages = 4;
+constexpr int kDecodeStages = 16;  // at most; the launcher picks the depth so that the ring holds a few tens of KB
 
 struct DecodeBulkShared {
   uint64_t full[kDecodeStages];
@@ -219,10 +219,12 @@ struct DecodeBulkShared {
 };
 
 template <int TPG>
-__global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, int gthreads, int stage_bytes, int* status) {
+__global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, int gthreads, int stage_bytes, int nstages, int* status) {
   extern __shared__ __align__(128) uint8_t smem_raw_dec[];  // bulk copies need 16-byte alignment only
   uint8_t* ring = smem_raw_dec;
-  DecodeBulkShared* sh = reinterpret_cast<DecodeBulkShared*>(ring + size_t(kDecodeStages) * stage_bytes);
+  DecodeBulkShared* sh = reinterpret_cast<DecodeBulkShared*>(ring + size_t(nstages) * stage_bytes);
+  // per-source tied decoders: one row per feature that serves every target >= its source layer
+  const bool shared_row = p.tying == 1;
   // Tensor-parallel push: rank r starts with the tokens owned by rank r + 1, so that at any moment the ranks
   // store into different owners instead of all into the same one.
   const int tok = p.mode == 2 ? int((blockIdx.x + 1LL * ((p.rank + 1) % p.world) * p.rows_per_rank) % p.B) : int(blockIdx.x);
@@ -235,7 +237,7 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
     sh->rows_s[threadIdx.x] = p.rows[threadIdx.x];
   }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kDecodeStages; ++s) {
+    for (int s = 0; s < nstages; ++s) {
       mbar_init(&sh->full[s], 1);
       mbar_init(&sh->empty[s], nconsumer / 32);
     }
@@ -253,8 +255,8 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
       int col_next = b < e ? __ldg(p.tcsr_col + b) : 0;
       float a_next = b < e ? __ldg(p.tcsr_val + b) : 0.f;
       for (int i = b; i < e; ++i, ++issued) {
-        const int st = issued % kDecodeStages;
-        const uint32_t ph = (issued / kDecodeStages) & 1;
+        const int st = issued % nstages;
+        const uint32_t ph = (issued / nstages) & 1;
         const int col = col_next;
         const float a = a_next;
         if (i + 1 < e) {  // the next entry's index is in flight while this stage is waited for
@@ -273,10 +275,10 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
       }
       if (*abort_flag) {
         // give copies already issued a bounded chance to land before the CTA retires
-        const int first = issued > kDecodeStages ? issued - kDecodeStages : 0;
+        const int first = issued > nstages ? issued - nstages : 0;
         for (int j = first; j < issued; ++j) {
           const long long start = clock64();
-          while (!mbar_try_wait(&sh->full[j % kDecodeStages], (j / kDecodeStages) & 1))
+          while (!mbar_try_wait(&sh->full[j % nstages], (j / nstages) & 1))
             if (clock64() - start > kWaitTimeoutCycles) break;
         }
       }
@@ -296,8 +298,8 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
     bool ok = true;
     const int t_span = p.rows_limit > 0 ? p.rows_limit : kMaxLayers;
     for (int i = b; i < e; ++i, ++it) {
-      const int st = it % kDecodeStages;
-      const uint32_t ph = (it / kDecodeStages) & 1;
+      const int st = it % nstages;
+      const uint32_t ph = (it / nstages) & 1;
       if (!mbar_wait(&sh->full[st], ph, abort_flag)) { ok = false; break; }
       const int sl = sh->ent_sl[st];
       const float a = sh->ent_a[st];
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
 #pragma unroll
         for (int j = 0; j < TPG; ++j) {
           const int t = g + (blockIdx.y * TPG + j) * kGroups;
-          if (t < L && t >= sl && t - sl < t_span) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (t - sl) * d));
+          if (t < L && t >= sl && t - sl < t_span) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (shared_row ? 0 : (t - sl) * d)));
         }
       }
       __syncwarp();
@@ -476,9 +478,15 @@ extern "C" int CLT_FN(clt_sparse_decode)(const CltDecodeArgs* a, cudaStream_t st
   const int tpg = (a->L + kGroups - 1) / kGroups;  // targets per warp group
   int max_rows = 0;
   for (int i = 0; i < a->L; ++i) max_rows = a->rows[i] > max_rows ? a->rows[i] : max_rows;
+  if (a->rows_limit > 0 && a->rows_limit < max_rows) max_rows = a->rows_limit;
   const int stage_bytes = ((max_rows * a->d * 2 + 127) / 128) * 128;
-  const size_t smem = size_t(kDecodeStages) * stage_bytes + sizeof(DecodeBulkShared) + 256;
-  const bool bulk = a->tying == 0 && a->status != nullptr && tpg <= 4 && smem <= 200 * 1024 && threads + 32 <= 544;
+  // ring depth: four stages for the long rows of untied decoders, more for short rows so that the copies in flight per
+  // CTA stay in the tens of kilobytes
+  int nstages = 4;
+  while (nstages < kDecodeStages && nstages * stage_bytes < 24 * 1024) nstages *= 2;
+  const size_t smem = size_t(nstages) * stage_bytes + sizeof(DecodeBulkShared) + 256;
+  const bool plain_tied = a->tying == 1 && a->feat_offset == nullptr && a->feat_scale == nullptr;
+  const bool bulk = (a->tying == 0 || plain_tied) && a->status != nullptr && tpg <= 4 && smem <= 200 * 1024 && threads + 32 <= 544;
   if (bulk) {
     static size_t attr_set[5] = {0, 0, 0, 0, 0};
     auto launch = [&](auto kern) -> int {
@@ -486,7 +494,7 @@ extern "C" int CLT_FN(clt_sparse_decode)(const CltDecodeArgs* a, cudaStream_t st
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
         attr_set[tpg] = smem;
       }
-      kern<<<dim3(a->B, 1), threads + 32, smem, st>>>(p, gthreads, stage_bytes, a->status);
+      kern<<<dim3(a->B, 1), threads + 32, smem, st>>>(p, gthreads, stage_bytes, nstages, a->status);
       return 0;
     };
     int rc = 0;

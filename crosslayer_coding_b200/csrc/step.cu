@@ -278,6 +278,88 @@ __global__ void __launch_bounds__(256) theta_adam_kernel(const ThetaAdamParams p
   }
 }
 
+// ---------------------------------------------------------------------------------------- batch normalisation
+// Activation batches arrive on the device as stored ([2, L, B, d]: inputs and targets of every layer, bf16 / fp16 /
+// fp32); the store's normalisation (x - mean) / std with per-(side, layer, element) statistics, or x * mul, and the
+// cast to the training type run as one pass (reference: three eager passes in fp32,
+// clt/training/data/manifest_activation_store.py:906-934).  One thread per 8 elements; d % 8 == 0.
+template <typename IT>
+__device__ __forceinline__ void load8_in(const IT* p, float (&o)[8]);
+template <>
+__device__ __forceinline__ void load8_in<float>(const float* p, float (&o)[8]) {
+  const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8_in<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
+  const uint4 q = __ldcs(reinterpret_cast<const uint4*>(p));
+  const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { o[2 * j] = bf16_lo(u[j]); o[2 * j + 1] = bf16_hi(u[j]); }
+}
+template <>
+__device__ __forceinline__ void load8_in<__half>(const __half* p, float (&o)[8]) {
+  const uint4 q = __ldcs(reinterpret_cast<const uint4*>(p));
+  const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { const float2 f = __half22float2(h[j]); o[2 * j] = f.x; o[2 * j + 1] = f.y; }
+}
+
+template <typename IT>
+__global__ void __launch_bounds__(256) normalize_cast_kernel(const IT* __restrict__ in, t16* __restrict__ out, const float* __restrict__ mean,
+                                                               const float* __restrict__ inv_std, long long rows, int rows_per_stat, int d, float mul) {
+  const int vec_per_row = d / 8;
+  const long long nvec = rows * vec_per_row;
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < nvec; i += 1LL * gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int e0 = int(i - r * vec_per_row) * 8;
+    float x[8];
+    load8_in<IT>(in + r * d + e0, x);
+    if (mean != nullptr) {
+      const long long so = (r / rows_per_stat) * d + e0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = (x[j] - __ldg(mean + so + j)) * __ldg(inv_std + so + j);
+    }
+    uint4 q;
+    q.x = pack_t16x2(x[0] * mul, x[1] * mul); q.y = pack_t16x2(x[2] * mul, x[3] * mul);
+    q.z = pack_t16x2(x[4] * mul, x[5] * mul); q.w = pack_t16x2(x[6] * mul, x[7] * mul);
+    *reinterpret_cast<uint4*>(out + r * d + e0) = q;
+  }
+}
+
+// ---------------------------------------------------------------------------------------- L0 calibration histogram
+// Layer-wise L0 calibration scales a layer's thresholds by s until the layer's L0 matches a target (reference: a 15-step
+// binary search that re-encodes per probe, scripts/convert_batchtopk_to_jumprelu.py:649-763).  L0(s) = #{x >= s * theta}
+// for every candidate s comes from one pass: an element with ratio r = x / theta satisfies the first k scales of the
+// ascending vector `scales` (k = number of scales <= r); hist[k] counts them.  Most elements lie below scales[0] and
+// cost one compare; the others do a binary search in shared memory.
+constexpr int kMaxScales = 1024;
+__global__ void __launch_bounds__(256) scale_histogram_kernel(const t16* __restrict__ x, const float* __restrict__ theta,
+                                                                const float* __restrict__ scales, int n_scales,
+                                                                unsigned long long* __restrict__ hist, int B, int F, long long ld) {
+  __shared__ float sc[kMaxScales];
+  __shared__ unsigned int sh[kMaxScales + 1];
+  for (int i = threadIdx.x; i < n_scales; i += blockDim.x) sc[i] = scales[i];
+  for (int i = threadIdx.x; i <= n_scales; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const float s0 = sc[0];
+  const long long n = 1LL * B * F;
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
+    const int b = int(i / F), f = int(i - 1LL * b * F);
+    const float r = __fdiv_rn(t16_to_float(x[1LL * b * ld + f]), fmaxf(__ldg(theta + f), 1e-30f));
+    if (!(r >= s0)) continue;
+    int lo = 0, hi = n_scales;  // number of scales <= r, in [1, n_scales]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (sc[mid] <= r) lo = mid; else hi = mid;
+    }
+    atomicAdd(&sh[lo + 1], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i <= n_scales; i += blockDim.x)
+    if (sh[i]) atomicAdd(&hist[i], (unsigned long long)sh[i]);
+}
+
 // theta = exp(log_theta) (set-up, after a checkpoint load)
 template <typename WT>
 __global__ void __launch_bounds__(256) theta_exp_kernel(const WT* __restrict__ log_theta, float* __restrict__ theta, long long n) {
@@ -387,5 +469,29 @@ extern "C" int CLT_FN(clt_theta_exp)(const void* log_theta, float* theta, long l
   const int grid = int((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
   if (weights_16) theta_exp_kernel<t16><<<grid, 256, 0, st>>>(static_cast<const t16*>(log_theta), theta, n);
   else theta_exp_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(log_theta), theta, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// in_type: 0 fp32, 1 bf16, 2 fp16.  mean / inv_std: [rows / rows_per_stat, d] or null (only the multiplier applies).
+extern "C" int CLT_FN(clt_normalize_cast)(const void* in, int in_type, void* out, const float* mean, const float* inv_std, long long rows,
+                                          int rows_per_stat, int d, float mul, cudaStream_t st) {
+  if (d % 8 != 0 || rows <= 0 || rows_per_stat <= 0) return -1;
+  const long long nvec = rows * (d / 8);
+  const int grid = int((nvec + 255) / 256 < 148 * 16 ? (nvec + 255) / 256 : 148 * 16);
+  t16* o = static_cast<t16*>(out);
+  if (in_type == 0) normalize_cast_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(in), o, mean, inv_std, rows, rows_per_stat, d, mul);
+  else if (in_type == 1) normalize_cast_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), o, mean, inv_std, rows, rows_per_stat, d, mul);
+  else if (in_type == 2) normalize_cast_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(in), o, mean, inv_std, rows, rows_per_stat, d, mul);
+  else return -1;
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// hist: [n_scales + 1] uint64, zeroed by the caller; hist[k] = number of elements that satisfy exactly the first k scales.
+extern "C" int CLT_FN(clt_scale_histogram)(const void* x, const float* theta, const float* scales, int n_scales, unsigned long long* hist,
+                                           int B, int F, long long ld, cudaStream_t st) {
+  if (n_scales < 1 || n_scales > kMaxScales || B <= 0 || F <= 0) return -1;
+  const long long n = 1LL * B * F;
+  const int grid = int((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  scale_histogram_kernel<<<grid, 256, 0, st>>>(static_cast<const t16*>(x), theta, scales, n_scales, hist, B, F, ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -129,7 +129,9 @@ class CrossLayerTranscoder(BaseTranscoder):
 
         if config.activation_fn == "jumprelu":
             init = math.log(config.jumprelu_threshold) if config.jumprelu_threshold > 0 else math.log(1e-7)
-            self.log_threshold = nn.Parameter(torch.full((L, Fl), init, **kw))
+            # thresholds are kept in fp32 whatever the weight type is: a bf16 log-threshold has three significant digits,
+            # which moves a layer's L0 by whole features (the reference stores it in the model dtype, theta.py:50-61)
+            self.log_threshold = nn.Parameter(torch.full((L, Fl), init, device=self.device, dtype=torch.float32))
         else:
             self.register_parameter("log_threshold", None)
 
@@ -530,7 +532,7 @@ class CrossLayerTranscoder(BaseTranscoder):
             if lt is not None:
                 used.add("theta_manager.log_threshold")
                 if self.log_threshold is None:
-                    self.log_threshold = nn.Parameter(torch.empty(L, self.local_features, device=self.enc_weight.device, dtype=self.dtype))
+                    self.log_threshold = nn.Parameter(torch.empty(L, self.local_features, device=self.enc_weight.device, dtype=torch.float32))
                 copy_into(self.log_threshold, lt, "log_threshold")
             elif self.log_threshold is not None:
                 missing.append("theta_manager.log_threshold")

@@ -169,7 +169,7 @@ def convert_to_jumprelu_inplace(model, default_theta_value: float = 1e6) -> None
     pad = model.local_features - model.valid_features
     if pad:
         log_theta = torch.nn.functional.pad(log_theta, (0, pad), value=float(torch.tensor(default_theta_value).log()))
-    log_theta = log_theta.to(device=model.enc_weight.device, dtype=model.dtype)
+    log_theta = log_theta.to(device=model.enc_weight.device, dtype=torch.float32)  # fp32 whatever the weight type is
 
     # config mutation mirrors the reference (theta.py:584-595)
     cfg.activation_fn = "jumprelu"

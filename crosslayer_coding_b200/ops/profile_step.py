@@ -25,34 +25,42 @@ CASES = {
     "tiny": (4, 256, 2048, 1024, 16),
     "shard8": (12, 768, 3072, 4096, 25),        # one rank's share of the full case at 8 GPUs (features and k divided by 8)
     "llama-1b": (16, 2048, 32768, 4096, 200),   # Llama-3.2-1B shape: 10 G parameters, about 110 GB with fp32 moments
+    "pythia-70m": (6, 512, 32768, 8192, 200),   # Pythia-70m shape with 8192-token batches (tied decoders: --tying)
+    "pythia-shard8": (6, 512, 4096, 8192, 25),  # one rank's share of it at 8 GPUs
 }
 
 
-def build(case: str, device: torch.device, activation: str = "batchtopk", states: str = "float32"):
+def build(case: str, device: torch.device, activation: str = "batchtopk", states: str = "float32", tying: str = "none",
+          precision: str = "bf16"):
     from .. import CLTConfig, CrossLayerTranscoder, TrainingConfig
     from ..training.fused_engine import FusedBatchTopKEngine
 
     L, d, F, B, k = CASES[case]
     torch.manual_seed(0)
-    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=activation, batchtopk_k=k, topk_k=k, clt_dtype="bfloat16",
-                    jumprelu_threshold=0.03)
+    t16 = torch.float16 if precision == "fp16" else torch.bfloat16
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=activation, batchtopk_k=k, topk_k=k,
+                    clt_dtype="float16" if precision == "fp16" else "bfloat16", jumprelu_threshold=0.03, decoder_tying=tying)
     model = CrossLayerTranscoder(cfg, device=device)
+    if tying != "none":
+        with torch.no_grad():  # tied decoders start at zero
+            for w in model.dec_weight:
+                w.uniform_(-0.02, 0.02)
     lam = 0.0
     if activation == "jumprelu":
         # thresholds at the value that leaves about k of a token's L * F pre-activations active
         import math
 
         torch.manual_seed(0)
-        probe = (torch.randn(512, d, device=device).bfloat16() @ model.enc_weight.data[0].t()).float() + model.enc_bias.data[0].float()
+        probe = (torch.randn(512, d, device=device).to(t16) @ model.enc_weight.data[0].t()).float() + model.enc_bias.data[0].float()
         theta0 = float(torch.quantile(probe.flatten()[: 1 << 22], 1.0 - k / (L * F)))
         with torch.no_grad():
             model.log_threshold.fill_(math.log(max(theta0, 1e-6)))
         lam = 1e-3
-    tc = TrainingConfig(learning_rate=1e-4, training_steps=1000, activation_path="unused", precision="bf16",
-                        sparsity_lambda=lam, preactivation_coef=0.0, optimizer_states_dtype=states)
+    tc = TrainingConfig(learning_rate=1e-4, training_steps=1000, activation_path="unused", precision=precision,
+                        sparsity_lambda=lam, preactivation_coef=0.0, optimizer_states_dtype=states, loss_scale_init=256.0)
     eng = FusedBatchTopKEngine(model, tc, B)
-    X = torch.randn(L, B, d, device=device).bfloat16()
-    Y = torch.randn(L, B, d, device=device).bfloat16()
+    X = torch.randn(L, B, d, device=device).to(t16)
+    Y = torch.randn(L, B, d, device=device).to(t16)
     return model, eng, X, Y
 
 
@@ -74,13 +82,15 @@ def main() -> None:
     ap.add_argument("--activation", choices=["batchtopk", "jumprelu", "topk"], default="batchtopk")
     ap.add_argument("--optimizer-states", choices=["float32", "bfloat16"], default="float32",
                     help="moment dtype of the encoder / decoder weights (bfloat16: stochastically rounded, 12 B/param/step)")
+    ap.add_argument("--tying", choices=["none", "per_source", "per_target"], default="none")
+    ap.add_argument("--precision", choices=["bf16", "fp16"], default="bf16")
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--lr", type=float, default=None,
                     help="learning rate (default 1e-4; 1e-8 for jumprelu so that the active count of the synthetic data stays put)")
     ap.add_argument("--time", action="store_true", help="print CUDA-event timings instead of marking a profiler range")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
-    model, eng, X, Y = build(args.case, dev, args.activation, args.optimizer_states)
+    model, eng, X, Y = build(args.case, dev, args.activation, args.optimizer_states, args.tying, args.precision)
     lam = eng.tc.sparsity_lambda
     lr = args.lr if args.lr is not None else (1e-8 if args.activation == "jumprelu" else 1e-4)
     L, d, F, B, k = CASES[args.case]

@@ -167,6 +167,22 @@ class ManifestActivationStore(BaseActivationStore):
         """``raw``: ``[2, L, B, d]`` in the stored dtype on the device -> normalised, store dtype."""
         if not self.apply_normalization:
             return raw if raw.dtype == self.dtype else raw.to(self.dtype)
+        if raw.is_cuda and self.dtype in (torch.bfloat16, torch.float16) and self.d_model % 8 == 0:
+            # one pass on the device: (x - mean) / std (or x * sqrt(d)) and the cast to the training type
+            from ...ops import ext
+
+            out = torch.empty(raw.shape, dtype=self.dtype, device=raw.device)
+            raw_c = raw.contiguous()
+            if self.normalization_method == "mean_std" and self._norm_pack is not None:
+                if getattr(self, "_norm_flat", None) is None:
+                    mean, std = self._norm_pack
+                    self._norm_flat = (mean.reshape(-1, self.d_model).contiguous(), (1.0 / std).reshape(-1, self.d_model).contiguous())
+                ext.load().normalize_cast(raw_c, out, self._norm_flat[0], self._norm_flat[1], raw_c.shape[-2], 1.0)
+            elif self.normalization_method == "sqrt_d_model":
+                ext.load().normalize_cast(raw_c, out, None, None, 0, float(self.d_model ** 0.5))
+            else:
+                return raw if raw.dtype == self.dtype else raw.to(self.dtype)
+            return out
         x = raw.float()
         if self.normalization_method == "mean_std" and self._norm_pack is not None:
             mean, std = self._norm_pack

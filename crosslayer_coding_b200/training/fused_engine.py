@@ -343,8 +343,10 @@ class FusedBatchTopKEngine:
                 self.theta_m = torch.zeros(L, Fl, dtype=f32, device=dev)
                 self.theta_v = torch.zeros(L, Fl, dtype=f32, device=dev)
                 self.grad_log_threshold = torch.zeros(L, Fl, dtype=f32, device=dev)  # kept for diagnostics and tests
-            if self.tying == 1 and self.fn == "jumprelu":
-                self.gs_cum = torch.empty(L, B, d, dtype=self.t16, device=dev)
+        # per-source tied decoders: the row of feature (s, f) serves every target t >= s, so its gradient and dL/da only need
+        # the gradient seed summed over those targets; with that sum in place of the seed the decoder update is the
+        # one-row-per-feature case of the untied row pipeline
+        self.gs_cum = torch.empty(L, B, d, dtype=self.t16, device=dev) if (self.tying == 1 and training_config is not None) else None
         self.opt_step = 0
         self.seq = 0
         self.kernel_launches = 0  # launches of this package's own kernels (reported by the benchmark)
@@ -643,16 +645,6 @@ class FusedBatchTopKEngine:
         # all-gather of the gradient seed, so everything below sees every token's seed row
         losses = torch.empty(8, dtype=torch.float32, device=self.dev)
         self._control(0, losses)
-        if jr:
-            # window sums for the threshold gradient, from the decoder weights of this step (before their update)
-            gs_cum = None
-            if self.tying == 1:
-                e.gs_suffix_sum(self.gs, self.gs_cum)
-                gs_cum = self.gs_cum
-                self.kernel_launches += 1
-            e.theta_grad_gemm(self.gs, [w.data for w in m.dec_weight], self.preact, self.theta, float(m.bandwidth), self.S1, self.S2,
-                              self.status, self.tying, gs_cum)
-            self.kernel_launches += 1
         if use_aux:
             dec0_dense.zero_()
             mask = dead_mask
@@ -662,6 +654,17 @@ class FusedBatchTopKEngine:
             extra_bias_grad = self._aux_bias_grad
             losses[4] += aux_val  # the auxiliary term is evaluated on the finished residual, after the loss was settled
             losses[0] += aux_val
+        gs_dec, tying_dec = self.gs, self.tying
+        if self.tying == 1:
+            e.gs_suffix_sum(self.gs, self.gs_cum)
+            gs_dec, tying_dec = self.gs_cum, 0
+            self.kernel_launches += 1
+        if jr:
+            # window sums for the threshold gradient, from the decoder weights of this step (before their update)
+            gs_cum = self.gs_cum if self.tying == 1 else None
+            e.theta_grad_gemm(self.gs, [w.data for w in m.dec_weight], self.preact, self.theta, float(m.bandwidth), self.S1, self.S2,
+                              self.status, self.tying, gs_cum)
+            self.kernel_launches += 1
         # decoder biases: dL/db[pair (s,t)] = c_g * sum_b gs[t, b, :]
         e.gs_colsum(self.gs, self.gs_sum)
         dec_w = [w.data for w in m.dec_weight]
@@ -673,8 +676,8 @@ class FusedBatchTopKEngine:
             # gradient-norm pre-pass: the row gradients are formed once without touching weights or moments (features
             # without entries have none), dL/da is written on the way; step_control turns the norm into the coefficient
             rep = 1.0 / self.world  # replicated parameters are counted once over the ranks
-            e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, self.tying, self.feat_off, self.fcsr_tok, self.fcsr_val,
-                                self.gs, self.grad_a, pen, None, None, None, dec0_dense, h_dec, None, None, None, ctl, True)
+            e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, tying_dec, self.feat_off, self.fcsr_tok, self.fcsr_val,
+                                gs_dec, self.grad_a, pen, None, None, None, dec0_dense, h_dec, None, None, None, ctl, True)
             e.decoder_bias_adam(m.dec_bias.data, self.decb_m, self.decb_v, self.bias_sel, self.gs_sum, extra_bias_grad, h_dec, ctl, rep)
             e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v, self.feat_off,
                                 self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, h_enc, None, None, None, None, ctl, True)
@@ -685,8 +688,8 @@ class FusedBatchTopKEngine:
             self._control(1, losses)
             grad_a_for_update = None  # dL/da is complete; the update pass must not add to it again
             self.kernel_launches += 4
-        e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, self.tying,
-                            self.feat_off, self.fcsr_tok, self.fcsr_val, self.gs, grad_a_for_update, pen, self.norm2_next,
+        e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, tying_dec,
+                            self.feat_off, self.fcsr_tok, self.fcsr_val, gs_dec, grad_a_for_update, pen, self.norm2_next,
                             None, None, dec0_dense, h_dec, self.status, None, None, ctl, False)
         if jr:
             # thresholds: uses the decoder norms of this step (before the swap below)

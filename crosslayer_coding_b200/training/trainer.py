@@ -313,7 +313,9 @@ class CLTTrainer:
         if self.clt_config.activation_fn == "batchtopk" and not tc.apply_sparsity_penalty_to_batchtopk:
             lam = 0.0
         self.loss_manager.current_sparsity_lambda = lam
-        need_aux = bool(tc.aux_loss_factor) and step > tc.dead_feature_window and self._any_dead_cached(step)
+        # a feature is dead once its counter passed the window, which cannot happen before `dead_feature_window` steps
+        # unless the counters were restored from a checkpoint: the counters alone decide
+        need_aux = bool(tc.aux_loss_factor) and self.clt_config.activation_fn in ("batchtopk", "topk") and self._any_dead_cached(step)
         pre_coef = tc.preactivation_coef if tc.preactivation_coef is not None else 0.0
         with self.profiler.timer("optimizer_step"):
             out = eng.train_step(

@@ -121,5 +121,7 @@ def test_collect_top_activations_with_base_model_in_the_loop(tiny_gpt2, tmp_path
         want = sorted(best[f], reverse=True)[:2]
         got = merged[str(f)]["activations"]
         assert abs(got["0"]["score"] - want[0][0]) < 1e-4 and abs(got["1"]["score"] - want[1][0]) < 1e-4
-        assert len(got["0"]["text"]) == len(got["0"]["values"]) == len(texts[want[0][1]].split())
-        assert all(abs(u - v) < 1e-4 for u, v in zip(got["0"]["values"], want[0][2]))
+        assert len(got["0"]["text"]) == len(got["0"]["values"])
+        if want[0][0] - sorted(best[f], reverse=True)[1][0] > 1e-6:  # a unique best sequence (equal scores may come in any order)
+            assert len(got["0"]["text"]) == len(texts[want[0][1]].split())
+            assert all(abs(u - v) < 1e-4 for u, v in zip(got["0"]["values"], want[0][2]))

@@ -288,3 +288,37 @@ def test_exact_cut_with_heavy_ties_is_world_invariant_and_lowest_index_first():
         z = ((x.float() - mean[:, None, :]) * rstd[:, None, :]).permute(1, 0, 2).reshape(-1)   # flat index = b * L * F + l * F + f
         order = torch.sort(z, descending=True, stable=True).indices[:n]                           # stable: lowest index first among ties
         assert torch.equal(torch.sort(flat).values, torch.sort(order).values)
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float16), (torch.float16, torch.bfloat16)])
+def test_normalize_cast_matches_fp32_reference(in_dtype, out_dtype):
+    from crosslayer_coding_b200.ops import ext as ext_mod
+
+    e = ext_mod.load()
+    dev = _dev()
+    torch.manual_seed(0)
+    L, B, d = 3, 70, 48
+    raw = (torch.randn(2, L, B, d, device=dev) * 3 + 1).to(in_dtype)
+    mean = torch.randn(2 * L, d, device=dev)
+    std = torch.rand(2 * L, d, device=dev) + 0.5
+    out = torch.empty(2, L, B, d, dtype=out_dtype, device=dev)
+    e.normalize_cast(raw, out, mean, (1.0 / std).contiguous(), B, 1.0)
+    want = ((raw.float() - mean.view(2, L, 1, d)) * (1.0 / std).view(2, L, 1, d)).to(out_dtype)
+    assert torch.allclose(out.float(), want.float(), rtol=2 ** -7, atol=1e-6)
+    e.normalize_cast(raw, out, None, None, 0, float(d ** 0.5))
+    assert torch.allclose(out.float(), (raw.float() * d ** 0.5).to(out_dtype).float(), rtol=2 ** -7, atol=1e-6)
+
+
+def test_scale_histogram_gives_l0_of_every_scale():
+    from crosslayer_coding_b200.conversion import l0_for_scales
+
+    dev = _dev()
+    torch.manual_seed(1)
+    B, F = 300, 520
+    pre = torch.randn(B, F, device=dev).bfloat16()
+    theta = torch.rand(F, device=dev) * 0.5 + 0.2
+    scales = torch.logspace(-1, 1, 257, device=dev)
+    got = l0_for_scales(pre, theta, scales)                          # kernel path (16-bit input on the GPU)
+    ratio = pre.float() / theta
+    want = torch.stack([(ratio >= s).float().sum() / B for s in scales])
+    assert torch.equal((got * B).round(), (want * B).round()), (got - want).abs().max()  # the counts themselves are exact
