@@ -741,6 +741,45 @@ void scale_histogram(const Tensor& x, const Tensor& theta, const Tensor& scales,
                                             cur_stream()), "scale_histogram");
 }
 
+// C[g] = alpha * sum over the segments (a, b) of group g of A[a] @ B[b]^T.  A [LA, M, K], B [LB, N, K] (16-bit, contiguous),
+// C [G, M, N] fp32 or 16-bit; group_off int32 [G + 1], segs int32 [n_segs, 2] on the device.
+void dense_gemm(const Tensor& A, const Tensor& B, Tensor& C, const Tensor& group_off, const Tensor& segs, double alpha, Tensor& status) {
+  const bool half = is_half(A, "A");
+  need(A, t16_of(half), "A"); need(B, t16_of(half), "B"); need(group_off, at::kInt, "group_off"); need(segs, at::kInt, "segs"); need(status, at::kInt, "status");
+  TORCH_CHECK(A.dim() == 3 && B.dim() == 3 && C.dim() == 3 && A.size(2) == B.size(2) && C.size(1) == A.size(1) && C.size(2) == B.size(1), "A [LA, M, K], B [LB, N, K], C [G, M, N]");
+  const bool out_f32 = C.scalar_type() == at::kFloat;
+  need(C, out_f32 ? at::kFloat : t16_of(half), "C");
+  const int G = int(C.size(0));
+  TORCH_CHECK(group_off.numel() == G + 1 && segs.dim() == 2 && segs.size(1) == 2, "group_off [G + 1], segs [n, 2]");
+  c10::cuda::CUDAGuard guard(A.device());
+  check(CLT_PICK(half, clt_dense_gemm)(A.data_ptr(), int(A.size(0)), A.size(2), A.size(1) * A.size(2), B.data_ptr(), int(B.size(0)), B.size(2),
+                                       B.size(1) * B.size(2), C.data_ptr(), out_f32 ? 1 : 0, group_off.data_ptr<int>(), segs.data_ptr<int>(), G,
+                                       int(A.size(1)), int(B.size(1)), int(A.size(2)), float(alpha), status.data_ptr<int>(), num_sms(), cur_stream()),
+        "dense_gemm");
+}
+
+// out[l] = in[l]^T for 16-bit [L, R, C] tensors
+void transpose16(const Tensor& in, Tensor& out) {
+  const bool half = is_half(in, "in");
+  need(in, t16_of(half), "in"); need(out, t16_of(half), "out");
+  TORCH_CHECK(in.dim() == 3 && out.dim() == 3 && out.size(0) == in.size(0) && out.size(1) == in.size(2) && out.size(2) == in.size(1), "in [L, R, C], out [L, C, R]");
+  c10::cuda::CUDAGuard guard(in.device());
+  check(CLT_PICK(half, clt_transpose16)(in.data_ptr(), out.data_ptr(), int(in.size(0)), int(in.size(1)), int(in.size(2)), in.size(2),
+                                        in.size(1) * in.size(2), cur_stream()), "transpose16");
+}
+
+// ind[l][f, b] = 1[pre[l][b, f] < 0]; bias_grad[l, f] -= c * count; loss[0] += c * sum relu(-pre)   (c = coef / numel)
+void negative_indicator(const Tensor& pre, Tensor& ind, Tensor& bias_grad, Tensor& loss, int64_t f_valid, double coef_over_numel) {
+  const bool half = is_half(pre, "pre");
+  need(pre, t16_of(half), "pre"); need(ind, t16_of(half), "ind"); need(bias_grad, at::kFloat, "bias_grad"); need(loss, at::kDouble, "loss");
+  TORCH_CHECK(pre.dim() == 3 && ind.dim() == 3 && ind.size(0) == pre.size(0) && ind.size(1) == pre.size(2) && ind.size(2) == pre.size(1) &&
+              bias_grad.numel() == pre.size(0) * pre.size(2) && loss.numel() >= 1, "pre [L, B, F], ind [L, F, B], bias_grad [L, F]");
+  c10::cuda::CUDAGuard guard(pre.device());
+  check(CLT_PICK(half, clt_negative_indicator)(pre.data_ptr(), ind.data_ptr(), bias_grad.data_ptr<float>(), loss.data_ptr<double>(), int(pre.size(0)),
+                                               int(pre.size(1)), int(pre.size(2)), int(f_valid), pre.size(2), float(coef_over_numel), cur_stream()),
+        "negative_indicator");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -793,6 +832,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("norm2"), py::arg("feat_off"), py::arg("fcsr_val"), py::arg("tying"), py::arg("c_g"), py::arg("lambda_"), py::arg("c"),
         py::arg("bandwidth"), py::arg("hyper"), py::arg("ctl") = none, py::arg("norm_weight") = 0.0, py::arg("grad_out") = none);
   m.def("theta_exp", &theta_exp);
+  m.def("dense_gemm", &dense_gemm);
+  m.def("transpose16", &transpose16);
+  m.def("negative_indicator", &negative_indicator);
   m.def("scale_histogram", &scale_histogram);
   m.def("normalize_cast", &normalize_cast, py::arg("inp"), py::arg("out"), py::arg("mean") = none, py::arg("inv_std") = none,
         py::arg("rows_per_stat") = 0, py::arg("mul") = 1.0);

@@ -362,6 +362,7 @@ class FusedBatchTopKEngine:
     def _begin_step(self) -> None:
         """One memset for everything that has to start at zero (histograms, counters, loss sums, dL/da, next norms)."""
         self.arena.clear_for_step(1 - self._norm_cur)
+        self._XT_of = None  # the transposed inputs belong to one step
 
     def _ensure_theta(self) -> None:
         if self.fn == "jumprelu" and not self._theta_valid:
@@ -424,37 +425,70 @@ class FusedBatchTopKEngine:
             self.ext.step_finish(None, None, self.model.dec_bias.data, self.bias_sel, self.bias_sum)
             self._bias_sum_valid = True
 
-    # The skip connection (reference: clt/models/decoder.py:310,332) is a handful of small dense [B, d] x [d, d]
-    # products: library GEMMs.  Its output enters the fused loss epilogue as the `addend` of the decode kernel and
-    # its weights are updated by the dense Adam kernel from gs^T @ x.
-    def _skip_pairs(self, s: int):
+    # ------------------------------------------------------------------ dense side terms (grouped tcgen05 GEMM)
+    def _seg_tables(self, groups):
+        """Device tables of ``ext.dense_gemm``: ``groups`` is a list of segment lists ``[(a_layer, b_layer), ...]``."""
+        off, segs = [0], []
+        for g in groups:
+            segs.extend(g)
+            off.append(len(segs))
+        return (torch.tensor(off, dtype=torch.int32, device=self.dev),
+                torch.tensor(segs, dtype=torch.int32, device=self.dev).view(-1, 2).contiguous())
+
+    def _transposed_inputs(self, X: torch.Tensor) -> torch.Tensor:
+        """``x^T [L, d, B]`` of this step's inputs (the gradient GEMMs contract over the tokens)."""
+        if getattr(self, "_XT", None) is None:
+            self._XT = torch.empty(self.L, self.d, self.B, dtype=self.t16, device=self.dev)
+            self._XT_of = None
+        if self._XT_of is not X:
+            self.ext.transpose16(X, self._XT)
+            self._XT_of = X
+            self.kernel_launches += 1
+        return self._XT
+
+    # The skip connection (reference: clt/models/decoder.py:298-338): y_hat[t] += sum_{s <= t} x[s] W_skip[s -> t]^T (untied)
+    # or x[t] W_skip[t]^T (tied).  Forward: one grouped GEMM whose K dimension runs over the source layers; its output
+    # enters the loss epilogue of the decode kernel as `addend`.  Backward: dW_skip[s -> t] = gs[t]^T x[s], one grouped
+    # GEMM over the transposed seed and inputs (K = tokens), fed to the dense Adam kernel.
+    def _skip_setup(self) -> None:
+        if getattr(self, "_skip_fwd", None) is not None:
+            return
         from ..models.clt import pair_index
 
-        return [pair_index(s, t, self.L) for t in range(s, self.L)]
+        L = self.L
+        if self.tying == 0:
+            fwd = [[(s, pair_index(s, t, L)) for s in range(t + 1)] for t in range(L)]
+            bwd = [None] * self.model.num_pairs
+            for s in range(L):
+                for t in range(s, L):
+                    bwd[pair_index(s, t, L)] = [(t, s)]
+        else:
+            fwd = [[(l, l)] for l in range(L)]
+            bwd = [[(l, l)] for l in range(L)]
+        self._skip_fwd = self._seg_tables(fwd)
+        self._skip_bwd = self._seg_tables(bwd)
+        self._skip_out = torch.empty(L, self.B, self.d, dtype=torch.float32, device=self.dev)
+        self._skip_grad_buf = torch.empty(self.model.skip_weight.shape, dtype=torch.float32, device=self.dev)
+        self._gsT = torch.empty(L, self.d, self.B, dtype=self.t16, device=self.dev)
 
     def _skip_term(self, X: torch.Tensor) -> Optional[torch.Tensor]:
         W = self.model.skip_weight
         if W is None:
             return None
-        out = torch.zeros(self.L, self.B, self.d, dtype=torch.float32, device=self.dev)
-        if self.tying == 0:
-            for s in range(self.L):
-                w = W.data[self._skip_pairs(s)]                     # [R, d, d], row t - s is the pair (s, t)
-                out[s:] += torch.matmul(X[s].to(w.dtype), w.transpose(1, 2)).float()
-        else:
-            out += torch.matmul(X.to(W.dtype), W.data.transpose(1, 2)).float()
-        return out
+        self._skip_setup()
+        off, segs = self._skip_fwd
+        self.ext.dense_gemm(X, W.data, self._skip_out, off, segs, 1.0, self.status)
+        self.kernel_launches += 1
+        return self._skip_out
 
     def _skip_grad(self, X: torch.Tensor) -> torch.Tensor:
-        W = self.model.skip_weight
-        gs = self.gs
-        if self.tying == 0:
-            grad = torch.zeros(W.shape, dtype=torch.float32, device=self.dev)
-            for s in range(self.L):
-                # d loss / d W[s -> t] = c_g * gs[t]^T @ x[s]
-                grad[self._skip_pairs(s)] = torch.matmul(gs[s:].transpose(1, 2), X[s].to(gs.dtype)).float()
-            return grad
-        return torch.matmul(gs.transpose(1, 2), X.to(gs.dtype)).float().contiguous()
+        self._skip_setup()
+        XT = self._transposed_inputs(X)
+        self.ext.transpose16(self.gs, self._gsT)
+        off, segs = self._skip_bwd
+        self.ext.dense_gemm(self._gsT, XT, self._skip_grad_buf, off, segs, 1.0, self.status)
+        self.kernel_launches += 2
+        return self._skip_grad_buf
 
     def decode_loss(self, Y: torch.Tensor, want_yhat: bool = False) -> Optional[torch.Tensor]:
         """Kernel 5: sparse decode, reconstruction loss sums and the gradient seed."""
@@ -535,19 +569,19 @@ class FusedBatchTopKEngine:
     @torch.no_grad()
     def _preactivation_term(self, X: torch.Tensor, coef: float) -> None:
         """``coef * mean(relu(-preact))`` (reference losses.py:203-261) and its dense encoder gradient
-        ``-(coef/numel) * 1[preact < 0]^T X`` - a library GEMM per layer on the stored pre-activations.  The loss sum of
-        this shard goes to ``scalars[1]``."""
+        ``-(coef / numel) * 1[preact < 0]^T x`` on the stored pre-activations: one pass writes the transposed indicator,
+        the bias gradient and the loss sum of this shard (``scalars[1]``), one grouped tensor-core GEMM per step (all
+        layers in one launch) the ``[F, d]`` weight gradient."""
         enc_dense, encb_dense, _ = self._extra_buffers()
-        numel = float(self.L * self.B * self.F)
-        total = torch.zeros((), device=self.dev, dtype=torch.float64)
-        for l in range(self.L):
-            pl = self.preact[l][:, : self.Fv]
-            neg = pl < 0
-            total = total + torch.where(neg, -pl.float(), torch.zeros((), device=self.dev)).sum().double()
-            g = neg.to(self.t16)
-            enc_dense[l, : self.Fv].add_((g.t() @ X[l]).float(), alpha=-coef / numel)
-            encb_dense[l, : self.Fv].add_(g.float().sum(dim=0), alpha=-coef / numel)
-        self.scalars[1] += coef * total / numel
+        if getattr(self, "_ind_T", None) is None:
+            self._ind_T = torch.empty(self.L, self.Fl, self.B, dtype=self.t16, device=self.dev)
+            self._layer_tables = self._seg_tables([[(l, l)] for l in range(self.L)])
+        c = coef / float(self.L * self.B * self.F)
+        self.ext.negative_indicator(self.preact, self._ind_T, encb_dense, self.scalars[1:2], self.Fv, c)
+        XT = self._transposed_inputs(X)
+        off, segs = self._layer_tables
+        self.ext.dense_gemm(self._ind_T, XT, enc_dense, off, segs, -c, self.status)
+        self.kernel_launches += 2
 
     @torch.no_grad()
     def _auxiliary_term(self, X: torch.Tensor, dead_mask: torch.Tensor, factor: float, k_aux_default: int = 512) -> torch.Tensor:
@@ -634,10 +668,11 @@ class FusedBatchTopKEngine:
             self.kernel_launches += 1
         if use_pre or use_aux:
             enc_dense, encb_dense, dec0_dense = self._extra_buffers()
-            enc_dense.zero_()
             encb_dense.zero_()
             if use_pre:
-                self._preactivation_term(X, float(preactivation_coef))
+                self._preactivation_term(X, float(preactivation_coef))  # writes every element of enc_dense
+            else:
+                enc_dense.zero_()
             if not use_aux:
                 dec0_dense = None
         self.decode_loss(Y)

@@ -322,3 +322,42 @@ def test_scale_histogram_gives_l0_of_every_scale():
     ratio = pre.float() / theta
     want = torch.stack([(ratio >= s).float().sum() / B for s in scales])
     assert torch.equal((got * B).round(), (want * B).round()), (got - want).abs().max()  # the counts themselves are exact
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("out_dtype", ["f32", "t16"])
+def test_grouped_dense_gemm_matches_fp32_reference(dtype, out_dtype):
+    """C[g] = alpha * sum over the group's segments of A[a] @ B[b]^T, odd sizes (tile tails in M, N and K)."""
+    from crosslayer_coding_b200.ops import ext as ext_mod
+
+    e = ext_mod.load()
+    dev = _dev()
+    torch.manual_seed(2)
+    LA, LB, M, N, K = 4, 5, 200, 328, 136
+    A = (torch.randn(LA, M, K, device=dev) * 0.5).to(dtype)
+    Bm = (torch.randn(LB, N, K, device=dev) * 0.5).to(dtype)
+    groups = [[(0, 1)], [(1, 0), (2, 4), (3, 3)], [(3, 2), (0, 0)]]
+    off = torch.tensor([0, 1, 4, 6], dtype=torch.int32, device=dev)
+    segs = torch.tensor([p for g in groups for p in g], dtype=torch.int32, device=dev)
+    C = torch.empty(len(groups), M, N, dtype=torch.float32 if out_dtype == "f32" else dtype, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    e.dense_gemm(A, Bm, C, off, segs, -0.25, status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    for g, seg in enumerate(groups):
+        want = -0.25 * sum(A[a].float() @ Bm[b].float().t() for a, b in seg)
+        tol = 2e-3 if out_dtype == "f32" else 3e-2
+        assert torch.allclose(C[g].float(), want, rtol=tol, atol=tol), (g, (C[g].float() - want).abs().max())
+    # transposes and the negative-indicator pass
+    T = torch.empty(LA, K, M, dtype=dtype, device=dev)
+    e.transpose16(A, T)
+    assert torch.equal(T, A.transpose(1, 2).contiguous())
+    pre = torch.randn(3, 130, 72, device=dev).to(dtype)
+    ind = torch.empty(3, 72, 130, dtype=dtype, device=dev)
+    bias_grad = torch.zeros(3, 72, device=dev)
+    loss = torch.zeros(1, dtype=torch.float64, device=dev)
+    e.negative_indicator(pre, ind, bias_grad, loss, 64, 0.5)     # the last 8 columns are padding
+    neg = (pre.float() < 0)
+    neg[:, :, 64:] = False
+    assert torch.equal(ind.float(), neg.float().transpose(1, 2))
+    assert torch.allclose(bias_grad, -0.5 * neg.float().sum(dim=1)) and abs(float(loss) - 0.5 * float((-pre.float() * neg).sum())) < 1e-2
