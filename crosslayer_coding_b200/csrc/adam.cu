@@ -488,6 +488,7 @@ __global__ void __launch_bounds__(288) decoder_rows_adam_bulk_kernel(const DecAd
         const bool in = mt.b + j < mt.e;
         mt.tok[j] = in ? __ldg(p.fcsr_tok + mt.b + j) : 0;
         mt.a[j] = in ? __ldg(p.fcsr_val + mt.b + j) : 0.f;
+        if (!clt_in_bounds(mt.tok[j], B, status, 201)) { mt.tok[j] = 0; mt.a[j] = 0.f; }  // debug build: token index from the CSR
       }
     };
     // rows are touched once per step, the gradient seed is re-read by every feature: keep the latter in L2

@@ -42,7 +42,26 @@ enum StatusCode : int {
   STATUS_CAPACITY = 2,           // an output list did not fit its buffer
   STATUS_SELECT_RANGE = 3,       // threshold not inside the histogram range
   STATUS_TIE_OVERFLOW = 4,       // more ties at the cut than the tie buffer holds
+  STATUS_BOUNDS = 5,             // debug build (-DCLT_DEBUG_BOUNDS): an index or peer offset was out of range; the access was skipped
 };
+
+// Index checks of the debug build.  Compute-sanitizer is not available everywhere these kernels run, so the build with
+// -DCLT_DEBUG_BOUNDS checks the indices that come from data (entry lists, token ids, peer ranks and offsets) before they
+// are used: a bad one records STATUS_BOUNDS, the site code and the offending value in the status words 0, 2 and 3 and the
+// access is skipped - nothing traps and nothing is read or written out of range.  In the regular build the check
+// compiles to `true`.
+#ifdef CLT_DEBUG_BOUNDS
+__device__ __forceinline__ bool clt_in_bounds(long long idx, long long limit, int* status, int site) {
+  if (idx >= 0 && idx < limit) return true;
+  if (status != nullptr && atomicCAS(status, STATUS_OK, STATUS_BOUNDS) == STATUS_OK) {
+    status[2] = site;
+    status[3] = int(idx);
+  }
+  return false;
+}
+#else
+__device__ __forceinline__ bool clt_in_bounds(long long, long long, int*, int) { return true; }
+#endif
 
 // ~1 s at 2 GHz; every spin-wait in this library gives up after this many cycles.
 constexpr long long kWaitTimeoutCycles = 2000000000LL;

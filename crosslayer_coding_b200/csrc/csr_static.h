@@ -23,6 +23,10 @@
 //   * Every call on a device shares the one scratch array, and the array keeps whatever the previous call left
 //     there; the counters are cleared at the start of each call.  Two calls whose work overlaps on the same GPU
 //     (different streams, different threads) race on it - serialise them.
+//   * Entries are range-checked on the device: an entry whose token is outside [0, num_tokens) or whose column is outside
+//     [0, num_cols) (a stale entry count, a wrong col_pitch) is left out of both views; tok_off[num_tokens] and
+//     feat_off[num_cols] then add up to less than the entry count, which is how a caller can notice.  Nothing is
+//     written outside the scratch regions of this call or beyond `ent_cap` slots of the payload arrays.
 //   * Inputs and outputs are the caller's: entries (ent_*), the control block `ctl` whose slot 3 holds the entry
 //     count (as written by clt_batchtopk_select), the offset arrays tok_off[num_tokens + 1] and
 //     feat_off[num_cols + 1], and the four CSR payload arrays of capacity `ent_cap`.

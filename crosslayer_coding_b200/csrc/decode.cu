@@ -44,6 +44,7 @@ struct DecodeParams {
   // seed that leaves the 16-bit range or is NaN raises ctl[SC_FOUND_INF] (the step is then skipped)
   float* ctl;
   int rows_limit;  // > 0: only the first rows_limit target rows of a feature are decoded (auxiliary loss: same layer only)
+  int* dbg_status; // status words for the index checks of the debug build (may be null)
 };
 
 __device__ __forceinline__ void fma8(float (&acc)[8], float a, const uint4& v) {
@@ -70,6 +71,7 @@ __device__ __forceinline__ float decode_epilogue(const DecodeParams& p, int tok,
     // reduce-scatter by push: peer store into the owner's slot for this rank (NVLink posted writes)
     const int owner = tok / p.rows_per_rank;
     const int lrow = tok - owner * p.rows_per_rank;
+    if (!clt_in_bounds(owner, p.world, p.dbg_status, 105)) return 0.f;  // peer rank derived from the token index
     float4* dst = reinterpret_cast<float4*>(p.stage_peers[owner] + ((1LL * p.rank * p.L + t) * p.rows_per_rank + lrow) * p.d + e0);
     dst[0] = make_float4(a[0], a[1], a[2], a[3]);
     dst[1] = make_float4(a[4], a[5], a[6], a[7]);
@@ -149,6 +151,7 @@ __global__ void __launch_bounds__(1024) decode_kernel(const DecodeParams p, int 
       const int s = col >> 24;
       const int f = col & 0xFFFFFF;
       if (a == 0.f) continue;
+      if (!clt_in_bounds(s, L, p.dbg_status, 101) || !clt_in_bounds(f, p.col_pitch, p.dbg_status, 102)) continue;
       if (tying == 0) {
         // row (t - s) of feature f; rows of one feature are contiguous
         const t16* base = w_s[s] + (1LL * f * rows_s[s] - s) * d + e0;
@@ -258,13 +261,14 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
         const int st = issued % nstages;
         const uint32_t ph = (issued / nstages) & 1;
         const int col = col_next;
-        const float a = a_next;
+        float a = a_next;
         if (i + 1 < e) {  // the next entry's index is in flight while this stage is waited for
           col_next = __ldg(p.tcsr_col + i + 1);
           a_next = __ldg(p.tcsr_val + i + 1);
         }
         if (!mbar_wait(&sh->empty[st], ph ^ 1, abort_flag)) break;
-        const int sl = col >> 24, f = col & 0xFFFFFF;
+        int sl = col >> 24, f = col & 0xFFFFFF;
+        if (!clt_in_bounds(sl, L, p.dbg_status, 103) || !clt_in_bounds(f, p.col_pitch, p.dbg_status, 104)) { sl = 0; f = 0; a = 0.f; }  // decode a harmless row with weight zero
         const int R = sh->rows_s[sl];
         const int r_eff = (p.rows_limit > 0 && p.rows_limit < R) ? p.rows_limit : R;
         const uint32_t bytes = uint32_t(r_eff) * uint32_t(d) * 2u;
@@ -471,7 +475,7 @@ extern "C" int CLT_FN(clt_sparse_decode)(const CltDecodeArgs* a, cudaStream_t st
   p.gs = static_cast<t16*>(a->gs); p.yhat_out = a->yhat_out; p.sq_err = a->sq_err; p.mode = a->mode;
   for (int i = 0; i < 8; ++i) p.stage_peers[i] = static_cast<float*>(a->stage_peers[i]);
   p.rows_per_rank = a->rows_per_rank; p.rank = a->rank; p.world = a->world;
-  p.ctl = a->ctl; p.rows_limit = a->rows_limit;
+  p.ctl = a->ctl; p.rows_limit = a->rows_limit; p.dbg_status = a->status;
   const int gthreads = ((a->d / 8 + 31) / 32) * 32;
   const int threads = gthreads * kGroups;
   if (threads > 1024) return -1;

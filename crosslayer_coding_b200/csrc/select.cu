@@ -1078,14 +1078,19 @@ __global__ void __launch_bounds__(256) finalize_kernel(Lists o, FlatGeom fg, lon
 __global__ void __launch_bounds__(256) csr_count_kernel(const int* __restrict__ ent_tok, const int* __restrict__ ent_col,
                                                           const float* __restrict__ ent_val, long long cap,
                                                           const long long* __restrict__ ctl, int* __restrict__ tok_cnt,
-                                                          int* __restrict__ feat_cnt, unsigned char* __restrict__ fired) {
+                                                          int* __restrict__ feat_cnt, unsigned char* __restrict__ fired,
+                                                          int num_tokens, int num_cols) {
   long long n = ctl[CTL_NUM_ENTRIES];
   if (n > cap) n = cap;
   for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
-    atomicAdd(&tok_cnt[ent_tok[i]], 1);
+    const int t = ent_tok[i];
     const int c = ent_col[i];
+    // an entry outside the problem (a stale count, a wrong pitch on the caller's side) is left out of both views
+    // instead of being counted into a neighbouring region
+    if (t < 0 || t >= num_tokens || c < 0 || c >= num_cols) continue;
+    atomicAdd(&tok_cnt[t], 1);
     atomicAdd(&feat_cnt[c], 1);
-    if (fired != nullptr && ent_val[i] > 1e-6f) fired[c] = 1;
+    if (fired != nullptr && ent_val[i] > 1e-6f) fired[c] = 1;  // c was range-checked above
   }
 }
 
@@ -1215,26 +1220,30 @@ __global__ void __launch_bounds__(256) csr_scatter_kernel(const int* __restrict_
                                                             const long long* __restrict__ ctl, int* __restrict__ tok_cursor,
                                                             int* __restrict__ feat_cursor, int* __restrict__ tcsr_col,
                                                             float* __restrict__ tcsr_val, int* __restrict__ fcsr_tok,
-                                                            float* __restrict__ fcsr_val, int col_pitch) {
+                                                            float* __restrict__ fcsr_val, int col_pitch, int num_tokens, int num_cols) {
   long long n = ctl[CTL_NUM_ENTRIES];
   if (n > cap) n = cap;
   for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
     const int t = ent_tok[i], c = ent_col[i];
+    if (t < 0 || t >= num_tokens || c < 0 || c >= num_cols) continue;  // the same entries that the count pass left out
     const float v = ent_val[i];
     const int p = atomicAdd(&tok_cursor[t], 1);
     const int layer = c / col_pitch;  // token-major view stores (layer << 24) | feature for the decoder
-    tcsr_col[p] = (layer << 24) | (c - layer * col_pitch); tcsr_val[p] = v;
+    if (p >= 0 && p < cap) { tcsr_col[p] = (layer << 24) | (c - layer * col_pitch); tcsr_val[p] = v; }
     const int q = atomicAdd(&feat_cursor[c], 1);
-    fcsr_tok[q] = t; fcsr_val[q] = v;
+    if (q >= 0 && q < cap) { fcsr_tok[q] = t; fcsr_val[q] = v; }
   }
 }
 
 // Sort every CSR segment by its integer key (segments are short: insertion sort by one thread), so the
 // order of the entries - and with it every floating-point sum over a segment - is reproducible.
+constexpr int kShortSegment = 32;  // longer segments are sorted by a whole CTA (csr_sort_long_segments_kernel)
+
 __global__ void __launch_bounds__(256) csr_sort_segments_kernel(const int* __restrict__ off, int nseg, int* __restrict__ key,
                                                                   float* __restrict__ val) {
   for (int sidx = blockIdx.x * blockDim.x + threadIdx.x; sidx < nseg; sidx += gridDim.x * blockDim.x) {
     const int b = off[sidx], e = off[sidx + 1];
+    if (e - b > kShortSegment) continue;
     for (int i = b + 1; i < e; ++i) {
       const int k = key[i];
       const float v = val[i];
@@ -1242,6 +1251,47 @@ __global__ void __launch_bounds__(256) csr_sort_segments_kernel(const int* __res
       while (j >= b && key[j] > k) { key[j + 1] = key[j]; val[j + 1] = val[j]; --j; }
       key[j + 1] = k; val[j + 1] = v;
     }
+  }
+}
+
+// Long segments (a feature that fires on most tokens of the batch, a token with a thousand active features): an insertion
+// sort by one thread would take O(n^2) dependent global-memory moves.  Here a CTA walks the segments, skips the short
+// ones and sorts a long one cooperatively with a bitonic network in place (keys inside a segment are distinct, so no
+// stability is needed); out-of-range partners of the virtual power-of-two padding are skipped.
+__global__ void __launch_bounds__(256) csr_sort_long_segments_kernel(const int* __restrict__ off, int nseg, int* __restrict__ key,
+                                                                       float* __restrict__ val) {
+  for (int sidx = blockIdx.x; sidx < nseg; sidx += gridDim.x) {
+    const int b = off[sidx], n = off[sidx + 1] - b;
+    if (n <= kShortSegment) continue;  // uniform over the CTA
+    int* k = key + b;
+    float* v = val + b;
+    int p2 = 1;
+    while (p2 < n) p2 <<= 1;
+    // every comparator puts the smaller key at the lower index (the first step of a merge pairs mirrored positions), so
+    // the virtual padding, which stands for +infinity at the end of the array, never has to move
+    for (int size = 2; size <= p2; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < p2 / 2; i += blockDim.x) {
+          int lo, hi;
+          if (stride == (size >> 1)) {
+            const int blk = i / stride, j = i - blk * stride;
+            lo = blk * size + j;
+            hi = blk * size + size - 1 - j;
+          } else {
+            lo = 2 * i - (i & (stride - 1));
+            hi = lo + stride;
+          }
+          if (hi >= n) continue;
+          const int ka = k[lo], kb = k[hi];
+          if (ka > kb) {
+            k[lo] = kb; k[hi] = ka;
+            const float t = v[lo]; v[lo] = v[hi]; v[hi] = t;
+          }
+        }
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -1431,15 +1481,20 @@ struct CltCsrArgs {
 
 extern "C" int clt_build_csr(const CltCsrArgs* a, cudaStream_t st) {
   const int blocks = 592;
-  csr_count_kernel<<<blocks, 256, 0, st>>>(a->ent_tok, a->ent_col, a->ent_val, a->ent_cap, a->ctl, a->tok_cnt, a->feat_cnt, a->fired);
+  csr_count_kernel<<<blocks, 256, 0, st>>>(a->ent_tok, a->ent_col, a->ent_val, a->ent_cap, a->ctl, a->tok_cnt, a->feat_cnt, a->fired,
+                                           a->num_tokens, a->num_cols);
   launch_exclusive_scan(a->tok_cnt, a->tok_off, a->tok_cursor, a->num_tokens, st);
   launch_exclusive_scan(a->feat_cnt, a->feat_off, a->feat_cursor, a->num_cols, st);
   csr_scatter_kernel<<<blocks, 256, 0, st>>>(a->ent_tok, a->ent_col, a->ent_val, a->ent_cap, a->ctl, a->tok_cursor, a->feat_cursor,
-                                             a->tcsr_col, a->tcsr_val, a->fcsr_tok, a->fcsr_val, a->col_pitch);
-  if (a->sort_segments & 1)
+                                             a->tcsr_col, a->tcsr_val, a->fcsr_tok, a->fcsr_val, a->col_pitch, a->num_tokens, a->num_cols);
+  if (a->sort_segments & 1) {
     csr_sort_segments_kernel<<<(a->num_tokens + 255) / 256, 256, 0, st>>>(a->tok_off, a->num_tokens, a->tcsr_col, a->tcsr_val);
-  if (a->sort_segments & 2)
+    csr_sort_long_segments_kernel<<<a->num_tokens < 1184 ? a->num_tokens : 1184, 256, 0, st>>>(a->tok_off, a->num_tokens, a->tcsr_col, a->tcsr_val);
+  }
+  if (a->sort_segments & 2) {
     csr_sort_segments_kernel<<<(a->num_cols + 255) / 256, 256, 0, st>>>(a->feat_off, a->num_cols, a->fcsr_tok, a->fcsr_val);
+    csr_sort_long_segments_kernel<<<a->num_cols < 1184 ? a->num_cols : 1184, 256, 0, st>>>(a->feat_off, a->num_cols, a->fcsr_tok, a->fcsr_val);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -1507,13 +1562,19 @@ extern "C" int clt_build_csr_static(const int* ent_tok, const int* ent_col, cons
   if (cudaMemsetAsync(tok_cnt, 0, sizeof(int) * size_t(num_tokens), stream) != cudaSuccess) return -5;
   if (cudaMemsetAsync(feat_cnt, 0, sizeof(int) * size_t(num_cols), stream) != cudaSuccess) return -5;
   const int blocks = 592;
-  csr_count_kernel<<<blocks, 256, 0, stream>>>(ent_tok, ent_col, ent_val, ent_cap, ctl, tok_cnt, feat_cnt, nullptr);
+  csr_count_kernel<<<blocks, 256, 0, stream>>>(ent_tok, ent_col, ent_val, ent_cap, ctl, tok_cnt, feat_cnt, nullptr, num_tokens, num_cols);
   exclusive_scan_kernel<<<1, 1024, 0, stream>>>(tok_cnt, tok_off, tok_cursor, num_tokens);
   exclusive_scan_kernel<<<1, 1024, 0, stream>>>(feat_cnt, feat_off, feat_cursor, num_cols);
   csr_scatter_kernel<<<blocks, 256, 0, stream>>>(ent_tok, ent_col, ent_val, ent_cap, ctl, tok_cursor, feat_cursor, tcsr_col, tcsr_val,
-                                                 fcsr_tok, fcsr_val, col_pitch);
-  if (sort_segments & 1) csr_sort_segments_kernel<<<(num_tokens + 255) / 256, 256, 0, stream>>>(tok_off, num_tokens, tcsr_col, tcsr_val);
-  if (sort_segments & 2) csr_sort_segments_kernel<<<(num_cols + 255) / 256, 256, 0, stream>>>(feat_off, num_cols, fcsr_tok, fcsr_val);
+                                                 fcsr_tok, fcsr_val, col_pitch, num_tokens, num_cols);
+  if (sort_segments & 1) {
+    csr_sort_segments_kernel<<<(num_tokens + 255) / 256, 256, 0, stream>>>(tok_off, num_tokens, tcsr_col, tcsr_val);
+    csr_sort_long_segments_kernel<<<num_tokens < 1184 ? num_tokens : 1184, 256, 0, stream>>>(tok_off, num_tokens, tcsr_col, tcsr_val);
+  }
+  if (sort_segments & 2) {
+    csr_sort_segments_kernel<<<(num_cols + 255) / 256, 256, 0, stream>>>(feat_off, num_cols, fcsr_tok, fcsr_val);
+    csr_sort_long_segments_kernel<<<num_cols < 1184 ? num_cols : 1184, 256, 0, stream>>>(feat_off, num_cols, fcsr_tok, fcsr_val);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 #endif  // !CLT_T16_IS_HALF

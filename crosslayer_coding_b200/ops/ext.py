@@ -28,6 +28,11 @@ NVCC_FLAGS = [
 
 _lock = threading.Lock()
 _module = None
+_debug_module = None
+# CLT_DEBUG_BOUNDS=1 in the environment makes load() return the debug build: the same sources compiled with
+# -DCLT_DEBUG_BOUNDS, where indices that come from data are checked before use and reported through the status word
+DEBUG_ENV = "CLT_DEBUG_BOUNDS"
+DEBUG_NAME = EXT_NAME + "_dbg"
 
 
 def _so_path() -> Path:
@@ -46,22 +51,46 @@ def _stale() -> bool:
     return newest > os.path.getmtime(so)
 
 
-def build(verbose: bool = False):
-    """Compile every CUDA source for sm_100a and import the result."""
+def build(verbose: bool = False, debug: bool = False):
+    """Compile every CUDA source for sm_100a and import the result (``debug``: the index-checking build)."""
     from torch.utils import cpp_extension
 
-    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    out_dir = BUILD_DIR / "dbg" if debug else BUILD_DIR
+    out_dir.mkdir(parents=True, exist_ok=True)
     os.environ.setdefault("MAX_JOBS", "8")
     return cpp_extension.load(
-        name=EXT_NAME,
+        name=DEBUG_NAME if debug else EXT_NAME,
         sources=_sources(),
         extra_cflags=["-O3", "-std=c++17"],
-        extra_cuda_cflags=NVCC_FLAGS,
+        extra_cuda_cflags=NVCC_FLAGS + (["-DCLT_DEBUG_BOUNDS"] if debug else []),
         extra_include_paths=[str(CSRC)],
-        build_directory=str(BUILD_DIR),
+        build_directory=str(out_dir),
         with_cuda=True,
         verbose=verbose,
     )
+
+
+def load_debug(allow_build: bool = True):
+    """The index-checking build (``-DCLT_DEBUG_BOUNDS``), compiled on first use into ``_ext/dbg``."""
+    global _debug_module
+    with _lock:
+        if _debug_module is not None:
+            return _debug_module
+        so = BUILD_DIR / "dbg" / f"{DEBUG_NAME}.so"
+        newest = max(os.path.getmtime(p) for p in _sources() + [str(CSRC / "common.cuh"), str(CSRC / "clt_api.inc")])
+        if so.exists() and os.path.getmtime(so) >= newest:
+            import torch  # noqa: F401
+
+            spec = importlib.util.spec_from_file_location(DEBUG_NAME, str(so))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            sys.modules[DEBUG_NAME] = mod
+            _debug_module = mod
+            return mod
+        if not allow_build:
+            raise RuntimeError(f"{so} is missing or out of date; run __graft_entry__.build()")
+        _debug_module = build(debug=True)
+        return _debug_module
 
 
 def _import_prebuilt():
@@ -77,6 +106,8 @@ def _import_prebuilt():
 def load(allow_build: bool = True):
     """Return the extension module, importing the prebuilt ``.so`` or compiling it."""
     global _module
+    if os.environ.get(DEBUG_ENV, "") not in ("", "0"):
+        return load_debug(allow_build)
     with _lock:
         if _module is not None:
             return _module

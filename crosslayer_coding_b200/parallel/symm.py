@@ -9,6 +9,10 @@ kernels receive plain peer pointers).  It holds
 * ``stage``  ``[world][L][B/W][d]`` fp32 — partial reconstructions pushed by the peers' decode kernels,
 * ``gs``     ``[L][B][d]`` bf16 — gradient seed, written by the owners of the token rows.
 
+Every section is followed by a 256-byte guard filled with a fixed pattern; ``check_canaries`` reports the sections whose
+guard was overwritten (a peer store that ran past its slot).  Compute-sanitizer cannot watch peer stores of other
+processes, so this is the check that the index-checking build and the multi-GPU tests use.
+
 Reference counterpart: the NCCL collectives C1-C4 of the reference's forward pass
 (clt/models/parallel.py:143,197; clt/models/activations_local_global.py:122-123).  NCCL remains the control
 plane (barriers at setup, scalar all-reduces).
@@ -24,6 +28,7 @@ HIST_ROUNDS = 16
 HIST_BINS = 8192
 HIST_SLOT = HIST_BINS + 32  # a slot also carries the pool-overflow word of the selection
 BARRIER_SLOTS = 4
+CANARY = 0xC5  # byte pattern of the guard regions behind every section
 
 
 class SymmetricExchange:
@@ -41,11 +46,12 @@ class SymmetricExchange:
         def align(n: int) -> int:
             return (n + 255) // 256 * 256
 
-        self.hist_bytes = align(HIST_ROUNDS * W * HIST_SLOT * 4)
-        self.hflag_bytes = align(HIST_ROUNDS * W * 4)
-        self.bflag_bytes = align(BARRIER_SLOTS * W * 4)
-        self.stage_bytes = align(W * num_layers * self.rows_per_rank * d_model * 4)
-        self.gs_bytes = align(num_layers * batch_tokens * d_model * 2)
+        guard = 256
+        self.hist_bytes = align(HIST_ROUNDS * W * HIST_SLOT * 4) + guard
+        self.hflag_bytes = align(HIST_ROUNDS * W * 4) + guard
+        self.bflag_bytes = align(BARRIER_SLOTS * W * 4) + guard
+        self.stage_bytes = align(W * num_layers * self.rows_per_rank * d_model * 4) + guard
+        self.gs_bytes = align(num_layers * batch_tokens * d_model * 2) + guard
         total = self.hist_bytes + self.hflag_bytes + self.bflag_bytes + self.stage_bytes + self.gs_bytes
         self.buffer = symm_mem.empty(total, dtype=torch.uint8, device=device)
         self.buffer.zero_()
@@ -63,6 +69,13 @@ class SymmetricExchange:
         self.slot_elems = HIST_SLOT
         self.stage = self.buffer[o_stage : o_stage + W * num_layers * self.rows_per_rank * d_model * 4].view(torch.float32)
         self.gs = self.buffer[o_gs : o_gs + num_layers * batch_tokens * d_model * 2].view(torch.bfloat16).view(num_layers, batch_tokens, d_model)
+        self._guards = {}
+        end = 0
+        for name, nbytes in (("hist", self.hist_bytes), ("hflag", self.hflag_bytes), ("bflag", self.bflag_bytes), ("stage", self.stage_bytes),
+                             ("gs", self.gs_bytes)):
+            end += nbytes
+            self._guards[name] = self.buffer[end - guard: end]
+            self._guards[name].fill_(CANARY)
         self.barrier_seq = 0
         self.supports_reduce = True
         torch.cuda.synchronize(device)
@@ -71,6 +84,10 @@ class SymmetricExchange:
     @classmethod
     def create(cls, group, device, clt_config, batch_tokens: int) -> "SymmetricExchange":
         return cls(group, torch.device(device), clt_config.num_layers, batch_tokens, clt_config.d_model)
+
+    def check_canaries(self):
+        """Names of the sections whose guard bytes no longer hold the pattern (host read; for tests and debug runs)."""
+        return [name for name, g in self._guards.items() if not bool((g == CANARY).all().item())]
 
     def barrier(self, ext, status: torch.Tensor) -> None:
         """Cross-GPU phase barrier on the current stream (one tiny kernel, bounded wait)."""

@@ -36,7 +36,8 @@ from ..config import CLTConfig, TrainingConfig
 from ..ops import ext
 from ..parallel import ops as pops
 
-STATUS_NAMES = {0: "ok", 1: "wait timeout", 2: "list capacity exceeded", 3: "threshold outside histogram range", 4: "tie overflow"}
+STATUS_NAMES = {0: "ok", 1: "wait timeout", 2: "list capacity exceeded", 3: "threshold outside histogram range", 4: "tie overflow",
+                5: "index out of range (debug build)"}
 
 
 class EngineStatusError(RuntimeError):
@@ -347,6 +348,9 @@ class FusedBatchTopKEngine:
         # the gradient seed summed over those targets; with that sum in place of the seed the decoder update is the
         # one-row-per-feature case of the untied row pipeline
         self.gs_cum = torch.empty(L, B, d, dtype=self.t16, device=dev) if (self.tying == 1 and training_config is not None) else None
+        import os as _os
+
+        self._check_guards = _os.environ.get(ext.DEBUG_ENV, "") not in ("", "0")  # debug runs read the guard bytes at every status check
         self.opt_step = 0
         self.seq = 0
         self.kernel_launches = 0  # launches of this package's own kernels (reported by the benchmark)
@@ -787,9 +791,14 @@ class FusedBatchTopKEngine:
     def check_status(self) -> None:
         """Host read of the kernels' status word; raises when a kernel reported a problem."""
         code = int(self.status[0].item())
+        if self.symm is not None and hasattr(self.symm, "check_canaries") and (code != 0 or self._check_guards):
+            hit = self.symm.check_canaries()
+            if hit:
+                raise EngineStatusError(f"rank {self.rank}: guard bytes behind the exchange sections {hit} were overwritten")
         if code != 0:
+            detail = f" (site {int(self.status[2])}, value {int(self.status[3])})" if code == 5 else ""
             self.status.zero_()
-            raise EngineStatusError(f"rank {self.rank}: fused step reported '{STATUS_NAMES.get(code, code)}'")
+            raise EngineStatusError(f"rank {self.rank}: fused step reported '{STATUS_NAMES.get(code, code)}'{detail}")
 
     # ------------------------------------------------------- optimizer state io
     def optimizer_state_dict(self) -> Dict[str, torch.Tensor]:

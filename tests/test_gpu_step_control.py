@@ -361,3 +361,40 @@ def test_grouped_dense_gemm_matches_fp32_reference(dtype, out_dtype):
     neg[:, :, 64:] = False
     assert torch.equal(ind.float(), neg.float().transpose(1, 2))
     assert torch.allclose(bias_grad, -0.5 * neg.float().sum(dim=1)) and abs(float(loss) - 0.5 * float((-pre.float() * neg).sum())) < 1e-2
+
+
+def test_long_csr_segments_are_sorted_by_the_cooperative_path():
+    """A feature that fires on every token and a token with hundreds of entries: both CSR views come out sorted."""
+    from crosslayer_coding_b200.ops import ext as ext_mod
+
+    e = ext_mod.load()
+    dev = _dev()
+    g = torch.Generator().manual_seed(4)
+    T, L, pitch = 700, 2, 512
+    ncols = L * pitch
+    toks = torch.randperm(T, generator=g)                                   # column 5 on every token, shuffled
+    ent_tok = [toks, torch.full((600,), 3)]                                  # token 3 with 600 more columns
+    ent_col = [torch.full((T,), 5), torch.randperm(ncols - 10, generator=g)[:600] + 10]
+    more = torch.randperm(T * ncols, generator=g)[:2000]
+    more = more[((more % ncols) >= 10) & ((more // ncols) != 3)]
+    ent_tok.append(more // ncols)
+    ent_col.append(more % ncols)
+    tok = torch.cat(ent_tok).to(torch.int32).to(dev)
+    col = torch.cat(ent_col).to(torch.int32).to(dev)
+    n = tok.numel()
+    val = torch.randn(n, generator=g).to(dev)
+    ctl = torch.zeros(16, dtype=torch.int64, device=dev)
+    ctl[3] = n
+    i32, f32 = torch.int32, torch.float32
+    z = lambda k, dt=i32: torch.zeros(k, dtype=dt, device=dev)  # noqa: E731
+    tok_off, feat_off = z(T + 1), z(ncols + 1)
+    tcsr_col, tcsr_val, fcsr_tok, fcsr_val = z(n), z(n, f32), z(n), z(n, f32)
+    e.build_csr(tok, col, val, ctl, T, ncols, z(T), z(ncols), tok_off, feat_off, z(T), z(ncols), tcsr_col, tcsr_val, fcsr_tok, fcsr_val, None, 3, pitch)
+    torch.cuda.synchronize()
+    b, en = int(feat_off[5]), int(feat_off[6])
+    assert en - b == T and torch.equal(fcsr_tok[b:en].cpu(), torch.arange(T, dtype=torch.int32))
+    order = torch.argsort(toks)
+    assert torch.equal(fcsr_val[b:en].cpu(), val[:T].cpu()[order])          # values moved with their keys
+    b, en = int(tok_off[3]), int(tok_off[4])
+    seg = tcsr_col[b:en].cpu()
+    assert en - b >= 600 and bool((seg[1:] > seg[:-1]).all())

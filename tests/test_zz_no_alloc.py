@@ -87,3 +87,62 @@ def test_static_csr_rejects_oversized_problems():
     assert rc == -2
     rc = fn(p, p, f.data_ptr(), 64, ctl.data_ptr(), 0, 16, 16, p, p, p, f.data_ptr(), p, f.data_ptr(), 0, None)
     assert rc == -1
+
+
+def test_static_csr_skips_out_of_range_entries_and_handles_the_size_limits():
+    """Entries outside the problem are left out of both views (nothing is written outside this call's regions), and a
+    problem at the documented limits (65 536 tokens, 1 048 576 columns) goes through."""
+    from crosslayer_coding_b200.ops import ext as ext_mod
+
+    ext_mod.load()
+    lib = ctypes.CDLL(ext_mod.so_file())
+    fn = lib.clt_build_csr_static
+    fn.restype = ctypes.c_int
+    vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+    fn.argtypes = [vp, vp, vp, ll, vp, ci, ci, ci, vp, vp, vp, vp, vp, vp, ci, vp]
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call(tok, col, val, ctl, num_tokens, num_cols, col_pitch):
+        out = _alloc_outputs(tok.numel(), num_tokens, num_cols, dev)
+        rc = fn(tok.data_ptr(), col.data_ptr(), val.data_ptr(), tok.numel(), ctl.data_ptr(), num_tokens, num_cols, col_pitch,
+                out["tok_off"].data_ptr(), out["feat_off"].data_ptr(), out["tcsr_col"].data_ptr(), out["tcsr_val"].data_ptr(),
+                out["fcsr_tok"].data_ptr(), out["fcsr_val"].data_ptr(), 3, stream)
+        torch.cuda.synchronize()
+        return rc, out
+
+    num_tokens, num_layers, col_pitch = 40, 2, 64
+    tok, col, val, ctl = _make_entries(5, 200, num_tokens, num_layers, col_pitch, dev)
+    good_rc, good = call(tok, col, val, ctl, num_tokens, num_layers * col_pitch, col_pitch)
+    bad_tok, bad_col = tok.clone(), col.clone()
+    bad_tok[7] = num_tokens + 3          # token beyond the problem
+    bad_col[11] = num_layers * col_pitch  # first column beyond the problem
+    bad_col[13] = -1
+    rc, got = call(bad_tok, bad_col, val, ctl, num_tokens, num_layers * col_pitch, col_pitch)
+    assert good_rc == 0 and rc == 0
+    assert int(got["tok_off"][-1]) == 197 and int(got["feat_off"][-1]) == 197
+    keep = torch.ones(200, dtype=torch.bool, device=dev)
+    keep[[7, 11, 13]] = False
+    ctl2 = ctl.clone()
+    ctl2[3] = 197
+    rc, want = call(tok[keep].contiguous(), col[keep].contiguous(), val[keep].contiguous(), ctl2, num_tokens, num_layers * col_pitch, col_pitch)
+    for name in ("tok_off", "feat_off"):
+        assert torch.equal(got[name], want[name]), name
+    for name in ("tcsr_col", "tcsr_val", "fcsr_tok", "fcsr_val"):
+        assert torch.equal(got[name][:197], want[name][:197]), name
+    # at the limits
+    T, C = 65536, 1 << 20
+    g = torch.Generator().manual_seed(9)
+    n = 5000
+    tok = torch.randint(0, T, (n,), generator=g).to(torch.int32).to(dev)
+    col = torch.randperm(C, generator=g)[:n].to(torch.int32).to(dev)
+    tok[0], col[0] = T - 1, C - 1
+    val = torch.randn(n, generator=g).to(dev)
+    ctl = torch.zeros(16, dtype=torch.int64, device=dev)
+    ctl[3] = n
+    rc, out = call(tok, col, val, ctl, T, C, 1 << 16)
+    assert rc == 0 and int(out["tok_off"][-1]) == n and int(out["feat_off"][-1]) == n
+    cnt = torch.bincount(tok.long(), minlength=T)
+    assert torch.equal(out["tok_off"][1:].long() - out["tok_off"][:-1].long(), cnt)
+    assert int(out["feat_off"][C]) - int(out["feat_off"][C - 1]) == 1
