@@ -140,6 +140,14 @@ int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int*
 int clt_sparsity_penalty(const int* feat_off, const float* fcsr_val, const float* norm2, int ncols, float lambda, float c,
                          float* grad_a, float* pen_coef, double* penalty_out, cudaStream_t st);
 int clt_step_control(const CltStepControlArgs* a, const CltExchangeArgs* exa, cudaStream_t st);
+int clt_aux_compact(const long long* dead_counter, long long window, int L, int F_pitch, int F_valid, int nd_cap, int* dead_cols, int* nd,
+                    int* nd_all, int* extra_idx, cudaStream_t st);
+int clt_scatter_add_rows(float* dst, float* dst_bias, const float* src, const float* src_bias, const int* extra_idx, long long n_dst_rows, int d,
+                         cudaStream_t st);
+struct CltAuxRowsArgs {
+  const void* w[32];
+  int rows[32];
+};
 // entry points that exist once per 16-bit storage type: name (bf16) and name_h (fp16)
 #define CLT_API(name) name
 #include "clt_api.inc"
@@ -758,14 +766,18 @@ void dense_gemm(const Tensor& A, const Tensor& B, Tensor& C, const Tensor& group
         "dense_gemm");
 }
 
-// out[l] = in[l]^T for 16-bit [L, R, C] tensors
-void transpose16(const Tensor& in, Tensor& out) {
+// out[l] = in[l]^T for 16-bit [L, R, C] tensors; with `mask` (shape of `in`) the elements whose mask value is zero become zero
+void transpose16(const Tensor& in, Tensor& out, const OptTensor& mask) {
   const bool half = is_half(in, "in");
   need(in, t16_of(half), "in"); need(out, t16_of(half), "out");
+  if (mask.has_value() && mask->defined()) {
+    need(*mask, t16_of(half), "mask");
+    TORCH_CHECK(mask->sizes() == in.sizes(), "mask: the shape of in");
+  }
   TORCH_CHECK(in.dim() == 3 && out.dim() == 3 && out.size(0) == in.size(0) && out.size(1) == in.size(2) && out.size(2) == in.size(1), "in [L, R, C], out [L, C, R]");
   c10::cuda::CUDAGuard guard(in.device());
   check(CLT_PICK(half, clt_transpose16)(in.data_ptr(), out.data_ptr(), int(in.size(0)), int(in.size(1)), int(in.size(2)), in.size(2),
-                                        in.size(1) * in.size(2), cur_stream()), "transpose16");
+                                        in.size(1) * in.size(2), opt_ptr<const void>(mask), cur_stream()), "transpose16");
 }
 
 // ind[l][f, b] = 1[pre[l][b, f] < 0]; bias_grad[l, f] -= c * count; loss[0] += c * sum relu(-pre)   (c = coef / numel)
@@ -778,6 +790,97 @@ void negative_indicator(const Tensor& pre, Tensor& ind, Tensor& bias_grad, Tenso
   check(CLT_PICK(half, clt_negative_indicator)(pre.data_ptr(), ind.data_ptr(), bias_grad.data_ptr<float>(), loss.data_ptr<double>(), int(pre.size(0)),
                                                int(pre.size(1)), int(pre.size(2)), int(f_valid), pre.size(2), float(coef_over_numel), cur_stream()),
         "negative_indicator");
+}
+
+// ---- auxiliary loss on dead features (aux.cu)
+// dead_cols [L, nd_cap], nd / nd_all [L], extra_idx [L * F_pitch] from the counters: feature f of layer l is dead when counter > window
+void aux_compact(const Tensor& counter, int64_t window, int64_t L, int64_t f_valid, Tensor& dead_cols, Tensor& nd, Tensor& nd_all, Tensor& extra_idx) {
+  need(counter, at::kLong, "counter"); need(dead_cols, at::kInt, "dead_cols"); need(nd, at::kInt, "nd"); need(nd_all, at::kInt, "nd_all");
+  need(extra_idx, at::kInt, "extra_idx");
+  TORCH_CHECK(counter.numel() % L == 0 && dead_cols.dim() == 2 && dead_cols.size(0) == L && nd.numel() == L && nd_all.numel() == L &&
+              extra_idx.numel() == counter.numel(), "counter [L * F], dead_cols [L, nd_cap], nd [L], nd_all [L], extra_idx [L * F]");
+  c10::cuda::CUDAGuard guard(counter.device());
+  check(clt_aux_compact(reinterpret_cast<const long long*>(counter.data_ptr<int64_t>()), window, int(L), int(counter.numel() / L), int(f_valid),
+                        int(dead_cols.size(1)), dead_cols.data_ptr<int>(), nd.data_ptr<int>(), nd_all.data_ptr<int>(), extra_idx.data_ptr<int>(),
+                        cur_stream()), "aux_compact");
+}
+
+// A [L, B, nd_cap]: per token the top k_aux dead pre-activations of the layer (the others zero).  Either `pre` [L, B, F] (the
+// stored pre-activations, gathered at the dead columns) or `enc_bias` [L, F] (A already holds x W_dead^T; the bias is added and
+// A is rewritten in place).
+void aux_gather_select(const OptTensor& pre, const OptTensor& enc_bias, const Tensor& dead_cols, const Tensor& nd, const Tensor& nd_all,
+                       int64_t k_aux_max, Tensor& A) {
+  const bool half = is_half(A, "A");
+  need(A, t16_of(half), "A"); need(dead_cols, at::kInt, "dead_cols"); need(nd, at::kInt, "nd"); need(nd_all, at::kInt, "nd_all");
+  const bool from_pre = pre.has_value() && pre->defined();
+  TORCH_CHECK(from_pre != (enc_bias.has_value() && enc_bias->defined()), "either pre or enc_bias");
+  TORCH_CHECK(A.dim() == 3 && A.size(2) == dead_cols.size(1) && dead_cols.size(0) == A.size(0), "A [L, B, nd_cap], dead_cols [L, nd_cap]");
+  const void* pre_p = nullptr; const void* bias_p = nullptr;
+  int64_t ld = 0, stride = 0, f_pitch = 0; int bias16 = 0;
+  if (from_pre) {
+    need(*pre, t16_of(half), "pre");
+    TORCH_CHECK(pre->dim() == 3 && pre->size(0) == A.size(0) && pre->size(1) == A.size(1), "pre [L, B, F]");
+    pre_p = pre->data_ptr(); ld = pre->size(2); stride = pre->size(1) * pre->size(2);
+  } else {
+    TORCH_CHECK(enc_bias->is_cuda() && enc_bias->is_contiguous() && enc_bias->dim() == 2 && enc_bias->size(0) == A.size(0) &&
+                (enc_bias->scalar_type() == at::kFloat || enc_bias->scalar_type() == t16_of(half)), "enc_bias [L, F], fp32 or the 16-bit type");
+    bias_p = enc_bias->data_ptr(); f_pitch = enc_bias->size(1); bias16 = enc_bias->scalar_type() == at::kFloat ? 0 : 1;
+  }
+  c10::cuda::CUDAGuard guard(A.device());
+  check(CLT_PICK(half, clt_aux_gather_select)(pre_p, ld, stride, bias_p, bias16, int(f_pitch), dead_cols.data_ptr<int>(), nd.data_ptr<int>(),
+                                              nd_all.data_ptr<int>(), int(A.size(2)), int(k_aux_max), int(A.size(0)), int(A.size(1)), A.data_ptr(),
+                                              cur_stream()), "aux_gather_select");
+}
+
+// W0 [L, nd_cap, d]: first row (the layer's own target) of every dead feature's decoder block
+void aux_gather_rows(const std::vector<Tensor>& dec_w, const Tensor& dead_cols, const Tensor& nd, Tensor& W0) {
+  TORCH_CHECK(!dec_w.empty() && dec_w.size() <= 32 && W0.dim() == 3 && int64_t(dec_w.size()) == W0.size(0), "one decoder tensor per layer (at most 32)");
+  const bool half = is_half(W0, "W0");
+  CltAuxRowsArgs a{};
+  for (size_t i = 0; i < dec_w.size(); ++i) {
+    need(dec_w[i], t16_of(half), "dec_w");
+    TORCH_CHECK(dec_w[i].dim() == 3 && dec_w[i].size(2) == W0.size(2), "dec_w[l] [F, R, d]");
+    a.w[i] = dec_w[i].data_ptr(); a.rows[i] = int(dec_w[i].size(1));
+  }
+  c10::cuda::CUDAGuard guard(W0.device());
+  check(CLT_PICK(half, clt_aux_gather_rows)(&a, dead_cols.data_ptr<int>(), nd.data_ptr<int>(), int(W0.size(1)), int(W0.size(0)), int(W0.size(2)),
+                                            W0.data_ptr(), cur_stream()), "aux_gather_rows");
+}
+
+// r = recon + bias[bias_row[l]] - residual(gs); loss[0] += factor mean r^2; g = dL/d recon (16-bit); gs += the term's gradient through the residual
+void aux_residual(const Tensor& recon, const Tensor& bias, const Tensor& bias_row, const c10::optional<Tensor>& sigma, Tensor& gs, Tensor& g_out,
+                  Tensor& loss, const Tensor& nd, const c10::optional<Tensor>& ctl, double factor) {
+  const bool half = is_half(gs, "gs");
+  need(recon, at::kFloat, "recon"); need(gs, t16_of(half), "gs"); need(g_out, t16_of(half), "g_out"); need(loss, at::kDouble, "loss");
+  need(bias_row, at::kInt, "bias_row"); need(nd, at::kInt, "nd");
+  TORCH_CHECK(bias.is_cuda() && bias.is_contiguous() && (bias.scalar_type() == at::kFloat || bias.scalar_type() == t16_of(half)), "bias: fp32 or the 16-bit type");
+  TORCH_CHECK(recon.dim() == 3 && gs.sizes() == recon.sizes() && g_out.sizes() == recon.sizes(), "recon, gs, g_out [L, B, d]");
+  c10::cuda::CUDAGuard guard(gs.device());
+  check(CLT_PICK(half, clt_aux_residual)(recon.data_ptr<float>(), bias.data_ptr(), bias.scalar_type() == at::kFloat ? 0 : 1, bias_row.data_ptr<int>(),
+                                         opt_ptr<float>(sigma), gs.data_ptr(), g_out.data_ptr(), loss.data_ptr<double>(), nd.data_ptr<int>(),
+                                         ctl_ptr(ctl), int(recon.size(0)), int(recon.size(1)), int(recon.size(2)), float(factor), cur_stream()),
+        "aux_residual");
+}
+
+// out[r] = sum of row r of the 16-bit matrix in [rows, n]
+void rowsum16(const Tensor& in, Tensor& out) {
+  const bool half = is_half(in, "in");
+  need(in, t16_of(half), "in"); need(out, at::kFloat, "out");
+  const int64_t n = in.size(-1);
+  TORCH_CHECK(out.numel() * n == in.numel(), "out: one value per row");
+  c10::cuda::CUDAGuard guard(in.device());
+  check(CLT_PICK(half, clt_rowsum16)(in.data_ptr(), out.data_ptr<float>(), out.numel(), int(n), cur_stream()), "rowsum16");
+}
+
+// dst[r, :] += src[extra_idx[r], :] (and dst_bias[r] += src_bias[extra_idx[r]]) for the rows with extra_idx >= 0
+void scatter_add_rows(Tensor& dst, const c10::optional<Tensor>& dst_bias, const Tensor& src, const c10::optional<Tensor>& src_bias, const Tensor& extra_idx) {
+  need(dst, at::kFloat, "dst"); need(src, at::kFloat, "src"); need(extra_idx, at::kInt, "extra_idx");
+  const int64_t d = dst.size(-1);
+  TORCH_CHECK(src.size(-1) == d && dst.numel() == extra_idx.numel() * d, "dst [rows, d], src [n, d], extra_idx [rows]");
+  TORCH_CHECK(dst_bias.has_value() == src_bias.has_value(), "both bias tensors or none");
+  c10::cuda::CUDAGuard guard(dst.device());
+  check(clt_scatter_add_rows(dst.data_ptr<float>(), opt_ptr<float>(dst_bias), src.data_ptr<float>(), opt_ptr<float>(src_bias), extra_idx.data_ptr<int>(),
+                             extra_idx.numel(), int(d), cur_stream()), "scatter_add_rows");
 }
 
 }  // namespace
@@ -833,9 +936,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("bandwidth"), py::arg("hyper"), py::arg("ctl") = none, py::arg("norm_weight") = 0.0, py::arg("grad_out") = none);
   m.def("theta_exp", &theta_exp);
   m.def("dense_gemm", &dense_gemm);
-  m.def("transpose16", &transpose16);
+  m.def("transpose16", &transpose16, py::arg("inp"), py::arg("out"), py::arg("mask") = none);
   m.def("negative_indicator", &negative_indicator);
   m.def("scale_histogram", &scale_histogram);
+  m.def("aux_compact", &aux_compact);
+  m.def("aux_gather_select", &aux_gather_select);
+  m.def("aux_gather_rows", &aux_gather_rows);
+  m.def("aux_residual", &aux_residual);
+  m.def("rowsum16", &rowsum16);
+  m.def("scatter_add_rows", &scatter_add_rows);
   m.def("normalize_cast", &normalize_cast, py::arg("inp"), py::arg("out"), py::arg("mean") = none, py::arg("inv_std") = none,
         py::arg("rows_per_stat") = 0, py::arg("mul") = 1.0);
 }

@@ -253,6 +253,53 @@ __global__ void __launch_bounds__(256) transpose16_kernel(const t16* __restrict_
   }
 }
 
+// The same for shapes and addresses that allow 16-byte accesses on both sides (R, C, ld_in multiples of 8).  With `mask`
+// (same layout as `in`) the elements whose mask value is zero are written as zero: the straight-through gradient of a
+// selection, applied while the gradient is transposed for the GEMM that consumes it.
+__global__ void __launch_bounds__(256) transpose16_vec_kernel(const t16* __restrict__ in, const t16* __restrict__ mask, t16* __restrict__ out, int R,
+                                                                int C, long long ld_in, long long layer_stride_in) {
+  __shared__ uint32_t tile[64][33];  // 64 rows x 64 elements, two per word
+  const int l = blockIdx.z;
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const t16* src = in + 1LL * l * layer_stride_in;
+  const t16* msk = mask != nullptr ? mask + 1LL * l * layer_stride_in : nullptr;
+  t16* dst = out + 1LL * l * R * C;
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int r = (threadIdx.x >> 3) + 32 * it, v = threadIdx.x & 7;
+    uint4 q = make_uint4(0, 0, 0, 0);
+    if (r0 + r < R && c0 + 8 * v < C) {
+      q = __ldg(reinterpret_cast<const uint4*>(src + 1LL * (r0 + r) * ld_in + c0 + 8 * v));
+      if (msk != nullptr) {
+        const uint4 k = __ldg(reinterpret_cast<const uint4*>(msk + 1LL * (r0 + r) * ld_in + c0 + 8 * v));
+        const uint32_t ku[4] = {k.x, k.y, k.z, k.w};
+        uint32_t qu[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if ((ku[j] & 0x7FFFu) == 0u) qu[j] &= 0xFFFF0000u;
+          if ((ku[j] & 0x7FFF0000u) == 0u) qu[j] &= 0x0000FFFFu;
+        }
+        q = make_uint4(qu[0], qu[1], qu[2], qu[3]);
+      }
+    }
+    tile[r][4 * v + 0] = q.x; tile[r][4 * v + 1] = q.y; tile[r][4 * v + 2] = q.z; tile[r][4 * v + 3] = q.w;
+  }
+  __syncthreads();
+  const unsigned short* t16s = reinterpret_cast<const unsigned short*>(&tile[0][0]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int c = 8 * warp + (lane & 7), rg = 4 * it + (lane >> 3);  // output row c, elements 8 rg .. 8 rg + 7
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t lo = t16s[(8 * rg + 2 * j) * 66 + c], hi = t16s[(8 * rg + 2 * j + 1) * 66 + c];
+      w[j] = lo | (hi << 16);
+    }
+    if (c0 + c < C && r0 + 8 * rg < R) *reinterpret_cast<uint4*>(dst + 1LL * (c0 + c) * R + r0 + 8 * rg) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // Pre-activation loss, first half: ind[l][f, b] = 1 where pre[l][b, f] < 0 (transposed, as the A operand of the gradient
 // GEMM), loss[0] += coef / numel * sum relu(-pre), bias_grad[l, f] = -(coef / numel) * #{b : pre < 0}.
 __global__ void __launch_bounds__(256) negative_indicator_kernel(const t16* __restrict__ pre, t16* __restrict__ ind, float* __restrict__ bias_grad,
@@ -360,9 +407,17 @@ extern "C" int CLT_FN(clt_dense_gemm)(const void* A, int LA, long long lda, long
 }
 
 extern "C" int CLT_FN(clt_transpose16)(const void* in, void* out, int L, int R, int C, long long ld_in, long long layer_stride_in,
-                                       cudaStream_t st) {
+                                       const void* mask, cudaStream_t st) {
   if (L <= 0 || R <= 0 || C <= 0) return 0;
   dim3 grid((C + 63) / 64, (R + 63) / 64, L);
+  const bool vec = R % 8 == 0 && C % 8 == 0 && ld_in % 8 == 0 && layer_stride_in % 8 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(mask)) & 15) == 0;
+  if (vec) {
+    transpose16_vec_kernel<<<grid, 256, 0, st>>>(static_cast<const t16*>(in), static_cast<const t16*>(mask), static_cast<t16*>(out), R, C, ld_in,
+                                                 layer_stride_in);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  }
+  if (mask != nullptr) return -1;  // the masked form needs the 16-byte layout
   transpose16_kernel<<<grid, 256, 0, st>>>(static_cast<const t16*>(in), static_cast<t16*>(out), R, C, ld_in, layer_stride_in);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -19,7 +19,7 @@ CSRC = _PKG / "csrc"
 BUILD_DIR = _PKG / "_ext"
 EXT_NAME = "clt_b200_ext"
 # every kernel file is compiled for bf16 and, through a one-line wrapper that defines CLT_HALF, for fp16
-KERNEL_FILES = ["encoder_gemm.cu", "theta_grad_gemm.cu", "select.cu", "decode.cu", "adam.cu", "comm.cu", "step.cu", "dense_gemm.cu"]
+KERNEL_FILES = ["encoder_gemm.cu", "theta_grad_gemm.cu", "select.cu", "decode.cu", "adam.cu", "comm.cu", "step.cu", "dense_gemm.cu", "aux.cu"]
 SOURCES = ["bindings.cpp"] + KERNEL_FILES + [f"half/{name[:-3]}_h.cu" for name in KERNEL_FILES]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

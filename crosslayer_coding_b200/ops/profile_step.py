@@ -85,6 +85,9 @@ def main() -> None:
     ap.add_argument("--tying", choices=["none", "per_source", "per_target"], default="none")
     ap.add_argument("--precision", choices=["bf16", "fp16"], default="bf16")
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--dead-frac", type=float, default=0.0,
+                    help="mark this fraction of every layer's features dead and train with the auxiliary loss on them")
+    ap.add_argument("--preactivation-coef", type=float, default=0.0)
     ap.add_argument("--lr", type=float, default=None,
                     help="learning rate (default 1e-4; 1e-8 for jumprelu so that the active count of the synthetic data stays put)")
     ap.add_argument("--time", action="store_true", help="print CUDA-event timings instead of marking a profiler range")
@@ -94,15 +97,23 @@ def main() -> None:
     lam = eng.tc.sparsity_lambda
     lr = args.lr if args.lr is not None else (1e-8 if args.activation == "jumprelu" else 1e-4)
     L, d, F, B, k = CASES[args.case]
+    extra = {"preactivation_coef": args.preactivation_coef}
+    if args.dead_frac > 0:
+        # every (1 / frac)-th feature never fires again: its encoder bias is far below the cut
+        stride = max(1, int(round(1.0 / args.dead_frac)))
+        with torch.no_grad():
+            model.enc_bias.data[:, ::stride] = -30.0
+        eng.dead_counter.view(L, -1)[:, ::stride] = 10 ** 6
+        extra.update(aux_factor=1.0 / 32, dead_window=10 ** 5)
     for s in range(args.warmup):
-        eng.train_step(X, Y, s, lr, sparsity_lambda=lam)
+        eng.train_step(X, Y, s, lr, sparsity_lambda=lam, **extra)
     torch.cuda.synchronize()
     if args.time:
         e = eng.ext
         step = [args.warmup]
 
         def full():
-            eng.train_step(X, Y, step[0], lr, sparsity_lambda=lam)
+            eng.train_step(X, Y, step[0], lr, sparsity_lambda=lam, **extra)
             step[0] += 1
 
         res = {
@@ -133,7 +144,7 @@ def main() -> None:
         print(json.dumps(res))
         return
     torch.cuda.profiler.start()
-    eng.train_step(X, Y, args.warmup, lr, sparsity_lambda=lam)
+    eng.train_step(X, Y, args.warmup, lr, sparsity_lambda=lam, **extra)
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
     eng.check_status()

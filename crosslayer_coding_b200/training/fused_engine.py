@@ -638,9 +638,92 @@ class FusedBatchTopKEngine:
             encb_dense[l].index_add_(0, idx, g_aux.sum(dim=0))
         return total
 
+    AUX_MAX_CAP = 4096  # compact dead features per layer that the selection kernel ranks in shared memory
+
+    def set_dead_count_hint(self, max_dead_per_layer: int) -> None:
+        """Sizes the compact dead-feature set of the auxiliary term from an occasional host read of the counters
+        (the largest per-layer dead count).  The capacity carries 25 % head-room; a layer that outgrows it between
+        two hints uses its first ``capacity`` dead features until the next hint.  Counts beyond ``AUX_MAX_CAP`` take
+        the unfused path."""
+        n = int(max_dead_per_layer)
+        self._aux_hint = n
+        cap = -(-max(256, n + n // 4 + 64) // 256) * 256
+        self._aux_cap_wanted = cap if n <= self.AUX_MAX_CAP else 0
+        if self._aux_cap_wanted:
+            self._aux_cap_wanted = min(self._aux_cap_wanted, self.AUX_MAX_CAP)
+
+    def _aux_buffers(self, cap: int):
+        b = getattr(self, "_aux_buf", None)
+        if b is not None and b["cap"] == cap:
+            return b
+        from ..models.clt import pair_index
+
+        L, B, d, dev, t16 = self.L, self.B, self.d, self.dev, self.t16
+        i32, f32 = torch.int32, torch.float32
+        b = {"cap": cap}
+        b["dead_cols"] = torch.zeros(L, cap, dtype=i32, device=dev)
+        b["nd"] = torch.zeros(L, dtype=i32, device=dev)
+        b["nd_all"] = torch.zeros(L, dtype=i32, device=dev)
+        b["extra_idx"] = torch.full((L * self.Fl,), -1, dtype=i32, device=dev)
+        for name in ("A", "G"):
+            b[name] = torch.empty(L, B, cap, dtype=t16, device=dev)
+            b[name + "T"] = torch.empty(L, cap, B, dtype=t16, device=dev)
+        b["W0"] = torch.empty(L, cap, d, dtype=t16, device=dev)
+        b["W0T"] = torch.empty(L, d, cap, dtype=t16, device=dev)
+        b["recon"] = torch.empty(L, B, d, dtype=f32, device=dev)
+        b["g"] = torch.empty(L, B, d, dtype=t16, device=dev)
+        b["gT"] = torch.empty(L, d, B, dtype=t16, device=dev)
+        b["dW0"] = torch.empty(L, cap, d, dtype=f32, device=dev)
+        b["dWenc"] = torch.empty(L, cap, d, dtype=f32, device=dev)
+        b["dbenc"] = torch.empty(L * cap, dtype=f32, device=dev)
+        b["gsum"] = torch.empty(L, d, dtype=f32, device=dev)
+        b["loss"] = torch.zeros(1, dtype=torch.float64, device=dev)
+        rows = [pair_index(l, l, L) if self.tying == 0 else l for l in range(L)]
+        b["bias_row"] = torch.tensor(rows, dtype=i32, device=dev)
+        b["bias_row_long"] = b["bias_row"].long()
+        b["bias_grad"] = torch.zeros(self.model.dec_bias.shape, dtype=f32, device=dev)
+        b["layers"] = self._seg_tables([[(l, l)] for l in range(L)])
+        self._aux_buf = b
+        return b
+
+    @torch.no_grad()
+    def _auxiliary_term_fused(self, X: torch.Tensor, counter: torch.Tensor, window: int, factor: float, cap: int, k_aux_default: int = 512):
+        """The auxiliary term as kernels on the compact dead set (single GPU): compaction of the dead columns, per-token
+        exact selection of the top ``k_aux`` dead pre-activations, and four grouped tensor-core GEMMs (all layers in
+        one launch each) for the auxiliary reconstruction and its three gradients.  No host read, no per-layer loop.
+        Returns the buffers whose ``extra_idx`` / ``dW0`` / ``dWenc`` / ``dbenc`` / ``bias_grad`` feed the optimizer."""
+        e, m = self.ext, self.model
+        b = self._aux_buffers(cap)
+        off, segs = b["layers"]
+        e.aux_compact(counter, int(window), self.L, self.Fv, b["dead_cols"], b["nd"], b["nd_all"], b["extra_idx"])
+        # A = x W_dead^T on the gathered encoder rows, then bias + per-token top k_aux in place (cheaper than gathering
+        # single 16-bit values out of the [B, F] pre-activation rows)
+        e.aux_gather_rows([m.enc_weight.data[l].unsqueeze(1) for l in range(self.L)], b["dead_cols"], b["nd"], b["W0"])
+        e.dense_gemm(X, b["W0"], b["A"], off, segs, 1.0, self.status)
+        e.aux_gather_select(None, m.enc_bias.data, b["dead_cols"], b["nd"], b["nd_all"], int(k_aux_default), b["A"])
+        e.aux_gather_rows([w.data for w in m.dec_weight][: self.L], b["dead_cols"], b["nd"], b["W0"])
+        e.transpose16(b["W0"], b["W0T"])
+        e.dense_gemm(b["A"], b["W0T"], b["recon"], off, segs, 1.0, self.status)            # recon = A W0
+        b["loss"].zero_()
+        e.aux_residual(b["recon"], m.dec_bias.data, b["bias_row"], self.sigma, self.gs, b["g"], b["loss"], b["nd"], self.step_ctl, float(factor))
+        e.dense_gemm(b["g"], b["W0"], b["G"], off, segs, 1.0, self.status)                 # G = g W0^T
+        e.transpose16(b["A"], b["AT"])
+        e.transpose16(b["G"], b["GT"], b["A"])   # straight-through: the gradient stays at the kept positions
+        e.transpose16(b["g"], b["gT"])
+        XT = self._transposed_inputs(X)
+        e.dense_gemm(b["AT"], b["gT"], b["dW0"], off, segs, 1.0, self.status)              # dW0 = A^T g
+        e.dense_gemm(b["GT"], XT, b["dWenc"], off, segs, 1.0, self.status)                 # dW_enc = G^T x
+        e.rowsum16(b["GT"], b["dbenc"])
+        e.rowsum16(b["gT"], b["gsum"])
+        b["bias_grad"].zero_()
+        b["bias_grad"].index_copy_(0, b["bias_row_long"], b["gsum"])
+        self.kernel_launches += 16
+        return b
+
     # -------------------------------------------------------------------- step
     def train_step(self, X: torch.Tensor, Y: torch.Tensor, step: int, lr: float, sparsity_lambda: float = 0.0,
-                   preactivation_coef: float = 0.0, aux_factor: float = 0.0, dead_mask: Optional[torch.Tensor] = None) -> StepOutput:
+                   preactivation_coef: float = 0.0, aux_factor: float = 0.0, dead_mask: Optional[torch.Tensor] = None,
+                   dead_window: Optional[int] = None) -> StepOutput:
         """One optimisation step on inputs/targets ``[L, B, d]`` (bf16 or fp16, already normalised).
 
         Everything that decides whether and how the update is applied stays on the device: the loss kernels raise a
@@ -648,8 +731,10 @@ class FusedBatchTopKEngine:
         status word and loss into the skip decision, keeps the loss scale and (with ``gradient_clip_val``) computes
         the clip coefficient from the norm pre-pass; the optimizer kernels read all of it from ``step_ctl``.
 
-        ``preactivation_coef`` and ``aux_factor`` (with ``dead_mask [L, valid_features]``) switch on the two loss
-        terms that are not sparse; they enter the optimizer kernels as side gradients."""
+        ``preactivation_coef`` and ``aux_factor`` switch on the two loss terms that are not sparse; they enter the
+        optimizer kernels as side gradients.  The dead features of the auxiliary term come from ``dead_window`` (a
+        feature is dead when its counter exceeds it; everything stays on the device) or from an explicit
+        ``dead_mask [L, valid_features]``."""
         e, m, tc = self.ext, self.model, self.tc
         L, B, d = self.L, self.B, self.d
         self.opt_step += 1
@@ -661,7 +746,15 @@ class FusedBatchTopKEngine:
         enc_dense = encb_dense = dec0_dense = None
         extra_bias_grad = None
         use_pre = abs(preactivation_coef) >= 1e-9
-        use_aux = bool(aux_factor) and dead_mask is not None
+        use_aux = bool(aux_factor) and (dead_mask is not None or dead_window is not None)
+        aux_cap = 0
+        if use_aux and self.world == 1:
+            if getattr(self, "_aux_cap_wanted", None) is None:
+                src = dead_mask if dead_mask is not None else (self.dead_counter.view(L, self.Fl)[:, : self.Fv] > int(dead_window))
+                self.set_dead_count_hint(int(src.sum(dim=1).max().item()))  # first use without a hint: one host read
+            aux_cap = self._aux_cap_wanted
+        aux = None
+        enc_x_idx = enc_x_rows = enc_x_bias = dec_x_idx = dec_x_rows = None
         # loss terms that only need the selection come first, so that their sums are there when the loss is settled
         pen = None
         use_pen = sparsity_lambda > 1e-9 and (self.fn != "batchtopk" or (tc.apply_sparsity_penalty_to_batchtopk if tc is not None else True))
@@ -670,7 +763,7 @@ class FusedBatchTopKEngine:
                                self.grad_a, self.pen_coef, self.penalty)
             pen = self.pen_coef
             self.kernel_launches += 1
-        if use_pre or use_aux:
+        if use_pre or (use_aux and aux_cap == 0):
             enc_dense, encb_dense, dec0_dense = self._extra_buffers()
             encb_dense.zero_()
             if use_pre:
@@ -684,9 +777,25 @@ class FusedBatchTopKEngine:
         # all-gather of the gradient seed, so everything below sees every token's seed row
         losses = torch.empty(8, dtype=torch.float32, device=self.dev)
         self._control(0, losses)
-        if use_aux:
+        if use_aux and aux_cap > 0:
+            if dead_mask is not None:
+                counter, window = torch.nn.functional.pad(dead_mask.to(torch.int64), (0, self.Fl - dead_mask.shape[-1])).reshape(-1), 0
+            else:
+                counter, window = self.dead_counter, int(dead_window)
+            aux = self._auxiliary_term_fused(X, counter, window, float(aux_factor), aux_cap)
+            extra_bias_grad = aux["bias_grad"]
+            dec0_dense = None
+            dec_x_idx, dec_x_rows = aux["extra_idx"], aux["dW0"]
+            if use_pre:  # the dense encoder gradient of the pre-activation term takes the compact rows in
+                e.scatter_add_rows(enc_dense, encb_dense, aux["dWenc"], aux["dbenc"], aux["extra_idx"])
+                self.kernel_launches += 1
+            else:
+                enc_dense = encb_dense = None
+                enc_x_idx, enc_x_rows, enc_x_bias = aux["extra_idx"], aux["dWenc"], aux["dbenc"]
+            losses[0::4].add_(aux["loss"].float())  # evaluated on the finished residual, after the loss was settled
+        elif use_aux:
             dec0_dense.zero_()
-            mask = dead_mask
+            mask = dead_mask if dead_mask is not None else (self.dead_counter.view(L, self.Fl)[:, : self.Fv] > int(dead_window))
             if mask.shape[-1] != self.Fl:
                 mask = torch.nn.functional.pad(mask, (0, self.Fl - mask.shape[-1]))
             aux_val = self._auxiliary_term(X, mask, float(aux_factor))
@@ -716,10 +825,10 @@ class FusedBatchTopKEngine:
             # without entries have none), dL/da is written on the way; step_control turns the norm into the coefficient
             rep = 1.0 / self.world  # replicated parameters are counted once over the ranks
             e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, tying_dec, self.feat_off, self.fcsr_tok, self.fcsr_val,
-                                gs_dec, self.grad_a, pen, None, None, None, dec0_dense, h_dec, None, None, None, ctl, True)
+                                gs_dec, self.grad_a, pen, None, None, None, dec0_dense, h_dec, None, dec_x_idx, dec_x_rows, ctl, True)
             e.decoder_bias_adam(m.dec_bias.data, self.decb_m, self.decb_v, self.bias_sel, self.gs_sum, extra_bias_grad, h_dec, ctl, rep)
             e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v, self.feat_off,
-                                self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, h_enc, None, None, None, None, ctl, True)
+                                self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, h_enc, None, enc_x_idx, enc_x_rows, enc_x_bias, ctl, True)
             if skip_grad is not None:
                 e.dense_adam(m.skip_weight.data, self.skip_m, self.skip_v, skip_grad, h_dec, ctl, True, rep)
             if jr:
@@ -729,7 +838,7 @@ class FusedBatchTopKEngine:
             self.kernel_launches += 4
         e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, tying_dec,
                             self.feat_off, self.fcsr_tok, self.fcsr_val, gs_dec, grad_a_for_update, pen, self.norm2_next,
-                            None, None, dec0_dense, h_dec, self.status, None, None, ctl, False)
+                            None, None, dec0_dense, h_dec, self.status, dec_x_idx, dec_x_rows, ctl, False)
         if jr:
             # thresholds: uses the decoder norms of this step (before the swap below)
             self._theta_update(lr, c_g, float(sparsity_lambda) if use_pen else 0.0)
@@ -738,7 +847,7 @@ class FusedBatchTopKEngine:
         if skip_grad is not None:
             e.dense_adam(m.skip_weight.data, self.skip_m, self.skip_v, skip_grad, h_dec, ctl, True, 0.0)
         e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v,
-                            self.feat_off, self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, h_enc, self.status, None, None, None, ctl, False)
+                            self.feat_off, self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, h_enc, self.status, enc_x_idx, enc_x_rows, enc_x_bias, ctl, False)
         # dead-feature counters and the bias sums of the next step's loss epilogue
         e.step_finish(self.dead_counter, self.fired, m.dec_bias.data, self.bias_sel, self.bias_sum)
         self.kernel_launches += 6  # gs_colsum, decoder rows, decoder biases, encoder rows (+ bias), finish

@@ -320,7 +320,7 @@ class CLTTrainer:
         with self.profiler.timer("optimizer_step"):
             out = eng.train_step(
                 X, Y, step, lr, sparsity_lambda=lam, preactivation_coef=pre_coef,
-                aux_factor=(tc.aux_loss_factor if need_aux else 0.0), dead_mask=(self.dead_neurons_mask if need_aux else None),
+                aux_factor=(tc.aux_loss_factor if need_aux else 0.0), dead_window=(tc.dead_feature_window if need_aux else None),
             )
         return out.as_dict()
 
@@ -329,10 +329,13 @@ class CLTTrainer:
         slowly).  The answer is agreed over the process group (all-reduce MAX at the same steps on every rank):
         the auxiliary term runs collectives, so every rank has to take the same branch."""
         if not hasattr(self, "_dead_seen") or step % 100 == 0:
-            flag = self.dead_neurons_mask.any().to(torch.int32).reshape(1)
+            count = self.dead_neurons_mask.sum(dim=1).max().to(torch.int32).reshape(1)  # largest per-layer dead count
             if self.world_size > 1:
-                pops.all_reduce(flag, op=pops.MAX, group=self.process_group)
-            self._dead_seen = bool(flag.item())
+                pops.all_reduce(count, op=pops.MAX, group=self.process_group)
+            n = int(count.item())
+            self._dead_seen = n > 0
+            if self.engine is not None:
+                self.engine.set_dead_count_hint(n)  # sizes the compact dead set of the fused auxiliary term
         return self._dead_seen
 
     def _train_step_autograd(self, inputs, targets, step: int, lr: float) -> Dict[str, torch.Tensor]:

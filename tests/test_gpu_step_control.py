@@ -398,3 +398,122 @@ def test_long_csr_segments_are_sorted_by_the_cooperative_path():
     b, en = int(tok_off[3]), int(tok_off[4])
     seg = tcsr_col[b:en].cpu()
     assert en - b >= 600 and bool((seg[1:] > seg[:-1]).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_aux_compaction_and_per_token_selection(dtype):
+    """Dead-column compaction and the exact per-token top-k of the dead pre-activations (ties by lowest index)."""
+    from crosslayer_coding_b200.ops import ext as ext_mod
+
+    ext = ext_mod.load()
+    dev = _dev()
+    torch.manual_seed(5)
+    L, B, F, Fv, cap, k_aux = 3, 70, 1024, 1000, 512, 24
+    counter = torch.zeros(L, F, dtype=torch.int64, device=dev)
+    counter[0, ::3] = 11          # 342 dead (some beyond the valid range are ignored)
+    counter[1, 5:17] = 99         # 12 dead: fewer than k_aux, all kept
+    counter[2, :] = 50            # every valid feature dead: more than the capacity, truncated to the first `cap`
+    dead_cols = torch.zeros(L, cap, dtype=torch.int32, device=dev)
+    nd = torch.zeros(L, dtype=torch.int32, device=dev)
+    nd_all = torch.zeros(L, dtype=torch.int32, device=dev)
+    extra_idx = torch.zeros(L * F, dtype=torch.int32, device=dev)
+    ext.aux_compact(counter.reshape(-1), 10, L, Fv, dead_cols, nd, nd_all, extra_idx)
+    dead = (counter > 10) & (torch.arange(F, device=dev) < Fv)
+    assert nd_all.tolist() == dead.sum(dim=1).tolist()
+    assert nd.tolist() == [min(cap, n) for n in nd_all.tolist()]
+    xi = extra_idx.view(L, F)
+    for l in range(L):
+        cols = dead[l].nonzero().flatten()[:cap]
+        assert torch.equal(dead_cols[l, : len(cols)].long(), cols)
+        assert torch.equal(xi[l, cols].long(), l * cap + torch.arange(len(cols), device=dev))
+        rest = torch.ones(F, dtype=torch.bool, device=dev)
+        rest[cols] = False
+        assert bool((xi[l, rest] == -1).all())
+    # values on a coarse grid, so that many of them tie at the cut
+    pre = (torch.randint(-6, 7, (L, B, F), device=dev).float() * 0.25).to(dtype)
+    A = torch.full((L, B, cap), 7.0, dtype=dtype, device=dev)
+    ext.aux_gather_select(pre, None, dead_cols, nd, nd_all, k_aux, A)
+    # second source: A holds the bias-free products, the bias of each dead column is added in the kernel
+    bias = (torch.randint(-3, 4, (L, F), device=dev).float() * 0.25)
+    A2 = torch.zeros(L, B, cap, dtype=dtype, device=dev)
+    for l in range(L):
+        cols = dead_cols[l, : int(nd[l])].long()
+        A2[l, :, : len(cols)] = (pre[l][:, cols].float() - bias[l, cols]).to(dtype)
+    ext.aux_gather_select(None, bias, dead_cols, nd, nd_all, k_aux, A2)
+    assert torch.equal(A2, A)
+    for l in range(L):
+        n = int(nd[l])
+        vals = pre[l][:, dead_cols[l, :n].long()].float()
+        k = min(k_aux, int(nd_all[l]))
+        want = torch.zeros(B, cap, device=dev)
+        if n <= k:
+            want[:, :n] = vals
+        else:
+            # stable descending sort = ties resolved towards the lowest index
+            order = torch.sort(vals, dim=1, descending=True, stable=True).indices[:, :k]
+            want[:, :n] = torch.zeros_like(vals).scatter_(1, order, vals.gather(1, order))
+        assert torch.equal(A[l].float(), want), l
+    # masked transpose: the gradient survives where the selection kept a value
+    Bp = 72
+    Gp = torch.randn(L, Bp, cap, device=dev).to(dtype)
+    Ap = torch.zeros(L, Bp, cap, dtype=dtype, device=dev)
+    Ap[:, :B] = A
+    GT = torch.empty(L, cap, Bp, dtype=dtype, device=dev)
+    ext.transpose16(Gp, GT, Ap)
+    assert torch.equal(GT, (Gp * (Ap != 0)).transpose(1, 2).contiguous())
+    ext.transpose16(Gp, GT)
+    assert torch.equal(GT, Gp.transpose(1, 2).contiguous())
+
+
+def test_fused_auxiliary_term_matches_loss_manager_beyond_k_aux():
+    """More dead features than k_aux = 512: the kernel path (selection + grouped GEMMs + compact extra rows) against
+    the PyTorch loss and one AdamW step; then the same step through the unfused per-layer path."""
+    import copy
+
+    from crosslayer_coding_b200.training.losses import LossManager
+
+    cfg, model, tc, eng, X, Y = _make(L=2, B=128, d=64, F=2048, k=16, seed=21)
+    tc.aux_loss_factor = 0.25
+    ref = _fp32_copy(model)
+    twin = copy.deepcopy(model)
+    snap = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+    L, F = 2, 2048
+    dead = torch.zeros(L, F, dtype=torch.bool, device=X.device)
+    dead[0, 100:1500] = True   # 1400 dead, 512 kept per token
+    dead[1, ::9] = True        # 228 dead, all kept
+    out = eng.train_step(X, Y, step=0, lr=1e-3, aux_factor=0.25, dead_mask=dead)
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert eng._aux_buf["cap"] >= 1400
+    x = {l: X[l].float() for l in range(L)}
+    y = {l: Y[l].float() for l in range(L)}
+    acts_k = eng.activations_dense()
+    pre = {l: torch.nn.functional.linear(x[l], ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    acts = {l: (pre[l] + (eng.preact[l].float() - pre[l]).detach()) * (acts_k[l] != 0) for l in range(L)}
+    preds = {t: ref.decode({s: acts[s] for s in range(t + 1)}, t) for t in range(L)}
+    lm = LossManager(tc)
+    recon = lm.compute_reconstruction_loss(preds, y)
+    pre_k = {l: pre[l] + (eng.preact[l].float() - pre[l]).detach() for l in range(L)}  # the values the kernels ranked
+    aux = lm.compute_auxiliary_loss(ref, x, {l: y[l] - preds[l] for l in range(L)}, dead, preacts=pre_k)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3)
+    (recon + aux).backward()
+    opt.step()
+    assert abs(out.auxiliary.item() - aux.item()) < 3e-2 * max(1e-3, aux.item()), (out.auxiliary.item(), aux.item())
+    assert abs(out.total.item() - (recon + aux).item()) < 1e-2 * (recon + aux).item()
+    ref_params = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        old = snap[name]
+        upd, ref_upd = p.detach().float() - old, ref_params[name].detach() - old
+        bad = ((upd - ref_upd).abs() > 0.008 * old.abs() + 3e-4).float().mean().item()
+        assert bad < 2e-2, (name, bad)
+    # the unfused path (taken under tensor parallelism and for very large dead sets) gives the same step
+    from crosslayer_coding_b200.training.fused_engine import FusedBatchTopKEngine
+
+    eng2 = FusedBatchTopKEngine(twin, tc, X.shape[1])
+    eng2._aux_cap_wanted = 0
+    out2 = eng2.train_step(X, Y, step=0, lr=1e-3, aux_factor=0.25, dead_mask=dead)
+    eng2.check_status()
+    assert abs(out2.auxiliary.item() - out.auxiliary.item()) < 2e-2 * max(1e-3, out.auxiliary.item())
+    for (name, p), (_, q) in zip(model.named_parameters(), twin.named_parameters()):
+        diff = ((p.detach().float() - q.detach().float()).abs() > 0.008 * snap[name].abs() + 3e-4).float().mean().item()
+        assert diff < 2e-2, (name, diff)
