@@ -140,6 +140,19 @@ int clt_peer_barrier(const CltPeerTable* flags, int slot, unsigned int seq, int*
 int clt_sparsity_penalty(const int* feat_off, const float* fcsr_val, const float* norm2, int ncols, float lambda, float c,
                          float* grad_a, float* pen_coef, double* penalty_out, cudaStream_t st);
 int clt_step_control(const CltStepControlArgs* a, const CltExchangeArgs* exa, cudaStream_t st);
+struct CltTopkTpArgs {
+  const int* cand_col; const float* cand_val;
+  unsigned long long* cand_key;
+  const float* mean; const float* rstd; int stat_pitch;
+  int col_pitch, feat_offset; long long full_F;
+  int B, k, world, rank, rows_per_rank;
+  void* stage[8];
+  void* cut[8];
+  long long* ctl;
+  int* ent_tok; int* ent_col; float* ent_val; long long ent_cap;
+  int* status;
+};
+int clt_token_topk_tp(const CltTopkTpArgs* a, int phase, cudaStream_t st);
 int clt_aux_compact(const long long* dead_counter, long long window, int L, int F_pitch, int F_valid, int nd_cap, int* dead_cols, int* nd,
                     int* nd_all, int* extra_idx, cudaStream_t st);
 int clt_scatter_add_rows(float* dst, float* dst_bias, const float* src, const float* src_bias, const int* extra_idx, long long n_dst_rows, int d,
@@ -319,7 +332,7 @@ void threshold_select(const Tensor& x, const Tensor& theta, int64_t f_valid, int
 
 // Per-token top-k of the batch z-scores: exactly k entries per token at [token * k, token * k + k) of the entry list.
 void token_topk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, int64_t col_pitch, int64_t k, Tensor& ctl, Tensor& ent_tok,
-                       Tensor& ent_col, Tensor& ent_val, Tensor& status) {
+                       Tensor& ent_col, Tensor& ent_val, Tensor& status, int64_t f_valid) {
   const bool half = is_half(x, "x");
   need(x, t16_of(half), "x"); need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd"); need(ctl, at::kLong, "ctl");
   need(status, at::kInt, "status"); need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
@@ -331,11 +344,39 @@ void token_topk_select(const Tensor& x, const Tensor& mean, const Tensor& rstd, 
   a.L = x.size(0); a.B = x.size(1); a.F = x.size(2); a.stat_pitch = int(mean.size(1));
   a.ld = x.size(2); a.layer_stride = 1LL * x.size(1) * x.size(2);
   a.col_pitch = int(col_pitch); a.k_total = k;
+  a.feat_offset = int(f_valid);  // valid columns per layer (0: all of them)
   a.ctl = reinterpret_cast<long long*>(ctl.data_ptr<int64_t>());
   a.ent_tok = ent_tok.data_ptr<int>(); a.ent_col = ent_col.data_ptr<int>(); a.ent_val = ent_val.data_ptr<float>(); a.ent_cap = ent_tok.numel();
   a.status = status.data_ptr<int>();
   c10::cuda::CUDAGuard guard(x.device());
   check(CLT_PICK(half, clt_token_topk_select)(&a, cur_stream()), "token_topk_select");
+}
+
+// One phase of the TokenTopK selection across feature shards (0: push the local candidates' keys to the token owners,
+// 1: owners find the cut of their tokens and publish it, 2: keep the candidates at or above the cut).  The caller separates
+// the phases with peer barriers.  cand_* [B * k]: the local top k of every token (token_topk_select into scratch lists).
+void token_topk_tp(int64_t phase, const Tensor& cand_col, const Tensor& cand_val, Tensor& cand_key, const Tensor& mean, const Tensor& rstd,
+                   int64_t col_pitch, int64_t feat_offset, int64_t full_F, int64_t B, int64_t k, int64_t rank, int64_t rows_per_rank,
+                   const std::vector<int64_t>& stage_ptrs, const std::vector<int64_t>& cut_ptrs, Tensor& ctl, Tensor& ent_tok, Tensor& ent_col,
+                   Tensor& ent_val, Tensor& status) {
+  need(cand_col, at::kInt, "cand_col"); need(cand_val, at::kFloat, "cand_val"); need(cand_key, at::kLong, "cand_key");
+  need(mean, at::kFloat, "mean"); need(rstd, at::kFloat, "rstd"); need(ctl, at::kLong, "ctl"); need(status, at::kInt, "status");
+  need(ent_tok, at::kInt, "ent_tok"); need(ent_col, at::kInt, "ent_col"); need(ent_val, at::kFloat, "ent_val");
+  TORCH_CHECK(cand_col.numel() >= B * k && cand_val.numel() >= B * k && cand_key.numel() >= B * k, "candidate lists hold B * k elements");
+  TORCH_CHECK(stage_ptrs.size() == cut_ptrs.size() && !stage_ptrs.empty() && stage_ptrs.size() <= 8, "one staging and one cut pointer per rank");
+  CltTopkTpArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.cand_col = cand_col.data_ptr<int>(); a.cand_val = cand_val.data_ptr<float>();
+  a.cand_key = reinterpret_cast<unsigned long long*>(cand_key.data_ptr<int64_t>());
+  a.mean = mean.data_ptr<float>(); a.rstd = rstd.data_ptr<float>(); a.stat_pitch = int(mean.size(1));
+  a.col_pitch = int(col_pitch); a.feat_offset = int(feat_offset); a.full_F = full_F;
+  a.B = int(B); a.k = int(k); a.world = int(stage_ptrs.size()); a.rank = int(rank); a.rows_per_rank = int(rows_per_rank);
+  for (size_t i = 0; i < stage_ptrs.size(); ++i) { a.stage[i] = reinterpret_cast<void*>(stage_ptrs[i]); a.cut[i] = reinterpret_cast<void*>(cut_ptrs[i]); }
+  a.ctl = reinterpret_cast<long long*>(ctl.data_ptr<int64_t>());
+  a.ent_tok = ent_tok.data_ptr<int>(); a.ent_col = ent_col.data_ptr<int>(); a.ent_val = ent_val.data_ptr<float>(); a.ent_cap = ent_tok.numel();
+  a.status = status.data_ptr<int>();
+  c10::cuda::CUDAGuard guard(cand_col.device());
+  check(clt_token_topk_tp(&a, int(phase), cur_stream()), "token_topk_tp");
 }
 
 // JumpReLU threshold gradient sums: S1[l, f] += sum_b window * x * (gs . W_dec rows), S2[l, f] += sum_b window * x.
@@ -892,7 +933,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("colstats_from_tiles", &colstats_from_tiles);
   m.def("batchtopk_select", &batchtopk_select);
   m.def("threshold_select", &threshold_select);
-  m.def("token_topk_select", &token_topk_select);
+  m.def("token_topk_select", &token_topk_select, py::arg("x"), py::arg("mean"), py::arg("rstd"), py::arg("col_pitch"), py::arg("k"), py::arg("ctl"),
+        py::arg("ent_tok"), py::arg("ent_col"), py::arg("ent_val"), py::arg("status"), py::arg("f_valid") = 0);
+  m.def("token_topk_tp", &token_topk_tp);
   m.def("theta_grad_gemm", &theta_grad_gemm, py::arg("gs"), py::arg("dec_w"), py::arg("preact"), py::arg("theta"), py::arg("bandwidth"),
         py::arg("S1"), py::arg("S2"), py::arg("status"), py::arg("tying") = 0, py::arg("gs_cum") = none);
   m.def("build_csr", &build_csr);

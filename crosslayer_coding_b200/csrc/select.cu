@@ -627,7 +627,7 @@ __device__ __forceinline__ void token_rows_scan(const t16* __restrict__ x, const
 }
 
 __global__ void __launch_bounds__(256) token_topk_kernel(const t16* __restrict__ x, const float* __restrict__ mean,
-                                                           const float* __restrict__ rstd, ScanGeom g, int col_pitch, int k,
+                                                           const float* __restrict__ rstd, ScanGeom g, int col_pitch, int f_valid, int k,
                                                            long long* __restrict__ ctl, Lists o, int* __restrict__ status) {
   extern __shared__ uint8_t tk_smem[];
   TokenTopkShared* sh = reinterpret_cast<TokenTopkShared*>(tk_smem);
@@ -644,8 +644,8 @@ __global__ void __launch_bounds__(256) token_topk_kernel(const t16* __restrict__
     const uint32_t nb = 1u << widths[round];
     for (int i = tid; i < kTokPerCta * kTokBins; i += blockDim.x) (&sh->hist[0][0])[i] = 0;
     __syncthreads();
-    token_rows_scan(x, mean, rstd, g, tok0, ntok, [&](int t, int, int, float, uint32_t key) {
-      if ((key & sh->mask[t]) == sh->prefix[t]) atomicAdd(&sh->hist[t][(key >> shift) & (nb - 1u)], 1u);
+    token_rows_scan(x, mean, rstd, g, tok0, ntok, [&](int t, int, int c, float, uint32_t key) {
+      if (c < f_valid && (key & sh->mask[t]) == sh->prefix[t]) atomicAdd(&sh->hist[t][(key >> shift) & (nb - 1u)], 1u);
     });
     __syncthreads();
     if (tid < ntok) {
@@ -666,6 +666,7 @@ __global__ void __launch_bounds__(256) token_topk_kernel(const t16* __restrict__
   // prefix[t] is now the cut key T of token t, need[t] the number of keys equal to T that are kept
   token_rows_scan(x, mean, rstd, g, tok0, ntok, [&](int t, int l, int c, float xv, uint32_t key) {
     const uint32_t T = sh->prefix[t];
+    if (c >= f_valid) return;  // padding columns of a shard take no part
     if (key > T) {
       const int slot = atomicAdd(&sh->emitted[t], 1);
       if (slot < k) {
@@ -1448,11 +1449,13 @@ extern "C" int CLT_FN(clt_threshold_select)(const CltSelectArgs* a, cudaStream_t
 }
 
 // Per-token top-k of the batch z-scores (TokenTopK).  Uses x, mean, rstd, L, B, F, stat_pitch, ld, layer_stride,
-// col_pitch, ctl, ent_* (capacity >= B * k), status of the argument block; k_total carries the per-token k.
+// col_pitch, ctl, ent_* (capacity >= B * k), status of the argument block; k_total carries the per-token k and feat_offset
+// (when positive) the number of valid columns per layer (the rest of F is shard padding).
 extern "C" int CLT_FN(clt_token_topk_select)(const CltSelectArgs* a, cudaStream_t st) {
   if (a->ld % 8 != 0 || a->layer_stride % 8 != 0 || a->F % 8 != 0 || a->stat_pitch % 4 != 0 || a->F > a->ld) return -1;
   const long long k = a->k_total;
-  if (k <= 0 || k > 1LL * a->L * a->F || 1LL * a->B * k > a->ent_cap) return -1;
+  const int f_valid = a->feat_offset > 0 && a->feat_offset <= a->F ? a->feat_offset : a->F;  // feat_offset carries the valid column count here
+  if (k <= 0 || k > 1LL * a->L * f_valid || 1LL * a->B * k > a->ent_cap) return -1;
   const ScanGeom g = scan_geom(a);
   static bool attr_set = false;
   if (!attr_set) {
@@ -1461,11 +1464,123 @@ extern "C" int CLT_FN(clt_token_topk_select)(const CltSelectArgs* a, cudaStream_
   }
   const int grid = (a->B + kTokPerCta - 1) / kTokPerCta;
   token_topk_kernel<<<grid, 256, sizeof(TokenTopkShared), st>>>(static_cast<const t16*>(a->x), a->mean, a->rstd, g, a->col_pitch,
-                                                                 int(k), a->ctl, lists_of(a), a->status);
+                                                                 f_valid, int(k), a->ctl, lists_of(a), a->status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 #if !CLT_T16_IS_HALF
+// ------------------------------------------------------------------ TokenTopK across feature shards
+// Every rank holds a slice of the columns; a token keeps its k largest z-scores over all ranks' columns (reference:
+// clt/models/activations.py:360-491, where the full pre-activations are gathered and the mask is broadcast).  Here each
+// rank first takes the exact top k of its own columns (token_topk_kernel: a superset of what survives), then
+//   1. token_topk_push:   composite keys (z key << 32 | inverted global flat index) of the local candidates go to the
+//                         owner of the token (tokens are dealt to the ranks in blocks of rows_per_rank) by peer stores;
+//   2. token_topk_cut:    the owner ranks the W * k keys of each of its tokens, takes the k-th largest as the cut and stores
+//                         it into every rank's cut array;
+//   3. token_topk_filter: every rank keeps its candidates at or above the cut and appends them to its entry list.
+// The composite keys are distinct and their order does not depend on the number of ranks (larger z first, lower flat index
+// first among equal z), so the selection equals the single-GPU one entry for entry.  Phase barriers (peer_barrier) separate
+// the three kernels; nothing here waits.
+struct CltTopkTpArgs {
+  const int* cand_col; const float* cand_val;   // [B * k] local candidates (token t at t * k ...), from token_topk_select
+  unsigned long long* cand_key;                 // [B * k] composite keys (written by push, read by filter)
+  const float* mean; const float* rstd; int stat_pitch;
+  int col_pitch, feat_offset; long long full_F;
+  int B, k, world, rank, rows_per_rank;
+  void* stage[8];                               // every rank's key staging [world][rows_per_rank][k] u64
+  void* cut[8];                                 // every rank's cut array [B] u64
+  long long* ctl;
+  int* ent_tok; int* ent_col; float* ent_val; long long ent_cap;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) token_topk_push_kernel(CltTopkTpArgs a) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) a.ctl[CTL_NUM_ENTRIES] = 0;  // refilled by the filter pass
+  const long long n = 1LL * a.B * a.k;
+  for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < n; i += 1LL * gridDim.x * blockDim.x) {
+    const int t = int(i / a.k), j = int(i - 1LL * t * a.k);
+    const int col = a.cand_col[i];
+    const int l = col / a.col_pitch, c = col - l * a.col_pitch;
+    const float z = (a.cand_val[i] - a.mean[1LL * l * a.stat_pitch + c]) * a.rstd[1LL * l * a.stat_pitch + c];
+    const unsigned long long flat = (unsigned long long)l * (unsigned long long)a.full_F + (unsigned long long)(a.feat_offset + c);
+    const unsigned long long key = ((unsigned long long)float_to_key(z) << 32) | (0xFFFFFFFFULL - flat);
+    a.cand_key[i] = key;
+    const int owner = t / a.rows_per_rank, lt = t - owner * a.rows_per_rank;
+    static_cast<unsigned long long*>(a.stage[owner])[(1LL * a.rank * a.rows_per_rank + lt) * a.k + j] = key;
+  }
+}
+
+// One CTA per owned token; dynamic shared memory world * k keys.
+__global__ void __launch_bounds__(256) token_topk_cut_kernel(CltTopkTpArgs a) {
+  extern __shared__ unsigned long long tk_keys[];
+  const int lt = blockIdx.x;
+  const int t = a.rank * a.rows_per_rank + lt;
+  if (t >= a.B) return;
+  const int n = a.world * a.k;
+  const unsigned long long* mine = static_cast<const unsigned long long*>(a.stage[a.rank]);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int w = i / a.k, j = i - w * a.k;
+    tk_keys[i] = mine[(1LL * w * a.rows_per_rank + lt) * a.k + j];
+  }
+  __syncthreads();
+  // the key that exactly k - 1 keys exceed (the keys are distinct)
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const unsigned long long ki = tk_keys[i];
+    int above = 0;
+    for (int j = 0; j < n; ++j) above += tk_keys[j] > ki;
+    if (above == a.k - 1) {
+      for (int w = 0; w < a.world; ++w) static_cast<unsigned long long*>(a.cut[w])[t] = ki;
+    }
+  }
+}
+
+// One warp per token: candidates at or above the cut are appended to the entry list.
+__global__ void __launch_bounds__(256) token_topk_filter_kernel(CltTopkTpArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (t >= a.B) return;
+  const unsigned long long cut = static_cast<const unsigned long long*>(a.cut[a.rank])[t];
+  unsigned long long* n_ent = reinterpret_cast<unsigned long long*>(a.ctl + CTL_NUM_ENTRIES);
+  for (int j0 = 0; j0 < a.k; j0 += 32) {
+    const int j = j0 + lane;
+    const long long i = 1LL * t * a.k + j;
+    const bool keep = j < a.k && a.cand_key[i] >= cut;
+    const unsigned ball = __ballot_sync(0xFFFFFFFFu, keep);
+    if (ball == 0u) continue;
+    unsigned long long base = 0;
+    if (lane == 0) base = atomicAdd(n_ent, (unsigned long long)__popc(ball));
+    base = __shfl_sync(0xFFFFFFFFu, base, 0);
+    if (keep) {
+      const long long q = (long long)base + __popc(ball & ((1u << lane) - 1u));
+      if (q < a.ent_cap) { a.ent_tok[q] = t; a.ent_col[q] = a.cand_col[i]; a.ent_val[q] = a.cand_val[i]; }
+      else atomicCAS(a.status, STATUS_OK, STATUS_CAPACITY);
+    }
+  }
+}
+
+// phase: 0 push, 1 cut, 2 filter (the caller puts a phase barrier between them)
+extern "C" int clt_token_topk_tp(const CltTopkTpArgs* a, int phase, cudaStream_t st) {
+  if (a->world < 1 || a->world > 8 || a->k <= 0 || a->B <= 0 || a->rows_per_rank <= 0) return -1;
+  if (1LL * a->world * a->rows_per_rank < a->B) return -1;
+  const size_t smem = sizeof(unsigned long long) * size_t(a->world) * size_t(a->k);
+  if (smem > 200 * 1024) return -2;
+  if (phase == 0) {
+    const long long n = 1LL * a->B * a->k;
+    const int grid = int((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    token_topk_push_kernel<<<grid, 256, 0, st>>>(*a);
+  } else if (phase == 1) {
+    static size_t attr_smem = 0;
+    if (smem > 48 * 1024 && smem > attr_smem) {
+      if (cudaFuncSetAttribute(token_topk_cut_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
+      attr_smem = smem;
+    }
+    token_topk_cut_kernel<<<a->rows_per_rank, 256, smem, st>>>(*a);
+  } else {
+    token_topk_filter_kernel<<<(a->B + 7) / 8, 256, 0, st>>>(*a);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 struct CltCsrArgs {
   const int* ent_tok; const int* ent_col; const float* ent_val; long long ent_cap;
   const long long* ctl;

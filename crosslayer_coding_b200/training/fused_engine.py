@@ -72,7 +72,13 @@ def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingCon
     if clt_config.activation_fn in ("batchtopk", "topk") and clt_config.topk_mode != "global":
         return "topk_mode='per_layer'"
     if clt_config.activation_fn == "topk" and model is not None and model.world_size > 1:
-        return "per-token topk under tensor parallelism"
+        from ..models.activations import resolve_token_k
+
+        k_tok = resolve_token_k(float(clt_config.topk_k), clt_config.num_layers * clt_config.num_features)
+        if 2 * k_tok > clt_config.num_layers * clt_config.d_model or model.world_size * k_tok * 8 > 200 * 1024:
+            return "per-token topk under tensor parallelism with k beyond the key staging area"
+        if k_tok > clt_config.num_layers * model.valid_features:
+            return "per-token topk with k above the columns of one shard"
     if clt_config.activation_fn == "jumprelu" and (clt_config.enable_feature_offset or clt_config.enable_feature_scale) \
             and clt_config.decoder_tying != "none":
         return "jumprelu with feature offset/scale (the threshold-gradient GEMM has no per-target affine)"
@@ -403,11 +409,16 @@ class FusedBatchTopKEngine:
             e.colstats_from_tiles(self.tile_stats, self.mean, self.rstd, self.B)
         else:
             e.colstats(self.preact, self.mean, self.rstd)
-        if self.fn == "topk":
+        if self.fn == "topk" and self.world == 1:
             e.token_topk_select(self.preact, self.mean, self.rstd, self.Fl, self.k_token, self.ctl, self.ent_tok, self.ent_col,
-                                self.ent_val, self.status)
+                                self.ent_val, self.status, self.Fv)
             self._build_csr()
             self.kernel_launches += 3 + 5  # gemm, colstats, per-token selection, csr (5)
+            return
+        if self.fn == "topk":
+            self._token_topk_sharded()
+            self._build_csr()
+            self.kernel_launches += 3 + 5 + 5
             return
         world, rank, dptr, fptr, slot, seq = self._exchange_args()
         if self.world > 1 and self.symm is None:
@@ -422,6 +433,36 @@ class FusedBatchTopKEngine:
         # gemm, colstats, select (collect, find_bin, classify, fallback x3, refine, finalize | zhist, find_bin, compact,
         # refine, finalize), csr (5)
         self.kernel_launches += 2 + (8 if self.key_lo != 0 else 5) + 5
+
+    def _token_topk_sharded(self) -> None:
+        """TokenTopK across feature shards (reference: clt/models/activations.py:360-491, which gathers the full
+        pre-activations and broadcasts the mask).  Every rank takes the exact top k of its own columns, the owners of
+        the tokens rank the W * k composite keys that arrive by peer stores and publish the cut, every rank keeps what
+        is at or above it.  The keys order by (z-score, lower flat index first), so the result equals the single-GPU
+        selection entry for entry.  Staging reuses the decode's partial-sum area (idle during the selection); the cut
+        array sits in the histogram section, which this activation does not use otherwise."""
+        e, sy = self.ext, self.symm
+        if sy is None:
+            raise RuntimeError("tensor-parallel fused engine needs a symmetric exchange area (parallel.symm)")
+        B, k = self.B, self.k_token
+        if getattr(self, "_tk_col", None) is None:
+            from ..parallel import symm as symm_mod
+
+            assert B * 8 <= 14 * self.world * symm_mod.HIST_SLOT * 4, "cut array does not fit the histogram section"
+            assert 2 * k <= self.L * self.d, "key staging does not fit the partial-sum area"
+            self._tk_tok = torch.empty(B * k, dtype=torch.int32, device=self.dev)
+            self._tk_col = torch.empty(B * k, dtype=torch.int32, device=self.dev)
+            self._tk_val = torch.empty(B * k, dtype=torch.float32, device=self.dev)
+            self._tk_key = torch.empty(B * k, dtype=torch.int64, device=self.dev)
+        # 1. exact local top k of every token into scratch lists
+        e.token_topk_select(self.preact, self.mean, self.rstd, self.Fl, k, self.ctl, self._tk_tok, self._tk_col, self._tk_val, self.status, self.Fv)
+        args = (self._tk_col, self._tk_val, self._tk_key, self.mean, self.rstd, self.Fl, self.model.feature_start, self.F, B, k, self.rank,
+                sy.rows_per_rank, sy.stage_ptrs, sy.hist_data_ptrs, self.ctl, self.ent_tok, self.ent_col, self.ent_val, self.status)
+        e.token_topk_tp(0, *args)   # 2. keys to the token owners
+        sy.barrier(e, self.status)
+        e.token_topk_tp(1, *args)   # 3. owners publish the cut of their tokens
+        sy.barrier(e, self.status)
+        e.token_topk_tp(2, *args)   # 4. keep what is at or above the cut
 
     def _ensure_bias_sum(self) -> None:
         """Per-target sums of the decoder biases; kept current by the last kernel of every training step."""

@@ -88,3 +88,22 @@ def test_tp_variants_match_single_gpu(tmp_path, extra, activation, lam):
         assert w.shape == w_ref.shape, key
         bad = ((w - w_ref).abs() > 0.01 * w_ref.abs() + 2e-3).float().mean().item()
         assert bad < 5e-3, (key, bad)
+
+
+@pytest.mark.parametrize("world,features", [(2, 512), (2, 520), (4, 512)])
+def test_tp_token_topk_equals_single_gpu_selection(tmp_path, world, features):
+    """Per-token top-k across feature shards: local top k, composite keys to the token owners, cut published to every
+    rank.  The selection equals the single-GPU one entry for entry (k per token, ties by the lowest flat index)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ref = _run(1, str(tmp_path / "w1.pt"), features, 29671, 0.0, "topk")
+    got = _run(world, str(tmp_path / f"w{world}.pt"), features, 29673 + world, 0.0, "topk")
+    assert len(ref["selection"]) == 128 * 8
+    assert got["selection"] == ref["selection"]
+    assert got["entries"] == ref["entries"], (got["entries"], ref["entries"])
+    for a, b in zip(got["losses"], ref["losses"]):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(b)), (got["losses"], ref["losses"])
+    for key, w_ref in ref["state"].items():
+        w = got["state"][key]
+        bad = ((w - w_ref).abs() > 0.01 * w_ref.abs() + 4e-4).float().mean().item()
+        assert bad < 5e-3, (key, bad)

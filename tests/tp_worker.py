@@ -45,7 +45,7 @@ def main():
         group = dist.group.WORLD
     L, d, F, B, k = 3, 64, args.features, 128, 8
     t16 = torch.float16 if args.dtype == "float16" else torch.bfloat16
-    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k, clt_dtype=args.dtype,
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k, topk_k=k, clt_dtype=args.dtype,
                     jumprelu_threshold=0.25, decoder_tying=args.tying)
     full_state = build_full_state(cfg)
     if args.tying != "none":  # tied decoders start at zero; give them values so that the first steps have a signal
@@ -67,6 +67,17 @@ def main():
     X = torch.randn(L, B, d, generator=g).to(t16).to(dev)
     A = torch.randn(d, d, generator=g) / d ** 0.5
     Y = (X.float().cpu() @ A).to(t16).to(dev)
+    # the selection on the initial weights, as (token, global flat feature index) pairs of all ranks
+    eng.encode_select(X)
+    n0 = int(eng.ctl[3])
+    col = eng.ent_col[:n0].long()
+    flat = (col // eng.Fl) * F + model.feature_start + col % eng.Fl
+    pairs = torch.stack([eng.ent_tok[:n0].long(), flat], dim=1).cpu()
+    if world > 1:
+        gathered_pairs = [None] * world
+        dist.all_gather_object(gathered_pairs, pairs)
+        pairs = torch.cat(gathered_pairs)
+    selection = sorted(map(tuple, pairs.tolist()))
     losses, entries, norms = [], [], []
     for step in range(args.steps):
         out = eng.train_step(X, Y, step, 1e-3, sparsity_lambda=args.lam)
@@ -122,7 +133,7 @@ def main():
     else:
         merged = sd
     if rank == 0:
-        torch.save({"losses": losses, "entries": entries, "grad_norms": norms, "skipped": float(out.skipped_steps), "state": merged, "world": world, "staging_ok": bool(flag.item() == 1.0),
+        torch.save({"selection": selection, "losses": losses, "entries": entries, "grad_norms": norms, "skipped": float(out.skipped_steps), "state": merged, "world": world, "staging_ok": bool(flag.item() == 1.0),
                     "h2d_bytes_per_rank": store.h2d_bytes_per_rank, "h2d_bytes": store.h2d_bytes_per_batch}, args.out)
     if world > 1:
         dist.barrier()
