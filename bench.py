@@ -89,6 +89,10 @@ def parse_args():
     ap.add_argument("--parity-steps", type=int, default=0,
                     help="after the timed loops, train this many further steps over the pool and report the normalised MSE "
                          "on a held-out synthetic batch (key 'parity'); use the same value and --pool for both arms")
+    ap.add_argument("--parity-fresh", action="store_true",
+                    help="--parity-steps draws a fresh synthetic batch every step (seeded by the step, the same stream in both arms) "
+                         "instead of cycling the pool: a convergence run")
+    ap.add_argument("--parity-log-every", type=int, default=0, help="record the held-out normalised MSE every this many parity steps (key 'parity.curve')")
     ap.add_argument("--decoder-tying", choices=["none", "per_source", "per_target"], default="none")
     ap.add_argument("--precision", choices=["bf16", "fp16"], default="bf16", help="fp16: fp16 weights / activations with dynamic loss scaling")
     ap.add_argument("--batch", type=int, default=None, help="tokens per batch (default: the shape's)")
@@ -190,6 +194,24 @@ def heldout_batch(device):
     out = torch.stack([x, y])
     del synth
     return out
+
+
+class FreshBatches:
+    """The seeded synthetic stream, one new ``[2, L, B, d]`` batch per call, generated on the device (convergence runs)."""
+
+    def __init__(self, device):
+        from crosslayer_coding_b200.activation_generation.synthetic import SparseDictionarySynth, SyntheticSpec
+
+        L, d = MODEL["num_layers"], MODEL["d_model"]
+        self.synth = SparseDictionarySynth(SyntheticSpec(num_layers=L, d_model=d, dict_size=MODEL["dict_mult"] * d, active_mean=MODEL["active"], seed=1234), device=device)
+        self.synth.fit_norm_stats(8192)
+
+    def __call__(self, i: int):
+        import torch
+
+        t16 = torch.float16 if MODEL.get("precision") == "fp16" else torch.bfloat16
+        x, y = self.synth.sample(MODEL["batch"], seed=100000 + i, normalize=True, dtype=t16)
+        return torch.stack([x, y])
 
 
 def nmse_of(yhat, y) -> float:
@@ -310,7 +332,7 @@ def run_ours(args, world, rank, local):
     fp16 = args.precision == "fp16"
     clt_cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k,
                         clt_dtype="float16" if fp16 else "bfloat16", jumprelu_threshold=jumprelu_theta(), decoder_tying=args.decoder_tying)
-    total = args.warmup * 2 + args.steps * 2 + 8
+    total = args.warmup * 2 + args.steps * 2 + 8 + args.parity_steps
     tc = TrainingConfig(
         learning_rate=1e-4, training_steps=max(total, 1000), train_batch_size_tokens=B, precision=args.precision,
         activation_path="in-memory", activation_dtype="float16" if fp16 else "bfloat16", normalization_method="mean_std",
@@ -402,15 +424,28 @@ def run_ours(args, world, rank, local):
 
     parity = None
     if args.parity_steps > 0:
+        held = heldout_batch(dev)
+        fresh = FreshBatches(dev) if args.parity_fresh else None
+        curve = []
+
+        def heldout_nmse():
+            with torch.no_grad():
+                yhat = engine.forward(held[0].to(engine.t16), held[1].to(engine.t16))
+            return nmse_of(yhat, held[1])
+
         for i in range(args.parity_steps):
-            inputs, targets = next(store)
+            if fresh is not None:
+                b = fresh(i)
+                inputs, targets = LayerBatch.from_stacked(b[0], layers), LayerBatch.from_stacked(b[1], layers)
+            else:
+                inputs, targets = next(store)
             trainer.train_step(inputs, targets, step_box[0])
             step_box[0] += 1
-        held = heldout_batch(dev)
-        with torch.no_grad():
-            yhat = engine.forward(held[0].to(engine.t16), held[1].to(engine.t16))
+            if args.parity_log_every and (i + 1) % args.parity_log_every == 0:
+                curve.append([i + 1, round(heldout_nmse(), 5)])
         engine.check_status()
-        parity = {"steps_trained": step_box[0], "nmse_heldout": nmse_of(yhat, held[1]), "pool_batches": args.pool}
+        parity = {"steps_trained": step_box[0], "nmse_heldout": heldout_nmse(), "pool_batches": args.pool,
+                  "data": "fresh batch per step" if fresh is not None else "pool cycled", "curve": curve}
 
     value = B * args.steps / (ms / 1e3)
     e2e_value = B * args.steps / (e2e_ms / 1e3)
@@ -468,7 +503,7 @@ def run_reference(args, world, rank, local):
     cfg = RefCLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k,
                        jumprelu_threshold=jumprelu_theta(), clt_dtype="bfloat16" if bf16_params else None, decoder_tying=args.decoder_tying)
     tc = RefTrainingConfig(
-        learning_rate=1e-4, training_steps=1000, train_batch_size_tokens=B, precision=args.precision,
+        learning_rate=1e-4, training_steps=max(args.warmup * 2 + args.steps * 2 + 8 + args.parity_steps, 1000), train_batch_size_tokens=B, precision=args.precision,
         activation_path="in-memory", activation_dtype="float16" if fp16 else "bfloat16", normalization_method="mean_std",
         sparsity_lambda=(1e-3 if jr else 0.0), sparsity_lambda_schedule="linear", sparsity_lambda_delay_frac=0.0,
         preactivation_coef=0, aux_loss_factor=1 / 32, apply_sparsity_penalty_to_batchtopk=False,
@@ -551,16 +586,27 @@ def run_reference(args, world, rank, local):
     parity = None
     if args.parity_steps > 0:
         done = args.warmup + args.steps + min(args.warmup, 2) + args.steps
+        held = heldout_batch(dev)
+        fresh = FreshBatches(dev) if args.parity_fresh else None
+        curve = []
+
+        def heldout_nmse():
+            with torch.no_grad(), torch.autocast(device_type="cuda", dtype=amp_dtype, enabled=True):
+                out = model({l: held[0, l] for l in range(L)})
+            return nmse_of(torch.stack([out[l].float() for l in range(L)]), held[1])
+
         for i in range(args.parity_steps):
-            buf = stage[i % 2]
-            buf.copy_(host[i % args.pool], non_blocking=True)
+            if fresh is not None:
+                buf = fresh(i)
+            else:
+                buf = stage[i % 2]
+                buf.copy_(host[i % args.pool], non_blocking=True)
             x, y = as_dicts(buf)
             step_fn(x, y, done + i)
-        held = heldout_batch(dev)
-        with torch.no_grad(), torch.autocast(device_type="cuda", dtype=amp_dtype, enabled=True):
-            out = model({l: held[0, l] for l in range(L)})
-        yhat = torch.stack([out[l].float() for l in range(L)])
-        parity = {"steps_trained": done + args.parity_steps, "nmse_heldout": nmse_of(yhat, held[1]), "pool_batches": args.pool}
+            if args.parity_log_every and (i + 1) % args.parity_log_every == 0:
+                curve.append([i + 1, round(heldout_nmse(), 5)])
+        parity = {"steps_trained": done + args.parity_steps, "nmse_heldout": heldout_nmse(), "pool_batches": args.pool,
+                  "data": "fresh batch per step" if fresh is not None else "pool cycled", "curve": curve}
     return {
         "metric": metric_name(jr),
         "value": B * args.steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,

@@ -728,7 +728,10 @@ void* clt_h5r_open(const char* path) {
   struct stat st;
   if (fstat(r->fd, &st) != 0 || st.st_size < 96) { close(r->fd); fail("file too small to be HDF5"); return nullptr; }
   r->size = uint64_t(st.st_size);
-  void* mp = mmap(nullptr, r->size, PROT_READ, MAP_PRIVATE, r->fd, 0);
+  // MAP_POPULATE: the page tables are filled in one go at open time (read-ahead from disk when the file is not cached);
+  // a batch assembly that touches tens of thousands of pages would otherwise take one minor fault per page
+  void* mp = mmap(nullptr, r->size, PROT_READ, MAP_PRIVATE | MAP_POPULATE, r->fd, 0);
+  if (mp == MAP_FAILED) mp = mmap(nullptr, r->size, PROT_READ, MAP_PRIVATE, r->fd, 0);
   if (mp == MAP_FAILED) { close(r->fd); fail("mmap failed"); return nullptr; }
   r->base = static_cast<const uint8_t*>(mp);
   uint64_t sb = 0;
@@ -806,7 +809,8 @@ int clt_h5r_scatter_rows(void* handle, const char* paths, int npaths, const uint
                          void* const* dst_bases, uint64_t dst_row_stride, int nthreads) {
   Reader& r = *static_cast<Reader*>(handle);
   std::lock_guard<std::mutex> lock(r.mu);
-  struct Job { const uint8_t* src; uint8_t* dst; uint64_t rb; };
+  // a job copies rows of one dataset: contiguous layout (src) or unfiltered chunks (file address per chunk of chunk_rows rows)
+  struct Job { const uint8_t* src; uint8_t* dst; uint64_t rb; uint64_t chunk_rows; std::vector<uint64_t> chunk_addr; };
   std::vector<Job> jobs;
   std::vector<std::string> names;
   {
@@ -824,9 +828,20 @@ int clt_h5r_scatter_rows(void* handle, const char* paths, int npaths, const uint
     if (rb > dst_row_stride) return fail("scatter_rows: destination rows are too short");
     for (uint64_t i = 0; i < n; ++i)
       if (rows[i] >= d.rows) return fail("row index out of range");
+    bool plain_chunks = d.layout == 2 && !d.deflate && !d.shuffle && d.chunk_rows > 0 && d.btree_addr != UNDEF && load_chunk_index(r, d);
+    if (plain_chunks) {
+      for (size_t c = 0; c < d.chunks.size(); ++c)
+        if (d.chunk_mask[c] != 0 || d.chunks[c].nbytes != d.chunk_rows * rb || !r.ok(d.chunks[c].addr, d.chunk_rows * rb)) { plain_chunks = false; break; }
+    }
     if (d.layout == 1 && d.data_addr != UNDEF) {
       if (!r.ok(d.data_addr, d.rows * rb)) return fail("dataset outside the file");
-      jobs.push_back({r.base + d.data_addr, static_cast<uint8_t*>(dst_bases[p]), rb});
+      jobs.push_back({r.base + d.data_addr, static_cast<uint8_t*>(dst_bases[p]), rb, 0, {}});
+    } else if (plain_chunks) {
+      Job j{nullptr, static_cast<uint8_t*>(dst_bases[p]), rb, d.chunk_rows, {}};
+      j.chunk_addr.assign((d.rows + d.chunk_rows - 1) / d.chunk_rows, UNDEF);
+      for (const ChunkRec& c : d.chunks)
+        if (c.row0 / d.chunk_rows < j.chunk_addr.size()) j.chunk_addr[c.row0 / d.chunk_rows] = c.addr;
+      jobs.push_back(std::move(j));
     } else {
       tmp.resize(n * rb);
       if (read_rows_impl(r, names[p], rows, n, false, tmp.data()) != 0) return -1;
@@ -839,10 +854,26 @@ int clt_h5r_scatter_rows(void* handle, const char* paths, int npaths, const uint
   int T = nthreads < 1 ? 1 : nthreads;
   if (uint64_t(T) > total / 256 + 1) T = int(total / 256 + 1);
   auto work = [&](uint64_t lo, uint64_t hi) {
-    for (uint64_t k = lo; k < hi; ++k) {
+    for (uint64_t k = lo; k < hi;) {
       const Job& j = jobs[k / n];
       const uint64_t i = k % n;
-      memcpy(j.dst + uint64_t(dst_pos[i]) * dst_row_stride, j.src + rows[i] * j.rb, j.rb);
+      const uint64_t row = rows[i];
+      // consecutive source rows (of one chunk) that land in consecutive, gap-free destination rows move as one copy
+      uint64_t lim = std::min<uint64_t>(hi - k, n - i);
+      const uint8_t* src;
+      if (j.src != nullptr) {
+        src = j.src + row * j.rb;
+      } else {
+        const uint64_t c = row / j.chunk_rows, in_chunk = row - c * j.chunk_rows;
+        lim = std::min<uint64_t>(lim, j.chunk_rows - in_chunk);
+        src = j.chunk_addr[c] == UNDEF ? nullptr : r.base + j.chunk_addr[c] + in_chunk * j.rb;
+      }
+      uint64_t run = 1;
+      if (j.rb == dst_row_stride)
+        while (run < lim && rows[i + run] == row + run && dst_pos[i + run] == dst_pos[i] + int64_t(run)) ++run;
+      uint8_t* dst = j.dst + uint64_t(dst_pos[i]) * dst_row_stride;
+      if (src != nullptr) memcpy(dst, src, j.rb * run); else memset(dst, 0, j.rb * run);  // unallocated chunk reads as zeros
+      k += run;
     }
   };
   if (T == 1) { work(0, total); return 0; }

@@ -31,7 +31,7 @@ CASES = {
 
 
 def build(case: str, device: torch.device, activation: str = "batchtopk", states: str = "float32", tying: str = "none",
-          precision: str = "bf16"):
+          precision: str = "bf16", group=None):
     from .. import CLTConfig, CrossLayerTranscoder, TrainingConfig
     from ..training.fused_engine import FusedBatchTopKEngine
 
@@ -40,7 +40,7 @@ def build(case: str, device: torch.device, activation: str = "batchtopk", states
     t16 = torch.float16 if precision == "fp16" else torch.bfloat16
     cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=activation, batchtopk_k=k, topk_k=k,
                     clt_dtype="float16" if precision == "fp16" else "bfloat16", jumprelu_threshold=0.03, decoder_tying=tying)
-    model = CrossLayerTranscoder(cfg, device=device)
+    model = CrossLayerTranscoder(cfg, process_group=group, device=device)
     if tying != "none":
         with torch.no_grad():  # tied decoders start at zero
             for w in model.dec_weight:
@@ -58,7 +58,13 @@ def build(case: str, device: torch.device, activation: str = "batchtopk", states
         lam = 1e-3
     tc = TrainingConfig(learning_rate=1e-4, training_steps=1000, activation_path="unused", precision=precision,
                         sparsity_lambda=lam, preactivation_coef=0.0, optimizer_states_dtype=states, loss_scale_init=256.0)
-    eng = FusedBatchTopKEngine(model, tc, B)
+    symm = None
+    if group is not None:
+        from ..parallel.symm import SymmetricExchange
+
+        symm = SymmetricExchange.create(group, device, cfg, B)
+    eng = FusedBatchTopKEngine(model, tc, B, symm=symm)
+    torch.manual_seed(1)  # the same batch on every rank
     X = torch.randn(L, B, d, device=device).to(t16)
     Y = torch.randn(L, B, d, device=device).to(t16)
     return model, eng, X, Y
@@ -76,6 +82,126 @@ def _best_of(fn, n: int = 5) -> float:
     return min(ev[i].elapsed_time(ev[i + 1]) for i in range(n))
 
 
+class _TimedCalls:
+    """Wraps an object so that every call of one of its functions is bracketed by a pair of CUDA events."""
+
+    def __init__(self, inner, prefix: str, records: list):
+        self._inner, self._prefix, self._records = inner, prefix, records
+
+    def __getattr__(self, name):
+        f = getattr(self._inner, name)
+        if not callable(f):
+            return f
+
+        def timed(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = f(*a, **kw)
+            e1.record()
+            self._records.append((self._prefix + name, e0, e1))
+            return r
+
+        return timed
+
+
+def tp_per_call(args) -> None:
+    """CUDA-event time of every extension call, phase barrier and library collective of the tensor-parallel step, per rank
+    (run under ``python -m torch.distributed.run --nproc-per-node N``; no profiler involved).  Rank 0 prints one JSON line
+    with the per-call means of the slowest rank, the device time of the whole step (max over ranks) and the NVLink bytes
+    that the two pushes of the decode exchange move per rank and step."""
+    import collections
+    import os
+
+    import torch.distributed as dist
+
+    from ..training import fused_engine as fe
+
+    world, rank, local = (int(os.environ.get(n, d)) for n, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    model, eng, X, Y = build(args.case, dev, args.activation, args.optimizer_states, args.tying, args.precision, group=group)
+    lam = eng.tc.sparsity_lambda
+    lr = args.lr if args.lr is not None else (1e-8 if args.activation == "jumprelu" else 1e-4)
+    for s in range(max(args.warmup, 3)):
+        eng.train_step(X, Y, s, lr, sparsity_lambda=lam)
+    torch.cuda.synchronize()
+    steps = 10
+
+    def timed_steps() -> float:
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        s0.record()
+        for s in range(steps):
+            eng.train_step(X, Y, 100 + s, lr, sparsity_lambda=lam)
+        s1.record()
+        torch.cuda.synchronize()
+        return s0.elapsed_time(s1) / steps
+
+    plain_ms = timed_steps()  # without the event pairs
+    records: list = []
+    raw_ext = eng.ext
+    eng.ext = _TimedCalls(raw_ext, "", records)
+    orig_all_reduce = fe.pops.all_reduce
+
+    def all_reduce(*a, **kw):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r = orig_all_reduce(*a, **kw)
+        e1.record()
+        records.append(("nccl all_reduce", e0, e1))
+        return r
+
+    fe.pops.all_reduce = all_reduce
+    if eng.symm is not None:
+        orig_barrier = eng.symm.barrier
+
+        def barrier(ext_obj, status):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            orig_barrier(raw_ext, status)
+            e1.record()
+            records.append(("peer_barrier", e0, e1))
+
+        eng.symm.barrier = barrier
+    timed_ms = timed_steps()
+    eng.check_status()
+    agg = collections.OrderedDict()
+    for name, e0, e1 in records:
+        agg.setdefault(name, [0.0, 0])
+        agg[name][0] += e0.elapsed_time(e1) / steps
+        agg[name][1] += 1
+    names = list(agg)
+    vals = torch.tensor([agg[n][0] for n in names] + [plain_ms, timed_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        L, d, F, B, k = CASES[args.case]
+        push_partial = (world - 1) / world * L * B * d * 4 if world > 1 else 0       # fp32 partial sums to the owners
+        push_seed = (world - 1) / world * L * B * d * 2 if world > 1 else 0          # 16-bit gradient seed to every peer
+        out = {
+            "case": args.case, "world": world, "activation": args.activation, "tying": args.tying, "precision": args.precision,
+            "step_ms": float(vals[-2]), "step_ms_with_event_pairs": float(vals[-1]),
+            "per_call_ms": {n: round(float(v), 4) for n, v in zip(names, vals[:-2].tolist())},
+            "calls_per_step": {n: agg[n][1] / steps for n in names},
+            "nvlink_bytes_per_rank_per_step": {"decode_partials_out": int(push_partial), "gradient_seed_out": int(push_seed)},
+        }
+        if world > 1:
+            call = out["per_call_ms"]
+            exch = call.get("sparse_decode", 0.0) + call.get("owner_reduce_loss", 0.0) + call.get("peer_barrier", 0.0)
+            out["exchange_ms"] = round(exch, 4)
+            out["exchange_floor_ms_at_770GBs"] = round((push_partial + push_seed) / 770e9 * 1e3, 4)
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--case", choices=sorted(CASES), default="full")
@@ -91,7 +217,12 @@ def main() -> None:
     ap.add_argument("--lr", type=float, default=None,
                     help="learning rate (default 1e-4; 1e-8 for jumprelu so that the active count of the synthetic data stays put)")
     ap.add_argument("--time", action="store_true", help="print CUDA-event timings instead of marking a profiler range")
+    ap.add_argument("--tp-per-call", action="store_true",
+                    help="per-call CUDA-event times of the tensor-parallel step (launch with torch.distributed.run, one rank per GPU)")
     args = ap.parse_args()
+    if args.tp_per_call:
+        tp_per_call(args)
+        return
     dev = torch.device("cuda:0")
     model, eng, X, Y = build(args.case, dev, args.activation, args.optimizer_states, args.tying, args.precision)
     lam = eng.tc.sparsity_lambda

@@ -37,7 +37,8 @@ class InMemoryActivationStore(BaseActivationStore):
         self.apply_normalization = False
         self.mean_tg: Dict[int, torch.Tensor] = {}
         self.std_tg: Dict[int, torch.Tensor] = {}
-        self.stager = DeviceStager(tuple(pool.shape[1:]), pool.dtype, self.device, depth=max(2, prefetch + 1),
+        self.stager = DeviceStager(tuple(pool.shape[1:]), pool.dtype, self.device, depth=max(2, prefetch + 2),  # one spare slot: a refill never has to wait for the slot the consumer released last
+                                  
                                    shard_group=shard_group, row_dim=2)
         self.cursor = 0
         self.epoch = 0

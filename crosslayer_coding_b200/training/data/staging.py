@@ -60,6 +60,9 @@ class DeviceStager:
             self.host = [torch.empty(shape, dtype=dtype) for _ in range(self.depth)]
             self.dev = list(self.host)
         self._next = 0
+        # optional callable returning the CUDA event a copy has to wait for before it starts (the consumer can place the
+        # copies in a phase of its step where the extra memory traffic costs least)
+        self.gate = None
         if not self.cuda:
             self.shard_world = 1
 
@@ -68,6 +71,7 @@ class DeviceStager:
         import torch.distributed as dist
 
         self.shard_world, self.shard_rank, self.gather_group = 1, 0, None
+        self.peer_outer: Optional[int] = None  # leading outer indices whose rows the peers receive (None: all of them)
         if shard_group is None or not dist.is_initialized() or dist.get_world_size(shard_group) <= 1:
             return
         W = dist.get_world_size(shard_group)
@@ -120,6 +124,17 @@ class DeviceStager:
             return False
         return True
 
+    def push_only_leading(self, outer_count: Optional[int]) -> bool:
+        """Restrict the peer pushes to the first ``outer_count`` outer indices; the remaining ones (the target half of an
+        ``[2, L, B, d]`` batch when ``outer_count == L``) stay valid on the rank that loaded the rows only.  For consumers
+        that need every token's inputs but only their own token rows of the targets (the tensor-parallel fused step: the
+        loss of a token is finished by the rank that owns its row block, the same block this stager loads).  Returns
+        whether the restriction is in force (push staging only)."""
+        if not (self.cuda and getattr(self, "push", False)):
+            return False
+        self.peer_outer = None if outer_count is None else max(0, min(int(outer_count), self.outer))
+        return self.peer_outer is not None
+
     def _push_rows(self, slot: int, host: torch.Tensor) -> None:
         """Own rows: pinned host -> own slot -> every peer's slot, as strided copies on the staging stream."""
         es = host.element_size()
@@ -129,9 +144,12 @@ class DeviceStager:
         mine = self.dev[slot].data_ptr() + off
         self._barrier()                                        # every rank's consumer has released this slot
         self._ext.memcpy_2d(mine, pitch, host.data_ptr() + off, pitch, width, self.outer)
+        height = self.outer if self.peer_outer is None else self.peer_outer
         for i in range(1, self.shard_world):
+            if height == 0:
+                break
             p = (self.shard_rank + i) % self.shard_world       # staggered: no two ranks start on the same peer
-            self._ext.memcpy_2d(self._peer_base[p] + slot * self._slot_bytes + off, pitch, mine, pitch, width, self.outer)
+            self._ext.memcpy_2d(self._peer_base[p] + slot * self._slot_bytes + off, pitch, mine, pitch, width, height)
         self._barrier()                                        # every rank's pushes have landed
 
     def _barrier(self) -> None:
@@ -170,6 +188,9 @@ class DeviceStager:
         with torch.cuda.stream(self.stream):
             if self.released[slot] is not None:
                 self.stream.wait_event(self.released[slot])  # consumer is done with the old contents
+            gate = self.gate() if self.gate is not None else None
+            if gate is not None:
+                self.stream.wait_event(gate)
             host = self.host[slot] if src is None else src
             if self.shard_world == 1:
                 self.dev[slot].copy_(host, non_blocking=True)

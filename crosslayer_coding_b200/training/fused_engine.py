@@ -359,6 +359,9 @@ class FusedBatchTopKEngine:
         self._check_guards = _os.environ.get(ext.DEBUG_ENV, "") not in ("", "0")  # debug runs read the guard bytes at every status check
         self.opt_step = 0
         self.seq = 0
+        # recorded right before the optimizer sweep of every step: the staging copies of later batches are released at this
+        # point (their host-to-device writes slow the read-streaming kernels at the start of a step far more than the sweep)
+        self.sweep_begin: Optional[torch.cuda.Event] = None
         self.kernel_launches = 0  # launches of this package's own kernels (reported by the benchmark)
         self.last_output: Optional[StepOutput] = None
 
@@ -877,6 +880,8 @@ class FusedBatchTopKEngine:
             self._control(1, losses)
             grad_a_for_update = None  # dL/da is complete; the update pass must not add to it again
             self.kernel_launches += 4
+        if self.sweep_begin is not None:
+            self.sweep_begin.record()
         e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, tying_dec,
                             self.feat_off, self.fcsr_tok, self.fcsr_val, gs_dec, grad_a_for_update, pen, self.norm2_next,
                             None, None, dec0_dense, h_dec, self.status, dec_x_idx, dec_x_rows, ctl, False)

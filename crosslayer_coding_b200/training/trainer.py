@@ -221,11 +221,55 @@ class CLTTrainer:
             self.engine = FusedBatchTopKEngine(self.model, tc, tc.train_batch_size_tokens, sigma_tg=sigma,
                                                symm=getattr(self, "_symm", None))
             logger.info("Rank %d: using the fused sm_100a step engine", self.rank)
+            self._restrict_target_staging()
+            self._gate_staging()
             return
         if want == "fused":
             raise ValueError(f"engine='fused' requested but not available: {reason}")
         logger.info("Rank %d: using the autograd step (%s)", self.rank, reason)
         self._build_autograd_optimizer()
+
+    def _restrict_target_staging(self) -> None:
+        """Tensor-parallel fused runs: the loss of a token is finished by the rank that owns its row block, which is the
+        block that rank's stager loads from the host, so the targets need not travel to the peers (half of the staging
+        traffic over NVLink).  Evaluation gathers the owners' target rows again (``_full_targets``)."""
+        self._target_rows = None
+        stager = getattr(self.activation_store, "stager", None)
+        if self.world_size <= 1 or stager is None or getattr(stager, "shard_world", 1) != self.world_size:
+            return
+        B = self.training_config.train_batch_size_tokens
+        symm = getattr(self, "_symm", None)
+        if symm is None or B % self.world_size != 0 or symm.rows_per_rank != getattr(stager, "rows_per_rank", -1):
+            return
+        if getattr(stager, "shard_rank", -1) != self.rank:
+            return
+        if stager.push_only_leading(self.clt_config.num_layers):
+            self._target_rows = (self.rank * symm.rows_per_rank, symm.rows_per_rank)
+
+    def _gate_staging(self) -> None:
+        """Lets the store's staging copies start when a step reaches its optimizer sweep instead of at the step boundary:
+        host-to-device writes that arrive during the read-streaming kernels at the start of a step (column statistics,
+        selection pass) slow those by far more than their own volume; the sweep mixes reads and writes anyway."""
+        stager = getattr(self.activation_store, "stager", None)
+        if stager is None or not getattr(stager, "cuda", False) or not hasattr(stager, "gate"):
+            return
+        eng = self.engine
+        eng.sweep_begin = torch.cuda.Event()
+        eng.sweep_begin.record()
+        stager.gate = lambda: eng.sweep_begin
+
+    def _full_targets(self, Y: torch.Tensor) -> torch.Tensor:
+        """``[L, B, d]`` targets with every rank's owned rows filled in (all-gather over the process group)."""
+        if getattr(self, "_target_rows", None) is None:
+            return Y
+        import torch.distributed as dist
+
+        r0, n = self._target_rows
+        L, B, d = Y.shape
+        own = Y[:, r0:r0 + n].contiguous()
+        out = torch.empty(self.world_size, L, n, d, dtype=Y.dtype, device=Y.device)
+        dist.all_gather_into_tensor(out, own, group=self.process_group)
+        return out.permute(1, 0, 2, 3).reshape(L, B, d).contiguous()
 
     def _build_autograd_optimizer(self) -> None:
         tc = self.training_config
@@ -495,10 +539,14 @@ class CLTTrainer:
         # fused runs evaluate through the sparse forward (no dense [B, F] activations) unless the dense diagnostics
         # were asked for; the dead-feature counters are not touched by an evaluation forward
         fused_eval = self.engine is not None and not tc.compute_sparsity_diagnostics
+        if getattr(self, "_target_rows", None) is not None and not fused_eval:
+            layers = list(range(self.clt_config.num_layers))
+            full = self._full_targets(_stack_layers(targets, layers))
+            targets = {l: full[l] for l in layers}
         with self.profiler.timer("evaluation"):
             if fused_eval:
                 layers = list(range(self.clt_config.num_layers))
-                X, Y = _stack_layers(inputs, layers), _stack_layers(targets, layers)
+                X, Y = _stack_layers(inputs, layers), self._full_targets(_stack_layers(targets, layers))
                 if X.dtype != self.engine.t16:
                     X, Y = X.to(self.engine.t16), Y.to(self.engine.t16)
                 metrics = self.evaluator.compute_metrics_from_engine(self.engine, X, Y, dead_neuron_mask=self.dead_neurons_mask)
