@@ -961,17 +961,32 @@ __global__ void __launch_bounds__(1024) refine_kernel(const uint32_t* __restrict
     if (fits_s) {
       const int G = total_s;
       const unsigned long long want = need;  // the want-th largest word is the cut
-      for (int i = tid; i < G; i += 1024) {
-        const unsigned long long mine = comp[i];
-        int above = 0;
-        for (int j = 0; j < G; ++j) above += comp[j] > mine;
-        if ((unsigned long long)above + 1ULL == want) {
-          ctl[CTL_CUT_KEY] = (long long)(mine >> 45);
-          ctl[CTL_TIE_MODE] = 1;
-          ctl[CTL_CUT_FLAT] = (long long)(kFlatMask - (mine & kFlatMask));
+      // bitonic sort of the words in shared memory, descending (the words are distinct; zero pads the power of two)
+      int P = 1;
+      while (P < G) P <<= 1;
+      for (int i = G + tid; i < P; i += 1024) comp[i] = 0ULL;
+      __syncthreads();
+      for (int size = 2; size <= P; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+          for (int t = tid; t < P / 2; t += 1024) {
+            const int lo = 2 * t - (t & (stride - 1)), hi = lo + stride;
+            const unsigned long long a = comp[lo], b = comp[hi];
+            const bool descending = (lo & size) == 0;
+            if (descending ? a < b : a > b) { comp[lo] = b; comp[hi] = a; }
+          }
+          __syncthreads();
         }
       }
-      if (tid == 0 && (want == 0 || want > (unsigned long long)G)) atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
+      if (tid == 0) {
+        if (want == 0 || want > (unsigned long long)G) {
+          atomicCAS(status, STATUS_OK, STATUS_SELECT_RANGE);
+        } else {
+          const unsigned long long cutw = comp[want - 1];
+          ctl[CTL_CUT_KEY] = (long long)(cutw >> 45);
+          ctl[CTL_TIE_MODE] = 1;
+          ctl[CTL_CUT_FLAT] = (long long)(kFlatMask - (cutw & kFlatMask));
+        }
+      }
       return;
     }
   }
@@ -1261,36 +1276,48 @@ __global__ void __launch_bounds__(256) csr_sort_segments_kernel(const int* __res
 // stability is needed); out-of-range partners of the virtual power-of-two padding are skipped.
 __global__ void __launch_bounds__(256) csr_sort_long_segments_kernel(const int* __restrict__ off, int nseg, int* __restrict__ key,
                                                                        float* __restrict__ val) {
-  for (int sidx = blockIdx.x; sidx < nseg; sidx += gridDim.x) {
-    const int b = off[sidx], n = off[sidx + 1] - b;
-    if (n <= kShortSegment) continue;  // uniform over the CTA
-    int* k = key + b;
-    float* v = val + b;
-    int p2 = 1;
-    while (p2 < n) p2 <<= 1;
-    // every comparator puts the smaller key at the lower index (the first step of a merge pairs mirrored positions), so
-    // the virtual padding, which stands for +infinity at the end of the array, never has to move
-    for (int size = 2; size <= p2; size <<= 1) {
-      for (int stride = size >> 1; stride > 0; stride >>= 1) {
-        __syncthreads();
-        for (int i = threadIdx.x; i < p2 / 2; i += blockDim.x) {
-          int lo, hi;
-          if (stride == (size >> 1)) {
-            const int blk = i / stride, j = i - blk * stride;
-            lo = blk * size + j;
-            hi = blk * size + size - 1 - j;
-          } else {
-            lo = 2 * i - (i & (stride - 1));
-            hi = lo + stride;
-          }
-          if (hi >= n) continue;
-          const int ka = k[lo], kb = k[hi];
-          if (ka > kb) {
-            k[lo] = kb; k[hi] = ka;
-            const float t = v[lo]; v[lo] = v[hi]; v[hi] = t;
+  __shared__ int long_list[256];
+  __shared__ int long_count;
+  // every thread looks at one segment of a block of 256; the few long ones are then sorted one after the other by the CTA
+  for (int base = blockIdx.x * 256; base < nseg; base += gridDim.x * 256) {
+    if (threadIdx.x == 0) long_count = 0;
+    __syncthreads();
+    const int mine = base + threadIdx.x;
+    if (mine < nseg && off[mine + 1] - off[mine] > kShortSegment) long_list[atomicAdd(&long_count, 1)] = mine;
+    __syncthreads();
+    const int nlong = long_count;
+    for (int q = 0; q < nlong; ++q) {
+      const int sidx = long_list[q];
+      const int b = off[sidx], n = off[sidx + 1] - b;
+      int* k = key + b;
+      float* v = val + b;
+      int p2 = 1;
+      while (p2 < n) p2 <<= 1;
+      // every comparator puts the smaller key at the lower index (the first step of a merge pairs mirrored positions), so
+      // the virtual padding, which stands for +infinity at the end of the array, never has to move
+      for (int size = 2; size <= p2; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+          __syncthreads();
+          for (int i = threadIdx.x; i < p2 / 2; i += blockDim.x) {
+            int lo, hi;
+            if (stride == (size >> 1)) {
+              const int blk = i / stride, j = i - blk * stride;
+              lo = blk * size + j;
+              hi = blk * size + size - 1 - j;
+            } else {
+              lo = 2 * i - (i & (stride - 1));
+              hi = lo + stride;
+            }
+            if (hi >= n) continue;
+            const int ka = k[lo], kb = k[hi];
+            if (ka > kb) {
+              k[lo] = kb; k[hi] = ka;
+              const float t = v[lo]; v[lo] = v[hi]; v[hi] = t;
+            }
           }
         }
       }
+      __syncthreads();
     }
     __syncthreads();
   }
@@ -1604,11 +1631,11 @@ extern "C" int clt_build_csr(const CltCsrArgs* a, cudaStream_t st) {
                                              a->tcsr_col, a->tcsr_val, a->fcsr_tok, a->fcsr_val, a->col_pitch, a->num_tokens, a->num_cols);
   if (a->sort_segments & 1) {
     csr_sort_segments_kernel<<<(a->num_tokens + 255) / 256, 256, 0, st>>>(a->tok_off, a->num_tokens, a->tcsr_col, a->tcsr_val);
-    csr_sort_long_segments_kernel<<<a->num_tokens < 1184 ? a->num_tokens : 1184, 256, 0, st>>>(a->tok_off, a->num_tokens, a->tcsr_col, a->tcsr_val);
+    csr_sort_long_segments_kernel<<<(a->num_tokens + 255) / 256 < 1184 ? (a->num_tokens + 255) / 256 : 1184, 256, 0, st>>>(a->tok_off, a->num_tokens, a->tcsr_col, a->tcsr_val);
   }
   if (a->sort_segments & 2) {
     csr_sort_segments_kernel<<<(a->num_cols + 255) / 256, 256, 0, st>>>(a->feat_off, a->num_cols, a->fcsr_tok, a->fcsr_val);
-    csr_sort_long_segments_kernel<<<a->num_cols < 1184 ? a->num_cols : 1184, 256, 0, st>>>(a->feat_off, a->num_cols, a->fcsr_tok, a->fcsr_val);
+    csr_sort_long_segments_kernel<<<(a->num_cols + 255) / 256 < 1184 ? (a->num_cols + 255) / 256 : 1184, 256, 0, st>>>(a->feat_off, a->num_cols, a->fcsr_tok, a->fcsr_val);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
