@@ -93,6 +93,9 @@ def parse_args():
                     help="--parity-steps draws a fresh synthetic batch every step (seeded by the step, the same stream in both arms) "
                          "instead of cycling the pool: a convergence run")
     ap.add_argument("--parity-log-every", type=int, default=0, help="record the held-out normalised MSE every this many parity steps (key 'parity.curve')")
+    ap.add_argument("--stochastic-rounding", action="store_true",
+                    help="our arm: round the updated 16-bit weights stochastically (TrainingConfig.enable_stochastic_rounding); small "
+                         "late-schedule updates are otherwise lost to round-to-nearest")
     ap.add_argument("--decoder-tying", choices=["none", "per_source", "per_target"], default="none")
     ap.add_argument("--precision", choices=["bf16", "fp16"], default="bf16", help="fp16: fp16 weights / activations with dynamic loss scaling")
     ap.add_argument("--batch", type=int, default=None, help="tokens per batch (default: the shape's)")
@@ -339,7 +342,7 @@ def run_ours(args, world, rank, local):
         sparsity_lambda=(1e-3 if jr else 0.0), sparsity_lambda_schedule="linear", sparsity_lambda_delay_frac=0.0,
         preactivation_coef=0.0, aux_loss_factor=1 / 32, apply_sparsity_penalty_to_batchtopk=False,
         optimizer="adamw", lr_scheduler="linear", eval_interval=10 ** 9, checkpoint_interval=10 ** 9, log_interval=10 ** 9,
-        engine="fused", dead_feature_window=DEAD_WINDOW,
+        engine="fused", dead_feature_window=DEAD_WINDOW, enable_stochastic_rounding=bool(args.stochastic_rounding),
     )
     shard_group = None
     if world > 1:

@@ -153,6 +153,8 @@ struct DecAdamParams {
   float* norm2_out;            // optional [L * F_pitch]: sum of squares of the updated rows (atomicAdd; zeroed by caller)
   const float* feat_offset;    // tied decoders: optional [L, F_pitch] affine applied to the activation
   const float* feat_scale;
+  float* d_feat_offset;        // optional [L, F_pitch] gradient accumulators of the affine terms (zeroed by the caller); filled in
+  float* d_feat_scale;         // the pass that also writes grad_a
   int moments_bf16;            // bulk pipeline only: m / v hold bf16 (stochastically rounded) instead of fp32
   const float* dgrad_row0;     // optional [ntensors, F_pitch, d] fp32: extra gradient of every feature's first row
   // optional compact extras (auxiliary loss on dead features): extra_idx[col] = row of extra_rows, or -1
@@ -721,6 +723,7 @@ __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamPar
   const int nseg = (p.d + 255) / 256;
   const long long per_tensor = 1LL * p.F_pitch * nseg;
   const long long total_items = per_tensor * p.ntensors;
+  const bool affine_grads = p.tying != 0 && p.grad_a != nullptr && (p.d_feat_offset != nullptr || p.d_feat_scale != nullptr);
   for (long long item = warp_global; item < total_items; item += nwarps) {
     const int ti = int(item / per_tensor);
     const long long rem = item - ti * per_tensor;
@@ -772,18 +775,29 @@ __global__ void __launch_bounds__(256) decoder_rows_adam_kernel(const DecAdamPar
           const int t_end = t_fixed >= 0 ? t_fixed : p.L - 1;
           float dot = 0.f;
           for (int t = t_begin; t <= t_end; ++t) {
-            float av = a, dscale = 1.f;
+            float av = a, dscale = 1.f, shifted = a;
             if (p.tying != 0 && a != 0.f) {
               if (p.feat_offset) av += p.feat_offset[1LL * t * p.F_pitch + f];
+              shifted = av;
               if (p.feat_scale) { const float fsc = p.feat_scale[1LL * t * p.F_pitch + f]; av *= fsc; dscale = fsc; }
             }
+            float dot_t = 0.f;
             if (act) {
               float gv[8];
               unpack8(__ldg(reinterpret_cast<const uint4*>(p.gs + (1LL * t * p.B + tok) * p.d + e0)), gv);
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
                 g[k] = fmaf(av, gv[k], g[k]);
-                dot = fmaf(gv[k] * dscale, w[k], dot);
+                dot_t = fmaf(gv[k], w[k], dot_t);
+              }
+            }
+            dot = fmaf(dot_t, dscale, dot);
+            // gradients of the affine terms of target t: d/d offset = scale * (gs_t . w), d/d scale = (a + offset) * (gs_t . w)
+            if (affine_grads && a != 0.f) {
+              const float ds = warp_sum(dot_t) * gsc;
+              if (lane == 0 && ds != 0.f) {
+                if (p.d_feat_offset != nullptr) atomicAdd(&p.d_feat_offset[1LL * t * p.F_pitch + f], ds * dscale);
+                if (p.d_feat_scale != nullptr) atomicAdd(&p.d_feat_scale[1LL * t * p.F_pitch + f], ds * shifted);
               }
             }
           }
@@ -1120,6 +1134,7 @@ struct CltDecAdamArgs {
   const int* extra_idx; const float* extra_rows;  // compact extra gradient rows (auxiliary loss), see DecAdamParams
   float* ctl;        // step control block (skip flag, 1 / loss scale, clip coefficient); may be null
   int norm_only;     // 1: gradient-norm pre-pass (adds to ctl[SC_GRAD_NORM_SQ], writes grad_a, updates nothing)
+  float* d_feat_offset; float* d_feat_scale;  // tied decoders: gradient accumulators of the affine terms, see DecAdamParams
 };
 
 // Launch geometry of the bulk-copy row pipeline (shared by the decoder and the encoder update).
@@ -1208,6 +1223,7 @@ extern "C" int CLT_FN(clt_decoder_rows_adam)(const CltDecAdamArgs* a, int num_sm
   p.feat_off = a->feat_off; p.fcsr_tok = a->fcsr_tok; p.fcsr_val = a->fcsr_val;
   p.gs = static_cast<const t16*>(a->gs); p.grad_a = a->grad_a; p.pen_coef = a->pen_coef; p.norm2_out = a->norm2_out;
   p.feat_offset = a->feat_offset; p.feat_scale = a->feat_scale; p.dgrad_row0 = a->dgrad_row0; p.h = to_hyper(a->h);
+  p.d_feat_offset = a->d_feat_offset; p.d_feat_scale = a->d_feat_scale;
   p.moments_bf16 = a->moments_bf16;
   p.extra_idx = a->extra_idx; p.extra_rows = a->extra_rows; p.ctl = a->ctl; p.use_inv_scale = 1;
   p.norm_sq_out = a->ctl != nullptr ? a->ctl + SC_GRAD_NORM_SQ : nullptr;
@@ -1293,6 +1309,7 @@ extern "C" int CLT_FN(clt_encoder_rows_adam)(const CltEncAdamArgs* a, int num_sm
     q.ntensors = a->L; q.L = a->L; q.B = a->B; q.d = a->d; q.F_pitch = a->F_pitch; q.tying = 0;
     q.feat_off = a->feat_off; q.fcsr_tok = a->fcsr_tok; q.fcsr_val = a->delta; q.gs = p.x;
     q.grad_a = nullptr; q.pen_coef = nullptr; q.norm2_out = nullptr; q.feat_offset = nullptr; q.feat_scale = nullptr;
+    q.d_feat_offset = nullptr; q.d_feat_scale = nullptr;
     q.dgrad_row0 = a->dense_grad; q.h = p.h;
     q.moments_bf16 = a->moments_bf16;
     q.extra_idx = a->dense_grad == nullptr ? a->extra_idx : nullptr; q.extra_rows = a->extra_rows;

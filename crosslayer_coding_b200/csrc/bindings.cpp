@@ -103,6 +103,7 @@ struct CltDecAdamArgs {
   const int* extra_idx; const float* extra_rows;
   float* ctl;
   int norm_only;
+  float* d_feat_offset; float* d_feat_scale;
 };
 struct CltEncAdamArgs {
   void* w; float* m; float* v; void* bias; float* bias_m; float* bias_v;
@@ -567,7 +568,7 @@ void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vect
                        const Tensor& gs, const OptTensor& grad_a, const OptTensor& pen_coef, const OptTensor& norm2_out,
                        const OptTensor& feat_offset, const OptTensor& feat_scale, const OptTensor& dgrad_row0,
                        const std::vector<double>& hyper, const OptTensor& status, const OptTensor& extra_idx, const OptTensor& extra_rows,
-                       const OptTensor& ctl, bool norm_only) {
+                       const OptTensor& ctl, bool norm_only, const OptTensor& d_feat_offset, const OptTensor& d_feat_scale) {
   TORCH_CHECK(w.size() >= 1 && w.size() <= 32 && w.size() == m.size() && w.size() == v.size(), "bad tensor lists");
   CltDecAdamArgs a;
   std::memset(&a, 0, sizeof(a));
@@ -597,6 +598,10 @@ void decoder_rows_adam(std::vector<Tensor>& w, std::vector<Tensor>& m, std::vect
   a.moments_bf16 = m[0].scalar_type() == at::kBFloat16 ? 1 : 0;
   a.ctl = ctl_ptr(ctl);
   a.norm_only = norm_only ? 1 : 0;
+  a.d_feat_offset = opt_ptr<float>(d_feat_offset); a.d_feat_scale = opt_ptr<float>(d_feat_scale);
+  for (const OptTensor* t : {&d_feat_offset, &d_feat_scale})
+    if (t->has_value() && (*t)->defined())
+      TORCH_CHECK((*t)->is_cuda() && (*t)->scalar_type() == at::kFloat && (*t)->is_contiguous() && (*t)->numel() >= L * F_pitch, "affine gradient accumulators: fp32 [L, F]");
   c10::cuda::CUDAGuard guard(gs.device());
   check(CLT_PICK(half, clt_decoder_rows_adam)(&a, num_sms(), cur_stream()), "decoder_rows_adam");
 }
@@ -957,7 +962,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decoder_rows_adam", &decoder_rows_adam, py::arg("w"), py::arg("m"), py::arg("v"), py::arg("L"), py::arg("B"), py::arg("d"),
         py::arg("F_pitch"), py::arg("tying"), py::arg("feat_off"), py::arg("fcsr_tok"), py::arg("fcsr_val"), py::arg("gs"), py::arg("grad_a"),
         py::arg("pen_coef"), py::arg("norm2_out"), py::arg("feat_offset"), py::arg("feat_scale"), py::arg("dgrad_row0"), py::arg("hyper"),
-        py::arg("status"), py::arg("extra_idx") = none, py::arg("extra_rows") = none, py::arg("ctl") = none, py::arg("norm_only") = false);
+        py::arg("status"), py::arg("extra_idx") = none, py::arg("extra_rows") = none, py::arg("ctl") = none, py::arg("norm_only") = false,
+        py::arg("d_feat_offset") = none, py::arg("d_feat_scale") = none);
   m.def("encoder_rows_adam", &encoder_rows_adam, py::arg("w"), py::arg("m"), py::arg("v"), py::arg("bias"), py::arg("bias_m"), py::arg("bias_v"),
         py::arg("feat_off"), py::arg("fcsr_tok"), py::arg("delta"), py::arg("x"), py::arg("dense_grad"), py::arg("dense_bias_grad"),
         py::arg("hyper"), py::arg("status"), py::arg("extra_idx") = none, py::arg("extra_rows") = none, py::arg("extra_bias") = none,

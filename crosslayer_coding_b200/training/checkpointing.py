@@ -170,7 +170,7 @@ def optimizer_shard_axis(name: str, tensor: torch.Tensor) -> Optional[int]:
     if name.endswith("::step"):
         return None
     if base in ("enc_m", "enc_v", "encb_m", "encb_v", "theta_m", "theta_v", "enc_weight", "enc_bias", "log_threshold",
-                "feature_offset", "feature_scale", "dead_counter_2d"):
+                "feature_offset", "feature_scale", "dead_counter_2d", "foff_m", "foff_v", "fsc_m", "fsc_v"):
         return 1
     if base.startswith(("dec_m.", "dec_v.", "dec_weight.")):
         return 0

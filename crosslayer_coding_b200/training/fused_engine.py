@@ -82,8 +82,9 @@ def engine_supports(clt_config: CLTConfig, training_config: Optional[TrainingCon
     if clt_config.activation_fn == "jumprelu" and (clt_config.enable_feature_offset or clt_config.enable_feature_scale) \
             and clt_config.decoder_tying != "none":
         return "jumprelu with feature offset/scale (the threshold-gradient GEMM has no per-target affine)"
-    if (clt_config.enable_feature_offset or clt_config.enable_feature_scale) and clt_config.decoder_tying != "none":
-        return "feature offset/scale"
+    if (clt_config.enable_feature_offset or clt_config.enable_feature_scale) and clt_config.decoder_tying != "none" \
+            and training_config is not None and training_config.aux_loss_factor:
+        return "feature offset/scale together with the auxiliary loss (its decode has no affine)"
     if clt_config.d_model % 8 != 0 or clt_config.d_model > 2048:
         return "d_model must be a multiple of 8 and <= 2048"
     if clt_config.num_layers > 32:
@@ -353,7 +354,25 @@ class FusedBatchTopKEngine:
         # per-source tied decoders: the row of feature (s, f) serves every target t >= s, so its gradient and dL/da only need
         # the gradient seed summed over those targets; with that sum in place of the seed the decoder update is the
         # one-row-per-feature case of the untied row pipeline
-        self.gs_cum = torch.empty(L, B, d, dtype=self.t16, device=dev) if (self.tying == 1 and training_config is not None) else None
+        # feature affine of tied decoders (reference clt/models/decoder.py:228-285): a' = (a + offset_t[f]) * scale_t[f] at the
+        # active entries, per target layer t.  The kernels read fp32 copies; the gradients of the two terms come out of the
+        # tied decoder sweep (per entry and target: scale * (gs_t . w) and (a + offset) * (gs_t . w)), one small Adam kernel each.
+        self.affine = self.tying != 0 and (model.feature_offset is not None or model.feature_scale is not None)
+        self.foff32 = self.fsc32 = self.d_foff = self.d_fsc = None
+        if self.affine:
+            if model.feature_offset is not None:
+                self.foff32 = model.feature_offset.data.float().contiguous()
+                self.d_foff = torch.zeros(L, Fl, dtype=f32, device=dev)
+            if model.feature_scale is not None:
+                self.fsc32 = model.feature_scale.data.float().contiguous()
+                self.d_fsc = torch.zeros(L, Fl, dtype=f32, device=dev)
+            if training_config is not None:
+                z32 = lambda p: torch.zeros_like(p, dtype=f32)  # noqa: E731
+                if model.feature_offset is not None:
+                    self.foff_m, self.foff_v = z32(model.feature_offset), z32(model.feature_offset)
+                if model.feature_scale is not None:
+                    self.fsc_m, self.fsc_v = z32(model.feature_scale), z32(model.feature_scale)
+        self.gs_cum = torch.empty(L, B, d, dtype=self.t16, device=dev) if (self.tying == 1 and training_config is not None and not self.affine) else None
         import os as _os
 
         self._check_guards = _os.environ.get(ext.DEBUG_ENV, "") not in ("", "0")  # debug runs read the guard bytes at every status check
@@ -548,7 +567,7 @@ class FusedBatchTopKEngine:
         addend = self._skip_term(self._X_last) if m.skip_weight is not None else None
         if self.world == 1:
             e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
-                            None, None, None, bias_sum, addend, Y, self.sigma, self.gs, yhat, self.sq_err, 1, [], 0, 0, self.status,
+                            self.foff32, self.fsc32, None, bias_sum, addend, Y, self.sigma, self.gs, yhat, self.sq_err, 1, [], 0, 0, self.status,
                             self.step_ctl)
             self.kernel_launches += 1
         else:
@@ -557,7 +576,7 @@ class FusedBatchTopKEngine:
                 yhat.zero_()
             # 1. decode, pushing every token's partial sums into its owner's staging slot (peer stores)
             e.sparse_decode(dec_w, self.L, self.B, self.d, self.Fl, self.tying, self.tok_off, self.tcsr_col, self.tcsr_val,
-                            None, None, None, None, None, None, None, None, None, None, 2, sy.stage_ptrs, sy.rows_per_rank, self.rank, self.status)
+                            self.foff32, self.fsc32, None, None, None, None, None, None, None, None, 2, sy.stage_ptrs, sy.rows_per_rank, self.rank, self.status)
             sy.barrier(e, self.status)
             # 2. owners reduce their rows, finish their part of the loss and push the gradient seed to every rank; the
             #    exchange inside the step-control kernel that follows is the barrier behind these pushes
@@ -847,13 +866,17 @@ class FusedBatchTopKEngine:
             losses[4] += aux_val  # the auxiliary term is evaluated on the finished residual, after the loss was settled
             losses[0] += aux_val
         gs_dec, tying_dec = self.gs, self.tying
-        if self.tying == 1:
+        if self.affine:
+            for g in (self.d_foff, self.d_fsc):
+                if g is not None:
+                    g.zero_()
+        if self.tying == 1 and not self.affine:
             e.gs_suffix_sum(self.gs, self.gs_cum)
             gs_dec, tying_dec = self.gs_cum, 0
             self.kernel_launches += 1
         if jr:
             # window sums for the threshold gradient, from the decoder weights of this step (before their update)
-            gs_cum = self.gs_cum if self.tying == 1 else None
+            gs_cum = self.gs_cum if (self.tying == 1 and not self.affine) else None
             e.theta_grad_gemm(self.gs, [w.data for w in m.dec_weight], self.preact, self.theta, float(m.bandwidth), self.S1, self.S2,
                               self.status, self.tying, gs_cum)
             self.kernel_launches += 1
@@ -869,7 +892,9 @@ class FusedBatchTopKEngine:
             # without entries have none), dL/da is written on the way; step_control turns the norm into the coefficient
             rep = 1.0 / self.world  # replicated parameters are counted once over the ranks
             e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, tying_dec, self.feat_off, self.fcsr_tok, self.fcsr_val,
-                                gs_dec, self.grad_a, pen, None, None, None, dec0_dense, h_dec, None, dec_x_idx, dec_x_rows, ctl, True)
+                                gs_dec, self.grad_a, pen, None, self.foff32, self.fsc32, dec0_dense, h_dec, None, dec_x_idx, dec_x_rows, ctl, True,
+                                self.d_foff, self.d_fsc)
+            self._affine_adam(h_enc, ctl, norm_weight=1.0)
             e.decoder_bias_adam(m.dec_bias.data, self.decb_m, self.decb_v, self.bias_sel, self.gs_sum, extra_bias_grad, h_dec, ctl, rep)
             e.encoder_rows_adam(m.enc_weight.data, self.enc_m, self.enc_v, m.enc_bias.data, self.encb_m, self.encb_v, self.feat_off,
                                 self.fcsr_tok, self.grad_a, X, enc_dense, encb_dense, h_enc, None, enc_x_idx, enc_x_rows, enc_x_bias, ctl, True)
@@ -884,7 +909,9 @@ class FusedBatchTopKEngine:
             self.sweep_begin.record()
         e.decoder_rows_adam(dec_w, self.dec_m, self.dec_v, L, B, d, self.Fl, tying_dec,
                             self.feat_off, self.fcsr_tok, self.fcsr_val, gs_dec, grad_a_for_update, pen, self.norm2_next,
-                            None, None, dec0_dense, h_dec, self.status, dec_x_idx, dec_x_rows, ctl, False)
+                            self.foff32, self.fsc32, dec0_dense, h_dec, self.status, dec_x_idx, dec_x_rows, ctl, False,
+                            self.d_foff, self.d_fsc)
+        self._affine_adam(h_enc, ctl)
         if jr:
             # thresholds: uses the decoder norms of this step (before the swap below)
             self._theta_update(lr, c_g, float(sparsity_lambda) if use_pen else 0.0)
@@ -901,6 +928,21 @@ class FusedBatchTopKEngine:
         out = StepOutput(losses, self.ctl[3])
         self.last_output = out
         return out
+
+    def _affine_adam(self, hyper, ctl, norm_weight: float = 0.0) -> None:
+        """AdamW on the feature offset / scale of tied decoders from the accumulators that the decoder sweep filled; the fp32
+        copies that the kernels read follow the stored (16-bit) parameters.  ``norm_weight`` > 0: gradient-norm pre-pass."""
+        if not self.affine:
+            return
+        m = self.model
+        for prm, mirror, grad, names in ((m.feature_offset, self.foff32, self.d_foff, ("foff_m", "foff_v")),
+                                         (m.feature_scale, self.fsc32, self.d_fsc, ("fsc_m", "fsc_v"))):
+            if prm is None:
+                continue
+            self.ext.dense_adam(prm.data, getattr(self, names[0]), getattr(self, names[1]), grad, hyper, ctl, False, norm_weight)
+            if norm_weight == 0.0:
+                mirror.copy_(prm.data)
+            self.kernel_launches += 1
 
     def _swap_norms(self) -> None:
         self.norm2, self.norm2_next = self.norm2_next, self.norm2
@@ -967,6 +1009,9 @@ class FusedBatchTopKEngine:
             sd["theta_m"], sd["theta_v"] = self.theta_m, self.theta_v
         if self.model.skip_weight is not None:
             sd["skip_m"], sd["skip_v"] = self.skip_m, self.skip_v
+        for name in ("foff_m", "foff_v", "fsc_m", "fsc_v"):
+            if hasattr(self, name):
+                sd[name] = getattr(self, name)
         return sd
 
     def load_optimizer_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
@@ -984,7 +1029,18 @@ class FusedBatchTopKEngine:
             self.theta_v.copy_(sd["theta_v"])
         if "step_ctl" in sd:
             self.step_ctl.copy_(sd["step_ctl"].to(self.step_ctl.dtype))
+        for name in ("foff_m", "foff_v", "fsc_m", "fsc_v"):
+            if hasattr(self, name) and name in sd:
+                getattr(self, name).copy_(sd[name])
         self.invalidate_cached()
+
+    def refresh_affine(self) -> None:
+        """Re-reads the fp32 copies of the feature offset / scale after the parameters were changed from outside."""
+        if getattr(self, "affine", False):
+            if self.foff32 is not None:
+                self.foff32.copy_(self.model.feature_offset.data)
+            if self.fsc32 is not None:
+                self.fsc32.copy_(self.model.feature_scale.data)
 
     def invalidate_cached(self) -> None:
         """Forget everything derived from the parameters (after a checkpoint load or an external weight change)."""
@@ -992,3 +1048,4 @@ class FusedBatchTopKEngine:
         self._bias_sum_valid = False
         if self.fn == "jumprelu":
             self._theta_valid = False
+        self.refresh_affine()

@@ -517,3 +517,63 @@ def test_fused_auxiliary_term_matches_loss_manager_beyond_k_aux():
     for (name, p), (_, q) in zip(model.named_parameters(), twin.named_parameters()):
         diff = ((p.detach().float() - q.detach().float()).abs() > 0.008 * snap[name].abs() + 3e-4).float().mean().item()
         assert diff < 2e-2, (name, diff)
+
+
+@pytest.mark.parametrize("tying,fn", [("per_source", "batchtopk"), ("per_target", "batchtopk"), ("per_source", "relu")])
+def test_fused_feature_affine_of_tied_decoders_matches_autograd(tying, fn):
+    """Feature offset / scale of tied decoders on the fused step: loss, first moments of every parameter (gradients) and the
+    updated offset / scale against autograd on the entries that the engine selected."""
+    from crosslayer_coding_b200 import CLTConfig, CrossLayerTranscoder, TrainingConfig
+    from crosslayer_coding_b200.training.fused_engine import FusedBatchTopKEngine, engine_supports
+
+    torch.manual_seed(31)
+    dev = _dev()
+    L, B, d, F, k = 3, 192, 64, 256, 6
+    cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=fn, batchtopk_k=k, clt_dtype="bfloat16", decoder_tying=tying,
+                    enable_feature_offset=True, enable_feature_scale=True)
+    model = CrossLayerTranscoder(cfg, device=dev)
+    with torch.no_grad():
+        model.enc_weight.normal_(0, 1.0 / math.sqrt(d))
+        if fn == "relu":
+            model.enc_bias.fill_(-1.2)
+        for w in model.dec_weight:
+            w.uniform_(-0.05, 0.05)
+        model.feature_offset.copy_(torch.randn_like(model.feature_offset) * 0.2)
+        model.feature_scale.copy_(1.0 + torch.randn_like(model.feature_scale) * 0.2)
+    tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="bf16", sparsity_lambda=0.0,
+                        preactivation_coef=0.0, aux_loss_factor=0.0, optimizer="adamw")
+    assert engine_supports(cfg, tc, model) is None
+    eng = FusedBatchTopKEngine(model, tc, B)
+    ref = _fp32_copy(model)
+    snap = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+    X = torch.randn(L, B, d, device=dev).bfloat16()
+    Y = torch.randn(L, B, d, device=dev).bfloat16()
+    lr = 2e-2  # large enough to move a 16-bit scale near 1.0 by more than half an ulp
+    out = eng.train_step(X, Y, 0, lr)
+    torch.cuda.synchronize()
+    eng.check_status()
+    acts_k = eng.activations_dense()
+    x = {l: X[l].float() for l in range(L)}
+    pre = {l: torch.nn.functional.linear(x[l], ref.enc_weight[l], ref.enc_bias[l]) for l in range(L)}
+    acts = {l: (pre[l] + (eng.preact[l].float() - pre[l]).detach()) * (acts_k[l] != 0) for l in range(L)}
+    loss = sum(torch.nn.functional.mse_loss(ref.decode({s: acts[s] for s in range(t + 1)}, t), Y[t].float()) for t in range(L))
+    loss.backward()
+    assert abs(float(out.reconstruction) - float(loss)) < 3e-3 * float(loss), (float(out.reconstruction), float(loss))
+    for name, mom in (("feature_offset", eng.foff_m), ("feature_scale", eng.fsc_m)):
+        g_ref = dict(ref.named_parameters())[name].grad
+        g = mom / 0.1  # first moment after one step = (1 - beta1) * gradient
+        assert _rel_err(g, g_ref) < 0.03, (name, _rel_err(g, g_ref))
+    assert _rel_err(eng.enc_m / 0.1, ref.enc_weight.grad) < 0.03
+    for i, w in enumerate(ref.dec_weight):
+        assert _rel_err(eng.dec_m[i] / 0.1, w.grad) < 0.03, i
+    opt = torch.optim.AdamW(ref.parameters(), lr=lr)
+    opt.step()
+    for name in ("feature_offset", "feature_scale"):
+        new = dict(model.named_parameters())[name].detach().float()
+        want = dict(ref.named_parameters())[name].detach()
+        moved = want.bfloat16().float() != snap[name]  # updates that survive the rounding to the storage type
+        assert moved.float().mean().item() > 0.5
+        agree = (torch.sign(new - snap[name])[moved] == torch.sign(want - snap[name])[moved]).float().mean().item()
+        assert agree > 0.97, (name, agree)
+    # the copies that the kernels read follow the stored parameters
+    assert torch.equal(eng.foff32, model.feature_offset.data.float()) and torch.equal(eng.fsc32, model.feature_scale.data.float())
