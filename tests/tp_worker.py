@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--tying", default="none")
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--clip", type=float, default=0.0)
+    ap.add_argument("--affine", action="store_true", help="feature offset / scale of tied decoders")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -46,13 +47,20 @@ def main():
     L, d, F, B, k = 3, 64, args.features, 128, 8
     t16 = torch.float16 if args.dtype == "float16" else torch.bfloat16
     cfg = CLTConfig(num_features=F, num_layers=L, d_model=d, activation_fn=args.activation, batchtopk_k=k, topk_k=k, clt_dtype=args.dtype,
-                    jumprelu_threshold=0.25, decoder_tying=args.tying)
+                    jumprelu_threshold=0.25, decoder_tying=args.tying, enable_feature_offset=args.affine, enable_feature_scale=args.affine)
     full_state = build_full_state(cfg)
     if args.tying != "none":  # tied decoders start at zero; give them values so that the first steps have a signal
         gen = torch.Generator().manual_seed(99)
         for key in list(full_state):
             if key.startswith("decoder_module.decoders.") and key.endswith(".weight"):
                 full_state[key] = (torch.rand(full_state[key].shape, generator=gen) * 0.1 - 0.05).to(full_state[key].dtype)
+    if args.affine:
+        gen = torch.Generator().manual_seed(123)
+        for key in list(full_state):
+            if ".feature_offset." in key:
+                full_state[key] = (torch.randn(full_state[key].shape, generator=gen) * 0.2).to(full_state[key].dtype)
+            if ".feature_scale." in key:
+                full_state[key] = (1.0 + torch.randn(full_state[key].shape, generator=gen) * 0.2).to(full_state[key].dtype)
     model = CrossLayerTranscoder(cfg, process_group=group, device=dev)
     model.load_state_dict(slice_for_rank(full_state, rank, world, F) if world > 1 else full_state)
     tc = TrainingConfig(learning_rate=1e-3, training_steps=100, activation_path="unused", precision="fp16" if args.dtype == "float16" else "bf16",
