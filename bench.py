@@ -115,11 +115,14 @@ def parse_args():
 class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, active: bool = True):
         self.samples, self.reasons = [], set()
         self.max_mhz = None
         self._stop = threading.Event()
         self._thread = None
+        self.nv = None
+        if not active:
+            return
         try:
             import pynvml
 
@@ -275,7 +278,9 @@ def time_loop(fn, warmup: int, steps: int, world: int, local: int):
     for i in range(warmup):
         fn(i)
     sync_all(world)
-    sampler = ClockSampler(local)
+    # rank 0 samples its own GPU; NVML queries from every rank at once take the driver's lock often enough to show in a
+    # timed region of a few tens of milliseconds
+    sampler = ClockSampler(local, active=int(os.environ.get("RANK", "0")) == 0)
     sampler.start()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()

@@ -221,7 +221,8 @@ class CLTTrainer:
             self.engine = FusedBatchTopKEngine(self.model, tc, tc.train_batch_size_tokens, sigma_tg=sigma,
                                                symm=getattr(self, "_symm", None))
             logger.info("Rank %d: using the fused sm_100a step engine", self.rank)
-            self._restrict_target_staging()
+            if not getattr(self, "_probe_pending", False):
+                self._restrict_target_staging()  # while the first batch may still send the run to the autograd step, every row travels
             self._gate_staging()
             return
         if want == "fused":
@@ -342,8 +343,13 @@ class CLTTrainer:
         if bool(too_dense.item()):
             logger.info("Rank %d: %.0f active features per token on the first batch: using the autograd step", self.rank, float(per_token.item()))
             self.engine = None
+            stager = getattr(self.activation_store, "stager", None)
+            if stager is not None and hasattr(stager, "gate"):
+                stager.gate = None
             self._build_autograd_optimizer()
             self.n_forward_passes_since_fired = torch.zeros(self.clt_config.num_layers, self.model.valid_features, dtype=torch.long, device=self.device)
+        else:
+            self._restrict_target_staging()  # batches staged from here on carry the targets of the owned token rows only
 
     def _train_step_fused(self, inputs, targets, step: int, lr: float) -> Dict[str, torch.Tensor]:
         tc, eng = self.training_config, self.engine
