@@ -226,12 +226,14 @@ __global__ void __launch_bounds__(256) aux_residual_kernel(const float* __restri
                                                              const int* __restrict__ bias_row, const float* __restrict__ sigma,
                                                              t16* __restrict__ gs, t16* __restrict__ g_out, double* __restrict__ loss,
                                                              const int* __restrict__ nd, const float* __restrict__ ctl, int L, int B, int d,
-                                                             float factor) {
+                                                             float factor, int scale_g) {
   const int l = blockIdx.y;
   const bool live = nd[l] > 0;  // a layer without dead features has no auxiliary term
   const float scale = ctl != nullptr ? ctl[SC_LOSS_SCALE] : 1.f;
   const float inv_scale = 1.f / scale;
-  const float gcoef = 2.f * factor / (float(B) * float(d));
+  // dL/d recon is of the order 1e-8 per element at training sizes: below the smallest fp16 value.  With scale_g it is kept
+  // times the loss scale (like the main gradient seed) and the fp32 products are unscaled afterwards (unscale_kernel).
+  const float gcoef = 2.f * factor / (float(B) * float(d)) * (scale_g ? scale : 1.f);
   const int vec = d / 8;
   float sq = 0.f;
   for (long long i = blockIdx.x * 1LL * blockDim.x + threadIdx.x; i < 1LL * B * vec; i += 1LL * gridDim.x * blockDim.x) {
@@ -270,6 +272,20 @@ __global__ void __launch_bounds__(256) aux_residual_kernel(const float* __restri
     float tot = 0.f;
     for (int w = 0; w < 8; ++w) tot += red[w];
     if (tot != 0.f) atomicAdd(loss, double(tot) * double(factor) / (double(B) * double(d)));
+  }
+}
+
+// buf *= 1 / loss scale (gradients that were formed from a scaled 16-bit factor)
+__global__ void __launch_bounds__(256) unscale_kernel(float* __restrict__ buf, long long n, const float* __restrict__ ctl) {
+  const float inv = ctl[SC_INV_SCALE];
+  for (long long i = (blockIdx.x * 1LL * blockDim.x + threadIdx.x) * 4; i < n; i += 1LL * gridDim.x * blockDim.x * 4) {
+    if (i + 4 <= n) {
+      float4 v = *reinterpret_cast<float4*>(buf + i);
+      v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv;
+      *reinterpret_cast<float4*>(buf + i) = v;
+    } else {
+      for (long long j = i; j < n; ++j) buf[j] *= inv;
+    }
   }
 }
 
@@ -322,6 +338,15 @@ extern "C" int clt_aux_compact(const long long* dead_counter, long long window, 
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+extern "C" int clt_unscale(float* buf, long long n, const float* ctl, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (ctl == nullptr || (reinterpret_cast<uintptr_t>(buf) & 15) != 0) return -1;
+  const long long nv = (n + 3) / 4;
+  const int grid = int((nv + 255) / 256 < 148 * 16 ? (nv + 255) / 256 : 148 * 16);
+  unscale_kernel<<<grid, 256, 0, st>>>(buf, n, ctl);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 extern "C" int clt_scatter_add_rows(float* dst, float* dst_bias, const float* src, const float* src_bias, const int* extra_idx,
                                     long long n_dst_rows, int d, cudaStream_t st) {
   if (d % 4 != 0) return -1;
@@ -358,12 +383,12 @@ extern "C" int CLT_FN(clt_aux_gather_rows)(const CltAuxRowsArgs* a, const int* d
 
 extern "C" int CLT_FN(clt_aux_residual)(const float* recon, const void* bias, int bias_is_16, const int* bias_row, const float* sigma, void* gs,
                                         void* g_out, double* loss, const int* nd, const float* ctl, int L, int B, int d, float factor,
-                                        cudaStream_t st) {
+                                        int scale_g, cudaStream_t st) {
   if (d % 8 != 0) return -1;
   const long long n = 1LL * B * (d / 8);
   const int gx = int((n + 255) / 256 < 592 ? (n + 255) / 256 : 592);
   aux_residual_kernel<<<dim3(gx, L), 256, 0, st>>>(recon, bias, bias_is_16, bias_row, sigma, static_cast<t16*>(gs), static_cast<t16*>(g_out), loss,
-                                                   nd, ctl, L, B, d, factor);
+                                                   nd, ctl, L, B, d, factor, scale_g);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

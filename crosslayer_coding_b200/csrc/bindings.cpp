@@ -158,6 +158,7 @@ int clt_aux_compact(const long long* dead_counter, long long window, int L, int 
                     int* nd_all, int* extra_idx, cudaStream_t st);
 int clt_scatter_add_rows(float* dst, float* dst_bias, const float* src, const float* src_bias, const int* extra_idx, long long n_dst_rows, int d,
                          cudaStream_t st);
+int clt_unscale(float* buf, long long n, const float* ctl, cudaStream_t st);
 struct CltAuxRowsArgs {
   const void* w[32];
   int rows[32];
@@ -895,7 +896,7 @@ void aux_gather_rows(const std::vector<Tensor>& dec_w, const Tensor& dead_cols, 
 
 // r = recon + bias[bias_row[l]] - residual(gs); loss[0] += factor mean r^2; g = dL/d recon (16-bit); gs += the term's gradient through the residual
 void aux_residual(const Tensor& recon, const Tensor& bias, const Tensor& bias_row, const c10::optional<Tensor>& sigma, Tensor& gs, Tensor& g_out,
-                  Tensor& loss, const Tensor& nd, const c10::optional<Tensor>& ctl, double factor) {
+                  Tensor& loss, const Tensor& nd, const c10::optional<Tensor>& ctl, double factor, bool scale_g) {
   const bool half = is_half(gs, "gs");
   need(recon, at::kFloat, "recon"); need(gs, t16_of(half), "gs"); need(g_out, t16_of(half), "g_out"); need(loss, at::kDouble, "loss");
   need(bias_row, at::kInt, "bias_row"); need(nd, at::kInt, "nd");
@@ -904,8 +905,15 @@ void aux_residual(const Tensor& recon, const Tensor& bias, const Tensor& bias_ro
   c10::cuda::CUDAGuard guard(gs.device());
   check(CLT_PICK(half, clt_aux_residual)(recon.data_ptr<float>(), bias.data_ptr(), bias.scalar_type() == at::kFloat ? 0 : 1, bias_row.data_ptr<int>(),
                                          opt_ptr<float>(sigma), gs.data_ptr(), g_out.data_ptr(), loss.data_ptr<double>(), nd.data_ptr<int>(),
-                                         ctl_ptr(ctl), int(recon.size(0)), int(recon.size(1)), int(recon.size(2)), float(factor), cur_stream()),
+                                         ctl_ptr(ctl), int(recon.size(0)), int(recon.size(1)), int(recon.size(2)), float(factor), scale_g ? 1 : 0, cur_stream()),
         "aux_residual");
+}
+
+// buf *= 1 / loss scale (read from the step control block on the device)
+void unscale(Tensor& buf, const Tensor& ctl) {
+  need(buf, at::kFloat, "buf");
+  c10::cuda::CUDAGuard guard(buf.device());
+  check(clt_unscale(buf.data_ptr<float>(), buf.numel(), ctl_ptr(ctl), cur_stream()), "unscale");
 }
 
 // out[r] = sum of row r of the 16-bit matrix in [rows, n]
@@ -991,7 +999,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("aux_compact", &aux_compact);
   m.def("aux_gather_select", &aux_gather_select);
   m.def("aux_gather_rows", &aux_gather_rows);
-  m.def("aux_residual", &aux_residual);
+  m.def("aux_residual", &aux_residual, py::arg("recon"), py::arg("bias"), py::arg("bias_row"), py::arg("sigma"), py::arg("gs"), py::arg("g_out"),
+        py::arg("loss"), py::arg("nd"), py::arg("ctl"), py::arg("factor"), py::arg("scale_g") = false);
+  m.def("unscale", &unscale);
   m.def("rowsum16", &rowsum16);
   m.def("scatter_add_rows", &scatter_add_rows);
   m.def("normalize_cast", &normalize_cast, py::arg("inp"), py::arg("out"), py::arg("mean") = none, py::arg("inv_std") = none,

@@ -768,7 +768,9 @@ class FusedBatchTopKEngine:
         e.transpose16(b["W0"], b["W0T"])
         e.dense_gemm(b["A"], b["W0T"], b["recon"], off, segs, 1.0, self.status)            # recon = A W0
         b["loss"].zero_()
-        e.aux_residual(b["recon"], m.dec_bias.data, b["bias_row"], self.sigma, self.gs, b["g"], b["loss"], b["nd"], self.step_ctl, float(factor))
+        # fp16: dL/d recon (about 1e-8 per element) is kept times the loss scale, the fp32 gradient products are unscaled below
+        e.aux_residual(b["recon"], m.dec_bias.data, b["bias_row"], self.sigma, self.gs, b["g"], b["loss"], b["nd"], self.step_ctl, float(factor),
+                       self.fp16)
         e.dense_gemm(b["g"], b["W0"], b["G"], off, segs, 1.0, self.status)                 # G = g W0^T
         e.transpose16(b["A"], b["AT"])
         e.transpose16(b["G"], b["GT"], b["A"])   # straight-through: the gradient stays at the kept positions
@@ -778,6 +780,10 @@ class FusedBatchTopKEngine:
         e.dense_gemm(b["GT"], XT, b["dWenc"], off, segs, 1.0, self.status)                 # dW_enc = G^T x
         e.rowsum16(b["GT"], b["dbenc"])
         e.rowsum16(b["gT"], b["gsum"])
+        if self.fp16:
+            for name in ("dW0", "dWenc", "dbenc", "gsum"):
+                e.unscale(b[name], self.step_ctl)
+            self.kernel_launches += 4
         b["bias_grad"].zero_()
         b["bias_grad"].index_copy_(0, b["bias_row_long"], b["gsum"])
         self.kernel_launches += 16

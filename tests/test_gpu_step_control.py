@@ -465,14 +465,16 @@ def test_aux_compaction_and_per_token_selection(dtype):
     assert torch.equal(GT, Gp.transpose(1, 2).contiguous())
 
 
-def test_fused_auxiliary_term_matches_loss_manager_beyond_k_aux():
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_fused_auxiliary_term_matches_loss_manager_beyond_k_aux(dtype):
     """More dead features than k_aux = 512: the kernel path (selection + grouped GEMMs + compact extra rows) against
-    the PyTorch loss and one AdamW step; then the same step through the unfused per-layer path."""
+    the PyTorch loss and one AdamW step; then the same step through the unfused per-layer path.  In fp16 the gradient of
+    the auxiliary reconstruction travels times the loss scale and the fp32 products are unscaled on the device."""
     import copy
 
     from crosslayer_coding_b200.training.losses import LossManager
 
-    cfg, model, tc, eng, X, Y = _make(L=2, B=128, d=64, F=2048, k=16, seed=21)
+    cfg, model, tc, eng, X, Y = _make(L=2, B=128, d=64, F=2048, k=16, seed=21, dtype=dtype, loss_scale_init=4096.0)
     tc.aux_loss_factor = 0.25
     ref = _fp32_copy(model)
     twin = copy.deepcopy(model)
