@@ -99,6 +99,11 @@ def build_parser() -> argparse.ArgumentParser:
                    help="fused JumpReLU step: capacity of the active-entry lists per token")
     g.add_argument("--peer-health-timeout-s", type=float, default=None,
                    help="tensor-parallel runs: declare a rank lost when it has not announced the next step for this long")
+    g.add_argument("--async-checkpoint", action=argparse.BooleanOptionalAction, default=None,
+                   help="snapshot the state to pinned memory on a side stream and write checkpoints from a thread (default: on for CUDA runs)")
+    g.add_argument("--loss-scale-init", type=float, default=65536.0, help="fp16 on the fused step: initial dynamic loss scale")
+    g.add_argument("--loss-scale-growth-interval", type=int, default=2000,
+                   help="fp16 on the fused step: steps without overflow before the loss scale doubles")
     g.add_argument("--prefetch-batches", type=int, default=2)
     g.add_argument("--sampling-strategy", choices=["sequential", "random_chunk"], default="sequential")
     g = p.add_argument_group("Logging")
@@ -214,6 +219,8 @@ def configs_from_args(args):
         optimizer_states_dtype=getattr(args, "optimizer_states_dtype", "model_dtype"),
         fused_max_active_per_token=getattr(args, "fused_max_active_per_token", 1024),
         peer_health_timeout_s=getattr(args, "peer_health_timeout_s", None), prefetch_batches=getattr(args, "prefetch_batches", 2),
+        async_checkpoint=getattr(args, "async_checkpoint", None), loss_scale_init=getattr(args, "loss_scale_init", 65536.0),
+        loss_scale_growth_interval=getattr(args, "loss_scale_growth_interval", 2000),
     )
     return clt_config, training_config
 
