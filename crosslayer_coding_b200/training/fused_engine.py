@@ -703,17 +703,20 @@ class FusedBatchTopKEngine:
 
     AUX_MAX_CAP = 4096  # compact dead features per layer that the selection kernel ranks in shared memory
 
-    def set_dead_count_hint(self, max_dead_per_layer: int) -> None:
+    def set_dead_count_hint(self, max_dead_per_layer: int, max_dead_per_layer_all_ranks: Optional[int] = None) -> None:
         """Sizes the compact dead-feature set of the auxiliary term from an occasional host read of the counters
-        (the largest per-layer dead count).  The capacity carries 25 % head-room; a layer that outgrows it between
-        two hints uses its first ``capacity`` dead features until the next hint.  Counts beyond ``AUX_MAX_CAP`` take
-        the unfused path."""
+        (the largest per-layer dead count of this shard).  The capacity carries 25 % head-room; a layer that outgrows it
+        between two hints uses its first ``capacity`` dead features until the next hint.  Counts beyond ``AUX_MAX_CAP``
+        take the unfused path.  Under tensor parallelism the kernel path serves runs whose layers have at most ``k_aux``
+        (512) dead features over all ranks (``max_dead_per_layer_all_ranks``, the same number on every rank): then every
+        dead feature is kept and no selection has to be agreed across the shards."""
         n = int(max_dead_per_layer)
         self._aux_hint = n
         cap = -(-max(256, n + n // 4 + 64) // 256) * 256
         self._aux_cap_wanted = cap if n <= self.AUX_MAX_CAP else 0
         if self._aux_cap_wanted:
             self._aux_cap_wanted = min(self._aux_cap_wanted, self.AUX_MAX_CAP)
+        self._aux_global_hint = int(max_dead_per_layer_all_ranks) if max_dead_per_layer_all_ranks is not None else n
 
     def _aux_buffers(self, cap: int):
         b = getattr(self, "_aux_buf", None)
@@ -759,6 +762,10 @@ class FusedBatchTopKEngine:
         b = self._aux_buffers(cap)
         off, segs = b["layers"]
         e.aux_compact(counter, int(window), self.L, self.Fv, b["dead_cols"], b["nd"], b["nd_all"], b["extra_idx"])
+        live = b["nd"]  # layers with dead features (any rank) have an auxiliary term
+        if self.world > 1:
+            pops.all_reduce(b["nd_all"], group=self.group)  # dead features of the layer over all shards (device side, no host read)
+            live = b["nd_all"]
         # A = x W_dead^T on the gathered encoder rows, then bias + per-token top k_aux in place (cheaper than gathering
         # single 16-bit values out of the [B, F] pre-activation rows)
         e.aux_gather_rows([m.enc_weight.data[l].unsqueeze(1) for l in range(self.L)], b["dead_cols"], b["nd"], b["W0"])
@@ -767,9 +774,11 @@ class FusedBatchTopKEngine:
         e.aux_gather_rows([w.data for w in m.dec_weight][: self.L], b["dead_cols"], b["nd"], b["W0"])
         e.transpose16(b["W0"], b["W0T"])
         e.dense_gemm(b["A"], b["W0T"], b["recon"], off, segs, 1.0, self.status)            # recon = A W0
+        if self.world > 1:
+            pops.all_reduce(b["recon"], group=self.group)  # every rank goes on with the whole auxiliary reconstruction
         b["loss"].zero_()
         # fp16: dL/d recon (about 1e-8 per element) is kept times the loss scale, the fp32 gradient products are unscaled below
-        e.aux_residual(b["recon"], m.dec_bias.data, b["bias_row"], self.sigma, self.gs, b["g"], b["loss"], b["nd"], self.step_ctl, float(factor),
+        e.aux_residual(b["recon"], m.dec_bias.data, b["bias_row"], self.sigma, self.gs, b["g"], b["loss"], live, self.step_ctl, float(factor),
                        self.fp16)
         e.dense_gemm(b["g"], b["W0"], b["G"], off, segs, 1.0, self.status)                 # G = g W0^T
         e.transpose16(b["A"], b["AT"])
@@ -817,11 +826,18 @@ class FusedBatchTopKEngine:
         use_pre = abs(preactivation_coef) >= 1e-9
         use_aux = bool(aux_factor) and (dead_mask is not None or dead_window is not None)
         aux_cap = 0
-        if use_aux and self.world == 1:
-            if getattr(self, "_aux_cap_wanted", None) is None:
+        if use_aux:
+            if getattr(self, "_aux_cap_wanted", None) is None:  # first use without a hint: one host read (agreed over the ranks)
                 src = dead_mask if dead_mask is not None else (self.dead_counter.view(L, self.Fl)[:, : self.Fv] > int(dead_window))
-                self.set_dead_count_hint(int(src.sum(dim=1).max().item()))  # first use without a hint: one host read
+                counts = src.sum(dim=1).to(torch.int32)
+                local_max = counts.max().reshape(1)
+                if self.world > 1:
+                    pops.all_reduce(counts, group=self.group)
+                    pops.all_reduce(local_max, op=pops.MAX, group=self.group)
+                self.set_dead_count_hint(int(local_max.item()), int(counts.max().item()))
             aux_cap = self._aux_cap_wanted
+            if self.world > 1 and self._aux_global_hint > 512:
+                aux_cap = 0  # more dead features than k_aux: the per-token selection has to be agreed across the shards
         aux = None
         enc_x_idx = enc_x_rows = enc_x_bias = dec_x_idx = dec_x_rows = None
         # loss terms that only need the selection come first, so that their sums are there when the loss is settled

@@ -379,13 +379,15 @@ class CLTTrainer:
         slowly).  The answer is agreed over the process group (all-reduce MAX at the same steps on every rank):
         the auxiliary term runs collectives, so every rank has to take the same branch."""
         if not hasattr(self, "_dead_seen") or step % 100 == 0:
-            count = self.dead_neurons_mask.sum(dim=1).max().to(torch.int32).reshape(1)  # largest per-layer dead count
+            per_layer = self.dead_neurons_mask.sum(dim=1).to(torch.int32)
+            count = per_layer.max().reshape(1)  # largest per-layer dead count of any shard
             if self.world_size > 1:
                 pops.all_reduce(count, op=pops.MAX, group=self.process_group)
-            n = int(count.item())
-            self._dead_seen = n > 0
+                pops.all_reduce(per_layer, group=self.process_group)  # per layer over all shards
+            n, n_all = int(count.item()), int(per_layer.max().item())
+            self._dead_seen = n_all > 0
             if self.engine is not None:
-                self.engine.set_dead_count_hint(n)  # sizes the compact dead set of the fused auxiliary term
+                self.engine.set_dead_count_hint(n, n_all)  # sizes the compact dead set of the fused auxiliary term
         return self._dead_seen
 
     def _train_step_autograd(self, inputs, targets, step: int, lr: float) -> Dict[str, torch.Tensor]:

@@ -72,6 +72,8 @@ def test_tp_jumprelu_matches_single_gpu(tmp_path):
     (("--tying", "per_source"), "jumprelu", 0.02),                      # tied JumpReLU: threshold-gradient GEMM on the summed seed
     (("--tying", "per_target", "--clip", "0.05"), "batchtopk", 0.02),   # global-norm clipping: norm summed across ranks in the control kernel
     (("--tying", "per_source", "--affine"), "batchtopk", 0.0),           # feature offset / scale: sharded with the features
+    (("--dead",), "batchtopk", 0.0),                                      # auxiliary loss, dead features on one shard only / on all shards
+    (("--dead", "--aux-unfused"), "batchtopk", 0.0),                     # the same through the per-layer PyTorch form of the term
 ])
 def test_tp_variants_match_single_gpu(tmp_path, extra, activation, lam):
     if torch.cuda.device_count() < 2:

@@ -34,6 +34,8 @@ def main():
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--clip", type=float, default=0.0)
     ap.add_argument("--affine", action="store_true", help="feature offset / scale of tied decoders")
+    ap.add_argument("--dead", action="store_true", help="mark features dead (some on one shard only) and train with the auxiliary loss")
+    ap.add_argument("--aux-unfused", action="store_true", help="with --dead under tensor parallelism: take the per-layer PyTorch form of the term")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -87,8 +89,17 @@ def main():
         pairs = torch.cat(gathered_pairs)
     selection = sorted(map(tuple, pairs.tolist()))
     losses, entries, norms = [], [], []
+    extra = {}
+    if args.dead:
+        dead_full = torch.zeros(L, F, dtype=torch.bool)
+        dead_full[0, 3:40] = True       # on the first shard only
+        dead_full[2, ::5] = True        # spread over every shard
+        lo = model.feature_start
+        extra = dict(aux_factor=0.5, dead_mask=dead_full[:, lo:lo + model.valid_features].to(dev))
+        if args.aux_unfused and world > 1:
+            eng.set_dead_count_hint(int(extra["dead_mask"].sum(dim=1).max()), 10 ** 6)  # as if more than k_aux features were dead
     for step in range(args.steps):
-        out = eng.train_step(X, Y, step, 1e-3, sparsity_lambda=args.lam)
+        out = eng.train_step(X, Y, step, 1e-3, sparsity_lambda=args.lam, **extra)
         losses.append(float(out.total))
         norms.append(float(out.grad_norm))
         n = out.num_entries.clone().float()
