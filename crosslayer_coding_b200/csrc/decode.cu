@@ -221,7 +221,9 @@ struct DecodeBulkShared {
   float ent_a[kDecodeStages];
 };
 
-template <int TPG>
+// V: 8-element column chunks per thread (1 for d <= 1024, 2 up to d = 2048: chunk v of thread gt covers columns
+// (v * gthreads + gt) * 8 ...), so that the CTA stays at four groups of at most 128 threads plus the producer warp.
+template <int TPG, int V>
 __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, int gthreads, int stage_bytes, int nstages, int* status) {
   extern __shared__ __align__(128) uint8_t smem_raw_dec[];  // bulk copies need 16-byte alignment only
   uint8_t* ring = smem_raw_dec;
@@ -290,14 +292,18 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
   } else {
     const int g = threadIdx.x / gthreads;
     const int gt = threadIdx.x - g * gthreads;
-    const int e0 = gt * 8;
-    const bool active = e0 < d;
     const int lane = threadIdx.x & 31;
-    float acc[TPG][8];
+    int e0[V];
+    bool active[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) { e0[v] = (v * gthreads + gt) * 8; active[v] = e0[v] < d; }
+    float acc[TPG][V][8];
 #pragma unroll
     for (int j = 0; j < TPG; ++j)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+      for (int v = 0; v < V; ++v)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[j][v][i] = 0.f;
     int it = 0;
     bool ok = true;
     const int t_span = p.rows_limit > 0 ? p.rows_limit : kMaxLayers;
@@ -307,12 +313,17 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
       if (!mbar_wait(&sh->full[st], ph, abort_flag)) { ok = false; break; }
       const int sl = sh->ent_sl[st];
       const float a = sh->ent_a[st];
-      if (active && a != 0.f) {
-        const t16* rows = reinterpret_cast<const t16*>(ring + size_t(st) * stage_bytes) + e0;
+      if (a != 0.f) {
+        const t16* rows = reinterpret_cast<const t16*>(ring + size_t(st) * stage_bytes);
 #pragma unroll
         for (int j = 0; j < TPG; ++j) {
           const int t = g + (blockIdx.y * TPG + j) * kGroups;
-          if (t < L && t >= sl && t - sl < t_span) fma8(acc[j], a, *reinterpret_cast<const uint4*>(rows + (shared_row ? 0 : (t - sl) * d)));
+          if (t < L && t >= sl && t - sl < t_span) {
+            const t16* row = rows + (shared_row ? 0 : (t - sl) * d);
+#pragma unroll
+            for (int v = 0; v < V; ++v)
+              if (active[v]) fma8(acc[j][v], a, *reinterpret_cast<const uint4*>(row + e0[v]));
+          }
         }
       }
       __syncwarp();
@@ -323,7 +334,10 @@ __global__ void __launch_bounds__(544) decode_bulk_kernel(const DecodeParams p, 
     for (int j = 0; j < TPG; ++j) {
       const int t = g + (blockIdx.y * TPG + j) * kGroups;
       if (t >= L) continue;
-      float sq = (ok && active) ? decode_epilogue(p, tok, t, e0, acc[j], loss_scale) : 0.f;
+      float sq = 0.f;
+#pragma unroll
+      for (int v = 0; v < V; ++v)
+        if (ok && active[v]) sq += decode_epilogue(p, tok, t, e0[v], acc[j][v], loss_scale);
       if (p.mode == 1) {
         sq = warp_sum(sq);
         if (lane == 0) atomicAdd(&sh->sq_s[t], sq);
@@ -476,8 +490,8 @@ extern "C" int CLT_FN(clt_sparse_decode)(const CltDecodeArgs* a, cudaStream_t st
   for (int i = 0; i < 8; ++i) p.stage_peers[i] = static_cast<float*>(a->stage_peers[i]);
   p.rows_per_rank = a->rows_per_rank; p.rank = a->rank; p.world = a->world;
   p.ctl = a->ctl; p.rows_limit = a->rows_limit; p.dbg_status = a->status;
-  const int gthreads = ((a->d / 8 + 31) / 32) * 32;
-  const int threads = gthreads * kGroups;
+  int gthreads = ((a->d / 8 + 31) / 32) * 32;
+  int threads = gthreads * kGroups;
   if (threads > 1024) return -1;
   const int tpg = (a->L + kGroups - 1) / kGroups;  // targets per warp group
   int max_rows = 0;
@@ -488,24 +502,38 @@ extern "C" int CLT_FN(clt_sparse_decode)(const CltDecodeArgs* a, cudaStream_t st
   // CTA stay in the tens of kilobytes
   int nstages = 4;
   while (nstages < kDecodeStages && nstages * stage_bytes < 24 * 1024) nstages *= 2;
+  // long rows (d_model 2048 with many target layers): fewer, larger stages; two column chunks per thread
+  while (nstages > 2 && size_t(nstages) * stage_bytes + sizeof(DecodeBulkShared) + 256 > 200 * 1024) --nstages;
   const size_t smem = size_t(nstages) * stage_bytes + sizeof(DecodeBulkShared) + 256;
   const bool plain_tied = a->tying == 1 && a->feat_offset == nullptr && a->feat_scale == nullptr;
-  const bool bulk = (a->tying == 0 || plain_tied) && a->status != nullptr && tpg <= 4 && smem <= 200 * 1024 && threads + 32 <= 544;
+  const int vchunks = a->d > 1024 ? 2 : 1;
+  const int bulk_gthreads = vchunks == 2 ? ((a->d / 16 + 31) / 32) * 32 : gthreads;
+  const bool bulk = (a->tying == 0 || plain_tied) && a->status != nullptr && tpg <= 4 && smem <= 200 * 1024 && bulk_gthreads * kGroups + 32 <= 544;
   if (bulk) {
-    static size_t attr_set[5] = {0, 0, 0, 0, 0};
+    gthreads = bulk_gthreads;
+    threads = gthreads * kGroups;
+    static size_t attr_set[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
     auto launch = [&](auto kern) -> int {
-      if (attr_set[tpg] < smem) {
+      size_t& have = attr_set[tpg + 5 * (vchunks - 1)];
+      if (have < smem) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
-        attr_set[tpg] = smem;
+        have = smem;
       }
       kern<<<dim3(a->B, 1), threads + 32, smem, st>>>(p, gthreads, stage_bytes, nstages, a->status);
       return 0;
     };
     int rc = 0;
-    if (tpg <= 1) rc = launch(decode_bulk_kernel<1>);
-    else if (tpg == 2) rc = launch(decode_bulk_kernel<2>);
-    else if (tpg == 3) rc = launch(decode_bulk_kernel<3>);
-    else rc = launch(decode_bulk_kernel<4>);
+    if (vchunks == 1) {
+      if (tpg <= 1) rc = launch(decode_bulk_kernel<1, 1>);
+      else if (tpg == 2) rc = launch(decode_bulk_kernel<2, 1>);
+      else if (tpg == 3) rc = launch(decode_bulk_kernel<3, 1>);
+      else rc = launch(decode_bulk_kernel<4, 1>);
+    } else {
+      if (tpg <= 1) rc = launch(decode_bulk_kernel<1, 2>);
+      else if (tpg == 2) rc = launch(decode_bulk_kernel<2, 2>);
+      else if (tpg == 3) rc = launch(decode_bulk_kernel<3, 2>);
+      else rc = launch(decode_bulk_kernel<4, 2>);
+    }
     if (rc != 0) return rc;
   } else if (tpg <= 1) decode_kernel<1><<<dim3(a->B, 1), threads, 0, st>>>(p, gthreads);
   else if (tpg == 2) decode_kernel<2><<<dim3(a->B, 1), threads, 0, st>>>(p, gthreads);

@@ -385,6 +385,23 @@ def test_dead_counter_and_csr_consistency():
         assert torch.all(seg[1:] >= seg[:-1])
 
 
+@pytest.mark.parametrize("L,d", [(16, 2048), (6, 1536), (5, 2048)])
+def test_sparse_decode_wide_rows_take_the_bulk_ring(L, d):
+    """d_model above 1024: two column chunks per thread and a ring of fewer, larger stages (64 KB per stage at 16 layers x 2048)."""
+    cfg, model, tc, eng, X, Y = _engine_and_model(L=L, d=d, F=256, B=64, k=6, seed=5)
+    yhat = eng.forward(X, Y)
+    torch.cuda.synchronize()
+    eng.check_status()
+    acts = eng.activations_dense()
+    ref_model = _fp32_copy(model)
+    a = {l: acts[l] for l in range(L)}
+    for t in range(L):
+        ref = ref_model.decode({s: a[s] for s in range(t + 1)}, t)
+        assert torch.allclose(yhat[t], ref, atol=3e-3, rtol=3e-3), (t, (yhat[t] - ref).abs().max())
+    sq = torch.stack([((yhat[t] - Y[t].float()) ** 2).sum() for t in range(L)]).double()
+    assert torch.allclose(eng.sq_err, sq, rtol=1e-3)
+
+
 def test_decoder_norm2(ext):
     dev = _dev()
     w = torch.randn(40, 3, 64, device=dev).bfloat16()
