@@ -105,95 +105,116 @@ __device__ __forceinline__ int warp_find_bin_from_top(const unsigned int* hist, 
   return bin;
 }
 
-// One CTA (256 threads) per (token, layer).  A [L, B, nd_cap] 16-bit: the token's dead pre-activations, the top k_aux of
-// them (k_aux = min(k_aux_max, nd_all[l])) kept, the rest zero; columns >= nd[l] are zero.  Two sources:
+// bias_c[l][i] = encoder bias of dead column i of layer l (0 beyond nd[l]): gathered once per step, so that the selection
+// below reads it coalesced instead of chasing column index -> bias for every token.
+__global__ void __launch_bounds__(256) aux_gather_bias_kernel(const void* __restrict__ enc_bias, int bias_is_16, int F_pitch,
+                                                                const int* __restrict__ dead_cols, const int* __restrict__ nd, int nd_cap,
+                                                                float* __restrict__ bias_c) {
+  const int l = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nd_cap) return;
+  float v = 0.f;
+  if (i < nd[l]) {
+    const long long bi = 1LL * l * F_pitch + __ldg(dead_cols + 1LL * l * nd_cap + i);
+    v = bias_is_16 ? t16_to_float(static_cast<const t16*>(enc_bias)[bi]) : static_cast<const float*>(enc_bias)[bi];
+  }
+  bias_c[1LL * l * nd_cap + i] = v;
+}
+
+// One warp per (token, layer), eight of them per CTA, each with its own key array and histogram in shared memory (no CTA-wide
+// barrier anywhere).  A [L, B, nd_cap] 16-bit: the token's dead pre-activations, the top k_aux of them
+// (k_aux = min(k_aux_max, nd_all[l])) kept, the rest zero; columns >= nd[l] are zero.  Two sources:
 //   enc_bias == nullptr: the values are gathered from the stored pre-activations `pre` [L, B, ld] at the dead columns;
-//   enc_bias != nullptr: A already holds x W_dead^T (the encoder rows of the dead features, one GEMM for all layers); the
-//                        encoder bias of each dead column is added here and A is rewritten in place.
+//   bias_c != nullptr:   A already holds x W_dead^T (the encoder rows of the dead features, one GEMM for all layers); the
+//                        compact encoder bias bias_c [L, nd_cap] is added here and A is rewritten in place.
+// Dynamic shared memory: 8 * (nd_cap * 2 + 1024) bytes.
 __global__ void __launch_bounds__(256) aux_gather_select_kernel(const t16* __restrict__ pre, long long ld, long long layer_stride,
-                                                                  const void* __restrict__ enc_bias, int bias_is_16, int F_pitch,
+                                                                  const float* __restrict__ bias_c,
                                                                   const int* __restrict__ dead_cols, const int* __restrict__ nd,
                                                                   const int* __restrict__ nd_all, int nd_cap, int k_aux_max, int B,
                                                                   t16* __restrict__ A) {
-  __shared__ unsigned short keys[kAuxMaxCap];
-  __shared__ unsigned int hist[256];
-  __shared__ int sel_bin, sel_need;
-  __shared__ int warp_ties[8];
-  const int tok = blockIdx.x, l = blockIdx.y;
+  extern __shared__ __align__(16) uint8_t aux_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tok = blockIdx.x * 8 + warp, l = blockIdx.y;
+  if (tok >= B) return;  // whole warp
+  unsigned short* keys = reinterpret_cast<unsigned short*>(aux_smem + size_t(warp) * (size_t(nd_cap) * 2 + 1024));
+  unsigned int* hist = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(keys) + size_t(nd_cap) * 2);
   const int n = nd[l];
   const int k_aux = min(k_aux_max, nd_all[l]);
   t16* out = A + (1LL * l * B + tok) * nd_cap;
   unsigned short* obits = reinterpret_cast<unsigned short*>(out);
   const int* cols = dead_cols + 1LL * l * nd_cap;
-  if (enc_bias == nullptr) {
+  if (bias_c == nullptr) {
     const unsigned short* rbits = reinterpret_cast<const unsigned short*>(pre + 1LL * l * layer_stride + 1LL * tok * ld);
-    for (int i = threadIdx.x; i < nd_cap; i += 256) keys[i] = i < n ? rbits[__ldg(cols + i)] : (unsigned short)0;
+    for (int i = lane; i < nd_cap; i += 32) keys[i] = i < n ? rbits[__ldg(cols + i)] : (unsigned short)0;
   } else {
-    for (int i = threadIdx.x; i < nd_cap; i += 256) {
-      unsigned short v = 0;
+    // eight values per lane and step: one 16-byte load of the products, two of the bias
+    const float* bl = bias_c + 1LL * l * nd_cap;
+    for (int i8 = lane; i8 < nd_cap / 8; i8 += 32) {
+      const int i = i8 * 8;
+      uint4 q = make_uint4(0, 0, 0, 0);
       if (i < n) {
-        const long long bi = 1LL * l * F_pitch + __ldg(cols + i);
-        const float bv = bias_is_16 ? t16_to_float(static_cast<const t16*>(enc_bias)[bi]) : static_cast<const float*>(enc_bias)[bi];
-        const t16 r = float_to_t16(t16_to_float(out[i]) + bv);
-        v = *reinterpret_cast<const unsigned short*>(&r);
+        const uint4 pv = *reinterpret_cast<const uint4*>(out + i);
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(bl + i)), b1 = __ldg(reinterpret_cast<const float4*>(bl + i + 4));
+        const uint32_t pu[4] = {pv.x, pv.y, pv.z, pv.w};
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        uint32_t r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // columns at or beyond n hold zero products and zero bias: they stay zero
+          const float lo = i + 2 * j < n ? t16_lo(pu[j]) + bb[2 * j] : 0.f, hi = i + 2 * j + 1 < n ? t16_hi(pu[j]) + bb[2 * j + 1] : 0.f;
+          r[j] = pack_t16x2(lo, hi);
+        }
+        q = make_uint4(r[0], r[1], r[2], r[3]);
       }
-      keys[i] = v;
+      *reinterpret_cast<uint4*>(keys + i) = q;
     }
   }
-  __syncthreads();
-  if (n <= k_aux) {  // every dead feature is kept
-    for (int i = threadIdx.x; i < nd_cap; i += 256) obits[i] = keys[i];
-    return;
-  }
-  // exact k_aux-th largest of the n values: two radix rounds over the monotone 16-bit key
-  uint32_t prefix = 0;
-  int need = k_aux;
-  for (int round = 0; round < 2; ++round) {
-    const int shift = round == 0 ? 8 : 0;
-    hist[threadIdx.x] = 0;
-    __syncthreads();
-    for (int i = threadIdx.x; i < n; i += 256) {
-      const uint32_t k = key16(keys[i]);
-      if (round == 0 || (k >> 8) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
-    }
-    __syncthreads();
-    if (warp == 0) {
+  __syncwarp();
+  if (n > k_aux) {
+    // exact k_aux-th largest of the n values: two radix rounds over the monotone 16-bit key
+    uint32_t prefix = 0;
+    int need = k_aux;
+    for (int round = 0; round < 2; ++round) {
+      const int shift = round == 0 ? 8 : 0;
+      for (int i = lane; i < 256; i += 32) hist[i] = 0;
+      __syncwarp();
+      for (int i = lane; i < n; i += 32) {
+        const uint32_t k = key16(keys[i]);
+        if (round == 0 || (k >> 8) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
+      }
+      __syncwarp();
       int left;
       const int bin = warp_find_bin_from_top(hist, need, lane, &left);
-      if (lane == 0) { sel_bin = bin; sel_need = left; }
+      prefix = round == 0 ? uint32_t(bin) : ((prefix << 8) | uint32_t(bin));
+      need = left;
+      __syncwarp();
     }
-    __syncthreads();
-    prefix = round == 0 ? uint32_t(sel_bin) : ((prefix << 8) | uint32_t(sel_bin));
-    need = sel_need;
-    __syncthreads();
-  }
-  const uint32_t T = prefix;  // cut key; `need` of the values equal to it are kept, lowest index first
-  // ties: every thread owns a contiguous chunk of indices; exclusive scan of the per-chunk tie counts
-  const int chunk = (n + 255) / 256;
-  const int i0 = min(n, int(threadIdx.x) * chunk), i1 = min(n, i0 + chunk);
-  int ties = 0;
-  for (int i = i0; i < i1; ++i) ties += key16(keys[i]) == T;
-  int incl = ties;
+    const uint32_t T = prefix;  // cut key; `need` of the values equal to it are kept, lowest index first
+    // ties: every lane owns a contiguous chunk of indices; exclusive scan of the per-chunk tie counts
+    const int chunk = (n + 31) / 32;
+    const int i0 = min(n, lane * chunk), i1 = min(n, i0 + chunk);
+    int ties = 0;
+    for (int i = i0; i < i1; ++i) ties += key16(keys[i]) == T;
+    int incl = ties;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-    if (lane >= o) incl += t;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    int tie_rank = incl - ties;
+    for (int i = i0; i < i1; ++i) {
+      const uint32_t k = key16(keys[i]);
+      bool keep = k > T;
+      if (k == T) { keep = tie_rank < need; ++tie_rank; }
+      if (!keep) keys[i] = 0;
+    }
+    __syncwarp();
   }
-  if (lane == 31) warp_ties[warp] = incl;
-  __syncthreads();
-  int tie_rank = incl - ties;
-  for (int w = 0; w < warp; ++w) tie_rank += warp_ties[w];
-  __syncthreads();
-  // the kept flags go back into the key array (zero = dropped), then one coalesced pass writes the row
-  for (int i = i0; i < i1; ++i) {
-    const uint32_t k = key16(keys[i]);
-    bool keep = k > T;
-    if (k == T) { keep = tie_rank < need; ++tie_rank; }
-    if (!keep) keys[i] = 0;
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < nd_cap; i += 256) obits[i] = keys[i];
+  // one coalesced pass writes the row (16 bytes per lane and step; nd_cap is a multiple of 8)
+  const uint4* k4 = reinterpret_cast<const uint4*>(keys);
+  uint4* o4 = reinterpret_cast<uint4*>(obits);
+  for (int i = lane; i < nd_cap / 8; i += 32) o4[i] = k4[i];
 }
 
 // ------------------------------------------------------------------ same-layer decoder rows of the dead features
@@ -358,10 +379,20 @@ extern "C" int clt_scatter_add_rows(float* dst, float* dst_bias, const float* sr
 #endif
 
 extern "C" int CLT_FN(clt_aux_gather_select)(const void* pre, long long ld, long long layer_stride, const void* enc_bias, int bias_is_16,
-                                             int F_pitch, const int* dead_cols, const int* nd, const int* nd_all, int nd_cap, int k_aux_max,
-                                             int L, int B, void* A, cudaStream_t st) {
+                                             int F_pitch, float* bias_c, const int* dead_cols, const int* nd, const int* nd_all, int nd_cap,
+                                             int k_aux_max, int L, int B, void* A, cudaStream_t st) {
   if (nd_cap > kAuxMaxCap || nd_cap % 8 != 0 || (pre == nullptr) == (enc_bias == nullptr)) return -1;
-  aux_gather_select_kernel<<<dim3(B, L), 256, 0, st>>>(static_cast<const t16*>(pre), ld, layer_stride, enc_bias, bias_is_16, F_pitch, dead_cols,
+  if (enc_bias != nullptr) {
+    if (bias_c == nullptr) return -1;  // scratch [L, nd_cap] fp32 for the compact bias
+    aux_gather_bias_kernel<<<dim3((nd_cap + 255) / 256, L), 256, 0, st>>>(enc_bias, bias_is_16, F_pitch, dead_cols, nd, nd_cap, bias_c);
+  }
+  const size_t smem = 8 * (size_t(nd_cap) * 2 + 1024);
+  static size_t attr_smem = 0;
+  if (smem > 48 * 1024 && smem > attr_smem) {
+    if (cudaFuncSetAttribute(aux_gather_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -4;
+    attr_smem = smem;
+  }
+  aux_gather_select_kernel<<<dim3((B + 7) / 8, L), 256, smem, st>>>(static_cast<const t16*>(pre), ld, layer_stride, enc_bias != nullptr ? bias_c : nullptr, dead_cols,
                                                         nd, nd_all, nd_cap, k_aux_max, B, static_cast<t16*>(A));
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -856,7 +856,7 @@ void aux_compact(const Tensor& counter, int64_t window, int64_t L, int64_t f_val
 // stored pre-activations, gathered at the dead columns) or `enc_bias` [L, F] (A already holds x W_dead^T; the bias is added and
 // A is rewritten in place).
 void aux_gather_select(const OptTensor& pre, const OptTensor& enc_bias, const Tensor& dead_cols, const Tensor& nd, const Tensor& nd_all,
-                       int64_t k_aux_max, Tensor& A) {
+                       int64_t k_aux_max, Tensor& A, const OptTensor& bias_scratch) {
   const bool half = is_half(A, "A");
   need(A, t16_of(half), "A"); need(dead_cols, at::kInt, "dead_cols"); need(nd, at::kInt, "nd"); need(nd_all, at::kInt, "nd_all");
   const bool from_pre = pre.has_value() && pre->defined();
@@ -872,9 +872,11 @@ void aux_gather_select(const OptTensor& pre, const OptTensor& enc_bias, const Te
     TORCH_CHECK(enc_bias->is_cuda() && enc_bias->is_contiguous() && enc_bias->dim() == 2 && enc_bias->size(0) == A.size(0) &&
                 (enc_bias->scalar_type() == at::kFloat || enc_bias->scalar_type() == t16_of(half)), "enc_bias [L, F], fp32 or the 16-bit type");
     bias_p = enc_bias->data_ptr(); f_pitch = enc_bias->size(1); bias16 = enc_bias->scalar_type() == at::kFloat ? 0 : 1;
+    TORCH_CHECK(bias_scratch.has_value() && bias_scratch->defined() && bias_scratch->is_cuda() && bias_scratch->scalar_type() == at::kFloat &&
+                bias_scratch->is_contiguous() && bias_scratch->numel() >= A.size(0) * A.size(2), "bias_scratch: fp32 [L, nd_cap]");
   }
   c10::cuda::CUDAGuard guard(A.device());
-  check(CLT_PICK(half, clt_aux_gather_select)(pre_p, ld, stride, bias_p, bias16, int(f_pitch), dead_cols.data_ptr<int>(), nd.data_ptr<int>(),
+  check(CLT_PICK(half, clt_aux_gather_select)(pre_p, ld, stride, bias_p, bias16, int(f_pitch), opt_ptr<float>(bias_scratch), dead_cols.data_ptr<int>(), nd.data_ptr<int>(),
                                               nd_all.data_ptr<int>(), int(A.size(2)), int(k_aux_max), int(A.size(0)), int(A.size(1)), A.data_ptr(),
                                               cur_stream()), "aux_gather_select");
 }
@@ -997,7 +999,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("negative_indicator", &negative_indicator);
   m.def("scale_histogram", &scale_histogram);
   m.def("aux_compact", &aux_compact);
-  m.def("aux_gather_select", &aux_gather_select);
+  m.def("aux_gather_select", &aux_gather_select, py::arg("pre"), py::arg("enc_bias"), py::arg("dead_cols"), py::arg("nd"), py::arg("nd_all"),
+        py::arg("k_aux_max"), py::arg("A"), py::arg("bias_scratch") = none);
   m.def("aux_gather_rows", &aux_gather_rows);
   m.def("aux_residual", &aux_residual, py::arg("recon"), py::arg("bias"), py::arg("bias_row"), py::arg("sigma"), py::arg("gs"), py::arg("g_out"),
         py::arg("loss"), py::arg("nd"), py::arg("ctl"), py::arg("factor"), py::arg("scale_g") = false);

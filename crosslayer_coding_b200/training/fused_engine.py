@@ -742,6 +742,7 @@ class FusedBatchTopKEngine:
         b["dW0"] = torch.empty(L, cap, d, dtype=f32, device=dev)
         b["dWenc"] = torch.empty(L, cap, d, dtype=f32, device=dev)
         b["dbenc"] = torch.empty(L * cap, dtype=f32, device=dev)
+        b["bias_c"] = torch.empty(L, cap, dtype=f32, device=dev)
         b["gsum"] = torch.empty(L, d, dtype=f32, device=dev)
         b["loss"] = torch.zeros(1, dtype=torch.float64, device=dev)
         rows = [pair_index(l, l, L) if self.tying == 0 else l for l in range(L)]
@@ -770,7 +771,7 @@ class FusedBatchTopKEngine:
         # single 16-bit values out of the [B, F] pre-activation rows)
         e.aux_gather_rows([m.enc_weight.data[l].unsqueeze(1) for l in range(self.L)], b["dead_cols"], b["nd"], b["W0"])
         e.dense_gemm(X, b["W0"], b["A"], off, segs, 1.0, self.status)
-        e.aux_gather_select(None, m.enc_bias.data, b["dead_cols"], b["nd"], b["nd_all"], int(k_aux_default), b["A"])
+        e.aux_gather_select(None, m.enc_bias.data, b["dead_cols"], b["nd"], b["nd_all"], int(k_aux_default), b["A"], b["bias_c"])
         e.aux_gather_rows([w.data for w in m.dec_weight][: self.L], b["dead_cols"], b["nd"], b["W0"])
         e.transpose16(b["W0"], b["W0T"])
         e.dense_gemm(b["A"], b["W0T"], b["recon"], off, segs, 1.0, self.status)            # recon = A W0
@@ -795,7 +796,7 @@ class FusedBatchTopKEngine:
             self.kernel_launches += 4
         b["bias_grad"].zero_()
         b["bias_grad"].index_copy_(0, b["bias_row_long"], b["gsum"])
-        self.kernel_launches += 16
+        self.kernel_launches += 17
         return b
 
     # -------------------------------------------------------------------- step

@@ -439,7 +439,7 @@ def test_aux_compaction_and_per_token_selection(dtype):
     for l in range(L):
         cols = dead_cols[l, : int(nd[l])].long()
         A2[l, :, : len(cols)] = (pre[l][:, cols].float() - bias[l, cols]).to(dtype)
-    ext.aux_gather_select(None, bias, dead_cols, nd, nd_all, k_aux, A2)
+    ext.aux_gather_select(None, bias, dead_cols, nd, nd_all, k_aux, A2, torch.empty(L, cap, device=dev))
     assert torch.equal(A2, A)
     for l in range(L):
         n = int(nd[l])
