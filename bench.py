@@ -277,10 +277,11 @@ def time_loop(fn, warmup: int, steps: int, world: int, local: int):
 
     for i in range(warmup):
         fn(i)
-    sync_all(world)
     # rank 0 samples its own GPU; NVML queries from every rank at once take the driver's lock often enough to show in a
-    # timed region of a few tens of milliseconds
+    # timed region of a few tens of milliseconds.  NVML is initialised before the barrier: a rank that enters the timed
+    # region late keeps the others waiting at their first exchange.
     sampler = ClockSampler(local, active=int(os.environ.get("RANK", "0")) == 0)
+    sync_all(world)
     sampler.start()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
