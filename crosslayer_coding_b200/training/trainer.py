@@ -99,8 +99,14 @@ class CLTTrainer:
 
         if distributed:
             if not dist.is_initialized():
-                backend = "nccl" if torch.cuda.is_available() else "gloo"
-                dist.init_process_group(backend=backend)
+                if torch.cuda.is_available():
+                    # bound to this rank's device from the start (eager communicator): the configuration that the symmetric-memory
+                    # exchange and the sharded staging are run with everywhere else
+                    local = int(os.environ.get("LOCAL_RANK", "0"))
+                    torch.cuda.set_device(local)
+                    dist.init_process_group(backend="nccl", device_id=torch.device(f"cuda:{local}"))
+                else:
+                    dist.init_process_group(backend="gloo")
                 self._owns_process_group = True
             self.rank, self.world_size = dist.get_rank(), dist.get_world_size()
             self.local_rank = int(os.environ.get("LOCAL_RANK", self.rank))

@@ -110,3 +110,34 @@ def test_tp_token_topk_equals_single_gpu_selection(tmp_path, world, features):
         w = got["state"][key]
         bad = ((w - w_ref).abs() > 0.01 * w_ref.abs() + 4e-4).float().mean().item()
         assert bad < 5e-3, (key, bad)
+
+
+def test_tp_trainer_loop_with_owner_only_targets(tmp_path):
+    """CLTTrainer.train() on 2 GPUs with the fused engine: sharded staging where the targets stay with the token owners,
+    evaluation (which gathers the owners' rows again), asynchronous distributed checkpoints."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    if os.environ.get("CLT_RUN_UNVERIFIED", "") in ("", "0"):
+        # Its only run so far used a worker that kept using the process group after the trainer had destroyed it and ran into
+        # the time limit; the worker now owns the group, but the test has not completed once on a 2-GPU box since.
+        pytest.skip("not yet completed once on a 2-GPU box (set CLT_RUN_UNVERIFIED=1 to run it)")
+    import json
+
+    from crosslayer_coding_b200.activation_generation.synthetic import SyntheticSpec, write_synthetic_dataset
+
+    data = write_synthetic_dataset(str(tmp_path / "ds"), SyntheticSpec(num_layers=3, d_model=64, dict_size=256, active_mean=5, seed=0),
+                                   total_tokens=2048, chunk_tokens=512, dtype="bfloat16", device="cuda:0")
+    out = str(tmp_path / "out.json")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29691",
+           os.path.join(HERE, "tp_trainer_worker.py"), "--data", data, "--log-dir", str(tmp_path / "run"), "--out", out]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    got = json.load(open(out))
+    assert got["owner_only"], "the trainer did not restrict the staging of the targets"
+    assert got["targets_ok"], "evaluation would not see the same targets as an unsharded store"
+    assert got["recon"][-1] < got["recon"][0], got["recon"]
+    ev = got["eval"]
+    assert 0.0 < ev["reconstruction/normalized_mean_reconstruction_error"] < 1.5, ev
+    for want in ("clt_checkpoint_8", "latest", "final", "metrics.json"):
+        assert any(want in name for name in got["files"]), (want, got["files"])
