@@ -248,3 +248,21 @@ def test_row_sharded_assembly_fills_only_this_ranks_rows(dataset):
         part.close()
     assert torch.equal(got, want)
     full.close()
+
+
+def test_stager_options_are_inert_on_cpu():
+    """The staging options of tensor-parallel GPU runs (targets stay with the token owners, copies gated on an event of the
+    consumer's step) must not change anything on a CPU stager."""
+    import torch
+
+    from crosslayer_coding_b200.training.data.staging import DeviceStager
+
+    st = DeviceStager((2, 2, 8, 4), torch.float32, torch.device("cpu"), depth=3)
+    assert st.push_only_leading(2) is False and st.gate is None
+    st.gate = lambda: None
+    slot, host = st.host_slot()
+    host.copy_(torch.arange(128, dtype=torch.float32).view(2, 2, 8, 4))
+    st.submit(slot)
+    got = st.acquire(slot)
+    assert torch.equal(got, host)
+    st.release(slot)
