@@ -73,3 +73,24 @@ def test_scramble_compress_compare(workdir):
     assert np.array_equal(all_rows(comp, 4), a)
     out = _run("compare_norm_stats.py", os.path.join(data, "norm_stats.json"), os.path.join(scr, "norm_stats.json"), "--tolerance", "1e-9")
     assert "max_abs_diff" in out
+
+
+def test_two_rank_smoke_run_on_gloo(tmp_path):
+    """scripts/smoke_train.py under torch.distributed.run with two Gloo ranks: the whole tensor-parallel training loop
+    (sharded model, evaluation, distributed checkpoint with merge, final save) on the autograd step."""
+    import json
+    import subprocess
+    import sys
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CLT_SMOKE_DIR=str(tmp_path), CLT_SMOKE_STEPS="8", CLT_SMOKE_TOKENS="16384", MASTER_ADDR="127.0.0.1", CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29537", os.path.join(repo, "scripts", "smoke_train.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    run = os.path.join(str(tmp_path), "run")
+    names = set(os.listdir(run))
+    assert {"metrics.json", "cfg.json", "latest", "final"} <= names, sorted(names)
+    assert {"model.safetensors", "rank_0_model.safetensors", "rank_1_model.safetensors", "shard_meta.json"} <= set(os.listdir(os.path.join(run, "latest")))
+    metrics = json.load(open(os.path.join(run, "metrics.json")))
+    assert metrics["eval_metrics"] and all(v["total"] == v["total"] for v in metrics["train_losses"])
