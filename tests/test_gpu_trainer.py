@@ -8,7 +8,6 @@ import json
 import os
 
 import pytest
-import torch
 
 from crosslayer_coding_b200 import CLTConfig, TrainingConfig
 from crosslayer_coding_b200.activation_generation.synthetic import SyntheticSpec, write_synthetic_dataset
