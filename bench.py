@@ -8,6 +8,11 @@ batches, bf16) on N GPUs of one node, features tensor-parallel over the GPUs.
         bench.py --gpus 2 --steps 20 --warmup 5
     python bench.py --impl reference ...      # the unmodified reference from baseline/_ref, same config
 
+Variants of the same measurement: ``--shape pythia-70m|llama-3.2-1b``, ``--decoder-tying``, ``--precision fp16``, ``--activation
+jumprelu``, ``--dead-frac`` (AuxK in every step), ``--store local`` (HDF5 chunks on disk), ``--parity-steps`` (held-out normalised
+MSE after further training, optionally a fresh batch per step and a curve), ``--stochastic-rounding``; other measurements:
+``--mode inference|convert|decode-reduce``.
+
 Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, max over ranks) over steps whose inputs
 are already on the device; ``e2e`` is the same metric through the public trainer API with the per-step
 host->device copy of the batch from pinned memory and a device->host read of the loss inside the timed region.
