@@ -274,9 +274,9 @@ class CLTTrainer:
         r0, n = self._target_rows
         L, B, d = Y.shape
         own = Y[:, r0:r0 + n].contiguous()
-        out = torch.empty(self.world_size, L, n, d, dtype=Y.dtype, device=Y.device)
-        dist.all_gather_into_tensor(out, own, group=self.process_group)
-        return out.permute(1, 0, 2, 3).reshape(L, B, d).contiguous()
+        parts = [torch.empty_like(own) for _ in range(self.world_size)]
+        dist.all_gather(parts, own, group=self.process_group)  # list form: available on every backend
+        return torch.cat(parts, dim=1)[:, :B].contiguous()
 
     def _build_autograd_optimizer(self) -> None:
         tc = self.training_config

@@ -200,3 +200,29 @@ def test_standalone_parallel_linear_layers():
     x = torch.randn(2, 4)
     assert col(x).shape == (2, 10) and row(col(x)).shape == (2, 3) and col.local_features == 10
     mp.spawn(_layers_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def _full_targets_worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from types import SimpleNamespace
+
+        from crosslayer_coding_b200.training.trainer import CLTTrainer
+
+        L, B, d = 3, 8, 4
+        rows = B // world
+        truth = torch.arange(L * B * d, dtype=torch.float32).view(L, B, d)
+        mine = torch.full((L, B, d), -1.0)  # the rows of the other owners are stale on this rank
+        mine[:, rank * rows:(rank + 1) * rows] = truth[:, rank * rows:(rank + 1) * rows]
+        stub = SimpleNamespace(_target_rows=(rank * rows, rows), world_size=world, process_group=dist.group.WORLD)
+        assert torch.equal(CLTTrainer._full_targets(stub, mine), truth)
+        stub._target_rows = None  # without the restriction the tensor is passed through
+        assert CLTTrainer._full_targets(stub, mine) is mine
+    finally:
+        dist.destroy_process_group()
+
+
+def test_evaluation_reassembles_the_owners_target_rows():
+    """Tensor-parallel fused runs stage the targets of the owned token rows only; evaluation gathers them again."""
+    mp.spawn(_full_targets_worker, args=(2, _free_port()), nprocs=2, join=True)
