@@ -579,9 +579,12 @@ class CLTTrainer:
                         metrics.update(compute_sparsity_diagnostics(self.model, tc, acts))
         self.metric_logger.log_evaluation_metrics(step, metrics)
         if self.rank == 0:
+            from ..utils import format_elapsed_time
+
             logger.info(
-                "step %d: NMSE %.4f, EV %.4f, avg L0 %.1f, dead %d",
-                step, metrics.get("reconstruction/normalized_mean_reconstruction_error", float("nan")),
+                "step %d [%s]: NMSE %.4f, EV %.4f, avg L0 %.1f, dead %d",
+                step, format_elapsed_time(time.time() - self.start_time),
+                metrics.get("reconstruction/normalized_mean_reconstruction_error", float("nan")),
                 metrics.get("reconstruction/explained_variance", float("nan")), metrics.get("sparsity/avg_l0", float("nan")),
                 metrics.get("dead_features/total_eval", 0),
             )

@@ -125,3 +125,26 @@ def test_global_tokentopk_per_row_count():
     out = act.apply_global_tokentopk(pre, 3)
     per_row = sum((o != 0).sum(dim=1) for o in out.values())
     assert torch.equal(per_row, torch.full((10,), 3))
+
+
+def test_small_helpers_and_the_example_config():
+    import json
+    import os
+
+    import numpy as np
+    import torch
+
+    from crosslayer_coding_b200 import CLTConfig
+    from crosslayer_coding_b200.utils import format_elapsed_time, numpy_uint16_to_torch_bfloat16, torch_bfloat16_to_numpy_uint16
+
+    assert format_elapsed_time(59.9) == "00:59" and format_elapsed_time(3725) == "01:02:05" and format_elapsed_time(90000) == "25:00:00"
+    x = torch.tensor([[1.0, -2.5, 3.140625], [0.0, 65280.0, -0.0078125]]).bfloat16()
+    bits = torch_bfloat16_to_numpy_uint16(x)
+    assert bits.dtype == np.uint16 and bits.shape == (2, 3)
+    assert bits[0, 0] == 0x3F80 and bits[0, 1] == 0xC020  # 1.0 and -2.5 as bf16 bit patterns
+    assert torch.equal(numpy_uint16_to_torch_bfloat16(bits), x)
+    with pytest.raises(TypeError):
+        torch_bfloat16_to_numpy_uint16(torch.zeros(2))
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = CLTConfig(**json.load(open(os.path.join(repo, "example_clt_config_gpt2_local.json"))))
+    assert cfg.num_layers == 12 and cfg.activation_fn == "batchtopk" and cfg.batchtopk_k == 200
